@@ -1,0 +1,219 @@
+"""GPT-J: parallel attention+MLP residual, interleaved rotary embedding on the first ``rotary_dim`` dims.
+
+Semantics follow the eager model of the reference (oslo/models/gptj/modeling_gptj.py: block
+:306-320, rotary :49-77, attention :151-191, loss :749-768) with the fused-path scale bug fixed:
+scores are always multiplied by ``1/sqrt(head_dim)``.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+import torch.nn as nn
+from torch import Tensor
+
+from ... import ops
+from ...fused_kernels_utils import ACT2FN, GELU_TANH_NAMES
+from ...modeling_utils import PretrainedConfig, PreTrainedModel
+from ...parallel.layers import Embedding, LayerNorm, Linear
+from ...parallel.mpu import Layer, LayerPolicy
+from ..common import (AttentionCore, CausalLMHeadMixin, DecoderBackbone, SequenceClassificationMixin,
+                      maybe_dropout, merge_heads, split_heads)
+
+
+class GPTJConfig(PretrainedConfig):
+    model_type = "gptj"
+    attribute_map = {"max_position_embeddings": "n_positions", "hidden_size": "n_embd",
+                     "num_attention_heads": "n_head", "num_hidden_layers": "n_layer"}
+
+    def __init__(self, vocab_size=50400, n_positions=2048, n_embd=4096, n_layer=28, n_head=16, rotary_dim=64,
+                 n_inner=None, activation_function="gelu_new", resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0,
+                 layer_norm_epsilon=1e-5, initializer_range=0.02, scale_attn_weights=True, use_cache=True,
+                 bos_token_id=50256, eos_token_id=50256, tie_word_embeddings=False, **kwargs):
+        self.vocab_size, self.n_positions, self.n_embd, self.n_layer, self.n_head = vocab_size, n_positions, n_embd, n_layer, n_head
+        self.n_inner, self.rotary_dim, self.activation_function = n_inner, rotary_dim, activation_function
+        self.resid_pdrop, self.embd_pdrop, self.attn_pdrop = resid_pdrop, embd_pdrop, attn_pdrop
+        self.layer_norm_epsilon, self.initializer_range, self.scale_attn_weights = layer_norm_epsilon, initializer_range, scale_attn_weights
+        super().__init__(use_cache=use_cache, bos_token_id=bos_token_id, eos_token_id=eos_token_id,
+                         tie_word_embeddings=tie_word_embeddings, **kwargs)
+
+
+class GPTJAttention(AttentionCore):
+    def __init__(self, config: GPTJConfig) -> None:
+        super().__init__()
+        self.embed_dim = config.n_embd
+        self.num_attention_heads = config.n_head
+        self.head_dim = self.embed_dim // self.num_attention_heads
+        if self.head_dim * self.num_attention_heads != self.embed_dim:
+            raise ValueError("n_embd must be divisible by n_head")
+        self.scale = 1.0 / math.sqrt(self.head_dim)
+        self.rotary_dim = config.rotary_dim
+        self.attn_pdrop, self.resid_pdrop = config.attn_pdrop, config.resid_pdrop
+        self.k_proj = Linear(self.embed_dim, self.embed_dim, bias=False)
+        self.v_proj = Linear(self.embed_dim, self.embed_dim, bias=False)
+        self.q_proj = Linear(self.embed_dim, self.embed_dim, bias=False)
+        self.out_proj = Linear(self.embed_dim, self.embed_dim, bias=False)
+
+    def forward(self, hidden_states: Tensor, layer_past=None, attention_mask=None, position_ids=None,
+                head_mask=None, use_cache=False, output_attentions=False, cache=None, layer_id=0):
+        b, s, _ = hidden_states.shape
+        nh, hd = self.num_attention_heads, self.head_dim
+        q = self.q_proj(hidden_states).view(b, s, nh, hd)
+        k = self.k_proj(hidden_states).view(b, s, nh, hd)
+        v = self.v_proj(hidden_states).view(b, s, nh, hd)
+        rd = self.rotary_dim if self.rotary_dim is not None else hd
+        rot = ops.rotary_interleaved if self.fused else ops.reference.rotary_interleaved
+        q, k = rot(q, position_ids, rd), rot(k, position_ids, rd)
+        q, k, v = (t.permute(0, 2, 1, 3) for t in (q, k, v))
+        out, present, probs = self.attend_with_cache(q, k, v, layer_past, cache, layer_id, attention_mask,
+                                                     use_cache, output_attentions, head_mask)
+        out = self.out_proj(merge_heads(out))
+        return maybe_dropout(out, self.resid_pdrop, self.training), present, probs
+
+
+class FusedGPTJAttention(GPTJAttention):
+    fused = True
+
+
+class GPTJMLP(nn.Module):
+    fused = False
+
+    def __init__(self, intermediate_size: int, config: GPTJConfig) -> None:
+        super().__init__()
+        self.fc_in = Linear(config.n_embd, intermediate_size)
+        self.fc_out = Linear(intermediate_size, config.n_embd)
+        self.activation = config.activation_function
+        self.resid_pdrop = config.resid_pdrop
+
+    def forward(self, x: Tensor) -> Tensor:
+        if self.fused and self.activation in GELU_TANH_NAMES:
+            h = self.fc_in(x, activation="gelu_new")
+        else:
+            h = ACT2FN[self.activation](self.fc_in(x))
+        return maybe_dropout(self.fc_out(h), self.resid_pdrop, self.training)
+
+
+class FusedGPTJMLP(GPTJMLP):
+    fused = True
+
+
+class GPTJBlock(nn.Module):
+    def __init__(self, config: GPTJConfig) -> None:
+        super().__init__()
+        inner = config.n_inner if config.n_inner is not None else 4 * config.n_embd
+        self.ln_1 = LayerNorm(config.n_embd, eps=config.layer_norm_epsilon)
+        self.attn = GPTJAttention(config)
+        self.mlp = GPTJMLP(inner, config)
+
+    def forward(self, hidden_states: Tensor, **kw):
+        x = self.ln_1(hidden_states)
+        a, present, probs = self.attn(x, **kw)
+        m = self.mlp(x)
+        return a + m + hidden_states, present, probs
+
+
+class GPTJPreTrainedModel(PreTrainedModel):
+    config_class = GPTJConfig
+    base_model_prefix = "transformer"
+
+    def get_layer_policies(self):
+        return [GPTJLayerPolicy]
+
+
+class GPTJModel(DecoderBackbone, GPTJPreTrainedModel):
+    def __init__(self, config: GPTJConfig) -> None:
+        super().__init__(config)
+        self.embed_dim = config.n_embd
+        self.wte = Embedding(config.vocab_size, self.embed_dim)
+        self.embd_pdrop = config.embd_pdrop
+        self.h = nn.ModuleList([GPTJBlock(config) for _ in range(config.n_layer)])
+        self.ln_f = LayerNorm(self.embed_dim, eps=config.layer_norm_epsilon)
+        self.post_init()
+
+    def embed(self, input_ids, position_ids, token_type_ids, inputs_embeds):
+        hs = self.wte(input_ids) if inputs_embeds is None else inputs_embeds
+        if token_type_ids is not None:
+            hs = hs + self.wte(token_type_ids)
+        return maybe_dropout(hs, self.embd_pdrop, self.training)
+
+
+class GPTJForCausalLM(CausalLMHeadMixin, GPTJPreTrainedModel):
+    _keys_to_ignore_on_load_missing = [r"attn.masked_bias", r"attn.bias"]
+
+    def __init__(self, config: GPTJConfig) -> None:
+        super().__init__(config)
+        self.transformer = GPTJModel(config)
+        self.lm_head = Linear(config.n_embd, config.vocab_size)
+        self.post_init()
+
+    def get_head_layers(self) -> List[Layer]:
+        # vocabulary-sharded head (the reference keeps it whole on every rank,
+        # oslo/models/gptj/modeling_gptj.py:734-742); split checkpoints still store it whole.
+        return [Layer(module=self.lm_head, weight=self.lm_head.weight, bias=self.lm_head.bias,
+                      replace={Linear: "vocab_head"}, parallel=True, gather_output=True)]
+
+
+class GPTJForSequenceClassification(SequenceClassificationMixin, GPTJPreTrainedModel):
+    def __init__(self, config: GPTJConfig) -> None:
+        super().__init__(config)
+        self.num_labels = config.num_labels
+        self.transformer = GPTJModel(config)
+        self.score = Linear(config.n_embd, self.num_labels, bias=False)
+        self.post_init()
+
+    def get_head_layers(self) -> List[Layer]:
+        return [Layer(module=self.score, weight=self.score.weight, parallel=False)]
+
+
+class GPTJLayerPolicy(LayerPolicy):
+    @staticmethod
+    def reduce_arguments(layer, world_size, config):
+        layer.attn.embed_dim = config.n_embd // world_size
+        layer.attn.num_attention_heads = config.n_head // world_size
+
+    @staticmethod
+    def fused_modules():
+        return {GPTJAttention: FusedGPTJAttention, GPTJMLP: FusedGPTJMLP}
+
+    @staticmethod
+    def attn_qkv(layer, config):
+        return [Layer(module=m, weight=m.weight, bias=None, replace={Linear: "column"})
+                for m in (layer.attn.q_proj, layer.attn.k_proj, layer.attn.v_proj)]
+
+    @staticmethod
+    def attn_out(layer, config):
+        m = layer.attn.out_proj
+        return [Layer(module=m, weight=m.weight, bias=None, replace={Linear: "row"})]
+
+    @staticmethod
+    def attn_norm(layer, config):
+        return [Layer(module=layer.ln_1, weight=layer.ln_1.weight, bias=layer.ln_1.bias, parallel=False)]
+
+    @staticmethod
+    def mlp_in(layer, config):
+        m = layer.mlp.fc_in
+        return [Layer(module=m, weight=m.weight, bias=m.bias, replace={Linear: "column"})]
+
+    @staticmethod
+    def mlp_out(layer, config):
+        m = layer.mlp.fc_out
+        return [Layer(module=m, weight=m.weight, bias=m.bias, replace={Linear: "row"})]
+
+    @staticmethod
+    def word_embedding(model, config):
+        wte = model.base_model.wte
+        return [Layer(module=wte, weight=wte.weight, replace={Embedding: "vocab_embedding"})]
+
+    @staticmethod
+    def block_layers(model, config):
+        return list(model.base_model.h)
+
+    @staticmethod
+    def postblock_layers(model, config):
+        ln = model.base_model.ln_f
+        return [Layer(module=ln, weight=ln.weight, bias=ln.bias, parallel=False)]
+
+    @staticmethod
+    def original_layer_class():
+        return GPTJBlock

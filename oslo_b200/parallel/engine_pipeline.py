@@ -1,0 +1,433 @@
+"""Pipeline-parallel engine: contiguous stage partition and a true 1F1B micro-batch schedule
+behind the generator API of the reference.
+
+User contract (reference: oslo/parallelism/engine_pipeline.py:262-303, :597-738): ``model(**batch)``
+takes keyword arguments only and returns a generator with one output per micro-batch, the same
+count on every stage; ``output.loss.backward()`` (or any wrapper that ends in autograd, such as a
+grad scaler) must be called inside the loop.
+
+What differs from the reference: its schedule runs one micro-batch through all stages, ring-sends the
+full output (logits included) back to every stage, and only then starts the next one, so stages
+never overlap. Here stage ``s`` runs ``P-1-s`` forwards ahead before yielding, then alternates one
+forward with the backward the user triggers (1F1B). Only the ``[mb, S, H]`` activation and its
+gradient cross stage boundaries (every stage slices the batch itself; shapes are known to both
+sides so no metadata is exchanged); activations and gradients travel on two separate process
+groups so the opposite directions never queue behind each other. Non-last stages yield a proxy
+loss: an autograd node whose backward receives the gradient (and the loss value) from the next
+stage, so plain autograd drives the whole chain.
+"""
+from __future__ import annotations
+
+import logging
+from typing import Any, Callable, Dict, Iterator, List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+from torch import Tensor
+
+from .mpu import MPU
+
+logger = logging.getLogger(__name__)
+
+
+def one_f_one_b_order(num_stages: int, stage: int, num_micro: int) -> List[str]:
+    """The sequence of ``F<i>`` / ``B<i>`` actions stage ``stage`` executes in one step (pure function)."""
+    warm = min(num_stages - 1 - stage, num_micro)
+    order = [f"F{i}" for i in range(warm)]
+    done = warm
+    for i in range(num_micro):
+        if done < num_micro:
+            order.append(f"F{done}")
+            done += 1
+        order.append(f"B{i}")
+    return order
+
+
+class MicroLossTensor(torch.Tensor):
+    """Marker subclass for the loss yielded on stages that do not own the model head.
+
+    Its value is filled in when the gradient message of that micro-batch arrives; ``backward``
+    is ordinary autograd (the proxy node does the receive).
+    """
+
+    @staticmethod
+    def wrap(t: Tensor) -> "MicroLossTensor":
+        return t.as_subclass(MicroLossTensor)
+
+
+class _ProxyLoss(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, stage_out: Tensor, engine: "PipelineParallelEngine", mb: int):
+        ctx.engine, ctx.mb = engine, mb
+        ctx.shape, ctx.dtype = stage_out.shape, stage_out.dtype
+        return stage_out.new_zeros((), dtype=torch.float32)
+
+    @staticmethod
+    def backward(ctx, _g):
+        eng: PipelineParallelEngine = ctx.engine
+        grad = eng._recv_grad(ctx.mb, ctx.shape, ctx.dtype)
+        return grad, None, None
+
+
+class P2PCommunicator:
+    """Fixed-shape tensor exchange between neighbouring stages.
+
+    The reference ships whole Python dicts element by element with a type-tagged protocol
+    (oslo/parallelism/engine_pipeline.py:741-1199); here both sides derive shape and dtype
+    from their own copy of the batch, so a message is exactly one tensor.
+    """
+
+    def __init__(self, mpu: MPU) -> None:
+        self.mpu = mpu
+        ranks = mpu.get_pipeline_parallel_global_ranks()
+        self.fwd_group = self.bwd_group = None
+        # every rank creates every group (collective call), two per pipeline group
+        for rs in mpu.get_pipeline_parallel_global_ranks_across_all_groups():
+            f = dist.new_group(ranks=rs, backend=mpu.backend)
+            b = dist.new_group(ranks=rs, backend=mpu.backend)
+            if rs == ranks:
+                self.fwd_group, self.bwd_group = f, b
+
+    def _rank(self, stage: int) -> int:
+        return self.mpu.stage_to_global_rank(stage)
+
+    def send_forward(self, t: Tensor, dst_stage: int):
+        return dist.isend(t.contiguous(), dst=self._rank(dst_stage), group=self.fwd_group)
+
+    def recv_forward(self, t: Tensor, src_stage: int):
+        return dist.irecv(t, src=self._rank(src_stage), group=self.fwd_group)
+
+    def send_backward(self, t: Tensor, dst_stage: int):
+        return dist.isend(t.contiguous(), dst=self._rank(dst_stage), group=self.bwd_group)
+
+    def recv_backward(self, t: Tensor, src_stage: int):
+        return dist.irecv(t, src=self._rank(src_stage), group=self.bwd_group)
+
+
+class _StageModule(nn.ModuleList):
+    """This rank's modules; calling it runs the pipeline generator (what DDP / ZeRO wrappers call)."""
+
+    def forward(self, *args, **kwargs):
+        return self._engine_forward(*args, **kwargs)
+
+
+class PipelineParallelEngine:
+    def __init__(self, model: nn.Module, mpu: MPU, micro_batch_size: int = 1, device=None) -> None:
+        self.model, self.mpu = model, mpu
+        self.micro_batch_size = int(micro_batch_size)
+        self.device = device or mpu.device
+        self.pp = mpu.get_pipeline_parallel_world_size()
+        self.stage = mpu.get_pipeline_parallel_rank()
+        self.first, self.last = self.stage == 0, self.stage == self.pp - 1
+        self._owned_ids: set = set()
+        self._owned_params: set = set()
+        self._key_stage: Dict[str, int] = {}
+        self.block_range = (0, 0)
+        self.stage_module: Optional[_StageModule] = None
+        self.p2p: Optional[P2PCommunicator] = None
+        self._grad_hooks_cb: List[Callable[[], None]] = []
+        self.on_last_backward: Optional[Callable[[bool], None]] = None
+
+    # ------------------------------------------------------------------ partition
+    def _stage_modules(self, stage: int) -> List[nn.Module]:
+        model, cfg = self.model, self.model.config
+        L = model.num_blocks()
+        bounds = self.mpu.make_pipeline_partition(L, self.pp)
+        mods: List[nn.Module] = []
+        for policy in model.get_layer_policies():
+            blocks = policy.block_layers(model, cfg)
+            if stage == 0:
+                mods += [l.module for l in policy.word_embedding(model, cfg) + policy.preblock_layers(model, cfg)]
+            mods += blocks[bounds[stage]:bounds[stage + 1]]
+            if stage == self.pp - 1:
+                mods += [l.module for l in policy.postblock_layers(model, cfg)]
+        if stage == self.pp - 1:
+            mods += [l.module for l in model.get_head_layers() if l.module is not None]
+        return mods
+
+    def assign_stages(self) -> None:
+        L = self.model.num_blocks()
+        if L < self.pp:
+            raise ValueError(f"{L} blocks cannot be split over {self.pp} pipeline stages")
+        bounds = self.mpu.make_pipeline_partition(L, self.pp)
+        self.block_range = (bounds[self.stage], bounds[self.stage + 1])
+        names = {}
+        for n, p in self.model.named_parameters(remove_duplicate=False):
+            names.setdefault(id(p), []).append(n)
+        for n, b in self.model.named_buffers(remove_duplicate=False):
+            names.setdefault(id(b), []).append(n)
+        for s in range(self.pp):
+            for m in self._stage_modules(s):
+                for sub in m.modules():
+                    if s == self.stage:
+                        self._owned_ids.add(id(sub))
+                for t in list(m.parameters()) + list(m.buffers()):
+                    if s == self.stage:
+                        self._owned_params.add(id(t))
+                    for n in names.get(id(t), []):
+                        self._key_stage.setdefault(n, s)
+        self._owned_modules = self._stage_modules(self.stage)
+        self._owned_keys = {n for tid in self._owned_params for n in names.get(tid, [])}
+
+    def owns(self, module: nn.Module) -> bool:
+        return self.pp == 1 or id(module) in self._owned_ids
+
+    def owns_key(self, key: str) -> bool:
+        return self.pp == 1 or key in self._owned_keys
+
+    def finalize(self) -> None:
+        model = self.model
+        for t in list(model.parameters()) + list(model.buffers()):
+            if self.pp == 1 or id(t) in self._owned_params:
+                if t.device != self.device:
+                    t.data = t.data.to(self.device)
+            else:
+                t.data = torch.empty(0, dtype=t.dtype, device=self.device)
+                if isinstance(t, nn.Parameter):
+                    t.requires_grad_(False)
+        if self.pp == 1:
+            return
+        self.p2p = P2PCommunicator(self.mpu)
+        sm = _StageModule(self._owned_modules)
+        sm._engine_forward = self.forward
+        self.stage_module = sm
+        # keep the engine and the stage list out of state_dict / module registration
+        object.__setattr__(model, "_pipe_engine", self)
+        object.__setattr__(model, "_orig_forward", model.forward)
+        object.__setattr__(model, "forward", self.forward)
+
+    # ------------------------------------------------------------------ batch handling
+    def _split_batches(self, kwargs: Dict[str, Any]) -> List[Dict[str, Any]]:
+        bsz = None
+        for v in kwargs.values():
+            if torch.is_tensor(v) and v.dim() >= 1:
+                bsz = v.size(0)
+                break
+        if bsz is None:
+            raise ValueError("no batched tensor found in the inputs")
+        mbs = max(1, min(self.micro_batch_size, bsz))
+        if bsz % mbs:
+            raise ValueError(f"batch size {bsz} is not divisible by micro_batch_size {mbs}")
+        n = bsz // mbs
+        out = [dict() for _ in range(n)]
+        for k, v in kwargs.items():
+            if torch.is_tensor(v) and v.dim() >= 1 and v.size(0) == bsz:
+                for i, c in enumerate(torch.chunk(v, n, dim=0)):
+                    out[i][k] = c.to(self.device, non_blocking=True)
+            else:
+                for i in range(n):
+                    out[i][k] = v
+        return out
+
+    def _hidden_shape(self, kw: Dict[str, Any]):
+        ref = kw.get("input_ids")
+        if ref is None:
+            ref = kw.get("inputs_embeds")
+        b = ref.numel() // ref.size(-1) if kw.get("input_ids") is not None else ref.size(0)
+        s = ref.size(-1) if kw.get("input_ids") is not None else ref.size(1)
+        cfg = self.model.config
+        h = getattr(cfg, "n_embd", None) or cfg.hidden_size
+        return (b, s, h)
+
+    # ------------------------------------------------------------------ stage execution
+    def _run_stage(self, mb_kw: Dict[str, Any], hidden: Optional[Tensor]) -> Dict[str, Any]:
+        model = self.model
+        if self.first:
+            kw = model.preblock_fn(**mb_kw)
+        else:
+            kw = model.base_model.prepare_fn(**mb_kw)
+            kw["hidden_states"] = hidden
+        for i in range(*self.block_range):
+            kw = model.block_fn(layer_id=i, **kw)
+        if self.last:
+            kw = model.postblock_fn(**kw)
+            kw = model.head_fn(**kw)
+            kw = model.loss_fn(**kw)
+        return kw
+
+    def _recv_grad(self, mb: int, shape, dtype) -> Tensor:
+        g = torch.empty(shape, dtype=dtype, device=self.device)
+        lossv = torch.empty(1, dtype=torch.float32, device=self.device)
+        w1 = self.p2p.recv_backward(g, self.stage + 1)
+        w2 = self.p2p.recv_backward(lossv, self.stage + 1)
+        w1.wait()
+        w2.wait()
+        proxy = self._proxies.pop(mb, None)
+        if proxy is not None:
+            proxy.data.copy_(lossv[0])
+        self._loss_values[mb] = lossv
+        return g
+
+    def _make_input_hook(self, mb: int):
+        def hook(grad: Tensor):
+            lossv = self._loss_values.pop(mb, None)
+            if lossv is None:
+                lossv = torch.zeros(1, dtype=torch.float32, device=self.device)
+            self._pending.append(self.p2p.send_backward(grad, self.stage - 1))
+            self._pending.append(self.p2p.send_backward(lossv, self.stage - 1))
+            return grad
+        return hook
+
+    def forward(self, *args, **kwargs) -> Iterator[Any]:
+        if args:
+            raise ValueError("pipeline-parallel models take keyword arguments only, e.g. model(**batch)")
+        return self._generator(kwargs)
+
+    def _generator(self, kwargs: Dict[str, Any]) -> Iterator[Any]:
+        batches = self._split_batches(kwargs)
+        m = len(batches)
+        train = torch.is_grad_enabled()
+        self._pending: List[Any] = []
+        self._proxies: Dict[int, Tensor] = {}
+        self._loss_values: Dict[int, Tensor] = {}
+        model = self.model
+        dtype = model.dtype
+        outputs: Dict[int, Any] = {}
+        recv_buf: Dict[int, Any] = {}
+
+        def post_recv(j: int) -> None:
+            if self.first or j >= m or j in recv_buf:
+                return
+            buf = torch.empty(self._hidden_shape(batches[j]), dtype=dtype, device=self.device)
+            recv_buf[j] = (buf, self.p2p.recv_forward(buf, self.stage - 1))
+
+        def do_forward(j: int) -> None:
+            hidden = None
+            if not self.first:
+                post_recv(j)
+                hidden, work = recv_buf.pop(j)
+                work.wait()
+                post_recv(j + 1)
+                if train:
+                    hidden.requires_grad_(True)
+                    hidden.register_hook(self._make_input_hook(j))
+            kw = self._run_stage(batches[j], hidden)
+            if not self.last:
+                hs = kw["hidden_states"]
+                self._pending.append(self.p2p.send_forward(hs.detach(), self.stage + 1))
+                if train:
+                    proxy = MicroLossTensor.wrap(_ProxyLoss.apply(hs, self, j))
+                    self._proxies[j] = proxy
+                    kw["loss"] = proxy
+                kw.setdefault("logits", None)
+                kw.setdefault("loss", None)
+                outputs[j] = self._organize_partial(kw)
+            else:
+                if train and kw.get("loss") is not None and not self.first:
+                    self._loss_values[j] = kw["loss"].detach().float().reshape(1)
+                outputs[j] = model.organize_fn(**kw)
+
+        if not train:
+            for j in range(m):
+                do_forward(j)
+                yield self._broadcast_output(outputs.pop(j))
+            self._flush()
+            return
+
+        warm = min(self.pp - 1 - self.stage, m)
+        done = 0
+        for _ in range(warm):
+            do_forward(done)
+            done += 1
+        for i in range(m):
+            if done < m:
+                do_forward(done)
+                done += 1
+            if i == m - 1 and self.on_last_backward is not None:
+                self.on_last_backward(True)
+            yield outputs.pop(i)
+        self._flush()
+        self._allreduce_tied_embedding()
+
+    def _organize_partial(self, kw: Dict[str, Any]):
+        """Output object of a stage that has no head: same type as the last stage's, loss = proxy."""
+        kw = dict(kw)
+        for k in ("all_hidden_states", "all_attentions"):
+            kw.setdefault(k, None)
+        kw.setdefault("return_dict", True)
+        try:
+            return self.model.organize_fn(**kw)
+        except Exception:  # head-specific fields missing on this stage
+            from ..modeling_utils import ModelOutput
+            return ModelOutput(loss=kw.get("loss"))
+
+    def _flush(self) -> None:
+        for w in self._pending:
+            w.wait()
+        self._pending = []
+
+    # ------------------------------------------------------------------ collectives around the schedule
+    def _broadcast_output(self, out):
+        """Inference: every stage returns what the last stage computed (tensors only; caches stay local)."""
+        group = self.mpu.get_pipeline_parallel_group()
+        src = self.mpu.stage_to_global_rank(self.pp - 1)
+        if self.last:
+            items = [(k, tuple(v.shape), v.dtype) for k, v in out.items() if torch.is_tensor(v)]
+            meta = [items, type(out)]
+        else:
+            meta = [None, None]
+        dist.broadcast_object_list(meta, src=src, group=group)
+        items, cls = meta
+        res = out if self.last else cls()
+        for k, shape, dt in items:
+            t = out[k].contiguous() if self.last else torch.empty(shape, dtype=dt, device=self.device)
+            dist.broadcast(t, src=src, group=group)
+            if not self.last:
+                res[k] = t
+        if not self.last and hasattr(out, "get") and out.get("past_key_values") is not None:
+            res["past_key_values"] = out["past_key_values"]
+        return res
+
+    def _allreduce_tied_embedding(self) -> None:
+        """Sum the gradients of an embedding shared by the first and the last stage
+        (reference: oslo/parallelism/engine_pipeline.py:439-451)."""
+        model = self.model
+        if not (self.first or self.last) or self.pp == 1:
+            return
+        if not getattr(model.config, "tie_word_embeddings", True) or model.get_output_embeddings() is None:
+            return
+        w = model.get_input_embeddings().weight
+        if w.grad is None:
+            w.grad = torch.zeros_like(w)
+        dist.all_reduce(w.grad, group=self.mpu.get_embedding_tied_group())
+
+
+class PipelineDeparallelEngine:
+    """Collect every stage's tensors onto all ranks of a pipeline group (cold path, per-tensor broadcast)."""
+
+    def __init__(self, model: nn.Module, mpu: MPU) -> None:
+        self.model, self.mpu = model, mpu
+
+    def gather_state(self, state: Dict[str, Tensor]) -> Dict[str, Tensor]:
+        pp = self.mpu.get_pipeline_parallel_world_size()
+        if pp == 1:
+            return dict(state)
+        eng: PipelineParallelEngine = self.model._pipe_engine
+        group = self.mpu.get_pipeline_parallel_group()
+        out: Dict[str, Tensor] = {}
+        for key in sorted(state.keys()):
+            stage = eng._key_stage.get(key, 0)
+            src = self.mpu.stage_to_global_rank(stage)
+            mine = self.mpu.get_pipeline_parallel_rank() == stage
+            meta = [(tuple(state[key].shape), state[key].dtype) if mine else None]
+            dist.broadcast_object_list(meta, src=src, group=group)
+            shape, dt = meta[0]
+            t = state[key].detach().to(self.mpu.device).contiguous() if mine else \
+                torch.empty(shape, dtype=dt, device=self.mpu.device)
+            dist.broadcast(t, src=src, group=group)
+            out[key] = t
+        return out
+
+    def deparallelize(self) -> nn.Module:
+        full = self.gather_state(self.model.state_dict())
+        named = dict(self.model.named_parameters(remove_duplicate=False))
+        named.update(dict(self.model.named_buffers(remove_duplicate=False)))
+        for k, t in full.items():
+            if k in named:
+                named[k].data = t
+                if isinstance(named[k], nn.Parameter):
+                    named[k].requires_grad_(True)
+        if hasattr(self.model, "_orig_forward"):
+            object.__setattr__(self.model, "forward", self.model._orig_forward)
+        return self.model

@@ -1,0 +1,157 @@
+"""Building-block modules: plain and tensor-parallel linear / embedding / norm layers.
+
+Every module carries ``oslo_fused``: ``False`` runs library PyTorch ops (the state before
+``model.fuse()``), ``True`` runs the sm_100a kernels of ``oslo_b200.ops``. The tensor-parallel
+classes are installed by swapping ``module.__class__`` after the weights were sliced, so
+``state_dict`` keys never change (reference: oslo/modeling_utils.py:15-104,
+oslo/parallelism/engine_tensor.py:439-446).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch import Tensor
+
+from .. import ops
+from .mpu import ceil_split_sizes
+
+
+def _linear(x: Tensor, weight: Tensor, bias: Optional[Tensor], reversed: bool, fused: bool,
+            activation: Optional[str] = None) -> Tensor:
+    if fused:
+        return ops.linear(x, weight, bias, reversed, activation)
+    return ops.reference.linear(x, weight, bias, reversed, activation)
+
+
+class Linear(nn.Linear):
+    """``nn.Linear`` (weight ``[out, in]``) with an optional fused activation epilogue."""
+
+    oslo_fused = False
+    reversed = False
+
+    def forward(self, x: Tensor, activation: Optional[str] = None) -> Tensor:
+        return _linear(x, self.weight, self.bias, False, self.oslo_fused, activation)
+
+
+class Conv1D(nn.Module):
+    """GPT-2 style projection with weight stored ``[in, out]``."""
+
+    oslo_fused = False
+    reversed = True
+
+    def __init__(self, nf: int, nx: int) -> None:
+        super().__init__()
+        self.nf = nf
+        self.weight = nn.Parameter(torch.empty(nx, nf))
+        self.bias = nn.Parameter(torch.zeros(nf))
+        nn.init.normal_(self.weight, std=0.02)
+
+    @property
+    def in_features(self) -> int:
+        return self.weight.size(0)
+
+    @property
+    def out_features(self) -> int:
+        return self.weight.size(1)
+
+    def forward(self, x: Tensor, activation: Optional[str] = None) -> Tensor:
+        return _linear(x, self.weight, self.bias, True, self.oslo_fused, activation)
+
+
+class LayerNorm(nn.LayerNorm):
+    oslo_fused = False
+
+    def forward(self, x: Tensor) -> Tensor:
+        if self.oslo_fused:
+            return ops.layer_norm(x, self.weight, self.bias, self.eps)
+        return F.layer_norm(x, self.normalized_shape, self.weight, self.bias, self.eps)
+
+
+class Embedding(nn.Embedding):
+    oslo_fused = False
+
+
+class VocabParallelEmbedding(nn.Embedding):
+    """Embedding whose rows are split over the tensor-parallel group (``torch.chunk`` row ranges).
+
+    Ids outside this rank's range contribute zero rows; the all-reduce over the group restores
+    the full lookup (reference: oslo/modeling_utils.py:15-64).
+    """
+
+    oslo_fused = False
+    mpu = None
+    full_num_embeddings: Optional[int] = None
+
+    def vocab_range(self):
+        total = self.full_num_embeddings or self.num_embeddings * self.mpu.tp
+        sizes = ceil_split_sizes(total, self.mpu.tp)
+        start = sum(sizes[: self.mpu.tp_rank])
+        return start, start + sizes[self.mpu.tp_rank]
+
+    def forward(self, ids: Tensor) -> Tensor:
+        if self.mpu is None or self.mpu.tp == 1:
+            return F.embedding(ids, self.weight, self.padding_idx)
+        lo, hi = self.vocab_range()
+        outside = (ids < lo) | (ids >= hi)
+        local = (ids - lo).masked_fill(outside, 0)
+        out = F.embedding(local, self.weight)
+        out = out.masked_fill(outside.unsqueeze(-1), 0.0)
+        return self.mpu.reduce(out)
+
+
+class ColumnParallelLinear(nn.Linear):
+    """Linear layer whose output features are split over the tensor-parallel group.
+
+    forward: ``broadcast`` (identity / all-reduce in backward) -> GEMM -> optional gather -> bias.
+    With ``parallel=False`` and a ``tied_embedding`` it is the tied LM head of a vocab-parallel
+    embedding: the local product yields a vocabulary shard (reference: oslo/modeling_utils.py:67-84).
+    """
+
+    oslo_fused = False
+    mpu = None
+    reversed = False
+    gather_output = False
+    sequence_parallel = False
+    full_out_features: Optional[int] = None
+
+    def forward(self, x: Tensor, activation: Optional[str] = None) -> Tensor:
+        mpu = self.mpu
+        if mpu is not None:
+            x = mpu.gather_sequence(x, dim=-2) if self.sequence_parallel else mpu.broadcast(x)
+        if self.gather_output and mpu is not None and mpu.tp > 1:
+            y = _linear(x, self.weight, None, self.reversed, self.oslo_fused)
+            y = mpu.gather(y, dim=-1, full_size=self.full_out_features)
+            if self.bias is not None:
+                y = y + self.bias
+            if activation is not None:
+                y = ops.bias_gelu(y, None)
+            return y
+        return _linear(x, self.weight, self.bias, self.reversed, self.oslo_fused, activation)
+
+
+class RowParallelLinear(nn.Linear):
+    """Linear layer whose input features are split over the tensor-parallel group.
+
+    forward: optional scatter -> GEMM -> all-reduce (or reduce-scatter along the sequence) -> bias.
+    The bias is kept whole and added once, after the reduction (reference: oslo/modeling_utils.py:87-104).
+    """
+
+    oslo_fused = False
+    mpu = None
+    reversed = False
+    input_is_parallel = True
+    sequence_parallel = False
+
+    def forward(self, x: Tensor, activation: Optional[str] = None) -> Tensor:
+        mpu = self.mpu
+        if mpu is not None and not self.input_is_parallel:
+            x = mpu.scatter(x, dim=-1)
+        y = _linear(x, self.weight, None, self.reversed, self.oslo_fused)
+        if mpu is not None:
+            y = mpu.reduce_scatter_sequence(y, dim=-2) if self.sequence_parallel else mpu.reduce(y)
+        if self.bias is not None:
+            y = y + self.bias
+        return y

@@ -1,0 +1,67 @@
+"""Single-process model numerics against the Hugging Face implementations (same weights, CPU fp32)."""
+import pytest
+import torch
+
+import oslo_b200 as ob
+
+transformers = pytest.importorskip("transformers")
+
+
+def _pair(kind):
+    torch.manual_seed(0)
+    if kind == "gpt2":
+        cfg = ob.GPT2Config(vocab_size=97, n_positions=32, n_embd=48, n_layer=2, n_head=4,
+                            resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+        ours = ob.GPT2LMHeadModel(cfg)
+        hf_cfg = transformers.GPT2Config(vocab_size=97, n_positions=32, n_embd=48, n_layer=2, n_head=4,
+                                         resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+        hf = transformers.GPT2LMHeadModel(hf_cfg)
+    elif kind == "gpt_neo":
+        cfg = ob.GPTNeoConfig(vocab_size=97, max_position_embeddings=32, hidden_size=48, num_layers=2, num_heads=4,
+                              window_size=4, attention_types=[[["global", "local"], 1]])
+        ours = ob.GPTNeoForCausalLM(cfg)
+        hf_cfg = transformers.GPTNeoConfig(vocab_size=97, max_position_embeddings=32, hidden_size=48, num_layers=2,
+                                           num_heads=4, window_size=4, attention_types=[[["global", "local"], 1]])
+        hf = transformers.GPTNeoForCausalLM(hf_cfg)
+    else:
+        cfg = ob.GPTJConfig(vocab_size=97, n_positions=32, n_embd=48, n_layer=2, n_head=4, rotary_dim=8)
+        ours = ob.GPTJForCausalLM(cfg)
+        hf_cfg = transformers.GPTJConfig(vocab_size=97, n_positions=32, n_embd=48, n_layer=2, n_head=4, rotary_dim=8,
+                                         resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+        hf = transformers.GPTJForCausalLM(hf_cfg)
+    missing, unexpected = hf.load_state_dict(ours.state_dict(), strict=False)
+    missing = [k for k in missing if not k.endswith((".attn.bias", ".attn.masked_bias", "attention.bias", "attention.masked_bias"))]
+    assert not missing and not unexpected, (missing, unexpected)
+    return ours.eval(), hf.eval()
+
+
+@pytest.mark.parametrize("kind", ["gpt2", "gpt_neo", "gptj"])
+def test_logits_and_loss_match_hf(kind):
+    ours, hf = _pair(kind)
+    x = torch.randint(0, 97, (2, 12))
+    with torch.no_grad():
+        a = ours(input_ids=x, labels=x)
+        b = hf(input_ids=x, labels=x)
+    assert torch.allclose(a.logits, b.logits, atol=2e-4, rtol=1e-4)
+    assert torch.allclose(a.loss, b.loss, atol=1e-5)
+
+
+@pytest.mark.parametrize("kind", ["gpt2", "gpt_neo", "gptj"])
+def test_greedy_generate_matches_hf(kind):
+    ours, hf = _pair(kind)
+    x = torch.randint(0, 97, (2, 5))
+    a = ours.generate(x, max_length=14, eos_token_id=None, pad_token_id=0)
+    b = hf.generate(x, max_length=14, do_sample=False, eos_token_id=None, pad_token_id=0)
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("kind", ["gpt2", "gptj"])
+def test_fused_loss_without_logits(kind):
+    ours, _ = _pair(kind)
+    x = torch.randint(0, 97, (2, 12))
+    with torch.no_grad():
+        a = ours(input_ids=x, labels=x)
+        ours.fuse()
+        b = ours(input_ids=x, labels=x, output_logits=False)
+    assert b.logits is None
+    assert torch.allclose(a.loss, b.loss, atol=1e-5)
