@@ -332,11 +332,8 @@ class CausalLMHeadMixin:
         if want_logits:
             if vocab_sharded:
                 x = mpu.broadcast(hs)
-                local = ops.linear(x, head.weight, None) if head.oslo_fused else F.linear(x, head.weight)
-                logits = mpu.gather(local, dim=-1, full_size=head.full_out_features)
-                if head.bias is not None:
-                    logits = logits + _full_bias(head, mpu)
-                kw["logits"] = logits
+                local = ops.linear(x, head.weight, head.bias) if head.oslo_fused else F.linear(x, head.weight, head.bias)
+                kw["logits"] = mpu.gather(local, dim=-1, full_size=head.full_out_features)
             else:
                 kw["logits"] = head(hs)
             return kw
@@ -395,10 +392,6 @@ class CausalLMHeadMixin:
         if isinstance(past, StaticKVCache):
             return past.reorder(beam_idx)
         return tuple(tuple(t.index_select(0, beam_idx.to(t.device)) for t in layer) for layer in past)
-
-
-def _full_bias(head, mpu) -> Tensor:
-    return mpu._gather(head.bias, dim=0, full_size=head.full_out_features)
 
 
 class SequenceClassificationMixin:

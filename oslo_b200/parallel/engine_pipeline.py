@@ -173,6 +173,9 @@ class PipelineParallelEngine:
     def owns(self, module: nn.Module) -> bool:
         return self.pp == 1 or id(module) in self._owned_ids
 
+    def owns_param(self, t: Tensor) -> bool:
+        return self.pp == 1 or id(t) in self._owned_params
+
     def owns_key(self, key: str) -> bool:
         return self.pp == 1 or key in self._owned_keys
 

@@ -66,10 +66,12 @@ def unshard_tensors(shards: List[Tensor], dim: int, n_fused: int = 1) -> Tensor:
 
 
 class TensorParallelEngine:
-    def __init__(self, model: nn.Module, mpu: MPU, owned: Optional[Callable[[nn.Module], bool]] = None,
+    def __init__(self, model: nn.Module, mpu: MPU, owned: Optional[Callable[[Tensor], bool]] = None,
                  device=None, sequence_parallel: bool = False) -> None:
         self.model, self.mpu = model, mpu
-        self.owned = owned or (lambda m: True)
+        # ``owned(param)``: does this rank's pipeline stage hold the parameter (tied weights may be
+        # held by a stage that does not own the module they are declared in)
+        self.owned = owned or (lambda p: True)
         self.device = device
         self.sequence_parallel = sequence_parallel
         self.tp, self.rank = mpu.get_tensor_parallel_world_size(), mpu.get_tensor_parallel_rank()
@@ -118,7 +120,7 @@ class TensorParallelEngine:
         if p is None:
             return
         self._record(p, ShardSpec(kind, dim, n_fused, p.size(dim) if p.numel() else -1))
-        if self.owned(module) and p.numel():
+        if self.owned(p) and p.numel():
             p.data = shard_tensor(p.data, self.tp, self.rank, dim, n_fused)
 
     def _column(self, layer: Layer) -> None:
@@ -151,7 +153,7 @@ class TensorParallelEngine:
         m.__class__ = VocabParallelEmbedding
         m.mpu = self.mpu
         m.full_num_embeddings = full
-        m.num_embeddings = layer.weight.size(0) if self.owned(m) else ceil_split_sizes(full, self.tp)[self.rank]
+        m.num_embeddings = ceil_split_sizes(full, self.tp)[self.rank]
 
     def _head(self, layer: Layer) -> None:
         m = layer.module

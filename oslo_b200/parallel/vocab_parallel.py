@@ -1,0 +1,133 @@
+"""LM-head projection fused with softmax cross-entropy, optionally over a vocabulary-sharded head.
+
+The ``[tokens, vocab]`` logits are produced ``chunk_rows`` rows at a time and reduced to three
+numbers per row (max, sum of exponentials, target logit). With a sharded vocabulary those are
+combined over the tensor-parallel group (MAX / SUM / SUM all-reduces of ``[rows]`` vectors), so no
+rank ever holds or gathers full logits - the reference all-gathers ``[B, S, V]`` instead
+(oslo/parallelism/mpu.py:759, oslo/models/gpt2/modeling_gpt2.py:983-1019). The backward recomputes
+each chunk of logits, forms ``softmax - onehot`` in place and feeds the two gradient GEMMs.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+from .mpu import ceil_split_sizes
+
+
+def _proj(x: Tensor, w: Tensor, b: Optional[Tensor], fused: bool) -> Tensor:
+    if fused and x.is_cuda:
+        from .. import ops
+        return ops.linear(x, w, b)
+    y = x @ w.t()
+    return y if b is None else y + b
+
+
+def _stats(logits: Tensor, labels: Tensor, lo: int, fused: bool):
+    """Row max, sum(exp(l - max)) and the target logit (0 when the target is not in this shard)."""
+    if fused and logits.is_cuda:
+        from ..ops import cuda_ops
+        return cuda_ops.ce_stats(logits, labels, lo)
+    lf = logits.float()
+    mx = lf.max(dim=-1).values
+    se = torch.exp(lf - mx[:, None]).sum(-1)
+    local = labels - lo
+    inside = (local >= 0) & (local < logits.size(-1))
+    tgt = lf.gather(1, local.clamp(0, logits.size(-1) - 1)[:, None]).squeeze(1)
+    return mx, se, torch.where(inside, tgt, torch.zeros_like(tgt))
+
+
+def _grad_inplace(logits: Tensor, labels: Tensor, lo: int, lse: Tensor, scale: Tensor, fused: bool) -> Tensor:
+    """``(softmax - onehot) * scale`` written over ``logits`` (rows with ignored labels get zero)."""
+    if fused and logits.is_cuda:
+        from ..ops import cuda_ops
+        return cuda_ops.ce_grad_(logits, labels, lo, lse, scale)
+    p = torch.exp(logits.float() - lse[:, None])
+    local = labels - lo
+    inside = (local >= 0) & (local < logits.size(-1))
+    rows = torch.nonzero(inside, as_tuple=True)[0]
+    p[rows, local[rows]] -= 1.0
+    p *= scale[:, None]
+    logits.copy_(p)
+    return logits
+
+
+class _LinearCrossEntropy(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, hidden, weight, bias, labels, mpu, full_vocab, ignore_index, chunk_rows, fused):
+        tp = mpu.tp if mpu is not None else 1
+        lo = 0
+        if tp > 1:
+            sizes = ceil_split_sizes(full_vocab, tp)
+            lo = sum(sizes[: mpu.tp_rank])
+        n = hidden.size(0)
+        mx = torch.empty(n, dtype=torch.float32, device=hidden.device)
+        se = torch.empty_like(mx)
+        tg = torch.empty_like(mx)
+        for s in range(0, n, chunk_rows):
+            e = min(n, s + chunk_rows)
+            lg = _proj(hidden[s:e], weight, bias, fused)
+            mx[s:e], se[s:e], tg[s:e] = _stats(lg, labels[s:e], lo, fused)
+        if tp > 1:
+            gmx = mx.clone()
+            dist.all_reduce(gmx, op=dist.ReduceOp.MAX, group=mpu.get_tensor_parallel_group())
+            se = se * torch.exp(mx - gmx)
+            packed = torch.stack((se, tg))
+            dist.all_reduce(packed, group=mpu.get_tensor_parallel_group())
+            se, tg, mx = packed[0], packed[1], gmx
+        lse = torch.log(se) + mx
+        valid = labels != ignore_index
+        count = valid.sum().clamp(min=1).to(torch.float32)
+        loss = torch.where(valid, lse - tg, torch.zeros_like(lse)).sum() / count
+        ctx.save_for_backward(hidden, weight, bias, labels, lse, valid, count)
+        ctx.mpu, ctx.lo, ctx.chunk, ctx.fused = mpu, lo, chunk_rows, fused
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        hidden, weight, bias, labels, lse, valid, count = ctx.saved_tensors
+        mpu, lo, fused = ctx.mpu, ctx.lo, ctx.fused
+        n = hidden.size(0)
+        scale = (g.float() / count) * valid.to(torch.float32)
+        dx = torch.empty_like(hidden)
+        on_kernels = fused and hidden.is_cuda
+        dw = None if on_kernels else torch.zeros_like(weight, dtype=torch.float32)
+        dw_acc = None
+        db = torch.zeros(weight.size(0), dtype=torch.float32, device=weight.device) if bias is not None else None
+        for s in range(0, n, ctx.chunk):
+            e = min(n, s + ctx.chunk)
+            x = hidden[s:e]
+            lg = _proj(x, weight, bias, fused)
+            d = _grad_inplace(lg, labels[s:e], lo, lse[s:e], scale[s:e], fused)
+            if on_kernels:
+                from ..ops import cuda_ops
+                dx[s:e] = cuda_ops.gemm_nn(d, weight)
+                part = cuda_ops.gemm_tn(d, x, out_dtype=torch.float32)
+                dw_acc = part if dw_acc is None else dw_acc.add_(part)
+            else:
+                dx[s:e] = (d @ weight).to(dx.dtype)
+                dw += d.float().t() @ x.float()
+            if db is not None:
+                db += d.float().sum(0)
+        if dw_acc is not None:
+            dw = dw_acc
+        if mpu is not None and mpu.tp > 1:
+            dist.all_reduce(dx, group=mpu.get_tensor_parallel_group())
+        return (dx, dw.to(weight.dtype), db.to(bias.dtype) if db is not None else None,
+                None, None, None, None, None, None)
+
+
+def linear_cross_entropy(hidden: Tensor, weight: Tensor, bias: Optional[Tensor], labels: Tensor,
+                         ignore_index: int = -100, chunk_rows: int = 4096, fused: bool = True) -> Tensor:
+    return _LinearCrossEntropy.apply(hidden, weight, bias, labels, None, weight.size(0), ignore_index,
+                                     chunk_rows, fused)
+
+
+def vocab_parallel_linear_cross_entropy(hidden: Tensor, weight: Tensor, bias: Optional[Tensor], labels: Tensor,
+                                        mpu, full_vocab: int, ignore_index: int = -100, chunk_rows: int = 4096,
+                                        fused: bool = False) -> Tensor:
+    """Mean loss over rows with a label; ``weight`` / ``bias`` hold this rank's vocabulary rows."""
+    return _LinearCrossEntropy.apply(hidden, weight, bias, labels, mpu, full_vocab, ignore_index, chunk_rows, fused)

@@ -131,7 +131,7 @@ class ParallelizationMixin:
         pipe = PipelineParallelEngine(self, mpu, micro_batch_size=micro_batch_size, device=device)
         pipe.assign_stages()
         if tp > 1:
-            TensorParallelEngine(self, mpu, owned=pipe.owns, device=device,
+            TensorParallelEngine(self, mpu, owned=pipe.owns_param, device=device,
                                  sequence_parallel=sequence_parallel).parallelize()
         pipe.finalize()
         self.initial_parameters = dict(

@@ -1,0 +1,38 @@
+"""Rank layout and partition helpers (pure functions; no process group needed)."""
+from oslo_b200.parallel.engine_pipeline import one_f_one_b_order
+from oslo_b200.parallel.mpu import MPU, ceil_split_sizes
+
+
+def test_sixteen_rank_example():
+    # the 16-rank, tp=2, pp=4 example documented in the reference (oslo/parallelism/mpu.py:29-38)
+    assert MPU.layout_pipeline_groups(16, 4) == [[0, 4, 8, 12], [1, 5, 9, 13], [2, 6, 10, 14], [3, 7, 11, 15]]
+    assert MPU.layout_tensor_groups(16, 2) == [[i, i + 1] for i in range(0, 16, 2)]
+    assert MPU.layout_data_groups(16, 2, 4) == [[0, 2], [1, 3], [4, 6], [5, 7], [8, 10], [9, 11], [12, 14], [13, 15]]
+    assert MPU.layout_model_groups(16, 2, 4) == [[0, 1, 4, 5, 8, 9, 12, 13], [2, 3, 6, 7, 10, 11, 14, 15]]
+
+
+def test_vocab_split_sizes():
+    assert ceil_split_sizes(50257, 4) == [12565, 12565, 12565, 12562]
+    assert ceil_split_sizes(50257, 2) == [25129, 25128]
+    assert ceil_split_sizes(50400, 8) == [6300] * 8
+
+
+def test_pipeline_partition():
+    assert MPU.make_pipeline_partition(28, 4) == [0, 7, 14, 21, 28]
+    assert MPU.make_pipeline_partition(10, 4) == [0, 2, 4, 6, 10]  # remainder goes to the last stage
+    assert MPU.extend_pipeline_partition([0, 2, 5]) == [0, 0, 1, 1, 1]
+
+
+def test_one_f_one_b_order():
+    assert one_f_one_b_order(2, 0, 3) == ["F0", "F1", "B0", "F2", "B1", "B2"]
+    assert one_f_one_b_order(2, 1, 3) == ["F0", "B0", "F1", "B1", "F2", "B2"]
+    # every stage runs each forward before its backward and holds at most P - stage activations
+    for P in (2, 4):
+        for s in range(P):
+            order = one_f_one_b_order(P, s, 8)
+            live = peak = 0
+            for a in order:
+                live += 1 if a[0] == "F" else -1
+                peak = max(peak, live)
+                assert live >= 0
+            assert peak <= P - s
