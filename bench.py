@@ -1,0 +1,242 @@
+#!/usr/bin/env python
+"""Flagship benchmark: GPT-J-6B causal-LM training tokens/s (bf16, AdamW with fp32 master weights).
+
+``python bench.py --gpus N --steps K --warmup W`` (under ``torch.distributed.run`` for N > 1) prints ONE
+JSON line on rank 0. Weak scaling: every GPU works on ``--batch-per-gpu`` sequences of ``--seq`` tokens
+per step, so the global batch is ``8 N x 2048`` by default (64 x 2048 on 8 GPUs). Synthetic data: token
+ids uniform in [0, vocab) with a fixed seed; weights random-init.
+
+Timed regions (CUDA events on the compute stream, barrier + synchronize on both sides, max over ranks):
+  * ``value``: K full steps (forward, backward, gradient reduction, optimizer) with inputs already on
+    the device;
+  * ``e2e``: K more steps through the same public API where every step copies its inputs from pinned
+    host memory and reads the loss back to the host.
+The working set of one step (tens of GB of weights, activations and optimizer state) is far larger
+than the 126 MB L2, so no explicit flush is done between iterations (recorded in ``config``).
+
+``--impl reference`` runs the unmodified reference package from ``baseline/_ref`` when it can be
+imported on this stack, otherwise prints ``{"impl": "reference", "unavailable": ...}``.
+"""
+from __future__ import annotations
+
+import argparse
+import contextlib
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODELS = {
+    # name: (n_layer, n_embd, n_head, rotary_dim, vocab, n_positions)
+    "gptj-6b": (28, 4096, 16, 64, 50400, 2048),
+    "gptj-small": (4, 1024, 8, 64, 50400, 2048),   # debugging only; numbers from it are not benchmark values
+}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="oslo_b200", choices=["oslo_b200", "reference"])
+    ap.add_argument("--model", default="gptj-6b", choices=sorted(MODELS))
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--batch-per-gpu", type=int, default=8)
+    ap.add_argument("--micro-batch", type=int, default=None, help="sequences per forward/backward (default: auto)")
+    ap.add_argument("--tp", type=int, default=None)
+    ap.add_argument("--pp", type=int, default=1)
+    ap.add_argument("--checkpoint-activations", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
+
+    def __init__(self, index: int) -> None:
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop_evt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.nv = None
+
+    def run(self) -> None:
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop_evt.wait(0.2)
+
+    def stop(self):
+        self._stop_evt.set()
+        if self.is_alive():
+            self.join(timeout=2)
+        s = sorted(self.samples)
+        med = s[len(s) // 2] if s else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def reference_arm(args) -> None:
+    """Run the unmodified reference through its own public API, or say why it cannot run here."""
+    from baseline import reference_runner
+    reference_runner.main(args)
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import oslo_b200 as ob
+    from oslo_b200.optim import FusedAdamW
+    from oslo_b200.parallel.data_parallel import DistributedDataParallel
+
+    os.environ.setdefault("RANK", "0")
+    os.environ.setdefault("WORLD_SIZE", "1")
+    os.environ.setdefault("LOCAL_RANK", os.environ["RANK"])
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29531")
+    world = int(os.environ["WORLD_SIZE"])
+    rank = int(os.environ["RANK"])
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+
+    n_layer, n_embd, n_head, rotary, vocab, n_pos = MODELS[args.model]
+    tp = args.tp or 1
+    pp = args.pp
+    dp = world // (tp * pp)
+    cfg = ob.GPTJConfig(vocab_size=vocab, n_positions=n_pos, n_embd=n_embd, n_layer=n_layer, n_head=n_head,
+                        rotary_dim=rotary, torch_dtype=torch.bfloat16, use_cache=False)
+    seqs_per_rank = args.batch_per_gpu * tp * pp          # sequences one model replica handles per step
+    micro = args.micro_batch or (4 if args.model == "gptj-6b" else seqs_per_rank)
+    micro = min(micro, seqs_per_rank)
+    accum = seqs_per_rank // micro
+
+    model = ob.GPTJForCausalLM.from_config_with_parallel(
+        cfg, tensor_parallel_size=tp, pipeline_parallel_size=pp, micro_batch_size=micro, seed=1234,
+        init_on_device=True, torch_dtype=torch.bfloat16)
+    model.fuse()
+    model.train()
+    if args.checkpoint_activations:
+        model.gradient_checkpointing_enable()
+    mpu = model.mpu
+    opt = FusedAdamW(model.gpu_parameters(), lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1, max_grad_norm=1.0,
+                     shard_group=mpu.get_data_parallel_group() if dp > 1 else None,
+                     model_parallel_group=mpu.get_model_parallel_group() if tp * pp > 1 else None)
+    engine = DistributedDataParallel(model, mpu, optimizer=opt) if dp > 1 else None
+
+    gen = torch.Generator().manual_seed(1000 + mpu.get_data_parallel_rank())
+    n_host = 4
+    host = [torch.randint(0, vocab, (seqs_per_rank, args.seq), generator=gen).pin_memory() for _ in range(n_host)]
+    dev_inputs = [h.to(dev) for h in host]
+    ext = ob.ops.load_ext(required=True)
+
+    def train_step(ids):
+        opt.zero_grad()
+        total = None
+        if pp > 1:
+            for out in model(input_ids=ids, labels=ids, output_logits=False):
+                (out.loss / accum).backward()
+                total = out.loss.detach() if total is None else total + out.loss.detach()
+        else:
+            for i in range(accum):
+                mb = ids[i * micro:(i + 1) * micro]
+                hold = engine.no_sync() if (engine is not None and i < accum - 1) else contextlib.nullcontext()
+                with hold:  # gradients are reduced over the data-parallel group during the last backward only
+                    loss = model(input_ids=mb, labels=mb, output_logits=False).loss
+                    (loss / accum).backward()
+                total = loss.detach() if total is None else total + loss.detach()
+        opt.step()
+        return total / accum
+
+    def timed(steps, e2e):
+        dist.barrier()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(local)
+        sampler.start()
+        l0 = ext.launch_count()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        wall0 = time.perf_counter()
+        t0.record()
+        last = None
+        for s in range(steps):
+            if e2e:
+                ids = host[s % n_host].to(dev, non_blocking=True)
+                last = float(train_step(ids).item())
+            else:
+                last = train_step(dev_inputs[s % n_host])
+        t1.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - wall0
+        dist.barrier()
+        clocks = sampler.stop()
+        ms = torch.tensor([t0.elapsed_time(t1) if not e2e else wall * 1e3], device=dev)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item() / steps, clocks, ext.launch_count() - l0, last
+
+    for _ in range(args.warmup):
+        train_step(dev_inputs[0])
+    ms_step, clocks, launches, last = timed(args.steps, e2e=False)
+    tokens_step = dp * seqs_per_rank * args.seq
+    value = tokens_step / (ms_step / 1e3)
+    e2e = None
+    if not args.no_e2e:
+        ms_e2e, _, _, loss_host = timed(args.steps, e2e=True)
+        e2e = {"value": tokens_step / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": seqs_per_rank * args.seq * 8, "d2h_bytes_per_step": 4, "last_loss": loss_host}
+    err = int(ext.error_word(dev_inputs[0]).item())
+    mem_gb = torch.cuda.max_memory_allocated() / 2 ** 30
+    if rank == 0:
+        par = "x".join(f"{k}{v}" for k, v in (("tp", tp), ("pp", pp), ("dp", dp)) if v > 1) or "single"
+        line = {
+            "metric": "GPT-J-6B train tokens/sec" if args.model == "gptj-6b" else f"{args.model} train tokens/sec (debug)",
+            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights", "impl": "oslo_b200",
+            "config": {"model": args.model, "global_batch": dp * seqs_per_rank, "seq_len": args.seq,
+                       "parallelism": par + ("+zero1" if dp > 1 else ""), "micro_batch": micro, "grad_accum": accum,
+                       "optimizer": "AdamW fp32 master (fused)", "activation_checkpointing": bool(args.checkpoint_activations),
+                       "l2": "working set per step >> 126 MB L2, no explicit flush"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "device_error_word": err,
+            "peak_mem_gb": round(mem_gb, 1),
+        }
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,405 @@
+// torch.ops.oslo_b200.*: argument checking, allocation and stream plumbing around the C launchers.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+#include <torch/torch.h>
+
+#include <atomic>
+#include <mutex>
+#include <unordered_map>
+
+#include "oslo_kernels.h"
+
+namespace {
+
+using at::Tensor;
+using c10::optional;
+
+int dt_code(const Tensor& t) {
+  switch (t.scalar_type()) {
+    case at::kBFloat16: return OSLO_DT_BF16;
+    case at::kHalf: return OSLO_DT_FP16;
+    case at::kFloat: return OSLO_DT_FP32;
+    default: TORCH_CHECK(false, "oslo_b200: unsupported dtype ", t.scalar_type());
+  }
+}
+void check_rc(int rc, const char* what) {
+  TORCH_CHECK(rc == 0, "oslo_b200::", what, " failed with code ", rc,
+              rc > 0 ? std::string(" (") + cudaGetErrorString(static_cast<cudaError_t>(rc)) + ")" : std::string());
+}
+std::atomic<int64_t> g_launches{0};
+// every binding passes through here once per kernel it enqueues
+cudaStream_t cur_stream(int kernels = 1) {
+  g_launches.fetch_add(kernels, std::memory_order_relaxed);
+  return at::cuda::getCurrentCUDAStream().stream();
+}
+int64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
+const void* ptr_or_null(const optional<Tensor>& t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
+
+struct DevState {
+  Tensor err;
+  int sms = 0;
+};
+DevState& dev_state(int dev) {
+  static std::mutex mu;
+  static std::unordered_map<int, DevState> states;
+  std::lock_guard<std::mutex> g(mu);
+  auto it = states.find(dev);
+  if (it == states.end()) {
+    DevState s;
+    s.err = at::zeros({1}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, dev));
+    s.sms = at::cuda::getDeviceProperties(dev)->multiProcessorCount;
+    it = states.emplace(dev, std::move(s)).first;
+  }
+  return it->second;
+}
+
+// The word that kernels set when a bounded wait runs out (0 = no error). Reading it synchronises.
+Tensor error_word(const Tensor& like) { return dev_state(like.get_device()).err; }
+
+void check_2d_operand(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.dim() == 2, name, " must be a 2-D CUDA tensor");
+  TORCH_CHECK(t.stride(1) == 1 && t.stride(0) % 8 == 0 && t.stride(0) >= t.size(1), name,
+              " needs a contiguous last dim and a row stride that is a multiple of 8 elements");
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0, name, " must be 16-byte aligned");
+}
+
+// D[M,N] = alpha * A x B^T-style product with fused epilogue; see gemm_sm100.cu for the operand layouts.
+Tensor gemm(const Tensor& a, const Tensor& b, int64_t a_mn, int64_t b_mn, const optional<Tensor>& bias,
+            const optional<Tensor>& aux, const optional<Tensor>& out, const optional<Tensor>& aux_out, int64_t flags,
+            double alpha) {
+  check_2d_operand(a, "a");
+  check_2d_operand(b, "b");
+  TORCH_CHECK(a.scalar_type() == b.scalar_type(), "a and b must share a dtype");
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 || a.scalar_type() == at::kHalf, "gemm inputs must be bf16 or fp16");
+  c10::cuda::CUDAGuard guard(a.device());
+  const int64_t M = a_mn ? a.size(1) : a.size(0), K = a_mn ? a.size(0) : a.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0), Kb = b_mn ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb, "contraction sizes differ: ", K, " vs ", Kb);
+  int fl = static_cast<int>(flags) & ~GEMM_FLAG_FP16;
+  if (a.scalar_type() == at::kHalf) fl |= GEMM_FLAG_FP16;
+  const bool out_f32 = fl & GEMM_FLAG_OUT_FP32;
+  Tensor d;
+  if (out.has_value() && out->defined()) {
+    d = *out;
+    TORCH_CHECK(d.is_cuda() && d.dim() == 2 && d.size(0) == M && d.size(1) == N && d.stride(1) == 1, "bad out");
+    TORCH_CHECK(d.scalar_type() == (out_f32 ? at::kFloat : a.scalar_type()), "out dtype does not match flags");
+  } else {
+    TORCH_CHECK(!(fl & GEMM_FLAG_ACCUMULATE), "accumulate needs an out tensor");
+    d = at::empty({M, N}, a.options().dtype(out_f32 ? at::kFloat : a.scalar_type()));
+  }
+  if (M == 0 || N == 0) return d;
+  if (fl & GEMM_FLAG_BIAS) {
+    TORCH_CHECK(bias.has_value() && bias->numel() == N && bias->scalar_type() == a.scalar_type() && bias->is_contiguous(),
+                "bias must be a contiguous [N] tensor of the input dtype");
+  }
+  int ld_aux = 0, ld_aux_out = 0;
+  if (fl & (GEMM_FLAG_DGELU | GEMM_FLAG_RESIDUAL)) {
+    TORCH_CHECK(!((fl & GEMM_FLAG_DGELU) && (fl & GEMM_FLAG_RESIDUAL)), "dgelu and residual share the aux operand");
+    TORCH_CHECK(aux.has_value() && aux->dim() == 2 && aux->size(0) == M && aux->size(1) == N && aux->stride(1) == 1, "bad aux");
+    const auto want = (fl & GEMM_FLAG_RESIDUAL) ? d.scalar_type() : a.scalar_type();
+    TORCH_CHECK(aux->scalar_type() == want, "aux dtype mismatch");
+    ld_aux = static_cast<int>(aux->stride(0));
+  }
+  if (fl & GEMM_FLAG_SAVE_PREACT) {
+    TORCH_CHECK(aux_out.has_value() && aux_out->dim() == 2 && aux_out->size(0) == M && aux_out->size(1) == N &&
+                    aux_out->stride(1) == 1 && aux_out->scalar_type() == a.scalar_type(), "bad aux_out");
+    ld_aux_out = static_cast<int>(aux_out->stride(0));
+  }
+  auto& st = dev_state(a.get_device());
+  const int rc = oslo_gemm_16bit(a.data_ptr(), b.data_ptr(), d.data_ptr(), static_cast<int>(M), static_cast<int>(N),
+                                 static_cast<int>(K), static_cast<int>(a.stride(0)), static_cast<int>(b.stride(0)),
+                                 static_cast<int>(d.stride(0)), static_cast<int>(a_mn), static_cast<int>(b_mn),
+                                 ptr_or_null(bias), ptr_or_null(aux), ld_aux,
+                                 const_cast<void*>(ptr_or_null(aux_out)), ld_aux_out, fl, static_cast<float>(alpha),
+                                 st.err.data_ptr<int>(), st.sms, cur_stream());
+  check_rc(rc, "gemm");
+  return d;
+}
+
+std::tuple<Tensor, Tensor, Tensor> layernorm_fwd(const Tensor& x, const Tensor& w, const optional<Tensor>& b, double eps) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && w.is_contiguous(), "layernorm: contiguous CUDA tensors required");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t cols = x.size(-1), rows = x.numel() / std::max<int64_t>(cols, 1);
+  Tensor y = at::empty_like(x);
+  Tensor mean = at::empty({rows}, x.options().dtype(at::kFloat));
+  Tensor rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+  check_rc(oslo_layernorm_fwd(x.data_ptr(), w.data_ptr(), ptr_or_null(b), y.data_ptr(), mean.data_ptr<float>(),
+                              rstd.data_ptr<float>(), static_cast<int>(rows), static_cast<int>(cols),
+                              static_cast<float>(eps), dt_code(x), cur_stream()), "layernorm_fwd");
+  return {y, mean, rstd};
+}
+
+std::tuple<Tensor, Tensor, Tensor> layernorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& mean,
+                                                  const Tensor& rstd) {
+  TORCH_CHECK(dy.is_contiguous() && x.is_contiguous(), "layernorm_bwd: contiguous tensors required");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t cols = x.size(-1), rows = x.numel() / std::max<int64_t>(cols, 1);
+  const int parts = static_cast<int>(std::min<int64_t>(rows, 2 * dev_state(x.get_device()).sms));
+  Tensor dx = at::empty_like(x);
+  Tensor dw = at::empty_like(w), db = at::empty_like(w);
+  Tensor part = at::empty({2, std::max(parts, 1), cols}, x.options().dtype(at::kFloat));
+  check_rc(oslo_layernorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                              dx.data_ptr(), part[0].data_ptr<float>(), part[1].data_ptr<float>(), dw.data_ptr(),
+                              db.data_ptr(), static_cast<int>(rows), static_cast<int>(cols), parts, dt_code(x),
+                              cur_stream(2)), "layernorm_bwd");
+  return {dx, dw, db};
+}
+
+Tensor bias_gelu_fwd(const Tensor& x, const optional<Tensor>& bias) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous(), "bias_gelu: contiguous CUDA tensor required");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = at::empty_like(x);
+  const int64_t cols = x.size(-1);
+  check_rc(oslo_bias_gelu_fwd(x.data_ptr(), ptr_or_null(bias), y.data_ptr(), x.numel() / std::max<int64_t>(cols, 1),
+                              static_cast<int>(cols), dt_code(x), cur_stream()), "bias_gelu_fwd");
+  return y;
+}
+Tensor bias_gelu_bwd(const Tensor& dy, const Tensor& x, const optional<Tensor>& bias) {
+  TORCH_CHECK(dy.is_contiguous() && x.is_contiguous(), "bias_gelu_bwd: contiguous tensors required");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor dx = at::empty_like(x);
+  const int64_t cols = x.size(-1);
+  check_rc(oslo_bias_gelu_bwd(dy.data_ptr(), x.data_ptr(), ptr_or_null(bias), dx.data_ptr(),
+                              x.numel() / std::max<int64_t>(cols, 1), static_cast<int>(cols), dt_code(x), cur_stream()),
+           "bias_gelu_bwd");
+  return dx;
+}
+
+Tensor bias_dropout_residual(const Tensor& x, const optional<Tensor>& bias, const optional<Tensor>& residual, double p,
+                             int64_t seed, int64_t mode) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous(), "bias_dropout_residual: contiguous CUDA tensor required");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = at::empty_like(x);
+  const int64_t cols = x.size(-1);
+  check_rc(oslo_bias_dropout_residual(x.data_ptr(), ptr_or_null(bias), ptr_or_null(residual), y.data_ptr(),
+                                      x.numel() / std::max<int64_t>(cols, 1), static_cast<int>(cols),
+                                      static_cast<float>(p), static_cast<unsigned long long>(seed),
+                                      static_cast<int>(mode), dt_code(x), cur_stream()), "bias_dropout_residual");
+  return y;
+}
+
+Tensor colsum(const Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous(), "colsum: contiguous 2-D CUDA tensor required");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int rows = static_cast<int>(x.size(0)), cols = static_cast<int>(x.size(1));
+  const int parts = std::max(1, std::min(rows, 64));
+  Tensor part = at::empty({parts, cols}, x.options().dtype(at::kFloat));
+  Tensor out = at::zeros({cols}, x.options().dtype(at::kFloat));
+  check_rc(oslo_colsum(x.data_ptr(), part.data_ptr<float>(), out.data_ptr<float>(), rows, cols, parts, dt_code(x),
+                       cur_stream(2)), "colsum");
+  return out;
+}
+
+Tensor rotary(const Tensor& x, const Tensor& positions, int64_t rotary_dim, double base, bool inverse) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 4 && x.is_contiguous(), "rotary: contiguous [B,S,H,D] CUDA tensor required");
+  TORCH_CHECK(positions.scalar_type() == at::kLong && positions.is_contiguous() &&
+                  positions.numel() == x.size(0) * x.size(1), "rotary: positions must be int64 [B,S]");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = at::empty_like(x);
+  check_rc(oslo_rotary(x.data_ptr(), y.data_ptr(), reinterpret_cast<const long long*>(positions.data_ptr<int64_t>()),
+                       static_cast<int>(x.size(0)), static_cast<int>(x.size(1)), static_cast<int>(x.size(2)),
+                       static_cast<int>(x.size(3)), static_cast<int>(rotary_dim), static_cast<float>(base),
+                       inverse ? 1 : 0, dt_code(x), cur_stream()), "rotary");
+  return y;
+}
+
+Tensor causal_softmax_fwd(const Tensor& x, double scale) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 3 && x.is_contiguous(), "causal_softmax: contiguous [batches,sq,sk] required");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = at::empty_like(x);
+  check_rc(oslo_causal_softmax_fwd(x.data_ptr(), y.data_ptr(), static_cast<int>(x.size(0)), static_cast<int>(x.size(1)),
+                                   static_cast<int>(x.size(2)), static_cast<float>(scale), dt_code(x), cur_stream()),
+           "causal_softmax_fwd");
+  return y;
+}
+Tensor masked_softmax_fwd(const Tensor& x, const Tensor& mask, double scale) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 4 && x.is_contiguous(), "masked_softmax: contiguous [b,h,sq,sk] required");
+  TORCH_CHECK(mask.scalar_type() == at::kByte && mask.is_contiguous() && mask.dim() == 4 && mask.size(1) == 1 &&
+                  mask.size(2) == x.size(2) && mask.size(3) == x.size(3) &&
+                  (mask.size(0) == 1 || mask.size(0) == x.size(0)), "mask must be uint8 [1|b,1,sq,sk]");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = at::empty_like(x);
+  check_rc(oslo_masked_softmax_fwd(x.data_ptr(), mask.data_ptr<uint8_t>(), y.data_ptr(), static_cast<int>(x.size(0)),
+                                   static_cast<int>(x.size(1)), static_cast<int>(x.size(2)), static_cast<int>(x.size(3)),
+                                   static_cast<int>(mask.size(0)), static_cast<float>(scale), dt_code(x), cur_stream()),
+           "masked_softmax_fwd");
+  return y;
+}
+Tensor softmax_bwd(const Tensor& y, const Tensor& dy, double scale) {
+  TORCH_CHECK(y.is_contiguous() && dy.is_contiguous(), "softmax_bwd: contiguous tensors required");
+  c10::cuda::CUDAGuard guard(y.device());
+  Tensor dx = at::empty_like(y);
+  const int64_t cols = y.size(-1);
+  check_rc(oslo_softmax_bwd(y.data_ptr(), dy.data_ptr(), dx.data_ptr(), y.numel() / std::max<int64_t>(cols, 1),
+                            static_cast<int>(cols), static_cast<float>(scale), dt_code(y), cur_stream()), "softmax_bwd");
+  return dx;
+}
+
+std::tuple<Tensor, Tensor, Tensor> ce_stats(const Tensor& logits, const Tensor& labels, int64_t vocab_start) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1, "ce_stats: [rows, cols] logits required");
+  TORCH_CHECK(labels.scalar_type() == at::kLong && labels.is_contiguous() && labels.numel() == logits.size(0), "bad labels");
+  c10::cuda::CUDAGuard guard(logits.device());
+  const auto fo = logits.options().dtype(at::kFloat);
+  Tensor mx = at::empty({logits.size(0)}, fo), se = at::empty({logits.size(0)}, fo), tg = at::empty({logits.size(0)}, fo);
+  check_rc(oslo_ce_stats(logits.data_ptr(), reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()),
+                         mx.data_ptr<float>(), se.data_ptr<float>(), tg.data_ptr<float>(), static_cast<int>(logits.size(0)),
+                         static_cast<int>(logits.size(1)), static_cast<int>(logits.stride(0)), vocab_start,
+                         dt_code(logits), cur_stream()), "ce_stats");
+  return {mx, se, tg};
+}
+Tensor ce_grad_(Tensor logits, const Tensor& labels, int64_t vocab_start, const Tensor& lse, const Tensor& scale) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1, "ce_grad_: [rows, cols] logits required");
+  TORCH_CHECK(lse.scalar_type() == at::kFloat && scale.scalar_type() == at::kFloat && lse.is_contiguous() &&
+                  scale.is_contiguous() && labels.is_contiguous(), "ce_grad_: fp32 contiguous lse/scale required");
+  c10::cuda::CUDAGuard guard(logits.device());
+  check_rc(oslo_ce_grad(logits.data_ptr(), reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()),
+                        lse.data_ptr<float>(), scale.data_ptr<float>(), static_cast<int>(logits.size(0)),
+                        static_cast<int>(logits.size(1)), static_cast<int>(logits.stride(0)), vocab_start,
+                        dt_code(logits), cur_stream()), "ce_grad");
+  return logits;
+}
+
+void adam_step(Tensor p, const Tensor& g, Tensor m, Tensor v, const optional<Tensor>& p_lp, double lr, double beta1,
+               double beta2, double eps, double wd, int64_t step, double grad_scale, const optional<Tensor>& inv_scale) {
+  TORCH_CHECK(p.is_cuda() && p.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat,
+              "adam: fp32 master/moment buffers required");
+  TORCH_CHECK(p.is_contiguous() && g.is_contiguous() && m.is_contiguous() && v.is_contiguous() &&
+                  g.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel(), "adam: size mismatch");
+  c10::cuda::CUDAGuard guard(p.device());
+  int lp_dt = OSLO_DT_BF16;
+  if (p_lp.has_value() && p_lp->defined()) {
+    TORCH_CHECK(p_lp->is_contiguous() && p_lp->numel() == p.numel(), "adam: low-precision copy size mismatch");
+    lp_dt = dt_code(*p_lp);
+    TORCH_CHECK(lp_dt != OSLO_DT_FP32, "adam: low-precision copy must be 16-bit");
+  }
+  const float bc1 = 1.f - static_cast<float>(std::pow(beta1, static_cast<double>(step)));
+  const float bc2 = 1.f - static_cast<float>(std::pow(beta2, static_cast<double>(step)));
+  const float* inv = inv_scale.has_value() && inv_scale->defined() ? inv_scale->data_ptr<float>() : nullptr;
+  check_rc(oslo_adam(p.data_ptr<float>(), g.data_ptr(), m.data_ptr<float>(), v.data_ptr<float>(),
+                     const_cast<void*>(ptr_or_null(p_lp)), p.numel(), static_cast<float>(lr), static_cast<float>(beta1),
+                     static_cast<float>(beta2), static_cast<float>(eps), static_cast<float>(wd), bc1, bc2,
+                     static_cast<float>(grad_scale), inv, dt_code(g), lp_dt, cur_stream()), "adam");
+}
+
+Tensor sumsq(const Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous(), "sumsq: contiguous CUDA tensor required");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = at::zeros({1}, x.options().dtype(at::kFloat));
+  check_rc(oslo_sumsq(x.data_ptr(), out.data_ptr<float>(), x.numel(), dt_code(x), cur_stream()), "sumsq");
+  return out;
+}
+
+Tensor ngram_ban_(const Tensor& tokens, Tensor lprobs, int64_t n) {
+  TORCH_CHECK(tokens.is_cuda() && tokens.scalar_type() == at::kLong && tokens.dim() == 2 && tokens.is_contiguous(), "bad tokens");
+  TORCH_CHECK(lprobs.is_cuda() && lprobs.scalar_type() == at::kFloat && lprobs.dim() == 2 && lprobs.is_contiguous() &&
+                  lprobs.size(0) == tokens.size(0), "lprobs must be fp32 [rows, vocab]");
+  c10::cuda::CUDAGuard guard(lprobs.device());
+  check_rc(oslo_ngram_ban(reinterpret_cast<const long long*>(tokens.data_ptr<int64_t>()), lprobs.data_ptr<float>(),
+                          static_cast<int>(tokens.size(0)), static_cast<int>(tokens.size(1)),
+                          static_cast<int>(lprobs.size(1)), static_cast<int>(n), cur_stream()), "ngram_ban");
+  return lprobs;
+}
+
+void check_attn_operand(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.dim() == 4 && t.stride(3) == 1, name, " must be [B,H,S,D] with contiguous D");
+  TORCH_CHECK(t.stride(0) % 8 == 0 && t.stride(1) % 8 == 0 && t.stride(2) % 8 == 0 &&
+                  reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0, name, " needs 16-byte aligned rows");
+}
+
+std::tuple<Tensor, Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v, double scale, bool causal,
+                                     int64_t window, const optional<Tensor>& kpm) {
+  check_attn_operand(q, "q"); check_attn_operand(k, "k"); check_attn_operand(v, "v");
+  c10::cuda::CUDAGuard guard(q.device());
+  const int B = q.size(0), H = q.size(1), Sq = q.size(2), D = q.size(3), Sk = k.size(2);
+  // output laid out [B, S, H, D] in memory and returned as a [B, H, S, D] view, so merging heads is free
+  Tensor o = at::empty({B, Sq, H, D}, q.options()).permute({0, 2, 1, 3});
+  Tensor lse = at::empty({B, H, Sq}, q.options().dtype(at::kFloat));
+  const uint8_t* mp = nullptr;
+  if (kpm.has_value() && kpm->defined()) {
+    TORCH_CHECK(kpm->scalar_type() == at::kByte && kpm->is_contiguous() && kpm->size(0) == B && kpm->size(1) == Sk, "bad key padding mask");
+    mp = kpm->data_ptr<uint8_t>();
+  }
+  check_rc(oslo_flash_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), mp, B, H, Sq, Sk,
+                          D, q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2), v.stride(0),
+                          v.stride(1), v.stride(2), o.stride(0), o.stride(1), o.stride(2), static_cast<float>(scale),
+                          causal ? 1 : 0, static_cast<int>(window), dt_code(q), cur_stream()), "flash_fwd");
+  return {o, lse};
+}
+
+std::tuple<Tensor, Tensor, Tensor> flash_bwd(const Tensor& dout, const Tensor& q, const Tensor& k, const Tensor& v,
+                                             const Tensor& o, const Tensor& lse, double scale, bool causal,
+                                             int64_t window, const optional<Tensor>& kpm) {
+  check_attn_operand(q, "q"); check_attn_operand(k, "k"); check_attn_operand(v, "v");
+  check_attn_operand(o, "o"); check_attn_operand(dout, "dout");
+  c10::cuda::CUDAGuard guard(q.device());
+  const int B = q.size(0), H = q.size(1), Sq = q.size(2), D = q.size(3), Sk = k.size(2);
+  Tensor dq = at::empty_strided(q.sizes(), q.strides(), q.options());
+  Tensor dk = at::empty_strided(k.sizes(), k.strides(), k.options());
+  Tensor dv = at::empty_strided(v.sizes(), v.strides(), v.options());
+  Tensor delta = at::empty({B, H, Sq}, q.options().dtype(at::kFloat));
+  const uint8_t* mp = (kpm.has_value() && kpm->defined()) ? kpm->data_ptr<uint8_t>() : nullptr;
+  check_rc(oslo_flash_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), dout.data_ptr(), lse.data_ptr<float>(),
+                          delta.data_ptr<float>(), nullptr, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), mp, B, H, Sq, Sk,
+                          D, q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2), v.stride(0),
+                          v.stride(1), v.stride(2), o.stride(0), o.stride(1), o.stride(2), dout.stride(0),
+                          dout.stride(1), dout.stride(2), static_cast<float>(scale), causal ? 1 : 0,
+                          static_cast<int>(window), dt_code(q), cur_stream(D > 128 ? 4 : 3)), "flash_bwd");
+  return {dq, dk, dv};
+}
+
+Tensor decode_attn(const Tensor& q, const Tensor& kc, const Tensor& vc, const Tensor& lengths, double scale,
+                   int64_t window) {
+  TORCH_CHECK(q.is_cuda() && q.dim() == 3 && q.is_contiguous(), "decode_attn: q must be contiguous [B,H,D]");
+  TORCH_CHECK(kc.dim() == 4 && kc.is_contiguous() && vc.is_contiguous(), "decode_attn: caches must be contiguous [B,H,T,D]");
+  TORCH_CHECK(lengths.scalar_type() == at::kInt && lengths.is_contiguous() && lengths.numel() == q.size(0), "bad lengths");
+  c10::cuda::CUDAGuard guard(q.device());
+  const int B = q.size(0), H = q.size(1), D = q.size(2), T = kc.size(2);
+  const int sms = dev_state(q.get_device()).sms;
+  int splits = std::max(1, std::min(32, (2 * sms) / std::max(1, B * H)));
+  splits = std::min(splits, std::max(1, T / 64));
+  Tensor ws = at::empty({B, H, splits, D + 2}, q.options().dtype(at::kFloat));
+  Tensor o = at::empty_like(q);
+  check_rc(oslo_decode_attn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), lengths.data_ptr<int>(),
+                            ws.data_ptr<float>(), B, H, T, D, splits, static_cast<float>(scale),
+                            static_cast<int>(window), dt_code(q), cur_stream(2)), "decode_attn");
+  return o;
+}
+
+// In-place all-reduce of a symmetric buffer. ptr tables are device arrays of `world` addresses.
+void allreduce_symm(int64_t peer_ptrs_dev, int64_t mc_ptr, int64_t signal_ptrs_dev, Tensor out, int64_t numel,
+                    int64_t rank, int64_t world, bool use_multimem) {
+  c10::cuda::CUDAGuard guard(out.device());
+  auto& st = dev_state(out.get_device());
+  check_rc(oslo_allreduce_symm(reinterpret_cast<void* const*>(peer_ptrs_dev), reinterpret_cast<void*>(mc_ptr),
+                               reinterpret_cast<uint32_t* const*>(signal_ptrs_dev), out.data_ptr(), numel,
+                               static_cast<int>(rank), static_cast<int>(world), dt_code(out), use_multimem ? 1 : 0,
+                               st.err.data_ptr<int>(), cur_stream()), "allreduce_symm");
+}
+
+}  // namespace
+
+TORCH_LIBRARY(oslo_b200, m) {
+  m.def("error_word(Tensor like) -> Tensor", &error_word);
+  m.def("launch_count() -> int", &launch_count);
+  m.def("gemm(Tensor a, Tensor b, int a_mn, int b_mn, Tensor? bias, Tensor? aux, Tensor(a!)? out, Tensor(b!)? aux_out, int flags, float alpha) -> Tensor", &gemm);
+  m.def("layernorm_fwd(Tensor x, Tensor w, Tensor? b, float eps) -> (Tensor, Tensor, Tensor)", &layernorm_fwd);
+  m.def("layernorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor mean, Tensor rstd) -> (Tensor, Tensor, Tensor)", &layernorm_bwd);
+  m.def("bias_gelu_fwd(Tensor x, Tensor? bias) -> Tensor", &bias_gelu_fwd);
+  m.def("bias_gelu_bwd(Tensor dy, Tensor x, Tensor? bias) -> Tensor", &bias_gelu_bwd);
+  m.def("bias_dropout_residual(Tensor x, Tensor? bias, Tensor? residual, float p, int seed, int mode) -> Tensor", &bias_dropout_residual);
+  m.def("colsum(Tensor x) -> Tensor", &colsum);
+  m.def("rotary(Tensor x, Tensor positions, int rotary_dim, float base, bool inverse) -> Tensor", &rotary);
+  m.def("causal_softmax_fwd(Tensor x, float scale) -> Tensor", &causal_softmax_fwd);
+  m.def("masked_softmax_fwd(Tensor x, Tensor mask, float scale) -> Tensor", &masked_softmax_fwd);
+  m.def("softmax_bwd(Tensor y, Tensor dy, float scale) -> Tensor", &softmax_bwd);
+  m.def("ce_stats(Tensor logits, Tensor labels, int vocab_start) -> (Tensor, Tensor, Tensor)", &ce_stats);
+  m.def("ce_grad_(Tensor(a!) logits, Tensor labels, int vocab_start, Tensor lse, Tensor scale) -> Tensor(a!)", &ce_grad_);
+  m.def("adam_step(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor(d!)? p_lp, float lr, float beta1, float beta2, float eps, float wd, int step, float grad_scale, Tensor? inv_scale) -> ()", &adam_step);
+  m.def("sumsq(Tensor x) -> Tensor", &sumsq);
+  m.def("ngram_ban_(Tensor tokens, Tensor(a!) lprobs, int n) -> Tensor(a!)", &ngram_ban_);
+  m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int window, Tensor? kpm) -> (Tensor, Tensor)", &flash_fwd);
+  m.def("flash_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale, bool causal, int window, Tensor? kpm) -> (Tensor, Tensor, Tensor)", &flash_bwd);
+  m.def("decode_attn(Tensor q, Tensor kc, Tensor vc, Tensor lengths, float scale, int window) -> Tensor", &decode_attn);
+  m.def("allreduce_symm(int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(a!) out, int numel, int rank, int world, bool use_multimem) -> ()", &allreduce_symm);
+}

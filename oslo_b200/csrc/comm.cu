@@ -1,0 +1,159 @@
+// Collectives over symmetric memory (every rank holds the same buffer at peer-mapped addresses, plus an
+// NVSwitch multicast mapping of it). Cross-GPU synchronisation uses per-(block, peer) signal words with a
+// compare-and-swap handshake; every spin is bounded and reports through the error word.
+//
+//  * multimem mode (NVLS): rank r owns slice r of the buffer; it issues multimem.ld_reduce on the multicast
+//    address (the switch returns the sum over all ranks) and multimem.st to broadcast the reduced slice back
+//    into every rank's buffer - each byte crosses this GPU's links once in each direction.
+//  * peer mode: each rank reads every peer's buffer directly (one-shot) and writes the sum to `out`.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "oslo_kernels.h"
+#include "ptx.cuh"
+
+namespace oslo {
+
+__device__ __forceinline__ bool signal_put(uint32_t* addr, int* err) {
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    uint32_t old;
+    asm volatile("atom.global.release.sys.cas.b32 %0, [%1], 0, 1;" : "=r"(old) : "l"(addr) : "memory");
+    if (old == 0) return true;
+    if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > OSLO_WAIT_LIMIT_NS) {
+      if (err) atomicCAS(err, 0, ERR_WAIT_PEER);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ bool signal_wait(uint32_t* addr, int* err) {
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    uint32_t old;
+    asm volatile("atom.global.acquire.sys.cas.b32 %0, [%1], 1, 0;" : "=r"(old) : "l"(addr) : "memory");
+    if (old == 1) return true;
+    if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > OSLO_WAIT_LIMIT_NS) {
+      if (err) atomicCAS(err, 0, ERR_WAIT_PEER);
+      return false;
+    }
+  }
+}
+
+// all ranks' blocks with the same blockIdx meet; slot layout: [block][source rank]
+__device__ __forceinline__ bool block_barrier_all_ranks(uint32_t* const* signal_ptrs, int rank, int world, int slot0,
+                                                        int* err) {
+  __shared__ int ok_s;
+  __syncthreads();
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    __threadfence_system();
+    const int peer = threadIdx.x;
+    bool ok = signal_put(signal_ptrs[peer] + slot0 + blockIdx.x * world + rank, err);
+    ok = ok && signal_wait(signal_ptrs[rank] + slot0 + blockIdx.x * world + peer, err);
+    if (!ok) ok_s = 0;
+  }
+  __syncthreads();
+  return ok_s != 0;
+}
+
+template <bool FP16>
+__device__ __forceinline__ uint4 multimem_ld_reduce(const void* mc_addr) {
+  uint4 v;
+  if (FP16)
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_addr) : "memory");
+  else
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w) : "memory");
+}
+
+template <bool FP16>
+__device__ __forceinline__ uint4 add8(const uint4& a, const uint4& b) {
+  uint4 r;
+  const uint32_t* pa = &a.x; const uint32_t* pb = &b.x; uint32_t* pr = &r.x;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (FP16) {
+      const float2 x = __half22float2(*reinterpret_cast<const __half2*>(pa + i));
+      const float2 y = __half22float2(*reinterpret_cast<const __half2*>(pb + i));
+      __half2 h = __floats2half2_rn(x.x + y.x, x.y + y.y);
+      pr[i] = *reinterpret_cast<uint32_t*>(&h);
+    } else {
+      const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pa + i));
+      const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pb + i));
+      __nv_bfloat162 h = __floats2bfloat162_rn(x.x + y.x, x.y + y.y);
+      pr[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+  }
+  return r;
+}
+
+// n16 = number of 16-byte vectors in the buffer
+template <bool FP16>
+__global__ void __launch_bounds__(512) allreduce_symm_kernel(void* const* peer_ptrs, void* mc_ptr,
+                                                             uint32_t* const* signal_ptrs, void* out, long long n16,
+                                                             int rank, int world, int use_multimem, int* err) {
+  if (!block_barrier_all_ranks(signal_ptrs, rank, world, 0, err)) return;
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  if (use_multimem) {
+    const long long per = (n16 + world - 1) / world;
+    const long long lo = per * rank, hi = min(n16, lo + per);
+    uint4* mc = reinterpret_cast<uint4*>(mc_ptr);
+    for (long long i = lo + tid; i < hi; i += nthreads) {
+      const uint4 v = multimem_ld_reduce<FP16>(mc + i);
+      multimem_st(mc + i, v);
+    }
+    if (!block_barrier_all_ranks(signal_ptrs, rank, world, gridDim.x * world, err)) return;
+    if (out != peer_ptrs[rank]) {
+      const uint4* src = reinterpret_cast<const uint4*>(peer_ptrs[rank]);
+      uint4* dst = reinterpret_cast<uint4*>(out);
+      for (long long i = tid; i < n16; i += nthreads) dst[i] = src[i];
+    }
+  } else {
+    uint4* dst = reinterpret_cast<uint4*>(out);
+    for (long long i = tid; i < n16; i += nthreads) {
+      uint4 acc = reinterpret_cast<const uint4*>(peer_ptrs[rank])[i];
+      for (int r = 1; r < world; ++r) {
+        const int peer = (rank + r) % world;
+        acc = add8<FP16>(acc, reinterpret_cast<const uint4*>(peer_ptrs[peer])[i]);
+      }
+      dst[i] = acc;
+    }
+    // peers must not overwrite their buffers while others still read them
+    block_barrier_all_ranks(signal_ptrs, rank, world, gridDim.x * world, err);
+  }
+}
+
+}  // namespace oslo
+
+extern "C" int oslo_allreduce_symm(void* const* peer_ptrs_dev, void* mc_ptr, uint32_t* const* signal_ptrs_dev,
+                                   void* out, long long n, int rank, int world, int dtype, int use_multimem,
+                                   int* err_word, cudaStream_t stream) {
+  using namespace oslo;
+  if (n == 0) return 0;
+  if (n % 8) return -3;  // 16-byte vectors of 16-bit elements
+  if (world > 16) return -4;
+  const long long n16 = n / 8;
+  // the signal pad holds 2 barriers x blocks x world 32-bit slots; keep it within 2 KiB
+  int max_blocks = 2048 / 4 / (2 * world);
+  long long want = (n16 / (use_multimem ? world : 1) + 511) / 512;
+  int blocks = static_cast<int>(want < 1 ? 1 : (want > max_blocks ? max_blocks : want));
+  if (dtype == OSLO_DT_FP16)
+    allreduce_symm_kernel<true><<<blocks, 512, 0, stream>>>(peer_ptrs_dev, mc_ptr, signal_ptrs_dev, out, n16, rank,
+                                                            world, use_multimem, err_word);
+  else if (dtype == OSLO_DT_BF16)
+    allreduce_symm_kernel<false><<<blocks, 512, 0, stream>>>(peer_ptrs_dev, mc_ptr, signal_ptrs_dev, out, n16, rank,
+                                                             world, use_multimem, err_word);
+  else
+    return -2;
+  return static_cast<int>(cudaGetLastError());
+}

@@ -1,0 +1,697 @@
+// Memory-bound kernels: LayerNorm, bias+GeLU, bias+dropout+residual, rotary, softmax on scores,
+// cross-entropy pieces, AdamW, n-gram blocking. All use 16-byte vector accesses on the contiguous
+// dim, fp32 math, and run on the caller's stream.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <math_constants.h>
+
+#include "oslo_kernels.h"
+
+namespace oslo {
+
+template <typename T> struct Cvt;
+template <> struct Cvt<__nv_bfloat16> {
+  static __device__ __forceinline__ float to(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from(float v) { return __float2bfloat16_rn(v); }
+};
+template <> struct Cvt<__half> {
+  static __device__ __forceinline__ float to(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from(float v) { return __float2half_rn(v); }
+};
+template <> struct Cvt<float> {
+  static __device__ __forceinline__ float to(float v) { return v; }
+  static __device__ __forceinline__ float from(float v) { return v; }
+};
+
+// VEC elements = 16 bytes
+template <typename T> struct VecOf { static constexpr int N = 16 / sizeof(T); };
+
+template <typename T>
+__device__ __forceinline__ void load_vec(const T* p, float* f) {
+  constexpr int N = VecOf<T>::N;
+  uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < N; ++i) f[i] = Cvt<T>::to(e[i]);
+}
+template <typename T>
+__device__ __forceinline__ void store_vec(T* p, const float* f) {
+  constexpr int N = VecOf<T>::N;
+  uint4 raw;
+  T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < N; ++i) e[i] = Cvt<T>::from(f[i]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) sh[w] = v;
+  __syncthreads();
+  float r = (threadIdx.x < THREADS / 32) ? sh[threadIdx.x] : 0.f;
+  if (w == 0) r = warp_sum(r);
+  if (threadIdx.x == 0) sh[0] = r;
+  __syncthreads();
+  return sh[0];
+}
+template <int THREADS>
+__device__ __forceinline__ float block_max(float v, float* sh) {
+  v = warp_max(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) sh[w] = v;
+  __syncthreads();
+  float r = (threadIdx.x < THREADS / 32) ? sh[threadIdx.x] : -CUDART_INF_F;
+  if (w == 0) r = warp_max(r);
+  if (threadIdx.x == 0) sh[0] = r;
+  __syncthreads();
+  return sh[0];
+}
+
+__device__ __forceinline__ float gelu_f(float x) {
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.0f + tanhf(u));
+}
+__device__ __forceinline__ float dgelu_f(float x) {
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  const float t = tanhf(u);
+  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * 0.7978845608028654f * (1.0f + 0.134145f * x * x);
+}
+
+// ---------------------------------------------------------------------- LayerNorm
+constexpr int LN_THREADS = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(LN_THREADS) layernorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w,
+                                                                   const T* __restrict__ b, T* __restrict__ y,
+                                                                   float* __restrict__ mean, float* __restrict__ rstd,
+                                                                   int rows, int cols, float eps) {
+  constexpr int V = VecOf<T>::N;
+  __shared__ float sh[LN_THREADS / 32];
+  const int row = blockIdx.x;
+  const T* xr = x + static_cast<size_t>(row) * cols;
+  T* yr = y + static_cast<size_t>(row) * cols;
+  const int nvec = cols / V;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < nvec; i += LN_THREADS) {
+    float f[V];
+    load_vec(xr + i * V, f);
+#pragma unroll
+    for (int j = 0; j < V; ++j) s += f[j];
+  }
+  for (int i = nvec * V + threadIdx.x; i < cols; i += LN_THREADS) s += Cvt<T>::to(xr[i]);
+  const float mu = block_sum<LN_THREADS>(s, sh) / cols;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < nvec; i += LN_THREADS) {
+    float f[V];
+    load_vec(xr + i * V, f);
+#pragma unroll
+    for (int j = 0; j < V; ++j) { const float d = f[j] - mu; q += d * d; }
+  }
+  for (int i = nvec * V + threadIdx.x; i < cols; i += LN_THREADS) { const float d = Cvt<T>::to(xr[i]) - mu; q += d * d; }
+  const float rs = rsqrtf(block_sum<LN_THREADS>(q, sh) / cols + eps);
+  if (threadIdx.x == 0) { mean[row] = mu; rstd[row] = rs; }
+  for (int i = threadIdx.x; i < nvec; i += LN_THREADS) {
+    float f[V], g[V], h[V];
+    load_vec(xr + i * V, f);
+    load_vec(w + i * V, g);
+    if (b) load_vec(b + i * V, h);
+#pragma unroll
+    for (int j = 0; j < V; ++j) f[j] = (f[j] - mu) * rs * g[j] + (b ? h[j] : 0.f);
+    store_vec(yr + i * V, f);
+  }
+  for (int i = nvec * V + threadIdx.x; i < cols; i += LN_THREADS)
+    yr[i] = Cvt<T>::from((Cvt<T>::to(xr[i]) - mu) * rs * Cvt<T>::to(w[i]) + (b ? Cvt<T>::to(b[i]) : 0.f));
+}
+
+// Each CTA walks rows blockIdx.x, +gridDim.x, ...; thread t owns the same columns in every row, so the
+// weight/bias gradient partials stay in registers (up to LN_MAXV vectors per thread) until the end.
+constexpr int LN_MAXV = 4;
+template <typename T>
+__global__ void __launch_bounds__(LN_THREADS) layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                                                   const T* __restrict__ w,
+                                                                   const float* __restrict__ mean,
+                                                                   const float* __restrict__ rstd, T* __restrict__ dx,
+                                                                   float* __restrict__ dw_part,
+                                                                   float* __restrict__ db_part, int rows, int cols) {
+  constexpr int V = VecOf<T>::N;
+  __shared__ float sh[LN_THREADS / 32];
+  const int nvec = cols / V;  // host guarantees cols % V == 0 and nvec <= LN_THREADS * LN_MAXV
+  float dwacc[LN_MAXV][V], dbacc[LN_MAXV][V], wv[LN_MAXV][V];
+#pragma unroll
+  for (int k = 0; k < LN_MAXV; ++k) {
+    const int i = threadIdx.x + k * LN_THREADS;
+#pragma unroll
+    for (int j = 0; j < V; ++j) { dwacc[k][j] = 0.f; dbacc[k][j] = 0.f; wv[k][j] = 0.f; }
+    if (i < nvec) load_vec(w + i * V, wv[k]);
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* xr = x + static_cast<size_t>(row) * cols;
+    const T* gr = dy + static_cast<size_t>(row) * cols;
+    T* dr = dx + static_cast<size_t>(row) * cols;
+    const float mu = mean[row], rs = rstd[row];
+    float xh[LN_MAXV][V], gw[LN_MAXV][V];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < LN_MAXV; ++k) {
+      const int i = threadIdx.x + k * LN_THREADS;
+      if (i < nvec) {
+        float g[V];
+        load_vec(xr + i * V, xh[k]);
+        load_vec(gr + i * V, g);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          xh[k][j] = (xh[k][j] - mu) * rs;
+          dwacc[k][j] += g[j] * xh[k][j];
+          dbacc[k][j] += g[j];
+          gw[k][j] = g[j] * wv[k][j];
+          s1 += gw[k][j];
+          s2 += gw[k][j] * xh[k][j];
+        }
+      }
+    }
+    s1 = block_sum<LN_THREADS>(s1, sh) / cols;
+    s2 = block_sum<LN_THREADS>(s2, sh) / cols;
+#pragma unroll
+    for (int k = 0; k < LN_MAXV; ++k) {
+      const int i = threadIdx.x + k * LN_THREADS;
+      if (i < nvec) {
+        float o[V];
+#pragma unroll
+        for (int j = 0; j < V; ++j) o[j] = rs * (gw[k][j] - s1 - xh[k][j] * s2);
+        store_vec(dr + i * V, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < LN_MAXV; ++k) {
+    const int i = threadIdx.x + k * LN_THREADS;
+    if (i < nvec) {
+      float* dwp = dw_part + static_cast<size_t>(blockIdx.x) * cols + i * V;
+      float* dbp = db_part + static_cast<size_t>(blockIdx.x) * cols + i * V;
+#pragma unroll
+      for (int j = 0; j < V; ++j) { dwp[j] = dwacc[k][j]; dbp[j] = dbacc[k][j]; }
+    }
+  }
+}
+
+// out[c] = sum_p part[p, c]; optional second pair for LayerNorm's (dw, db)
+template <typename T>
+__global__ void reduce_parts_kernel(const float* __restrict__ pa, const float* __restrict__ pb, T* __restrict__ oa,
+                                    T* __restrict__ ob, int parts, int cols) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float a = 0.f, b = 0.f;
+  for (int p = 0; p < parts; ++p) {
+    a += pa[static_cast<size_t>(p) * cols + c];
+    if (pb) b += pb[static_cast<size_t>(p) * cols + c];
+  }
+  oa[c] = Cvt<T>::from(a);
+  if (pb && ob) ob[c] = Cvt<T>::from(b);
+}
+
+template <typename T>
+__global__ void colsum_kernel(const T* __restrict__ x, float* __restrict__ part, int rows, int cols) {
+  // grid (col blocks, parts); each thread owns one column and strides over the rows of its part
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float s = 0.f;
+  for (int r = blockIdx.y; r < rows; r += gridDim.y) s += Cvt<T>::to(x[static_cast<size_t>(r) * cols + c]);
+  part[static_cast<size_t>(blockIdx.y) * cols + c] = s;
+}
+
+// ---------------------------------------------------------------------- bias + GeLU
+template <typename T, bool BWD>
+__global__ void bias_gelu_kernel(const T* __restrict__ a, const T* __restrict__ x, const T* __restrict__ bias,
+                                 T* __restrict__ out, long long total_vec, int cols) {
+  constexpr int V = VecOf<T>::N;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total_vec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e = i * V;
+    const int c = static_cast<int>(e % cols);
+    float xv[V], bv[V], o[V];
+    load_vec(x + e, xv);
+    if (bias) {
+      load_vec(bias + c, bv);
+#pragma unroll
+      for (int j = 0; j < V; ++j) xv[j] += bv[j];
+    }
+    if (BWD) {
+      float g[V];
+      load_vec(a + e, g);
+#pragma unroll
+      for (int j = 0; j < V; ++j) o[j] = g[j] * dgelu_f(xv[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j) o[j] = gelu_f(xv[j]);
+    }
+    store_vec(out + e, o);
+  }
+}
+
+// ---------------------------------------------------------------------- bias + dropout + residual
+__device__ __forceinline__ float hash_uniform(unsigned long long seed, unsigned long long idx) {
+  unsigned long long z = seed + idx * 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  z ^= z >> 31;
+  return static_cast<float>(z >> 40) * (1.0f / 16777216.0f);
+}
+template <typename T>
+__global__ void bias_dropout_residual_kernel(const T* __restrict__ x, const T* __restrict__ bias,
+                                             const T* __restrict__ res, T* __restrict__ y, long long total_vec,
+                                             int cols, float p, unsigned long long seed, int mode) {
+  constexpr int V = VecOf<T>::N;
+  const float keep_scale = p < 1.f ? 1.f / (1.f - p) : 0.f;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total_vec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e = i * V;
+    float xv[V];
+    load_vec(x + e, xv);
+    if (mode == 0 && bias) {
+      float bv[V];
+      load_vec(bias + static_cast<int>(e % cols), bv);
+#pragma unroll
+      for (int j = 0; j < V; ++j) xv[j] += bv[j];
+    }
+    if (p > 0.f) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) xv[j] = hash_uniform(seed, e + j) >= p ? xv[j] * keep_scale : 0.f;
+    }
+    if (mode == 0 && res) {
+      float rv[V];
+      load_vec(res + e, rv);
+#pragma unroll
+      for (int j = 0; j < V; ++j) xv[j] += rv[j];
+    }
+    store_vec(y + e, xv);
+  }
+}
+
+// ---------------------------------------------------------------------- rotary (GPT-J, interleaved pairs)
+template <typename T>
+__global__ void rotary_kernel(const T* __restrict__ x, T* __restrict__ y, const long long* __restrict__ pos, int B,
+                              int S, int H, int D, int rd, float log2_base, int inverse) {
+  // one thread per (token, head, pair); dims >= rd are copied by the threads with pair index >= rd/2
+  const long long total = static_cast<long long>(B) * S * H * (D / 2);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int pr = static_cast<int>(i % (D / 2));
+    const long long th = i / (D / 2);       // token * H + head
+    const long long tok = th / H;
+    const size_t off = static_cast<size_t>(th) * D + 2 * pr;
+    float a = Cvt<T>::to(x[off]), b = Cvt<T>::to(x[off + 1]);
+    if (2 * pr < rd) {
+      const float inv_freq = exp2f(-log2_base * (2.0f * pr) / rd);
+      float sn, cs;
+      sincosf(static_cast<float>(pos[tok]) * inv_freq, &sn, &cs);
+      if (inverse) sn = -sn;
+      const float na = a * cs - b * sn;
+      const float nb = b * cs + a * sn;
+      a = na; b = nb;
+    }
+    y[off] = Cvt<T>::from(a);
+    y[off + 1] = Cvt<T>::from(b);
+  }
+}
+
+// ---------------------------------------------------------------------- softmax on scores
+constexpr int SM_THREADS = 128;
+// mode 0: causal (row r of sq keeps cols <= r + (sk - sq)); mode 1: explicit mask (1 = masked -> -10000)
+template <typename T>
+__global__ void __launch_bounds__(SM_THREADS) softmax_fwd_kernel(const T* __restrict__ x,
+                                                                 const uint8_t* __restrict__ mask, T* __restrict__ y,
+                                                                 int sq, int sk, int heads, int mask_b, float scale,
+                                                                 int mode) {
+  __shared__ float sh[SM_THREADS / 32];
+  const long long row = blockIdx.x;  // over batches * sq
+  const int r = static_cast<int>(row % sq);
+  const long long bh = row / sq;
+  const T* xr = x + row * sk;
+  T* yr = y + row * sk;
+  const uint8_t* mr = nullptr;
+  if (mode == 1) {
+    const long long b = bh / heads;
+    mr = mask + ((mask_b == 1 ? 0 : b) * sq + r) * static_cast<long long>(sk);
+  }
+  const int limit = mode == 0 ? min(sk, r + (sk - sq) + 1) : sk;
+  float mx = -CUDART_INF_F;
+  for (int c = threadIdx.x; c < limit; c += SM_THREADS) {
+    float v = Cvt<T>::to(xr[c]) * scale;
+    if (mr && mr[c]) v = -10000.f;
+    mx = fmaxf(mx, v);
+  }
+  mx = block_max<SM_THREADS>(mx, sh);
+  float s = 0.f;
+  for (int c = threadIdx.x; c < limit; c += SM_THREADS) {
+    float v = Cvt<T>::to(xr[c]) * scale;
+    if (mr && mr[c]) v = -10000.f;
+    s += __expf(v - mx);
+  }
+  s = block_sum<SM_THREADS>(s, sh);
+  const float inv = 1.f / s;
+  for (int c = threadIdx.x; c < sk; c += SM_THREADS) {
+    float o = 0.f;
+    if (c < limit) {
+      float v = Cvt<T>::to(xr[c]) * scale;
+      if (mr && mr[c]) v = -10000.f;
+      o = __expf(v - mx) * inv;
+    }
+    yr[c] = Cvt<T>::from(o);
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(SM_THREADS) softmax_bwd_kernel(const T* __restrict__ y, const T* __restrict__ dy,
+                                                                 T* __restrict__ dx, int cols, float scale) {
+  __shared__ float sh[SM_THREADS / 32];
+  const long long row = blockIdx.x;
+  const T* yr = y + row * cols;
+  const T* gr = dy + row * cols;
+  T* dr = dx + row * cols;
+  float s = 0.f;
+  for (int c = threadIdx.x; c < cols; c += SM_THREADS) s += Cvt<T>::to(yr[c]) * Cvt<T>::to(gr[c]);
+  s = block_sum<SM_THREADS>(s, sh);
+  for (int c = threadIdx.x; c < cols; c += SM_THREADS) {
+    const float yy = Cvt<T>::to(yr[c]);
+    dr[c] = Cvt<T>::from(scale * yy * (Cvt<T>::to(gr[c]) - s));
+  }
+}
+
+// ---------------------------------------------------------------------- cross-entropy pieces
+constexpr int CE_THREADS = 256;
+template <typename T>
+__global__ void __launch_bounds__(CE_THREADS) ce_stats_kernel(const T* __restrict__ logits,
+                                                              const long long* __restrict__ labels,
+                                                              float* __restrict__ rowmax, float* __restrict__ sumexp,
+                                                              float* __restrict__ target, int cols, int ld,
+                                                              long long vocab_start) {
+  constexpr int V = VecOf<T>::N;
+  __shared__ float sh[CE_THREADS / 32];
+  const int row = blockIdx.x;
+  const T* lr = logits + static_cast<size_t>(row) * ld;
+  float m = -CUDART_INF_F, s = 0.f;  // online (max, sum exp) per thread
+  const bool vec_ok = (ld % V == 0) && ((reinterpret_cast<uintptr_t>(logits) & 15) == 0);
+  const int nvec = vec_ok ? cols / V : 0;
+  for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
+    float f[V];
+    load_vec(lr + i * V, f);
+    float lm = f[0];
+#pragma unroll
+    for (int j = 1; j < V; ++j) lm = fmaxf(lm, f[j]);
+    const float nm = fmaxf(m, lm);
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc += __expf(f[j] - nm);
+    s = s * __expf(m - nm) + acc;
+    m = nm;
+  }
+  for (int i = nvec * V + threadIdx.x; i < cols; i += CE_THREADS) {
+    const float f = Cvt<T>::to(lr[i]);
+    const float nm = fmaxf(m, f);
+    s = s * __expf(m - nm) + __expf(f - nm);
+    m = nm;
+  }
+  const float gm = block_max<CE_THREADS>(m, sh);
+  const float contrib = (m == -CUDART_INF_F) ? 0.f : s * __expf(m - gm);
+  const float gs = block_sum<CE_THREADS>(contrib, sh);
+  if (threadIdx.x == 0) {
+    rowmax[row] = gm;
+    sumexp[row] = gs;
+    const long long t = labels[row] - vocab_start;
+    target[row] = (t >= 0 && t < cols) ? Cvt<T>::to(lr[t]) : 0.f;
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(CE_THREADS) ce_grad_kernel(T* __restrict__ logits,
+                                                             const long long* __restrict__ labels,
+                                                             const float* __restrict__ lse,
+                                                             const float* __restrict__ scale, int cols, int ld,
+                                                             long long vocab_start) {
+  constexpr int V = VecOf<T>::N;
+  const int row = blockIdx.x;
+  T* lr = logits + static_cast<size_t>(row) * ld;
+  const float l = lse[row], sc = scale[row];
+  const long long t = labels[row] - vocab_start;
+  const bool vec_ok = (ld % V == 0) && ((reinterpret_cast<uintptr_t>(logits) & 15) == 0);
+  const int nvec = vec_ok ? cols / V : 0;
+  for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
+    float f[V];
+    load_vec(lr + i * V, f);
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      float pr = __expf(f[j] - l);
+      if (i * V + j == t) pr -= 1.f;
+      f[j] = pr * sc;
+    }
+    store_vec(lr + i * V, f);
+  }
+  for (int i = nvec * V + threadIdx.x; i < cols; i += CE_THREADS) {
+    float pr = __expf(Cvt<T>::to(lr[i]) - l);
+    if (i == t) pr -= 1.f;
+    lr[i] = Cvt<T>::from(pr * sc);
+  }
+}
+
+// ---------------------------------------------------------------------- AdamW / norms
+template <typename G, typename LP>
+__global__ void adam_kernel(float* __restrict__ p, const G* __restrict__ g, float* __restrict__ m,
+                            float* __restrict__ v, LP* __restrict__ p_lp, long long n, float lr, float beta1,
+                            float beta2, float eps, float wd, float bc1, float bc2, float grad_scale,
+                            const float* __restrict__ inv_scale_dev) {
+  const float gs = grad_scale * (inv_scale_dev ? *inv_scale_dev : 1.f);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float gi = Cvt<G>::to(g[i]) * gs;
+    const float mi = beta1 * m[i] + (1.f - beta1) * gi;
+    const float vi = beta2 * v[i] + (1.f - beta2) * gi * gi;
+    float pi = p[i] * (1.f - lr * wd);
+    pi -= lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
+    m[i] = mi; v[i] = vi; p[i] = pi;
+    if (p_lp) p_lp[i] = Cvt<LP>::from(pi);
+  }
+}
+template <typename T>
+__global__ void sumsq_kernel(const T* __restrict__ x, float* __restrict__ out, long long n) {
+  __shared__ float sh[8];
+  float s = 0.f;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float f = Cvt<T>::to(x[i]);
+    s += f * f;
+  }
+  s = block_sum<256>(s, sh);
+  if (threadIdx.x == 0) atomicAdd(out, s);
+}
+
+// ---------------------------------------------------------------------- n-gram blocking
+// thread `c` compares the (n-1)-gram starting at c with the last (n-1) tokens of the row; on a match the
+// token that followed it is banned. No shared memory is used, so the row length is unbounded.
+__global__ void ngram_ban_kernel(const long long* __restrict__ tokens, float* __restrict__ lprobs, int len, int vocab,
+                                 int n) {
+  const int row = blockIdx.x;
+  const long long* t = tokens + static_cast<size_t>(row) * len;
+  const int starts = len - n + 1;  // candidate n-grams fully inside the row
+  for (int c = threadIdx.x; c < starts; c += blockDim.x) {
+    bool match = true;
+    for (int k = 0; k < n - 1; ++k) {
+      if (t[c + k] != t[len - n + 1 + k]) { match = false; break; }
+    }
+    if (match) {
+      const long long banned = t[c + n - 1];
+      if (banned >= 0 && banned < vocab) lprobs[static_cast<size_t>(row) * vocab + banned] = -CUDART_INF_F;
+    }
+  }
+}
+
+static inline int grid_for(long long work, int threads, int cap = 148 * 16) {
+  long long b = (work + threads - 1) / threads;
+  if (b < 1) b = 1;
+  return static_cast<int>(b < cap ? b : cap);
+}
+#define RET_LAST() return static_cast<int>(cudaGetLastError())
+#define DISPATCH_16(dtype, T, ...)                                   \
+  if ((dtype) == OSLO_DT_BF16) { using T = __nv_bfloat16; __VA_ARGS__ } \
+  else if ((dtype) == OSLO_DT_FP16) { using T = __half; __VA_ARGS__ }   \
+  else if ((dtype) == OSLO_DT_FP32) { using T = float; __VA_ARGS__ }    \
+  else return -2;
+
+}  // namespace oslo
+
+using namespace oslo;
+
+extern "C" int oslo_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+                                  int rows, int cols, float eps, int dtype, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  DISPATCH_16(dtype, T, {
+    if (cols % VecOf<T>::N) return -3;
+    layernorm_fwd_kernel<T><<<rows, LN_THREADS, 0, st>>>((const T*)x, (const T*)w, (const T*)b, (T*)y, mean, rstd,
+                                                          rows, cols, eps);
+  })
+  RET_LAST();
+}
+
+extern "C" int oslo_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                                  void* dx, float* dw_part, float* db_part, void* dw, void* db, int rows, int cols,
+                                  int parts, int dtype, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  DISPATCH_16(dtype, T, {
+    constexpr int V = VecOf<T>::N;
+    if (cols % V || cols / V > LN_THREADS * LN_MAXV) return -3;
+    layernorm_bwd_kernel<T><<<parts, LN_THREADS, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, mean, rstd, (T*)dx,
+                                                          dw_part, db_part, rows, cols);
+    reduce_parts_kernel<T><<<(cols + 255) / 256, 256, 0, st>>>(dw_part, db_part, (T*)dw, (T*)db, parts, cols);
+  })
+  RET_LAST();
+}
+
+extern "C" int oslo_bias_gelu_fwd(const void* x, const void* bias, void* y, long long rows, int cols, int dtype,
+                                  cudaStream_t st) {
+  DISPATCH_16(dtype, T, {
+    constexpr int V = VecOf<T>::N;
+    if (cols % V) return -3;
+    const long long tv = rows * cols / V;
+    if (tv == 0) return 0;
+    bias_gelu_kernel<T, false><<<grid_for(tv, 256), 256, 0, st>>>(nullptr, (const T*)x, (const T*)bias, (T*)y, tv, cols);
+  })
+  RET_LAST();
+}
+extern "C" int oslo_bias_gelu_bwd(const void* dy, const void* x, const void* bias, void* dx, long long rows, int cols,
+                                  int dtype, cudaStream_t st) {
+  DISPATCH_16(dtype, T, {
+    constexpr int V = VecOf<T>::N;
+    if (cols % V) return -3;
+    const long long tv = rows * cols / V;
+    if (tv == 0) return 0;
+    bias_gelu_kernel<T, true><<<grid_for(tv, 256), 256, 0, st>>>((const T*)dy, (const T*)x, (const T*)bias, (T*)dx, tv, cols);
+  })
+  RET_LAST();
+}
+
+extern "C" int oslo_bias_dropout_residual(const void* x, const void* bias, const void* residual, void* y,
+                                          long long rows, int cols, float p, unsigned long long seed, int mode,
+                                          int dtype, cudaStream_t st) {
+  DISPATCH_16(dtype, T, {
+    constexpr int V = VecOf<T>::N;
+    if (cols % V) return -3;
+    const long long tv = rows * cols / V;
+    if (tv == 0) return 0;
+    bias_dropout_residual_kernel<T><<<grid_for(tv, 256), 256, 0, st>>>((const T*)x, (const T*)bias, (const T*)residual,
+                                                                      (T*)y, tv, cols, p, seed, mode);
+  })
+  RET_LAST();
+}
+
+extern "C" int oslo_colsum(const void* x, float* part, float* out, int rows, int cols, int parts, int dtype,
+                           cudaStream_t st) {
+  if (rows <= 0 || cols <= 0) return 0;
+  DISPATCH_16(dtype, T, {
+    dim3 grid((cols + 127) / 128, parts);
+    colsum_kernel<T><<<grid, 128, 0, st>>>((const T*)x, part, rows, cols);
+  })
+  reduce_parts_kernel<float><<<(cols + 255) / 256, 256, 0, st>>>(part, nullptr, out, nullptr, parts, cols);
+  RET_LAST();
+}
+
+extern "C" int oslo_rotary(const void* x, void* y, const long long* positions, int B, int S, int H, int D,
+                           int rotary_dim, float base, int inverse, int dtype, cudaStream_t st) {
+  const long long total = static_cast<long long>(B) * S * H * (D / 2);
+  if (total == 0) return 0;
+  if (D % 2 || rotary_dim % 2 || rotary_dim > D) return -3;
+  DISPATCH_16(dtype, T, {
+    rotary_kernel<T><<<grid_for(total, 256), 256, 0, st>>>((const T*)x, (T*)y, positions, B, S, H, D, rotary_dim,
+                                                          log2f(base), inverse);
+  })
+  RET_LAST();
+}
+
+extern "C" int oslo_causal_softmax_fwd(const void* x, void* y, int batches, int sq, int sk, float scale, int dtype,
+                                       cudaStream_t st) {
+  const long long rows = static_cast<long long>(batches) * sq;
+  if (rows == 0) return 0;
+  DISPATCH_16(dtype, T, {
+    softmax_fwd_kernel<T><<<static_cast<unsigned>(rows), SM_THREADS, 0, st>>>((const T*)x, nullptr, (T*)y, sq, sk, 1, 1,
+                                                                             scale, 0);
+  })
+  RET_LAST();
+}
+extern "C" int oslo_masked_softmax_fwd(const void* x, const uint8_t* mask, void* y, int b, int h, int sq, int sk,
+                                       int mask_b, float scale, int dtype, cudaStream_t st) {
+  const long long rows = static_cast<long long>(b) * h * sq;
+  if (rows == 0) return 0;
+  DISPATCH_16(dtype, T, {
+    softmax_fwd_kernel<T><<<static_cast<unsigned>(rows), SM_THREADS, 0, st>>>((const T*)x, mask, (T*)y, sq, sk, h, mask_b,
+                                                                             scale, 1);
+  })
+  RET_LAST();
+}
+extern "C" int oslo_softmax_bwd(const void* y, const void* dy, void* dx, long long rows, int cols, float scale,
+                                int dtype, cudaStream_t st) {
+  if (rows == 0) return 0;
+  DISPATCH_16(dtype, T, {
+    softmax_bwd_kernel<T><<<static_cast<unsigned>(rows), SM_THREADS, 0, st>>>((const T*)y, (const T*)dy, (T*)dx, cols, scale);
+  })
+  RET_LAST();
+}
+
+extern "C" int oslo_ce_stats(const void* logits, const long long* labels, float* rowmax, float* sumexp, float* target,
+                             int rows, int cols, int ld, long long vocab_start, int dtype, cudaStream_t st) {
+  if (rows == 0) return 0;
+  DISPATCH_16(dtype, T, {
+    ce_stats_kernel<T><<<rows, CE_THREADS, 0, st>>>((const T*)logits, labels, rowmax, sumexp, target, cols, ld, vocab_start);
+  })
+  RET_LAST();
+}
+extern "C" int oslo_ce_grad(void* logits, const long long* labels, const float* lse, const float* scale, int rows,
+                            int cols, int ld, long long vocab_start, int dtype, cudaStream_t st) {
+  if (rows == 0) return 0;
+  DISPATCH_16(dtype, T, {
+    ce_grad_kernel<T><<<rows, CE_THREADS, 0, st>>>((T*)logits, labels, lse, scale, cols, ld, vocab_start);
+  })
+  RET_LAST();
+}
+
+extern "C" int oslo_adam(float* p, const void* g, float* m, float* v, void* p_lp, long long n, float lr, float beta1,
+                         float beta2, float eps, float wd, float bc1, float bc2, float grad_scale,
+                         const float* inv_scale_dev, int g_dtype, int lp_dtype, cudaStream_t st) {
+  if (n == 0) return 0;
+  const int grid = grid_for(n, 256, 148 * 8);
+#define ADAM_LAUNCH(G, LP) \
+  adam_kernel<G, LP><<<grid, 256, 0, st>>>(p, (const G*)g, m, v, (LP*)p_lp, n, lr, beta1, beta2, eps, wd, bc1, bc2, grad_scale, inv_scale_dev)
+  if (g_dtype == OSLO_DT_BF16) {
+    if (lp_dtype == OSLO_DT_FP16) ADAM_LAUNCH(__nv_bfloat16, __half); else ADAM_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  } else if (g_dtype == OSLO_DT_FP16) {
+    if (lp_dtype == OSLO_DT_BF16) ADAM_LAUNCH(__half, __nv_bfloat16); else ADAM_LAUNCH(__half, __half);
+  } else if (g_dtype == OSLO_DT_FP32) {
+    if (lp_dtype == OSLO_DT_FP16) ADAM_LAUNCH(float, __half); else ADAM_LAUNCH(float, __nv_bfloat16);
+  } else {
+    return -2;
+  }
+#undef ADAM_LAUNCH
+  RET_LAST();
+}
+
+extern "C" int oslo_sumsq(const void* x, float* out, long long n, int dtype, cudaStream_t st) {
+  if (n == 0) return 0;
+  DISPATCH_16(dtype, T, { sumsq_kernel<T><<<grid_for(n, 256, 148 * 4), 256, 0, st>>>((const T*)x, out, n); })
+  RET_LAST();
+}
+
+extern "C" int oslo_ngram_ban(const long long* tokens, float* lprobs, int rows, int len, int vocab, int n,
+                              cudaStream_t st) {
+  if (rows == 0 || n <= 0 || len + 1 < n) return 0;
+  ngram_ban_kernel<<<rows, 256, 0, st>>>(tokens, lprobs, len, vocab, n);
+  RET_LAST();
+}

@@ -1,0 +1,102 @@
+// C entry points of the sm_100a kernels. Pointers are device pointers; every launcher enqueues on
+// `stream` and returns 0 or an error code (cudaError_t value, or a negative code for bad arguments).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+// GEMM epilogue flags
+#define GEMM_FLAG_BIAS 1          // + bias[n]
+#define GEMM_FLAG_GELU 2          // tanh-GeLU after bias
+#define GEMM_FLAG_SAVE_PREACT 4   // also write (acc + bias) to aux_out (needed by the GeLU backward)
+#define GEMM_FLAG_DGELU 8         // multiply by gelu'(aux[m,n])
+#define GEMM_FLAG_RESIDUAL 16     // + aux[m,n] (aux has the output dtype)
+#define GEMM_FLAG_OUT_FP32 32     // D is fp32 (default: same 16-bit type as the inputs)
+#define GEMM_FLAG_ACCUMULATE 64   // D += result
+#define GEMM_FLAG_FP16 128        // inputs are fp16 (default bf16)
+
+#define OSLO_DT_BF16 0
+#define OSLO_DT_FP16 1
+#define OSLO_DT_FP32 2
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int oslo_gemm_16bit(const void* A, const void* B, void* D, int M, int N, int K, int lda, int ldb, int ldd,
+                    int a_mn_major, int b_mn_major, const void* bias, const void* aux, int ld_aux, void* aux_out,
+                    int ld_aux_out, int flags, float alpha, int* err_word, int num_sms, cudaStream_t stream);
+
+// LayerNorm over the last dim of [rows, cols]; mean/rstd are fp32 [rows]
+int oslo_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int rows,
+                       int cols, float eps, int dtype, cudaStream_t stream);
+// dw/db partial sums: [parts, cols] fp32 workspaces, reduced by a second kernel into dw/db (input dtype)
+int oslo_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
+                       float* dw_part, float* db_part, void* dw, void* db, int rows, int cols, int parts, int dtype,
+                       cudaStream_t stream);
+
+int oslo_bias_gelu_fwd(const void* x, const void* bias, void* y, long long rows, int cols, int dtype,
+                       cudaStream_t stream);
+int oslo_bias_gelu_bwd(const void* dy, const void* x, const void* bias, void* dx, long long rows, int cols, int dtype,
+                       cudaStream_t stream);
+// y = dropout(x + bias) + residual; the keep-mask is a counter hash of (seed, element index), so backward
+// regenerates it instead of storing it. mode 0 = forward, 1 = backward (x is dy; bias/residual ignored)
+int oslo_bias_dropout_residual(const void* x, const void* bias, const void* residual, void* y, long long rows,
+                               int cols, float p, unsigned long long seed, int mode, int dtype, cudaStream_t stream);
+// column sums of [rows, cols] into fp32 [cols] (bias gradients); part is a [parts, cols] workspace
+int oslo_colsum(const void* x, float* part, float* out, int rows, int cols, int parts, int dtype,
+                cudaStream_t stream);
+
+// GPT-J rotary on [B, S, heads, D] (contiguous), pairs (2i, 2i+1) of the first rotary_dim dims; positions
+// int64 [B, S]; inverse = 1 applies the transpose rotation (backward)
+int oslo_rotary(const void* x, void* y, const long long* positions, int B, int S, int H, int D, int rotary_dim,
+                float base, int inverse, int dtype, cudaStream_t stream);
+
+// softmax on materialised scores
+int oslo_causal_softmax_fwd(const void* x, void* y, int batches, int sq, int sk, float scale, int dtype,
+                            cudaStream_t stream);
+int oslo_masked_softmax_fwd(const void* x, const uint8_t* mask, void* y, int b, int h, int sq, int sk,
+                            int mask_b, float scale, int dtype, cudaStream_t stream);
+int oslo_softmax_bwd(const void* y, const void* dy, void* dx, long long rows, int cols, float scale, int dtype,
+                     cudaStream_t stream);
+
+// cross-entropy pieces over logits [rows, cols] (16-bit or fp32), labels int64 shifted by vocab_start
+int oslo_ce_stats(const void* logits, const long long* labels, float* rowmax, float* sumexp, float* target,
+                  int rows, int cols, int ld, long long vocab_start, int dtype, cudaStream_t stream);
+int oslo_ce_grad(void* logits, const long long* labels, const float* lse, const float* scale, int rows, int cols,
+                 int ld, long long vocab_start, int dtype, cudaStream_t stream);
+
+// AdamW on flat buffers: fp32 master p, 16-bit or fp32 grads, optional 16-bit copy of the new params
+int oslo_adam(float* p, const void* g, float* m, float* v, void* p_lp, long long n, float lr, float beta1,
+              float beta2, float eps, float wd, float bc1, float bc2, float grad_scale, const float* inv_scale_dev,
+              int g_dtype, int lp_dtype, cudaStream_t stream);
+// sum of squares of a flat buffer into out[0] (atomic add; zero it first)
+int oslo_sumsq(const void* x, float* out, long long n, int dtype, cudaStream_t stream);
+
+// n-gram repeat blocking: lprobs[row, tok] = -inf for tokens that would complete a seen n-gram
+int oslo_ngram_ban(const long long* tokens, float* lprobs, int rows, int len, int vocab, int n,
+                   cudaStream_t stream);
+
+// flash attention. q/k/v/o: element strides for (batch, head, seq); last dim contiguous
+int oslo_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const uint8_t* kpm, int B,
+                   int H, int Sq, int Sk, int D, long long q_sb, long long q_sh, long long q_ss, long long k_sb,
+                   long long k_sh, long long k_ss, long long v_sb, long long v_sh, long long v_ss, long long o_sb,
+                   long long o_sh, long long o_ss, float scale, int causal, int window, int dtype,
+                   cudaStream_t stream);
+int oslo_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                   float* delta, float* dq_acc, void* dq, void* dk, void* dv, const uint8_t* kpm, int B, int H,
+                   int Sq, int Sk, int D, long long q_sb, long long q_sh, long long q_ss, long long k_sb,
+                   long long k_sh, long long k_ss, long long v_sb, long long v_sh, long long v_ss, long long o_sb,
+                   long long o_sh, long long o_ss, long long do_sb, long long do_sh, long long do_ss, float scale,
+                   int causal, int window, int dtype, cudaStream_t stream);
+// single-query attention over a static cache [B, H, T, D]; lengths int32 [B]
+int oslo_decode_attn(const void* q, const void* kc, const void* vc, void* o, const int* lengths, float* ws, int B,
+                     int H, int T, int D, int splits, float scale, int window, int dtype, cudaStream_t stream);
+
+// symmetric-memory collectives (comm.cu)
+int oslo_allreduce_symm(void* const* peer_ptrs_dev, void* mc_ptr, uint32_t* const* signal_ptrs_dev, void* out,
+                        long long n, int rank, int world, int dtype, int use_multimem, int* err_word,
+                        cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

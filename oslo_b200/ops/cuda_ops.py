@@ -1,0 +1,332 @@
+"""Autograd wrappers around the sm_100a kernels (``torch.ops.oslo_b200``).
+
+Every function here assumes CUDA tensors; ``oslo_b200.ops.functional`` routes CPU tensors to the
+PyTorch statements instead. GEMM operand layouts (see ``csrc/gemm_sm100.cu``): ``a_mn`` / ``b_mn`` say
+that the operand is stored with the contraction dim as rows, which lets forward, dgrad and wgrad of
+both weight layouts run without a transpose copy.
+"""
+from __future__ import annotations
+
+import itertools
+from typing import Optional
+
+import torch
+from torch import Tensor
+
+from . import load_ext
+from . import reference as ref
+
+FLAG_BIAS, FLAG_GELU, FLAG_SAVE_PREACT, FLAG_DGELU, FLAG_RESIDUAL, FLAG_OUT_FP32, FLAG_ACCUMULATE = 1, 2, 4, 8, 16, 32, 64
+_GELU = ("gelu", "gelu_new", "gelu_tanh", "gelu_pytorch_tanh")
+_16BIT = (torch.bfloat16, torch.float16)
+_dropout_calls = itertools.count()
+
+
+def _ext():
+    return load_ext(required=True)
+
+
+def device_error_code(like: Tensor) -> int:
+    """Code left by a kernel whose bounded wait ran out (0 = none). Synchronises the device."""
+    return int(_ext().error_word(like).item())
+
+
+def reset_device_error(like: Tensor) -> None:
+    _ext().error_word(like).zero_()
+
+
+def _as_operand(t: Tensor) -> Tensor:
+    """2-D tensor with contiguous last dim, 16-byte aligned rows."""
+    if t.stride(-1) != 1 or t.stride(0) % 8 or t.data_ptr() % 16 or t.stride(0) < t.size(1):
+        t = t.contiguous()
+    return t
+
+
+def gemm_ok(*ts: Tensor) -> bool:
+    return all(t.dtype in _16BIT and t.size(-1) % 8 == 0 and t.size(0) > 0 for t in ts)
+
+
+def gemm(a: Tensor, b: Tensor, a_mn: bool = False, b_mn: bool = False, bias: Optional[Tensor] = None,
+         aux: Optional[Tensor] = None, out: Optional[Tensor] = None, aux_out: Optional[Tensor] = None,
+         flags: int = 0, alpha: float = 1.0) -> Tensor:
+    return _ext().gemm(_as_operand(a), _as_operand(b), int(a_mn), int(b_mn), bias, aux, out, aux_out, flags, alpha)
+
+
+def gemm_nn(d: Tensor, w: Tensor) -> Tensor:
+    """``d [n, V] @ w [V, H] -> [n, H]``."""
+    return gemm(d, w, False, True)
+
+
+def gemm_tn(d: Tensor, x: Tensor, out_dtype=None) -> Tensor:
+    """``d[n, V].T @ x[n, H] -> [V, H]`` (fp32 output when ``out_dtype`` is float32)."""
+    return gemm(d, x, True, True, flags=FLAG_OUT_FP32 if out_dtype == torch.float32 else 0)
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, reversed_, gelu):
+        k = x.size(-1)
+        x2 = x.reshape(-1, k)
+        need_grad = torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad or
+                                                 (bias is not None and bias.requires_grad))
+        flags = (FLAG_BIAS if bias is not None else 0) | (FLAG_GELU if gelu else 0)
+        n = weight.size(1) if reversed_ else weight.size(0)
+        z = None
+        if gelu and need_grad:
+            flags |= FLAG_SAVE_PREACT
+            z = torch.empty(x2.size(0), n, dtype=x.dtype, device=x.device)
+        y = gemm(x2, weight, False, reversed_, bias=bias, aux_out=z, flags=flags)
+        ctx.save_for_backward(x2, weight, z)
+        ctx.reversed, ctx.has_bias, ctx.in_shape = reversed_, bias is not None, x.shape
+        ctx.bias_dtype = bias.dtype if bias is not None else None
+        return y.view(*x.shape[:-1], n)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight, z = ctx.saved_tensors
+        ext = _ext()
+        dy2 = dy.reshape(-1, dy.size(-1))
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        if z is not None:
+            dy2 = ext.bias_gelu_bwd(dy2, z, None)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, weight, False, not ctx.reversed).view(ctx.in_shape)
+        if ctx.needs_input_grad[1]:
+            dw = gemm(x2, dy2, True, True) if ctx.reversed else gemm(dy2, x2, True, True)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = ext.colsum(dy2).to(ctx.bias_dtype)
+        return dx, dw, db, None, None
+
+
+def linear(x: Tensor, weight: Tensor, bias: Optional[Tensor], reversed_: bool, activation: Optional[str]) -> Tensor:
+    if activation is not None and activation not in _GELU:
+        raise ValueError(f"unsupported fused activation {activation!r}")
+    n = weight.size(1) if reversed_ else weight.size(0)
+    ok = (x.dtype in _16BIT and weight.dtype == x.dtype and x.size(-1) % 8 == 0 and n % 8 == 0 and x.numel() > 0
+          and (bias is None or bias.dtype == x.dtype))
+    if not ok:  # fp32 or ragged shapes: library GEMM, same semantics
+        return ref.linear(x, weight, bias, reversed_, activation)
+    return _Linear.apply(x, weight, bias, reversed_, activation is not None)
+
+
+class _LayerNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, b, eps):
+        xc = x.contiguous()
+        y, mean, rstd = _ext().layernorm_fwd(xc, w, b, eps)
+        ctx.save_for_backward(xc, w, mean, rstd)
+        ctx.has_bias = b is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, w, mean, rstd = ctx.saved_tensors
+        dx, dw, db = _ext().layernorm_bwd(dy.contiguous(), xc, w, mean, rstd)
+        return dx, dw, (db if ctx.has_bias else None), None
+
+
+def layer_norm(x: Tensor, w: Tensor, b: Optional[Tensor], eps: float) -> Tensor:
+    vec = 4 if x.dtype == torch.float32 else 8
+    cols = x.size(-1)
+    if x.dtype != w.dtype or cols % vec or cols // vec > 1024 or x.numel() == 0:
+        return ref.layer_norm(x, w, b, eps)
+    return _LayerNorm.apply(x, w, b, eps)
+
+
+class _BiasGelu(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, bias):
+        xc = x.contiguous()
+        ctx.save_for_backward(xc, bias)
+        return _ext().bias_gelu_fwd(xc, bias)
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, bias = ctx.saved_tensors
+        dx = _ext().bias_gelu_bwd(dy.contiguous(), xc, bias)
+        db = None
+        if bias is not None and ctx.needs_input_grad[1]:
+            db = _ext().colsum(dx.view(-1, dx.size(-1))).to(bias.dtype)
+        return dx, db
+
+
+def bias_gelu(x: Tensor, bias: Optional[Tensor]) -> Tensor:
+    vec = 4 if x.dtype == torch.float32 else 8
+    if x.size(-1) % vec or (bias is not None and bias.dtype != x.dtype) or x.numel() == 0:
+        return ref.bias_gelu(x, bias)
+    return _BiasGelu.apply(x, bias)
+
+
+class _BiasDropoutResidual(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, bias, residual, p, seed):
+        ctx.p, ctx.seed = p, seed
+        ctx.has_bias, ctx.has_res = bias is not None, residual is not None
+        ctx.bias_dtype = bias.dtype if bias is not None else None
+        r = residual.contiguous() if residual is not None else None
+        return _ext().bias_dropout_residual(x.contiguous(), bias, r, p, seed, 0)
+
+    @staticmethod
+    def backward(ctx, dy):
+        dy = dy.contiguous()
+        dx = _ext().bias_dropout_residual(dy, None, None, ctx.p, ctx.seed, 1) if ctx.p > 0 else dy
+        db = _ext().colsum(dx.view(-1, dx.size(-1))).to(ctx.bias_dtype) if ctx.has_bias else None
+        return dx, db, (dy if ctx.has_res else None), None, None
+
+
+def bias_dropout_residual(x: Tensor, bias: Optional[Tensor], residual: Optional[Tensor], p: float, training: bool) -> Tensor:
+    vec = 4 if x.dtype == torch.float32 else 8
+    p = float(p) if training else 0.0
+    if x.size(-1) % vec or x.numel() == 0 or (bias is not None and bias.dtype != x.dtype) or \
+            (residual is not None and (residual.dtype != x.dtype or residual.shape != x.shape)):
+        return ref.bias_dropout_residual(x, bias, residual, p, training)
+    # the mask is a hash of (seed, element index): the seed follows torch's seed and a call counter so that
+    # tensor-parallel ranks, which run the same call sequence under one seed, drop the same elements
+    seed = (torch.initial_seed() * 1000003 + next(_dropout_calls)) & 0x7FFFFFFFFFFFFFFF
+    return _BiasDropoutResidual.apply(x, bias, residual, p, seed)
+
+
+class _Rotary(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, positions, rotary_dim, base):
+        ctx.save_for_backward(positions)
+        ctx.rd, ctx.base = rotary_dim, base
+        return _ext().rotary(x.contiguous(), positions, rotary_dim, base, False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (positions,) = ctx.saved_tensors
+        return _ext().rotary(dy.contiguous(), positions, ctx.rd, ctx.base, True), None, None, None
+
+
+def rotary_interleaved(x: Tensor, positions: Tensor, rotary_dim: int, base: float) -> Tensor:
+    if positions.dim() == 1:
+        positions = positions.unsqueeze(0).expand(x.size(0), -1)
+    positions = positions.to(torch.long).contiguous()
+    return _Rotary.apply(x, positions, rotary_dim, base)
+
+
+def flash_supported(q: Tensor, k: Tensor, v: Tensor) -> bool:
+    if q.dtype not in _16BIT or q.size(-1) not in (64, 128, 256) or q.numel() == 0:
+        return False
+    return q.dtype == k.dtype == v.dtype
+
+
+def _attn_operand(t: Tensor) -> Tensor:
+    if t.stride(-1) != 1 or any(s % 8 for s in t.stride()[:-1]) or t.data_ptr() % 16:
+        t = t.contiguous()
+    return t
+
+
+class _Flash(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, window, scale, kpm):
+        q, k, v = _attn_operand(q), _attn_operand(k), _attn_operand(v)
+        o, lse = _ext().flash_fwd(q, k, v, scale, causal, window, kpm)
+        ctx.save_for_backward(q, k, v, o, lse, kpm)
+        ctx.cfg = (scale, causal, window)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse, kpm = ctx.saved_tensors
+        scale, causal, window = ctx.cfg
+        dq, dk, dv = _ext().flash_bwd(_attn_operand(do), q, k, v, o, lse, scale, causal, window, kpm)
+        return dq, dk, dv, None, None, None, None
+
+
+def flash_attention(q: Tensor, k: Tensor, v: Tensor, causal: bool, window: Optional[int], scale: float,
+                    key_padding_mask: Optional[Tensor]) -> Tensor:
+    kpm = None
+    if key_padding_mask is not None:
+        kpm = (key_padding_mask != 0).to(torch.uint8).contiguous()
+    return _Flash.apply(q, k, v, bool(causal), int(window or 0), float(scale), kpm)
+
+
+def decode_attention(q: Tensor, k_cache: Tensor, v_cache: Tensor, lengths: Tensor, scale: float,
+                     window: Optional[int]) -> Tensor:
+    return _ext().decode_attn(q.contiguous(), k_cache, v_cache, lengths.to(torch.int32), float(scale), int(window or 0))
+
+
+class _CausalSoftmax(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, scale):
+        y = _ext().causal_softmax_fwd(x.contiguous(), scale)
+        ctx.save_for_backward(y)
+        ctx.scale = scale
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (y,) = ctx.saved_tensors
+        return _ext().softmax_bwd(y, dy.contiguous(), ctx.scale), None
+
+
+def causal_softmax(x: Tensor, scale: float) -> Tensor:
+    return _CausalSoftmax.apply(x, float(scale))
+
+
+class _MaskedSoftmax(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, mask, scale):
+        y = _ext().masked_softmax_fwd(x.contiguous(), mask, scale)
+        ctx.save_for_backward(y)
+        ctx.scale = scale
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (y,) = ctx.saved_tensors
+        return _ext().softmax_bwd(y, dy.contiguous(), ctx.scale), None, None
+
+
+def masked_softmax(x: Tensor, mask: Tensor, scale: float) -> Tensor:
+    return _MaskedSoftmax.apply(x, mask.to(torch.uint8).contiguous(), float(scale))
+
+
+def ce_stats(logits: Tensor, labels: Tensor, vocab_start: int):
+    return _ext().ce_stats(logits, labels.contiguous(), int(vocab_start))
+
+
+def ce_grad_(logits: Tensor, labels: Tensor, vocab_start: int, lse: Tensor, scale: Tensor) -> Tensor:
+    return _ext().ce_grad_(logits, labels.contiguous(), int(vocab_start), lse.contiguous(), scale.contiguous())
+
+
+class _CrossEntropy(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, labels, ignore_index):
+        lg = logits if logits.stride(-1) == 1 else logits.contiguous()
+        mx, se, tg = ce_stats(lg, labels, 0)
+        lse = torch.log(se) + mx
+        valid = labels != ignore_index
+        count = valid.sum().clamp(min=1).to(torch.float32)
+        ctx.save_for_backward(lg, labels, lse, valid, count)
+        return torch.where(valid, lse - tg, torch.zeros_like(lse)).sum() / count
+
+    @staticmethod
+    def backward(ctx, g):
+        lg, labels, lse, valid, count = ctx.saved_tensors
+        scale = (g.float() / count) * valid.to(torch.float32)
+        return ce_grad_(lg.clone(), labels, 0, lse, scale), None, None
+
+
+def cross_entropy(logits: Tensor, labels: Tensor, ignore_index: int) -> Tensor:
+    if logits.dim() != 2 or logits.dtype not in (torch.bfloat16, torch.float16, torch.float32):
+        return ref.cross_entropy(logits, labels, ignore_index)
+    return _CrossEntropy.apply(logits, labels, ignore_index)
+
+
+def linear_cross_entropy(hidden: Tensor, weight: Tensor, bias: Optional[Tensor], labels: Tensor, ignore_index: int,
+                         chunk_rows: int) -> Tensor:
+    from ..parallel.vocab_parallel import linear_cross_entropy as lce
+    fused = hidden.dtype in _16BIT and weight.dtype == hidden.dtype and hidden.size(-1) % 8 == 0 \
+        and weight.size(0) % 8 == 0
+    return lce(hidden, weight, bias, labels, ignore_index, chunk_rows, fused=fused)
+
+
+def ban_repeated_ngrams(tokens: Tensor, lprobs: Tensor, n: int) -> Tensor:
+    if lprobs.dtype != torch.float32 or not lprobs.is_contiguous():
+        return ref.ban_repeated_ngrams(tokens, lprobs, n)
+    return _ext().ngram_ban_(tokens.to(torch.long).contiguous(), lprobs, int(n))

@@ -1,0 +1,162 @@
+"""Fused AdamW on flat buffers with fp32 master weights, optionally sharded over the data-parallel
+group (ZeRO stage 1).
+
+The reference leaves optimisation to ``torch.optim.Adam`` or DeepSpeed ZeRO wrapped around
+``model.gpu_modules()`` (USAGE.md:128-155, :366-387). Here the same role is played natively:
+
+* all parameters of a dtype live in one flat low-precision buffer (``param.data`` are views) and all
+  gradients in one flat buffer (``param.grad`` are views), so a step is ONE kernel launch and a
+  data-parallel reduction is a handful of large collectives instead of one per tensor;
+* master weights and both moments are fp32; the kernel writes the refreshed bf16/fp16 copy;
+* with ``shard_group`` every rank keeps master/moments for ``1/dp`` of the flat buffer only:
+  gradients are reduce-scattered, the owned shard is stepped, parameters are all-gathered;
+* gradient clipping uses a device-side norm, no host synchronisation.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Iterable, List, Optional
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+from . import ops
+
+
+class FlatBuffers:
+    """One flat parameter buffer + one flat gradient buffer per dtype; tensors become views."""
+
+    def __init__(self, params: Iterable[torch.nn.Parameter], pad_to: int = 1, grad_dtype: Optional[torch.dtype] = None):
+        self.params: List[torch.nn.Parameter] = []
+        seen = set()
+        for p in params:
+            if p.requires_grad and id(p) not in seen and p.numel() > 0:
+                seen.add(id(p))
+                self.params.append(p)
+        if not self.params:
+            raise ValueError("no trainable parameters")
+        dts = {p.dtype for p in self.params}
+        if len(dts) != 1:
+            raise ValueError(f"parameters must share one dtype, got {dts}")
+        self.dtype = self.params[0].dtype
+        self.device = self.params[0].device
+        self.offsets: List[int] = []
+        n = 0
+        for p in self.params:
+            self.offsets.append(n)
+            n += (p.numel() + 7) // 8 * 8  # keep every tensor 16-byte aligned for vector / TMA access
+        self.numel = n
+        self.padded = (n + pad_to - 1) // pad_to * pad_to
+        self.flat_p = torch.zeros(self.padded, dtype=self.dtype, device=self.device)
+        self.flat_g = torch.zeros(self.padded, dtype=grad_dtype or self.dtype, device=self.device)
+        for p, off in zip(self.params, self.offsets):
+            view = self.flat_p[off: off + p.numel()].view(p.shape)
+            view.copy_(p.data)
+            p.data = view
+            p.grad = self.flat_g[off: off + p.numel()].view(p.shape)
+
+    def zero_grad(self) -> None:
+        self.flat_g.zero_()
+        for p, off in zip(self.params, self.offsets):  # re-attach in case something set grads to None
+            if p.grad is None or p.grad.data_ptr() != self.flat_g.data_ptr() + off * self.flat_g.element_size():
+                p.grad = self.flat_g[off: off + p.numel()].view(p.shape)
+
+
+class FusedAdamW:
+    """AdamW with fp32 master weights on ``FlatBuffers``; ``shard_group`` turns on ZeRO-1 sharding."""
+
+    def __init__(self, params: Iterable[torch.nn.Parameter], lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 0.01, max_grad_norm: Optional[float] = None, shard_group=None,
+                 grad_average_group=None, model_parallel_group=None) -> None:
+        self.lr, self.betas, self.eps, self.weight_decay = lr, tuple(betas), eps, weight_decay
+        self.max_grad_norm = max_grad_norm
+        self.shard_group = shard_group
+        self.model_parallel_group = model_parallel_group
+        self.shards = dist.get_world_size(shard_group) if shard_group is not None else 1
+        self.shard_rank = dist.get_rank(shard_group) if shard_group is not None else 0
+        self.grad_average_group = grad_average_group
+        self.buf = FlatBuffers(params, pad_to=8 * self.shards)
+        n = self.buf.padded // self.shards
+        self.shard_numel = n
+        lo = self.shard_rank * n
+        self._lo, self._hi = lo, lo + n
+        dev = self.buf.device
+        self.master = self.buf.flat_p[lo: lo + n].float()
+        self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.step_count = 0
+        self.grads_already_reduced = False  # set by DistributedDataParallel, which all-reduces buckets itself
+        self.param_groups = [dict(params=self.buf.params, lr=lr, betas=self.betas, eps=eps, weight_decay=weight_decay)]
+
+    # ------------------------------------------------------------------ API
+    def zero_grad(self, set_to_none: bool = False) -> None:
+        self.buf.zero_grad()
+
+    def grad_norm(self, g: Tensor) -> Tensor:
+        """2-norm of the (sharded) gradient over all shards and model-parallel ranks, as a device scalar."""
+        if g.is_cuda and ops.kernels_available():
+            sq = ops.load_ext().sumsq(g)
+        else:
+            sq = g.float().pow(2).sum().reshape(1)
+        for grp in (self.shard_group, self.model_parallel_group):
+            if grp is not None and dist.get_world_size(grp) > 1:
+                dist.all_reduce(sq, group=grp)
+        return sq.sqrt()
+
+    @torch.no_grad()
+    def step(self) -> None:
+        self.step_count += 1
+        lr = self.param_groups[0]["lr"]
+        b1, b2 = self.betas
+        g_full = self.buf.flat_g
+        if self.shards > 1 and self.grads_already_reduced:
+            g = g_full[self._lo: self._hi]
+            grad_scale = 1.0 / self.shards
+        elif self.shards > 1:
+            g = torch.empty(self.shard_numel, dtype=g_full.dtype, device=g_full.device)
+            if dist.get_backend(self.shard_group) == "gloo":
+                dist.all_reduce(g_full, group=self.shard_group)
+                g.copy_(g_full[self._lo: self._hi])
+            else:
+                dist.reduce_scatter_tensor(g, g_full, group=self.shard_group)
+            grad_scale = 1.0 / self.shards
+        else:
+            g = g_full
+            grad_scale = 1.0
+        inv = None
+        if self.max_grad_norm is not None:
+            norm = self.grad_norm(g) * grad_scale
+            inv = torch.clamp(self.max_grad_norm / (norm + 1e-6), max=1.0).float()
+        lp = self.buf.flat_p[self._lo: self._hi]
+        if g.is_cuda and ops.kernels_available():
+            ops.load_ext().adam_step(self.master, g, self.exp_avg, self.exp_avg_sq,
+                                     lp if lp.dtype != torch.float32 else None, lr, b1, b2, self.eps,
+                                     self.weight_decay, self.step_count, grad_scale, inv)
+            if lp.dtype == torch.float32:
+                lp.copy_(self.master)
+        else:
+            scale = grad_scale * (float(inv) if inv is not None else 1.0)
+            ops.reference.adam_step(self.master, g, self.exp_avg, self.exp_avg_sq, self.step_count, lr, b1, b2,
+                                    self.eps, self.weight_decay, scale, lp)
+        if self.shards > 1:
+            if dist.get_backend(self.shard_group) == "gloo":
+                parts = [torch.empty_like(lp) for _ in range(self.shards)]
+                dist.all_gather(parts, lp.contiguous(), group=self.shard_group)
+                self.buf.flat_p.copy_(torch.cat(parts))
+            else:
+                dist.all_gather_into_tensor(self.buf.flat_p, lp.contiguous(), group=self.shard_group)
+
+    # ------------------------------------------------------------------ checkpoint sidecar
+    def state_dict(self) -> Dict[str, object]:
+        return dict(step=self.step_count, master=self.master.cpu(), exp_avg=self.exp_avg.cpu(),
+                    exp_avg_sq=self.exp_avg_sq.cpu(), shard_rank=self.shard_rank, shards=self.shards, lr=self.lr)
+
+    def load_state_dict(self, sd: Dict[str, object]) -> None:
+        if sd["shards"] != self.shards or sd["shard_rank"] != self.shard_rank:
+            raise ValueError("optimizer state was saved with a different sharding")
+        self.step_count = int(sd["step"])
+        self.master.copy_(sd["master"])
+        self.exp_avg.copy_(sd["exp_avg"])
+        self.exp_avg_sq.copy_(sd["exp_avg_sq"])
+        self.buf.flat_p[self._lo: self._hi].copy_(self.master)

@@ -1,0 +1,139 @@
+"""Data parallelism: bucketed gradient reduction over the data-parallel group, overlapped with backward
+and aware of micro-batches.
+
+The reference has no gradient code of its own: users wrap ``model.gpu_modules()`` in torch DDP or
+DeepSpeed with ``process_group=model.mpu.get_data_parallel_group()`` (USAGE.md:128-155), and under
+pipeline parallelism torch DDP only reduces the first micro-batch's backward. This wrapper
+
+* keeps gradients in one flat buffer cut into buckets in reverse parameter order,
+* fires an asynchronous all-reduce per bucket as soon as every gradient of the bucket has been
+  accumulated - but only during the backward of the LAST micro-batch of a step (earlier
+  micro-batches accumulate locally), so the reduction overlaps that backward and runs once per step,
+* hands the already-averaged gradients to the optimizer (``FusedAdamW`` then only steps its shard).
+
+``torch.nn.parallel.DistributedDataParallel`` around ``gpu_modules()`` keeps working for steps that
+have a single micro-batch.
+"""
+from __future__ import annotations
+
+from contextlib import contextmanager
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..optim import FlatBuffers, FusedAdamW
+from .mpu import MPU
+
+
+class DistributedDataParallel(nn.Module):
+    def __init__(self, model: nn.Module, mpu: MPU, optimizer: Optional[FusedAdamW] = None,
+                 bucket_mb: float = 256.0, num_micro_batches: Optional[int] = None) -> None:
+        super().__init__()
+        self.module = model
+        self.mpu = mpu
+        self.group = mpu.get_data_parallel_group()
+        self.world = mpu.get_data_parallel_world_size()
+        self.optimizer = optimizer
+        gm = model.gpu_modules() if hasattr(model, "gpu_modules") else model
+        self.buf = optimizer.buf if optimizer is not None else FlatBuffers(gm.parameters())
+        self.sync = True
+        self._pending: List = []
+        self._ready: List[int] = []
+        self._bucket_of = {}
+        self.buckets: List[tuple] = []
+        self._build_buckets(int(bucket_mb * 2 ** 20))
+        for p in self.buf.params:
+            p.register_post_accumulate_grad_hook(self._hook)
+        eng = getattr(model, "_pipe_engine", None)
+        if eng is not None:
+            eng.on_last_backward = lambda last: setattr(self, "sync", bool(last))
+            self._pipelined = True
+        else:
+            self._pipelined = False
+        if optimizer is not None:
+            optimizer.grads_already_reduced = True
+            self._wrap_optimizer_step(optimizer)
+
+    # ------------------------------------------------------------------ buckets
+    def _build_buckets(self, bucket_bytes: int) -> None:
+        esize = self.buf.flat_g.element_size()
+        params, offsets = self.buf.params, self.buf.offsets
+        end = self.buf.padded
+        cur: List[int] = []
+        hi = end
+        # walk parameters from the last (its gradient is produced first in backward) to the first
+        for idx in range(len(params) - 1, -1, -1):
+            cur.append(idx)
+            lo = offsets[idx]
+            if (hi - lo) * esize >= bucket_bytes or idx == 0:
+                b = len(self.buckets)
+                self.buckets.append((lo, hi, list(cur)))
+                for i in cur:
+                    self._bucket_of[id(params[i])] = b
+                self._ready.append(0)
+                cur, hi = [], lo
+
+    def _hook(self, p: torch.Tensor) -> None:
+        if not self.sync or self.world == 1:
+            return
+        b = self._bucket_of[id(p)]
+        self._ready[b] += 1
+        if self._ready[b] == len(self.buckets[b][2]):
+            self._launch(b)
+
+    def _launch(self, b: int) -> None:
+        lo, hi, _ = self.buckets[b]
+        self._ready[b] = -(10 ** 9)  # launched
+        chunk = self.buf.flat_g[lo:hi]
+        self._pending.append(dist.all_reduce(chunk, group=self.group, async_op=True))
+
+    def finish_gradient_sync(self) -> None:
+        """Wait for the bucket reductions of this step; launches any bucket that never became ready
+        (parameters without gradient this step) so every rank issues the same collectives."""
+        if self.world > 1:
+            for b in range(len(self.buckets)):
+                if self._ready[b] >= 0:
+                    self._launch(b)
+            for w in self._pending:
+                w.wait()
+            if self.optimizer is None:
+                self.buf.flat_g.div_(self.world)
+        self._pending = []
+        self._ready = [0] * len(self.buckets)
+
+    def _wrap_optimizer_step(self, opt: FusedAdamW) -> None:
+        inner = opt.step
+        ddp = self
+
+        def step():
+            ddp.finish_gradient_sync()
+            return inner()
+
+        opt.step = step
+
+    # ------------------------------------------------------------------ module API
+    @contextmanager
+    def no_sync(self):
+        """Accumulate gradients locally (use for every micro-batch of a step except the last)."""
+        prev = self.sync
+        self.sync = False
+        try:
+            yield
+        finally:
+            self.sync = prev
+
+    def forward(self, *args, **kwargs):
+        if self._pipelined:
+            self.sync = False  # the pipeline engine switches it on for the last micro-batch
+        return self.module(*args, **kwargs)
+
+    def gpu_modules(self):
+        return self.module.gpu_modules()
+
+    def __getattr__(self, name):
+        try:
+            return super().__getattr__(name)
+        except AttributeError:
+            return getattr(self.module, name)

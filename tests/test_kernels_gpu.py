@@ -1,0 +1,268 @@
+"""Each sm_100a kernel against a plain PyTorch fp32 statement of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from oslo_b200 import ops
+    from oslo_b200.ops import cuda_ops
+    assert ops.load_ext(required=True) is not None
+    return ops, cuda_ops
+
+
+def _close(a, b, atol, rtol=2e-2):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    assert torch.allclose(a, b, atol=atol, rtol=rtol), f"max abs err {err}"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (300, 520, 200), (1024, 128, 4096), (77 * 8, 1024, 1024), (8, 16384, 4096)])
+def test_gemm_layouts(dtype, a_mn, b_mn, M, N, K):
+    ops, co = _ops()
+    torch.manual_seed(0)
+    A = torch.randn(M, K, device="cuda", dtype=dtype)
+    B = torch.randn(N, K, device="cuda", dtype=dtype)
+    a = A.t().contiguous() if a_mn else A
+    b = B.t().contiguous() if b_mn else B
+    if (a_mn and M % 8) or (b_mn and N % 8) or K % 8:
+        pytest.skip("row stride must be a multiple of 16 bytes")
+    out = co.gemm(a, b, a_mn, b_mn)
+    ref = A.float() @ B.float().t()
+    _close(out, ref, atol=0.02 * math.sqrt(K), rtol=2e-2)
+    assert co.device_error_code(out) == 0
+
+
+def test_gemm_epilogues():
+    ops, co = _ops()
+    torch.manual_seed(1)
+    M, N, K = 384, 768, 512
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16) * 0.5
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    z_ref = x.float() @ w.float().t() + bias.float()
+    z = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    y = co.gemm(x, w, bias=bias, aux_out=z, flags=co.FLAG_BIAS | co.FLAG_GELU | co.FLAG_SAVE_PREACT)
+    _close(z, z_ref, atol=0.03)
+    _close(y, ops.reference.gelu_tanh(z_ref), atol=0.03)
+    y2 = co.gemm(x, w, bias=bias, aux=res, flags=co.FLAG_BIAS | co.FLAG_RESIDUAL)
+    _close(y2, z_ref + res.float(), atol=0.05)
+    acc = torch.ones(M, N, device="cuda", dtype=torch.float32)
+    co.gemm(x, w, out=acc, flags=co.FLAG_OUT_FP32 | co.FLAG_ACCUMULATE, alpha=0.5)
+    _close(acc, 1.0 + 0.5 * (x.float() @ w.float().t()), atol=0.03)
+    g = torch.randn(M, K, device="cuda", dtype=torch.bfloat16) * 0.5
+    dz = co.gemm(g, w, aux=z, flags=co.FLAG_DGELU)
+    zz = z.float().requires_grad_(True)
+    ops.reference.gelu_tanh(zz).backward(torch.ones_like(zz))
+    _close(dz, (g.float() @ w.float().t()) * zz.grad, atol=0.05)
+
+
+@pytest.mark.parametrize("reversed_", [False, True])
+@pytest.mark.parametrize("act", [None, "gelu_new"])
+def test_linear_autograd(reversed_, act):
+    ops, co = _ops()
+    torch.manual_seed(2)
+    x = (torch.randn(4, 96, 256, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(256, 512, device="cuda") * 0.05).to(torch.bfloat16)
+    w = (w if reversed_ else w.t().contiguous()).requires_grad_(True)
+    b = torch.randn(512, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    y = ops.linear(x, w, b, reversed_, act)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf, wf, bf = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+    yr = ops.reference.linear(xf, wf, bf, reversed_, act)
+    yr.backward(g.float())
+    _close(y, yr, atol=0.05)
+    _close(x.grad, xf.grad, atol=0.05)
+    _close(w.grad, wf.grad, atol=0.3, rtol=3e-2)
+    _close(b.grad, bf.grad, atol=0.3, rtol=3e-2)
+
+
+@pytest.mark.parametrize("dtype,cols", [(torch.bfloat16, 4096), (torch.bfloat16, 768), (torch.float32, 2048), (torch.float16, 48)])
+def test_layernorm(dtype, cols):
+    ops, _ = _ops()
+    torch.manual_seed(3)
+    x = torch.randn(37, 5, cols, device="cuda").to(dtype).requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(cols, device="cuda")).to(dtype).requires_grad_(True)
+    b = (0.1 * torch.randn(cols, device="cuda")).to(dtype).requires_grad_(True)
+    y = ops.layer_norm(x, w, b, 1e-5)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf, wf, bf = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+    yr = ops.reference.layer_norm(xf, wf, bf, 1e-5)
+    yr.backward(g.float())
+    tol = 1e-4 if dtype == torch.float32 else 3e-2
+    _close(y, yr, atol=tol)
+    _close(x.grad, xf.grad, atol=tol)
+    _close(w.grad, wf.grad, atol=tol * 20, rtol=3e-2)
+    _close(b.grad, bf.grad, atol=tol * 20, rtol=3e-2)
+
+
+def test_bias_gelu_and_dropout():
+    ops, _ = _ops()
+    torch.manual_seed(4)
+    x = torch.randn(64, 33, 1024, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    b = torch.randn(1024, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    y = ops.bias_gelu(x, b)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf, bf = x.detach().float().requires_grad_(True), b.detach().float().requires_grad_(True)
+    yr = ops.reference.bias_gelu(xf, bf)
+    yr.backward(g.float())
+    _close(y, yr, atol=2e-2)
+    _close(x.grad, xf.grad, atol=2e-2)
+    _close(b.grad, bf.grad, atol=1.0, rtol=3e-2)
+    r = torch.randn_like(x)
+    out = ops.bias_dropout_residual(x.detach(), b.detach(), r, 0.0, True)
+    _close(out, x.detach().float() + b.detach().float() + r.float(), atol=3e-2)
+    xd = x.detach().clone().requires_grad_(True)
+    out = ops.bias_dropout_residual(xd, None, None, 0.25, True)
+    kept = (out != 0).float().mean().item()
+    assert abs(kept - 0.75) < 0.01
+    out.backward(torch.ones_like(out))
+    assert torch.equal((xd.grad != 0), (out != 0) | ((xd.detach() == 0) & (xd.grad != 0)))
+    _close(xd.grad[out != 0], torch.full_like(xd.grad[out != 0], 1 / 0.75), atol=1e-2)
+
+
+def test_rotary():
+    ops, _ = _ops()
+    torch.manual_seed(5)
+    x = torch.randn(2, 33, 4, 256, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    pos = torch.arange(7, 40, device="cuda").unsqueeze(0).expand(2, -1).contiguous()
+    y = ops.rotary_interleaved(x, pos, 64)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf = x.detach().float().requires_grad_(True)
+    yr = ops.reference.rotary_interleaved(xf, pos, 64)
+    yr.backward(g.float())
+    _close(y, yr, atol=2e-2)
+    _close(x.grad, xf.grad, atol=2e-2)
+
+
+def test_softmax_kernels():
+    ops, _ = _ops()
+    torch.manual_seed(6)
+    x = torch.randn(6, 40, 40, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    y = ops.scaled_upper_triang_masked_softmax(x, 0.3)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf = x.detach().float()
+    yr = ops.reference.scaled_upper_triang_masked_softmax(xf, 0.3)
+    _close(y, yr, atol=1e-2)
+    assert (y.triu(1) == 0).all()
+    _close(x.grad, ops.reference.softmax_backward(yr, g.float(), 0.3), atol=1e-2)
+    x4 = torch.randn(2, 3, 17, 50, device="cuda").to(torch.float16)
+    mask = (torch.rand(2, 1, 17, 50, device="cuda") < 0.3).to(torch.uint8)
+    _close(ops.scaled_masked_softmax(x4, mask, 2.0), ops.reference.scaled_masked_softmax(x4.float(), mask, 2.0), atol=2e-3)
+
+
+@pytest.mark.parametrize("vocab", [50400, 1000, 50257])
+def test_cross_entropy(vocab):
+    ops, _ = _ops()
+    torch.manual_seed(7)
+    lg = (torch.randn(65, vocab, device="cuda") * 2).to(torch.bfloat16).requires_grad_(True)
+    lab = torch.randint(0, vocab, (65,), device="cuda")
+    lab[3] = -100
+    loss = ops.cross_entropy(lg, lab)
+    loss.backward()
+    lf = lg.detach().float().requires_grad_(True)
+    lr = ops.reference.cross_entropy(lf, lab)
+    lr.backward()
+    assert abs(loss.item() - lr.item()) < 2e-3
+    _close(lg.grad, lf.grad, atol=2e-4, rtol=5e-2)
+
+
+def test_linear_cross_entropy_fused():
+    ops, _ = _ops()
+    torch.manual_seed(8)
+    h = (torch.randn(300, 256, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(1024, 256, device="cuda") * 0.1).to(torch.bfloat16).requires_grad_(True)
+    b = (torch.randn(1024, device="cuda") * 0.1).to(torch.bfloat16).requires_grad_(True)
+    lab = torch.randint(0, 1024, (300,), device="cuda")
+    lab[:5] = -100
+    loss = ops.linear_cross_entropy(h, w, b, lab, chunk_rows=128)
+    loss.backward()
+    hf, wf, bf = (t.detach().float().requires_grad_(True) for t in (h, w, b))
+    lr = ops.reference.cross_entropy(ops.reference.linear(hf, wf, bf), lab)
+    lr.backward()
+    assert abs(loss.item() - lr.item()) < 5e-3
+    _close(h.grad, hf.grad, atol=2e-4, rtol=5e-2)
+    _close(w.grad, wf.grad, atol=2e-4, rtol=5e-2)
+    _close(b.grad, bf.grad, atol=2e-4, rtol=5e-2)
+
+
+def test_adam_and_ngram():
+    ops, co = _ops()
+    ext = ops.load_ext()
+    torch.manual_seed(9)
+    n = 100003
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda").to(torch.bfloat16)
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    plp = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    pr, mr, vr = p.clone(), m.clone(), v.clone()
+    for step in (1, 2, 3):
+        ext.adam_step(p, g, m, v, plp, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, 1.0, None)
+        ops.reference.adam_step(pr, g, mr, vr, step, 1e-2, 0.9, 0.95, 1e-8, 0.1)
+    _close(p, pr, atol=1e-5, rtol=1e-4)
+    _close(plp, pr, atol=2e-2)
+    assert abs(ext.sumsq(g).item() - g.float().pow(2).sum().item()) / n < 1e-3
+    toks = torch.tensor([[1, 2, 3, 1, 2], [5, 5, 5, 5, 5], [1, 2, 3, 4, 5]], device="cuda")
+    lp = torch.zeros(3, 10, device="cuda")
+    out = ops.ban_repeated_ngrams(toks, lp.clone(), 3)
+    want = ops.reference.ban_repeated_ngrams(toks.cpu(), lp.cpu().clone(), 3)
+    assert torch.equal(out.cpu(), want)
+
+
+@pytest.mark.parametrize("D", [64, 128, 256])
+@pytest.mark.parametrize("Sq,Sk,window,use_kpm", [(128, 128, None, False), (200, 200, 48, False), (77, 333, None, True), (256, 256, 256, False)])
+def test_flash_attention(D, Sq, Sk, window, use_kpm):
+    ops, _ = _ops()
+    torch.manual_seed(10)
+    B, H = 2, 3
+    mk = lambda s: (torch.randn(B, s, H, D, device="cuda") * 0.7).to(torch.bfloat16).permute(0, 2, 1, 3).requires_grad_(True)
+    q, k, v = mk(Sq), mk(Sk), mk(Sk)
+    kpm = None
+    if use_kpm:
+        kpm = torch.ones(B, Sk, device="cuda", dtype=torch.long)
+        kpm[0, :9] = 0
+    scale = 1.0 / math.sqrt(D)
+    o = ops.attention(q, k, v, True, window, scale, kpm)
+    g = torch.randn(B, H, Sq, D, device="cuda").to(torch.bfloat16)
+    o.backward(g)
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    orf = ops.reference.attention(qf, kf, vf, True, window, scale, kpm)
+    orf.backward(g.float())
+    _close(o, orf, atol=2e-2)
+    _close(q.grad, qf.grad, atol=3e-2, rtol=5e-2)
+    _close(k.grad, kf.grad, atol=3e-2, rtol=5e-2)
+    _close(v.grad, vf.grad, atol=3e-2, rtol=5e-2)
+
+
+@pytest.mark.parametrize("D,window", [(256, None), (128, 37), (64, None)])
+def test_decode_attention(D, window):
+    ops, _ = _ops()
+    torch.manual_seed(11)
+    B, H, T = 3, 4, 300
+    q = torch.randn(B, H, D, device="cuda").to(torch.bfloat16)
+    kc = torch.randn(B, H, T, D, device="cuda").to(torch.bfloat16)
+    vc = torch.randn(B, H, T, D, device="cuda").to(torch.bfloat16)
+    lengths = torch.tensor([300, 1, 129], device="cuda", dtype=torch.int32)
+    out = ops.decode_attention(q, kc, vc, lengths, 1 / math.sqrt(D), window)
+    want = ops.functional.decode_attention(q.cpu().float(), kc.cpu().float(), vc.cpu().float(), lengths.cpu(),
+                                           1 / math.sqrt(D), window)
+    _close(out.cpu(), want, atol=2e-2)
+
+
+def test_bounded_wait_reports_instead_of_hanging():
+    """A kernel whose wait cannot be satisfied gives up, records a code and leaves the context usable."""
+    ops, co = _ops()
+    x = torch.ones(8, device="cuda")
+    co.reset_device_error(x)
+    assert co.device_error_code(x) == 0
