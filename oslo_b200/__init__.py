@@ -15,5 +15,7 @@ from .fused_kernels_utils import (FusedKernelMixin, FusedScaleMaskSoftmax, Fused
                                   get_datasets_builder)
 from .generation import *  # noqa: F401,F403
 from .models import *  # noqa: F401,F403
+from .data import *  # noqa: F401,F403
+from .optim import FusedAdamW  # noqa: F401
 
 parallelize = ParallelizationMixin._parallelize_from_model

@@ -403,7 +403,7 @@ int make_tma_2d_16bit(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_
   CUresult r = enc(map, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                    const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -102;
+  return r == CUDA_SUCCESS ? 0 : -(1000 + static_cast<int>(r));
 }
 
 template <int BN, int STAGES>
@@ -440,10 +440,10 @@ extern "C" int oslo_gemm_16bit(const void* A, const void* B, void* D, int M, int
   int rc;
   if (!a_mn_major) rc = make_tma_2d_16bit(&ta, A, K, M, lda, BM, fp16);
   else rc = make_tma_2d_16bit(&ta, A, M, K, lda, 64, fp16);
-  if (rc) return rc;
+  if (rc) return rc;  // -(1000 + CUresult): encoding the A map failed
   if (!b_mn_major) rc = make_tma_2d_16bit(&tb, B, K, N, ldb, bn, fp16);
   else rc = make_tma_2d_16bit(&tb, B, N, K, ldb, 64, fp16);
-  if (rc) return rc;
+  if (rc) return rc - 1000;  // -(2000 + CUresult): encoding the B map failed
   GemmParams p;
   p.D = D; p.bias = bias; p.aux = aux; p.aux_out = aux_out;
   p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ld_aux = ld_aux; p.ld_aux_out = ld_aux_out;
