@@ -51,6 +51,7 @@ def parse_args():
     ap.add_argument("--pp", type=int, default=1)
     ap.add_argument("--checkpoint-activations", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--layers", type=int, default=None, help="profiling only: override the layer count (result is labelled debug)")
     return ap.parse_args()
 
 
@@ -135,6 +136,8 @@ def main() -> None:
     dev = torch.device("cuda", local)
 
     n_layer, n_embd, n_head, rotary, vocab, n_pos = MODELS[args.model]
+    if args.layers is not None:
+        n_layer = args.layers
     tp = args.tp or 1
     pp = args.pp
     dp = world // (tp * pp)
@@ -222,7 +225,7 @@ def main() -> None:
     if rank == 0:
         par = "x".join(f"{k}{v}" for k, v in (("tp", tp), ("pp", pp), ("dp", dp)) if v > 1) or "single"
         line = {
-            "metric": "GPT-J-6B train tokens/sec" if args.model == "gptj-6b" else f"{args.model} train tokens/sec (debug)",
+            "metric": "GPT-J-6B train tokens/sec" if (args.model == "gptj-6b" and args.layers is None) else f"{args.model} train tokens/sec (debug)",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights", "impl": "oslo_b200",

@@ -1,0 +1,60 @@
+"""``OsloConfig``: process-wide switches, each overridable by an ``OSLO_B200_*`` environment variable.
+
+The reference has no configuration object (kwargs, HF configs and a few environment variables only); this
+collects the knobs the runtime itself needs: backend, fused-path switches, communication algorithm,
+timeouts and debug checks.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, fields
+
+
+def _env(name: str, default, cast):
+    raw = os.environ.get("OSLO_B200_" + name.upper())
+    if raw is None:
+        return default
+    if cast is bool:
+        return raw.strip().lower() in ("1", "true", "yes", "on")
+    return cast(raw)
+
+
+@dataclass
+class OsloConfig:
+    backend: str = ""                    # "" = nccl on CUDA, gloo on CPU
+    allow_fallback: bool = False         # let CUDA tensors run library ops when the extension is missing
+    fused_tp_comm: bool = True           # GEMM + all-reduce / all-gather kernels over symmetric memory
+    use_multimem: bool = True            # NVSwitch multicast (NVLS) loads / stores inside those kernels
+    symm_buffer_mb: int = 256            # symmetric-memory workspace per tensor-parallel group
+    ddp_bucket_mb: int = 256
+    pg_timeout_s: float = 1800.0         # process-group timeout (collectives fail instead of hanging)
+    heartbeat_s: float = 5.0             # watchdog heartbeat period
+    heartbeat_misses: int = 6            # missed heartbeats before a rank is declared dead
+    log_level: str = "INFO"
+    metrics_path: str = ""               # JSONL sink for per-step metrics
+
+    @classmethod
+    def from_env(cls) -> "OsloConfig":
+        kw = {}
+        for f in fields(cls):
+            kw[f.name] = _env(f.name, f.default, type(f.default))
+        return cls(**kw)
+
+
+_CONFIG = None
+
+
+def get_config() -> OsloConfig:
+    global _CONFIG
+    if _CONFIG is None:
+        _CONFIG = OsloConfig.from_env()
+    return _CONFIG
+
+
+def set_config(**kwargs) -> OsloConfig:
+    cfg = get_config()
+    for k, v in kwargs.items():
+        if not hasattr(cfg, k):
+            raise AttributeError(f"OsloConfig has no field {k!r}")
+        setattr(cfg, k, v)
+    return cfg

@@ -1,0 +1,82 @@
+"""Auxiliary subsystems on the host: heartbeat failure detection, deadlines, timers, metrics, config."""
+import json
+import time
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from oslo_b200 import config as cfgmod
+from oslo_b200.utils import (DeviceTimer, Heartbeat, MetricsLogger, RankFailure, StepDeadline, load_measured_peaks,
+                             roofline_fraction)
+from tests.dist_utils import run_distributed
+
+
+def _hb(rank, world):
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    store = dist.distributed_c10d._get_default_store()
+    hb = Heartbeat(store, rank, world, period_s=0.1, misses=3).start()
+    time.sleep(0.5)
+    hb.check_peers()  # everyone alive
+    dist.barrier()
+    if rank == 1:
+        hb.pause()  # rank 1 wedges: it stays in the job but stops beating
+        time.sleep(2.0)
+    else:
+        deadline = time.time() + 5
+        detected = None
+        while time.time() < deadline and detected is None:
+            time.sleep(0.1)
+            try:
+                hb.check_peers()
+            except RankFailure as e:
+                detected = e.dead
+        assert detected == [1], detected
+    hb.stop()
+
+
+def test_heartbeat_detects_wedged_rank():
+    run_distributed(_hb, 2)
+
+
+def _short_pg_timeout(rank, world):
+    import datetime
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=2))
+    t = torch.ones(1)
+    dist.all_reduce(t)
+    if rank == 1:
+        time.sleep(6)  # never joins the second collective in time
+        return
+    with pytest.raises(Exception):
+        dist.all_reduce(t)  # ends with an error instead of hanging
+
+
+def test_collective_timeout_instead_of_hang():
+    run_distributed(_short_pg_timeout, 2)
+
+
+def test_step_deadline_and_timer(tmp_path):
+    with pytest.raises(TimeoutError):
+        with StepDeadline(0.05):
+            time.sleep(0.2)
+    with StepDeadline(5):
+        pass
+    timer = DeviceTimer()
+    with timer("work"):
+        time.sleep(0.01)
+    assert timer.summary()["work"] >= 5.0
+    path = tmp_path / "m.jsonl"
+    ml = MetricsLogger(str(path), rank=0)
+    rec = ml.log_step(1, loss=2.5, tokens=1000, flops=1e12)
+    assert rec["loss"] == 2.5 and json.loads(path.read_text().splitlines()[0])["step"] == 1
+
+
+def test_roofline_and_config(monkeypatch):
+    peaks = load_measured_peaks("/nonexistent")
+    assert peaks["source"] == "fallback" and peaks["bf16_tflops"] == 1590.0
+    r = roofline_fraction(flops=1e15, nvlink_bytes=1e9, seconds=1.0, peak_tflops=1000.0)
+    assert abs(r["fraction"] - 1.0) < 1e-9 and r["t_link_s"] < r["t_compute_s"]
+    monkeypatch.setenv("OSLO_B200_DDP_BUCKET_MB", "32")
+    monkeypatch.setenv("OSLO_B200_USE_MULTIMEM", "0")
+    c = cfgmod.OsloConfig.from_env()
+    assert c.ddp_bucket_mb == 32 and c.use_multimem is False

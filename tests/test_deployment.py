@@ -1,0 +1,49 @@
+"""Deployment launcher on CPU workers (gloo): proxied generate / forward and dead-worker detection."""
+import os
+
+import pytest
+import torch
+
+import oslo_b200 as ob
+from oslo_b200.parallel.engine_deployment import DeploymentError
+
+
+def _model():
+    torch.manual_seed(5)
+    cfg = ob.GPT2Config(vocab_size=61, n_positions=32, n_embd=32, n_layer=2, n_head=4, resid_pdrop=0.0,
+                        embd_pdrop=0.0, attn_pdrop=0.0)
+    return ob.GPT2LMHeadModel(cfg).eval()
+
+
+@pytest.fixture()
+def gloo_env(monkeypatch):
+    monkeypatch.setenv("OSLO_B200_BACKEND", "gloo")
+
+
+def test_deployment_generate_and_forward(gloo_env):
+    ref = _model()
+    ids = torch.randint(0, 61, (2, 5), generator=torch.Generator().manual_seed(1))
+    want = ref.generate(ids, max_length=12, num_beams=3, eos_token_id=None, pad_token_id=0)
+    with torch.no_grad():
+        want_logits = ref(input_ids=ids).logits
+    model = ob.parallelize(_model(), tensor_parallel_size=2, pipeline_parallel_size=1, deployment=True,
+                           startup_timeout_s=120, request_timeout_s=120)
+    try:
+        got = model.generate(ids, max_length=12, num_beams=3, eos_token_id=None, pad_token_id=0)
+        assert torch.equal(got, want)
+        out = model(input_ids=ids)
+        assert torch.allclose(out.logits, want_logits, atol=1e-4)
+    finally:
+        model.cpu()  # shuts the workers down
+    assert not model._deployment_engine.procs
+
+
+def test_dead_worker_is_detected(gloo_env):
+    model = ob.parallelize(_model(), tensor_parallel_size=2, deployment=True, startup_timeout_s=120,
+                           request_timeout_s=30)
+    eng = model._deployment_engine
+    eng.procs[1].kill()
+    eng.procs[1].join(5)
+    with pytest.raises(DeploymentError):
+        model.generate(torch.zeros(1, 3, dtype=torch.long), max_length=6, eos_token_id=None, pad_token_id=0)
+    assert not eng.procs
