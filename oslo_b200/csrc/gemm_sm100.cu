@@ -432,6 +432,10 @@ extern "C" int oslo_gemm_16bit(const void* A, const void* B, void* D, int M, int
                                cudaStream_t stream) {
   using namespace oslo;
   if (M <= 0 || N <= 0 || K <= 0) return -1;
+  // the tensor-map encoder is a driver-API call and needs the primary context bound to THIS thread; the
+  // autograd engine's worker threads may not have made a runtime call yet
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) { cudaFree(nullptr); ctx_bound = true; }
   const bool fp16 = (flags & GEMM_FLAG_FP16) != 0;
   // narrow outputs use the 128-wide tile so that more CTAs share the work
   const bool wide = (N >= 256) && (static_cast<long long>((M + BM - 1) / BM) * ((N + 255) / 256) >= num_sms / 2);

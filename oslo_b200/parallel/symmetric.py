@@ -1,0 +1,82 @@
+"""Symmetric-memory workspace of one process group and the collectives that run on it.
+
+Allocation and rendezvous (CUDA VMM handles exchanged between the ranks, peer mappings, the NVSwitch
+multicast mapping and the signal pads) come from ``torch.distributed._symmetric_memory``; the device
+protocol and the kernels are this package's own (``csrc/comm.cu``, ``csrc/fused_comm_gemm.cu``): they get
+raw peer / multicast / signal-pad addresses and run the compare-and-swap handshake and the
+``multimem`` loads and stores themselves.
+
+A peer's memory is only ever touched by plain loads / stores or ``multimem`` instructions issued by these
+kernels; it is never handed to a library kernel or to a TMA load.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..config import get_config
+
+_WORKSPACES: Dict[str, "SymmetricWorkspace"] = {}
+
+
+class SymmetricWorkspace:
+    def __init__(self, group, nbytes: int, device: Optional[torch.device] = None) -> None:
+        import torch.distributed._symmetric_memory as symm
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.numel = (int(nbytes) + 255) // 256 * 128  # bf16 elements, 256-byte multiple
+        self.buf = symm.empty(self.numel, dtype=torch.bfloat16, device=self.device)
+        self.handle = symm.rendezvous(self.buf, group)
+        self.peer_ptrs_dev = int(self.handle.buffer_ptrs_dev)
+        self.signal_ptrs_dev = int(self.handle.signal_pad_ptrs_dev)
+        self.signal_pad_bytes = int(self.handle.signal_pad_size)
+        try:
+            self.mc_ptr = int(self.handle.multicast_ptr) if self.handle.has_multicast_support else 0
+        except Exception:
+            self.mc_ptr = 0
+        self.buf.zero_()
+        self.handle.barrier()
+
+    @property
+    def has_multicast(self) -> bool:
+        return self.mc_ptr != 0
+
+    def view(self, numel: int, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        t = self.buf if dtype == torch.bfloat16 else self.buf.view(dtype)
+        if numel > t.numel():
+            raise ValueError(f"symmetric workspace too small: need {numel} elements, have {t.numel()}")
+        return t[:numel]
+
+    def all_reduce_(self, x: torch.Tensor, use_multimem: Optional[bool] = None) -> torch.Tensor:
+        """Sum ``x`` (bf16 / fp16, numel % 8 == 0) over the group through the workspace; returns ``x``."""
+        n = x.numel()
+        if n % 8 or x.dtype not in (torch.bfloat16, torch.float16):
+            raise ValueError("all_reduce_ needs a 16-bit tensor whose numel is a multiple of 8")
+        if use_multimem is None:
+            use_multimem = get_config().use_multimem
+        use_multimem = bool(use_multimem) and self.has_multicast
+        stage = self.view(n, x.dtype)
+        flat = x.reshape(-1)
+        stage.copy_(flat)
+        ops.load_ext(required=True).allreduce_symm(self.peer_ptrs_dev, self.mc_ptr, self.signal_ptrs_dev,
+                                                  stage if use_multimem else flat, n, self.rank, self.world,
+                                                  use_multimem)
+        if use_multimem:
+            flat.copy_(stage)
+        return x
+
+
+def get_workspace(group, nbytes: Optional[int] = None) -> SymmetricWorkspace:
+    """One workspace per process group (created collectively on first use)."""
+    name = group.group_name
+    ws = _WORKSPACES.get(name)
+    want = nbytes or get_config().symm_buffer_mb * 2 ** 20
+    if ws is None or ws.numel * 2 < want:
+        ws = SymmetricWorkspace(group, want)
+        _WORKSPACES[name] = ws
+    return ws

@@ -1,0 +1,179 @@
+"""2-GPU checks (NCCL, one process per GPU): tensor-parallel fused training against a single-GPU run,
+ZeRO-1 data parallelism, and the symmetric-memory all-reduce kernels against NCCL."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _entry(rank, world, port, fn, args, errq):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE=os.environ.get("NCCL_NVLS_ENABLE", "1"))
+    import traceback
+    try:
+        torch.cuda.set_device(rank)
+        fn(rank, world, *args)
+    except BaseException:
+        errq.put((rank, traceback.format_exc()))
+        raise
+    finally:
+        import torch.distributed as dist
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def run_gpus(fn, world, *args, timeout=600):
+    ctx = mp.get_context("spawn")
+    errq = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, errq)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout)
+    bad = [p for p in procs if p.exitcode != 0]
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+    if bad:
+        msgs = []
+        while not errq.empty():
+            r, tb = errq.get()
+            msgs.append(f"--- rank {r} ---\n{tb}")
+        raise AssertionError("\n".join(msgs or ["worker crashed or timed out"]))
+
+
+def _cfg():
+    import oslo_b200 as ob
+    return ob.GPTJConfig(vocab_size=2048, n_positions=256, n_embd=512, n_layer=2, n_head=4, rotary_dim=32,
+                         torch_dtype=torch.bfloat16)
+
+
+def _tp_train(rank, world, tmp):
+    import oslo_b200 as ob
+    from oslo_b200.optim import FusedAdamW
+    torch.manual_seed(0)
+    model = ob.GPTJForCausalLM(_cfg()).to(torch.bfloat16)
+    ids = torch.randint(0, 2048, (4, 128), generator=torch.Generator().manual_seed(1)).cuda()
+    ref = torch.load(os.path.join(tmp, "ref.pt"), weights_only=True)
+    model.load_state_dict(ref["state"])
+    model = ob.parallelize(model, tensor_parallel_size=2)
+    model.fuse().train()
+    opt = FusedAdamW(model.gpu_parameters(), lr=1e-3)
+    losses = []
+    for _ in range(3):
+        opt.zero_grad()
+        loss = model(input_ids=ids, labels=ids, output_logits=False).loss
+        loss.backward()
+        opt.step()
+        losses.append(float(loss))
+    for a, b in zip(losses, ref["losses"]):
+        assert abs(a - b) < 0.05, (losses, ref["losses"])
+    model.eval()
+    gen = model.generate(ids[:, :8], max_new_tokens=8, eos_token_id=None, pad_token_id=0)
+    assert gen.shape == (4, 16)
+    assert int(ob.ops.load_ext().error_word(ids).item()) == 0
+
+
+def test_tensor_parallel_fused_training(tmp_path):
+    import oslo_b200 as ob
+    from oslo_b200.optim import FusedAdamW
+    torch.manual_seed(0)
+    model = ob.GPTJForCausalLM(_cfg()).to(torch.bfloat16)
+    state = {k: v.clone() for k, v in model.state_dict().items()}
+    model = model.cuda().fuse().train()
+    ids = torch.randint(0, 2048, (4, 128), generator=torch.Generator().manual_seed(1)).cuda()
+    opt = FusedAdamW(model.parameters(), lr=1e-3)
+    losses = []
+    for _ in range(3):
+        opt.zero_grad()
+        loss = model(input_ids=ids, labels=ids, output_logits=False).loss
+        loss.backward()
+        opt.step()
+        losses.append(float(loss))
+    torch.save({"state": state, "losses": losses}, tmp_path / "ref.pt")
+    run_gpus(_tp_train, 2, str(tmp_path))
+
+
+def _symm_allreduce(rank, world):
+    import torch.distributed as dist
+    from oslo_b200.parallel.mpu import MPU
+    from oslo_b200.parallel.symmetric import get_workspace
+    import oslo_b200 as ob
+    mpu = MPU(world, 1)
+    ws = get_workspace(mpu.get_tensor_parallel_group(), 64 * 2 ** 20)
+    for n in (8, 4096, 1 << 20, (1 << 22) + 8):
+        for mm in ([False, True] if ws.has_multicast else [False]):
+            torch.manual_seed(100 + rank)
+            x = torch.randn(n, device="cuda").to(torch.bfloat16)
+            want = x.clone().float()
+            dist.all_reduce(want, group=mpu.get_tensor_parallel_group())
+            for _ in range(3):  # back-to-back launches reuse the same signal words
+                y = x.clone()
+                ws.all_reduce_(y, use_multimem=mm)
+            torch.cuda.synchronize()
+            assert torch.allclose(y.float(), want, atol=0.05, rtol=0.02), (n, mm, (y.float() - want).abs().max())
+    assert int(ob.ops.load_ext().error_word(x).item()) == 0
+
+
+def test_symmetric_memory_allreduce():
+    run_gpus(_symm_allreduce, 2)
+
+
+def _zero_dp(rank, world, tmp):
+    import torch.distributed as dist
+    import oslo_b200 as ob
+    from oslo_b200.optim import FusedAdamW
+    from oslo_b200.parallel.data_parallel import DistributedDataParallel
+    torch.manual_seed(0)
+    model = ob.GPTJForCausalLM(_cfg()).to(torch.bfloat16)
+    ref = torch.load(os.path.join(tmp, "ref.pt"), weights_only=True)
+    model.load_state_dict(ref["state"])
+    model = ob.parallelize(model, tensor_parallel_size=1)
+    model.fuse().train()
+    mpu = model.mpu
+    opt = FusedAdamW(model.gpu_parameters(), lr=1e-3, shard_group=mpu.get_data_parallel_group())
+    ddp = DistributedDataParallel(model, mpu, optimizer=opt, bucket_mb=1)
+    ids = torch.randint(0, 2048, (4, 128), generator=torch.Generator().manual_seed(1)).cuda()
+    mine = ids[rank * 2:(rank + 1) * 2]
+    losses = []
+    for _ in range(3):
+        opt.zero_grad()
+        loss = ddp(input_ids=mine, labels=mine, output_logits=False).loss
+        loss.backward()
+        opt.step()
+        t = loss.detach().clone()
+        dist.all_reduce(t)
+        losses.append(float(t) / world)
+    for a, b in zip(losses, ref["losses"]):
+        assert abs(a - b) < 0.05, (losses, ref["losses"])
+
+
+def test_zero1_data_parallel(tmp_path):
+    import oslo_b200 as ob
+    from oslo_b200.optim import FusedAdamW
+    torch.manual_seed(0)
+    model = ob.GPTJForCausalLM(_cfg()).to(torch.bfloat16)
+    state = {k: v.clone() for k, v in model.state_dict().items()}
+    model = model.cuda().fuse().train()
+    ids = torch.randint(0, 2048, (4, 128), generator=torch.Generator().manual_seed(1)).cuda()
+    opt = FusedAdamW(model.parameters(), lr=1e-3)
+    losses = []
+    for _ in range(3):
+        opt.zero_grad()
+        loss = model(input_ids=ids, labels=ids, output_logits=False).loss
+        loss.backward()
+        opt.step()
+        losses.append(float(loss))
+    torch.save({"state": state, "losses": losses}, tmp_path / "ref.pt")
+    run_gpus(_zero_dp, 2, str(tmp_path))
