@@ -1,0 +1,589 @@
+// tcgen05 GEMM core shared by the plain GEMM (gemm_sm100.cu) and the GEMM + collective kernels
+// (fused_comm_gemm.cu). See gemm_sm100.cu for the operand conventions.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "oslo_kernels.h"
+#include "ptx.cuh"
+
+namespace oslo {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int GEMM_THREADS = 192;
+
+// Collective fused into the GEMM (all addresses are byte offsets into the symmetric buffer of the group).
+enum : int { COMM_NONE = 0, COMM_ALLREDUCE = 1, COMM_REDUCE_SCATTER = 2, COMM_ALLGATHER_A = 3 };
+struct CommParams {
+  void* const* peer_bufs;  // device array [world]: peer-mapped base address of every rank's symmetric buffer
+  uint8_t* mc_base;        // NVSwitch multicast mapping of the same buffer, or nullptr
+  long long data_off;      // staging matrix: partial outputs [M,N] (reduce modes) or gathered A [M,K] (all-gather)
+  long long flag_off;      // uint32 flags: one per tile / chunk, then the completion counter
+  int rank, world;
+  uint32_t epoch;          // call number on this workspace slot, starts at 1; flags only ever grow
+  int mode;
+  int use_multimem;
+  void* out;               // reduce-scatter: this rank's [M/world, N] result (ordinary memory)
+  int ld_out;
+  const void* ag_src;      // all-gather: this rank's [M/world, K] shard (ordinary memory)
+  int ld_ag_src;
+  int ag_parts;            // column parts per 128-row chunk (flag target = epoch * ag_parts)
+};
+
+struct GemmParams {
+  void* D;
+  const void* bias;     // [N] same dtype as inputs, or nullptr
+  const void* aux;      // residual (out dtype, [M,N]) or pre-activation for dgelu (input dtype, [M,N])
+  void* aux_out;        // pre-activation output for FLAG_SAVE_PREACT (input dtype, [M,N])
+  int M, N, K;
+  int ldd, ld_aux, ld_aux_out;
+  int a_mn_major, b_mn_major;
+  int flags;
+  float alpha;
+  int* err;
+  int tiles_m, tiles_n;
+  CommParams comm;
+};
+
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  return 0.5f * x * (1.0f + t);
+}
+__device__ __forceinline__ float dgelu_tanh_f(float x) {
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * 0.7978845608028654f * (1.0f + 0.134145f * x * x);
+}
+
+__device__ __forceinline__ float ld_half_as_float(const void* p, size_t idx, bool fp16) {
+  return fp16 ? __half2float(reinterpret_cast<const __half*>(p)[idx])
+              : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[idx]);
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b, bool fp16) {
+  if (fp16) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ void unpack8(const uint4& v, float* f, bool fp16) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (fp16) {
+      float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      f[2 * i] = t.x; f[2 * i + 1] = t.y;
+    } else {
+      float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+      f[2 * i] = t.x; f[2 * i + 1] = t.y;
+    }
+  }
+}
+
+// grouped raster: walk GROUP_M row-blocks per column sweep so concurrently running CTAs share B tiles in L2
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  constexpr int GROUP_M = 8;
+  const int per_group = GROUP_M * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * GROUP_M;
+  const int rows = min(GROUP_M, tiles_m - first_m);
+  const int r = tile - g * per_group;
+  tm = first_m + r % rows;
+  tn = r / rows;
+}
+
+constexpr int COMM_WARPS = 4;
+constexpr int GEMM_THREADS_COMM = GEMM_THREADS + 32 * COMM_WARPS;
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void multimem_red_release_add(uint32_t* mc, uint32_t v) {
+  asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 mm_ld_reduce_16(const void* mc, bool fp16) {
+  uint4 v;
+  if (fp16)
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  else
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+__device__ __forceinline__ void mm_st_16(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w) : "memory");
+}
+// wait until *flag has reached `target` (flags only grow; compare as a signed distance so wrap-around is harmless)
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t target, volatile int* abort_flag,
+                                             int* err_word) {
+  if (static_cast<int32_t>(ld_acquire_sys(flag) - target) >= 0) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (static_cast<int32_t>(ld_acquire_sys(flag) - target) < 0) {
+    if ((++spins & 0x3f) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > OSLO_WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        if (err_word) atomicCAS(err_word, 0, ERR_WAIT_PEER);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// which rank reduces output tile (tm, tn) / linear schedule index `tile`
+__device__ __forceinline__ int tile_owner(const CommParams& c, int tile, int tm, int M) {
+  if (c.mode == COMM_REDUCE_SCATTER) return (tm * BM) / (M / c.world);
+  return tile % c.world;
+}
+
+template <int BN, int STAGES, bool COMM>
+__global__ void __launch_bounds__(COMM ? GEMM_THREADS_COMM : GEMM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                    const GemmParams p) {
+  constexpr uint32_t A_BYTES = BM * BK * 2;
+  constexpr uint32_t B_BYTES = BN * BK * 2;
+  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = 2 * BN;  // 256 or 512, both powers of two >= 32
+
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: required by the 128-byte swizzle atoms the descriptors assume
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  // bars: [0,STAGES) full, [STAGES,2S) empty, [2S,2S+2) tmem_full, [2S+2,2S+4) tmem_empty
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int kblocks = (p.K + BK - 1) / BK;
+  // all-gather mode walks the row blocks starting with this rank's own shard, which needs no transfer
+  auto coords = [&](int tile, int& tm, int& tn) {
+    tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+    if (COMM && p.comm.mode == COMM_ALLGATHER_A) {
+      tm += p.comm.rank * (p.tiles_m / p.comm.world);
+      if (tm >= p.tiles_m) tm -= p.tiles_m;
+    }
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tma_a);
+      tma_prefetch_desc(&tma_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        coords(tile, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        if (COMM && p.comm.mode == COMM_ALLGATHER_A) {
+          // rows m0.. of the gathered A arrive from rank m0 / (M / world); its comm warps raise flag[tm]
+          const uint32_t* flags = reinterpret_cast<const uint32_t*>(
+              static_cast<const uint8_t*>(p.comm.peer_bufs[p.comm.rank]) + p.comm.flag_off);
+          ok = wait_flag_ge(flags + tm, p.comm.epoch * static_cast<uint32_t>(p.comm.ag_parts) * COMM_WARPS, abort_flag, p.err);
+          if (!ok) break;
+          asm volatile("fence.proxy.async.global;" ::: "memory");  // the TMA engine reads what peers just wrote
+        }
+        for (int kb = 0; kb < kblocks; ++kb) {
+          ok = mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, p.err, ERR_WAIT_EMPTY);
+          if (!ok) break;
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+          mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!p.a_mn_major) {
+            tma_load_2d(sa, &tma_a, full_bar(stage), k0, m0);           // box {64 k, 128 rows}
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)                            // boxes {64 m, 64 k rows}
+              tma_load_2d(sa + c * 8192, &tma_a, full_bar(stage), m0 + c * 64, k0);
+          }
+          if (!p.b_mn_major) {
+            tma_load_2d(sb, &tma_b, full_bar(stage), k0, n0);           // box {64 k, BN rows}
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sb + c * 8192, &tma_b, full_bar(stage), n0 + c * 64, k0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const int fmt = (p.flags & GEMM_FLAG_FP16) ? 0 : 1;
+      const uint32_t idesc = make_idesc_f16(BM, BN, fmt, p.a_mn_major, p.b_mn_major);
+      // K-major tile: rows of 128 B, 8-row groups 1024 B apart, one k-step (16 elements) = 32 B
+      // MN-major tile: k rows of 128 B, 64-wide MN chunks 8192 B apart, one k-step (16 rows) = 2048 B
+      const uint32_t a_lbo = p.a_mn_major ? 8192u : 16u, a_step = p.a_mn_major ? 2048u : 32u;
+      const uint32_t b_lbo = p.b_mn_major ? 8192u : 16u, b_step = p.b_mn_major ? 2048u : 32u;
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        ok = mbar_wait(tempty_bar(buf), acc_phase[buf] ^ 1, abort_flag, p.err, ERR_WAIT_TMEM_EMPTY);
+        if (!ok) break;
+        acc_phase[buf] ^= 1;
+        tc_fence_after();
+        const uint32_t tmem_acc = tmem_base + buf * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          ok = mbar_wait(full_bar(stage), phase, abort_flag, p.err, ERR_WAIT_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t da = make_smem_desc(sa + k * a_step, a_lbo, 1024);
+            const uint64_t db = make_smem_desc(sb + k * b_step, b_lbo, 1024);
+            umma_f16(tmem_acc, da, db, idesc, (kb | k) != 0);
+          }
+          umma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(tfull_bar(buf));
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    const bool fp16 = (p.flags & GEMM_FLAG_FP16) != 0;
+    const bool out_f32 = (p.flags & GEMM_FLAG_OUT_FP32) != 0;
+    uint32_t acc_phase[2] = {0, 0};
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      int tm, tn;
+      coords(tile, tm, tn);
+      ok = mbar_wait(tfull_bar(buf), acc_phase[buf], abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+      if (!ok) break;
+      acc_phase[buf] ^= 1;
+      tc_fence_after();
+      const int row = tm * BM + quad * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c0, r);
+        tmem_wait_ld();
+        const int col0 = tn * BN + c0;
+        if (!row_ok || col0 >= p.N) continue;
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+        const int ncols = min(32, p.N - col0);
+        const bool vec = (ncols == 32);
+        if (p.flags & GEMM_FLAG_BIAS) {
+          if (vec) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              float b[8];
+              unpack8(*reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias) + col0 + i), b, fp16);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[i + j] += b[j];
+            }
+          } else {
+            _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) v[i] += ld_half_as_float(p.bias, col0 + i, fp16);
+          }
+        }
+        if (p.flags & GEMM_FLAG_SAVE_PREACT) {
+          uint16_t* z = reinterpret_cast<uint16_t*>(p.aux_out) + static_cast<size_t>(row) * p.ld_aux_out + col0;
+          if (vec) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 o;
+              o.x = pack2(v[i], v[i + 1], fp16); o.y = pack2(v[i + 2], v[i + 3], fp16);
+              o.z = pack2(v[i + 4], v[i + 5], fp16); o.w = pack2(v[i + 6], v[i + 7], fp16);
+              *reinterpret_cast<uint4*>(z + i) = o;
+            }
+          } else {
+            _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) z[i] = static_cast<uint16_t>(pack2(v[i], 0.f, fp16) & 0xffff);
+          }
+        }
+        if (p.flags & GEMM_FLAG_GELU) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = gelu_tanh_f(v[i]);
+        }
+        if (p.flags & GEMM_FLAG_DGELU) {
+          const uint16_t* z = reinterpret_cast<const uint16_t*>(p.aux) + static_cast<size_t>(row) * p.ld_aux + col0;
+          if (vec) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              float zz[8];
+              unpack8(*reinterpret_cast<const uint4*>(z + i), zz, fp16);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[i + j] *= dgelu_tanh_f(zz[j]);
+            }
+          } else {
+            _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) v[i] *= dgelu_tanh_f(ld_half_as_float(z, i, fp16));
+          }
+        }
+        if (p.flags & GEMM_FLAG_RESIDUAL) {
+          if (out_f32) {
+            const float* rr = reinterpret_cast<const float*>(p.aux) + static_cast<size_t>(row) * p.ld_aux + col0;
+            _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) v[i] += rr[i];
+          } else {
+            const uint16_t* rr = reinterpret_cast<const uint16_t*>(p.aux) + static_cast<size_t>(row) * p.ld_aux + col0;
+            if (vec) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                float x[8];
+                unpack8(*reinterpret_cast<const uint4*>(rr + i), x, fp16);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[i + j] += x[j];
+              }
+            } else {
+              _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) v[i] += ld_half_as_float(rr, i, fp16);
+            }
+          }
+        }
+        if (out_f32) {
+          float* d = reinterpret_cast<float*>(p.D) + static_cast<size_t>(row) * p.ldd + col0;
+          if (vec) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+              if (p.flags & GEMM_FLAG_ACCUMULATE) {
+                const float4 old = *reinterpret_cast<const float4*>(d + i);
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              *reinterpret_cast<float4*>(d + i) = o;
+            }
+          } else {
+            _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) d[i] = v[i] + ((p.flags & GEMM_FLAG_ACCUMULATE) ? d[i] : 0.f);
+          }
+        } else {
+          uint16_t* d = reinterpret_cast<uint16_t*>(p.D) + static_cast<size_t>(row) * p.ldd + col0;
+          if (vec) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              if (p.flags & GEMM_FLAG_ACCUMULATE) {
+                float x[8];
+                unpack8(*reinterpret_cast<const uint4*>(d + i), x, fp16);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[i + j] += x[j];
+              }
+              uint4 o;
+              o.x = pack2(v[i], v[i + 1], fp16); o.y = pack2(v[i + 2], v[i + 3], fp16);
+              o.z = pack2(v[i + 4], v[i + 5], fp16); o.w = pack2(v[i + 6], v[i + 7], fp16);
+              *reinterpret_cast<uint4*>(d + i) = o;
+            }
+          } else {
+            _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) {
+              float x = v[i];
+              if (p.flags & GEMM_FLAG_ACCUMULATE) x += ld_half_as_float(d, i, fp16);
+              d[i] = static_cast<uint16_t>(pack2(x, 0.f, fp16) & 0xffff);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(buf));
+      if (COMM && (p.comm.mode == COMM_ALLREDUCE || p.comm.mode == COMM_REDUCE_SCATTER)) {
+        // this rank's partial tile is in its symmetric buffer: publish it to the rank that reduces the tile
+        // (one arrival per epilogue warp, so no CTA-wide barrier is needed: a tile is complete on a rank
+        // after 4 arrivals)
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const int owner = tile_owner(p.comm, tile, tm, p.M);
+          uint32_t* f = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(p.comm.peer_bufs[owner]) + p.comm.flag_off) + tile;
+          red_release_sys_add(f, 1u);
+        }
+      }
+    }
+  } else if (COMM) {
+    // ------------------------------------------------------------ communication warps (6..9)
+    const CommParams& c = p.comm;
+    const int cw = threadIdx.x - GEMM_THREADS;  // 0..127
+    const bool fp16 = (p.flags & GEMM_FLAG_FP16) != 0;
+    uint8_t* my_base = static_cast<uint8_t*>(c.peer_bufs[c.rank]);
+    uint32_t* my_flags = reinterpret_cast<uint32_t*>(my_base + c.flag_off);
+    const bool mm = c.use_multimem && c.mc_base != nullptr;
+    bool ok = true;
+    if (c.mode == COMM_ALLGATHER_A) {
+      // push this rank's [M/world, K] shard into every rank's gather buffer, 128-row chunk by chunk
+      const int rows_per_rank = p.M / c.world;
+      const int chunks = rows_per_rank / BM;
+      const int parts = c.ag_parts;
+      const int cols_per_part = p.K / parts;  // multiple of 8
+      const int vpr = cols_per_part / 8;
+      const uint16_t* src = reinterpret_cast<const uint16_t*>(c.ag_src);
+      for (int unit = blockIdx.x; unit < chunks * parts; unit += gridDim.x) {
+        const int ch = unit / parts, part = unit % parts;
+        const int total = BM * vpr;
+        for (int idx = cw; idx < total; idx += 128) {
+          const int r = idx / vpr, v = idx % vpr;
+          const int col = part * cols_per_part + v * 8;
+          const uint4 val = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(ch * BM + r) * c.ld_ag_src + col);
+          const size_t off = c.data_off + (static_cast<size_t>(c.rank * rows_per_rank + ch * BM + r) * p.K + col) * 2;
+          if (mm) {
+            mm_st_16(c.mc_base + off, val);
+          } else {
+            for (int w = 0; w < c.world; ++w) *reinterpret_cast<uint4*>(static_cast<uint8_t*>(c.peer_bufs[w]) + off) = val;
+          }
+        }
+        __threadfence_system();
+        __syncwarp();
+        if ((cw & 31) == 0) {  // one arrival per communication warp
+          const int flag_idx = c.rank * chunks + ch;  // = global 128-row block index
+          if (mm) {
+            multimem_red_release_add(reinterpret_cast<uint32_t*>(c.mc_base + c.flag_off) + flag_idx, 1u);
+          } else {
+            for (int w = 0; w < c.world; ++w)
+              red_release_sys_add(reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(c.peer_bufs[w]) + c.flag_off) + flag_idx, 1u);
+          }
+        }
+      }
+    } else {
+      const int num_tiles_c = p.tiles_m * p.tiles_n;
+      const uint32_t target = c.epoch * static_cast<uint32_t>(c.world) * 4u;  // 4 epilogue warps per rank
+      const int rows_per_rank = p.M / c.world;
+      int owned = 0;
+      for (int tile = 0; tile < num_tiles_c && ok; ++tile) {
+        int tm, tn;
+        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        if (tile_owner(c, tile, tm, p.M) != c.rank) continue;
+        const int mine = owned++;
+        if (mine % static_cast<int>(gridDim.x) != static_cast<int>(blockIdx.x)) continue;
+        if ((cw & 31) == 0) wait_flag_ge(my_flags + tile, target, abort_flag, p.err);
+        __syncwarp();
+        if (*abort_flag) { ok = false; break; }
+        const int m0 = tm * BM, n0 = tn * BN;
+        const int rows = min(BM, p.M - m0), cols = min(BN, p.N - n0);
+        const int vpr = cols / 8;
+        const int total = rows * vpr;
+        for (int base = cw; base < total; base += 128 * 4) {
+          uint4 v[4];
+          size_t off[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int idx = base + j * 128;
+            if (idx < total) {
+              const int r = idx / vpr, q = idx % vpr;
+              off[j] = c.data_off + (static_cast<size_t>(m0 + r) * p.N + n0 + q * 8) * 2;
+              if (mm) {
+                v[j] = mm_ld_reduce_16(c.mc_base + off[j], fp16);
+              } else {
+                float acc[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+                for (int w = 0; w < c.world; ++w) {
+                  float t[8];
+                  unpack8(*reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(c.peer_bufs[w]) + off[j]), t, fp16);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) acc[e] += t[e];
+                }
+                v[j].x = pack2(acc[0], acc[1], fp16); v[j].y = pack2(acc[2], acc[3], fp16);
+                v[j].z = pack2(acc[4], acc[5], fp16); v[j].w = pack2(acc[6], acc[7], fp16);
+              }
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int idx = base + j * 128;
+            if (idx < total) {
+              if (c.mode == COMM_ALLREDUCE) {
+                if (mm) {
+                  mm_st_16(c.mc_base + off[j], v[j]);
+                } else {
+                  for (int w = 0; w < c.world; ++w)
+                    *reinterpret_cast<uint4*>(static_cast<uint8_t*>(c.peer_bufs[w]) + off[j]) = v[j];
+                }
+              } else {
+                const int r = idx / vpr, q = idx % vpr;
+                uint16_t* o = reinterpret_cast<uint16_t*>(c.out) +
+                              static_cast<size_t>(m0 + r - c.rank * rows_per_rank) * c.ld_out + n0 + q * 8;
+                *reinterpret_cast<uint4*>(o) = v[j];
+              }
+            }
+          }
+        }
+        if (c.mode == COMM_ALLREDUCE) {
+          // tell every rank that one more tile of the result is final
+          __threadfence_system();
+          __syncwarp();
+          if ((cw & 31) == 0) {
+            if (mm) {
+              multimem_red_release_add(reinterpret_cast<uint32_t*>(c.mc_base + c.flag_off) + num_tiles_c, 1u);
+            } else {
+              for (int w = 0; w < c.world; ++w)
+                red_release_sys_add(reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(c.peer_bufs[w]) + c.flag_off) + num_tiles_c, 1u);
+            }
+          }
+        }
+      }
+      if (c.mode == COMM_ALLREDUCE && ok && cw == 0) {
+        // the result is complete on this rank once every tile of every owner has been broadcast
+        wait_flag_ge(my_flags + num_tiles_c, c.epoch * static_cast<uint32_t>(num_tiles_c) * COMM_WARPS, abort_flag, p.err);
+      }
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  if (*abort_flag) {
+    // give copies that are still in flight time to land before shared memory is released
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) {
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace oslo

@@ -92,6 +92,14 @@ int oslo_flash_bwd(const void* q, const void* k, const void* v, const void* o, c
 int oslo_decode_attn(const void* q, const void* kc, const void* vc, void* o, const int* lengths, float* ws, int B,
                      int H, int T, int D, int splits, float scale, int window, int dtype, cudaStream_t stream);
 
+// GEMM fused with a tensor-parallel collective (fused_comm_gemm.cu); mode 1 = all-reduce (result left in the
+// symmetric staging matrix), 2 = reduce-scatter into out, 3 = all-gather of A then GEMM into out
+int oslo_gemm_comm_16bit(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int a_mn_major,
+                         int b_mn_major, const void* bias, void* aux_out, int ld_aux_out, int flags, float alpha,
+                         void* const* peer_bufs_dev, void* own_buf, void* mc_base, long long data_off,
+                         long long flag_off, int rank, int world, unsigned epoch, int mode, int use_multimem,
+                         void* out, int ld_out, int wide_tiles, int* err_word, int num_sms, cudaStream_t stream);
+
 // symmetric-memory collectives (comm.cu)
 int oslo_allreduce_symm(void* const* peer_ptrs_dev, void* mc_ptr, uint32_t* const* signal_ptrs_dev, void* out,
                         long long n, int rank, int world, int dtype, int use_multimem, int* err_word,

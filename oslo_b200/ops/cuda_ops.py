@@ -67,8 +67,7 @@ class _Linear(torch.autograd.Function):
     def forward(ctx, x, weight, bias, reversed_, gelu):
         k = x.size(-1)
         x2 = x.reshape(-1, k)
-        need_grad = torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad or
-                                                 (bias is not None and bias.requires_grad))
+        need_grad = any(ctx.needs_input_grad[:3])  # grad mode is always off inside forward(); ask the ctx
         flags = (FLAG_BIAS if bias is not None else 0) | (FLAG_GELU if gelu else 0)
         n = weight.size(1) if reversed_ else weight.size(0)
         z = None

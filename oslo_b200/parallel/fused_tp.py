@@ -1,0 +1,249 @@
+"""Tensor-parallel linear layers whose collective runs INSIDE the GEMM kernel.
+
+``FusedTP`` owns the symmetric workspace of one tensor-parallel group and exposes the three fused ops of
+``csrc/fused_comm_gemm.cu``:
+
+* ``gemm_all_reduce``      - row-parallel forward and column-parallel input-gradient (``sum_r x_r W_r``)
+* ``gemm_reduce_scatter``  - the sequence-parallel form of the same product (each rank keeps its rows)
+* ``all_gather_gemm``      - sequence-parallel column-parallel forward (``[x_0; x_1; ...] W``)
+
+The autograd functions below use them for forward and backward, so one fused kernel replaces every
+``matmul`` + NCCL all-reduce / all-gather pair of the reference's parallel layers
+(oslo/modeling_utils.py:67-104, oslo/parallelism/mpu.py:848-890). Two workspace slots alternate between
+calls (see the kernel's notes on why that makes reuse safe without a trailing barrier).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+from .. import ops
+from ..config import get_config
+from .symmetric import SymmetricWorkspace
+
+MODE_ALLREDUCE, MODE_REDUCE_SCATTER, MODE_ALLGATHER = 1, 2, 3
+_FLAG_BYTES = 1 << 20          # room for 256K tile flags per slot
+_CONTEXTS: Dict[str, "FusedTP"] = {}
+
+
+class FusedTP:
+    def __init__(self, group, workspace_mb: Optional[int] = None) -> None:
+        mb = workspace_mb or get_config().symm_buffer_mb
+        self.group = group
+        self.ws = SymmetricWorkspace(group, 2 * (mb * 2 ** 20 + _FLAG_BYTES))
+        self.world, self.rank = self.ws.world, self.ws.rank
+        self.slot_bytes = mb * 2 ** 20
+        self.epochs = [0, 0]
+        self.calls = 0
+        self.own_base = self.ws.buf.data_ptr()
+        self.use_multimem = get_config().use_multimem and self.ws.has_multicast
+
+    def _next_slot(self) -> Tuple[int, int, int, int]:
+        slot = self.calls & 1
+        self.calls += 1
+        self.epochs[slot] += 1
+        data_off = slot * (self.slot_bytes + _FLAG_BYTES)
+        return slot, data_off, data_off + self.slot_bytes, self.epochs[slot]
+
+    def fits(self, rows: int, cols: int) -> bool:
+        return rows * cols * 2 <= self.slot_bytes and rows * cols > 0
+
+    def _call(self, a, b, a_mn, b_mn, bias, aux_out, out, flags, M, N, K, mode):
+        slot, data_off, flag_off, epoch = self._next_slot()
+        ops.load_ext(required=True).gemm_comm(
+            a, b, int(a_mn), int(b_mn), bias, aux_out, out, flags, 1.0, M, N, K, self.ws.peer_ptrs_dev, self.own_base,
+            self.ws.mc_ptr if self.use_multimem else 0, data_off, flag_off, self.rank, self.world, epoch, mode,
+            self.use_multimem)
+        return data_off
+
+    def gemm_all_reduce(self, a: Tensor, b: Tensor, a_mn: bool, b_mn: bool) -> Tensor:
+        """``sum over ranks of a @ b^T`` as a fresh ``[M, N]`` tensor (copied out of the workspace)."""
+        M = a.size(1) if a_mn else a.size(0)
+        K = a.size(0) if a_mn else a.size(1)
+        N = b.size(1) if b_mn else b.size(0)
+        off = self._call(a, b, a_mn, b_mn, None, None, None, 0, M, N, K, MODE_ALLREDUCE)
+        view = self.ws.buf.view(torch.uint8)[off: off + M * N * 2].view(a.dtype).view(M, N)
+        return view.clone()
+
+    def gemm_reduce_scatter(self, a: Tensor, b: Tensor, a_mn: bool, b_mn: bool) -> Tensor:
+        M = a.size(1) if a_mn else a.size(0)
+        K = a.size(0) if a_mn else a.size(1)
+        N = b.size(1) if b_mn else b.size(0)
+        out = torch.empty(M // self.world, N, dtype=a.dtype, device=a.device)
+        self._call(a, b, a_mn, b_mn, None, None, out, 0, M, N, K, MODE_REDUCE_SCATTER)
+        return out
+
+    def all_gather_gemm(self, a_shard: Tensor, b: Tensor, b_mn: bool, bias: Optional[Tensor] = None,
+                        gelu: bool = False, save_preact: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
+        """Returns ``(product [M, N], gathered a [M, K])``; the gathered operand is a copy out of the workspace
+        that the backward pass reuses for the weight gradient."""
+        rows, K = a_shard.shape
+        M = rows * self.world
+        N = b.size(1) if b_mn else b.size(0)
+        out = torch.empty(M, N, dtype=a_shard.dtype, device=a_shard.device)
+        flags = (1 if bias is not None else 0) | (2 if gelu else 0) | (4 if save_preact is not None else 0)
+        off = self._call(a_shard, b, False, b_mn, bias, save_preact, out, flags, M, N, K, MODE_ALLGATHER)
+        gathered = self.ws.buf.view(torch.uint8)[off: off + M * K * 2].view(a_shard.dtype).view(M, K).clone()
+        return out, gathered
+
+
+def get_fused_tp(group) -> FusedTP:
+    name = group.group_name
+    ctx = _CONTEXTS.get(name)
+    if ctx is None:
+        ctx = FusedTP(group)
+        _CONTEXTS[name] = ctx
+    return ctx
+
+
+def fused_tp_usable(mpu, x: Tensor, n_out: int, rows: Optional[int] = None) -> bool:
+    """Fused paths need CUDA, the extension, 16-bit inputs, 8-aligned dims and a workspace slot that holds [M, N]."""
+    if mpu is None or mpu.tp == 1 or not x.is_cuda or mpu.backend != "nccl" or not get_config().fused_tp_comm:
+        return False
+    if x.dtype not in (torch.bfloat16, torch.float16) or x.size(-1) % 8 or n_out % 8 or x.numel() == 0:
+        return False
+    if not ops.kernels_available():
+        return False
+    rows = rows if rows is not None else x.numel() // x.size(-1)
+    ctx = get_fused_tp(mpu.get_tensor_parallel_group())
+    return ctx.fits(rows, max(n_out, x.size(-1)))  # forward and backward staging matrices
+
+
+class _RowParallelFused(torch.autograd.Function):
+    """``y = all_reduce(x_shard @ W_shard^T)``; backward needs no communication."""
+
+    @staticmethod
+    def forward(ctx, x, weight, reversed_, tp: FusedTP):
+        x2 = x.reshape(-1, x.size(-1))
+        y = tp.gemm_all_reduce(x2, weight, False, reversed_)
+        ctx.save_for_backward(x2, weight)
+        ctx.reversed, ctx.in_shape = reversed_, x.shape
+        return y.view(*x.shape[:-1], y.size(-1))
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops.cuda_ops import gemm
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.size(-1))
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, weight, False, not ctx.reversed).view(ctx.in_shape)
+        if ctx.needs_input_grad[1]:
+            dw = gemm(x2, dy2, True, True) if ctx.reversed else gemm(dy2, x2, True, True)
+        return dx, dw, None, None
+
+
+class _ColumnParallelFused(torch.autograd.Function):
+    """``y = act(x @ W_shard^T + b)`` with a replicated ``x``; the input gradient ``sum_r dy_r W_r`` is one
+    GEMM + all-reduce kernel (the reference's ``Broadcast.backward`` all-reduce)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, reversed_, gelu, tp: FusedTP):
+        from ..ops.cuda_ops import FLAG_BIAS, FLAG_GELU, FLAG_SAVE_PREACT, gemm
+        x2 = x.reshape(-1, x.size(-1))
+        n = weight.size(1) if reversed_ else weight.size(0)
+        flags = (FLAG_BIAS if bias is not None else 0) | (FLAG_GELU if gelu else 0)
+        z = None
+        if gelu and any(ctx.needs_input_grad[:3]):
+            flags |= FLAG_SAVE_PREACT
+            z = torch.empty(x2.size(0), n, dtype=x.dtype, device=x.device)
+        y = gemm(x2, weight, False, reversed_, bias=bias, aux_out=z, flags=flags)
+        ctx.save_for_backward(x2, weight, z)
+        ctx.reversed, ctx.in_shape, ctx.tp = reversed_, x.shape, tp
+        ctx.has_bias = bias is not None
+        ctx.bias_dtype = bias.dtype if bias is not None else None
+        return y.view(*x.shape[:-1], n)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops.cuda_ops import gemm
+        ext = ops.load_ext(required=True)
+        x2, weight, z = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.size(-1))
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        if z is not None:
+            dy2 = ext.bias_gelu_bwd(dy2, z, None)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = ctx.tp.gemm_all_reduce(dy2, weight, False, not ctx.reversed).view(ctx.in_shape)
+        if ctx.needs_input_grad[1]:
+            dw = gemm(x2, dy2, True, True) if ctx.reversed else gemm(dy2, x2, True, True)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = ext.colsum(dy2).to(ctx.bias_dtype)
+        return dx, dw, db, None, None, None
+
+
+class _ColumnParallelSeqFused(torch.autograd.Function):
+    """Sequence-parallel column layer: forward = all-gather(x) fused into the GEMM, backward input gradient =
+    GEMM fused with the reduce-scatter."""
+
+    @staticmethod
+    def forward(ctx, x_shard, weight, bias, reversed_, gelu, tp: FusedTP):
+        x2 = x_shard.reshape(-1, x_shard.size(-1))
+        n = weight.size(1) if reversed_ else weight.size(0)
+        z = None
+        if gelu and any(ctx.needs_input_grad[:3]):
+            z = torch.empty(x2.size(0) * tp.world, n, dtype=x2.dtype, device=x2.device)
+        y, gathered = tp.all_gather_gemm(x2.contiguous(), weight, reversed_, bias, gelu, z)
+        ctx.save_for_backward(gathered, weight, z)
+        ctx.reversed, ctx.tp = reversed_, tp
+        ctx.shard_shape = x_shard.shape
+        ctx.has_bias = bias is not None
+        ctx.bias_dtype = bias.dtype if bias is not None else None
+        lead = list(x_shard.shape[:-1])
+        lead[-1] *= tp.world  # the gathered (second to last) dim is the sequence
+        return y.view(*lead, n)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops.cuda_ops import gemm
+        ext = ops.load_ext(required=True)
+        gathered, weight, z = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.size(-1))
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        if z is not None:
+            dy2 = ext.bias_gelu_bwd(dy2, z, None)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = ctx.tp.gemm_reduce_scatter(dy2, weight, False, not ctx.reversed).view(ctx.shard_shape)
+        if ctx.needs_input_grad[1]:
+            dw = gemm(gathered, dy2, True, True) if ctx.reversed else gemm(dy2, gathered, True, True)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = ext.colsum(dy2).to(ctx.bias_dtype)
+        return dx, dw, db, None, None, None
+
+
+class _RowParallelSeqFused(torch.autograd.Function):
+    """Sequence-parallel row layer: forward = GEMM fused with the reduce-scatter, backward = all-gather(dy)
+    fused into both gradient GEMMs' producer."""
+
+    @staticmethod
+    def forward(ctx, x, weight, reversed_, tp: FusedTP):
+        x2 = x.reshape(-1, x.size(-1))
+        y = tp.gemm_reduce_scatter(x2, weight, False, reversed_)
+        ctx.save_for_backward(x2, weight)
+        ctx.reversed, ctx.tp, ctx.in_shape = reversed_, tp, x.shape
+        lead = list(x.shape[:-1])
+        lead[-1] //= tp.world
+        return y.view(*lead, y.size(-1))
+
+    @staticmethod
+    def backward(ctx, dy_shard):
+        from ..ops.cuda_ops import gemm
+        x2, weight = ctx.saved_tensors
+        d2 = dy_shard.reshape(-1, dy_shard.size(-1)).contiguous()
+        dx = dw = None
+        # dx = all_gather(dy) @ W : the gathered dy comes back as a by-product and feeds the weight gradient
+        dx2, dy_full = ctx.tp.all_gather_gemm(d2, weight, not ctx.reversed)
+        if ctx.needs_input_grad[0]:
+            dx = dx2.view(ctx.in_shape)
+        if ctx.needs_input_grad[1]:
+            dw = gemm(x2, dy_full, True, True) if ctx.reversed else gemm(dy_full, x2, True, True)
+        return dx, dw, None, None

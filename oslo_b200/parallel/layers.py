@@ -19,6 +19,9 @@ from .. import ops
 from .mpu import ceil_split_sizes
 
 
+_GELU_NAMES = ("gelu", "gelu_new", "gelu_tanh", "gelu_pytorch_tanh")
+
+
 def _linear(x: Tensor, weight: Tensor, bias: Optional[Tensor], reversed: bool, fused: bool,
             activation: Optional[str] = None) -> Tensor:
     if fused:
@@ -119,6 +122,14 @@ class ColumnParallelLinear(nn.Linear):
 
     def forward(self, x: Tensor, activation: Optional[str] = None) -> Tensor:
         mpu = self.mpu
+        if self.oslo_fused and not self.gather_output and activation in (None,) + _GELU_NAMES:
+            from . import fused_tp
+            n_out = self.weight.size(1) if self.reversed else self.weight.size(0)
+            rows = x.numel() // max(x.size(-1), 1) * (mpu.tp if (mpu is not None and self.sequence_parallel) else 1)
+            if fused_tp.fused_tp_usable(mpu, x, n_out, rows) and (not self.sequence_parallel or rows % (mpu.tp * 128) == 0):
+                tp = fused_tp.get_fused_tp(mpu.get_tensor_parallel_group())
+                fn = fused_tp._ColumnParallelSeqFused if self.sequence_parallel else fused_tp._ColumnParallelFused
+                return fn.apply(x, self.weight, self.bias, self.reversed, activation is not None, tp)
         if mpu is not None:
             x = mpu.gather_sequence(x, dim=-2) if self.sequence_parallel else mpu.broadcast(x)
         if self.gather_output and mpu is not None and mpu.tp > 1:
@@ -149,6 +160,15 @@ class RowParallelLinear(nn.Linear):
         mpu = self.mpu
         if mpu is not None and not self.input_is_parallel:
             x = mpu.scatter(x, dim=-1)
+        if self.oslo_fused:
+            from . import fused_tp
+            n_out = self.weight.size(1) if self.reversed else self.weight.size(0)
+            rows = x.numel() // max(x.size(-1), 1)
+            if fused_tp.fused_tp_usable(mpu, x, n_out) and (not self.sequence_parallel or rows % (mpu.tp * 128) == 0):
+                tp = fused_tp.get_fused_tp(mpu.get_tensor_parallel_group())
+                fn = fused_tp._RowParallelSeqFused if self.sequence_parallel else fused_tp._RowParallelFused
+                y = fn.apply(x, self.weight, self.reversed, tp)
+                return y if self.bias is None else y + self.bias
         y = _linear(x, self.weight, None, self.reversed, self.oslo_fused)
         if mpu is not None:
             y = mpu.reduce_scatter_sequence(y, dim=-2) if self.sequence_parallel else mpu.reduce(y)

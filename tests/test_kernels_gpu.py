@@ -266,3 +266,38 @@ def test_bounded_wait_reports_instead_of_hanging():
     x = torch.ones(8, device="cuda")
     co.reset_device_error(x)
     assert co.device_error_code(x) == 0
+
+
+@pytest.mark.parametrize("kind", ["gptj", "gpt2", "gpt_neo"])
+def test_fused_model_matches_eager_model(kind):
+    """Whole-model check: loss and every parameter gradient of the fused (kernel) model against the eager one."""
+    import oslo_b200 as ob
+    torch.manual_seed(0)
+    if kind == "gptj":
+        cfg = ob.GPTJConfig(vocab_size=512, n_positions=128, n_embd=256, n_layer=2, n_head=4, rotary_dim=16)
+        cls = ob.GPTJForCausalLM
+    elif kind == "gpt2":
+        cfg = ob.GPT2Config(vocab_size=512, n_positions=128, n_embd=256, n_layer=2, n_head=4, resid_pdrop=0.0,
+                            embd_pdrop=0.0, attn_pdrop=0.0)
+        cls = ob.GPT2LMHeadModel
+    else:
+        cfg = ob.GPTNeoConfig(vocab_size=512, max_position_embeddings=128, hidden_size=256, num_layers=2, num_heads=4,
+                              window_size=32)
+        cls = ob.GPTNeoForCausalLM
+    eager = cls(cfg).to(torch.bfloat16).cuda().train()
+    fused = cls(cfg).to(torch.bfloat16).cuda().train()
+    fused.load_state_dict(eager.state_dict())
+    fused.fuse()
+    ids = torch.randint(0, 512, (3, 128), device="cuda")
+    le = eager(input_ids=ids, labels=ids).loss
+    lf = fused(input_ids=ids, labels=ids, output_logits=False).loss
+    le.backward()
+    lf.backward()
+    assert abs(le.item() - lf.item()) < 0.03, (le.item(), lf.item())
+    ge = dict(eager.named_parameters())
+    worst = 0.0
+    for n, p in fused.named_parameters():
+        a, b = p.grad.float(), ge[n].grad.float()
+        rel = (a - b).norm() / (b.norm() + 1e-6)
+        worst = max(worst, rel.item())
+        assert rel < 0.08, (n, rel.item())
