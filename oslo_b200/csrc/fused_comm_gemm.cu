@@ -45,9 +45,9 @@ static int launch_comm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams&
 extern "C" int oslo_gemm_comm_16bit(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int a_mn_major,
                                     int b_mn_major, const void* bias, void* aux_out, int ld_aux_out, int flags,
                                     float alpha, void* const* peer_bufs_dev, void* own_buf, void* mc_base,
-                                    long long data_off, long long flag_off, int rank, int world, unsigned epoch,
-                                    int mode, int use_multimem, void* out, int ld_out, int wide_tiles, int* err_word,
-                                    int num_sms, cudaStream_t stream) {
+                                    long long data_off, long long flag_off, long long flag_bytes, int rank, int world,
+                                    unsigned epoch, unsigned done_base, int mode, int use_multimem, void* out,
+                                    int ld_out, int wide_tiles, int* err_word, int num_sms, cudaStream_t stream) {
   using namespace oslo;
   if (M <= 0 || N <= 0 || K <= 0 || world < 1 || rank < 0 || rank >= world) return -1;
   if (N % 8 || K % 8) return -3;
@@ -65,6 +65,15 @@ extern "C" int oslo_gemm_comm_16bit(const void* A, const void* B, int M, int N, 
   CommParams& c = p.comm;
   c.peer_bufs = peer_bufs_dev; c.mc_base = static_cast<uint8_t*>(mc_base); c.data_off = data_off; c.flag_off = flag_off;
   c.rank = rank; c.world = world; c.epoch = epoch; c.mode = mode; c.use_multimem = use_multimem && mc_base != nullptr;
+  {
+    // readiness words of this call must fit below the completion counter, which sits in the last 64 bytes
+    const long long tiles = static_cast<long long>((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+    const long long words = mode == COMM_ALLGATHER_A ? static_cast<long long>((M + BM - 1) / BM) * 8 * COMM_WARPS
+                                                     : tiles * world * 4;
+    if (words * 4 > flag_bytes - 64) return -8;
+    c.done_off = flag_off + flag_bytes - 64;
+    c.done_target = done_base + static_cast<unsigned>(tiles) * COMM_WARPS;
+  }
   c.out = out; c.ld_out = ld_out; c.ag_src = nullptr; c.ld_ag_src = 0; c.ag_parts = 1;
   CUtensorMap ta, tb;
   int rc;

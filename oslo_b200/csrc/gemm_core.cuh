@@ -21,7 +21,11 @@ struct CommParams {
   long long data_off;      // staging matrix: partial outputs [M,N] (reduce modes) or gathered A [M,K] (all-gather)
   long long flag_off;      // uint32 flags: one per tile / chunk, then the completion counter
   int rank, world;
-  uint32_t epoch;          // call number on this workspace slot, starts at 1; flags only ever grow
+  uint32_t epoch;          // generation of this call on its workspace slot (1, 2, 3, ...). Readiness words are
+                           // WRITTEN with this value (never counted), so stale words of earlier calls - whatever
+                           // their shape or mode - are simply smaller and nothing ever needs a reset
+  long long done_off;      // all-reduce: byte offset of the completion counter (counted; fixed location per slot)
+  uint32_t done_target;    // value the completion counter reaches when every tile of this call is final
   int mode;
   int use_multimem;
   void* out;               // reduce-scatter: this rank's [M/world, N] result (ordinary memory)
@@ -144,6 +148,35 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t targ
   return true;
 }
 
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void multimem_red_release_max(uint32_t* mc, uint32_t v) {
+  asm volatile("multimem.red.release.sys.global.max.u32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
+}
+// Whole-warp wait: words[0 .. nwords) must all have reached generation `gen` (lanes stride over the words).
+// Returns the same value on every lane.
+__device__ __forceinline__ bool warp_wait_words(const uint32_t* words, int nwords, uint32_t gen,
+                                                volatile int* abort_flag, int* err_word) {
+  const int lane = threadIdx.x & 31;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    bool mine = true;
+    for (int i = lane; i < nwords; i += 32) mine = mine && (static_cast<int32_t>(ld_acquire_sys(words + i) - gen) >= 0);
+    if (__all_sync(0xffffffffu, mine)) return true;
+    if ((++spins & 0x3f) == 0) {
+      bool give_up = (*abort_flag != 0);
+      if (!give_up && globaltimer_ns() - t0 > OSLO_WAIT_LIMIT_NS) {
+        give_up = true;
+        *abort_flag = 1;
+        if (err_word) atomicCAS(err_word, 0, ERR_WAIT_PEER);
+      }
+      if (__any_sync(0xffffffffu, give_up)) return false;
+    }
+  }
+}
+
 // which rank reduces output tile (tm, tn) / linear schedule index `tile`
 __device__ __forceinline__ int tile_owner(const CommParams& c, int tile, int tm, int M) {
   if (c.mode == COMM_REDUCE_SCATTER) return (tm * BM) / (M / c.world);
@@ -208,7 +241,47 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     }
   };
 
-  if (warp == 0) {
+  if (COMM && warp == 0 && p.comm.mode == COMM_ALLGATHER_A) {
+    // ------------------------------------------------------------ TMA producer, all-gather mode: the whole warp
+    // waits for the row block to arrive from its source rank, lane 0 issues the copies
+    const uint32_t* words = reinterpret_cast<const uint32_t*>(
+        static_cast<const uint8_t*>(p.comm.peer_bufs[p.comm.rank]) + p.comm.flag_off);
+    const int nwords = p.comm.ag_parts * COMM_WARPS;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int tm, tn;
+      coords(tile, tm, tn);
+      const int m0 = tm * BM, n0 = tn * BN;
+      ok = warp_wait_words(words + static_cast<size_t>(tm) * nwords, nwords, p.comm.epoch, abort_flag, p.err);
+      if (!ok) break;
+      asm volatile("fence.proxy.async.global;" ::: "memory");  // the TMA engine reads what peers just wrote
+      for (int kb = 0; kb < kblocks; ++kb) {
+        int ok_l = 1;
+        if (lane == 0) {
+          ok_l = mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, p.err, ERR_WAIT_EMPTY) ? 1 : 0;
+          if (ok_l) {
+            const uint32_t sa = smem_base + stage * STAGE_BYTES;
+            const uint32_t sb = sa + A_BYTES;
+            mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+            const int k0 = kb * BK;
+            tma_load_2d(sa, &tma_a, full_bar(stage), k0, m0);
+            if (!p.b_mn_major) {
+              tma_load_2d(sb, &tma_b, full_bar(stage), k0, n0);
+            } else {
+#pragma unroll
+              for (int c = 0; c < BN / 64; ++c)
+                tma_load_2d(sb + c * 8192, &tma_b, full_bar(stage), n0 + c * 64, k0);
+            }
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok_l, 0) != 0;
+        if (!ok) break;
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tma_a);
@@ -220,14 +293,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         int tm, tn;
         coords(tile, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
-        if (COMM && p.comm.mode == COMM_ALLGATHER_A) {
-          // rows m0.. of the gathered A arrive from rank m0 / (M / world); its comm warps raise flag[tm]
-          const uint32_t* flags = reinterpret_cast<const uint32_t*>(
-              static_cast<const uint8_t*>(p.comm.peer_bufs[p.comm.rank]) + p.comm.flag_off);
-          ok = wait_flag_ge(flags + tm, p.comm.epoch * static_cast<uint32_t>(p.comm.ag_parts) * COMM_WARPS, abort_flag, p.err);
-          if (!ok) break;
-          asm volatile("fence.proxy.async.global;" ::: "memory");  // the TMA engine reads what peers just wrote
-        }
         for (int kb = 0; kb < kblocks; ++kb) {
           ok = mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, p.err, ERR_WAIT_EMPTY);
           if (!ok) break;
@@ -432,14 +497,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       if (lane == 0) mbar_arrive(tempty_bar(buf));
       if (COMM && (p.comm.mode == COMM_ALLREDUCE || p.comm.mode == COMM_REDUCE_SCATTER)) {
         // this rank's partial tile is in its symmetric buffer: publish it to the rank that reduces the tile
-        // (one arrival per epilogue warp, so no CTA-wide barrier is needed: a tile is complete on a rank
-        // after 4 arrivals)
+        // (one word per (tile, rank, epilogue warp), so no CTA-wide barrier and no counting is needed)
         __threadfence_system();
         __syncwarp();
         if (lane == 0) {
           const int owner = tile_owner(p.comm, tile, tm, p.M);
-          uint32_t* f = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(p.comm.peer_bufs[owner]) + p.comm.flag_off) + tile;
-          red_release_sys_add(f, 1u);
+          uint32_t* f = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(p.comm.peer_bufs[owner]) + p.comm.flag_off) +
+                        (static_cast<size_t>(tile) * p.comm.world + p.comm.rank) * 4 + (warp - 2);
+          st_release_sys(f, p.comm.epoch);
         }
       }
     }
@@ -476,19 +541,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         }
         __threadfence_system();
         __syncwarp();
-        if ((cw & 31) == 0) {  // one arrival per communication warp
-          const int flag_idx = c.rank * chunks + ch;  // = global 128-row block index
+        if ((cw & 31) == 0) {  // one word per (row block, part, communication warp)
+          const size_t word = (static_cast<size_t>(c.rank * chunks + ch) * parts + part) * COMM_WARPS + (cw >> 5);
           if (mm) {
-            multimem_red_release_add(reinterpret_cast<uint32_t*>(c.mc_base + c.flag_off) + flag_idx, 1u);
+            multimem_red_release_max(reinterpret_cast<uint32_t*>(c.mc_base + c.flag_off) + word, c.epoch);
           } else {
             for (int w = 0; w < c.world; ++w)
-              red_release_sys_add(reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(c.peer_bufs[w]) + c.flag_off) + flag_idx, 1u);
+              st_release_sys(reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(c.peer_bufs[w]) + c.flag_off) + word, c.epoch);
           }
         }
       }
     } else {
       const int num_tiles_c = p.tiles_m * p.tiles_n;
-      const uint32_t target = c.epoch * static_cast<uint32_t>(c.world) * 4u;  // 4 epilogue warps per rank
       const int rows_per_rank = p.M / c.world;
       int owned = 0;
       for (int tile = 0; tile < num_tiles_c && ok; ++tile) {
@@ -497,9 +561,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         if (tile_owner(c, tile, tm, p.M) != c.rank) continue;
         const int mine = owned++;
         if (mine % static_cast<int>(gridDim.x) != static_cast<int>(blockIdx.x)) continue;
-        if ((cw & 31) == 0) wait_flag_ge(my_flags + tile, target, abort_flag, p.err);
-        __syncwarp();
-        if (*abort_flag) { ok = false; break; }
+        ok = warp_wait_words(my_flags + static_cast<size_t>(tile) * c.world * 4, c.world * 4, c.epoch, abort_flag, p.err);
+        if (!ok) break;
         const int m0 = tm * BM, n0 = tn * BN;
         const int rows = min(BM, p.M - m0), cols = min(BN, p.N - n0);
         const int vpr = cols / 8;
@@ -556,17 +619,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           __syncwarp();
           if ((cw & 31) == 0) {
             if (mm) {
-              multimem_red_release_add(reinterpret_cast<uint32_t*>(c.mc_base + c.flag_off) + num_tiles_c, 1u);
+              multimem_red_release_add(reinterpret_cast<uint32_t*>(c.mc_base + c.done_off), 1u);
             } else {
               for (int w = 0; w < c.world; ++w)
-                red_release_sys_add(reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(c.peer_bufs[w]) + c.flag_off) + num_tiles_c, 1u);
+                red_release_sys_add(reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(c.peer_bufs[w]) + c.done_off), 1u);
             }
           }
         }
       }
       if (c.mode == COMM_ALLREDUCE && ok && cw == 0) {
         // the result is complete on this rank once every tile of every owner has been broadcast
-        wait_flag_ge(my_flags + num_tiles_c, c.epoch * static_cast<uint32_t>(num_tiles_c) * COMM_WARPS, abort_flag, p.err);
+        wait_flag_ge(reinterpret_cast<const uint32_t*>(my_base + c.done_off), c.done_target, abort_flag, p.err);
       }
     }
   }

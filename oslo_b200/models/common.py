@@ -164,6 +164,16 @@ def merge_heads(x: Tensor) -> Tensor:
     return x.permute(0, 2, 1, 3).reshape(b, s, h * d)
 
 
+def to_batch_seq(x: Tensor, seq_shape) -> Tensor:
+    """``[1, B*S, n] -> [B, S, n]`` under sequence parallelism (identity otherwise)."""
+    return x if seq_shape is None else x.reshape(seq_shape[0], seq_shape[1], x.size(-1))
+
+
+def to_token_rows(x: Tensor, seq_shape) -> Tensor:
+    """``[B, S, n] -> [1, B*S, n]`` under sequence parallelism (identity otherwise)."""
+    return x if seq_shape is None else x.reshape(1, seq_shape[0] * seq_shape[1], x.size(-1))
+
+
 def maybe_dropout(x: Tensor, p: float, training: bool) -> Tensor:
     return F.dropout(x, p, training) if (p > 0.0 and training) else x
 
@@ -227,8 +237,16 @@ class DecoderBackbone(PreTrainedModel):
         if head_mask is not None and head_mask.dim() == 1:
             head_mask = head_mask[None, :].expand(self.num_blocks(), -1)
         out = dict(rest)
+        if self.sequence_parallel_active():
+            # a training layout: no KV cache, and the token rows must split evenly over the group
+            if (bsz * seq) % (self.mpu.tp) or past_len:
+                raise ValueError("sequence parallelism needs batch*seq divisible by tensor_parallel_size and no past")
+            use_cache, cache, layer_pasts = False, None, [None] * self.num_blocks()
+            out_bs = (bsz, seq)
+        else:
+            out_bs = None
         out.update(
-            input_ids=input_ids, inputs_embeds=inputs_embeds, token_type_ids=token_type_ids,
+            _bs=out_bs, input_ids=input_ids, inputs_embeds=inputs_embeds, token_type_ids=token_type_ids,
             position_ids=position_ids, attention_mask=attention_mask, head_mask=head_mask,
             layer_pasts=layer_pasts, cache=cache, use_cache=use_cache, output_attentions=output_attentions,
             output_hidden_states=output_hidden_states, return_dict=return_dict,
@@ -238,9 +256,19 @@ class DecoderBackbone(PreTrainedModel):
         )
         return out
 
+    def sequence_parallel_active(self) -> bool:
+        mpu = getattr(self, "mpu", None)
+        return bool(getattr(self, "sequence_parallel", False)) and mpu is not None and mpu.tp > 1
+
     def preblock_fn(self, **kw) -> Dict[str, Any]:
         kw = self.prepare_fn(**kw)
-        kw["hidden_states"] = self.embed(kw["input_ids"], kw["position_ids"], kw["token_type_ids"], kw["inputs_embeds"])
+        hs = self.embed(kw["input_ids"], kw["position_ids"], kw["token_type_ids"], kw["inputs_embeds"])
+        if self.sequence_parallel_active():
+            # sequence parallelism: between the tensor-parallel GEMMs every rank keeps 1/tp of the flattened
+            # (batch, position) token rows; the column-parallel layers gather them, the row-parallel ones scatter
+            b, s_, h = hs.shape
+            hs = self.mpu.scatter(hs.reshape(1, b * s_, h), dim=1)
+        kw["hidden_states"] = hs
         return kw
 
     def block_fn(self, layer_id: int, **kw) -> Dict[str, Any]:
@@ -252,6 +280,8 @@ class DecoderBackbone(PreTrainedModel):
         args = dict(layer_past=kw["layer_pasts"][layer_id], attention_mask=kw["attention_mask"],
                     position_ids=kw["position_ids"], head_mask=hm, use_cache=kw["use_cache"],
                     output_attentions=kw["output_attentions"], cache=kw["cache"], layer_id=layer_id)
+        if kw.get("_bs") is not None:
+            args["seq_shape"] = kw["_bs"]
         for extra in ("encoder_hidden_states", "encoder_attention_mask"):
             if kw.get(extra) is not None:
                 args[extra] = kw[extra]
@@ -269,6 +299,11 @@ class DecoderBackbone(PreTrainedModel):
 
     def postblock_fn(self, **kw) -> Dict[str, Any]:
         hs = self.ln_f(kw["hidden_states"])
+        if kw.get("_bs") is not None:
+            b, s_ = kw["_bs"]
+            # what follows (head, loss) is computed identically on every rank and its input gradient is already
+            # summed over the group, so the backward of this gather keeps the local rows (no second reduction)
+            hs = self.mpu.gather(hs, dim=1, full_size=b * s_).reshape(b, s_, hs.size(-1))
         if kw["all_hidden_states"] is not None:
             kw["all_hidden_states"].append(hs)
         if kw["cache"] is not None:

@@ -22,7 +22,7 @@ from ...modeling_utils import (GPT2DoubleHeadsModelOutput, PretrainedConfig, Pre
 from ...parallel.layers import Conv1D, Embedding, LayerNorm, Linear
 from ...parallel.mpu import Layer, LayerPolicy
 from ..common import (AttentionCore, CausalLMHeadMixin, DecoderBackbone, SequenceClassificationMixin,
-                      maybe_dropout, merge_heads, split_heads)
+                      maybe_dropout, merge_heads, split_heads, to_batch_seq, to_token_rows)
 
 
 class GPT2Config(PretrainedConfig):
@@ -90,7 +90,7 @@ class GPT2Attention(AttentionCore):
 
     def forward(self, hidden_states: Tensor, layer_past=None, attention_mask=None, position_ids=None,
                 head_mask=None, use_cache=False, output_attentions=False, cache=None, layer_id=0,
-                encoder_hidden_states=None, encoder_attention_mask=None):
+                encoder_hidden_states=None, encoder_attention_mask=None, seq_shape=None):
         nh, hd = self.num_heads, self.head_dim
         if encoder_hidden_states is not None:
             if not self.is_cross_attention:
@@ -101,11 +101,11 @@ class GPT2Attention(AttentionCore):
             out, probs = self._cross_attention(q, k, v, encoder_attention_mask, head_mask)
             present = None
         else:
-            q, k, v = self.c_attn(hidden_states).split(self.split_size, dim=2)
+            q, k, v = to_batch_seq(self.c_attn(hidden_states), seq_shape).split(self.split_size, dim=2)
             q, k, v = split_heads(q, nh, hd), split_heads(k, nh, hd), split_heads(v, nh, hd)
             out, present, probs = self.attend_with_cache(q, k, v, layer_past, cache, layer_id, attention_mask,
                                                          use_cache, output_attentions, head_mask)
-        out = self.c_proj(merge_heads(out))
+        out = self.c_proj(to_token_rows(merge_heads(out), seq_shape))
         return maybe_dropout(out, self.resid_pdrop, self.training), present, probs
 
     def _cross_attention(self, q, k, v, encoder_attention_mask, head_mask):

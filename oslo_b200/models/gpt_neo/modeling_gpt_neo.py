@@ -19,7 +19,7 @@ from ...modeling_utils import PretrainedConfig, PreTrainedModel
 from ...parallel.layers import Embedding, LayerNorm, Linear
 from ...parallel.mpu import Layer, LayerPolicy
 from ..common import (AttentionCore, CausalLMHeadMixin, DecoderBackbone, SequenceClassificationMixin,
-                      maybe_dropout, merge_heads, split_heads)
+                      maybe_dropout, merge_heads, split_heads, to_batch_seq, to_token_rows)
 
 
 class GPTNeoConfig(PretrainedConfig):
@@ -77,14 +77,14 @@ class GPTNeoSelfAttention(AttentionCore):
         self.out_proj = Linear(self.embed_dim, self.embed_dim, bias=True)
 
     def forward(self, hidden_states: Tensor, layer_past=None, attention_mask=None, position_ids=None,
-                head_mask=None, use_cache=False, output_attentions=False, cache=None, layer_id=0):
+                head_mask=None, use_cache=False, output_attentions=False, cache=None, layer_id=0, seq_shape=None):
         nh, hd = self.num_heads, self.head_dim
-        q = split_heads(self.q_proj(hidden_states), nh, hd)
-        k = split_heads(self.k_proj(hidden_states), nh, hd)
-        v = split_heads(self.v_proj(hidden_states), nh, hd)
+        q = split_heads(to_batch_seq(self.q_proj(hidden_states), seq_shape), nh, hd)
+        k = split_heads(to_batch_seq(self.k_proj(hidden_states), seq_shape), nh, hd)
+        v = split_heads(to_batch_seq(self.v_proj(hidden_states), seq_shape), nh, hd)
         out, present, probs = self.attend_with_cache(q, k, v, layer_past, cache, layer_id, attention_mask,
                                                      use_cache, output_attentions, head_mask)
-        out = self.out_proj(merge_heads(out))
+        out = self.out_proj(to_token_rows(merge_heads(out), seq_shape))
         return maybe_dropout(out, self.resid_pdrop, self.training), present, probs
 
 

@@ -19,7 +19,7 @@ from ...modeling_utils import PretrainedConfig, PreTrainedModel
 from ...parallel.layers import Embedding, LayerNorm, Linear
 from ...parallel.mpu import Layer, LayerPolicy
 from ..common import (AttentionCore, CausalLMHeadMixin, DecoderBackbone, SequenceClassificationMixin,
-                      maybe_dropout, merge_heads, split_heads)
+                      maybe_dropout, merge_heads, split_heads, to_token_rows)
 
 
 class GPTJConfig(PretrainedConfig):
@@ -56,8 +56,8 @@ class GPTJAttention(AttentionCore):
         self.out_proj = Linear(self.embed_dim, self.embed_dim, bias=False)
 
     def forward(self, hidden_states: Tensor, layer_past=None, attention_mask=None, position_ids=None,
-                head_mask=None, use_cache=False, output_attentions=False, cache=None, layer_id=0):
-        b, s, _ = hidden_states.shape
+                head_mask=None, use_cache=False, output_attentions=False, cache=None, layer_id=0, seq_shape=None):
+        b, s = seq_shape if seq_shape is not None else hidden_states.shape[:2]
         nh, hd = self.num_attention_heads, self.head_dim
         q = self.q_proj(hidden_states).view(b, s, nh, hd)
         k = self.k_proj(hidden_states).view(b, s, nh, hd)
@@ -68,7 +68,7 @@ class GPTJAttention(AttentionCore):
         q, k, v = (t.permute(0, 2, 1, 3) for t in (q, k, v))
         out, present, probs = self.attend_with_cache(q, k, v, layer_past, cache, layer_id, attention_mask,
                                                      use_cache, output_attentions, head_mask)
-        out = self.out_proj(merge_heads(out))
+        out = self.out_proj(to_token_rows(merge_heads(out), seq_shape))
         return maybe_dropout(out, self.resid_pdrop, self.training), present, probs
 
 

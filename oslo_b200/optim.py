@@ -24,6 +24,21 @@ from torch import Tensor
 from . import ops
 
 
+def sync_sequence_parallel_grads(model) -> None:
+    """Sum, over the tensor-parallel group, the gradients of parameters that a sequence-parallel model applies
+    to a token shard (LayerNorm weights, row-parallel biases). ``FusedAdamW(model=...)`` does this itself;
+    call it by hand before ``step()`` of any other optimizer."""
+    params = [p for p in (getattr(model, "_sp_partial_params", None) or []) if p.grad is not None]
+    if not params:
+        return
+    flat = torch.cat([p.grad.reshape(-1) for p in params])
+    dist.all_reduce(flat, group=model.mpu.get_tensor_parallel_group())
+    off = 0
+    for p in params:
+        p.grad.copy_(flat[off: off + p.numel()].view_as(p.grad))
+        off += p.numel()
+
+
 class FlatBuffers:
     """One flat parameter buffer + one flat gradient buffer per dtype; tensors become views."""
 
@@ -68,7 +83,7 @@ class FusedAdamW:
 
     def __init__(self, params: Iterable[torch.nn.Parameter], lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 0.01, max_grad_norm: Optional[float] = None, shard_group=None,
-                 grad_average_group=None, model_parallel_group=None) -> None:
+                 grad_average_group=None, model_parallel_group=None, model=None) -> None:
         self.lr, self.betas, self.eps, self.weight_decay = lr, tuple(betas), eps, weight_decay
         self.max_grad_norm = max_grad_norm
         self.shard_group = shard_group
@@ -87,6 +102,10 @@ class FusedAdamW:
         self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
         self.step_count = 0
         self.grads_already_reduced = False  # set by DistributedDataParallel, which all-reduces buckets itself
+        # sequence parallelism: LayerNorm weights and row-parallel biases act on a token shard, so their
+        # gradients must be summed over the tensor-parallel group before the update
+        self._sp_params = list(getattr(model, "_sp_partial_params", []) or []) if model is not None else []
+        self._sp_group = model.mpu.get_tensor_parallel_group() if self._sp_params else None
         self.param_groups = [dict(params=self.buf.params, lr=lr, betas=self.betas, eps=eps, weight_decay=weight_decay)]
 
     # ------------------------------------------------------------------ API
@@ -104,8 +123,20 @@ class FusedAdamW:
                 dist.all_reduce(sq, group=grp)
         return sq.sqrt()
 
+    def sync_sequence_parallel_grads(self) -> None:
+        grads = [p.grad for p in self._sp_params if p.grad is not None]
+        if not grads:
+            return
+        flat = torch.cat([g.reshape(-1) for g in grads])
+        dist.all_reduce(flat, group=self._sp_group)
+        off = 0
+        for g in grads:
+            g.copy_(flat[off: off + g.numel()].view_as(g))
+            off += g.numel()
+
     @torch.no_grad()
     def step(self) -> None:
+        self.sync_sequence_parallel_grads()
         self.step_count += 1
         lr = self.param_groups[0]["lr"]
         b1, b2 = self.betas

@@ -231,6 +231,8 @@ class PipelineParallelEngine:
         s = ref.size(-1) if kw.get("input_ids") is not None else ref.size(1)
         cfg = self.model.config
         h = getattr(cfg, "n_embd", None) or cfg.hidden_size
+        if getattr(self.model.base_model, "sequence_parallel", False) and self.mpu.tp > 1:
+            return (1, b * s // self.mpu.tp, h)
         return (b, s, h)
 
     # ------------------------------------------------------------------ stage execution

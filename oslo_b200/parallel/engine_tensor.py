@@ -79,6 +79,8 @@ class TensorParallelEngine:
         for n, p in model.named_parameters(remove_duplicate=False):
             self._names.setdefault(id(p), []).append(n)
         self.specs: Dict[str, ShardSpec] = {}
+        self._sp_partial: List[Optional[nn.Parameter]] = []
+        self._in_block_or_post = False
 
     # ------------------------------------------------------------------ public
     def parallelize(self) -> None:
@@ -92,9 +94,14 @@ class TensorParallelEngine:
                 self._block(policy, block, cfg)
             for layer in policy.postblock_layers(model, cfg):
                 self._replicated(layer)
+                self._sp_partial += [layer.weight, layer.bias]
         for layer in model.get_head_layers():
             self._head(layer)
         model._tp_specs = self.specs
+        if self.sequence_parallel:
+            model.base_model.sequence_parallel = True
+            # parameters applied to a token shard see only 1/tp of the tokens: their gradients are partial sums
+            model._sp_partial_params = [p for p in self._sp_partial if p is not None]
 
     # ------------------------------------------------------------------ pieces
     def _block(self, policy, block: nn.Module, cfg) -> None:
@@ -111,6 +118,7 @@ class TensorParallelEngine:
             self._row(layer)
         for layer in policy.attn_norm(block, cfg) + policy.mlp_norm(block, cfg) + policy.copy_to_all(block, cfg):
             self._replicated(layer)
+            self._sp_partial += [layer.weight, layer.bias]
 
     def _record(self, p: Tensor, spec: ShardSpec) -> None:
         for n in self._names.get(id(p), []):
@@ -141,6 +149,7 @@ class TensorParallelEngine:
         self._cut(layer.weight, wdim, layer.n_fused, "row", m)
         if layer.bias is not None:
             self._record(layer.bias, ShardSpec("replicated", 0, 1, layer.bias.size(0)))
+            self._sp_partial.append(layer.bias)
         self._swap(m, RowParallelLinear, layer)
         m.input_is_parallel = layer.input_is_parallel
         m.sequence_parallel = self.sequence_parallel

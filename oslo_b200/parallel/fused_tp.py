@@ -25,7 +25,7 @@ from ..config import get_config
 from .symmetric import SymmetricWorkspace
 
 MODE_ALLREDUCE, MODE_REDUCE_SCATTER, MODE_ALLGATHER = 1, 2, 3
-_FLAG_BYTES = 1 << 20          # room for 256K tile flags per slot
+_FLAG_BYTES = 4 << 20          # readiness words (one per tile, rank and warp) + the completion counter, per slot
 _CONTEXTS: Dict[str, "FusedTP"] = {}
 
 
@@ -37,6 +37,7 @@ class FusedTP:
         self.world, self.rank = self.ws.world, self.ws.rank
         self.slot_bytes = mb * 2 ** 20
         self.epochs = [0, 0]
+        self.done_totals = [0, 0]
         self.calls = 0
         self.own_base = self.ws.buf.data_ptr()
         self.use_multimem = get_config().use_multimem and self.ws.has_multicast
@@ -53,10 +54,11 @@ class FusedTP:
 
     def _call(self, a, b, a_mn, b_mn, bias, aux_out, out, flags, M, N, K, mode):
         slot, data_off, flag_off, epoch = self._next_slot()
-        ops.load_ext(required=True).gemm_comm(
+        inc = ops.load_ext(required=True).gemm_comm(
             a, b, int(a_mn), int(b_mn), bias, aux_out, out, flags, 1.0, M, N, K, self.ws.peer_ptrs_dev, self.own_base,
-            self.ws.mc_ptr if self.use_multimem else 0, data_off, flag_off, self.rank, self.world, epoch, mode,
-            self.use_multimem)
+            self.ws.mc_ptr if self.use_multimem else 0, data_off, flag_off, _FLAG_BYTES, self.rank, self.world,
+            epoch, self.done_totals[slot] & 0xFFFFFFFF, mode, self.use_multimem)
+        self.done_totals[slot] += int(inc)
         return data_off
 
     def gemm_all_reduce(self, a: Tensor, b: Tensor, a_mn: bool, b_mn: bool) -> Tensor:

@@ -56,10 +56,11 @@ def oracle_steps(kind, steps, micro=None, lr=1e-2):
     return losses, {k: v.detach().clone() for k, v in model.state_dict().items()}
 
 
-def _train_parallel(rank, world, kind, tp, pp, steps, micro, expected_losses, tmpdir, fuse, out_logits):
+def _train_parallel(rank, world, kind, tp, pp, steps, micro, expected_losses, tmpdir, fuse, out_logits, seq_par=False):
+    from oslo_b200.optim import sync_sequence_parallel_grads
     model = build(kind).train()
     model = ob.parallelize(model, tensor_parallel_size=tp, pipeline_parallel_size=pp,
-                           micro_batch_size=micro or 1)
+                           micro_batch_size=micro or 1, sequence_parallel=seq_par)
     if fuse:
         model.fuse()
     mpu = model.mpu
@@ -82,6 +83,7 @@ def _train_parallel(rank, world, kind, tp, pp, steps, micro, expected_losses, tm
             out = model(**b, output_logits=out_logits)
             out.loss.backward()
             loss = float(out.loss)
+        sync_sequence_parallel_grads(model)
         if dp > 1:
             import torch.distributed as dist
             for p in params:
@@ -114,6 +116,22 @@ def test_tensor_parallel_training_matches_oracle(kind, fuse, out_logits):
         _check_merged(d, state, 1e-3)
         names = sorted(f for f in os.listdir(os.path.join(d, "split")) if f.endswith(".bin"))
         assert names == ["pytorch_model_tp=0_pp=0.bin", "pytorch_model_tp=1_pp=0.bin"]
+
+
+@pytest.mark.parametrize("kind", ["gpt2", "gpt_neo", "gptj"])
+def test_sequence_parallel_training_matches_oracle(kind):
+    """Megatron-style sequence parallelism inside the TP group (absent in the reference): same losses, same weights."""
+    losses, state = oracle_steps(kind, steps=3)
+    with tempfile.TemporaryDirectory() as d:
+        run_distributed(_train_parallel, 2, kind, 2, 1, 3, None, losses, d, False, True, True)
+        _check_merged(d, state, 1e-3)
+
+
+def test_sequence_parallel_with_pipeline():
+    losses, state = oracle_steps("gptj", steps=2, micro=2)
+    with tempfile.TemporaryDirectory() as d:
+        run_distributed(_train_parallel, 4, "gptj", 2, 2, 2, 2, losses, d, False, True, True)
+        _check_merged(d, state, 1e-3)
 
 
 @pytest.mark.parametrize("kind", ["gpt2", "gptj"])
