@@ -373,7 +373,7 @@ int64_t gemm_comm(const Tensor& a, const Tensor& b, int64_t a_mn, int64_t b_mn, 
                const optional<Tensor>& aux_out, const optional<Tensor>& out, int64_t flags, double alpha, int64_t M,
                int64_t N, int64_t K, int64_t peer_bufs_dev, int64_t own_buf, int64_t mc_base, int64_t data_off,
                int64_t flag_off, int64_t flag_bytes, int64_t rank, int64_t world, int64_t epoch, int64_t done_base,
-               int64_t mode, bool use_multimem) {
+               int64_t mode, bool use_multimem, const optional<Tensor>& trace) {
   check_2d_operand(a, "a");
   check_2d_operand(b, "b");
   TORCH_CHECK(a.scalar_type() == b.scalar_type() && (a.scalar_type() == at::kBFloat16 || a.scalar_type() == at::kHalf),
@@ -407,6 +407,7 @@ int64_t gemm_comm(const Tensor& a, const Tensor& b, int64_t a_mn, int64_t b_mn, 
       reinterpret_cast<void* const*>(peer_bufs_dev), reinterpret_cast<void*>(own_buf), reinterpret_cast<void*>(mc_base),
       data_off, flag_off, flag_bytes, static_cast<int>(rank), static_cast<int>(world), static_cast<unsigned>(epoch),
       static_cast<unsigned>(done_base), static_cast<int>(mode), use_multimem ? 1 : 0, out_ptr, ld_out, wide,
+      trace.has_value() && trace->defined() ? reinterpret_cast<unsigned long long*>(trace->data_ptr<int64_t>()) : nullptr,
       st.err.data_ptr<int>(), st.sms, cur_stream());
   check_rc(rc, "gemm_comm");
   // how far this call advances the slot's completion counter (the caller keeps the running total)
@@ -449,6 +450,6 @@ TORCH_LIBRARY(oslo_b200, m) {
   m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int window, Tensor? kpm) -> (Tensor, Tensor)", &flash_fwd);
   m.def("flash_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale, bool causal, int window, Tensor? kpm) -> (Tensor, Tensor, Tensor)", &flash_bwd);
   m.def("decode_attn(Tensor q, Tensor kc, Tensor vc, Tensor lengths, float scale, int window) -> Tensor", &decode_attn);
-  m.def("gemm_comm(Tensor a, Tensor b, int a_mn, int b_mn, Tensor? bias, Tensor(a!)? aux_out, Tensor(b!)? out, int flags, float alpha, int M, int N, int K, int peer_bufs_dev, int own_buf, int mc_base, int data_off, int flag_off, int flag_bytes, int rank, int world, int epoch, int done_base, int mode, bool use_multimem) -> int", &gemm_comm);
+  m.def("gemm_comm(Tensor a, Tensor b, int a_mn, int b_mn, Tensor? bias, Tensor(a!)? aux_out, Tensor(b!)? out, int flags, float alpha, int M, int N, int K, int peer_bufs_dev, int own_buf, int mc_base, int data_off, int flag_off, int flag_bytes, int rank, int world, int epoch, int done_base, int mode, bool use_multimem, Tensor(c!)? trace) -> int", &gemm_comm);
   m.def("allreduce_symm(int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(a!) out, int numel, int rank, int world, bool use_multimem) -> ()", &allreduce_symm);
 }

@@ -16,6 +16,8 @@
 //     LOCAL memory, with a plain (non-multicast) TMA load. Row blocks are walked starting at the local shard.
 // Flags are epoch-counted and never reset; two workspace slots alternate so a fast rank cannot overwrite data
 // a slow rank still reads. A wait that runs out records ERR_WAIT_PEER and the kernel tears down normally.
+#include <cstdlib>
+
 #include "gemm_core.cuh"
 
 namespace oslo {
@@ -47,12 +49,14 @@ extern "C" int oslo_gemm_comm_16bit(const void* A, const void* B, int M, int N, 
                                     float alpha, void* const* peer_bufs_dev, void* own_buf, void* mc_base,
                                     long long data_off, long long flag_off, long long flag_bytes, int rank, int world,
                                     unsigned epoch, unsigned done_base, int mode, int use_multimem, void* out,
-                                    int ld_out, int wide_tiles, int* err_word, int num_sms, cudaStream_t stream) {
+                                    int ld_out, int wide_tiles, unsigned long long* trace, int* err_word, int num_sms,
+                                    cudaStream_t stream) {
   using namespace oslo;
   if (M <= 0 || N <= 0 || K <= 0 || world < 1 || rank < 0 || rank >= world) return -1;
   if (N % 8 || K % 8) return -3;
   if (mode != COMM_ALLREDUCE && (M % (world * BM))) return -5;  // row ownership must fall on tile boundaries
   if (mode == COMM_ALLGATHER_A && a_mn_major) return -6;
+  if (!(use_multimem && mc_base != nullptr) && world > 8) return -9;  // peer-load reduction is unrolled for <= 8 ranks
   static thread_local bool ctx_bound = false;
   if (!ctx_bound) { cudaFree(nullptr); ctx_bound = true; }
   const bool fp16 = (flags & GEMM_FLAG_FP16) != 0;
@@ -75,6 +79,11 @@ extern "C" int oslo_gemm_comm_16bit(const void* A, const void* B, int M, int N, 
     c.done_target = done_base + static_cast<unsigned>(tiles) * COMM_WARPS;
   }
   c.out = out; c.ld_out = ld_out; c.ag_src = nullptr; c.ld_ag_src = 0; c.ag_parts = 1;
+  {
+    const char* dbg = getenv("OSLO_B200_COMM_DEBUG");
+    c.debug = dbg ? atoi(dbg) : 0;
+  }
+  c.trace = trace;
   CUtensorMap ta, tb;
   int rc;
   if (mode == COMM_ALLGATHER_A) {

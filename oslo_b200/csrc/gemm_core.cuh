@@ -32,7 +32,9 @@ struct CommParams {
   int ld_out;
   const void* ag_src;      // all-gather: this rank's [M/world, K] shard (ordinary memory)
   int ld_ag_src;
-  int ag_parts;            // column parts per 128-row chunk (flag target = epoch * ag_parts)
+  int ag_parts;            // column parts per 128-row chunk
+  unsigned long long* trace;  // optional [gridDim.x][8] device timestamps (ns) of the phases of every CTA, or nullptr
+  int debug;               // experiments: bit 0 = gpu-scope fence in the epilogue, bit 1 = communication warps move no data
 };
 
 struct GemmParams {
@@ -101,7 +103,8 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tn = r / rows;
 }
 
-constexpr int COMM_WARPS = 4;
+constexpr int COMM_WARPS = 8;
+constexpr int COMM_THREADS = 32 * COMM_WARPS;
 constexpr int GEMM_THREADS_COMM = GEMM_THREADS + 32 * COMM_WARPS;
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -165,6 +168,7 @@ __device__ __forceinline__ bool warp_wait_words(const uint32_t* words, int nword
     bool mine = true;
     for (int i = lane; i < nwords; i += 32) mine = mine && (static_cast<int32_t>(ld_acquire_sys(words + i) - gen) >= 0);
     if (__all_sync(0xffffffffu, mine)) return true;
+    __nanosleep(100);  // keep the polling traffic of idle communication warps off the L2
     if ((++spins & 0x3f) == 0) {
       bool give_up = (*abort_flag != 0);
       if (!give_up && globaltimer_ns() - t0 > OSLO_WAIT_LIMIT_NS) {
@@ -177,10 +181,11 @@ __device__ __forceinline__ bool warp_wait_words(const uint32_t* words, int nword
   }
 }
 
-// which rank reduces output tile (tm, tn) / linear schedule index `tile`
-__device__ __forceinline__ int tile_owner(const CommParams& c, int tile, int tm, int M) {
-  if (c.mode == COMM_REDUCE_SCATTER) return (tm * BM) / (M / c.world);
-  return tile % c.world;
+// Readiness words and ownership are indexed by idx = tm * tiles_n + tn.
+// all-reduce: owner = idx % world (work spread evenly); reduce-scatter: the rank that keeps row block tm.
+__device__ __forceinline__ int tile_owner(const CommParams& c, int idx, int tm, int tiles_m) {
+  if (c.mode == COMM_REDUCE_SCATTER) return tm / (tiles_m / c.world);
+  return idx % c.world;
 }
 
 template <int BN, int STAGES, bool COMM>
@@ -229,6 +234,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  unsigned long long* trace = nullptr;
+  if (COMM && p.comm.trace) {
+    trace = p.comm.trace + static_cast<size_t>(blockIdx.x) * 8;
+    if (threadIdx.x == 0) trace[0] = globaltimer_ns();
+  }
 
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int kblocks = (p.K + BK - 1) / BK;
@@ -238,6 +248,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     if (COMM && p.comm.mode == COMM_ALLGATHER_A) {
       tm += p.comm.rank * (p.tiles_m / p.comm.world);
       if (tm >= p.tiles_m) tm -= p.tiles_m;
+    }
+    if (COMM && p.comm.mode == COMM_REDUCE_SCATTER) {
+      // interleave the ranks' row blocks in time: raster position i -> block (i / world) of rank (i % world)
+      const int per = p.tiles_m / p.comm.world;
+      tm = (tm % p.comm.world) * per + tm / p.comm.world;
     }
   };
 
@@ -356,6 +371,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         }
         if (ok) umma_commit(tfull_bar(buf));
       }
+      if (trace) trace[2] = globaltimer_ns();
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------ epilogue (warps 2..5)
@@ -498,20 +514,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       if (COMM && (p.comm.mode == COMM_ALLREDUCE || p.comm.mode == COMM_REDUCE_SCATTER)) {
         // this rank's partial tile is in its symmetric buffer: publish it to the rank that reduces the tile
         // (one word per (tile, rank, epilogue warp), so no CTA-wide barrier and no counting is needed)
-        __threadfence_system();
+        // warp barrier orders the lanes' stores before lane 0's release at system scope (one fence per warp, not 32)
         __syncwarp();
         if (lane == 0) {
-          const int owner = tile_owner(p.comm, tile, tm, p.M);
+          const uint64_t tf0 = trace ? globaltimer_ns() : 0;
+          if (p.comm.debug & 1) __threadfence(); else __threadfence_system();
+          if (trace && warp == 2) trace[5] += globaltimer_ns() - tf0;
+          const int idx = tm * p.tiles_n + tn;
+          const int owner = tile_owner(p.comm, idx, tm, p.tiles_m);
           uint32_t* f = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(p.comm.peer_bufs[owner]) + p.comm.flag_off) +
-                        (static_cast<size_t>(tile) * p.comm.world + p.comm.rank) * 4 + (warp - 2);
-          st_release_sys(f, p.comm.epoch);
+                        (static_cast<size_t>(idx) * p.comm.world + p.comm.rank) * 4 + (warp - 2);
+          if (p.comm.debug & 1) *reinterpret_cast<volatile uint32_t*>(f) = p.comm.epoch; else st_release_sys(f, p.comm.epoch);
         }
       }
     }
+    if (trace && warp == 2 && lane == 0) trace[3] = globaltimer_ns();
   } else if (COMM) {
-    // ------------------------------------------------------------ communication warps (6..9)
+    // ------------------------------------------------------------ communication warps (6 ..)
     const CommParams& c = p.comm;
-    const int cw = threadIdx.x - GEMM_THREADS;  // 0..127
+    const int cw = threadIdx.x - GEMM_THREADS;  // 0 .. COMM_THREADS-1
     const bool fp16 = (p.flags & GEMM_FLAG_FP16) != 0;
     uint8_t* my_base = static_cast<uint8_t*>(c.peer_bufs[c.rank]);
     uint32_t* my_flags = reinterpret_cast<uint32_t*>(my_base + c.flag_off);
@@ -528,20 +549,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       for (int unit = blockIdx.x; unit < chunks * parts; unit += gridDim.x) {
         const int ch = unit / parts, part = unit % parts;
         const int total = BM * vpr;
-        for (int idx = cw; idx < total; idx += 128) {
-          const int r = idx / vpr, v = idx % vpr;
-          const int col = part * cols_per_part + v * 8;
-          const uint4 val = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(ch * BM + r) * c.ld_ag_src + col);
-          const size_t off = c.data_off + (static_cast<size_t>(c.rank * rows_per_rank + ch * BM + r) * p.K + col) * 2;
-          if (mm) {
-            mm_st_16(c.mc_base + off, val);
-          } else {
-            for (int w = 0; w < c.world; ++w) *reinterpret_cast<uint4*>(static_cast<uint8_t*>(c.peer_bufs[w]) + off) = val;
+        for (int base = cw; base < total; base += COMM_THREADS * 4) {
+          uint4 val[4];
+          size_t off[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int idx = base + j * COMM_THREADS;
+            if (idx < total) {
+              const int r = idx / vpr, v = idx % vpr;
+              const int col = part * cols_per_part + v * 8;
+              val[j] = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(ch * BM + r) * c.ld_ag_src + col);
+              off[j] = c.data_off + (static_cast<size_t>(c.rank * rows_per_rank + ch * BM + r) * p.K + col) * 2;
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (base + j * COMM_THREADS < total) {
+              if (mm) {
+                mm_st_16(c.mc_base + off[j], val[j]);
+              } else {
+                for (int w = 0; w < c.world; ++w)
+                  *reinterpret_cast<uint4*>(static_cast<uint8_t*>(c.peer_bufs[w]) + off[j]) = val[j];
+              }
+            }
           }
         }
-        __threadfence_system();
         __syncwarp();
         if ((cw & 31) == 0) {  // one word per (row block, part, communication warp)
+          __threadfence_system();
           const size_t word = (static_cast<size_t>(c.rank * chunks + ch) * parts + part) * COMM_WARPS + (cw >> 5);
           if (mm) {
             multimem_red_release_max(reinterpret_cast<uint32_t*>(c.mc_base + c.flag_off) + word, c.epoch);
@@ -554,39 +589,66 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     } else {
       const int num_tiles_c = p.tiles_m * p.tiles_n;
       const int rows_per_rank = p.M / c.world;
-      int owned = 0;
-      for (int tile = 0; tile < num_tiles_c && ok; ++tile) {
-        int tm, tn;
-        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
-        if (tile_owner(c, tile, tm, p.M) != c.rank) continue;
-        const int mine = owned++;
-        if (mine % static_cast<int>(gridDim.x) != static_cast<int>(blockIdx.x)) continue;
+      // enumerate only the tiles this rank owns (no scan over all tiles: integer division is slow), and give
+      // every CTA each gridDim-th of them, in the order in which they are produced
+      const int per_rank_rows = p.tiles_m / c.world;
+      const int n_owned = c.mode == COMM_REDUCE_SCATTER ? per_rank_rows * p.tiles_n
+                                                        : (num_tiles_c - c.rank + c.world - 1) / c.world;
+      for (int j = blockIdx.x; j < n_owned && ok; j += gridDim.x) {
+        int tm, tn, tile;
+        if (c.mode == COMM_REDUCE_SCATTER) {
+          tm = c.rank * per_rank_rows + j / p.tiles_n;
+          tn = j % p.tiles_n;
+          tile = tm * p.tiles_n + tn;
+        } else {
+          tile = c.rank + c.world * j;
+          tm = tile / p.tiles_n;
+          tn = tile % p.tiles_n;
+        }
+        const uint64_t tw0 = trace ? globaltimer_ns() : 0;
         ok = warp_wait_words(my_flags + static_cast<size_t>(tile) * c.world * 4, c.world * 4, c.epoch, abort_flag, p.err);
         if (!ok) break;
+        const uint64_t tw1 = trace ? globaltimer_ns() : 0;
+        if (trace && cw == 0) trace[6] += tw1 - tw0;
         const int m0 = tm * BM, n0 = tn * BN;
         const int rows = min(BM, p.M - m0), cols = min(BN, p.N - n0);
         const int vpr = cols / 8;
         const int total = rows * vpr;
-        for (int base = cw; base < total; base += 128 * 4) {
-          uint4 v[4];
-          size_t off[4];
+        constexpr int UNR = 8;  // 16-byte requests in flight per thread: NVLink round trips are ~10 us under load
+        for (int base = cw; base < ((c.debug & 2) ? 0 : total); base += COMM_THREADS * UNR) {
+          uint4 v[UNR];
+          size_t off[UNR];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int idx = base + j * 128;
+          for (int j = 0; j < UNR; ++j) {
+            const int idx = base + j * COMM_THREADS;
             if (idx < total) {
               const int r = idx / vpr, q = idx % vpr;
               off[j] = c.data_off + (static_cast<size_t>(m0 + r) * p.N + n0 + q * 8) * 2;
-              if (mm) {
-                v[j] = mm_ld_reduce_16(c.mc_base + off[j], fp16);
-              } else {
+              if (mm) v[j] = mm_ld_reduce_16(c.mc_base + off[j], fp16);
+            }
+          }
+          if (!mm) {
+            // plain peer loads: fetch every rank's copy of a vector before adding them up
+#pragma unroll
+            for (int j = 0; j < UNR; ++j) {
+              const int idx = base + j * COMM_THREADS;
+              if (idx < total) {
+                uint4 part[8];  // the launcher refuses peer mode beyond 8 ranks
+#pragma unroll
+                for (int w = 0; w < 8; ++w)
+                  if (w < c.world)
+                    part[w] = *reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(c.peer_bufs[w]) + off[j]);
                 float acc[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-                for (int w = 0; w < c.world; ++w) {
-                  float t[8];
-                  unpack8(*reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(c.peer_bufs[w]) + off[j]), t, fp16);
 #pragma unroll
-                  for (int e = 0; e < 8; ++e) acc[e] += t[e];
+                for (int w = 0; w < 8; ++w) {
+                  if (w < c.world) {
+                    float t[8];
+                    unpack8(part[w], t, fp16);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[e] += t[e];
+                  }
                 }
                 v[j].x = pack2(acc[0], acc[1], fp16); v[j].y = pack2(acc[2], acc[3], fp16);
                 v[j].z = pack2(acc[4], acc[5], fp16); v[j].w = pack2(acc[6], acc[7], fp16);
@@ -594,8 +656,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             }
           }
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int idx = base + j * 128;
+          for (int j = 0; j < UNR; ++j) {
+            const int idx = base + j * COMM_THREADS;
             if (idx < total) {
               if (c.mode == COMM_ALLREDUCE) {
                 if (mm) {
@@ -613,11 +675,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             }
           }
         }
+        if (trace && cw == 0) trace[7] += globaltimer_ns() - tw1;
         if (c.mode == COMM_ALLREDUCE) {
           // tell every rank that one more tile of the result is final
-          __threadfence_system();
           __syncwarp();
           if ((cw & 31) == 0) {
+            __threadfence_system();
             if (mm) {
               multimem_red_release_add(reinterpret_cast<uint32_t*>(c.mc_base + c.done_off), 1u);
             } else {
@@ -631,6 +694,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         // the result is complete on this rank once every tile of every owner has been broadcast
         wait_flag_ge(reinterpret_cast<const uint32_t*>(my_base + c.done_off), c.done_target, abort_flag, p.err);
       }
+      if (trace && cw == 0) trace[4] = globaltimer_ns();
     }
   }
 

@@ -99,7 +99,7 @@ int oslo_gemm_comm_16bit(const void* A, const void* B, int M, int N, int K, int 
                          void* const* peer_bufs_dev, void* own_buf, void* mc_base, long long data_off,
                          long long flag_off, long long flag_bytes, int rank, int world, unsigned epoch,
                          unsigned done_base, int mode, int use_multimem, void* out, int ld_out, int wide_tiles,
-                         int* err_word, int num_sms, cudaStream_t stream);
+                         unsigned long long* trace, int* err_word, int num_sms, cudaStream_t stream);
 
 // symmetric-memory collectives (comm.cu)
 int oslo_allreduce_symm(void* const* peer_ptrs_dev, void* mc_ptr, uint32_t* const* signal_ptrs_dev, void* out,

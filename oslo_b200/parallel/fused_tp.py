@@ -41,6 +41,10 @@ class FusedTP:
         self.calls = 0
         self.own_base = self.ws.buf.data_ptr()
         self.use_multimem = get_config().use_multimem and self.ws.has_multicast
+        # set to an int64 [>= grid, 8] CUDA tensor to receive per-CTA phase timestamps (ns) of the next calls:
+        # 0 start, 2 last MMA issued, 3 epilogue done, 4 communication done, 5 epilogue fence time,
+        # 6 time the communication warps waited for tiles, 7 time they moved data
+        self.trace: Optional[Tensor] = None
 
     def _next_slot(self) -> Tuple[int, int, int, int]:
         slot = self.calls & 1
@@ -57,7 +61,7 @@ class FusedTP:
         inc = ops.load_ext(required=True).gemm_comm(
             a, b, int(a_mn), int(b_mn), bias, aux_out, out, flags, 1.0, M, N, K, self.ws.peer_ptrs_dev, self.own_base,
             self.ws.mc_ptr if self.use_multimem else 0, data_off, flag_off, _FLAG_BYTES, self.rank, self.world,
-            epoch, self.done_totals[slot] & 0xFFFFFFFF, mode, self.use_multimem)
+            epoch, self.done_totals[slot] & 0xFFFFFFFF, mode, self.use_multimem, self.trace)
         self.done_totals[slot] += int(inc)
         return data_off
 
