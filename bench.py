@@ -144,7 +144,9 @@ def main() -> None:
     cfg = ob.GPTJConfig(vocab_size=vocab, n_positions=n_pos, n_embd=n_embd, n_layer=n_layer, n_head=n_head,
                         rotary_dim=rotary, torch_dtype=torch.bfloat16, use_cache=False)
     seqs_per_rank = args.batch_per_gpu * tp * pp          # sequences one model replica handles per step
-    micro = args.micro_batch or (4 if args.model == "gptj-6b" else seqs_per_rank)
+    # 4 sequences per forward/backward per GPU keeps activations within memory; model-parallel replicas
+    # spread a micro-batch over tp*pp GPUs, so they take proportionally more (fewer, larger launches)
+    micro = args.micro_batch or (4 * tp if args.model == "gptj-6b" else seqs_per_rank)
     micro = min(micro, seqs_per_rank)
     accum = seqs_per_rank // micro
 
