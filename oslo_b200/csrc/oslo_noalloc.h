@@ -1,10 +1,10 @@
 // Column sums without any allocation.
 //
 // This entry point has no counterpart in the reference package. It exists for callers that are not
-// allowed to obtain device memory at the moment of the call: code running while a CUDA stream is being
-// captured, code holding a memory-pool lock, real-time or interrupt-style host threads where cudaMalloc's
-// implicit device synchronisation is unacceptable, and embedders whose memory budget was fixed at start-up
-// and who therefore hand a library nothing but input and output buffers. The ordinary `oslo_colsum`
+// allowed to obtain device memory at the moment of the call: code holding a memory-pool lock, real-time or
+// interrupt-style host threads where cudaMalloc's implicit device synchronisation is unacceptable, and
+// embedders whose memory budget was fixed at start-up and who therefore hand a library nothing but input
+// and output buffers. The ordinary `oslo_colsum`
 // needs a [parts, cols] float workspace from its caller; here that workspace is a fixed array that lives in
 // the library image itself.
 #pragma once

@@ -1,7 +1,7 @@
 """The allocation-free column-sum entry point, called through its exported C symbol.
 
-Some callers cannot ask the driver for memory when they need a result: a stream is being captured, an
-allocator lock is held, or their memory was budgeted once at start-up. ``oslo_colsum_noalloc`` serves them
+Some callers cannot ask the driver for memory when they need a result: an allocator lock is held, the
+thread must not stall on cudaMalloc's synchronisation, or their memory was budgeted once at start-up. ``oslo_colsum_noalloc`` serves them
 from a workspace built into the library. This test compares it with the ordinary ``colsum`` op (which
 allocates its workspace) on two consecutive calls, since the calls share the built-in workspace. The file
 name sorts last so that a failure here never hides another test.
