@@ -307,8 +307,9 @@ void check_attn_operand(const Tensor& t, const char* name) {
                   reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0, name, " needs 16-byte aligned rows");
 }
 
+// impl 0 = mma.sync kernel (attention.cu), 1 = tcgen05/TMEM kernel (attention_sm100.cu)
 std::tuple<Tensor, Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v, double scale, bool causal,
-                                     int64_t window, const optional<Tensor>& kpm) {
+                                     int64_t window, const optional<Tensor>& kpm, int64_t impl) {
   check_attn_operand(q, "q"); check_attn_operand(k, "k"); check_attn_operand(v, "v");
   c10::cuda::CUDAGuard guard(q.device());
   const int B = q.size(0), H = q.size(1), Sq = q.size(2), D = q.size(3), Sk = k.size(2);
@@ -319,6 +320,14 @@ std::tuple<Tensor, Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Ten
   if (kpm.has_value() && kpm->defined()) {
     TORCH_CHECK(kpm->scalar_type() == at::kByte && kpm->is_contiguous() && kpm->size(0) == B && kpm->size(1) == Sk, "bad key padding mask");
     mp = kpm->data_ptr<uint8_t>();
+  }
+  if (impl == 1) {
+    check_rc(oslo_flash_fwd_sm100(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), mp, B, H,
+                                  Sq, Sk, D, q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+                                  v.stride(0), v.stride(1), v.stride(2), o.stride(0), o.stride(1), o.stride(2),
+                                  static_cast<float>(scale), causal ? 1 : 0, static_cast<int>(window), dt_code(q),
+                                  dev_state(q.get_device()).err.data_ptr<int>(), cur_stream()), "flash_fwd_sm100");
+    return {o, lse};
   }
   check_rc(oslo_flash_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), mp, B, H, Sq, Sk,
                           D, q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2), v.stride(0),
@@ -447,7 +456,7 @@ TORCH_LIBRARY(oslo_b200, m) {
   m.def("adam_step(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor(d!)? p_lp, float lr, float beta1, float beta2, float eps, float wd, int step, float grad_scale, Tensor? inv_scale) -> ()", &adam_step);
   m.def("sumsq(Tensor x) -> Tensor", &sumsq);
   m.def("ngram_ban_(Tensor tokens, Tensor(a!) lprobs, int n) -> Tensor(a!)", &ngram_ban_);
-  m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int window, Tensor? kpm) -> (Tensor, Tensor)", &flash_fwd);
+  m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int window, Tensor? kpm, int impl=1) -> (Tensor, Tensor)", &flash_fwd);
   m.def("flash_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale, bool causal, int window, Tensor? kpm) -> (Tensor, Tensor, Tensor)", &flash_bwd);
   m.def("decode_attn(Tensor q, Tensor kc, Tensor vc, Tensor lengths, float scale, int window) -> Tensor", &decode_attn);
   m.def("gemm_comm(Tensor a, Tensor b, int a_mn, int b_mn, Tensor? bias, Tensor(a!)? aux_out, Tensor(b!)? out, int flags, float alpha, int M, int N, int K, int peer_bufs_dev, int own_buf, int mc_base, int data_off, int flag_off, int flag_bytes, int rank, int world, int epoch, int done_base, int mode, bool use_multimem, Tensor(c!)? trace) -> int", &gemm_comm);

@@ -51,6 +51,26 @@ int make_tma_2d_16bit(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_
   return r == CUDA_SUCCESS ? 0 : -(1000 + static_cast<int>(r));
 }
 
+// N-D (rank 3..5) map over 16-bit elements; dim 0 is contiguous, `strides_elems[i]` is the element stride of
+// dim i + 1; the box is `box[]` elements per dim, 128-B swizzle (so box[0] must be 64), zero fill out of range
+int make_tma_nd_16bit(CUtensorMap* map, const void* ptr, int rank, const uint64_t* dims, const uint64_t* strides_elems,
+                      const uint32_t* box, bool fp16) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return -100;
+  if (rank < 2 || rank > 5 || (reinterpret_cast<uintptr_t>(ptr) & 15)) return -101;
+  cuuint64_t d[5], st[4];
+  cuuint32_t bx[5], estr[5];
+  for (int i = 0; i < rank; ++i) { d[i] = dims[i]; bx[i] = box[i]; estr[i] = 1; }
+  for (int i = 0; i + 1 < rank; ++i) {
+    st[i] = strides_elems[i] * 2;
+    if (st[i] % 16) return -101;
+  }
+  CUresult r = enc(map, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank,
+                   const_cast<void*>(ptr), d, st, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -(1000 + static_cast<int>(r));
+}
+
 template <int BN, int STAGES>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, int num_sms, cudaStream_t stream) {
   constexpr size_t smem = STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;

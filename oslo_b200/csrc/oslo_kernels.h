@@ -82,6 +82,12 @@ int oslo_flash_fwd(const void* q, const void* k, const void* v, void* o, float* 
                    long long k_sh, long long k_ss, long long v_sb, long long v_sh, long long v_ss, long long o_sb,
                    long long o_sh, long long o_ss, float scale, int causal, int window, int dtype,
                    cudaStream_t stream);
+// same contract as oslo_flash_fwd, on the tcgen05 tensor cores with TMEM accumulators (attention_sm100.cu)
+int oslo_flash_fwd_sm100(const void* q, const void* k, const void* v, void* o, float* lse, const uint8_t* kpm, int B,
+                         int H, int Sq, int Sk, int D, long long q_sb, long long q_sh, long long q_ss, long long k_sb,
+                         long long k_sh, long long k_ss, long long v_sb, long long v_sh, long long v_ss, long long o_sb,
+                         long long o_sh, long long o_ss, float scale, int causal, int window, int dtype, int* err_word,
+                         cudaStream_t stream);
 int oslo_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
                    float* delta, float* dq_acc, void* dq, void* dk, void* dv, const uint8_t* kpm, int B, int H,
                    int Sq, int Sk, int D, long long q_sb, long long q_sh, long long q_ss, long long k_sb,

@@ -8,6 +8,7 @@ both weight layouts run without a transpose copy.
 from __future__ import annotations
 
 import itertools
+import os
 from typing import Optional
 
 import torch
@@ -213,6 +214,11 @@ def flash_supported(q: Tensor, k: Tensor, v: Tensor) -> bool:
     return q.dtype == k.dtype == v.dtype
 
 
+def _flash_impl() -> int:
+    """1 = tcgen05/TMEM forward kernel (default), 0 = the mma.sync kernel (``OSLO_B200_ATTN=mma``)."""
+    return 0 if os.environ.get("OSLO_B200_ATTN", "tcgen05") == "mma" else 1
+
+
 def _attn_operand(t: Tensor) -> Tensor:
     if t.stride(-1) != 1 or any(s % 8 for s in t.stride()[:-1]) or t.data_ptr() % 16:
         t = t.contiguous()
@@ -223,7 +229,7 @@ class _Flash(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, causal, window, scale, kpm):
         q, k, v = _attn_operand(q), _attn_operand(k), _attn_operand(v)
-        o, lse = _ext().flash_fwd(q, k, v, scale, causal, window, kpm)
+        o, lse = _ext().flash_fwd(q, k, v, scale, causal, window, kpm, _flash_impl())
         ctx.save_for_backward(q, k, v, o, lse, kpm)
         ctx.cfg = (scale, causal, window)
         return o

@@ -245,6 +245,37 @@ def test_flash_attention(D, Sq, Sk, window, use_kpm):
     _close(v.grad, vf.grad, atol=3e-2, rtol=5e-2)
 
 
+@pytest.mark.parametrize("D", [64, 128, 256])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("Sq,Sk,causal,window,use_kpm", [
+    (640, 640, True, None, False), (300, 300, False, None, False), (128, 517, True, None, True),
+    (1, 130, True, None, False), (513, 513, True, 100, False), (384, 384, False, None, True)])
+def test_flash_forward_tcgen05(D, dtype, Sq, Sk, causal, window, use_kpm):
+    """tcgen05/TMEM forward kernel against the fp32 statement (output and log-sum-exp), many key blocks,
+    ragged tails, prefix offset (Sk > Sq), window, padding, and a second call on the same inputs."""
+    ops, _ = _ops()
+    ext = ops.load_ext(required=True)
+    torch.manual_seed(11)
+    B, H = 2, 3
+    mk = lambda s: (torch.randn(B, s, H, D, device="cuda") * 0.8).to(dtype).permute(0, 2, 1, 3)
+    q, k, v = mk(Sq), mk(Sk), mk(Sk)
+    kpm = kpm8 = None
+    if use_kpm:
+        kpm = torch.ones(B, Sk, device="cuda", dtype=torch.long)
+        kpm[0, :9] = 0
+        kpm[1, 100:140] = 0
+        kpm8 = kpm.to(torch.uint8)
+    scale = 1.0 / math.sqrt(D)
+    o, lse = ext.flash_fwd(q, k, v, scale, causal, int(window or 0), kpm8, 1)
+    o2, lse2 = ext.flash_fwd(q, k, v, scale, causal, int(window or 0), kpm8, 1)
+    want = ops.reference.attention(q.float(), k.float(), v.float(), causal, window, scale, kpm)
+    assert int(ext.error_word(q).item()) == 0
+    _close(o, want, atol=2e-2)
+    assert torch.equal(o, o2) and torch.equal(lse, lse2)
+    o_old, lse_old = ext.flash_fwd(q, k, v, scale, causal, int(window or 0), kpm8, 0)
+    _close(lse, lse_old, atol=2e-3, rtol=1e-3)
+
+
 @pytest.mark.parametrize("D,window", [(256, None), (128, 37), (64, None)])
 def test_decode_attention(D, window):
     ops, _ = _ops()
