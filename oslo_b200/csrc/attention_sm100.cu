@@ -17,6 +17,7 @@
 #include <math_constants.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "oslo_kernels.h"
 #include "ptx.cuh"
@@ -81,7 +82,9 @@ __device__ __forceinline__ uint32_t fa_pack2(float a, float b, bool fp16) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <int D, int BN>
+// PT = true: P goes back into TMEM (over the S buffer it came from, two bf16 per 32-bit column) and is the
+// A operand of P V straight from tensor memory; PT = false: P goes through a swizzled shared-memory tile.
+template <int D, int BN, bool PT>
 __global__ void __launch_bounds__(FA_THREADS, 1)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
               const __grid_constant__ CUtensorMap tv, const FaParams p) {
@@ -90,7 +93,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CU
   constexpr uint32_t KV_SUB = BN * 128;          // bytes of one [BN x 64] sub-tile (K and V)
   constexpr uint32_t Q_BYTES = DC * Q_SUB;
   constexpr uint32_t KV_BYTES = DC * KV_SUB;
-  constexpr uint32_t P_BYTES = (BN / 64) * Q_SUB;
+  constexpr uint32_t P_BYTES = PT ? 0u : (BN / 64) * Q_SUB;
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t O_COL = 2 * BN;             // S buffers at columns [0, BN) and [BN, 2 BN)
   static_assert(O_COL + D <= TMEM_COLS, "TMEM budget");
@@ -103,9 +106,10 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CU
   const uint32_t p_s = v_s + 2 * KV_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Q_BYTES + 4 * KV_BYTES + P_BYTES);
   const uint32_t bar0 = smem_u32(bars);
-  // 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full | 11,12 s_empty | 13 p_ready | 14 pv_done
+  // 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full | 11,12 s_empty | 13 p_ready[0] |
+  // 14 pv_done | 15 p_ready[1] (PT only: one per S/P buffer)
   auto bar = [&](int i) { return bar0 + 8u * i; };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -118,8 +122,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CU
   const int nblk = key_hi > key_lo ? (key_hi - key_lo + BN - 1) / BN : 0;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 15; ++i) {
-      const bool four = (i == 11 || i == 12 || i == 13);  // arrivals from the 4 softmax warps
+    for (int i = 0; i < 16; ++i) {
+      const bool four = (i == 11 || i == 12 || i == 13 || i == 15);  // arrivals from the 4 softmax warps
       mbar_init(bar(i), four ? 4 : 1);
     }
     *abort_flag = 0;
@@ -190,14 +194,19 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CU
         const int st = j & 1;
         ok = mbar_wait(bar(5 + st), (j >> 1) & 1, abort_flag, p.err, ERR_WAIT_FULL);
         if (!ok) break;
-        ok = mbar_wait(bar(13), j & 1, abort_flag, p.err, ERR_WAIT_FULL);
+        if (PT) ok = mbar_wait(bar(st ? 15 : 13), (j >> 1) & 1, abort_flag, p.err, ERR_WAIT_FULL);
+        else ok = mbar_wait(bar(13), j & 1, abort_flag, p.err, ERR_WAIT_FULL);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks) {
-          const uint64_t da = make_smem_desc(p_s + (ks >> 2) * Q_SUB + (ks & 3) * 32, 16, 1024);
           const uint64_t db = make_smem_desc(v_s + st * KV_BYTES + ks * 2048, KV_SUB, 1024);
-          umma_f16(tmem_base + O_COL, da, db, idesc_pv, (j | ks) != 0);
+          if (PT) {
+            umma_f16_ts(tmem_base + O_COL, tmem_base + st * BN + ks * 8, db, idesc_pv, (j | ks) != 0);
+          } else {
+            const uint64_t da = make_smem_desc(p_s + (ks >> 2) * Q_SUB + (ks & 3) * 32, 16, 1024);
+            umma_f16(tmem_base + O_COL, da, db, idesc_pv, (j | ks) != 0);
+          }
         }
         umma_commit(bar(7 + st));   // V stage free
         umma_commit(bar(14));       // O updated, P buffer reusable
@@ -269,8 +278,10 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CU
         psum += s[i];
       }
       l_sum += psum;
-      if (j > 0) {
-        ok = mbar_wait(bar(14), (j - 1) & 1, abort_flag, p.err, ERR_WAIT_TMEM_FULL);  // P V of block j-1 finished
+      // the shared P tile is single-buffered, so P V of block j-1 must have finished before it is rewritten; the
+      // TMEM P buffers alternate, so there only a rescale of O has to wait for it
+      if (j > 0 && (!PT || rescale)) {
+        ok = mbar_wait(bar(14), (j - 1) & 1, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
         if (!ok) break;
         tc_fence_after();
         if (rescale) {
@@ -285,6 +296,20 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CU
           }
           tmem_wait_st();
         }
+      }
+      if (PT) {
+#pragma unroll
+        for (int c0 = 0; c0 < BN / 2; c0 += 32) {
+          uint32_t r[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = fa_pack2(s[2 * (c0 + i)], s[2 * (c0 + i) + 1], fp16);
+          tmem_st_32x32(t_lane + st * BN + c0, r);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(st ? 15 : 13));
+        continue;
       }
       // ---- P (bf16) into shared memory: K-major, 128-byte swizzle: 16-byte chunk c of row r sits at c ^ (r & 7)
 #pragma unroll
@@ -373,19 +398,19 @@ static int make_qkv_map(CUtensorMap* map, const void* ptr, int B, int H, int S, 
   return make_tma_nd_16bit(map, ptr, 4, dims, strides, box, fp16);
 }
 
-template <int D, int BN>
+template <int D, int BN, bool PT>
 static int fa_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p,
                      cudaStream_t stream) {
-  constexpr size_t smem = FA_BM * D * 2 + 4 * BN * D * 2 + FA_BM * BN * 2 + 15 * 8 + 16 + 1024;
+  constexpr size_t smem = FA_BM * D * 2 + 4 * BN * D * 2 + (PT ? 0 : FA_BM * BN * 2) + 16 * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<D, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(fa_fwd_kernel<D, BN, PT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
   dim3 grid((p.Sq + FA_BM - 1) / FA_BM, p.H, p.B);
-  fa_fwd_kernel<D, BN><<<grid, FA_THREADS, smem, stream>>>(tq, tk, tv, p);
+  fa_fwd_kernel<D, BN, PT><<<grid, FA_THREADS, smem, stream>>>(tq, tk, tv, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -418,7 +443,13 @@ extern "C" int oslo_flash_fwd_sm100(const void* q, const void* k, const void* v,
   if (rc) return rc - 1000;
   rc = make_qkv_map(&tv, v, B, H, Sk, D, v_sb, v_sh, v_ss, bn, fp16, p.v_pos);
   if (rc) return rc - 2000;
-  if (D == 64) return fa_launch<64, 128>(tq, tk, tv, p, stream);
-  if (D == 128) return fa_launch<128, 128>(tq, tk, tv, p, stream);
-  return fa_launch<256, 64>(tq, tk, tv, p, stream);
+  static const bool p_smem = [] { const char* e = getenv("OSLO_B200_ATTN_P_SMEM"); return e && e[0] == '1'; }();
+  if (p_smem) {
+    if (D == 64) return fa_launch<64, 128, false>(tq, tk, tv, p, stream);
+    if (D == 128) return fa_launch<128, 128, false>(tq, tk, tv, p, stream);
+    return fa_launch<256, 64, false>(tq, tk, tv, p, stream);
+  }
+  if (D == 64) return fa_launch<64, 128, true>(tq, tk, tv, p, stream);
+  if (D == 128) return fa_launch<128, 128, true>(tq, tk, tv, p, stream);
+  return fa_launch<256, 64, true>(tq, tk, tv, p, stream);
 }
