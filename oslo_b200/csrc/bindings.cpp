@@ -338,7 +338,7 @@ std::tuple<Tensor, Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Ten
 
 std::tuple<Tensor, Tensor, Tensor> flash_bwd(const Tensor& dout, const Tensor& q, const Tensor& k, const Tensor& v,
                                              const Tensor& o, const Tensor& lse, double scale, bool causal,
-                                             int64_t window, const optional<Tensor>& kpm) {
+                                             int64_t window, const optional<Tensor>& kpm, int64_t impl) {
   check_attn_operand(q, "q"); check_attn_operand(k, "k"); check_attn_operand(v, "v");
   check_attn_operand(o, "o"); check_attn_operand(dout, "dout");
   c10::cuda::CUDAGuard guard(q.device());
@@ -348,6 +348,16 @@ std::tuple<Tensor, Tensor, Tensor> flash_bwd(const Tensor& dout, const Tensor& q
   Tensor dv = at::empty_strided(v.sizes(), v.strides(), v.options());
   Tensor delta = at::empty({B, H, Sq}, q.options().dtype(at::kFloat));
   const uint8_t* mp = (kpm.has_value() && kpm->defined()) ? kpm->data_ptr<uint8_t>() : nullptr;
+  if (impl == 1) {
+    check_rc(oslo_flash_bwd_sm100(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), dout.data_ptr(),
+                                  lse.data_ptr<float>(), delta.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(),
+                                  dv.data_ptr(), mp, B, H, Sq, Sk, D, q.stride(0), q.stride(1), q.stride(2), k.stride(0),
+                                  k.stride(1), k.stride(2), v.stride(0), v.stride(1), v.stride(2), o.stride(0),
+                                  o.stride(1), o.stride(2), dout.stride(0), dout.stride(1), dout.stride(2),
+                                  static_cast<float>(scale), causal ? 1 : 0, static_cast<int>(window), dt_code(q),
+                                  dev_state(q.get_device()).err.data_ptr<int>(), cur_stream(4)), "flash_bwd_sm100");
+    return {dq, dk, dv};
+  }
   check_rc(oslo_flash_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), dout.data_ptr(), lse.data_ptr<float>(),
                           delta.data_ptr<float>(), nullptr, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), mp, B, H, Sq, Sk,
                           D, q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2), v.stride(0),
@@ -457,7 +467,7 @@ TORCH_LIBRARY(oslo_b200, m) {
   m.def("sumsq(Tensor x) -> Tensor", &sumsq);
   m.def("ngram_ban_(Tensor tokens, Tensor(a!) lprobs, int n) -> Tensor(a!)", &ngram_ban_);
   m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int window, Tensor? kpm, int impl=1) -> (Tensor, Tensor)", &flash_fwd);
-  m.def("flash_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale, bool causal, int window, Tensor? kpm) -> (Tensor, Tensor, Tensor)", &flash_bwd);
+  m.def("flash_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale, bool causal, int window, Tensor? kpm, int impl=1) -> (Tensor, Tensor, Tensor)", &flash_bwd);
   m.def("decode_attn(Tensor q, Tensor kc, Tensor vc, Tensor lengths, float scale, int window) -> Tensor", &decode_attn);
   m.def("gemm_comm(Tensor a, Tensor b, int a_mn, int b_mn, Tensor? bias, Tensor(a!)? aux_out, Tensor(b!)? out, int flags, float alpha, int M, int N, int K, int peer_bufs_dev, int own_buf, int mc_base, int data_off, int flag_off, int flag_bytes, int rank, int world, int epoch, int done_base, int mode, bool use_multimem, Tensor(c!)? trace) -> int", &gemm_comm);
   m.def("allreduce_symm(int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(a!) out, int numel, int rank, int world, bool use_multimem) -> ()", &allreduce_symm);

@@ -94,6 +94,13 @@ int oslo_flash_bwd(const void* q, const void* k, const void* v, const void* o, c
                    long long k_sh, long long k_ss, long long v_sb, long long v_sh, long long v_ss, long long o_sb,
                    long long o_sh, long long o_ss, long long do_sb, long long do_sh, long long do_ss, float scale,
                    int causal, int window, int dtype, cudaStream_t stream);
+// same contract on the tcgen05 tensor cores (attention_bwd_sm100.cu); dq / dk / dv use the strides of q / k / v
+int oslo_flash_bwd_sm100(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                         float* delta, void* dq, void* dk, void* dv, const uint8_t* kpm, int B, int H, int Sq, int Sk,
+                         int D, long long q_sb, long long q_sh, long long q_ss, long long k_sb, long long k_sh,
+                         long long k_ss, long long v_sb, long long v_sh, long long v_ss, long long o_sb, long long o_sh,
+                         long long o_ss, long long do_sb, long long do_sh, long long do_ss, float scale, int causal,
+                         int window, int dtype, int* err_word, cudaStream_t stream);
 // single-query attention over a static cache [B, H, T, D]; lengths int32 [B]
 int oslo_decode_attn(const void* q, const void* kc, const void* vc, void* o, const int* lengths, float* ws, int B,
                      int H, int T, int D, int splits, float scale, int window, int dtype, cudaStream_t stream);

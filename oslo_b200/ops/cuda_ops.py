@@ -238,7 +238,7 @@ class _Flash(torch.autograd.Function):
     def backward(ctx, do):
         q, k, v, o, lse, kpm = ctx.saved_tensors
         scale, causal, window = ctx.cfg
-        dq, dk, dv = _ext().flash_bwd(_attn_operand(do), q, k, v, o, lse, scale, causal, window, kpm)
+        dq, dk, dv = _ext().flash_bwd(_attn_operand(do), q, k, v, o, lse, scale, causal, window, kpm, _flash_impl())
         return dq, dk, dv, None, None, None, None
 
 
