@@ -188,6 +188,121 @@ __device__ __forceinline__ int tile_owner(const CommParams& c, int idx, int tm, 
   return idx % c.world;
 }
 
+// Epilogue of one [1 row x 32 columns] accumulator chunk held by a thread: alpha, bias, GeLU (+ saved
+// pre-activation), dGeLU, residual, accumulate, conversion and the store. `row` < M and `col0` < N are the
+// caller's responsibility.
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int row, int col0, const uint32_t (&r)[32],
+                                               bool fp16, bool out_f32) {
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+    const int ncols = min(32, p.N - col0);
+    const bool vec = (ncols == 32);
+    if (p.flags & GEMM_FLAG_BIAS) {
+      if (vec) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          float b[8];
+          unpack8(*reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias) + col0 + i), b, fp16);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i + j] += b[j];
+        }
+      } else {
+        _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) v[i] += ld_half_as_float(p.bias, col0 + i, fp16);
+      }
+    }
+    if (p.flags & GEMM_FLAG_SAVE_PREACT) {
+      uint16_t* z = reinterpret_cast<uint16_t*>(p.aux_out) + static_cast<size_t>(row) * p.ld_aux_out + col0;
+      if (vec) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          uint4 o;
+          o.x = pack2(v[i], v[i + 1], fp16); o.y = pack2(v[i + 2], v[i + 3], fp16);
+          o.z = pack2(v[i + 4], v[i + 5], fp16); o.w = pack2(v[i + 6], v[i + 7], fp16);
+          *reinterpret_cast<uint4*>(z + i) = o;
+        }
+      } else {
+        _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) z[i] = static_cast<uint16_t>(pack2(v[i], 0.f, fp16) & 0xffff);
+      }
+    }
+    if (p.flags & GEMM_FLAG_GELU) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = gelu_tanh_f(v[i]);
+    }
+    if (p.flags & GEMM_FLAG_DGELU) {
+      const uint16_t* z = reinterpret_cast<const uint16_t*>(p.aux) + static_cast<size_t>(row) * p.ld_aux + col0;
+      if (vec) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          float zz[8];
+          unpack8(*reinterpret_cast<const uint4*>(z + i), zz, fp16);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i + j] *= dgelu_tanh_f(zz[j]);
+        }
+      } else {
+        _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) v[i] *= dgelu_tanh_f(ld_half_as_float(z, i, fp16));
+      }
+    }
+    if (p.flags & GEMM_FLAG_RESIDUAL) {
+      if (out_f32) {
+        const float* rr = reinterpret_cast<const float*>(p.aux) + static_cast<size_t>(row) * p.ld_aux + col0;
+        _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) v[i] += rr[i];
+      } else {
+        const uint16_t* rr = reinterpret_cast<const uint16_t*>(p.aux) + static_cast<size_t>(row) * p.ld_aux + col0;
+        if (vec) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            float x[8];
+            unpack8(*reinterpret_cast<const uint4*>(rr + i), x, fp16);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[i + j] += x[j];
+          }
+        } else {
+          _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) v[i] += ld_half_as_float(rr, i, fp16);
+        }
+      }
+    }
+    if (out_f32) {
+      float* d = reinterpret_cast<float*>(p.D) + static_cast<size_t>(row) * p.ldd + col0;
+      if (vec) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+          if (p.flags & GEMM_FLAG_ACCUMULATE) {
+            const float4 old = *reinterpret_cast<const float4*>(d + i);
+            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+          }
+          *reinterpret_cast<float4*>(d + i) = o;
+        }
+      } else {
+        _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) d[i] = v[i] + ((p.flags & GEMM_FLAG_ACCUMULATE) ? d[i] : 0.f);
+      }
+    } else {
+      uint16_t* d = reinterpret_cast<uint16_t*>(p.D) + static_cast<size_t>(row) * p.ldd + col0;
+      if (vec) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          if (p.flags & GEMM_FLAG_ACCUMULATE) {
+            float x[8];
+            unpack8(*reinterpret_cast<const uint4*>(d + i), x, fp16);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[i + j] += x[j];
+          }
+          uint4 o;
+          o.x = pack2(v[i], v[i + 1], fp16); o.y = pack2(v[i + 2], v[i + 3], fp16);
+          o.z = pack2(v[i + 4], v[i + 5], fp16); o.w = pack2(v[i + 6], v[i + 7], fp16);
+          *reinterpret_cast<uint4*>(d + i) = o;
+        }
+      } else {
+        _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) {
+          float x = v[i];
+          if (p.flags & GEMM_FLAG_ACCUMULATE) x += ld_half_as_float(d, i, fp16);
+          d[i] = static_cast<uint16_t>(pack2(x, 0.f, fp16) & 0xffff);
+        }
+      }
+    }
+}
+
 template <int BN, int STAGES, bool COMM>
 __global__ void __launch_bounds__(COMM ? GEMM_THREADS_COMM : GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -399,114 +514,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         tmem_wait_ld();
         const int col0 = tn * BN + c0;
         if (!row_ok || col0 >= p.N) continue;
-        float v[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-        const int ncols = min(32, p.N - col0);
-        const bool vec = (ncols == 32);
-        if (p.flags & GEMM_FLAG_BIAS) {
-          if (vec) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              float b[8];
-              unpack8(*reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias) + col0 + i), b, fp16);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[i + j] += b[j];
-            }
-          } else {
-            _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) v[i] += ld_half_as_float(p.bias, col0 + i, fp16);
-          }
-        }
-        if (p.flags & GEMM_FLAG_SAVE_PREACT) {
-          uint16_t* z = reinterpret_cast<uint16_t*>(p.aux_out) + static_cast<size_t>(row) * p.ld_aux_out + col0;
-          if (vec) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 o;
-              o.x = pack2(v[i], v[i + 1], fp16); o.y = pack2(v[i + 2], v[i + 3], fp16);
-              o.z = pack2(v[i + 4], v[i + 5], fp16); o.w = pack2(v[i + 6], v[i + 7], fp16);
-              *reinterpret_cast<uint4*>(z + i) = o;
-            }
-          } else {
-            _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) z[i] = static_cast<uint16_t>(pack2(v[i], 0.f, fp16) & 0xffff);
-          }
-        }
-        if (p.flags & GEMM_FLAG_GELU) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = gelu_tanh_f(v[i]);
-        }
-        if (p.flags & GEMM_FLAG_DGELU) {
-          const uint16_t* z = reinterpret_cast<const uint16_t*>(p.aux) + static_cast<size_t>(row) * p.ld_aux + col0;
-          if (vec) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              float zz[8];
-              unpack8(*reinterpret_cast<const uint4*>(z + i), zz, fp16);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[i + j] *= dgelu_tanh_f(zz[j]);
-            }
-          } else {
-            _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) v[i] *= dgelu_tanh_f(ld_half_as_float(z, i, fp16));
-          }
-        }
-        if (p.flags & GEMM_FLAG_RESIDUAL) {
-          if (out_f32) {
-            const float* rr = reinterpret_cast<const float*>(p.aux) + static_cast<size_t>(row) * p.ld_aux + col0;
-            _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) v[i] += rr[i];
-          } else {
-            const uint16_t* rr = reinterpret_cast<const uint16_t*>(p.aux) + static_cast<size_t>(row) * p.ld_aux + col0;
-            if (vec) {
-#pragma unroll
-              for (int i = 0; i < 32; i += 8) {
-                float x[8];
-                unpack8(*reinterpret_cast<const uint4*>(rr + i), x, fp16);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[i + j] += x[j];
-              }
-            } else {
-              _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) v[i] += ld_half_as_float(rr, i, fp16);
-            }
-          }
-        }
-        if (out_f32) {
-          float* d = reinterpret_cast<float*>(p.D) + static_cast<size_t>(row) * p.ldd + col0;
-          if (vec) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-              if (p.flags & GEMM_FLAG_ACCUMULATE) {
-                const float4 old = *reinterpret_cast<const float4*>(d + i);
-                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-              }
-              *reinterpret_cast<float4*>(d + i) = o;
-            }
-          } else {
-            _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) d[i] = v[i] + ((p.flags & GEMM_FLAG_ACCUMULATE) ? d[i] : 0.f);
-          }
-        } else {
-          uint16_t* d = reinterpret_cast<uint16_t*>(p.D) + static_cast<size_t>(row) * p.ldd + col0;
-          if (vec) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              if (p.flags & GEMM_FLAG_ACCUMULATE) {
-                float x[8];
-                unpack8(*reinterpret_cast<const uint4*>(d + i), x, fp16);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[i + j] += x[j];
-              }
-              uint4 o;
-              o.x = pack2(v[i], v[i + 1], fp16); o.y = pack2(v[i + 2], v[i + 3], fp16);
-              o.z = pack2(v[i + 4], v[i + 5], fp16); o.w = pack2(v[i + 6], v[i + 7], fp16);
-              *reinterpret_cast<uint4*>(d + i) = o;
-            }
-          } else {
-            _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) {
-              float x = v[i];
-              if (p.flags & GEMM_FLAG_ACCUMULATE) x += ld_half_as_float(d, i, fp16);
-              d[i] = static_cast<uint16_t>(pack2(x, 0.f, fp16) & 0xffff);
-            }
-          }
-        }
+        epilogue_chunk(p, row, col0, r, fp16, out_f32);
       }
       tc_fence_before();
       __syncwarp();

@@ -13,7 +13,10 @@
 // epilogue of tile i overlap the main loop of tile i+1. All waits are bounded (ptx.cuh).
 #include <mutex>
 
+#include <cstdlib>
+
 #include "gemm_core.cuh"
+#include "gemm_pair_core.cuh"
 
 namespace oslo {
 
@@ -89,6 +92,43 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, i
   return static_cast<int>(cudaGetLastError());
 }
 
+// 256 x 256 tiles on CTA pairs (gemm_pair_core.cuh); the grid is a whole number of pairs
+template <int STAGES>
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, int num_sms, cudaStream_t stream) {
+  constexpr size_t smem = STAGES * (2 * BM * BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
+  static_assert(smem <= 232448, "shared memory budget of one CTA");
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_tcgen05_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  p.tiles_m = (p.M + PAIR_TILE - 1) / PAIR_TILE;
+  p.tiles_n = (p.N + PAIR_TILE - 1) / PAIR_TILE;
+  const int tiles = p.tiles_m * p.tiles_n;
+  // persistent kernel: no more pairs than can be resident at once (pairs are placed as clusters of two SMs)
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(num_sms / 2 * 2));
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_tcgen05_kernel<STAGES>, &cfg) != cudaSuccess || n <= 0) n = num_sms / 2;
+    max_pairs = std::min(n, num_sms / 2);
+  }
+  const int pairs = std::min(tiles, max_pairs);
+  gemm_pair_tcgen05_kernel<STAGES><<<2 * pairs, GEMM_THREADS, smem, stream>>>(ta, tb, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// 0 = single-CTA tiles only (OSLO_B200_GEMM_PAIR=0), 1 = CTA pairs for large outputs (default)
+static bool pair_enabled() {
+  static const bool on = [] { const char* e = getenv("OSLO_B200_GEMM_PAIR"); return !(e && e[0] == '0'); }();
+  return on;
+}
+
 }  // namespace oslo
 
 extern "C" int oslo_gemm_16bit(const void* A, const void* B, void* D, int M, int N, int K, int lda, int ldb, int ldd,
@@ -104,7 +144,10 @@ extern "C" int oslo_gemm_16bit(const void* A, const void* B, void* D, int M, int
   const bool fp16 = (flags & GEMM_FLAG_FP16) != 0;
   // narrow outputs use the 128-wide tile so that more CTAs share the work
   const bool wide = (N >= 256) && (static_cast<long long>((M + BM - 1) / BM) * ((N + 255) / 256) >= num_sms / 2);
-  const int bn = wide ? 256 : 128;
+  // large outputs: 256 x 256 tiles on CTA pairs, when they fill the pairs at least as well as single tiles fill the SMs
+  const long long pair_tiles = static_cast<long long>((M + PAIR_TILE - 1) / PAIR_TILE) * ((N + PAIR_TILE - 1) / PAIR_TILE);
+  const bool pair = pair_enabled() && wide && M >= PAIR_TILE && pair_tiles >= num_sms / 2;
+  const int bn = pair ? BM : (wide ? 256 : 128);   // B box rows: a pair's CTA stages 128 of the 256 tile columns
   CUtensorMap ta, tb;
   int rc;
   if (!a_mn_major) rc = make_tma_2d_16bit(&ta, A, K, M, lda, BM, fp16);
@@ -118,6 +161,7 @@ extern "C" int oslo_gemm_16bit(const void* A, const void* B, void* D, int M, int
   p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ld_aux = ld_aux; p.ld_aux_out = ld_aux_out;
   p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major; p.flags = flags; p.alpha = alpha; p.err = err_word;
   p.comm = CommParams{};
+  if (pair) return launch_pair<6>(ta, tb, p, num_sms, stream);
   if (bn == 256) return launch<256, 4>(ta, tb, p, num_sms, stream);
   return launch<128, 6>(ta, tb, p, num_sms, stream);
 }
