@@ -466,33 +466,87 @@ __global__ void __launch_bounds__(CE_THREADS) ce_grad_kernel(T* __restrict__ log
 }
 
 // ---------------------------------------------------------------------- AdamW / norms
+__device__ __forceinline__ void adam_update(float& p, float& m, float& v, float g, float lr, float beta1, float beta2,
+                                            float eps, float decay, float inv_bc1, float inv_bc2) {
+  m = beta1 * m + (1.f - beta1) * g;
+  v = beta2 * v + (1.f - beta2) * g * g;
+  p = p * decay - lr * (m * inv_bc1) / (sqrtf(v * inv_bc2) + eps);
+}
+// Four elements per thread and iteration through 16-byte accesses (p, m, v) and 8-byte accesses (16-bit g and
+// p_lp); the launcher only takes this path when every pointer is 16-byte aligned. Elements past the last
+// multiple of 4 are handled by the first threads one by one.
 template <typename G, typename LP>
-__global__ void adam_kernel(float* __restrict__ p, const G* __restrict__ g, float* __restrict__ m,
-                            float* __restrict__ v, LP* __restrict__ p_lp, long long n, float lr, float beta1,
-                            float beta2, float eps, float wd, float bc1, float bc2, float grad_scale,
-                            const float* __restrict__ inv_scale_dev) {
+__global__ void __launch_bounds__(256) adam_kernel(float* __restrict__ p, const G* __restrict__ g, float* __restrict__ m,
+                                                   float* __restrict__ v, LP* __restrict__ p_lp, long long n, float lr,
+                                                   float beta1, float beta2, float eps, float wd, float bc1, float bc2,
+                                                   float grad_scale, const float* __restrict__ inv_scale_dev, int vec) {
   const float gs = grad_scale * (inv_scale_dev ? *inv_scale_dev : 1.f);
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const float gi = Cvt<G>::to(g[i]) * gs;
-    const float mi = beta1 * m[i] + (1.f - beta1) * gi;
-    const float vi = beta2 * v[i] + (1.f - beta2) * gi * gi;
-    float pi = p[i] * (1.f - lr * wd);
-    pi -= lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
-    m[i] = mi; v[i] = vi; p[i] = pi;
+  const float decay = 1.f - lr * wd, inv_bc1 = 1.f / bc1, inv_bc2 = 1.f / bc2;
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long n4 = vec ? n / 4 : 0;
+  for (long long i = tid; i < n4; i += nthreads) {
+    float4 pp = reinterpret_cast<const float4*>(p)[i];
+    float4 mm = reinterpret_cast<const float4*>(m)[i];
+    float4 vv = reinterpret_cast<const float4*>(v)[i];
+    float gg[4];
+    if constexpr (sizeof(G) == 4) {
+      const float4 t = reinterpret_cast<const float4*>(g)[i];
+      gg[0] = t.x; gg[1] = t.y; gg[2] = t.z; gg[3] = t.w;
+    } else {
+      const uint2 t = reinterpret_cast<const uint2*>(g)[i];
+      const G* h = reinterpret_cast<const G*>(&t);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) gg[k] = Cvt<G>::to(h[k]);
+    }
+    adam_update(pp.x, mm.x, vv.x, gg[0] * gs, lr, beta1, beta2, eps, decay, inv_bc1, inv_bc2);
+    adam_update(pp.y, mm.y, vv.y, gg[1] * gs, lr, beta1, beta2, eps, decay, inv_bc1, inv_bc2);
+    adam_update(pp.z, mm.z, vv.z, gg[2] * gs, lr, beta1, beta2, eps, decay, inv_bc1, inv_bc2);
+    adam_update(pp.w, mm.w, vv.w, gg[3] * gs, lr, beta1, beta2, eps, decay, inv_bc1, inv_bc2);
+    reinterpret_cast<float4*>(p)[i] = pp;
+    reinterpret_cast<float4*>(m)[i] = mm;
+    reinterpret_cast<float4*>(v)[i] = vv;
+    if (p_lp) {
+      LP o[4] = {Cvt<LP>::from(pp.x), Cvt<LP>::from(pp.y), Cvt<LP>::from(pp.z), Cvt<LP>::from(pp.w)};
+      reinterpret_cast<uint2*>(p_lp)[i] = *reinterpret_cast<const uint2*>(o);
+    }
+  }
+  for (long long i = n4 * 4 + tid; i < n; i += nthreads) {
+    float pi = p[i], mi = m[i], vi = v[i];
+    adam_update(pi, mi, vi, Cvt<G>::to(g[i]) * gs, lr, beta1, beta2, eps, decay, inv_bc1, inv_bc2);
+    p[i] = pi; m[i] = mi; v[i] = vi;
     if (p_lp) p_lp[i] = Cvt<LP>::from(pi);
   }
 }
+// sum of squares: 16-byte loads when `vec` (pointer 16-byte aligned), one atomic per block
 template <typename T>
-__global__ void sumsq_kernel(const T* __restrict__ x, float* __restrict__ out, long long n) {
+__global__ void __launch_bounds__(256) sumsq_kernel(const T* __restrict__ x, float* __restrict__ out, long long n, int vec) {
   __shared__ float sh[8];
-  float s = 0.f;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const float f = Cvt<T>::to(x[i]);
-    s += f * f;
+  constexpr int PER = 16 / sizeof(T);
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long nv = vec ? n / PER : 0;
+  float s0 = 0.f, s1 = 0.f;
+  for (long long i = tid; i < nv; i += 2 * nthreads) {
+    const uint4 a = reinterpret_cast<const uint4*>(x)[i];
+    const bool two = i + nthreads < nv;
+    uint4 b = make_uint4(0, 0, 0, 0);
+    if (two) b = reinterpret_cast<const uint4*>(x)[i + nthreads];
+    const T* ha = reinterpret_cast<const T*>(&a);
+    const T* hb = reinterpret_cast<const T*>(&b);
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      const float fa = Cvt<T>::to(ha[k]);
+      s0 += fa * fa;
+      const float fb = two ? Cvt<T>::to(hb[k]) : 0.f;
+      s1 += fb * fb;
+    }
   }
-  s = block_sum<256>(s, sh);
+  for (long long i = nv * PER + tid; i < n; i += nthreads) {
+    const float f = Cvt<T>::to(x[i]);
+    s0 += f * f;
+  }
+  const float s = block_sum<256>(s0 + s1, sh);
   if (threadIdx.x == 0) atomicAdd(out, s);
 }
 
@@ -667,9 +721,11 @@ extern "C" int oslo_adam(float* p, const void* g, float* m, float* v, void* p_lp
                          float beta2, float eps, float wd, float bc1, float bc2, float grad_scale,
                          const float* inv_scale_dev, int g_dtype, int lp_dtype, cudaStream_t st) {
   if (n == 0) return 0;
-  const int grid = grid_for(n, 256, 148 * 8);
+  const int grid = grid_for((n + 3) / 4, 256, 148 * 8);
+  const auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  const int vec = (al16(p) && al16(g) && al16(m) && al16(v) && al16(p_lp)) ? 1 : 0;
 #define ADAM_LAUNCH(G, LP) \
-  adam_kernel<G, LP><<<grid, 256, 0, st>>>(p, (const G*)g, m, v, (LP*)p_lp, n, lr, beta1, beta2, eps, wd, bc1, bc2, grad_scale, inv_scale_dev)
+  adam_kernel<G, LP><<<grid, 256, 0, st>>>(p, (const G*)g, m, v, (LP*)p_lp, n, lr, beta1, beta2, eps, wd, bc1, bc2, grad_scale, inv_scale_dev, vec)
   if (g_dtype == OSLO_DT_BF16) {
     if (lp_dtype == OSLO_DT_FP16) ADAM_LAUNCH(__nv_bfloat16, __half); else ADAM_LAUNCH(__nv_bfloat16, __nv_bfloat16);
   } else if (g_dtype == OSLO_DT_FP16) {
@@ -685,7 +741,8 @@ extern "C" int oslo_adam(float* p, const void* g, float* m, float* v, void* p_lp
 
 extern "C" int oslo_sumsq(const void* x, float* out, long long n, int dtype, cudaStream_t st) {
   if (n == 0) return 0;
-  DISPATCH_16(dtype, T, { sumsq_kernel<T><<<grid_for(n, 256, 148 * 4), 256, 0, st>>>((const T*)x, out, n); })
+  const int vec = (reinterpret_cast<uintptr_t>(x) & 15) == 0 ? 1 : 0;
+  DISPATCH_16(dtype, T, { sumsq_kernel<T><<<grid_for((n + 7) / 8, 256, 148 * 8), 256, 0, st>>>((const T*)x, out, n, vec); })
   RET_LAST();
 }
 
