@@ -51,6 +51,12 @@ def parse_args():
     ap.add_argument("--pp", type=int, default=1)
     ap.add_argument("--checkpoint-activations", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--mode", default="train", choices=["train", "decode"],
+                    help="train: tokens/s of a training step; decode: ms/token of greedy generation with a KV cache")
+    ap.add_argument("--prompt", type=int, default=512, help="decode: prompt length")
+    ap.add_argument("--new-tokens", type=int, default=128, help="decode: tokens generated per call")
+    ap.add_argument("--decode-batch", type=int, default=1, help="decode: sequences per call")
+    ap.add_argument("--no-graph", action="store_true", help="decode: run the token loop eagerly (no CUDA graph)")
     ap.add_argument("--layers", type=int, default=None, help="profiling only: override the layer count (result is labelled debug)")
     return ap.parse_args()
 
@@ -138,6 +144,9 @@ def main() -> None:
     n_layer, n_embd, n_head, rotary, vocab, n_pos = MODELS[args.model]
     if args.layers is not None:
         n_layer = args.layers
+    if args.mode == "decode":
+        decode_main(args, world, rank, local, dev, (n_layer, n_embd, n_head, rotary, vocab, n_pos))
+        return
     tp = args.tp or 1
     pp = args.pp
     dp = world // (tp * pp)
@@ -237,6 +246,100 @@ def main() -> None:
                        "l2": "working set per step >> 126 MB L2, no explicit flush"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "device_error_word": err,
             "peak_mem_gb": round(mem_gb, 1),
+        }
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def decode_main(args, world, rank, local, dev, dims) -> None:
+    """Greedy generation with a KV cache: tensor parallel over all GPUs, one CUDA-graph replay per token.
+
+    A "step" is one ``generate`` call (prompt prefill + ``--new-tokens`` tokens). ``value`` is the decode latency
+    per generated token after the prefill, device-timed, max over ranks; the end-to-end figure goes through
+    pinned host memory for the prompt and copies the generated ids back to the host every call."""
+    import torch
+    import torch.distributed as dist
+
+    import oslo_b200 as ob
+    from oslo_b200.generation.graph_decode import GraphedGreedyDecoder
+
+    n_layer, n_embd, n_head, rotary, vocab, n_pos = dims
+    tp = args.tp or world
+    cfg = ob.GPTJConfig(vocab_size=vocab, n_positions=n_pos, n_embd=n_embd, n_layer=n_layer, n_head=n_head,
+                        rotary_dim=rotary, torch_dtype=torch.bfloat16, use_cache=True)
+    model = ob.GPTJForCausalLM.from_config_with_parallel(cfg, tensor_parallel_size=tp, pipeline_parallel_size=1,
+                                                         seed=1234, init_on_device=True, torch_dtype=torch.bfloat16)
+    model.fuse()
+    model.eval()
+    ext = ob.ops.load_ext(required=True)
+    b, prompt, n_new = args.decode_batch, args.prompt, args.new_tokens
+    gen = torch.Generator().manual_seed(77)
+    host = [torch.randint(0, vocab, (b, prompt), generator=gen).pin_memory() for _ in range(4)]
+    dev_inputs = [h.to(dev) for h in host]
+    dec = GraphedGreedyDecoder(model, max_len=prompt + n_new, use_graph=not args.no_graph)
+    dec.record_events = True
+    dec.launch_counter = ext.launch_count
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", rank=rank, world_size=world)
+
+    def timed(steps, e2e):
+        dist.barrier()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(local)
+        sampler.start()
+        l0 = ext.launch_count()
+        r0 = dec.replays
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        wall0 = time.perf_counter()
+        t0.record()
+        decode_ms = prefill_ms = 0.0
+        evs = []
+        for s in range(steps):
+            if e2e:
+                ids = host[s % 4].to(dev, non_blocking=True)
+                out = dec.generate(ids, n_new).cpu()
+            else:
+                out = dec.generate(dev_inputs[s % 4], n_new)
+            evs.append(dec.events)
+        t1.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - wall0
+        for ev in evs:
+            prefill_ms += ev[0].elapsed_time(ev[1])
+            decode_ms += ev[1].elapsed_time(ev[2])
+        dist.barrier()
+        clocks = sampler.stop()
+        tot = t0.elapsed_time(t1) if not e2e else wall * 1e3
+        red = torch.tensor([tot, decode_ms, prefill_ms], device=dev)
+        dist.all_reduce(red, op=dist.ReduceOp.MAX)
+        tot, decode_ms, prefill_ms = red.tolist()
+        launches = ext.launch_count() - l0 + (dec.replays - r0) * dec.kernels_per_step  # eager + replayed kernels
+        return tot / steps, decode_ms / steps, prefill_ms / steps, clocks, launches, out
+
+    for _ in range(args.warmup):
+        dec.generate(dev_inputs[0], n_new)
+    ms_call, ms_dec, ms_pre, clocks, launches, _ = timed(args.steps, e2e=False)
+    e2e = None
+    if not args.no_e2e:
+        ms_e2e, _, _, _, _, out = timed(args.steps, e2e=True)
+        e2e = {"value": ms_e2e / n_new, "unit": "ms/token (whole generate call incl. prefill, host in/out)",
+               "ms_per_step": ms_e2e, "h2d_bytes_per_step": b * prompt * 8, "d2h_bytes_per_step": b * (prompt + n_new) * 8}
+    err = int(ext.error_word(dev_inputs[0]).item())
+    if rank == 0:
+        full = args.model == "gptj-6b" and args.layers is None
+        line = {
+            "metric": f"GPT-J-6B TP={tp} decode ms/token" if full else f"{args.model} TP={tp} decode ms/token (debug)",
+            "value": ms_dec / max(n_new - 1, 1), "unit": "ms/token", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_call, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
+            "impl": "oslo_b200",
+            "config": {"model": args.model, "global_batch": b, "seq_len": prompt, "new_tokens": n_new,
+                       "parallelism": f"tp{tp}", "decode": "greedy, static KV cache, " + ("eager loop" if args.no_graph else "CUDA-graph step"),
+                       "prefill_ms": ms_pre, "tokens_per_s": b * (n_new - 1) / (ms_dec / 1e3),
+                       "l2": "weights + KV cache per token >> 126 MB L2 per GPU only at tp<=2; no explicit flush"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "device_error_word": err,
+            "graph_replays": dec.replays, "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
         }
         print(json.dumps(line), flush=True)
     dist.barrier()

@@ -26,6 +26,7 @@ class OsloConfig:
     fused_tp_comm: bool = True           # GEMM + all-reduce / all-gather kernels over symmetric memory
     use_multimem: bool = True            # NVSwitch multicast (NVLS) loads / stores inside those kernels
     symm_buffer_mb: int = 256            # symmetric-memory workspace per tensor-parallel group
+    symm_allreduce_max_bytes: int = 1 << 20  # no-grad tensor-parallel all-reduces up to this size use the symmetric-memory kernel (0 = always NCCL)
     ddp_bucket_mb: int = 256
     pg_timeout_s: float = 1800.0         # process-group timeout (collectives fail instead of hanging)
     heartbeat_s: float = 5.0             # watchdog heartbeat period

@@ -9,7 +9,7 @@
 //   empty[s]   one per CTA; the MMA thread commits to both
 //   tfull[b]   one per CTA; the MMA thread commits to both
 //   tempty[b]  lives in the even CTA; 8 arrivals (4 epilogue warps of each CTA)
-// No load is multicast: each CTA fetches exactly the boxes it consumes. Every wait is bounded (ptx.cuh); the two
+// Each CTA fetches exactly the boxes it consumes itself. Every wait is bounded (ptx.cuh); the two
 // cluster-wide barriers (after set-up, before tear-down) are reached unconditionally by every thread.
 #pragma once
 #include "gemm_core.cuh"

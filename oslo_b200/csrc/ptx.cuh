@@ -186,7 +186,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // TMA tile load of a CTA pair: data lands in THIS CTA, completion bytes are counted on an mbarrier that may
-// belong to the pair's other CTA (shared::cluster address). No multicast: each CTA fetches its own box.
+// belong to the pair's other CTA (shared::cluster address). Each CTA fetches exactly its own box.
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"

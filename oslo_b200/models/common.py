@@ -37,6 +37,34 @@ class StaticKVCache:
         self.max_len = int(max_len)
         self.lengths_dev: Optional[Tensor] = None
         self.lengths_next: Optional[Tensor] = None
+        # device-position mode (CUDA-graph decoding): single-token appends are index_copy_ at a position kept
+        # in device memory, so the same captured step writes a new slot on every replay
+        self.write_index: Optional[Tensor] = None
+        self.device_positions = False
+
+    def use_device_positions(self, on: bool = True) -> None:
+        """Keep the write position of single-token appends on the device (needs one prior append). The position
+        tensor is allocated once and updated in place, so a CUDA graph captured earlier keeps addressing it."""
+        if not on:
+            self.device_positions = False
+            return
+        if self.lengths_dev is None:
+            raise RuntimeError("fill the cache (prefill) before switching to device positions")
+        self.lengths_dev.fill_(self.length)
+        self.lengths_next.fill_(self.length + 1)
+        if self.write_index is None:
+            self.write_index = torch.full((1,), self.length, dtype=torch.long, device=self.lengths_dev.device)
+        else:
+            self.write_index.fill_(self.length)
+        self.device_positions = True
+
+    def reset(self) -> None:
+        """Forget the contents (storage is kept) so the cache can take a new prompt."""
+        self.length = 0
+        self.device_positions = False
+        if self.lengths_dev is not None:
+            self.lengths_dev.zero_()
+            self.lengths_next.fill_(1)
 
     def append(self, layer: int, k: Tensor, v: Tensor) -> Tuple[Tensor, Tensor, int]:
         """Write ``k, v`` (``[B, heads, S, D]``) at the current position; returns the whole cache
@@ -51,6 +79,11 @@ class StaticKVCache:
         end = self.length + s
         if end > self.max_len:
             raise RuntimeError(f"KV cache overflow: {end} > {self.max_len}")
+        if self.device_positions and s == 1:
+            self.k[layer].index_copy_(2, self.write_index, k)
+            self.v[layer].index_copy_(2, self.write_index, v)
+            # `end` is only right outside graph replay; the decode kernel reads the valid length from lengths_next
+            return self.k[layer], self.v[layer], end
         self.k[layer][:, :, self.length:end].copy_(k)
         self.v[layer][:, :, self.length:end].copy_(v)
         return self.k[layer], self.v[layer], end
@@ -59,6 +92,8 @@ class StaticKVCache:
         self.length += s
         self.lengths_dev.add_(s)
         self.lengths_next.add_(s)
+        if self.device_positions:
+            self.write_index.add_(s)
 
     def get_seq_length(self) -> int:
         return self.length

@@ -271,8 +271,21 @@ class MPU:
         if self.tp == 1:
             return x
         x = x.contiguous()
+        if self._small_symm_ok(x):
+            # latency-bound sizes (decode steps): one-shot all-reduce kernel over symmetric memory; its
+            # signal words reset themselves, so the call can sit inside a captured CUDA graph
+            from .symmetric import get_workspace
+            return get_workspace(self._tp_group).all_reduce_(x)
         dist.all_reduce(x, group=self._tp_group)
         return x
+
+    def _small_symm_ok(self, x: Tensor) -> bool:
+        if not x.is_cuda or x.dtype not in (torch.bfloat16, torch.float16) or x.numel() % 8 or x.numel() == 0:
+            return False
+        from ..config import get_config
+        cfg = get_config()
+        limit = getattr(cfg, "symm_allreduce_max_bytes", 0)
+        return bool(limit) and x.numel() * 2 <= limit and not torch.is_grad_enabled()
 
     def _scatter(self, x: Tensor, dim: int = -1) -> Tensor:
         if self.tp == 1:

@@ -80,3 +80,17 @@ def test_roofline_and_config(monkeypatch):
     monkeypatch.setenv("OSLO_B200_USE_MULTIMEM", "0")
     c = cfgmod.OsloConfig.from_env()
     assert c.ddp_bucket_mb == 32 and c.use_multimem is False
+
+
+def test_graphed_greedy_decoder_matches_generate_on_cpu():
+    """The device-position cache bookkeeping of the CUDA-graph decoder, run eagerly, equals generate()."""
+    import oslo_b200 as ob
+    from oslo_b200.generation import GraphedGreedyDecoder
+    torch.manual_seed(0)
+    cfg = ob.GPTJConfig(vocab_size=512, n_positions=128, n_embd=64, n_layer=2, n_head=4, rotary_dim=8)
+    model = ob.GPTJForCausalLM(cfg).eval()
+    ids = torch.randint(0, 512, (2, 7))
+    dec = GraphedGreedyDecoder(model, max_len=64)
+    for prompt, n_new in ((7, 12), (5, 10)):
+        want = model.generate(ids[:, :prompt], max_length=prompt + n_new, do_sample=False)
+        assert torch.equal(dec.generate(ids[:, :prompt], n_new), want)

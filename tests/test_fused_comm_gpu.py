@@ -62,6 +62,14 @@ def test_fused_ops_world2():
     run_gpus(_check_ops, 2)
 
 
+@pytest.mark.multigpu
+@pytest.mark.parametrize("world", [4, 8])
+def test_fused_ops_world_n(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    run_gpus(_check_ops, world)
+
+
 def _tp_model(rank, world, tmp, seq_par):
     import oslo_b200 as ob
     from oslo_b200.config import set_config

@@ -333,3 +333,19 @@ def test_fused_model_matches_eager_model(kind):
         rel = (a - b).norm() / (b.norm() + 1e-6)
         worst = max(worst, rel.item())
         assert rel < 0.08, (n, rel.item())
+
+
+def test_graphed_greedy_decoder_gpu():
+    """CUDA-graph replayed greedy decoding produces the tokens of the eager generate() loop."""
+    import oslo_b200 as ob
+    from oslo_b200.generation import GraphedGreedyDecoder
+    torch.manual_seed(0)
+    cfg = ob.GPTJConfig(vocab_size=1024, n_positions=256, n_embd=256, n_layer=2, n_head=4, rotary_dim=16)
+    model = ob.GPTJForCausalLM(cfg).to(torch.bfloat16).cuda().fuse().eval()
+    ids = torch.randint(0, 1024, (3, 33), device="cuda")
+    dec = GraphedGreedyDecoder(model, max_len=128)
+    for prompt, n_new in ((33, 40), (20, 30)):
+        want = model.generate(ids[:, :prompt], max_length=prompt + n_new, do_sample=False)
+        got = dec.generate(ids[:, :prompt], n_new)
+        assert torch.equal(got, want)
+    assert dec.replays > 0
