@@ -500,26 +500,58 @@ __global__ void __launch_bounds__(128) decode_attn_kernel(const T* __restrict__ 
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
   const bool lane_active = l * 8 < D;
-  for (int t = t0 + w; t < t1; t += 4) {
-    float dot = 0.f;
-    if (lane_active) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(kb + static_cast<long long>(t) * D + l * 8);
-      const T* e = reinterpret_cast<const T*>(&raw);
+  // each warp walks its keys in batches of KB: all K and V rows of a batch are requested before any of them is
+  // used, so a warp keeps 2 * KB 16-byte loads in flight instead of one (the scan is latency-bound otherwise)
+  constexpr int KB = 8;
+  for (int tb = t0 + w * KB; tb < t1; tb += 4 * KB) {
+    uint4 kraw[KB], vraw[KB];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) dot += Mma<T>::to_f(e[i]) * qs[l * 8 + i];
+    for (int j = 0; j < KB; ++j) {
+      const int t = tb + j;
+      if (lane_active && t < t1) {
+        kraw[j] = *reinterpret_cast<const uint4*>(kb + static_cast<long long>(t) * D + l * 8);
+        vraw[j] = *reinterpret_cast<const uint4*>(vb + static_cast<long long>(t) * D + l * 8);
+      } else {
+        kraw[j] = make_uint4(0, 0, 0, 0);
+        vraw[j] = make_uint4(0, 0, 0, 0);
+      }
+    }
+    float dot[KB];
+#pragma unroll
+    for (int j = 0; j < KB; ++j) {
+      const T* e = reinterpret_cast<const T*>(&kraw[j]);
+      float d = 0.f;
+      if (lane_active) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d += Mma<T>::to_f(e[i]) * qs[l * 8 + i];
+      }
+      dot[j] = d;
     }
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-    const float mn = fmaxf(m, dot);
-    const float a = exp2f(m - mn), pr = exp2f(dot - mn);
-    s = s * a + pr;
+    for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+      for (int j = 0; j < KB; ++j) dot[j] += __shfl_xor_sync(0xffffffffu, dot[j], off);
+    }
+    float mn = m;
+#pragma unroll
+    for (int j = 0; j < KB; ++j) {
+      if (tb + j >= t1) dot[j] = -CUDART_INF_F;
+      mn = fmaxf(mn, dot[j]);
+    }
+    const float a = exp2f(m - mn);   // m = -inf on the first batch: a = 0 and s, acc are 0 anyway
+    float ps = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] *= a;
+#pragma unroll
+    for (int j = 0; j < KB; ++j) {
+      const float pr = exp2f(dot[j] - mn);
+      ps += pr;
+      const T* e = reinterpret_cast<const T*>(&vraw[j]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += pr * Mma<T>::to_f(e[i]);
+    }
+    s = s * a + ps;
     m = mn;
-    if (lane_active) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(vb + static_cast<long long>(t) * D + l * 8);
-      const T* e = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = acc[i] * a + pr * Mma<T>::to_f(e[i]);
-    }
   }
   if (l == 0) { stat[w * 2] = m; stat[w * 2 + 1] = s; }
   __syncthreads();

@@ -117,6 +117,38 @@ Tensor gemm(const Tensor& a, const Tensor& b, int64_t a_mn, int64_t b_mn, const 
   return d;
 }
 
+// y = act(a @ b^T + bias) for few rows (decode steps): split-K GEMM into fp32 planes, then one finalisation
+// kernel that sums them in a fixed order. Falls back to the ordinary GEMM when splitting the k range gains nothing.
+Tensor gemm_small_m(const Tensor& a, const Tensor& b, int64_t b_mn, const optional<Tensor>& bias, bool gelu) {
+  check_2d_operand(a, "a");
+  check_2d_operand(b, "b");
+  TORCH_CHECK(a.scalar_type() == b.scalar_type(), "a and b must share a dtype");
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 || a.scalar_type() == at::kHalf, "gemm inputs must be bf16 or fp16");
+  c10::cuda::CUDAGuard guard(a.device());
+  const int64_t M = a.size(0), K = a.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0), Kb = b_mn ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb, "contraction sizes differ: ", K, " vs ", Kb);
+  auto& st = dev_state(a.get_device());
+  const int split = oslo_gemm_split_k_for(static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), st.sms);
+  const bool has_bias = bias.has_value() && bias->defined();
+  if (has_bias)
+    TORCH_CHECK(bias->numel() == N && bias->scalar_type() == a.scalar_type() && bias->is_contiguous(), "bad bias");
+  if (split <= 1) {
+    const int64_t fl = (has_bias ? GEMM_FLAG_BIAS : 0) | (gelu ? GEMM_FLAG_GELU : 0);
+    return gemm(a, b, 0, b_mn, bias, optional<Tensor>(), optional<Tensor>(), optional<Tensor>(), fl, 1.0);
+  }
+  Tensor ws = at::empty({split, M, N}, a.options().dtype(at::kFloat));
+  check_rc(oslo_gemm_splitk_16bit(a.data_ptr(), b.data_ptr(), ws.data_ptr<float>(), static_cast<int>(M),
+                                  static_cast<int>(N), static_cast<int>(K), static_cast<int>(a.stride(0)),
+                                  static_cast<int>(b.stride(0)), static_cast<int>(N), 0, static_cast<int>(b_mn),
+                                  a.scalar_type() == at::kHalf ? 1 : 0, split, st.err.data_ptr<int>(), st.sms,
+                                  cur_stream()), "gemm_splitk");
+  Tensor y = at::empty({M, N}, a.options());
+  check_rc(oslo_splitk_finalize(ws.data_ptr<float>(), has_bias ? bias->data_ptr() : nullptr, y.data_ptr(), M,
+                                static_cast<int>(N), split, gelu ? 1 : 0, dt_code(a), cur_stream()), "splitk_finalize");
+  return y;
+}
+
 std::tuple<Tensor, Tensor, Tensor> layernorm_fwd(const Tensor& x, const Tensor& w, const optional<Tensor>& b, double eps) {
   TORCH_CHECK(x.is_cuda() && x.is_contiguous() && w.is_contiguous(), "layernorm: contiguous CUDA tensors required");
   c10::cuda::CUDAGuard guard(x.device());
@@ -376,7 +408,7 @@ Tensor decode_attn(const Tensor& q, const Tensor& kc, const Tensor& vc, const Te
   const int B = q.size(0), H = q.size(1), D = q.size(2), T = kc.size(2);
   const int sms = dev_state(q.get_device()).sms;
   int splits = std::max(1, std::min(32, (2 * sms) / std::max(1, B * H)));
-  splits = std::min(splits, std::max(1, T / 64));
+  splits = std::min(splits, std::max(1, T / 32));   // at least one 8-key batch per warp and slice
   Tensor ws = at::empty({B, H, splits, D + 2}, q.options().dtype(at::kFloat));
   Tensor o = at::empty_like(q);
   check_rc(oslo_decode_attn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), lengths.data_ptr<int>(),
@@ -451,6 +483,7 @@ TORCH_LIBRARY(oslo_b200, m) {
   m.def("error_word(Tensor like) -> Tensor", &error_word);
   m.def("launch_count() -> int", &launch_count);
   m.def("gemm(Tensor a, Tensor b, int a_mn, int b_mn, Tensor? bias, Tensor? aux, Tensor(a!)? out, Tensor(b!)? aux_out, int flags, float alpha) -> Tensor", &gemm);
+  m.def("gemm_small_m(Tensor a, Tensor b, int b_mn, Tensor? bias, bool gelu) -> Tensor", &gemm_small_m);
   m.def("layernorm_fwd(Tensor x, Tensor w, Tensor? b, float eps) -> (Tensor, Tensor, Tensor)", &layernorm_fwd);
   m.def("layernorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor mean, Tensor rstd) -> (Tensor, Tensor, Tensor)", &layernorm_bwd);
   m.def("bias_gelu_fwd(Tensor x, Tensor? bias) -> Tensor", &bias_gelu_fwd);

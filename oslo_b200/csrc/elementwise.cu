@@ -550,6 +550,21 @@ __global__ void __launch_bounds__(256) sumsq_kernel(const T* __restrict__ x, flo
   if (threadIdx.x == 0) atomicAdd(out, s);
 }
 
+// ---------------------------------------------------------------------- split-K GEMM finalisation
+// out[r, c] = T(act(sum_s ws[s, r, c] + bias[c])): sums the k-slice planes of a split-K GEMM in a fixed order
+template <typename T>
+__global__ void splitk_finalize_kernel(const float* __restrict__ ws, const T* __restrict__ bias, T* __restrict__ out,
+                                       long long n, int cols, int split_k, int gelu) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float v = 0.f;
+    for (int s = 0; s < split_k; ++s) v += ws[s * n + i];
+    if (bias) v += Cvt<T>::to(bias[i % cols]);
+    if (gelu) v = gelu_f(v);
+    out[i] = Cvt<T>::from(v);
+  }
+}
+
 // ---------------------------------------------------------------------- n-gram blocking
 // thread `c` compares the (n-1)-gram starting at c with the last (n-1) tokens of the row; on a match the
 // token that followed it is banned. No shared memory is used, so the row length is unbounded.
@@ -750,5 +765,18 @@ extern "C" int oslo_ngram_ban(const long long* tokens, float* lprobs, int rows, 
                               cudaStream_t st) {
   if (rows == 0 || n <= 0 || len + 1 < n) return 0;
   ngram_ban_kernel<<<rows, 256, 0, st>>>(tokens, lprobs, len, vocab, n);
+  RET_LAST();
+}
+
+extern "C" int oslo_splitk_finalize(const float* ws, const void* bias, void* out, long long rows, int cols, int split_k,
+                                    int gelu, int dtype, cudaStream_t st) {
+  const long long n = rows * cols;
+  if (n == 0) return 0;
+  if (dtype == OSLO_DT_BF16)
+    splitk_finalize_kernel<__nv_bfloat16><<<grid_for(n, 256), 256, 0, st>>>(ws, (const __nv_bfloat16*)bias, (__nv_bfloat16*)out, n, cols, split_k, gelu);
+  else if (dtype == OSLO_DT_FP16)
+    splitk_finalize_kernel<__half><<<grid_for(n, 256), 256, 0, st>>>(ws, (const __half*)bias, (__half*)out, n, cols, split_k, gelu);
+  else
+    return -2;
   RET_LAST();
 }

@@ -49,6 +49,8 @@ struct GemmParams {
   float alpha;
   int* err;
   int tiles_m, tiles_n;
+  int split_k = 1;      // > 1: every tile's k range is cut into this many work items; slice s writes its fp32 partial
+                        // result to plane s of D ([split_k, M, ldd] fp32); other epilogue flags are ignored
   CommParams comm;
 };
 
@@ -192,11 +194,23 @@ __device__ __forceinline__ int tile_owner(const CommParams& c, int idx, int tm, 
 // pre-activation), dGeLU, residual, accumulate, conversion and the store. `row` < M and `col0` < N are the
 // caller's responsibility.
 __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int row, int col0, const uint32_t (&r)[32],
-                                               bool fp16, bool out_f32) {
+                                               bool fp16, bool out_f32, int kslice = 0) {
     float v[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
     const int ncols = min(32, p.N - col0);
+    if (p.split_k > 1) {  // partial sums of k slice `kslice` go to their own [M, ldd] fp32 plane (deterministic)
+      float* d = reinterpret_cast<float*>(p.D) + (static_cast<size_t>(kslice) * p.M + row) * p.ldd + col0;
+      if (ncols == 32) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(d + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i < ncols) d[i] = v[i];
+      }
+      return;
+    }
     const bool vec = (ncols == 32);
     if (p.flags & GEMM_FLAG_BIAS) {
       if (vec) {
@@ -357,6 +371,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
 
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int kblocks = (p.K + BK - 1) / BK;
+  // work item = (tile, k slice); one slice per tile unless split_k > 1
+  const int split_k = COMM ? 1 : p.split_k;
+  const int num_items = num_tiles * split_k;
   // all-gather mode walks the row blocks starting with this rank's own shard, which needs no transfer
   auto coords = [&](int tile, int& tm, int& tn) {
     tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
@@ -419,11 +436,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const int tile = item % num_tiles, ks = item / num_tiles;
+        const int kb0 = ks * kblocks / split_k, kb1 = (ks + 1) * kblocks / split_k;
         int tm, tn;
         coords(tile, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, p.err, ERR_WAIT_EMPTY);
           if (!ok) break;
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
@@ -462,14 +481,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       uint32_t acc_phase[2] = {0, 0};
       int local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++local) {
+        const int ks = item / num_tiles;
+        const int kb0 = ks * kblocks / split_k, kb1 = (ks + 1) * kblocks / split_k;
         const int buf = local & 1;
         ok = mbar_wait(tempty_bar(buf), acc_phase[buf] ^ 1, abort_flag, p.err, ERR_WAIT_TMEM_EMPTY);
         if (!ok) break;
         acc_phase[buf] ^= 1;
         tc_fence_after();
         const uint32_t tmem_acc = tmem_base + buf * BN;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(full_bar(stage), phase, abort_flag, p.err, ERR_WAIT_FULL);
           if (!ok) break;
           tc_fence_after();
@@ -479,7 +500,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           for (int k = 0; k < BK / 16; ++k) {
             const uint64_t da = make_smem_desc(sa + k * a_step, a_lbo, 1024);
             const uint64_t db = make_smem_desc(sb + k * b_step, b_lbo, 1024);
-            umma_f16(tmem_acc, da, db, idesc, (kb | k) != 0);
+            umma_f16(tmem_acc, da, db, idesc, (kb != kb0) || (k != 0));
           }
           umma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -496,7 +517,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     uint32_t acc_phase[2] = {0, 0};
     int local = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++local) {
+      const int tile = item % num_tiles, kslice = item / num_tiles;
       const int buf = local & 1;
       int tm, tn;
       coords(tile, tm, tn);
@@ -514,7 +536,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         tmem_wait_ld();
         const int col0 = tn * BN + c0;
         if (!row_ok || col0 >= p.N) continue;
-        epilogue_chunk(p, row, col0, r, fp16, out_f32);
+        epilogue_chunk(p, row, col0, r, fp16, out_f32, kslice);
       }
       tc_fence_before();
       __syncwarp();

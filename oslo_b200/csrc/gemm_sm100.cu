@@ -75,6 +75,17 @@ int make_tma_nd_16bit(CUtensorMap* map, const void* ptr, int rank, const uint64_
 }
 
 template <int BN, int STAGES>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, int num_sms, cudaStream_t stream);
+
+// Few-row GEMM (decode steps): 128 x 128 tiles whose k range is cut into `split_k` slices so that all SMs stream
+// weights; slice s writes its partial sums to plane s of the fp32 workspace D [split_k, M, N].
+static int launch_split_k(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, int split_k, int num_sms,
+                          cudaStream_t stream) {
+  p.split_k = split_k;
+  return launch<128, 6>(ta, tb, p, num_sms, stream);
+}
+
+template <int BN, int STAGES>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, int num_sms, cudaStream_t stream) {
   constexpr size_t smem = STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
   static bool configured = false;
@@ -86,7 +97,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, i
   }
   p.tiles_m = (p.M + BM - 1) / BM;
   p.tiles_n = (p.N + BN - 1) / BN;
-  const int tiles = p.tiles_m * p.tiles_n;
+  const int tiles = p.tiles_m * p.tiles_n * p.split_k;
   const int grid = tiles < num_sms ? tiles : num_sms;
   gemm_tcgen05_kernel<BN, STAGES, false><<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, p);
   return static_cast<int>(cudaGetLastError());
@@ -164,4 +175,40 @@ extern "C" int oslo_gemm_16bit(const void* A, const void* B, void* D, int M, int
   if (pair) return launch_pair<6>(ta, tb, p, num_sms, stream);
   if (bn == 256) return launch<256, 4>(ta, tb, p, num_sms, stream);
   return launch<128, 6>(ta, tb, p, num_sms, stream);
+}
+
+// how many k slices a few-row GEMM should use so that about two work items exist per SM (1 = do not split)
+extern "C" int oslo_gemm_split_k_for(int M, int N, int K, int num_sms) {
+  using namespace oslo;
+  if (M > BM) return 1;
+  const int tiles = (N + 127) / 128;
+  const int kblocks = (K + BK - 1) / BK;
+  int s = (2 * num_sms) / (tiles > 0 ? tiles : 1);
+  if (s > kblocks / 2) s = kblocks / 2;
+  return s < 2 ? 1 : s;
+}
+
+// D[s, M, N] (fp32) = partial A B^T of k slice s, for s < split_k; M <= 128. The planes need no initialisation.
+extern "C" int oslo_gemm_splitk_16bit(const void* A, const void* B, float* D, int M, int N, int K, int lda, int ldb,
+                                      int ldd, int a_mn_major, int b_mn_major, int fp16, int split_k, int* err_word,
+                                      int num_sms, cudaStream_t stream) {
+  using namespace oslo;
+  if (M <= 0 || N <= 0 || K <= 0 || M > BM || split_k < 1 || split_k > (K + BK - 1) / BK) return -1;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) { cudaFree(nullptr); ctx_bound = true; }
+  CUtensorMap ta, tb;
+  int rc;
+  if (!a_mn_major) rc = make_tma_2d_16bit(&ta, A, K, M, lda, BM, fp16 != 0);
+  else rc = make_tma_2d_16bit(&ta, A, M, K, lda, 64, fp16 != 0);
+  if (rc) return rc;
+  if (!b_mn_major) rc = make_tma_2d_16bit(&tb, B, K, N, ldb, 128, fp16 != 0);
+  else rc = make_tma_2d_16bit(&tb, B, N, K, ldb, 64, fp16 != 0);
+  if (rc) return rc - 1000;
+  GemmParams p;
+  p.D = D; p.bias = nullptr; p.aux = nullptr; p.aux_out = nullptr;
+  p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ld_aux = 0; p.ld_aux_out = 0;
+  p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
+  p.flags = GEMM_FLAG_OUT_FP32 | (fp16 ? GEMM_FLAG_FP16 : 0); p.alpha = 1.f; p.err = err_word;
+  p.comm = CommParams{};
+  return launch_split_k(ta, tb, p, split_k, num_sms, stream);
 }

@@ -26,6 +26,16 @@ int oslo_gemm_16bit(const void* A, const void* B, void* D, int M, int N, int K, 
                     int a_mn_major, int b_mn_major, const void* bias, const void* aux, int ld_aux, void* aux_out,
                     int ld_aux_out, int flags, float alpha, int* err_word, int num_sms, cudaStream_t stream);
 
+// few-row GEMM for decode steps (M <= 128): k range cut into `split_k` slices, slice s writes its fp32 partial sums
+// to plane s of D [split_k, M, N]; oslo_gemm_split_k_for suggests the slice count (1 = use oslo_gemm_16bit)
+int oslo_gemm_split_k_for(int M, int N, int K, int num_sms);
+int oslo_gemm_splitk_16bit(const void* A, const void* B, float* D, int M, int N, int K, int lda, int ldb, int ldd,
+                           int a_mn_major, int b_mn_major, int fp16, int split_k, int* err_word, int num_sms,
+                           cudaStream_t stream);
+// out = T(act(sum over planes of ws + bias)) for the [split_k, rows, cols] fp32 result of the split-K GEMM
+int oslo_splitk_finalize(const float* ws, const void* bias, void* out, long long rows, int cols, int split_k, int gelu,
+                         int dtype, cudaStream_t stream);
+
 // LayerNorm over the last dim of [rows, cols]; mean/rstd are fp32 [rows]
 int oslo_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int rows,
                        int cols, float eps, int dtype, cudaStream_t stream);

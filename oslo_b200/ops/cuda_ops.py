@@ -63,6 +63,9 @@ def gemm_tn(d: Tensor, x: Tensor, out_dtype=None) -> Tensor:
     return gemm(d, x, True, True, flags=FLAG_OUT_FP32 if out_dtype == torch.float32 else 0)
 
 
+SMALL_M_ROWS = 64  # inference calls with at most this many rows use the split-K path
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, reversed_, gelu):
@@ -108,6 +111,12 @@ def linear(x: Tensor, weight: Tensor, bias: Optional[Tensor], reversed_: bool, a
           and (bias is None or bias.dtype == x.dtype))
     if not ok:  # fp32 or ragged shapes: library GEMM, same semantics
         return ref.linear(x, weight, bias, reversed_, activation)
+    rows = x.numel() // x.size(-1)
+    if rows <= SMALL_M_ROWS and not (torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)):
+        # decode steps: weight-streaming split-K GEMM so that every SM pulls weights, not just N / 128 of them
+        y = _ext().gemm_small_m(_as_operand(x.reshape(rows, x.size(-1))), _as_operand(weight), int(reversed_), bias,
+                                activation is not None)
+        return y.view(*x.shape[:-1], n)
     return _Linear.apply(x, weight, bias, reversed_, activation is not None)
 
 

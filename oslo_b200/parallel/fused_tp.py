@@ -114,6 +114,11 @@ def fused_tp_usable(mpu, x: Tensor, n_out: int, rows: Optional[int] = None) -> b
     if not ops.kernels_available():
         return False
     rows = rows if rows is not None else x.numel() // x.size(-1)
+    # decode-sized inputs gain nothing from overlapping tiles with their transfer, and the kernels take their
+    # generation numbers as launch arguments, which a replayed CUDA graph would freeze: such calls use the plain
+    # GEMM followed by the one-shot symmetric-memory all-reduce instead
+    if rows < 128 or torch.cuda.is_current_stream_capturing():
+        return False
     ctx = get_fused_tp(mpu.get_tensor_parallel_group())
     return ctx.fits(rows, max(n_out, x.size(-1)))  # forward and backward staging matrices
 

@@ -349,3 +349,24 @@ def test_graphed_greedy_decoder_gpu():
         got = dec.generate(ids[:, :prompt], n_new)
         assert torch.equal(got, want)
     assert dec.replays > 0
+
+
+@pytest.mark.parametrize("M,N,K,rev", [(1, 4096, 4096, False), (8, 512, 4096, False), (32, 16384, 4096, True),
+                                        (5, 4096, 16384, False), (64, 264, 520, True), (3, 50400, 1024, False)])
+def test_small_m_linear(M, N, K, rev):
+    """Decode-sized linear layers (split-K path) against fp32, and bit-identical when repeated."""
+    ops, co = _ops()
+    torch.manual_seed(3)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16) * 0.5
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    b = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    wt = w.t().contiguous() if rev else w
+    with torch.no_grad():
+        y = co.linear(x, wt, b, rev, "gelu_new")
+        y2 = co.linear(x, wt, b, rev, "gelu_new")
+        z = co.linear(x, wt, None, rev, None)
+    ref = x.float() @ w.float().t()
+    _close(z, ref, atol=0.03)
+    _close(y, ops.reference.gelu_tanh(ref + b.float()), atol=0.03)
+    assert torch.equal(y, y2)
+    assert co.device_error_code(y) == 0
