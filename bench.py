@@ -342,8 +342,20 @@ def decode_main(args, world, rank, local, dev, dims) -> None:
             "graph_replays": dec.replays, "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
         }
         print(json.dumps(line), flush=True)
+    # captured graphs hold the tensor-parallel communicator: free them first, and do not let a slow communicator
+    # shutdown keep a finished benchmark alive
+    dec.release()
+    import gc
+    import threading
+    gc.collect()
+    torch.cuda.synchronize()
     dist.barrier()
+    sys.stdout.flush()
+    killer = threading.Timer(30.0, lambda: os._exit(0))
+    killer.daemon = True
+    killer.start()
     dist.destroy_process_group()
+    killer.cancel()
 
 
 if __name__ == "__main__":

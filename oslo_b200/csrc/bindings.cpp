@@ -119,7 +119,9 @@ Tensor gemm(const Tensor& a, const Tensor& b, int64_t a_mn, int64_t b_mn, const 
 
 // y = act(a @ b^T + bias) for few rows (decode steps): split-K GEMM into fp32 planes, then one finalisation
 // kernel that sums them in a fixed order. Falls back to the ordinary GEMM when splitting the k range gains nothing.
-Tensor gemm_small_m(const Tensor& a, const Tensor& b, int64_t b_mn, const optional<Tensor>& bias, bool gelu) {
+// `gelu_from`: -1 = no activation, c >= 0 = tanh-GeLU on output columns >= c (0 = all of them), which lets one GEMM
+// serve several layers that share an input when only the last of them is followed by the activation.
+Tensor gemm_small_m(const Tensor& a, const Tensor& b, int64_t b_mn, const optional<Tensor>& bias, int64_t gelu_from) {
   check_2d_operand(a, "a");
   check_2d_operand(b, "b");
   TORCH_CHECK(a.scalar_type() == b.scalar_type(), "a and b must share a dtype");
@@ -129,12 +131,12 @@ Tensor gemm_small_m(const Tensor& a, const Tensor& b, int64_t b_mn, const option
   const int64_t N = b_mn ? b.size(1) : b.size(0), Kb = b_mn ? b.size(0) : b.size(1);
   TORCH_CHECK(K == Kb, "contraction sizes differ: ", K, " vs ", Kb);
   auto& st = dev_state(a.get_device());
-  const int split = oslo_gemm_split_k_for(static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), st.sms);
+  const int split = std::max(1, oslo_gemm_split_k_for(static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), st.sms));
   const bool has_bias = bias.has_value() && bias->defined();
   if (has_bias)
     TORCH_CHECK(bias->numel() == N && bias->scalar_type() == a.scalar_type() && bias->is_contiguous(), "bad bias");
-  if (split <= 1) {
-    const int64_t fl = (has_bias ? GEMM_FLAG_BIAS : 0) | (gelu ? GEMM_FLAG_GELU : 0);
+  if (split <= 1 && gelu_from <= 0) {
+    const int64_t fl = (has_bias ? GEMM_FLAG_BIAS : 0) | (gelu_from == 0 ? GEMM_FLAG_GELU : 0);
     return gemm(a, b, 0, b_mn, bias, optional<Tensor>(), optional<Tensor>(), optional<Tensor>(), fl, 1.0);
   }
   Tensor ws = at::empty({split, M, N}, a.options().dtype(at::kFloat));
@@ -145,7 +147,7 @@ Tensor gemm_small_m(const Tensor& a, const Tensor& b, int64_t b_mn, const option
                                   cur_stream()), "gemm_splitk");
   Tensor y = at::empty({M, N}, a.options());
   check_rc(oslo_splitk_finalize(ws.data_ptr<float>(), has_bias ? bias->data_ptr() : nullptr, y.data_ptr(), M,
-                                static_cast<int>(N), split, gelu ? 1 : 0, dt_code(a), cur_stream()), "splitk_finalize");
+                                static_cast<int>(N), split, static_cast<int>(gelu_from), dt_code(a), cur_stream()), "splitk_finalize");
   return y;
 }
 
@@ -477,13 +479,27 @@ void allreduce_symm(int64_t peer_ptrs_dev, int64_t mc_ptr, int64_t signal_ptrs_d
                                st.err.data_ptr<int>(), cur_stream()), "allreduce_symm");
 }
 
+// In-place one-kernel all-reduce of a small tensor through two alternating staging halves of a symmetric buffer.
+void allreduce_oneshot(Tensor x, int64_t peer_ptrs_dev, int64_t mc_ptr, int64_t signal_ptrs_dev, Tensor counters,
+                       int64_t stage_off, int64_t half_bytes, int64_t rank, int64_t world, bool use_multimem) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && counters.is_cuda() && counters.scalar_type() == at::kInt &&
+                  counters.numel() >= 64, "allreduce_oneshot: bad arguments");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto& st = dev_state(x.get_device());
+  check_rc(oslo_allreduce_oneshot(x.data_ptr(), x.data_ptr(), reinterpret_cast<void* const*>(peer_ptrs_dev),
+                                  reinterpret_cast<void*>(mc_ptr), reinterpret_cast<uint32_t* const*>(signal_ptrs_dev),
+                                  reinterpret_cast<uint32_t*>(counters.data_ptr<int>()), x.numel(), stage_off, half_bytes,
+                                  static_cast<int>(rank), static_cast<int>(world), dt_code(x), use_multimem ? 1 : 0,
+                                  st.err.data_ptr<int>(), cur_stream()), "allreduce_oneshot");
+}
+
 }  // namespace
 
 TORCH_LIBRARY(oslo_b200, m) {
   m.def("error_word(Tensor like) -> Tensor", &error_word);
   m.def("launch_count() -> int", &launch_count);
   m.def("gemm(Tensor a, Tensor b, int a_mn, int b_mn, Tensor? bias, Tensor? aux, Tensor(a!)? out, Tensor(b!)? aux_out, int flags, float alpha) -> Tensor", &gemm);
-  m.def("gemm_small_m(Tensor a, Tensor b, int b_mn, Tensor? bias, bool gelu) -> Tensor", &gemm_small_m);
+  m.def("gemm_small_m(Tensor a, Tensor b, int b_mn, Tensor? bias, int gelu_from) -> Tensor", &gemm_small_m);
   m.def("layernorm_fwd(Tensor x, Tensor w, Tensor? b, float eps) -> (Tensor, Tensor, Tensor)", &layernorm_fwd);
   m.def("layernorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor mean, Tensor rstd) -> (Tensor, Tensor, Tensor)", &layernorm_bwd);
   m.def("bias_gelu_fwd(Tensor x, Tensor? bias) -> Tensor", &bias_gelu_fwd);
@@ -503,5 +519,6 @@ TORCH_LIBRARY(oslo_b200, m) {
   m.def("flash_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale, bool causal, int window, Tensor? kpm, int impl=1) -> (Tensor, Tensor, Tensor)", &flash_bwd);
   m.def("decode_attn(Tensor q, Tensor kc, Tensor vc, Tensor lengths, float scale, int window) -> Tensor", &decode_attn);
   m.def("gemm_comm(Tensor a, Tensor b, int a_mn, int b_mn, Tensor? bias, Tensor(a!)? aux_out, Tensor(b!)? out, int flags, float alpha, int M, int N, int K, int peer_bufs_dev, int own_buf, int mc_base, int data_off, int flag_off, int flag_bytes, int rank, int world, int epoch, int done_base, int mode, bool use_multimem, Tensor(c!)? trace) -> int", &gemm_comm);
+  m.def("allreduce_oneshot(Tensor(a!) x, int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(b!) counters, int stage_off, int half_bytes, int rank, int world, bool use_multimem) -> ()", &allreduce_oneshot);
   m.def("allreduce_symm(int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(a!) out, int numel, int rank, int world, bool use_multimem) -> ()", &allreduce_symm);
 }

@@ -133,7 +133,73 @@ __global__ void __launch_bounds__(512) allreduce_symm_kernel(void* const* peer_p
   }
 }
 
+// One-shot all-reduce for latency-bound sizes, one kernel and one cross-rank barrier per call:
+//   1. every block copies its slice of `in` into this rank's symmetric staging buffer (half `parity`),
+//   2. meets the same block of every other rank,
+//   3. sums the slice over all ranks (multimem.ld_reduce, or peer loads) straight into `out` (may alias `in`).
+// The two staging halves alternate per call; the parity lives in device memory (one counter per block, bumped by
+// the block itself), so a replayed CUDA graph keeps alternating. A half is only rewritten two calls later, and a
+// rank can get there only after every rank has passed the barrier of the call in between, i.e. has finished
+// reading: no trailing barrier is needed.
+template <bool FP16>
+__global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const void* in, void* out, void* const* peer_ptrs,
+                                                                void* mc_ptr, uint32_t* const* signal_ptrs,
+                                                                uint32_t* counters, long long n16, long long stage_off16,
+                                                                long long half16, int rank, int world, int use_multimem,
+                                                                int* err) {
+  const uint32_t parity = counters[blockIdx.x] & 1u;
+  const long long base = stage_off16 + parity * half16;
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  uint4* mine = reinterpret_cast<uint4*>(peer_ptrs[rank]) + base;
+  for (long long i = tid; i < n16; i += nthreads) mine[i] = reinterpret_cast<const uint4*>(in)[i];
+  if (!block_barrier_all_ranks(signal_ptrs, rank, world, 0, err)) return;
+  uint4* dst = reinterpret_cast<uint4*>(out);
+  if (use_multimem) {
+    const uint4* mc = reinterpret_cast<const uint4*>(mc_ptr) + base;
+    for (long long i = tid; i < n16; i += nthreads) dst[i] = multimem_ld_reduce<FP16>(mc + i);
+  } else {
+    for (long long i = tid; i < n16; i += nthreads) {
+      uint4 acc = mine[i];
+      for (int r = 1; r < world; ++r) {
+        const int peer = (rank + r) % world;
+        acc = add8<FP16>(acc, (reinterpret_cast<const uint4*>(peer_ptrs[peer]) + base)[i]);
+      }
+      dst[i] = acc;
+    }
+  }
+  if (threadIdx.x == 0) counters[blockIdx.x] += 1;
+}
+
 }  // namespace oslo
+
+// `counters`: device uint32[>= 64], zero-initialised once, owned by this rank. `stage_off` / `half_bytes`: byte
+// offset of the two staging halves inside the symmetric buffer and the size of one half (n * 2 <= half_bytes).
+extern "C" int oslo_allreduce_oneshot(const void* in, void* out, void* const* peer_ptrs_dev, void* mc_ptr,
+                                      uint32_t* const* signal_ptrs_dev, uint32_t* counters, long long n,
+                                      long long stage_off, long long half_bytes, int rank, int world, int dtype,
+                                      int use_multimem, int* err_word, cudaStream_t stream) {
+  using namespace oslo;
+  if (n == 0) return 0;
+  if (n % 8 || stage_off % 16 || half_bytes % 16 || n * 2 > half_bytes) return -3;
+  if (world > 16) return -4;
+  const long long n16 = n / 8;
+  int max_blocks = 2048 / 4 / (2 * world);   // same signal-pad budget as the two-shot kernel
+  if (max_blocks > 64) max_blocks = 64;
+  long long want = (n16 + 511) / 512;
+  const int blocks = static_cast<int>(want < 1 ? 1 : (want > max_blocks ? max_blocks : want));
+  if (dtype == OSLO_DT_FP16)
+    allreduce_oneshot_kernel<true><<<blocks, 512, 0, stream>>>(in, out, peer_ptrs_dev, mc_ptr, signal_ptrs_dev, counters,
+                                                               n16, stage_off / 16, half_bytes / 16, rank, world,
+                                                               use_multimem, err_word);
+  else if (dtype == OSLO_DT_BF16)
+    allreduce_oneshot_kernel<false><<<blocks, 512, 0, stream>>>(in, out, peer_ptrs_dev, mc_ptr, signal_ptrs_dev, counters,
+                                                                n16, stage_off / 16, half_bytes / 16, rank, world,
+                                                                use_multimem, err_word);
+  else
+    return -2;
+  return static_cast<int>(cudaGetLastError());
+}
 
 extern "C" int oslo_allreduce_symm(void* const* peer_ptrs_dev, void* mc_ptr, uint32_t* const* signal_ptrs_dev,
                                    void* out, long long n, int rank, int world, int dtype, int use_multimem,

@@ -554,13 +554,14 @@ __global__ void __launch_bounds__(256) sumsq_kernel(const T* __restrict__ x, flo
 // out[r, c] = T(act(sum_s ws[s, r, c] + bias[c])): sums the k-slice planes of a split-K GEMM in a fixed order
 template <typename T>
 __global__ void splitk_finalize_kernel(const float* __restrict__ ws, const T* __restrict__ bias, T* __restrict__ out,
-                                       long long n, int cols, int split_k, int gelu) {
+                                       long long n, int cols, int split_k, int gelu_from) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     float v = 0.f;
     for (int s = 0; s < split_k; ++s) v += ws[s * n + i];
-    if (bias) v += Cvt<T>::to(bias[i % cols]);
-    if (gelu) v = gelu_f(v);
+    const int c = static_cast<int>(i % cols);
+    if (bias) v += Cvt<T>::to(bias[c]);
+    if (gelu_from >= 0 && c >= gelu_from) v = gelu_f(v);
     out[i] = Cvt<T>::from(v);
   }
 }
@@ -769,13 +770,13 @@ extern "C" int oslo_ngram_ban(const long long* tokens, float* lprobs, int rows, 
 }
 
 extern "C" int oslo_splitk_finalize(const float* ws, const void* bias, void* out, long long rows, int cols, int split_k,
-                                    int gelu, int dtype, cudaStream_t st) {
+                                    int gelu_from, int dtype, cudaStream_t st) {
   const long long n = rows * cols;
   if (n == 0) return 0;
   if (dtype == OSLO_DT_BF16)
-    splitk_finalize_kernel<__nv_bfloat16><<<grid_for(n, 256), 256, 0, st>>>(ws, (const __nv_bfloat16*)bias, (__nv_bfloat16*)out, n, cols, split_k, gelu);
+    splitk_finalize_kernel<__nv_bfloat16><<<grid_for(n, 256), 256, 0, st>>>(ws, (const __nv_bfloat16*)bias, (__nv_bfloat16*)out, n, cols, split_k, gelu_from);
   else if (dtype == OSLO_DT_FP16)
-    splitk_finalize_kernel<__half><<<grid_for(n, 256), 256, 0, st>>>(ws, (const __half*)bias, (__half*)out, n, cols, split_k, gelu);
+    splitk_finalize_kernel<__half><<<grid_for(n, 256), 256, 0, st>>>(ws, (const __half*)bias, (__half*)out, n, cols, split_k, gelu_from);
   else
     return -2;
   RET_LAST();

@@ -32,9 +32,10 @@ int oslo_gemm_split_k_for(int M, int N, int K, int num_sms);
 int oslo_gemm_splitk_16bit(const void* A, const void* B, float* D, int M, int N, int K, int lda, int ldb, int ldd,
                            int a_mn_major, int b_mn_major, int fp16, int split_k, int* err_word, int num_sms,
                            cudaStream_t stream);
-// out = T(act(sum over planes of ws + bias)) for the [split_k, rows, cols] fp32 result of the split-K GEMM
-int oslo_splitk_finalize(const float* ws, const void* bias, void* out, long long rows, int cols, int split_k, int gelu,
-                         int dtype, cudaStream_t stream);
+// out = T(act(sum over planes of ws + bias)) for the [split_k, rows, cols] fp32 result of the split-K GEMM;
+// tanh-GeLU on columns >= gelu_from (-1 = none)
+int oslo_splitk_finalize(const float* ws, const void* bias, void* out, long long rows, int cols, int split_k,
+                         int gelu_from, int dtype, cudaStream_t stream);
 
 // LayerNorm over the last dim of [rows, cols]; mean/rstd are fp32 [rows]
 int oslo_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int rows,
@@ -128,6 +129,12 @@ int oslo_gemm_comm_16bit(const void* A, const void* B, int M, int N, int K, int 
 int oslo_allreduce_symm(void* const* peer_ptrs_dev, void* mc_ptr, uint32_t* const* signal_ptrs_dev, void* out,
                         long long n, int rank, int world, int dtype, int use_multimem, int* err_word,
                         cudaStream_t stream);
+
+// one-kernel all-reduce for small tensors (comm.cu): in -> staging half in symmetric memory -> sum over ranks -> out
+int oslo_allreduce_oneshot(const void* in, void* out, void* const* peer_ptrs_dev, void* mc_ptr,
+                           uint32_t* const* signal_ptrs_dev, uint32_t* counters, long long n, long long stage_off,
+                           long long half_bytes, int rank, int world, int dtype, int use_multimem, int* err_word,
+                           cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -38,6 +38,13 @@ class GraphedGreedyDecoder:
         self.record_events = False   # when set, `events` holds (start, after prefill, end) CUDA events of the last call
         self.events = None
 
+    def release(self) -> None:
+        """Drop the captured graph and the cache. Call this before the process group is destroyed: a communicator
+        that is still referenced by a captured graph does not shut down."""
+        self.graph = None
+        self.cache = None
+        self._batch = None
+
     # ------------------------------------------------------------------ one decode step, positions on the device
     def _step(self) -> None:
         cache = self.cache

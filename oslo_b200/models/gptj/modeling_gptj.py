@@ -56,12 +56,16 @@ class GPTJAttention(AttentionCore):
         self.out_proj = Linear(self.embed_dim, self.embed_dim, bias=False)
 
     def forward(self, hidden_states: Tensor, layer_past=None, attention_mask=None, position_ids=None,
-                head_mask=None, use_cache=False, output_attentions=False, cache=None, layer_id=0, seq_shape=None):
+                head_mask=None, use_cache=False, output_attentions=False, cache=None, layer_id=0, seq_shape=None,
+                qkv=None):
         b, s = seq_shape if seq_shape is not None else hidden_states.shape[:2]
         nh, hd = self.num_attention_heads, self.head_dim
-        q = self.q_proj(hidden_states).view(b, s, nh, hd)
-        k = self.k_proj(hidden_states).view(b, s, nh, hd)
-        v = self.v_proj(hidden_states).view(b, s, nh, hd)
+        if qkv is not None:   # already projected by the block's packed decode GEMM
+            q, k, v = (t.reshape(b, s, nh, hd) for t in qkv)
+        else:
+            q = self.q_proj(hidden_states).view(b, s, nh, hd)
+            k = self.k_proj(hidden_states).view(b, s, nh, hd)
+            v = self.v_proj(hidden_states).view(b, s, nh, hd)
         rd = self.rotary_dim if self.rotary_dim is not None else hd
         rot = ops.rotary_interleaved if self.fused else ops.reference.rotary_interleaved
         q, k = rot(q, position_ids, rd), rot(k, position_ids, rd)
@@ -86,8 +90,10 @@ class GPTJMLP(nn.Module):
         self.activation = config.activation_function
         self.resid_pdrop = config.resid_pdrop
 
-    def forward(self, x: Tensor) -> Tensor:
-        if self.fused and self.activation in GELU_TANH_NAMES:
+    def forward(self, x: Tensor, h: Optional[Tensor] = None) -> Tensor:
+        if h is not None:     # fc_in + GeLU already done by the block's packed decode GEMM
+            pass
+        elif self.fused and self.activation in GELU_TANH_NAMES:
             h = self.fc_in(x, activation="gelu_new")
         else:
             h = ACT2FN[self.activation](self.fc_in(x))
@@ -106,10 +112,43 @@ class GPTJBlock(nn.Module):
         self.attn = GPTJAttention(config)
         self.mlp = GPTJMLP(inner, config)
 
+    def _packed_decode_projections(self, x: Tensor):
+        """Decode steps (few rows, no grad, fused kernels): q, k, v and fc_in + GeLU read the same LayerNorm output,
+        so they run as ONE weight-streaming GEMM over a packed copy of the four weights (rebuilt when any of them
+        changes). Returns ``(q, k, v, h)`` or ``None`` when the ordinary per-layer path applies."""
+        from ...config import get_config
+        from ...ops import cuda_ops
+        attn, mlp = self.attn, self.mlp
+        layers = (attn.q_proj, attn.k_proj, attn.v_proj, mlp.fc_in)
+        if not (attn.fused and mlp.fused and mlp.activation in GELU_TANH_NAMES and get_config().packed_decode):
+            return None
+        if any(getattr(l, "reversed", False) or not getattr(l, "oslo_fused", False) or getattr(l, "gather_output", False)
+               or getattr(l, "sequence_parallel", False) for l in layers):
+            return None
+        ws = [l.weight for l in layers]
+        if any(l.bias is not None for l in layers[:3]) or not cuda_ops.small_m_ok(x, *ws):
+            return None
+        key = tuple((w.data_ptr(), w._version) for w in ws) + ((mlp.fc_in.bias.data_ptr(), mlp.fc_in.bias._version)
+                                                               if mlp.fc_in.bias is not None else ())
+        if getattr(self, "_packed_key", None) != key:
+            n_qkv = sum(w.size(0) for w in ws[:3])
+            self._packed_w = torch.cat([w.detach() for w in ws], dim=0).contiguous()
+            fb = mlp.fc_in.bias
+            self._packed_b = (torch.cat([fb.new_zeros(n_qkv), fb.detach()]) if fb is not None else None)
+            self._packed_key = key
+            self._packed_sizes = [w.size(0) for w in ws]
+        y = cuda_ops.packed_linear_small_m(x, self._packed_w, self._packed_b, sum(self._packed_sizes[:3]))
+        return torch.split(y, self._packed_sizes, dim=-1)
+
     def forward(self, hidden_states: Tensor, **kw):
         x = self.ln_1(hidden_states)
-        a, present, probs = self.attn(x, **kw)
-        m = self.mlp(x)
+        packed = self._packed_decode_projections(x) if x.is_cuda else None
+        if packed is not None:
+            a, present, probs = self.attn(x, qkv=packed[:3], **kw)
+            m = self.mlp(x, h=packed[3])
+        else:
+            a, present, probs = self.attn(x, **kw)
+            m = self.mlp(x)
         return a + m + hidden_states, present, probs
 
 

@@ -115,9 +115,26 @@ def linear(x: Tensor, weight: Tensor, bias: Optional[Tensor], reversed_: bool, a
     if rows <= SMALL_M_ROWS and not (torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)):
         # decode steps: weight-streaming split-K GEMM so that every SM pulls weights, not just N / 128 of them
         y = _ext().gemm_small_m(_as_operand(x.reshape(rows, x.size(-1))), _as_operand(weight), int(reversed_), bias,
-                                activation is not None)
+                                0 if activation is not None else -1)
         return y.view(*x.shape[:-1], n)
     return _Linear.apply(x, weight, bias, reversed_, activation is not None)
+
+
+def small_m_ok(x: Tensor, *weights: Tensor) -> bool:
+    """Whether an inference call with input ``x`` takes the few-row (decode) GEMM path."""
+    if torch.is_grad_enabled() and (x.requires_grad or any(w.requires_grad for w in weights)):
+        return False
+    rows = x.numel() // max(x.size(-1), 1)
+    return (x.is_cuda and x.dtype in _16BIT and 0 < rows <= SMALL_M_ROWS and x.size(-1) % 8 == 0
+            and all(w.dtype == x.dtype and w.size(0) % 8 == 0 for w in weights))
+
+
+def packed_linear_small_m(x: Tensor, weight: Tensor, bias: Optional[Tensor], gelu_from: int) -> Tensor:
+    """``x @ weight^T + bias`` for a few rows with tanh-GeLU on output columns ``>= gelu_from`` (-1: none);
+    ``weight`` is the row-wise concatenation of several ``[out_i, in]`` layers that share the input."""
+    rows = x.numel() // x.size(-1)
+    y = _ext().gemm_small_m(_as_operand(x.reshape(rows, x.size(-1))), _as_operand(weight), 0, bias, int(gelu_from))
+    return y.view(*x.shape[:-1], weight.size(0))
 
 
 class _LayerNorm(torch.autograd.Function):

@@ -20,6 +20,7 @@ from .. import ops
 from ..config import get_config
 
 _WORKSPACES: Dict[str, "SymmetricWorkspace"] = {}
+ONESHOT_HALF = 1 << 20   # bytes per staging half of the one-kernel all-reduce
 
 
 class SymmetricWorkspace:
@@ -40,6 +41,11 @@ class SymmetricWorkspace:
         except Exception:
             self.mc_ptr = 0
         self.buf.zero_()
+        # the last two ONESHOT_HALF-sized pieces of the buffer are the alternating staging halves of the
+        # one-kernel all-reduce for small tensors; `oneshot_counters` holds their per-block parity on the device
+        self.oneshot_half = ONESHOT_HALF if self.numel * 2 >= 4 * ONESHOT_HALF else 0
+        self.oneshot_off = self.numel * 2 - 2 * self.oneshot_half
+        self.oneshot_counters = torch.zeros(64, dtype=torch.int32, device=self.device)
         self.handle.barrier()
 
     @property
@@ -60,6 +66,13 @@ class SymmetricWorkspace:
         if use_multimem is None:
             use_multimem = get_config().use_multimem
         use_multimem = bool(use_multimem) and self.has_multicast
+        if self.oneshot_half and n * 2 <= self.oneshot_half and x.is_contiguous():
+            ops.load_ext(required=True).allreduce_oneshot(x, self.peer_ptrs_dev, self.mc_ptr, self.signal_ptrs_dev,
+                                                         self.oneshot_counters, self.oneshot_off, self.oneshot_half,
+                                                         self.rank, self.world, use_multimem)
+            return x
+        if n * 2 > self.oneshot_off:
+            raise ValueError("tensor does not fit the symmetric workspace")
         stage = self.view(n, x.dtype)
         flat = x.reshape(-1)
         stage.copy_(flat)

@@ -370,3 +370,23 @@ def test_small_m_linear(M, N, K, rev):
     _close(y, ops.reference.gelu_tanh(ref + b.float()), atol=0.03)
     assert torch.equal(y, y2)
     assert co.device_error_code(y) == 0
+
+
+def test_packed_decode_projection_matches_per_layer_path():
+    """GPT-J decode step: the packed q/k/v/fc_in GEMM gives the logits of the per-layer path."""
+    import oslo_b200 as ob
+    from oslo_b200.config import set_config
+    torch.manual_seed(0)
+    cfg = ob.GPTJConfig(vocab_size=1024, n_positions=256, n_embd=256, n_layer=2, n_head=4, rotary_dim=16)
+    model = ob.GPTJForCausalLM(cfg).to(torch.bfloat16).cuda().fuse().eval()
+    ids = torch.randint(0, 1024, (3, 1), device="cuda")
+    outs = []
+    try:
+        for flag in (True, False):
+            set_config(packed_decode=flag)
+            with torch.no_grad():
+                outs.append(model(input_ids=ids, use_cache=False).logits.float())
+    finally:
+        set_config(packed_decode=True)
+    assert getattr(model.transformer.h[0], "_packed_w", None) is not None
+    _close(outs[0], outs[1], atol=2e-2)

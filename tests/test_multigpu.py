@@ -123,6 +123,27 @@ def _symm_allreduce(rank, world):
                 ws.all_reduce_(y, use_multimem=mm)
             torch.cuda.synchronize()
             assert torch.allclose(y.float(), want, atol=0.05, rtol=0.02), (n, mm, (y.float() - want).abs().max())
+    # the one-kernel path keeps its buffer parity on the device: replaying a captured call an odd number of times
+    # must stay correct
+    x = torch.randn(4096, device="cuda").to(torch.bfloat16)
+    want = x.clone().float()
+    dist.all_reduce(want, group=mpu.get_tensor_parallel_group())
+    y = torch.empty_like(x)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        y.copy_(x)
+        ws.all_reduce_(y)
+    torch.cuda.current_stream().wait_stream(side)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        y.copy_(x)
+        ws.all_reduce_(y)
+    for _ in range(5):
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.allclose(y.float(), want, atol=0.05, rtol=0.02)
+    del g
     assert int(ob.ops.load_ext().error_word(x).item()) == 0
 
 
