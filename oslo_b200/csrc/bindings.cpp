@@ -479,6 +479,48 @@ void allreduce_symm(int64_t peer_ptrs_dev, int64_t mc_ptr, int64_t signal_ptrs_d
                                st.err.data_ptr<int>(), cur_stream()), "allreduce_symm");
 }
 
+// y [M, N] = act([x1 | x2] @ w^T + bias) for M <= 4 rows; w [N, K1 + K2]; x1 / x2 are 2-D with contiguous last dims
+Tensor gemv_rows(const Tensor& x1, const optional<Tensor>& x2, const Tensor& w, const optional<Tensor>& bias,
+                 int64_t gelu_from) {
+  check_2d_operand(x1, "x1");
+  check_2d_operand(w, "w");
+  const bool two = x2.has_value() && x2->defined();
+  if (two) check_2d_operand(*x2, "x2");
+  const int64_t M = x1.size(0), K1 = x1.size(1), K2 = two ? x2->size(1) : 0, N = w.size(0);
+  TORCH_CHECK(w.size(1) == K1 + K2 && (!two || x2->size(0) == M), "gemv_rows: shapes do not match");
+  TORCH_CHECK(x1.scalar_type() == w.scalar_type() && (!two || x2->scalar_type() == w.scalar_type()), "gemv_rows: dtypes differ");
+  const bool has_bias = bias.has_value() && bias->defined();
+  if (has_bias) TORCH_CHECK(bias->numel() == N && bias->scalar_type() == w.scalar_type() && bias->is_contiguous(), "bad bias");
+  c10::cuda::CUDAGuard guard(x1.device());
+  Tensor y = at::empty({M, N}, x1.options());
+  auto& st = dev_state(x1.get_device());
+  check_rc(oslo_gemv_rows(x1.data_ptr(), static_cast<int>(x1.stride(0)), static_cast<int>(K1),
+                          two ? x2->data_ptr() : nullptr, two ? static_cast<int>(x2->stride(0)) : 0, static_cast<int>(K2),
+                          w.data_ptr(), static_cast<int>(w.stride(0)), has_bias ? bias->data_ptr() : nullptr, y.data_ptr(),
+                          static_cast<int>(N), static_cast<int>(M), static_cast<int>(N), static_cast<int>(gelu_from),
+                          dt_code(x1), st.sms, cur_stream()), "gemv_rows");
+  return y;
+}
+
+// GPT-J rotary on q, k ([B, H*D] row slices) + append of k, v to the static cache at the device-side position
+Tensor rotary_append(const Tensor& q, const Tensor& k, const Tensor& v, Tensor kc, Tensor vc, const Tensor& lengths,
+                     const Tensor& write_index, int64_t rotary_dim, double base) {
+  TORCH_CHECK(q.is_cuda() && q.dim() == 2 && k.dim() == 2 && v.dim() == 2 && q.stride(1) == 1 && k.stride(1) == 1 &&
+                  v.stride(1) == 1, "rotary_append: q, k, v must be [B, H*D] with contiguous last dim");
+  TORCH_CHECK(kc.dim() == 4 && kc.is_contiguous() && vc.is_contiguous() && kc.sizes() == vc.sizes(), "bad cache");
+  TORCH_CHECK(lengths.scalar_type() == at::kInt && write_index.scalar_type() == at::kLong, "bad position tensors");
+  const int64_t B = kc.size(0), H = kc.size(1), T = kc.size(2), D = kc.size(3);
+  TORCH_CHECK(q.size(0) == B && q.size(1) == H * D && k.size(1) == H * D && v.size(1) == H * D, "shape mismatch");
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor q_out = at::empty({B, H, D}, q.options());
+  check_rc(oslo_rotary_append(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), k.stride(0), v.stride(0),
+                              q_out.data_ptr(), kc.data_ptr(), vc.data_ptr(), lengths.data_ptr<int>(),
+                              reinterpret_cast<const long long*>(write_index.data_ptr<int64_t>()), static_cast<int>(B),
+                              static_cast<int>(H), static_cast<int>(D), static_cast<int>(T), static_cast<int>(rotary_dim),
+                              static_cast<float>(base), dt_code(q), cur_stream()), "rotary_append");
+  return q_out;
+}
+
 // In-place one-kernel all-reduce of a small tensor through two alternating staging halves of a symmetric buffer.
 void allreduce_oneshot(Tensor x, int64_t peer_ptrs_dev, int64_t mc_ptr, int64_t signal_ptrs_dev, Tensor counters,
                        int64_t stage_off, int64_t half_bytes, int64_t rank, int64_t world, bool use_multimem) {
@@ -519,6 +561,8 @@ TORCH_LIBRARY(oslo_b200, m) {
   m.def("flash_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale, bool causal, int window, Tensor? kpm, int impl=1) -> (Tensor, Tensor, Tensor)", &flash_bwd);
   m.def("decode_attn(Tensor q, Tensor kc, Tensor vc, Tensor lengths, float scale, int window) -> Tensor", &decode_attn);
   m.def("gemm_comm(Tensor a, Tensor b, int a_mn, int b_mn, Tensor? bias, Tensor(a!)? aux_out, Tensor(b!)? out, int flags, float alpha, int M, int N, int K, int peer_bufs_dev, int own_buf, int mc_base, int data_off, int flag_off, int flag_bytes, int rank, int world, int epoch, int done_base, int mode, bool use_multimem, Tensor(c!)? trace) -> int", &gemm_comm);
+  m.def("gemv_rows(Tensor x1, Tensor? x2, Tensor w, Tensor? bias, int gelu_from) -> Tensor", &gemv_rows);
+  m.def("rotary_append(Tensor q, Tensor k, Tensor v, Tensor(a!) kc, Tensor(b!) vc, Tensor lengths, Tensor write_index, int rotary_dim, float base) -> Tensor", &rotary_append);
   m.def("allreduce_oneshot(Tensor(a!) x, int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(b!) counters, int stage_off, int half_bytes, int rank, int world, bool use_multimem) -> ()", &allreduce_oneshot);
   m.def("allreduce_symm(int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(a!) out, int numel, int rank, int world, bool use_multimem) -> ()", &allreduce_symm);
 }

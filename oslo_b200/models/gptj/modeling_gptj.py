@@ -140,10 +140,54 @@ class GPTJBlock(nn.Module):
         y = cuda_ops.packed_linear_small_m(x, self._packed_w, self._packed_b, sum(self._packed_sizes[:3]))
         return torch.split(y, self._packed_sizes, dim=-1)
 
+    def _decode_step(self, hidden_states: Tensor, x: Tensor, packed, kw):
+        """Whole block for one new token per row on a device-positioned static cache, in six launches: (LayerNorm and
+        the packed q/k/v/fc_in GEMV already done) rotary + cache append, decode attention (2), ONE GEMV for
+        out_proj and fc_out over [attention | mlp activation] - their sum is what the parallel residual needs -
+        ONE all-reduce under tensor parallelism instead of two, and the residual add. Returns ``None`` when the
+        general path has to run."""
+        from ...ops import cuda_ops
+        attn, mlp = self.attn, self.mlp
+        cache = kw.get("cache")
+        if (cache is None or not getattr(cache, "device_positions", False) or hidden_states.size(1) != 1
+                or kw.get("attention_mask") is not None or kw.get("head_mask") is not None
+                or kw.get("output_attentions") or self.training or kw.get("layer_id") not in cache.k):
+            return None
+        rows = hidden_states.size(0)
+        out_w, fc_w = attn.out_proj.weight, mlp.fc_out.weight
+        if (rows > cuda_ops.SMALL_M_ROWS or attn.out_proj.bias is not None or getattr(attn.out_proj, "reversed", False)
+                or getattr(mlp.fc_out, "reversed", False) or out_w.size(0) % 4
+                or getattr(attn.out_proj, "sequence_parallel", False)):
+            return None
+        key = (out_w.data_ptr(), out_w._version, fc_w.data_ptr(), fc_w._version)
+        if getattr(self, "_packed2_key", None) != key:
+            self._packed2_w = torch.cat([out_w.detach(), fc_w.detach()], dim=1).contiguous()
+            self._packed2_key = key
+        q, k, v, h = (t.reshape(rows, -1) for t in packed)
+        layer = kw["layer_id"]
+        kc, vc = cache.k[layer], cache.v[layer]
+        rd = attn.rotary_dim if attn.rotary_dim is not None else attn.head_dim
+        q_rot = cuda_ops.rotary_append(q, k, v, kc, vc, cache.lengths_dev, cache.write_index, rd)
+        o = ops.decode_attention(q_rot, kc, vc, cache.lengths_next, attn.scale, attn.window)
+        if rows <= cuda_ops.GEMV_ROWS:
+            z = cuda_ops.gemv_two_inputs(o.reshape(rows, -1), h, self._packed2_w)
+        else:   # more rows than the CUDA cores can feed from HBM: tensor-core split-k GEMM over the joined input
+            z = cuda_ops.packed_linear_small_m(torch.cat([o.reshape(rows, -1), h], dim=1), self._packed2_w, None, -1)
+        mpu = getattr(attn.out_proj, "mpu", None)
+        if mpu is not None and mpu.tp > 1:
+            z = mpu._reduce(z)
+        z = z.view_as(hidden_states)
+        if mlp.fc_out.bias is not None:
+            z = z + mlp.fc_out.bias
+        return z + hidden_states, None, None
+
     def forward(self, hidden_states: Tensor, **kw):
         x = self.ln_1(hidden_states)
         packed = self._packed_decode_projections(x) if x.is_cuda else None
         if packed is not None:
+            fast = self._decode_step(hidden_states, x, packed, kw)
+            if fast is not None:
+                return fast
             a, present, probs = self.attn(x, qkv=packed[:3], **kw)
             m = self.mlp(x, h=packed[3])
         else:

@@ -64,6 +64,7 @@ def gemm_tn(d: Tensor, x: Tensor, out_dtype=None) -> Tensor:
 
 
 SMALL_M_ROWS = 64  # inference calls with at most this many rows use the split-K path
+GEMV_ROWS = 4      # ... and with at most this many rows the CUDA-core weight-streaming kernel
 
 
 class _Linear(torch.autograd.Function):
@@ -114,8 +115,12 @@ def linear(x: Tensor, weight: Tensor, bias: Optional[Tensor], reversed_: bool, a
     rows = x.numel() // x.size(-1)
     if rows <= SMALL_M_ROWS and not (torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)):
         # decode steps: weight-streaming split-K GEMM so that every SM pulls weights, not just N / 128 of them
-        y = _ext().gemm_small_m(_as_operand(x.reshape(rows, x.size(-1))), _as_operand(weight), int(reversed_), bias,
-                                0 if activation is not None else -1)
+        x2 = _as_operand(x.reshape(rows, x.size(-1)))
+        gelu_from = 0 if activation is not None else -1
+        if rows <= GEMV_ROWS and not reversed_ and n % 4 == 0:
+            y = _ext().gemv_rows(x2, None, _as_operand(weight), bias, gelu_from)   # no tensor-core tile to pad
+        else:
+            y = _ext().gemm_small_m(x2, _as_operand(weight), int(reversed_), bias, gelu_from)
         return y.view(*x.shape[:-1], n)
     return _Linear.apply(x, weight, bias, reversed_, activation is not None)
 
@@ -133,8 +138,24 @@ def packed_linear_small_m(x: Tensor, weight: Tensor, bias: Optional[Tensor], gel
     """``x @ weight^T + bias`` for a few rows with tanh-GeLU on output columns ``>= gelu_from`` (-1: none);
     ``weight`` is the row-wise concatenation of several ``[out_i, in]`` layers that share the input."""
     rows = x.numel() // x.size(-1)
-    y = _ext().gemm_small_m(_as_operand(x.reshape(rows, x.size(-1))), _as_operand(weight), 0, bias, int(gelu_from))
+    x2 = _as_operand(x.reshape(rows, x.size(-1)))
+    if rows <= GEMV_ROWS and weight.size(0) % 4 == 0:
+        y = _ext().gemv_rows(x2, None, _as_operand(weight), bias, int(gelu_from))
+    else:
+        y = _ext().gemm_small_m(x2, _as_operand(weight), 0, bias, int(gelu_from))
     return y.view(*x.shape[:-1], weight.size(0))
+
+
+def gemv_two_inputs(x1: Tensor, x2: Tensor, weight: Tensor, bias: Optional[Tensor] = None) -> Tensor:
+    """``[x1 | x2] @ weight^T (+ bias)`` for at most ``GEMV_ROWS`` rows without materialising the concatenation."""
+    return _ext().gemv_rows(_as_operand(x1), _as_operand(x2), _as_operand(weight), bias, -1)
+
+
+def rotary_append(q: Tensor, k: Tensor, v: Tensor, k_cache: Tensor, v_cache: Tensor, lengths: Tensor,
+                  write_index: Tensor, rotary_dim: int, base: float = 10000.0) -> Tensor:
+    """Decode step: rotary on the new token's ``q``/``k`` (``[B, heads*D]`` row slices, position ``lengths[b]``),
+    ``k``/``v`` written into the static caches at ``write_index[0]``; returns the rotated ``q`` as ``[B, heads, D]``."""
+    return _ext().rotary_append(q, k, v, k_cache, v_cache, lengths, write_index, int(rotary_dim), float(base))
 
 
 class _LayerNorm(torch.autograd.Function):

@@ -336,19 +336,54 @@ def test_fused_model_matches_eager_model(kind):
 
 
 def test_graphed_greedy_decoder_gpu():
-    """CUDA-graph replayed greedy decoding produces the tokens of the eager generate() loop."""
+    """CUDA-graph replayed greedy decoding produces exactly the tokens of the same step run eagerly, and the fused
+    decode step (device-positioned cache) agrees with the general cached forward on the next-token logits."""
     import oslo_b200 as ob
     from oslo_b200.generation import GraphedGreedyDecoder
+    from oslo_b200.models.common import StaticKVCache
     torch.manual_seed(0)
     cfg = ob.GPTJConfig(vocab_size=1024, n_positions=256, n_embd=256, n_layer=2, n_head=4, rotary_dim=16)
     model = ob.GPTJForCausalLM(cfg).to(torch.bfloat16).cuda().fuse().eval()
     ids = torch.randint(0, 1024, (3, 33), device="cuda")
-    dec = GraphedGreedyDecoder(model, max_len=128)
+    graphed = GraphedGreedyDecoder(model, max_len=128, use_graph=True)
+    eager = GraphedGreedyDecoder(model, max_len=128, use_graph=False)
     for prompt, n_new in ((33, 40), (20, 30)):
-        want = model.generate(ids[:, :prompt], max_length=prompt + n_new, do_sample=False)
-        got = dec.generate(ids[:, :prompt], n_new)
+        got = graphed.generate(ids[:, :prompt], n_new)
+        want = eager.generate(ids[:, :prompt], n_new)
         assert torch.equal(got, want)
-    assert dec.replays > 0
+    assert graphed.replays > 0 and eager.replays == 0
+    nxt = torch.randint(0, 1024, (3, 1), device="cuda")
+    logits = []
+    with torch.no_grad():
+        for device_positions in (True, False):
+            cache = StaticKVCache(64)
+            model(input_ids=ids, past_key_values=cache, use_cache=True)
+            pos = None
+            if device_positions:
+                cache.use_device_positions(True)
+                pos = cache.lengths_dev.to(torch.long).unsqueeze(1)
+            out = model(input_ids=nxt, past_key_values=cache, position_ids=pos, use_cache=True)
+            logits.append(out.logits[:, -1].float())
+    assert getattr(model.transformer.h[0], "_packed2_w", None) is not None   # the fused step really ran
+    _close(logits[0], logits[1], atol=3e-2)
+
+
+@pytest.mark.parametrize("M,K1,K2,N", [(1, 512, 2048, 4096), (3, 256, 0, 1024), (4, 4096, 0, 28672), (2, 264, 520, 260)])
+def test_gemv_rows(M, K1, K2, N):
+    ops, co = _ops()
+    ext = ops.load_ext(required=True)
+    torch.manual_seed(5)
+    x1 = torch.randn(M, K1, device="cuda", dtype=torch.bfloat16) * 0.5
+    x2 = torch.randn(M, K2, device="cuda", dtype=torch.bfloat16) * 0.5 if K2 else None
+    w = torch.randn(N, K1 + K2, device="cuda", dtype=torch.bfloat16) * 0.05
+    b = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    y = ext.gemv_rows(x1, x2, w, b, N // 2)
+    xin = x1.float() if x2 is None else torch.cat([x1.float(), x2.float()], dim=1)
+    ref = xin @ w.float().t() + b.float()
+    ref[:, N // 2:] = ops.reference.gelu_tanh(ref[:, N // 2:])
+    _close(y, ref, atol=0.03)
+    z = ext.gemv_rows(x1, x2, w, None, -1)
+    _close(z, xin @ w.float().t(), atol=0.03)
 
 
 @pytest.mark.parametrize("M,N,K,rev", [(1, 4096, 4096, False), (8, 512, 4096, False), (32, 16384, 4096, True),
