@@ -481,7 +481,7 @@ void allreduce_symm(int64_t peer_ptrs_dev, int64_t mc_ptr, int64_t signal_ptrs_d
 
 // y [M, N] = act([x1 | x2] @ w^T + bias) for M <= 4 rows; w [N, K1 + K2]; x1 / x2 are 2-D with contiguous last dims
 Tensor gemv_rows(const Tensor& x1, const optional<Tensor>& x2, const Tensor& w, const optional<Tensor>& bias,
-                 int64_t gelu_from) {
+                 int64_t gelu_from, const optional<Tensor>& res) {
   check_2d_operand(x1, "x1");
   check_2d_operand(w, "w");
   const bool two = x2.has_value() && x2->defined();
@@ -491,12 +491,17 @@ Tensor gemv_rows(const Tensor& x1, const optional<Tensor>& x2, const Tensor& w, 
   TORCH_CHECK(x1.scalar_type() == w.scalar_type() && (!two || x2->scalar_type() == w.scalar_type()), "gemv_rows: dtypes differ");
   const bool has_bias = bias.has_value() && bias->defined();
   if (has_bias) TORCH_CHECK(bias->numel() == N && bias->scalar_type() == w.scalar_type() && bias->is_contiguous(), "bad bias");
+  const bool has_res = res.has_value() && res->defined();
+  if (has_res)
+    TORCH_CHECK(res->dim() == 2 && res->size(0) == M && res->size(1) == N && res->stride(1) == 1 &&
+                    res->scalar_type() == w.scalar_type(), "bad residual");
   c10::cuda::CUDAGuard guard(x1.device());
   Tensor y = at::empty({M, N}, x1.options());
   auto& st = dev_state(x1.get_device());
   check_rc(oslo_gemv_rows(x1.data_ptr(), static_cast<int>(x1.stride(0)), static_cast<int>(K1),
                           two ? x2->data_ptr() : nullptr, two ? static_cast<int>(x2->stride(0)) : 0, static_cast<int>(K2),
-                          w.data_ptr(), static_cast<int>(w.stride(0)), has_bias ? bias->data_ptr() : nullptr, y.data_ptr(),
+                          w.data_ptr(), static_cast<int>(w.stride(0)), has_bias ? bias->data_ptr() : nullptr,
+                          has_res ? res->data_ptr() : nullptr, has_res ? static_cast<int>(res->stride(0)) : 0, y.data_ptr(),
                           static_cast<int>(N), static_cast<int>(M), static_cast<int>(N), static_cast<int>(gelu_from),
                           dt_code(x1), st.sms, cur_stream()), "gemv_rows");
   return y;
@@ -561,7 +566,7 @@ TORCH_LIBRARY(oslo_b200, m) {
   m.def("flash_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale, bool causal, int window, Tensor? kpm, int impl=1) -> (Tensor, Tensor, Tensor)", &flash_bwd);
   m.def("decode_attn(Tensor q, Tensor kc, Tensor vc, Tensor lengths, float scale, int window) -> Tensor", &decode_attn);
   m.def("gemm_comm(Tensor a, Tensor b, int a_mn, int b_mn, Tensor? bias, Tensor(a!)? aux_out, Tensor(b!)? out, int flags, float alpha, int M, int N, int K, int peer_bufs_dev, int own_buf, int mc_base, int data_off, int flag_off, int flag_bytes, int rank, int world, int epoch, int done_base, int mode, bool use_multimem, Tensor(c!)? trace) -> int", &gemm_comm);
-  m.def("gemv_rows(Tensor x1, Tensor? x2, Tensor w, Tensor? bias, int gelu_from) -> Tensor", &gemv_rows);
+  m.def("gemv_rows(Tensor x1, Tensor? x2, Tensor w, Tensor? bias, int gelu_from, Tensor? res=None) -> Tensor", &gemv_rows);
   m.def("rotary_append(Tensor q, Tensor k, Tensor v, Tensor(a!) kc, Tensor(b!) vc, Tensor lengths, Tensor write_index, int rotary_dim, float base) -> Tensor", &rotary_append);
   m.def("allreduce_oneshot(Tensor(a!) x, int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(b!) counters, int stage_off, int half_bytes, int rank, int world, bool use_multimem) -> ()", &allreduce_oneshot);
   m.def("allreduce_symm(int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(a!) out, int numel, int rank, int world, bool use_multimem) -> ()", &allreduce_symm);

@@ -2,7 +2,7 @@
 // weights and the KV cache stream out of HBM and by launch count, not by math, so the kernels are plain
 // wide-load CUDA-core code with as many 16-byte loads in flight as the register file allows, and they fuse what
 // the eager path runs as separate launches:
-//   * gemv_rows_kernel: y[m, n] = act(sum_k [x1 | x2][m, k] * W[n, k] + bias[n]) for m <= 4 (beyond that the CUDA
+//   * gemv_rows_kernel: y[m, n] = act(sum_k [x1 | x2][m, k] * W[n, k] + bias[n]) + res[m, n] for m <= 4 (beyond that the CUDA
 //     cores cannot keep up with HBM and the tensor-core split-k path takes over). One block owns four output
 //     columns and the whole k range, so there is no second pass; the input may come in two pieces
 //     (attention output and MLP activation feeding the merged out_proj / fc_out product of a parallel block).
@@ -91,8 +91,9 @@ template <typename T, int MR>
 __global__ void __launch_bounds__(GV_THREADS) gemv_rows_kernel(const T* __restrict__ x1, int ld1, int K1,
                                                                const T* __restrict__ x2, int ld2, int K2,
                                                                const T* __restrict__ W, int ldw,
-                                                               const T* __restrict__ bias, T* __restrict__ out, int ldo,
-                                                               int N, int m_valid, int gelu_from) {
+                                                               const T* __restrict__ bias,
+                                                               const T* __restrict__ res, int ldr, T* __restrict__ out,
+                                                               int ldo, int N, int m_valid, int gelu_from) {
   __shared__ float red[GV_THREADS / 32][GV_COLS * MR];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int k_begin = threadIdx.x * 8, k_step = GV_THREADS * 8;
@@ -124,6 +125,7 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_rows_kernel(const T* __restri
         const int n = n0 + c;
         if (bias) v += DCvt<T>::to(bias[n]);
         if (gelu_from >= 0 && n >= gelu_from) v = gelu_tanh_dec(v);
+        if (res) v += DCvt<T>::to(res[static_cast<size_t>(m) * ldr + n]);
         out[static_cast<size_t>(m) * ldo + n] = DCvt<T>::from(v);
       }
     }
@@ -170,13 +172,14 @@ __global__ void rotary_append_kernel(const T* __restrict__ q, const T* __restric
 
 template <typename T>
 static int gemv_launch(const void* x1, int ld1, int K1, const void* x2, int ld2, int K2, const void* W, int ldw,
-                       const void* bias, void* out, int ldo, int M, int N, int gelu_from, int num_sms, cudaStream_t st) {
+                       const void* bias, const void* res, int ldr, void* out, int ldo, int M, int N, int gelu_from,
+                       int num_sms, cudaStream_t st) {
   int blocks = N / GV_COLS;                   // one block per column group, at most 8 resident blocks per SM's worth
   if (blocks > num_sms * 8) blocks = num_sms * 8;
   if (blocks < 1) blocks = 1;
 #define GV_CASE(MR)                                                                                               \
   gemv_rows_kernel<T, MR><<<blocks, GV_THREADS, 0, st>>>((const T*)x1, ld1, K1, (const T*)x2, ld2, K2, (const T*)W, ldw, \
-                                                         (const T*)bias, (T*)out, ldo, N, M, gelu_from)
+                                                         (const T*)bias, (const T*)res, ldr, (T*)out, ldo, N, M, gelu_from)
   if (M <= 1) GV_CASE(1);
   else if (M <= 2) GV_CASE(2);
   else GV_CASE(4);
@@ -187,8 +190,8 @@ static int gemv_launch(const void* x1, int ld1, int K1, const void* x2, int ld2,
 }  // namespace oslo
 
 extern "C" int oslo_gemv_rows(const void* x1, int ld1, int K1, const void* x2, int ld2, int K2, const void* W, int ldw,
-                              const void* bias, void* out, int ldo, int M, int N, int gelu_from, int dtype, int num_sms,
-                              cudaStream_t stream) {
+                              const void* bias, const void* res, int ldr, void* out, int ldo, int M, int N,
+                              int gelu_from, int dtype, int num_sms, cudaStream_t stream) {
   using namespace oslo;
   if (M <= 0 || N <= 0) return 0;
   if (M > 4 || N % GV_COLS || K1 <= 0 || K1 % 8 || (x2 && (K2 <= 0 || K2 % 8)) || ld1 % 8 || ldw % 8 || (x2 && ld2 % 8))
@@ -197,9 +200,9 @@ extern "C" int oslo_gemv_rows(const void* x1, int ld1, int K1, const void* x2, i
   for (const void* p : ptrs)
     if (reinterpret_cast<uintptr_t>(p) & 15) return -4;
   if (dtype == OSLO_DT_BF16)
-    return gemv_launch<__nv_bfloat16>(x1, ld1, K1, x2, ld2, x2 ? K2 : 0, W, ldw, bias, out, ldo, M, N, gelu_from, num_sms, stream);
+    return gemv_launch<__nv_bfloat16>(x1, ld1, K1, x2, ld2, x2 ? K2 : 0, W, ldw, bias, res, ldr, out, ldo, M, N, gelu_from, num_sms, stream);
   if (dtype == OSLO_DT_FP16)
-    return gemv_launch<__half>(x1, ld1, K1, x2, ld2, x2 ? K2 : 0, W, ldw, bias, out, ldo, M, N, gelu_from, num_sms, stream);
+    return gemv_launch<__half>(x1, ld1, K1, x2, ld2, x2 ? K2 : 0, W, ldw, bias, res, ldr, out, ldo, M, N, gelu_from, num_sms, stream);
   return -2;
 }
 

@@ -132,9 +132,10 @@ int oslo_allreduce_symm(void* const* peer_ptrs_dev, void* mc_ptr, uint32_t* cons
 
 // decode-step kernels (decode_sm100.cu). gemv_rows: out[m, n] = act([x1 | x2][m, :] . W[n, :] + bias[n]) for M <= 4
 // rows, W [N, K1 + K2] K-major, tanh-GeLU on columns >= gelu_from (-1 = none); x2 may be null.
+// `res` [M, N] (row stride ldr) is added after the activation; bias and res may be null.
 int oslo_gemv_rows(const void* x1, int ld1, int K1, const void* x2, int ld2, int K2, const void* W, int ldw,
-                   const void* bias, void* out, int ldo, int M, int N, int gelu_from, int dtype, int num_sms,
-                   cudaStream_t stream);
+                   const void* bias, const void* res, int ldr, void* out, int ldo, int M, int N, int gelu_from,
+                   int dtype, int num_sms, cudaStream_t stream);
 // rotary on the new token's q and k, q -> q_out [B, H, D], k / v -> cache [B, H, Tmax, D] at write_index[0];
 // the rotary position of row b is lengths[b]
 int oslo_rotary_append(const void* q, const void* k, const void* v, long long ldq, long long ldk, long long ldv,

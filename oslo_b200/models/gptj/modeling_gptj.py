@@ -169,16 +169,24 @@ class GPTJBlock(nn.Module):
         rd = attn.rotary_dim if attn.rotary_dim is not None else attn.head_dim
         q_rot = cuda_ops.rotary_append(q, k, v, kc, vc, cache.lengths_dev, cache.write_index, rd)
         o = ops.decode_attention(q_rot, kc, vc, cache.lengths_next, attn.scale, attn.window)
-        if rows <= cuda_ops.GEMV_ROWS:
-            z = cuda_ops.gemv_two_inputs(o.reshape(rows, -1), h, self._packed2_w)
-        else:   # more rows than the CUDA cores can feed from HBM: tensor-core split-k GEMM over the joined input
-            z = cuda_ops.packed_linear_small_m(torch.cat([o.reshape(rows, -1), h], dim=1), self._packed2_w, None, -1)
         mpu = getattr(attn.out_proj, "mpu", None)
-        if mpu is not None and mpu.tp > 1:
+        tp = mpu.tp if mpu is not None else 1
+        fc_bias = mlp.fc_out.bias
+        if rows <= cuda_ops.GEMV_ROWS:
+            # bias and residual enter the sum exactly once: on tensor-parallel rank 0, before the all-reduce
+            first = tp == 1 or mpu.tp_rank == 0
+            z = cuda_ops.gemv_two_inputs(o.reshape(rows, -1), h, self._packed2_w, fc_bias if first else None,
+                                         hidden_states.reshape(rows, -1) if first else None)
+            if tp > 1:
+                z = mpu._reduce(z)
+            return z.view_as(hidden_states), None, None
+        # more rows than the CUDA cores can feed from HBM: tensor-core split-k GEMM over the joined input
+        z = cuda_ops.packed_linear_small_m(torch.cat([o.reshape(rows, -1), h], dim=1), self._packed2_w, None, -1)
+        if tp > 1:
             z = mpu._reduce(z)
         z = z.view_as(hidden_states)
-        if mlp.fc_out.bias is not None:
-            z = z + mlp.fc_out.bias
+        if fc_bias is not None:
+            z = z + fc_bias
         return z + hidden_states, None, None
 
     def forward(self, hidden_states: Tensor, **kw):

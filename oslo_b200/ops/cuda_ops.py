@@ -146,9 +146,11 @@ def packed_linear_small_m(x: Tensor, weight: Tensor, bias: Optional[Tensor], gel
     return y.view(*x.shape[:-1], weight.size(0))
 
 
-def gemv_two_inputs(x1: Tensor, x2: Tensor, weight: Tensor, bias: Optional[Tensor] = None) -> Tensor:
-    """``[x1 | x2] @ weight^T (+ bias)`` for at most ``GEMV_ROWS`` rows without materialising the concatenation."""
-    return _ext().gemv_rows(_as_operand(x1), _as_operand(x2), _as_operand(weight), bias, -1)
+def gemv_two_inputs(x1: Tensor, x2: Tensor, weight: Tensor, bias: Optional[Tensor] = None,
+                    residual: Optional[Tensor] = None) -> Tensor:
+    """``[x1 | x2] @ weight^T (+ bias) (+ residual)`` for at most ``GEMV_ROWS`` rows without materialising the
+    concatenation."""
+    return _ext().gemv_rows(_as_operand(x1), _as_operand(x2), _as_operand(weight), bias, -1, residual)
 
 
 def rotary_append(q: Tensor, k: Tensor, v: Tensor, k_cache: Tensor, v_cache: Tensor, lengths: Tensor,

@@ -382,8 +382,9 @@ def test_gemv_rows(M, K1, K2, N):
     ref = xin @ w.float().t() + b.float()
     ref[:, N // 2:] = ops.reference.gelu_tanh(ref[:, N // 2:])
     _close(y, ref, atol=0.03)
-    z = ext.gemv_rows(x1, x2, w, None, -1)
-    _close(z, xin @ w.float().t(), atol=0.03)
+    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    z = ext.gemv_rows(x1, x2, w, None, -1, res)
+    _close(z, xin @ w.float().t() + res.float(), atol=0.04)
 
 
 @pytest.mark.parametrize("M,N,K,rev", [(1, 4096, 4096, False), (8, 512, 4096, False), (32, 16384, 4096, True),
