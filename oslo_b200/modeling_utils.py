@@ -256,6 +256,7 @@ class PreTrainedModel(nn.Module, ParallelizationMixin, FusedKernelMixin, Generat
         out, inp = self.get_output_embeddings(), self.get_input_embeddings()
         if out is not None and inp is not None and getattr(self.config, "tie_word_embeddings", True):
             out.weight = inp.weight
+            inp.weight._oslo_shared = True   # two layers add into this gradient: no in-place weight-gradient GEMM
 
     def resize_token_embeddings(self, new_num_tokens: Optional[int] = None) -> nn.Module:
         """Grow/shrink the vocabulary. Only legal before tensor-parallel slicing.

@@ -67,6 +67,25 @@ SMALL_M_ROWS = 64  # inference calls with at most this many rows use the split-K
 GEMV_ROWS = 4      # ... and with at most this many rows the CUDA-core weight-streaming kernel
 
 
+def weight_grad(weight: Tensor, a: Tensor, b: Tensor) -> Optional[Tensor]:
+    """``a^T b`` (both ``[rows, *]``) as the gradient of ``weight``.
+
+    Parameters whose ``.grad`` is a persistent, zeroed-per-step view of a flat buffer (marked
+    ``_oslo_accum_grad`` by ``optim.FlatBuffers``) get the product accumulated into that view by the GEMM
+    epilogue and ``None`` is returned, which spares the separate gradient tensor and the add kernel of every
+    micro-batch; ``_oslo_grad_hook`` (set by the data-parallel wrapper) stands in for the post-accumulate hook
+    that autograd does not call in that case."""
+    g = weight.grad
+    if (g is not None and getattr(weight, "_oslo_accum_grad", False) and g.dtype == weight.dtype
+            and g.shape == weight.shape and g.is_contiguous() and not torch.is_grad_enabled()):
+        gemm(a, b, True, True, out=g, flags=FLAG_ACCUMULATE)
+        hook = getattr(weight, "_oslo_grad_hook", None)
+        if hook is not None:
+            hook(weight)
+        return None
+    return gemm(a, b, True, True)
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, reversed_, gelu):
@@ -98,7 +117,7 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, weight, False, not ctx.reversed).view(ctx.in_shape)
         if ctx.needs_input_grad[1]:
-            dw = gemm(x2, dy2, True, True) if ctx.reversed else gemm(dy2, x2, True, True)
+            dw = weight_grad(weight, x2, dy2) if ctx.reversed else weight_grad(weight, dy2, x2)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = ext.colsum(dy2).to(ctx.bias_dtype)
         return dx, dw, db, None, None

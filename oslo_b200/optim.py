@@ -70,6 +70,8 @@ class FlatBuffers:
             view.copy_(p.data)
             p.data = view
             p.grad = self.flat_g[off: off + p.numel()].view(p.shape)
+            # the view lives as long as the buffer and is zeroed every step: weight-gradient GEMMs may add into it
+            p._oslo_accum_grad = self.flat_g.dtype == p.dtype and not getattr(p, "_oslo_shared", False)
 
     def zero_grad(self) -> None:
         self.flat_g.zero_()

@@ -46,6 +46,7 @@ class DistributedDataParallel(nn.Module):
         self._build_buckets(int(bucket_mb * 2 ** 20))
         for p in self.buf.params:
             p.register_post_accumulate_grad_hook(self._hook)
+            p._oslo_grad_hook = self._hook   # called by weight-gradient GEMMs that add straight into p.grad
         eng = getattr(model, "_pipe_engine", None)
         if eng is not None:
             eng.on_last_backward = lambda last: setattr(self, "sync", bool(last))

@@ -136,7 +136,7 @@ class _RowParallelFused(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        from ..ops.cuda_ops import gemm
+        from ..ops.cuda_ops import gemm, weight_grad
         x2, weight = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.size(-1))
         if not dy2.is_contiguous():
@@ -145,7 +145,7 @@ class _RowParallelFused(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, weight, False, not ctx.reversed).view(ctx.in_shape)
         if ctx.needs_input_grad[1]:
-            dw = gemm(x2, dy2, True, True) if ctx.reversed else gemm(dy2, x2, True, True)
+            dw = weight_grad(weight, x2, dy2) if ctx.reversed else weight_grad(weight, dy2, x2)
         return dx, dw, None, None
 
 
@@ -172,7 +172,7 @@ class _ColumnParallelFused(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        from ..ops.cuda_ops import gemm
+        from ..ops.cuda_ops import gemm, weight_grad
         ext = ops.load_ext(required=True)
         x2, weight, z = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.size(-1))
@@ -184,7 +184,7 @@ class _ColumnParallelFused(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = ctx.tp.gemm_all_reduce(dy2, weight, False, not ctx.reversed).view(ctx.in_shape)
         if ctx.needs_input_grad[1]:
-            dw = gemm(x2, dy2, True, True) if ctx.reversed else gemm(dy2, x2, True, True)
+            dw = weight_grad(weight, x2, dy2) if ctx.reversed else weight_grad(weight, dy2, x2)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = ext.colsum(dy2).to(ctx.bias_dtype)
         return dx, dw, db, None, None, None
@@ -213,7 +213,7 @@ class _ColumnParallelSeqFused(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        from ..ops.cuda_ops import gemm
+        from ..ops.cuda_ops import gemm, weight_grad
         ext = ops.load_ext(required=True)
         gathered, weight, z = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.size(-1))
@@ -225,7 +225,7 @@ class _ColumnParallelSeqFused(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = ctx.tp.gemm_reduce_scatter(dy2, weight, False, not ctx.reversed).view(ctx.shard_shape)
         if ctx.needs_input_grad[1]:
-            dw = gemm(gathered, dy2, True, True) if ctx.reversed else gemm(dy2, gathered, True, True)
+            dw = weight_grad(weight, gathered, dy2) if ctx.reversed else weight_grad(weight, dy2, gathered)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = ext.colsum(dy2).to(ctx.bias_dtype)
         return dx, dw, db, None, None, None
@@ -247,7 +247,7 @@ class _RowParallelSeqFused(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy_shard):
-        from ..ops.cuda_ops import gemm
+        from ..ops.cuda_ops import gemm, weight_grad
         x2, weight = ctx.saved_tensors
         d2 = dy_shard.reshape(-1, dy_shard.size(-1)).contiguous()
         dx = dw = None
@@ -256,5 +256,5 @@ class _RowParallelSeqFused(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = dx2.view(ctx.in_shape)
         if ctx.needs_input_grad[1]:
-            dw = gemm(x2, dy_full, True, True) if ctx.reversed else gemm(dy_full, x2, True, True)
+            dw = weight_grad(weight, x2, dy_full) if ctx.reversed else weight_grad(weight, dy_full, x2)
         return dx, dw, None, None

@@ -426,3 +426,29 @@ def test_packed_decode_projection_matches_per_layer_path():
         set_config(packed_decode=True)
     assert getattr(model.transformer.h[0], "_packed_w", None) is not None
     _close(outs[0], outs[1], atol=2e-2)
+
+
+def test_weight_gradients_accumulate_into_flat_buffer():
+    """Weight-gradient GEMMs that add straight into the optimizer's flat gradient buffer give the gradients of the
+    ordinary autograd accumulation over two micro-batches."""
+    import oslo_b200 as ob
+    from oslo_b200.optim import FusedAdamW
+    torch.manual_seed(0)
+    cfg = ob.GPTJConfig(vocab_size=1024, n_positions=128, n_embd=256, n_layer=2, n_head=4, rotary_dim=16)
+    model = ob.GPTJForCausalLM(cfg).to(torch.bfloat16).cuda().fuse().train()
+    opt = FusedAdamW(model.parameters(), lr=1e-3)
+    ids = torch.randint(0, 1024, (4, 64), device="cuda")
+    flagged = [p for p in opt.buf.params if getattr(p, "_oslo_accum_grad", False)]
+    assert flagged
+    grads = []
+    for fused in (True, False):
+        for p in flagged:
+            p._oslo_accum_grad = fused
+        opt.zero_grad()
+        for mb in (ids[:2], ids[2:]):
+            (model(input_ids=mb, labels=mb, output_logits=False).loss / 2).backward()
+        grads.append(opt.buf.flat_g.float().clone())
+    for p in flagged:
+        p._oslo_accum_grad = True
+    assert grads[0].abs().max() > 0
+    _close(grads[0], grads[1], atol=2e-3, rtol=5e-2)
