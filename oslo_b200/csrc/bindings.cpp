@@ -238,6 +238,21 @@ Tensor rotary(const Tensor& x, const Tensor& positions, int64_t rotary_dim, doub
   return y;
 }
 
+// in place: only the first rotary_dim dims of every head are read and written. x is any contiguous tensor whose
+// memory is [tokens, heads, head_dim] (e.g. the [B, S, heads * head_dim] output of a projection)
+Tensor rotary_(Tensor x, const Tensor& positions, int64_t heads, int64_t head_dim, int64_t rotary_dim, double base,
+               bool inverse) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous(), "rotary_: contiguous CUDA tensor required");
+  TORCH_CHECK(positions.scalar_type() == at::kLong && positions.is_contiguous() &&
+                  positions.numel() * heads * head_dim == x.numel(), "rotary_: positions must be int64 [tokens]");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_rc(oslo_rotary_inplace(x.data_ptr(), reinterpret_cast<const long long*>(positions.data_ptr<int64_t>()), 1,
+                               static_cast<int>(positions.numel()), static_cast<int>(heads), static_cast<int>(head_dim),
+                               static_cast<int>(rotary_dim), static_cast<float>(base), inverse ? 1 : 0, dt_code(x),
+                               cur_stream()), "rotary_");
+  return x;
+}
+
 Tensor causal_softmax_fwd(const Tensor& x, double scale) {
   TORCH_CHECK(x.is_cuda() && x.dim() == 3 && x.is_contiguous(), "causal_softmax: contiguous [batches,sq,sk] required");
   c10::cuda::CUDAGuard guard(x.device());
@@ -554,6 +569,7 @@ TORCH_LIBRARY(oslo_b200, m) {
   m.def("bias_dropout_residual(Tensor x, Tensor? bias, Tensor? residual, float p, int seed, int mode) -> Tensor", &bias_dropout_residual);
   m.def("colsum(Tensor x) -> Tensor", &colsum);
   m.def("rotary(Tensor x, Tensor positions, int rotary_dim, float base, bool inverse) -> Tensor", &rotary);
+  m.def("rotary_(Tensor(a!) x, Tensor positions, int heads, int head_dim, int rotary_dim, float base, bool inverse) -> Tensor(a!)", &rotary_);
   m.def("causal_softmax_fwd(Tensor x, float scale) -> Tensor", &causal_softmax_fwd);
   m.def("masked_softmax_fwd(Tensor x, Tensor mask, float scale) -> Tensor", &masked_softmax_fwd);
   m.def("softmax_bwd(Tensor y, Tensor dy, float scale) -> Tensor", &softmax_bwd);

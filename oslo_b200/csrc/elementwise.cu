@@ -233,6 +233,71 @@ __global__ void colsum_kernel(const T* __restrict__ x, float* __restrict__ part,
   part[static_cast<size_t>(blockIdx.y) * cols + c] = s;
 }
 
+// 16-bit inputs, cols % 8 == 0, 16-byte aligned rows: each thread owns 8 adjacent columns (one 16-byte load per row)
+// and keeps four rows in flight
+template <typename T>
+__global__ void __launch_bounds__(128) colsum_vec8_kernel(const T* __restrict__ x, float* __restrict__ part, int rows,
+                                                          int cols) {
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= cols) return;
+  float s[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s[j] = 0.f;
+  const int step = gridDim.y;
+  int r = blockIdx.y;
+  for (; r + 3 * step < rows; r += 4 * step) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(r + u * step) * cols + c);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const T* e = reinterpret_cast<const T*>(&v[u]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s[j] += Cvt<T>::to(e[j]);
+    }
+  }
+  for (; r < rows; r += step) {
+    const uint4 v = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * cols + c);
+    const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s[j] += Cvt<T>::to(e[j]);
+  }
+  float* o = part + static_cast<size_t>(blockIdx.y) * cols + c;
+  *reinterpret_cast<float4*>(o) = make_float4(s[0], s[1], s[2], s[3]);
+  *reinterpret_cast<float4*>(o + 4) = make_float4(s[4], s[5], s[6], s[7]);
+}
+
+// rotary applied in place to the first `rd` dims of every head of x [tokens, H, D]; one thread rotates the four
+// pairs of one 16-byte vector, the other D - rd dims are never touched (rd % 8 == 0, D % 8 == 0)
+template <typename T>
+__global__ void rotary_inplace_kernel(T* __restrict__ x, const long long* __restrict__ pos, long long tokens, int H,
+                                      int D, int rd, float log2_base, int inverse) {
+  const int vec_per_head = rd / 8;
+  const long long total = tokens * H * vec_per_head;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int vi = static_cast<int>(i % vec_per_head);
+    const long long th = i / vec_per_head;   // token * H + head
+    const long long tok = th / H;
+    T* p = x + static_cast<size_t>(th) * D + vi * 8;
+    uint4 raw = *reinterpret_cast<const uint4*>(p);
+    T* e = reinterpret_cast<T*>(&raw);
+    const float ps = static_cast<float>(pos[tok]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int pr = vi * 4 + j;
+      const float inv_freq = exp2f(-log2_base * (2.0f * pr) / rd);
+      float sn, cs;
+      sincosf(ps * inv_freq, &sn, &cs);
+      if (inverse) sn = -sn;
+      const float a = Cvt<T>::to(e[2 * j]), b = Cvt<T>::to(e[2 * j + 1]);
+      e[2 * j] = Cvt<T>::from(a * cs - b * sn);
+      e[2 * j + 1] = Cvt<T>::from(b * cs + a * sn);
+    }
+    *reinterpret_cast<uint4*>(p) = raw;
+  }
+}
+
 // ---------------------------------------------------------------------- bias + GeLU
 template <typename T, bool BWD>
 __global__ void bias_gelu_kernel(const T* __restrict__ a, const T* __restrict__ x, const T* __restrict__ bias,
@@ -667,10 +732,17 @@ extern "C" int oslo_bias_dropout_residual(const void* x, const void* bias, const
 extern "C" int oslo_colsum(const void* x, float* part, float* out, int rows, int cols, int parts, int dtype,
                            cudaStream_t st) {
   if (rows <= 0 || cols <= 0) return 0;
-  DISPATCH_16(dtype, T, {
-    dim3 grid((cols + 127) / 128, parts);
-    colsum_kernel<T><<<grid, 128, 0, st>>>((const T*)x, part, rows, cols);
-  })
+  if (dtype != OSLO_DT_FP32 && cols % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(part) & 15) == 0) {
+    dim3 grid((cols / 8 + 127) / 128, parts);
+    if (dtype == OSLO_DT_BF16) colsum_vec8_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)x, part, rows, cols);
+    else colsum_vec8_kernel<__half><<<grid, 128, 0, st>>>((const __half*)x, part, rows, cols);
+  } else {
+    DISPATCH_16(dtype, T, {
+      dim3 grid((cols + 127) / 128, parts);
+      colsum_kernel<T><<<grid, 128, 0, st>>>((const T*)x, part, rows, cols);
+    })
+  }
   reduce_parts_kernel<float><<<(cols + 255) / 256, 256, 0, st>>>(part, nullptr, out, nullptr, parts, cols);
   RET_LAST();
 }
@@ -684,6 +756,24 @@ extern "C" int oslo_rotary(const void* x, void* y, const long long* positions, i
     rotary_kernel<T><<<grid_for(total, 256), 256, 0, st>>>((const T*)x, (T*)y, positions, B, S, H, D, rotary_dim,
                                                           log2f(base), inverse);
   })
+  RET_LAST();
+}
+
+// in-place variant: x [B, S, H, D] contiguous, only the first rotary_dim dims of each head are read and written
+extern "C" int oslo_rotary_inplace(void* x, const long long* positions, int B, int S, int H, int D, int rotary_dim,
+                                   float base, int inverse, int dtype, cudaStream_t st) {
+  const long long tokens = static_cast<long long>(B) * S;
+  if (tokens == 0 || rotary_dim == 0) return 0;
+  if (D % 8 || rotary_dim % 8 || rotary_dim > D || (reinterpret_cast<uintptr_t>(x) & 15)) return -3;
+  const long long total = tokens * H * (rotary_dim / 8);
+  if (dtype == OSLO_DT_BF16)
+    rotary_inplace_kernel<__nv_bfloat16><<<grid_for(total, 256), 256, 0, st>>>((__nv_bfloat16*)x, positions, tokens, H, D,
+                                                                               rotary_dim, log2f(base), inverse);
+  else if (dtype == OSLO_DT_FP16)
+    rotary_inplace_kernel<__half><<<grid_for(total, 256), 256, 0, st>>>((__half*)x, positions, tokens, H, D, rotary_dim,
+                                                                        log2f(base), inverse);
+  else
+    return -2;
   RET_LAST();
 }
 

@@ -62,6 +62,10 @@ int oslo_colsum(const void* x, float* part, float* out, int rows, int cols, int 
 int oslo_rotary(const void* x, void* y, const long long* positions, int B, int S, int H, int D, int rotary_dim,
                 float base, int inverse, int dtype, cudaStream_t stream);
 
+// same rotation applied in place; touches only the first rotary_dim dims of each head (rotary_dim % 8 == 0, D % 8 == 0)
+int oslo_rotary_inplace(void* x, const long long* positions, int B, int S, int H, int D, int rotary_dim, float base,
+                        int inverse, int dtype, cudaStream_t stream);
+
 // softmax on materialised scores
 int oslo_causal_softmax_fwd(const void* x, void* y, int batches, int sq, int sk, float scale, int dtype,
                             cudaStream_t stream);

@@ -93,6 +93,13 @@ class GPTJMLP(nn.Module):
     def forward(self, x: Tensor, h: Optional[Tensor] = None) -> Tensor:
         if h is not None:     # fc_in + GeLU already done by the block's packed decode GEMM
             pass
+        elif (self.fused and self.activation in GELU_TANH_NAMES and type(self.fc_in) is Linear
+              and type(self.fc_out) is Linear and x.is_cuda and self.fc_in.oslo_fused and self.fc_out.oslo_fused):
+            from ...ops import cuda_ops
+            if cuda_ops.fused_mlp_ok(x, self.fc_in.weight, self.fc_out.weight):   # both layers in one autograd node
+                y = cuda_ops.fused_mlp(x, self.fc_in.weight, self.fc_in.bias, self.fc_out.weight, self.fc_out.bias)
+                return maybe_dropout(y, self.resid_pdrop, self.training)
+            h = self.fc_in(x, activation="gelu_new")
         elif self.fused and self.activation in GELU_TANH_NAMES:
             h = self.fc_in(x, activation="gelu_new")
         else:

@@ -98,11 +98,14 @@ class _Linear(torch.autograd.Function):
         if gelu and need_grad:
             flags |= FLAG_SAVE_PREACT
             z = torch.empty(x2.size(0), n, dtype=x.dtype, device=x.device)
-        y = gemm(x2, weight, False, reversed_, bias=bias, aux_out=z, flags=flags)
+        # the result is allocated in its final shape and the GEMM writes through a 2-D view of it: a view RETURNED by
+        # a custom function could not be modified in place afterwards (the in-place rotary does that to q and k)
+        y = torch.empty(*x.shape[:-1], n, dtype=x.dtype, device=x.device)
+        gemm(x2, weight, False, reversed_, bias=bias, out=y.view(-1, n), aux_out=z, flags=flags)
         ctx.save_for_backward(x2, weight, z)
         ctx.reversed, ctx.has_bias, ctx.in_shape = reversed_, bias is not None, x.shape
         ctx.bias_dtype = bias.dtype if bias is not None else None
-        return y.view(*x.shape[:-1], n)
+        return y
 
     @staticmethod
     def backward(ctx, dy):
@@ -121,6 +124,60 @@ class _Linear(torch.autograd.Function):
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = ext.colsum(dy2).to(ctx.bias_dtype)
         return dx, dw, db, None, None
+
+
+class _FusedMLP(torch.autograd.Function):
+    """``fc_out(gelu(fc_in(x)))`` for ``[out, in]`` weights. The backward multiplies by ``gelu'`` inside the epilogue
+    of fc_out's input-gradient GEMM instead of running a separate pass over the ``[rows, 4 * hidden]`` activation
+    gradient."""
+
+    @staticmethod
+    def forward(ctx, x, w_in, b_in, w_out, b_out):
+        k = x.size(-1)
+        x2 = x.reshape(-1, k)
+        need_grad = any(ctx.needs_input_grad)
+        flags = FLAG_GELU | (FLAG_BIAS if b_in is not None else 0)
+        z = None
+        if need_grad:
+            flags |= FLAG_SAVE_PREACT
+            z = torch.empty(x2.size(0), w_in.size(0), dtype=x.dtype, device=x.device)
+        h = gemm(x2, w_in, False, False, bias=b_in, aux_out=z, flags=flags)
+        y = torch.empty(*x.shape[:-1], w_out.size(0), dtype=x.dtype, device=x.device)
+        gemm(h, w_out, False, False, bias=b_out, out=y.view(-1, w_out.size(0)), flags=FLAG_BIAS if b_out is not None else 0)
+        ctx.save_for_backward(x2, w_in, w_out, z, h)
+        ctx.has_b_in, ctx.has_b_out, ctx.in_shape = b_in is not None, b_out is not None, x.shape
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w_in, w_out, z, h = ctx.saved_tensors
+        ext = _ext()
+        dy2 = dy.reshape(-1, dy.size(-1))
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw_in = db_in = dw_out = db_out = None
+        dz = gemm(dy2, w_out, False, True, aux=z, flags=FLAG_DGELU)      # (dy W_out) * gelu'(z)
+        if ctx.needs_input_grad[3]:
+            dw_out = weight_grad(w_out, dy2, h)
+        if ctx.has_b_out and ctx.needs_input_grad[4]:
+            db_out = ext.colsum(dy2).to(dy.dtype)
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dz, w_in, False, True).view(ctx.in_shape)
+        if ctx.needs_input_grad[1]:
+            dw_in = weight_grad(w_in, dz, x2)
+        if ctx.has_b_in and ctx.needs_input_grad[2]:
+            db_in = ext.colsum(dz).to(dy.dtype)
+        return dx, dw_in, db_in, dw_out, db_out
+
+
+def fused_mlp_ok(x: Tensor, w_in: Tensor, w_out: Tensor) -> bool:
+    return (x.is_cuda and x.dtype in _16BIT and w_in.dtype == x.dtype and w_out.dtype == x.dtype and x.numel() > 0
+            and x.size(-1) % 8 == 0 and w_in.size(0) % 8 == 0 and w_out.size(0) % 8 == 0
+            and x.numel() // x.size(-1) > SMALL_M_ROWS)
+
+
+def fused_mlp(x: Tensor, w_in: Tensor, b_in: Optional[Tensor], w_out: Tensor, b_out: Optional[Tensor]) -> Tensor:
+    return _FusedMLP.apply(x, w_in, b_in, w_out, b_out)
 
 
 def linear(x: Tensor, weight: Tensor, bias: Optional[Tensor], reversed_: bool, activation: Optional[str]) -> Tensor:
@@ -269,10 +326,51 @@ class _Rotary(torch.autograd.Function):
         return _ext().rotary(dy.contiguous(), positions, ctx.rd, ctx.base, True), None, None, None
 
 
+class _RotaryInplace(torch.autograd.Function):
+    """Rotation of the first ``rotary_dim`` dims of every head, in place: the other dims (3/4 of a GPT-J head) are
+    neither read nor written. The input is the fresh output of a projection that nothing else needs, and the
+    incoming gradient is the attention kernel's own output, so both directions may overwrite their argument.
+    ``x`` is any contiguous tensor laid out ``[tokens, heads, head_dim]`` in memory."""
+
+    @staticmethod
+    def forward(ctx, x, positions, heads, head_dim, rotary_dim, base):
+        ctx.save_for_backward(positions)
+        ctx.cfg = (heads, head_dim, rotary_dim, base)
+        ctx.mark_dirty(x)
+        _ext().rotary_(x, positions, heads, head_dim, rotary_dim, base, False)
+        return x
+
+    @staticmethod
+    def backward(ctx, dy):
+        (positions,) = ctx.saved_tensors
+        heads, head_dim, rotary_dim, base = ctx.cfg
+        if not dy.is_contiguous():
+            dy = dy.contiguous()
+        return _ext().rotary_(dy, positions, heads, head_dim, rotary_dim, base, True), None, None, None, None, None
+
+
 def rotary_interleaved(x: Tensor, positions: Tensor, rotary_dim: int, base: float) -> Tensor:
     if positions.dim() == 1:
         positions = positions.unsqueeze(0).expand(x.size(0), -1)
     positions = positions.to(torch.long).contiguous()
+    heads, head_dim = x.size(-2), x.size(-1)
+    ok = (x.dim() == 4 and x.is_contiguous() and head_dim % 8 == 0 and rotary_dim % 8 == 0 and x.data_ptr() % 16 == 0
+          and not x.is_leaf and os.environ.get("OSLO_B200_ROTARY_INPLACE", "1") != "0")
+    if ok:
+        target = x
+        if x._is_view():
+            # work on the tensor the view was taken from (typically the projection's [B, S, heads * head_dim] output):
+            # autograd refuses in-place changes of views that a custom function returned, and a plain function output
+            # needs no view bookkeeping at all
+            base_t = x._base
+            if (base_t is not None and base_t.is_contiguous() and base_t.numel() == x.numel()
+                    and base_t.data_ptr() == x.data_ptr() and not base_t._is_view() and not base_t.is_leaf):
+                target = base_t
+            elif x.requires_grad:
+                ok = False
+        if ok:
+            out = _RotaryInplace.apply(target, positions, heads, head_dim, rotary_dim, base)
+            return out if target is x else out.view(x.shape)
     return _Rotary.apply(x, positions, rotary_dim, base)
 
 

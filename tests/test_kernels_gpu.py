@@ -144,6 +144,13 @@ def test_rotary():
     yr.backward(g.float())
     _close(y, yr, atol=2e-2)
     _close(x.grad, xf.grad, atol=2e-2)
+    # a non-leaf input takes the in-place kernel (first rotary_dim dims only); its backward overwrites the incoming
+    # gradient, so hand it a copy
+    x2 = x.detach().clone().requires_grad_(True)
+    y2 = ops.rotary_interleaved(x2 * 1.0, pos, 64)
+    y2.backward(g.clone())
+    _close(y2, yr, atol=2e-2)
+    _close(x2.grad, xf.grad, atol=2e-2)
 
 
 def test_softmax_kernels():
@@ -452,3 +459,26 @@ def test_weight_gradients_accumulate_into_flat_buffer():
         p._oslo_accum_grad = True
     assert grads[0].abs().max() > 0
     _close(grads[0], grads[1], atol=2e-3, rtol=5e-2)
+
+
+def test_fused_mlp_autograd():
+    """fc_in -> GeLU -> fc_out as one autograd node (dGeLU inside the dgrad GEMM epilogue) against fp32 autograd."""
+    ops, co = _ops()
+    torch.manual_seed(8)
+    rows, E, F = 200, 256, 1024
+    x = (torch.randn(2, rows // 2, E, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    w_in = (torch.randn(F, E, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_(True)
+    b_in = (torch.randn(F, device="cuda") * 0.1).to(torch.bfloat16).requires_grad_(True)
+    w_out = (torch.randn(E, F, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_(True)
+    b_out = (torch.randn(E, device="cuda") * 0.1).to(torch.bfloat16).requires_grad_(True)
+    assert co.fused_mlp_ok(x, w_in, w_out)
+    y = co.fused_mlp(x, w_in, b_in, w_out, b_out)
+    g = torch.randn_like(y)
+    y.backward(g)
+    ref_in = [t.detach().float().requires_grad_(True) for t in (x, w_in, b_in, w_out, b_out)]
+    xf, wi, bi, wo, bo = ref_in
+    yr = ops.reference.gelu_tanh(xf @ wi.t() + bi) @ wo.t() + bo
+    yr.backward(g.float())
+    _close(y, yr, atol=3e-2)
+    for got, want in zip((x, w_in, b_in, w_out, b_out), ref_in):
+        _close(got.grad, want.grad, atol=5e-2, rtol=5e-2)
