@@ -103,6 +103,8 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, i
   return static_cast<int>(cudaGetLastError());
 }
 
+constexpr int PAIR_STAGES = 6;   // 32 KB operand stages; OSLO_B200_PAIR_STAGES=7 fills the 227 KB (no measurable gain: the part is power-bound)
+
 // 256 x 256 tiles on CTA pairs (gemm_pair_core.cuh); the grid is a whole number of pairs
 template <int STAGES>
 static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, int num_sms, cudaStream_t stream) {
@@ -172,7 +174,11 @@ extern "C" int oslo_gemm_16bit(const void* A, const void* B, void* D, int M, int
   p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ld_aux = ld_aux; p.ld_aux_out = ld_aux_out;
   p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major; p.flags = flags; p.alpha = alpha; p.err = err_word;
   p.comm = CommParams{};
-  if (pair) return launch_pair<6>(ta, tb, p, num_sms, stream);
+  if (pair) {
+    static const int stages = [] { const char* e = getenv("OSLO_B200_PAIR_STAGES"); return e ? atoi(e) : PAIR_STAGES; }();
+    if (stages == 7) return launch_pair<7>(ta, tb, p, num_sms, stream);
+    return launch_pair<PAIR_STAGES>(ta, tb, p, num_sms, stream);
+  }
   if (bn == 256) return launch<256, 4>(ta, tb, p, num_sms, stream);
   return launch<128, 6>(ta, tb, p, num_sms, stream);
 }

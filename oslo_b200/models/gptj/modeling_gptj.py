@@ -14,6 +14,7 @@ import torch.nn as nn
 from torch import Tensor
 
 from ... import ops
+from ...config import get_config
 from ...fused_kernels_utils import ACT2FN, GELU_TANH_NAMES
 from ...modeling_utils import PretrainedConfig, PreTrainedModel
 from ...parallel.layers import Embedding, LayerNorm, Linear
@@ -57,11 +58,15 @@ class GPTJAttention(AttentionCore):
 
     def forward(self, hidden_states: Tensor, layer_past=None, attention_mask=None, position_ids=None,
                 head_mask=None, use_cache=False, output_attentions=False, cache=None, layer_id=0, seq_shape=None,
-                qkv=None):
+                qkv=None, residual=None):
         b, s = seq_shape if seq_shape is not None else hidden_states.shape[:2]
         nh, hd = self.num_attention_heads, self.head_dim
         if qkv is not None:   # already projected by the block's packed decode GEMM
             q, k, v = (t.reshape(b, s, nh, hd) for t in qkv)
+        elif self._one_node_qkv(hidden_states):
+            from ...ops import cuda_ops
+            q, k, v = (t.view(b, s, nh, hd) for t in cuda_ops.qkv_linear(
+                hidden_states, self.q_proj.weight, self.k_proj.weight, self.v_proj.weight))
         else:
             q = self.q_proj(hidden_states).view(b, s, nh, hd)
             k = self.k_proj(hidden_states).view(b, s, nh, hd)
@@ -72,8 +77,22 @@ class GPTJAttention(AttentionCore):
         q, k, v = (t.permute(0, 2, 1, 3) for t in (q, k, v))
         out, present, probs = self.attend_with_cache(q, k, v, layer_past, cache, layer_id, attention_mask,
                                                      use_cache, output_attentions, head_mask)
-        out = self.out_proj(to_token_rows(merge_heads(out), seq_shape))
+        merged = to_token_rows(merge_heads(out), seq_shape)
+        if residual is not None:   # only offered by the block when out_proj is a plain Linear and no dropout follows
+            return self.out_proj(merged, residual=residual), present, probs
+        out = self.out_proj(merged)
         return maybe_dropout(out, self.resid_pdrop, self.training), present, probs
+
+    def _one_node_qkv(self, x: Tensor) -> bool:
+        """q, k, v as one autograd node (their input gradients accumulate inside the GEMM epilogues): plain fused
+        bias-free ``Linear`` layers on a CUDA input that takes the large-input GEMM path."""
+        layers = (self.q_proj, self.k_proj, self.v_proj)
+        if not (self.fused and x.is_cuda and all(type(l) is Linear and l.oslo_fused and l.bias is None for l in layers)):
+            return False
+        if not get_config().block_fusion:
+            return False
+        from ...ops import cuda_ops
+        return cuda_ops.qkv_linear_ok(x, *(l.weight for l in layers))
 
 
 class FusedGPTJAttention(GPTJAttention):
@@ -90,20 +109,30 @@ class GPTJMLP(nn.Module):
         self.activation = config.activation_function
         self.resid_pdrop = config.resid_pdrop
 
-    def forward(self, x: Tensor, h: Optional[Tensor] = None) -> Tensor:
+    def forward(self, x: Tensor, h: Optional[Tensor] = None, residual: Optional[Tensor] = None) -> Tensor:
+        """``residual`` (only passed when no dropout follows) is added to the result, inside fc_out's GEMM epilogue
+        where the fused path applies."""
+        if residual is not None:
+            return self._forward(x, h, residual)
+        return self._forward(x, h, None)
+
+    def _forward(self, x: Tensor, h: Optional[Tensor], residual: Optional[Tensor]) -> Tensor:
         if h is not None:     # fc_in + GeLU already done by the block's packed decode GEMM
             pass
         elif (self.fused and self.activation in GELU_TANH_NAMES and type(self.fc_in) is Linear
               and type(self.fc_out) is Linear and x.is_cuda and self.fc_in.oslo_fused and self.fc_out.oslo_fused):
             from ...ops import cuda_ops
             if cuda_ops.fused_mlp_ok(x, self.fc_in.weight, self.fc_out.weight):   # both layers in one autograd node
-                y = cuda_ops.fused_mlp(x, self.fc_in.weight, self.fc_in.bias, self.fc_out.weight, self.fc_out.bias)
-                return maybe_dropout(y, self.resid_pdrop, self.training)
+                y = cuda_ops.fused_mlp(x, self.fc_in.weight, self.fc_in.bias, self.fc_out.weight, self.fc_out.bias,
+                                       residual)
+                return y if residual is not None else maybe_dropout(y, self.resid_pdrop, self.training)
             h = self.fc_in(x, activation="gelu_new")
         elif self.fused and self.activation in GELU_TANH_NAMES:
             h = self.fc_in(x, activation="gelu_new")
         else:
             h = ACT2FN[self.activation](self.fc_in(x))
+        if residual is not None:
+            return (self.fc_out(h, residual=residual) if type(self.fc_out) is Linear else self.fc_out(h) + residual)
         return maybe_dropout(self.fc_out(h), self.resid_pdrop, self.training)
 
 
@@ -205,9 +234,16 @@ class GPTJBlock(nn.Module):
                 return fast
             a, present, probs = self.attn(x, qkv=packed[:3], **kw)
             m = self.mlp(x, h=packed[3])
-        else:
-            a, present, probs = self.attn(x, **kw)
-            m = self.mlp(x)
+            return a + m + hidden_states, present, probs
+        no_dropout = not self.training or (self.attn.resid_pdrop == 0.0 and self.mlp.resid_pdrop == 0.0)
+        if (no_dropout and x.is_cuda and self.attn.fused and type(self.attn.out_proj) is Linear
+                and kw.get("seq_shape") is None and get_config().block_fusion):
+            # hidden + attn + mlp with both additions inside GEMM epilogues: out_proj adds the block input, fc_out adds
+            # that sum
+            a, present, probs = self.attn(x, residual=hidden_states, **kw)
+            return self.mlp(x, residual=a), present, probs
+        a, present, probs = self.attn(x, **kw)
+        m = self.mlp(x)
         return a + m + hidden_states, present, probs
 
 

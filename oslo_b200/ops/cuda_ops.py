@@ -88,12 +88,18 @@ def weight_grad(weight: Tensor, a: Tensor, b: Tensor) -> Optional[Tensor]:
 
 class _Linear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, bias, reversed_, gelu):
+    def forward(ctx, x, weight, bias, reversed_, gelu, residual=None):
         k = x.size(-1)
         x2 = x.reshape(-1, k)
         need_grad = any(ctx.needs_input_grad[:3])  # grad mode is always off inside forward(); ask the ctx
         flags = (FLAG_BIAS if bias is not None else 0) | (FLAG_GELU if gelu else 0)
         n = weight.size(1) if reversed_ else weight.size(0)
+        res2 = None
+        if residual is not None:   # y = x W^T + b + residual in the GEMM epilogue (no activation in between)
+            flags |= FLAG_RESIDUAL
+            res2 = residual.reshape(-1, n)
+            if res2.stride(-1) != 1:
+                res2 = res2.contiguous()
         z = None
         if gelu and need_grad:
             flags |= FLAG_SAVE_PREACT
@@ -101,9 +107,10 @@ class _Linear(torch.autograd.Function):
         # the result is allocated in its final shape and the GEMM writes through a 2-D view of it: a view RETURNED by
         # a custom function could not be modified in place afterwards (the in-place rotary does that to q and k)
         y = torch.empty(*x.shape[:-1], n, dtype=x.dtype, device=x.device)
-        gemm(x2, weight, False, reversed_, bias=bias, out=y.view(-1, n), aux_out=z, flags=flags)
+        gemm(x2, weight, False, reversed_, bias=bias, aux=res2, out=y.view(-1, n), aux_out=z, flags=flags)
         ctx.save_for_backward(x2, weight, z)
         ctx.reversed, ctx.has_bias, ctx.in_shape = reversed_, bias is not None, x.shape
+        ctx.has_residual = residual is not None
         ctx.bias_dtype = bias.dtype if bias is not None else None
         return y
 
@@ -123,7 +130,8 @@ class _Linear(torch.autograd.Function):
             dw = weight_grad(weight, x2, dy2) if ctx.reversed else weight_grad(weight, dy2, x2)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = ext.colsum(dy2).to(ctx.bias_dtype)
-        return dx, dw, db, None, None
+        d_res = dy if (ctx.has_residual and ctx.needs_input_grad[5]) else None
+        return dx, dw, db, None, None, d_res
 
 
 class _FusedMLP(torch.autograd.Function):
@@ -132,7 +140,7 @@ class _FusedMLP(torch.autograd.Function):
     gradient."""
 
     @staticmethod
-    def forward(ctx, x, w_in, b_in, w_out, b_out):
+    def forward(ctx, x, w_in, b_in, w_out, b_out, residual=None):
         k = x.size(-1)
         x2 = x.reshape(-1, k)
         need_grad = any(ctx.needs_input_grad)
@@ -143,9 +151,16 @@ class _FusedMLP(torch.autograd.Function):
             z = torch.empty(x2.size(0), w_in.size(0), dtype=x.dtype, device=x.device)
         h = gemm(x2, w_in, False, False, bias=b_in, aux_out=z, flags=flags)
         y = torch.empty(*x.shape[:-1], w_out.size(0), dtype=x.dtype, device=x.device)
-        gemm(h, w_out, False, False, bias=b_out, out=y.view(-1, w_out.size(0)), flags=FLAG_BIAS if b_out is not None else 0)
+        res2 = None
+        if residual is not None:
+            res2 = residual.reshape(-1, w_out.size(0))
+            if res2.stride(-1) != 1:
+                res2 = res2.contiguous()
+        gemm(h, w_out, False, False, bias=b_out, aux=res2, out=y.view(-1, w_out.size(0)),
+             flags=(FLAG_BIAS if b_out is not None else 0) | (FLAG_RESIDUAL if residual is not None else 0))
         ctx.save_for_backward(x2, w_in, w_out, z, h)
         ctx.has_b_in, ctx.has_b_out, ctx.in_shape = b_in is not None, b_out is not None, x.shape
+        ctx.has_residual = residual is not None
         return y
 
     @staticmethod
@@ -167,7 +182,8 @@ class _FusedMLP(torch.autograd.Function):
             dw_in = weight_grad(w_in, dz, x2)
         if ctx.has_b_in and ctx.needs_input_grad[2]:
             db_in = ext.colsum(dz).to(dy.dtype)
-        return dx, dw_in, db_in, dw_out, db_out
+        d_res = dy if (ctx.has_residual and ctx.needs_input_grad[5]) else None
+        return dx, dw_in, db_in, dw_out, db_out, d_res
 
 
 def fused_mlp_ok(x: Tensor, w_in: Tensor, w_out: Tensor) -> bool:
@@ -176,11 +192,71 @@ def fused_mlp_ok(x: Tensor, w_in: Tensor, w_out: Tensor) -> bool:
             and x.numel() // x.size(-1) > SMALL_M_ROWS)
 
 
-def fused_mlp(x: Tensor, w_in: Tensor, b_in: Optional[Tensor], w_out: Tensor, b_out: Optional[Tensor]) -> Tensor:
-    return _FusedMLP.apply(x, w_in, b_in, w_out, b_out)
+def fused_mlp(x: Tensor, w_in: Tensor, b_in: Optional[Tensor], w_out: Tensor, b_out: Optional[Tensor],
+              residual: Optional[Tensor] = None) -> Tensor:
+    """``fc_out(gelu(fc_in(x))) (+ residual)``; the residual is added in fc_out's GEMM epilogue."""
+    return _FusedMLP.apply(x, w_in, b_in, w_out, b_out, residual)
 
 
-def linear(x: Tensor, weight: Tensor, bias: Optional[Tensor], reversed_: bool, activation: Optional[str]) -> Tensor:
+class _QKVLinear(torch.autograd.Function):
+    """Three bias-free ``[out, in]`` projections of the same input. Forward is three GEMMs; the point is the
+    backward: the three input-gradient GEMMs accumulate into one tensor in their epilogues instead of leaving two
+    ``[rows, hidden]`` additions to autograd."""
+
+    @staticmethod
+    def forward(ctx, x, wq, wk, wv):
+        k = x.size(-1)
+        x2 = x.reshape(-1, k)
+        outs = []
+        for w in (wq, wk, wv):
+            y = torch.empty(*x.shape[:-1], w.size(0), dtype=x.dtype, device=x.device)
+            gemm(x2, w, False, False, out=y.view(-1, w.size(0)))
+            outs.append(y)
+        ctx.save_for_backward(x2, wq, wk, wv)
+        ctx.in_shape = x.shape
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        x2, wq, wk, wv = ctx.saved_tensors
+        dx = None
+        dws = [None, None, None]
+        for i, (d, w) in enumerate(((dq, wq), (dk, wk), (dv, wv))):
+            if d is None:
+                continue
+            d2 = d.reshape(-1, d.size(-1))
+            if not d2.is_contiguous():
+                d2 = d2.contiguous()
+            if ctx.needs_input_grad[0]:
+                if dx is None:
+                    dx = gemm(d2, w, False, True)
+                else:
+                    gemm(d2, w, False, True, out=dx, flags=FLAG_ACCUMULATE)
+            if ctx.needs_input_grad[1 + i]:
+                dws[i] = weight_grad(w, d2, x2)
+        return (dx.view(ctx.in_shape) if dx is not None else None, *dws)
+
+
+def qkv_linear(x: Tensor, wq: Tensor, wk: Tensor, wv: Tensor):
+    return _QKVLinear.apply(x, wq, wk, wv)
+
+
+def qkv_linear_ok(x: Tensor, *ws: Tensor) -> bool:
+    return (x.is_cuda and x.dtype in _16BIT and x.numel() > 0 and x.size(-1) % 8 == 0
+            and x.numel() // x.size(-1) > SMALL_M_ROWS and all(w.dtype == x.dtype and w.size(0) % 8 == 0 for w in ws))
+
+
+def linear(x: Tensor, weight: Tensor, bias: Optional[Tensor], reversed_: bool, activation: Optional[str],
+           residual: Optional[Tensor] = None) -> Tensor:
+    """``act(x W^T + b)``; ``residual`` (no activation) is added in the GEMM epilogue on the large-input path."""
+    if residual is not None:
+        n_ = weight.size(1) if reversed_ else weight.size(0)
+        big = (activation is None and x.is_cuda and x.dtype in _16BIT and weight.dtype == x.dtype and residual.dtype == x.dtype
+               and x.size(-1) % 8 == 0 and n_ % 8 == 0 and x.numel() // max(x.size(-1), 1) > SMALL_M_ROWS
+               and (bias is None or bias.dtype == x.dtype))
+        if big:
+            return _Linear.apply(x, weight, bias, reversed_, False, residual)
+        return linear(x, weight, bias, reversed_, activation) + residual
     if activation is not None and activation not in _GELU:
         raise ValueError(f"unsupported fused activation {activation!r}")
     n = weight.size(1) if reversed_ else weight.size(0)
@@ -198,7 +274,7 @@ def linear(x: Tensor, weight: Tensor, bias: Optional[Tensor], reversed_: bool, a
         else:
             y = _ext().gemm_small_m(x2, _as_operand(weight), int(reversed_), bias, gelu_from)
         return y.view(*x.shape[:-1], n)
-    return _Linear.apply(x, weight, bias, reversed_, activation is not None)
+    return _Linear.apply(x, weight, bias, reversed_, activation is not None, None)
 
 
 def small_m_ok(x: Tensor, *weights: Tensor) -> bool:

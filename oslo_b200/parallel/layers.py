@@ -23,10 +23,12 @@ _GELU_NAMES = ("gelu", "gelu_new", "gelu_tanh", "gelu_pytorch_tanh")
 
 
 def _linear(x: Tensor, weight: Tensor, bias: Optional[Tensor], reversed: bool, fused: bool,
-            activation: Optional[str] = None) -> Tensor:
-    if fused:
-        return ops.linear(x, weight, bias, reversed, activation)
-    return ops.reference.linear(x, weight, bias, reversed, activation)
+            activation: Optional[str] = None, residual: Optional[Tensor] = None) -> Tensor:
+    if fused and residual is not None and x.is_cuda:
+        from ..ops import cuda_ops
+        return cuda_ops.linear(x, weight, bias, reversed, activation, residual)
+    y = ops.linear(x, weight, bias, reversed, activation) if fused else ops.reference.linear(x, weight, bias, reversed, activation)
+    return y if residual is None else y + residual
 
 
 class Linear(nn.Linear):
@@ -35,8 +37,9 @@ class Linear(nn.Linear):
     oslo_fused = False
     reversed = False
 
-    def forward(self, x: Tensor, activation: Optional[str] = None) -> Tensor:
-        return _linear(x, self.weight, self.bias, False, self.oslo_fused, activation)
+    def forward(self, x: Tensor, activation: Optional[str] = None, residual: Optional[Tensor] = None) -> Tensor:
+        """``residual`` is added to the result (inside the GEMM epilogue on the kernel path)."""
+        return _linear(x, self.weight, self.bias, False, self.oslo_fused, activation, residual)
 
 
 class Conv1D(nn.Module):
