@@ -541,6 +541,26 @@ Tensor rotary_append(const Tensor& q, const Tensor& k, const Tensor& v, Tensor k
   return q_out;
 }
 
+// Vocab-parallel embedding: ids int64 [tokens], weight = this rank's [hi - lo, H] shard; returns [tokens, H]
+Tensor vocab_embed(const Tensor& ids, const Tensor& weight, int64_t lo, int64_t hi, int64_t peer_ptrs_dev,
+                   int64_t mc_ptr, int64_t signal_ptrs_dev, Tensor counters, int64_t half_bytes, int64_t rank,
+                   int64_t world, bool use_multimem) {
+  TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous(), "vocab_embed: ids must be contiguous int64");
+  TORCH_CHECK(weight.is_cuda() && weight.dim() == 2 && weight.is_contiguous() && weight.size(0) == hi - lo, "vocab_embed: bad weight shard");
+  TORCH_CHECK(counters.is_cuda() && counters.scalar_type() == at::kInt && counters.numel() >= 64, "vocab_embed: bad counters");
+  c10::cuda::CUDAGuard guard(ids.device());
+  const int64_t tokens = ids.numel(), H = weight.size(1);
+  Tensor out = at::empty({tokens, H}, weight.options());
+  auto& st = dev_state(ids.get_device());
+  check_rc(oslo_vocab_embed(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), weight.data_ptr(), out.data_ptr(),
+                            reinterpret_cast<void* const*>(peer_ptrs_dev), reinterpret_cast<void*>(mc_ptr),
+                            reinterpret_cast<uint32_t* const*>(signal_ptrs_dev),
+                            reinterpret_cast<uint32_t*>(counters.data_ptr<int>()), tokens, static_cast<int>(H), lo, hi,
+                            half_bytes, static_cast<int>(rank), static_cast<int>(world), dt_code(weight),
+                            use_multimem ? 1 : 0, st.err.data_ptr<int>(), st.sms, cur_stream()), "vocab_embed");
+  return out;
+}
+
 // In-place one-kernel all-reduce of a small tensor through two alternating staging halves of a symmetric buffer.
 void allreduce_oneshot(Tensor x, int64_t peer_ptrs_dev, int64_t mc_ptr, int64_t signal_ptrs_dev, Tensor counters,
                        int64_t stage_off, int64_t half_bytes, int64_t rank, int64_t world, bool use_multimem) {
@@ -584,6 +604,7 @@ TORCH_LIBRARY(oslo_b200, m) {
   m.def("gemm_comm(Tensor a, Tensor b, int a_mn, int b_mn, Tensor? bias, Tensor(a!)? aux_out, Tensor(b!)? out, int flags, float alpha, int M, int N, int K, int peer_bufs_dev, int own_buf, int mc_base, int data_off, int flag_off, int flag_bytes, int rank, int world, int epoch, int done_base, int mode, bool use_multimem, Tensor(c!)? trace) -> int", &gemm_comm);
   m.def("gemv_rows(Tensor x1, Tensor? x2, Tensor w, Tensor? bias, int gelu_from, Tensor? res=None) -> Tensor", &gemv_rows);
   m.def("rotary_append(Tensor q, Tensor k, Tensor v, Tensor(a!) kc, Tensor(b!) vc, Tensor lengths, Tensor write_index, int rotary_dim, float base) -> Tensor", &rotary_append);
+  m.def("vocab_embed(Tensor ids, Tensor weight, int lo, int hi, int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(a!) counters, int half_bytes, int rank, int world, bool use_multimem) -> Tensor", &vocab_embed);
   m.def("allreduce_oneshot(Tensor(a!) x, int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(b!) counters, int stage_off, int half_bytes, int rank, int world, bool use_multimem) -> ()", &allreduce_oneshot);
   m.def("allreduce_symm(int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(a!) out, int numel, int rank, int world, bool use_multimem) -> ()", &allreduce_symm);
 }

@@ -171,7 +171,75 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const void* in, 
   if (threadIdx.x == 0) counters[blockIdx.x] += 1;
 }
 
+// Vocab-parallel embedding lookup fused with its collective. Exactly one rank owns the row of a token id, so no
+// reduction is needed: the owner stores the row into EVERY rank's staging buffer (multimem.st through the switch,
+// or one plain store per peer), block b of every rank handles the same token range, meets block b of the other
+// ranks once, and copies its range out of its own staging buffer. Half as many bytes cross the links as in the
+// "masked lookup + all-reduce" form, and the lookup, mask, zero-fill and collective are one launch. Staging halves
+// alternate by a device-side per-block counter exactly as in the one-shot all-reduce.
+template <typename T>
+__global__ void __launch_bounds__(512) vocab_embed_kernel(const long long* __restrict__ ids, const T* __restrict__ weight,
+                                                          T* __restrict__ out, void* const* peer_ptrs, void* mc_ptr,
+                                                          uint32_t* const* signal_ptrs, uint32_t* counters,
+                                                          long long tokens, int H, long long lo, long long hi,
+                                                          long long half16, int rank, int world, int use_multimem,
+                                                          int* err) {
+  const uint32_t parity = counters[blockIdx.x] & 1u;
+  const long long base16 = parity * half16;
+  const int vpr = H / 8;                                         // 16-byte vectors per row
+  const long long per = (tokens + gridDim.x - 1) / gridDim.x;    // tokens of this block (same split on every rank)
+  const long long t0 = blockIdx.x * per, t1 = min(tokens, t0 + per);
+  const long long total = (t1 > t0 ? t1 - t0 : 0) * vpr;
+  for (long long i = threadIdx.x; i < total; i += blockDim.x) {
+    const long long t = t0 + i / vpr;
+    const int v = static_cast<int>(i % vpr);
+    const long long id = ids[t];
+    if (id >= lo && id < hi) {
+      const uint4 val = reinterpret_cast<const uint4*>(weight + (id - lo) * H)[v];
+      const long long off = base16 + t * vpr + v;
+      if (use_multimem) {
+        multimem_st(reinterpret_cast<uint4*>(mc_ptr) + off, val);
+      } else {
+        for (int r = 0; r < world; ++r) (reinterpret_cast<uint4*>(peer_ptrs[r]) + off)[0] = val;
+      }
+    }
+  }
+  if (!block_barrier_all_ranks(signal_ptrs, rank, world, 0, err)) return;
+  const uint4* mine = reinterpret_cast<const uint4*>(peer_ptrs[rank]) + base16 + t0 * vpr;
+  uint4* dst = reinterpret_cast<uint4*>(out) + t0 * vpr;
+  for (long long i = threadIdx.x; i < total; i += blockDim.x) dst[i] = mine[i];
+  if (threadIdx.x == 0) counters[blockIdx.x] += 1;
+}
+
 }  // namespace oslo
+
+// out [tokens, H] = rows of the vocabulary-sharded weight [hi - lo, H] (this rank owns ids in [lo, hi)); every id must
+// be owned by exactly one rank of the group. `half_bytes`: size of one of the two staging halves at the start of
+// the symmetric buffer (tokens * H * 2 <= half_bytes). `counters`: device uint32[>= 64], zeroed once.
+extern "C" int oslo_vocab_embed(const long long* ids, const void* weight, void* out, void* const* peer_ptrs_dev,
+                                void* mc_ptr, uint32_t* const* signal_ptrs_dev, uint32_t* counters, long long tokens,
+                                int H, long long lo, long long hi, long long half_bytes, int rank, int world, int dtype,
+                                int use_multimem, int* err_word, int num_sms, cudaStream_t stream) {
+  using namespace oslo;
+  if (tokens <= 0) return 0;
+  if (H % 8 || half_bytes % 16 || tokens * H * 2 > half_bytes || world > 16) return -3;
+  int max_blocks = 2048 / 4 / (2 * world);
+  if (max_blocks > 64) max_blocks = 64;
+  if (max_blocks > num_sms) max_blocks = num_sms;
+  const int blocks = static_cast<int>(tokens < max_blocks ? tokens : max_blocks);
+  if (dtype == OSLO_DT_BF16)
+    vocab_embed_kernel<__nv_bfloat16><<<blocks, 512, 0, stream>>>(ids, (const __nv_bfloat16*)weight, (__nv_bfloat16*)out,
+                                                                  peer_ptrs_dev, mc_ptr, signal_ptrs_dev, counters, tokens,
+                                                                  H, lo, hi, half_bytes / 16, rank, world, use_multimem,
+                                                                  err_word);
+  else if (dtype == OSLO_DT_FP16)
+    vocab_embed_kernel<__half><<<blocks, 512, 0, stream>>>(ids, (const __half*)weight, (__half*)out, peer_ptrs_dev, mc_ptr,
+                                                           signal_ptrs_dev, counters, tokens, H, lo, hi, half_bytes / 16,
+                                                           rank, world, use_multimem, err_word);
+  else
+    return -2;
+  return static_cast<int>(cudaGetLastError());
+}
 
 // `counters`: device uint32[>= 64], zero-initialised once, owned by this rank. `stage_off` / `half_bytes`: byte
 // offset of the two staging halves inside the symmetric buffer and the size of one half (n * 2 <= half_bytes).

@@ -146,6 +146,13 @@ int oslo_rotary_append(const void* q, const void* k, const void* v, long long ld
                        void* q_out, void* kc, void* vc, const int* lengths, const long long* write_index, int B, int H,
                        int D, int Tmax, int rotary_dim, float base, int dtype, cudaStream_t stream);
 
+// vocab-parallel embedding lookup + its collective in one kernel (comm.cu): the owner of a token's row stores it into
+// every rank's staging half of the symmetric buffer, one cross-rank barrier, copy-out
+int oslo_vocab_embed(const long long* ids, const void* weight, void* out, void* const* peer_ptrs_dev, void* mc_ptr,
+                     uint32_t* const* signal_ptrs_dev, uint32_t* counters, long long tokens, int H, long long lo,
+                     long long hi, long long half_bytes, int rank, int world, int dtype, int use_multimem, int* err_word,
+                     int num_sms, cudaStream_t stream);
+
 // one-kernel all-reduce for small tensors (comm.cu): in -> staging half in symmetric memory -> sum over ranks -> out
 int oslo_allreduce_oneshot(const void* in, void* out, void* const* peer_ptrs_dev, void* mc_ptr,
                            uint32_t* const* signal_ptrs_dev, uint32_t* counters, long long n, long long stage_off,

@@ -101,6 +101,13 @@ class VocabParallelEmbedding(nn.Embedding):
         if self.mpu is None or self.mpu.tp == 1:
             return F.embedding(ids, self.weight, self.padding_idx)
         lo, hi = self.vocab_range()
+        if self.oslo_fused and ids.is_cuda and self.mpu.backend == "nccl" and self.padding_idx is None:
+            from ..config import get_config
+            if get_config().fused_tp_comm and ops.kernels_available():
+                from .symmetric import get_workspace, vocab_embed, vocab_embed_usable
+                ws = get_workspace(self.mpu.get_tensor_parallel_group())
+                if vocab_embed_usable(ws, ids, self.weight):
+                    return vocab_embed(ws, ids, self.weight, lo, hi)   # lookup + collective in one kernel
         outside = (ids < lo) | (ids >= hi)
         local = (ids - lo).masked_fill(outside, 0)
         out = F.embedding(local, self.weight)

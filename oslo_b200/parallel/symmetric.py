@@ -46,6 +46,9 @@ class SymmetricWorkspace:
         self.oneshot_half = ONESHOT_HALF if self.numel * 2 >= 4 * ONESHOT_HALF else 0
         self.oneshot_off = self.numel * 2 - 2 * self.oneshot_half
         self.oneshot_counters = torch.zeros(64, dtype=torch.int32, device=self.device)
+        # the rest of the buffer, cut in two, stages the fused vocab-parallel embedding lookup
+        self.embed_half = (self.oneshot_off // 2) // 256 * 256
+        self.embed_counters = torch.zeros(64, dtype=torch.int32, device=self.device)
         self.handle.barrier()
 
     @property
@@ -82,6 +85,43 @@ class SymmetricWorkspace:
         if use_multimem:
             flat.copy_(stage)
         return x
+
+
+class _VocabEmbed(torch.autograd.Function):
+    """Lookup in a vocabulary-sharded table + its collective as one kernel (``vocab_embed_kernel``): the rank that
+    owns a token's row stores it into every rank's staging buffer. Backward is local: every rank holds the whole
+    output gradient and scatters the rows of the ids it owns into its shard."""
+
+    @staticmethod
+    def forward(ctx, ids, weight, lo, hi, ws):
+        flat = ids.reshape(-1).contiguous()
+        use_mm = bool(get_config().use_multimem) and ws.has_multicast
+        out = ops.load_ext(required=True).vocab_embed(flat, weight, lo, hi, ws.peer_ptrs_dev, ws.mc_ptr, ws.signal_ptrs_dev,
+                                                     ws.embed_counters, ws.embed_half, ws.rank, ws.world, use_mm)
+        ctx.save_for_backward(flat)
+        ctx.cfg = (lo, hi, weight.size(0))
+        return out.view(*ids.shape, weight.size(1))
+
+    @staticmethod
+    def backward(ctx, dy):
+        (flat,) = ctx.saved_tensors
+        lo, hi, rows = ctx.cfg
+        owned = (flat >= lo) & (flat < hi)
+        local = (flat - lo).masked_fill(~owned, 0)
+        g = dy.reshape(flat.numel(), -1).masked_fill(~owned.unsqueeze(-1), 0.0)
+        dw = torch.ops.aten.embedding_dense_backward(g, local, rows, -1, False)
+        return None, dw, None, None, None
+
+
+def vocab_embed_usable(ws: "SymmetricWorkspace", ids: torch.Tensor, weight: torch.Tensor) -> bool:
+    """16-bit contiguous shard with rows of a multiple of 8 elements, and an output that fits one staging half."""
+    return (weight.is_cuda and weight.dtype in (torch.bfloat16, torch.float16) and weight.dim() == 2
+            and weight.size(1) % 8 == 0 and weight.is_contiguous()
+            and 0 < ids.numel() * weight.size(1) * 2 <= ws.embed_half)
+
+
+def vocab_embed(ws: "SymmetricWorkspace", ids: torch.Tensor, weight: torch.Tensor, lo: int, hi: int) -> torch.Tensor:
+    return _VocabEmbed.apply(ids, weight, int(lo), int(hi), ws)
 
 
 def get_workspace(group, nbytes: Optional[int] = None) -> SymmetricWorkspace:

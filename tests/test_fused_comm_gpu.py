@@ -53,6 +53,40 @@ def _check_ops(rank, world):
         assert int(ext.error_word(a).item()) == 0
 
 
+def _check_vocab_embed(rank, world):
+    """Fused vocab-parallel embedding (owner pushes rows, one barrier) against a lookup in the whole table."""
+    import torch.distributed as dist
+    import oslo_b200 as ob
+    from oslo_b200.parallel.mpu import MPU
+    from oslo_b200.parallel.layers import VocabParallelEmbedding
+    from oslo_b200.parallel.mpu import ceil_split_sizes
+    mpu = MPU(world, 1)
+    torch.manual_seed(0)
+    vocab, hidden = 1003, 256
+    full = (torch.randn(vocab, hidden, device="cuda") * 0.5).to(torch.bfloat16)
+    sizes = ceil_split_sizes(vocab, world)
+    lo = sum(sizes[:rank])
+    emb = VocabParallelEmbedding(sizes[rank], hidden).to(torch.bfloat16).cuda()
+    emb.weight.data.copy_(full[lo: lo + sizes[rank]])
+    emb.mpu, emb.full_num_embeddings, emb.oslo_fused = mpu, vocab, True
+    for step in range(3):   # consecutive calls alternate the staging halves
+        ids = torch.randint(0, vocab, (4, 37 + step), generator=torch.Generator().manual_seed(step)).cuda()
+        out = emb(ids)
+        assert torch.equal(out, full[ids]), (step, (out.float() - full[ids].float()).abs().max())
+    g = torch.randn_like(out)
+    out.backward(g)
+    ref = full.clone().float().requires_grad_(True)
+    torch.nn.functional.embedding(ids, ref).backward(g.float())
+    want = ref.grad[lo: lo + sizes[rank]]
+    assert torch.allclose(emb.weight.grad.float(), want, atol=2e-2, rtol=2e-2)
+    assert int(ob.ops.load_ext().error_word(out).item()) == 0
+
+
+@pytest.mark.multigpu
+def test_fused_vocab_embedding_world2():
+    run_gpus(_check_vocab_embed, 2)
+
+
 def test_fused_ops_world1():
     run_gpus(_check_ops, 1)
 
