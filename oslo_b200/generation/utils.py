@@ -140,7 +140,10 @@ class GenerationMixin:
                  forced_bos_token_id: Optional[int] = None, forced_eos_token_id: Optional[int] = None,
                  remove_invalid_values: Optional[bool] = None, synced_gpus: bool = False,
                  fused_no_repeat_ngram_blocking: Optional[bool] = None, use_static_cache: bool = True,
-                 **model_kwargs) -> Union[Tensor, GenerateOutput]:
+                 cuda_graph: bool = False, **model_kwargs) -> Union[Tensor, GenerateOutput]:
+        """``cuda_graph=True`` (not in the reference) runs plain greedy decoding - one beam, no sampling, no logits
+        processors, no attention mask - through ``GraphedGreedyDecoder``: eager prefill, then one CUDA-graph replay per
+        token. Any other combination ignores the flag."""
         cfg = self.config
 
         def pick(v, name, default=None):
@@ -213,6 +216,9 @@ class GenerationMixin:
         if num_beams == 1 and not do_sample:
             if num_return_sequences > 1:
                 raise ValueError("greedy search returns one sequence; use sampling or beams")
+            if (cuda_graph and len(procs) == 0 and model_kwargs.get("attention_mask") is None and not output_scores
+                    and max_time is None and use_cache and not getattr(self, "is_pipeline_parallelized", lambda: False)()):
+                return self._graph_greedy(input_ids, max_length, pad_token_id, eos_token_id, return_dict_in_generate)
             return self.greedy_search(input_ids, procs, stops, **common, **model_kwargs)
         if num_beams == 1 and do_sample:
             warper = self._get_logits_warper(top_k, top_p, temperature, num_beams)
@@ -230,6 +236,27 @@ class GenerationMixin:
             warper = self._get_logits_warper(top_k, top_p, temperature, num_beams)
             return self.beam_sample(input_ids, scorer, procs, stops, warper, **common, **model_kwargs)
         return self.beam_search(input_ids, scorer, procs, stops, **common, **model_kwargs)
+
+    def _graph_greedy(self, input_ids, max_length, pad_token_id, eos_token_id, return_dict):
+        """Greedy search through the CUDA-graph decoder; rows that hit ``eos_token_id`` are padded afterwards and
+        the result is cut where the slowest row finished, which is what ``greedy_search`` returns."""
+        from .graph_decode import GraphedGreedyDecoder
+        dec = getattr(self, "_graph_decoder", None)
+        if dec is None or dec.max_len < max_length:
+            dec = GraphedGreedyDecoder(self, max_len=max_length)
+            object.__setattr__(self, "_graph_decoder", dec)
+        cur_len = input_ids.shape[-1]
+        seq = dec.generate(input_ids, max_length - cur_len)
+        if eos_token_id is not None:
+            new = seq[:, cur_len:]
+            is_eos = new == eos_token_id
+            after = (is_eos.long().cumsum(dim=1) - is_eos.long()) > 0      # strictly after the first eos of the row
+            new = new.masked_fill(after, pad_token_id)
+            done_at = torch.where(is_eos.any(dim=1), is_eos.long().argmax(dim=1) + 1,
+                                  torch.full_like(is_eos[:, 0], new.size(1), dtype=torch.long))
+            keep = int(done_at.max())
+            seq = torch.cat([seq[:, :cur_len], new[:, :keep]], dim=1)
+        return self._finish(seq, None, return_dict)
 
     # ------------------------------------------------------------------ search loops
     def _all_done(self, finished_here: bool, synced_gpus: bool) -> bool:

@@ -82,15 +82,37 @@ def test_roofline_and_config(monkeypatch):
     assert c.ddp_bucket_mb == 32 and c.use_multimem is False
 
 
-def test_graphed_greedy_decoder_matches_generate_on_cpu():
+@pytest.mark.parametrize("kind", ["gptj", "gpt2", "gpt_neo"])
+def test_graphed_greedy_decoder_matches_generate_on_cpu(kind):
     """The device-position cache bookkeeping of the CUDA-graph decoder, run eagerly, equals generate()."""
     import oslo_b200 as ob
     from oslo_b200.generation import GraphedGreedyDecoder
     torch.manual_seed(0)
-    cfg = ob.GPTJConfig(vocab_size=512, n_positions=128, n_embd=64, n_layer=2, n_head=4, rotary_dim=8)
-    model = ob.GPTJForCausalLM(cfg).eval()
+    if kind == "gptj":
+        model = ob.GPTJForCausalLM(ob.GPTJConfig(vocab_size=512, n_positions=128, n_embd=64, n_layer=2, n_head=4,
+                                                 rotary_dim=8)).eval()
+    elif kind == "gpt2":
+        model = ob.GPT2LMHeadModel(ob.GPT2Config(vocab_size=512, n_positions=128, n_embd=64, n_layer=2, n_head=4)).eval()
+    else:
+        model = ob.GPTNeoForCausalLM(ob.GPTNeoConfig(vocab_size=512, max_position_embeddings=128, hidden_size=64,
+                                                     num_layers=2, num_heads=4, window_size=8)).eval()
     ids = torch.randint(0, 512, (2, 7))
     dec = GraphedGreedyDecoder(model, max_len=64)
     for prompt, n_new in ((7, 12), (5, 10)):
         want = model.generate(ids[:, :prompt], max_length=prompt + n_new, do_sample=False)
         assert torch.equal(dec.generate(ids[:, :prompt], n_new), want)
+
+
+def test_generate_cuda_graph_flag_equals_greedy_search_with_eos():
+    """generate(cuda_graph=True) pads rows after their eos and stops where greedy_search stops."""
+    import oslo_b200 as ob
+    torch.manual_seed(0)
+    cfg = ob.GPTJConfig(vocab_size=64, n_positions=128, n_embd=64, n_layer=2, n_head=4, rotary_dim=8)
+    model = ob.GPTJForCausalLM(cfg).eval()
+    for rows in (1, 3):
+        ids = torch.randint(0, 64, (rows, 7))
+        full = model.generate(ids, max_length=32, do_sample=False)
+        for eos in sorted(set(full[0, 7:].tolist()))[:6] + [None]:
+            want = model.generate(ids, max_length=32, do_sample=False, eos_token_id=eos, pad_token_id=0)
+            got = model.generate(ids, max_length=32, do_sample=False, eos_token_id=eos, pad_token_id=0, cuda_graph=True)
+            assert want.shape == got.shape and torch.equal(want, got), (rows, eos)
