@@ -103,7 +103,7 @@ class VocabParallelEmbedding(nn.Embedding):
         lo, hi = self.vocab_range()
         if self.oslo_fused and ids.is_cuda and self.mpu.backend == "nccl" and self.padding_idx is None:
             from ..config import get_config
-            if get_config().fused_tp_comm and ops.kernels_available():
+            if get_config().fused_tp_comm and get_config().fused_vocab_embed and ops.kernels_available():
                 from .symmetric import get_workspace, vocab_embed, vocab_embed_usable
                 ws = get_workspace(self.mpu.get_tensor_parallel_group())
                 if vocab_embed_usable(ws, ids, self.weight):

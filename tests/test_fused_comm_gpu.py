@@ -60,6 +60,8 @@ def _check_vocab_embed(rank, world):
     from oslo_b200.parallel.mpu import MPU
     from oslo_b200.parallel.layers import VocabParallelEmbedding
     from oslo_b200.parallel.mpu import ceil_split_sizes
+    from oslo_b200.config import set_config
+    set_config(fused_vocab_embed=True)
     mpu = MPU(world, 1)
     torch.manual_seed(0)
     vocab, hidden = 1003, 256
