@@ -24,7 +24,7 @@ class OsloConfig:
     backend: str = ""                    # "" = nccl on CUDA, gloo on CPU
     allow_fallback: bool = False         # let CUDA tensors run library ops when the extension is missing
     fused_tp_comm: bool = True           # GEMM + all-reduce / all-gather kernels over symmetric memory
-    fused_vocab_embed: bool = False      # vocab-parallel embedding: owner-pushes-rows kernel instead of masked lookup + all-reduce
+    fused_vocab_embed: bool = True       # vocab-parallel embedding: owner-pushes-rows kernel instead of masked lookup + all-reduce
     use_multimem: bool = True            # NVSwitch multicast (NVLS) loads / stores inside those kernels
     symm_buffer_mb: int = 256            # symmetric-memory workspace per tensor-parallel group
     symm_allreduce_max_bytes: int = 1 << 20  # no-grad tensor-parallel all-reduces up to this size use the symmetric-memory kernel (0 = always NCCL)
