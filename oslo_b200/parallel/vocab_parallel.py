@@ -96,6 +96,9 @@ class _LinearCrossEntropy(torch.autograd.Function):
         on_kernels = fused and hidden.is_cuda
         dw = None if on_kernels else torch.zeros_like(weight, dtype=torch.float32)
         dw_acc = None
+        # weights whose gradient lives in the optimizer's flat buffer take the chunks' products there directly
+        direct_dw = (on_kernels and getattr(weight, "_oslo_accum_grad", False) and weight.grad is not None
+                     and weight.grad.dtype == weight.dtype and weight.grad.is_contiguous() and ctx.needs_input_grad[1])
         db = torch.zeros(weight.size(0), dtype=torch.float32, device=weight.device) if bias is not None else None
         for s in range(0, n, ctx.chunk):
             e = min(n, s + ctx.chunk)
@@ -104,19 +107,32 @@ class _LinearCrossEntropy(torch.autograd.Function):
             d = _grad_inplace(lg, labels[s:e], lo, lse[s:e], scale[s:e], fused)
             if on_kernels:
                 from ..ops import cuda_ops
-                dx[s:e] = cuda_ops.gemm_nn(d, weight)
-                part = cuda_ops.gemm_tn(d, x, out_dtype=torch.float32)
-                dw_acc = part if dw_acc is None else dw_acc.add_(part)
+                cuda_ops.gemm(d, weight, False, True, out=dx[s:e])      # written in place, no chunk copy
+                if direct_dw:
+                    # adds into the flat gradient buffer; only the last chunk goes through weight_grad, whose
+                    # gradient-ready hook must fire once per backward pass
+                    if e == n:
+                        part = cuda_ops.weight_grad(weight, d, x)
+                        if part is not None:   # the in-place route declined after all: add the product by hand
+                            weight.grad.add_(part)
+                    else:
+                        cuda_ops.gemm(d, x, True, True, out=weight.grad, flags=cuda_ops.FLAG_ACCUMULATE)
+                elif dw_acc is None:
+                    dw_acc = cuda_ops.gemm_tn(d, x, out_dtype=torch.float32)
+                else:                                                   # later chunks accumulate in the epilogue
+                    cuda_ops.gemm(d, x, True, True, out=dw_acc, flags=cuda_ops.FLAG_OUT_FP32 | cuda_ops.FLAG_ACCUMULATE)
+                if db is not None:
+                    db += cuda_ops._ext().colsum(d)                     # fp32 column sums without an fp32 copy of d
             else:
                 dx[s:e] = (d @ weight).to(dx.dtype)
                 dw += d.float().t() @ x.float()
-            if db is not None:
-                db += d.float().sum(0)
+                if db is not None:
+                    db += d.float().sum(0)
         if dw_acc is not None:
             dw = dw_acc
         if mpu is not None and mpu.tp > 1:
             dist.all_reduce(dx, group=mpu.get_tensor_parallel_group())
-        return (dx, dw.to(weight.dtype), db.to(bias.dtype) if db is not None else None,
+        return (dx, dw.to(weight.dtype) if dw is not None else None, db.to(bias.dtype) if db is not None else None,
                 None, None, None, None, None, None)
 
 
