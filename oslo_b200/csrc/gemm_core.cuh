@@ -49,6 +49,7 @@ struct GemmParams {
   float alpha;
   int* err;
   int tiles_m, tiles_n;
+  int group_m = 8;      // row blocks per column sweep of the tile raster
   int split_k = 1;      // > 1: every tile's k range is cut into this many work items; slice s writes its fp32 partial
                         // result to plane s of D ([split_k, M, ldd] fp32); other epilogue flags are ignored
   CommParams comm;
@@ -94,8 +95,7 @@ __device__ __forceinline__ void unpack8(const uint4& v, float* f, bool fp16) {
 }
 
 // grouped raster: walk GROUP_M row-blocks per column sweep so concurrently running CTAs share B tiles in L2
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
-  constexpr int GROUP_M = 8;
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn, int GROUP_M = 8) {
   const int per_group = GROUP_M * tiles_n;
   const int g = tile / per_group;
   const int first_m = g * GROUP_M;

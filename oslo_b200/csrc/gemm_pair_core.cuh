@@ -79,7 +79,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       bool ok = true;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += n_clusters) {
         int tm, tn;
-        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn, p.group_m);
         const int m0 = tm * PAIR_TILE + static_cast<int>(rank) * BM;
         const int n0 = tn * PAIR_TILE + static_cast<int>(rank) * BM;
         for (int kb = 0; kb < kblocks; ++kb) {
@@ -160,7 +160,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
     for (int tile = cluster_id; tile < num_tiles && ok; tile += n_clusters, ++local) {
       const int buf = local & 1;
       int tm, tn;
-      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn, p.group_m);
       ok = mbar_wait(tfull_bar(buf), acc_phase[buf], abort_flag, p.err, ERR_WAIT_TMEM_FULL);
       if (!ok) break;
       acc_phase[buf] ^= 1;

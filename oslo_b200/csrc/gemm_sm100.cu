@@ -119,6 +119,8 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams&
   }
   p.tiles_m = (p.M + PAIR_TILE - 1) / PAIR_TILE;
   p.tiles_n = (p.N + PAIR_TILE - 1) / PAIR_TILE;
+  static const int group_m = [] { const char* e = getenv("OSLO_B200_GEMM_GROUP_M"); const int v = e ? atoi(e) : 8; return v > 0 ? v : 8; }();
+  p.group_m = group_m;
   const int tiles = p.tiles_m * p.tiles_n;
   // persistent kernel: no more pairs than can be resident at once (pairs are placed as clusters of two SMs)
   static int max_pairs = 0;
