@@ -438,7 +438,8 @@ Tensor decode_attn(const Tensor& q, const Tensor& kc, const Tensor& vc, const Te
 // mode 1: all-reduce, the summed [M,N] is left in the staging matrix at data_off (returned view is built in
 // Python); mode 2: reduce-scatter into `out` [M/world, N]; mode 3: all-gather of `a` shards, product into `out`.
 int64_t gemm_comm(const Tensor& a, const Tensor& b, int64_t a_mn, int64_t b_mn, const optional<Tensor>& bias,
-               const optional<Tensor>& aux_out, const optional<Tensor>& out, int64_t flags, double alpha, int64_t M,
+               const optional<Tensor>& aux, const optional<Tensor>& aux_out, const optional<Tensor>& out, int64_t flags,
+               double alpha, int64_t M,
                int64_t N, int64_t K, int64_t peer_bufs_dev, int64_t own_buf, int64_t mc_base, int64_t data_off,
                int64_t flag_off, int64_t flag_bytes, int64_t rank, int64_t world, int64_t epoch, int64_t done_base,
                int64_t mode, bool use_multimem, const optional<Tensor>& trace) {
@@ -465,13 +466,20 @@ int64_t gemm_comm(const Tensor& a, const Tensor& b, int64_t a_mn, int64_t b_mn, 
     ld_aux_out = static_cast<int>(aux_out->stride(0));
   }
   if (fl & GEMM_FLAG_BIAS) TORCH_CHECK(bias.has_value() && bias->numel() == N && bias->is_contiguous(), "bad bias");
+  int ld_aux = 0;
+  if (fl & GEMM_FLAG_RESIDUAL) {
+    TORCH_CHECK(mode != 3 && aux.has_value() && aux->dim() == 2 && aux->size(0) == M && aux->size(1) == N &&
+                    aux->stride(1) == 1 && aux->scalar_type() == a.scalar_type(), "gemm_comm: bad partial-sum operand");
+    ld_aux = static_cast<int>(aux->stride(0));
+  }
   auto& st = dev_state(a.get_device());
   // tile shape must be the same on every rank: decide from the problem size only
   const int wide = (N >= 256 && ((M + 127) / 128) * ((N + 255) / 256) >= st.sms / 2) ? 1 : 0;
   const int rc = oslo_gemm_comm_16bit(
       a.data_ptr(), b.data_ptr(), static_cast<int>(M), static_cast<int>(N), static_cast<int>(K),
       static_cast<int>(a.stride(0)), static_cast<int>(b.stride(0)), static_cast<int>(a_mn), static_cast<int>(b_mn),
-      ptr_or_null(bias), const_cast<void*>(ptr_or_null(aux_out)), ld_aux_out, fl, static_cast<float>(alpha),
+      ptr_or_null(bias), (fl & GEMM_FLAG_RESIDUAL) ? aux->data_ptr() : nullptr, ld_aux,
+      const_cast<void*>(ptr_or_null(aux_out)), ld_aux_out, fl, static_cast<float>(alpha),
       reinterpret_cast<void* const*>(peer_bufs_dev), reinterpret_cast<void*>(own_buf), reinterpret_cast<void*>(mc_base),
       data_off, flag_off, flag_bytes, static_cast<int>(rank), static_cast<int>(world), static_cast<unsigned>(epoch),
       static_cast<unsigned>(done_base), static_cast<int>(mode), use_multimem ? 1 : 0, out_ptr, ld_out, wide,
@@ -601,7 +609,7 @@ TORCH_LIBRARY(oslo_b200, m) {
   m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int window, Tensor? kpm, int impl=1) -> (Tensor, Tensor)", &flash_fwd);
   m.def("flash_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale, bool causal, int window, Tensor? kpm, int impl=1) -> (Tensor, Tensor, Tensor)", &flash_bwd);
   m.def("decode_attn(Tensor q, Tensor kc, Tensor vc, Tensor lengths, float scale, int window) -> Tensor", &decode_attn);
-  m.def("gemm_comm(Tensor a, Tensor b, int a_mn, int b_mn, Tensor? bias, Tensor(a!)? aux_out, Tensor(b!)? out, int flags, float alpha, int M, int N, int K, int peer_bufs_dev, int own_buf, int mc_base, int data_off, int flag_off, int flag_bytes, int rank, int world, int epoch, int done_base, int mode, bool use_multimem, Tensor(c!)? trace) -> int", &gemm_comm);
+  m.def("gemm_comm(Tensor a, Tensor b, int a_mn, int b_mn, Tensor? bias, Tensor? aux, Tensor(a!)? aux_out, Tensor(b!)? out, int flags, float alpha, int M, int N, int K, int peer_bufs_dev, int own_buf, int mc_base, int data_off, int flag_off, int flag_bytes, int rank, int world, int epoch, int done_base, int mode, bool use_multimem, Tensor(c!)? trace) -> int", &gemm_comm);
   m.def("gemv_rows(Tensor x1, Tensor? x2, Tensor w, Tensor? bias, int gelu_from, Tensor? res=None) -> Tensor", &gemv_rows);
   m.def("rotary_append(Tensor q, Tensor k, Tensor v, Tensor(a!) kc, Tensor(b!) vc, Tensor lengths, Tensor write_index, int rotary_dim, float base) -> Tensor", &rotary_append);
   m.def("vocab_embed(Tensor ids, Tensor weight, int lo, int hi, int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(a!) counters, int half_bytes, int rank, int world, bool use_multimem) -> Tensor", &vocab_embed);

@@ -45,7 +45,7 @@ static int launch_comm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams&
 }  // namespace oslo
 
 extern "C" int oslo_gemm_comm_16bit(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int a_mn_major,
-                                    int b_mn_major, const void* bias, void* aux_out, int ld_aux_out, int flags,
+                                    int b_mn_major, const void* bias, const void* aux, int ld_aux, void* aux_out, int ld_aux_out, int flags,
                                     float alpha, void* const* peer_bufs_dev, void* own_buf, void* mc_base,
                                     long long data_off, long long flag_off, long long flag_bytes, int rank, int world,
                                     unsigned epoch, unsigned done_base, int mode, int use_multimem, void* out,
@@ -98,9 +98,16 @@ extern "C" int oslo_gemm_comm_16bit(const void* A, const void* B, int M, int N, 
     if (!a_mn_major) rc = make_tma_2d_16bit(&ta, A, K, M, lda, BM, fp16);
     else rc = make_tma_2d_16bit(&ta, A, M, K, lda, 64, fp16);
     p.D = stage; p.ldd = N;  // partial sums go to this rank's symmetric buffer
+    // epilogue math must follow the reduction, not precede it; the one exception is adding another per-rank partial
+    // sum (aux, [M, N], input dtype) to this rank's tile before it is reduced, which lets two row-parallel products
+    // (attention output projection and fc_out of a parallel block) share one collective
     if (flags & (GEMM_FLAG_BIAS | GEMM_FLAG_GELU | GEMM_FLAG_SAVE_PREACT | GEMM_FLAG_OUT_FP32 | GEMM_FLAG_ACCUMULATE |
-                 GEMM_FLAG_DGELU | GEMM_FLAG_RESIDUAL))
-      return -7;  // epilogue math must follow the reduction, not precede it
+                 GEMM_FLAG_DGELU))
+      return -7;
+    if (flags & GEMM_FLAG_RESIDUAL) {
+      if (!aux) return -7;
+      p.aux = aux; p.ld_aux = ld_aux;
+    }
   }
   if (rc) return rc;
   if (!b_mn_major) rc = make_tma_2d_16bit(&tb, B, K, N, ldb, bn, fp16);

@@ -122,8 +122,10 @@ int oslo_decode_attn(const void* q, const void* kc, const void* vc, void* o, con
 
 // GEMM fused with a tensor-parallel collective (fused_comm_gemm.cu); mode 1 = all-reduce (result left in the
 // symmetric staging matrix), 2 = reduce-scatter into out, 3 = all-gather of A then GEMM into out
+// aux / ld_aux: with GEMM_FLAG_RESIDUAL in the reduce modes, another per-rank partial sum [M, N] added before the reduction
 int oslo_gemm_comm_16bit(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int a_mn_major,
-                         int b_mn_major, const void* bias, void* aux_out, int ld_aux_out, int flags, float alpha,
+                         int b_mn_major, const void* bias, const void* aux, int ld_aux, void* aux_out, int ld_aux_out,
+                         int flags, float alpha,
                          void* const* peer_bufs_dev, void* own_buf, void* mc_base, long long data_off,
                          long long flag_off, long long flag_bytes, int rank, int world, unsigned epoch,
                          unsigned done_base, int mode, int use_multimem, void* out, int ld_out, int wide_tiles,

@@ -17,7 +17,7 @@ from ... import ops
 from ...config import get_config
 from ...fused_kernels_utils import ACT2FN, GELU_TANH_NAMES
 from ...modeling_utils import PretrainedConfig, PreTrainedModel
-from ...parallel.layers import Embedding, LayerNorm, Linear
+from ...parallel.layers import Embedding, LayerNorm, Linear, RowParallelLinear
 from ...parallel.mpu import Layer, LayerPolicy
 from ..common import (AttentionCore, CausalLMHeadMixin, DecoderBackbone, SequenceClassificationMixin,
                       maybe_dropout, merge_heads, split_heads, to_token_rows)
@@ -58,7 +58,7 @@ class GPTJAttention(AttentionCore):
 
     def forward(self, hidden_states: Tensor, layer_past=None, attention_mask=None, position_ids=None,
                 head_mask=None, use_cache=False, output_attentions=False, cache=None, layer_id=0, seq_shape=None,
-                qkv=None, residual=None):
+                qkv=None, residual=None, partial_only=False):
         b, s = seq_shape if seq_shape is not None else hidden_states.shape[:2]
         nh, hd = self.num_attention_heads, self.head_dim
         if qkv is not None:   # already projected by the block's packed decode GEMM
@@ -78,6 +78,8 @@ class GPTJAttention(AttentionCore):
         out, present, probs = self.attend_with_cache(q, k, v, layer_past, cache, layer_id, attention_mask,
                                                      use_cache, output_attentions, head_mask)
         merged = to_token_rows(merge_heads(out), seq_shape)
+        if partial_only:   # tensor parallel: leave the reduction to fc_out, which adds this partial sum to its own
+            return self.out_proj.partial_forward(merged), present, probs
         if residual is not None:   # only offered by the block when out_proj is a plain Linear and no dropout follows
             return self.out_proj(merged, residual=residual), present, probs
         out = self.out_proj(merged)
@@ -109,9 +111,15 @@ class GPTJMLP(nn.Module):
         self.activation = config.activation_function
         self.resid_pdrop = config.resid_pdrop
 
-    def forward(self, x: Tensor, h: Optional[Tensor] = None, residual: Optional[Tensor] = None) -> Tensor:
+    def forward(self, x: Tensor, h: Optional[Tensor] = None, residual: Optional[Tensor] = None,
+                partial: Optional[Tensor] = None) -> Tensor:
         """``residual`` (only passed when no dropout follows) is added to the result, inside fc_out's GEMM epilogue
-        where the fused path applies."""
+        where the fused path applies. ``partial`` (tensor parallel, no dropout): the attention output projection's
+        partial sum, reduced together with fc_out's."""
+        if partial is not None:
+            act = self.fc_in(x, activation="gelu_new") if (self.fused and self.activation in GELU_TANH_NAMES) \
+                else ACT2FN[self.activation](self.fc_in(x))
+            return self.fc_out(act, partial=partial)
         if residual is not None:
             return self._forward(x, h, residual)
         return self._forward(x, h, None)
@@ -242,6 +250,14 @@ class GPTJBlock(nn.Module):
             # that sum
             a, present, probs = self.attn(x, residual=hidden_states, **kw)
             return self.mlp(x, residual=a), present, probs
+        if (no_dropout and get_config().block_fusion and kw.get("seq_shape") is None
+                and isinstance(self.attn.out_proj, RowParallelLinear) and isinstance(self.mlp.fc_out, RowParallelLinear)
+                and self.attn.out_proj.bias is None and getattr(self.attn.out_proj, "mpu", None) is not None
+                and self.attn.out_proj.mpu.tp > 1 and not self.attn.out_proj.sequence_parallel):
+            # tensor parallel: attention projection and fc_out are both row-parallel and their sum is all the block
+            # needs, so ONE collective reduces both (the projection's partial sum rides along in fc_out's kernel)
+            a_part, present, probs = self.attn(x, partial_only=True, **kw)
+            return self.mlp(x, partial=a_part) + hidden_states, present, probs
         a, present, probs = self.attn(x, **kw)
         m = self.mlp(x)
         return a + m + hidden_states, present, probs

@@ -25,6 +25,7 @@ from ..config import get_config
 from .symmetric import SymmetricWorkspace
 
 MODE_ALLREDUCE, MODE_REDUCE_SCATTER, MODE_ALLGATHER = 1, 2, 3
+_FLAG_RESIDUAL = 16            # GEMM epilogue flag: add the aux operand (here: another per-rank partial sum)
 _FLAG_BYTES = 4 << 20          # readiness words (one per tile, rank and warp) + the completion counter, per slot
 _CONTEXTS: Dict[str, "FusedTP"] = {}
 
@@ -56,30 +57,33 @@ class FusedTP:
     def fits(self, rows: int, cols: int) -> bool:
         return rows * cols * 2 <= self.slot_bytes and rows * cols > 0
 
-    def _call(self, a, b, a_mn, b_mn, bias, aux_out, out, flags, M, N, K, mode):
+    def _call(self, a, b, a_mn, b_mn, bias, aux_out, out, flags, M, N, K, mode, aux=None):
         slot, data_off, flag_off, epoch = self._next_slot()
         inc = ops.load_ext(required=True).gemm_comm(
-            a, b, int(a_mn), int(b_mn), bias, aux_out, out, flags, 1.0, M, N, K, self.ws.peer_ptrs_dev, self.own_base,
+            a, b, int(a_mn), int(b_mn), bias, aux, aux_out, out, flags, 1.0, M, N, K, self.ws.peer_ptrs_dev, self.own_base,
             self.ws.mc_ptr if self.use_multimem else 0, data_off, flag_off, _FLAG_BYTES, self.rank, self.world,
             epoch, self.done_totals[slot] & 0xFFFFFFFF, mode, self.use_multimem, self.trace)
         self.done_totals[slot] += int(inc)
         return data_off
 
-    def gemm_all_reduce(self, a: Tensor, b: Tensor, a_mn: bool, b_mn: bool) -> Tensor:
-        """``sum over ranks of a @ b^T`` as a fresh ``[M, N]`` tensor (copied out of the workspace)."""
+    def gemm_all_reduce(self, a: Tensor, b: Tensor, a_mn: bool, b_mn: bool, partial: Optional[Tensor] = None) -> Tensor:
+        """``sum over ranks of (a @ b^T + partial)`` as a fresh ``[M, N]`` tensor (copied out of the workspace).
+        ``partial`` is another per-rank partial sum ``[M, N]`` that joins this rank's tiles before the reduction."""
         M = a.size(1) if a_mn else a.size(0)
         K = a.size(0) if a_mn else a.size(1)
         N = b.size(1) if b_mn else b.size(0)
-        off = self._call(a, b, a_mn, b_mn, None, None, None, 0, M, N, K, MODE_ALLREDUCE)
+        off = self._call(a, b, a_mn, b_mn, None, None, None, _FLAG_RESIDUAL if partial is not None else 0, M, N, K,
+                         MODE_ALLREDUCE, aux=partial)
         view = self.ws.buf.view(torch.uint8)[off: off + M * N * 2].view(a.dtype).view(M, N)
         return view.clone()
 
-    def gemm_reduce_scatter(self, a: Tensor, b: Tensor, a_mn: bool, b_mn: bool) -> Tensor:
+    def gemm_reduce_scatter(self, a: Tensor, b: Tensor, a_mn: bool, b_mn: bool, partial: Optional[Tensor] = None) -> Tensor:
         M = a.size(1) if a_mn else a.size(0)
         K = a.size(0) if a_mn else a.size(1)
         N = b.size(1) if b_mn else b.size(0)
         out = torch.empty(M // self.world, N, dtype=a.dtype, device=a.device)
-        self._call(a, b, a_mn, b_mn, None, None, out, 0, M, N, K, MODE_REDUCE_SCATTER)
+        self._call(a, b, a_mn, b_mn, None, None, out, _FLAG_RESIDUAL if partial is not None else 0, M, N, K,
+                   MODE_REDUCE_SCATTER, aux=partial)
         return out
 
     def all_gather_gemm(self, a_shard: Tensor, b: Tensor, b_mn: bool, bias: Optional[Tensor] = None,
@@ -127,11 +131,19 @@ class _RowParallelFused(torch.autograd.Function):
     """``y = all_reduce(x_shard @ W_shard^T)``; backward needs no communication."""
 
     @staticmethod
-    def forward(ctx, x, weight, reversed_, tp: FusedTP):
+    def forward(ctx, x, weight, reversed_, tp: FusedTP, partial=None):
+        """``partial``: this rank's partial sum of another row-parallel product with the same output shape; it joins
+        the tiles before the reduction, so both products share the one all-reduce."""
         x2 = x.reshape(-1, x.size(-1))
-        y = tp.gemm_all_reduce(x2, weight, False, reversed_)
+        p2 = None
+        if partial is not None:
+            p2 = partial.reshape(x2.size(0), -1)
+            if p2.stride(-1) != 1:
+                p2 = p2.contiguous()
+        y = tp.gemm_all_reduce(x2, weight, False, reversed_, partial=p2)
         ctx.save_for_backward(x2, weight)
         ctx.reversed, ctx.in_shape = reversed_, x.shape
+        ctx.partial_shape = partial.shape if partial is not None else None
         return y.view(*x.shape[:-1], y.size(-1))
 
     @staticmethod
@@ -146,7 +158,8 @@ class _RowParallelFused(torch.autograd.Function):
             dx = gemm(dy2, weight, False, not ctx.reversed).view(ctx.in_shape)
         if ctx.needs_input_grad[1]:
             dw = weight_grad(weight, x2, dy2) if ctx.reversed else weight_grad(weight, dy2, x2)
-        return dx, dw, None, None
+        d_partial = dy.reshape(ctx.partial_shape) if (ctx.partial_shape is not None and ctx.needs_input_grad[4]) else None
+        return dx, dw, None, None, d_partial
 
 
 class _ColumnParallelFused(torch.autograd.Function):

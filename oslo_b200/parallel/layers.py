@@ -166,7 +166,16 @@ class RowParallelLinear(nn.Linear):
     input_is_parallel = True
     sequence_parallel = False
 
-    def forward(self, x: Tensor, activation: Optional[str] = None) -> Tensor:
+    def partial_forward(self, x: Tensor) -> Tensor:
+        """This rank's partial sum ``x W^T`` without the reduction and without the bias; hand it to another
+        row-parallel layer's ``forward(..., partial=...)`` so that both products share one collective."""
+        if self.mpu is not None and not self.input_is_parallel:
+            x = self.mpu.scatter(x, dim=-1)
+        return _linear(x, self.weight, None, self.reversed, self.oslo_fused)
+
+    def forward(self, x: Tensor, activation: Optional[str] = None, partial: Optional[Tensor] = None) -> Tensor:
+        """``partial``: partial sum of another row-parallel layer (``partial_forward``), reduced together with this
+        layer's product; that layer's bias, if any, is the caller's business."""
         mpu = self.mpu
         if mpu is not None and not self.input_is_parallel:
             x = mpu.scatter(x, dim=-1)
@@ -176,10 +185,16 @@ class RowParallelLinear(nn.Linear):
             rows = x.numel() // max(x.size(-1), 1)
             if fused_tp.fused_tp_usable(mpu, x, n_out) and (not self.sequence_parallel or rows % (mpu.tp * 128) == 0):
                 tp = fused_tp.get_fused_tp(mpu.get_tensor_parallel_group())
-                fn = fused_tp._RowParallelSeqFused if self.sequence_parallel else fused_tp._RowParallelFused
-                y = fn.apply(x, self.weight, self.reversed, tp)
+                if self.sequence_parallel:
+                    y = fused_tp._RowParallelSeqFused.apply(x, self.weight, self.reversed, tp)
+                    if partial is not None:   # the sequence-parallel kernel path keeps the two reductions separate
+                        y = y + mpu.reduce_scatter_sequence(partial, dim=-2)
+                else:
+                    y = fused_tp._RowParallelFused.apply(x, self.weight, self.reversed, tp, partial)
                 return y if self.bias is None else y + self.bias
         y = _linear(x, self.weight, None, self.reversed, self.oslo_fused)
+        if partial is not None:
+            y = y + partial
         if mpu is not None:
             y = mpu.reduce_scatter_sequence(y, dim=-2) if self.sequence_parallel else mpu.reduce(y)
         if self.bias is not None:

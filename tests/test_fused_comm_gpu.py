@@ -34,6 +34,13 @@ def _check_ops(rank, world):
                 dist.all_reduce(want, group=g)
                 got = tp.gemm_all_reduce(a, b, False, False)
                 assert torch.allclose(got.float(), want, atol=0.25, rtol=0.03), ("AR", use_mm, M, N, K, rep, (got.float() - want).abs().max())
+                # a second per-rank partial sum joins the tiles before the reduction (two row-parallel products,
+                # one collective)
+                part = (torch.randn(M, N, device="cuda") * 0.5).to(torch.bfloat16)
+                want_p = a.float() @ b.float().t() + part.float()
+                dist.all_reduce(want_p, group=g)
+                got_p = tp.gemm_all_reduce(a, b, False, False, partial=part)
+                assert torch.allclose(got_p.float(), want_p, atol=0.3, rtol=0.03), ("AR+partial", use_mm, M, N, K, rep)
                 got_rs = tp.gemm_reduce_scatter(a, b.t().contiguous(), False, True)
                 rows = M // world
                 assert torch.allclose(got_rs.float(), want[rank * rows:(rank + 1) * rows], atol=0.25, rtol=0.03), ("RS", use_mm, M, N, K)
