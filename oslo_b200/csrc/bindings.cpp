@@ -585,34 +585,67 @@ void allreduce_oneshot(Tensor x, int64_t peer_ptrs_dev, int64_t mc_ptr, int64_t 
 
 }  // namespace
 
+// Schemas. Kernels that take tensors are registered for the CUDA dispatch key (below), which leaves the Meta /
+// fake-tensor slot free for the shape implementations that oslo_b200/ops/fake_impls.py registers from Python.
 TORCH_LIBRARY(oslo_b200, m) {
-  m.def("error_word(Tensor like) -> Tensor", &error_word);
+  m.def("error_word(Tensor like) -> Tensor");
   m.def("launch_count() -> int", &launch_count);
-  m.def("gemm(Tensor a, Tensor b, int a_mn, int b_mn, Tensor? bias, Tensor? aux, Tensor(a!)? out, Tensor(b!)? aux_out, int flags, float alpha) -> Tensor", &gemm);
-  m.def("gemm_small_m(Tensor a, Tensor b, int b_mn, Tensor? bias, int gelu_from) -> Tensor", &gemm_small_m);
-  m.def("layernorm_fwd(Tensor x, Tensor w, Tensor? b, float eps) -> (Tensor, Tensor, Tensor)", &layernorm_fwd);
-  m.def("layernorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor mean, Tensor rstd) -> (Tensor, Tensor, Tensor)", &layernorm_bwd);
-  m.def("bias_gelu_fwd(Tensor x, Tensor? bias) -> Tensor", &bias_gelu_fwd);
-  m.def("bias_gelu_bwd(Tensor dy, Tensor x, Tensor? bias) -> Tensor", &bias_gelu_bwd);
-  m.def("bias_dropout_residual(Tensor x, Tensor? bias, Tensor? residual, float p, int seed, int mode) -> Tensor", &bias_dropout_residual);
-  m.def("colsum(Tensor x) -> Tensor", &colsum);
-  m.def("rotary(Tensor x, Tensor positions, int rotary_dim, float base, bool inverse) -> Tensor", &rotary);
-  m.def("rotary_(Tensor(a!) x, Tensor positions, int heads, int head_dim, int rotary_dim, float base, bool inverse) -> Tensor(a!)", &rotary_);
-  m.def("causal_softmax_fwd(Tensor x, float scale) -> Tensor", &causal_softmax_fwd);
-  m.def("masked_softmax_fwd(Tensor x, Tensor mask, float scale) -> Tensor", &masked_softmax_fwd);
-  m.def("softmax_bwd(Tensor y, Tensor dy, float scale) -> Tensor", &softmax_bwd);
-  m.def("ce_stats(Tensor logits, Tensor labels, int vocab_start) -> (Tensor, Tensor, Tensor)", &ce_stats);
-  m.def("ce_grad_(Tensor(a!) logits, Tensor labels, int vocab_start, Tensor lse, Tensor scale) -> Tensor(a!)", &ce_grad_);
-  m.def("adam_step(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor(d!)? p_lp, float lr, float beta1, float beta2, float eps, float wd, int step, float grad_scale, Tensor? inv_scale) -> ()", &adam_step);
-  m.def("sumsq(Tensor x) -> Tensor", &sumsq);
-  m.def("ngram_ban_(Tensor tokens, Tensor(a!) lprobs, int n) -> Tensor(a!)", &ngram_ban_);
-  m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int window, Tensor? kpm, int impl=1) -> (Tensor, Tensor)", &flash_fwd);
-  m.def("flash_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale, bool causal, int window, Tensor? kpm, int impl=1) -> (Tensor, Tensor, Tensor)", &flash_bwd);
-  m.def("decode_attn(Tensor q, Tensor kc, Tensor vc, Tensor lengths, float scale, int window) -> Tensor", &decode_attn);
-  m.def("gemm_comm(Tensor a, Tensor b, int a_mn, int b_mn, Tensor? bias, Tensor? aux, Tensor(a!)? aux_out, Tensor(b!)? out, int flags, float alpha, int M, int N, int K, int peer_bufs_dev, int own_buf, int mc_base, int data_off, int flag_off, int flag_bytes, int rank, int world, int epoch, int done_base, int mode, bool use_multimem, Tensor(c!)? trace) -> int", &gemm_comm);
-  m.def("gemv_rows(Tensor x1, Tensor? x2, Tensor w, Tensor? bias, int gelu_from, Tensor? res=None) -> Tensor", &gemv_rows);
-  m.def("rotary_append(Tensor q, Tensor k, Tensor v, Tensor(a!) kc, Tensor(b!) vc, Tensor lengths, Tensor write_index, int rotary_dim, float base) -> Tensor", &rotary_append);
-  m.def("vocab_embed(Tensor ids, Tensor weight, int lo, int hi, int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(a!) counters, int half_bytes, int rank, int world, bool use_multimem) -> Tensor", &vocab_embed);
-  m.def("allreduce_oneshot(Tensor(a!) x, int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(b!) counters, int stage_off, int half_bytes, int rank, int world, bool use_multimem) -> ()", &allreduce_oneshot);
-  m.def("allreduce_symm(int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(a!) out, int numel, int rank, int world, bool use_multimem) -> ()", &allreduce_symm);
+  m.def("gemm(Tensor a, Tensor b, int a_mn, int b_mn, Tensor? bias, Tensor? aux, Tensor(a!)? out, Tensor(b!)? aux_out, int flags, float alpha) -> Tensor");
+  m.def("gemm_small_m(Tensor a, Tensor b, int b_mn, Tensor? bias, int gelu_from) -> Tensor");
+  m.def("layernorm_fwd(Tensor x, Tensor w, Tensor? b, float eps) -> (Tensor, Tensor, Tensor)");
+  m.def("layernorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor mean, Tensor rstd) -> (Tensor, Tensor, Tensor)");
+  m.def("bias_gelu_fwd(Tensor x, Tensor? bias) -> Tensor");
+  m.def("bias_gelu_bwd(Tensor dy, Tensor x, Tensor? bias) -> Tensor");
+  m.def("bias_dropout_residual(Tensor x, Tensor? bias, Tensor? residual, float p, int seed, int mode) -> Tensor");
+  m.def("colsum(Tensor x) -> Tensor");
+  m.def("rotary(Tensor x, Tensor positions, int rotary_dim, float base, bool inverse) -> Tensor");
+  m.def("rotary_(Tensor(a!) x, Tensor positions, int heads, int head_dim, int rotary_dim, float base, bool inverse) -> Tensor(a!)");
+  m.def("causal_softmax_fwd(Tensor x, float scale) -> Tensor");
+  m.def("masked_softmax_fwd(Tensor x, Tensor mask, float scale) -> Tensor");
+  m.def("softmax_bwd(Tensor y, Tensor dy, float scale) -> Tensor");
+  m.def("ce_stats(Tensor logits, Tensor labels, int vocab_start) -> (Tensor, Tensor, Tensor)");
+  m.def("ce_grad_(Tensor(a!) logits, Tensor labels, int vocab_start, Tensor lse, Tensor scale) -> Tensor(a!)");
+  m.def("adam_step(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor(d!)? p_lp, float lr, float beta1, float beta2, float eps, float wd, int step, float grad_scale, Tensor? inv_scale) -> ()");
+  m.def("sumsq(Tensor x) -> Tensor");
+  m.def("ngram_ban_(Tensor tokens, Tensor(a!) lprobs, int n) -> Tensor(a!)");
+  m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int window, Tensor? kpm, int impl=1) -> (Tensor, Tensor)");
+  m.def("flash_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale, bool causal, int window, Tensor? kpm, int impl=1) -> (Tensor, Tensor, Tensor)");
+  m.def("decode_attn(Tensor q, Tensor kc, Tensor vc, Tensor lengths, float scale, int window) -> Tensor");
+  m.def("gemm_comm(Tensor a, Tensor b, int a_mn, int b_mn, Tensor? bias, Tensor? aux, Tensor(a!)? aux_out, Tensor(b!)? out, int flags, float alpha, int M, int N, int K, int peer_bufs_dev, int own_buf, int mc_base, int data_off, int flag_off, int flag_bytes, int rank, int world, int epoch, int done_base, int mode, bool use_multimem, Tensor(c!)? trace) -> int");
+  m.def("gemv_rows(Tensor x1, Tensor? x2, Tensor w, Tensor? bias, int gelu_from, Tensor? res=None) -> Tensor");
+  m.def("rotary_append(Tensor q, Tensor k, Tensor v, Tensor(a!) kc, Tensor(b!) vc, Tensor lengths, Tensor write_index, int rotary_dim, float base) -> Tensor");
+  m.def("vocab_embed(Tensor ids, Tensor weight, int lo, int hi, int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(a!) counters, int half_bytes, int rank, int world, bool use_multimem) -> Tensor");
+  m.def("allreduce_oneshot(Tensor(a!) x, int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(b!) counters, int stage_off, int half_bytes, int rank, int world, bool use_multimem) -> ()");
+  m.def("allreduce_symm(int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(a!) out, int numel, int rank, int world, bool use_multimem) -> ()");
+}
+
+TORCH_LIBRARY_IMPL(oslo_b200, CUDA, m) {
+  m.impl("error_word", &error_word);
+  m.impl("gemm", &gemm);
+  m.impl("gemm_small_m", &gemm_small_m);
+  m.impl("layernorm_fwd", &layernorm_fwd);
+  m.impl("layernorm_bwd", &layernorm_bwd);
+  m.impl("bias_gelu_fwd", &bias_gelu_fwd);
+  m.impl("bias_gelu_bwd", &bias_gelu_bwd);
+  m.impl("bias_dropout_residual", &bias_dropout_residual);
+  m.impl("colsum", &colsum);
+  m.impl("rotary", &rotary);
+  m.impl("rotary_", &rotary_);
+  m.impl("causal_softmax_fwd", &causal_softmax_fwd);
+  m.impl("masked_softmax_fwd", &masked_softmax_fwd);
+  m.impl("softmax_bwd", &softmax_bwd);
+  m.impl("ce_stats", &ce_stats);
+  m.impl("ce_grad_", &ce_grad_);
+  m.impl("adam_step", &adam_step);
+  m.impl("sumsq", &sumsq);
+  m.impl("ngram_ban_", &ngram_ban_);
+  m.impl("flash_fwd", &flash_fwd);
+  m.impl("flash_bwd", &flash_bwd);
+  m.impl("decode_attn", &decode_attn);
+  m.impl("gemm_comm", &gemm_comm);
+  m.impl("gemv_rows", &gemv_rows);
+  m.impl("rotary_append", &rotary_append);
+  m.impl("vocab_embed", &vocab_embed);
+  m.impl("allreduce_oneshot", &allreduce_oneshot);
+  m.impl("allreduce_symm", &allreduce_symm);
 }

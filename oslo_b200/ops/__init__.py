@@ -33,6 +33,11 @@ def load_ext(required: bool = False):
                 raise FileNotFoundError(f"{path} not built; run `python -m oslo_b200.build`")
             torch.ops.load_library(path)
             _EXT = torch.ops.oslo_b200
+            try:   # shape / dtype implementations for graph capture; never fatal
+                from . import fake_impls
+                fake_impls.register()
+            except Exception:  # noqa: BLE001
+                pass
         except BaseException as e:  # noqa: BLE001 - reported below
             _EXT_ERR = e
     if _EXT is None and required:

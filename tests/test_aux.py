@@ -116,3 +116,25 @@ def test_generate_cuda_graph_flag_equals_greedy_search_with_eos():
             want = model.generate(ids, max_length=32, do_sample=False, eos_token_id=eos, pad_token_id=0)
             got = model.generate(ids, max_length=32, do_sample=False, eos_token_id=eos, pad_token_id=0, cuda_graph=True)
             assert want.shape == got.shape and torch.equal(want, got), (rows, eos)
+
+
+def test_fake_tensor_implementations_trace_without_a_gpu():
+    """The operators can be traced under FakeTensorMode: shapes, dtypes and the attention output layout."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    from oslo_b200 import ops
+    ext = ops.load_ext()
+    if ext is None:
+        pytest.skip("extension not built")
+    with FakeTensorMode():
+        a = torch.empty(64, 128, dtype=torch.bfloat16, device="cuda")
+        w = torch.empty(256, 128, dtype=torch.bfloat16, device="cuda")
+        y = ext.gemm(a, w, 0, 0, None, None, None, None, 0, 1.0)
+        assert y.shape == (64, 256) and y.dtype == torch.bfloat16
+        y32 = ext.gemm(a, w, 0, 0, None, None, None, None, 32, 1.0)
+        assert y32.dtype == torch.float32
+        q = torch.empty(2, 16, 4, 64, dtype=torch.bfloat16, device="cuda").permute(0, 2, 1, 3)
+        o, lse = ext.flash_fwd(q, q, q, 0.125, True, 0, None, 1)
+        assert o.shape == (2, 4, 16, 64) and o.stride(-1) == 1 and lse.shape == (2, 4, 16)
+        ln, mean, rstd = ext.layernorm_fwd(a, torch.empty(128, dtype=torch.bfloat16, device="cuda"), None, 1e-5)
+        assert ln.shape == a.shape and mean.shape == (64,) and mean.dtype == torch.float32
+        assert ext.gemv_rows(a[:2], None, w, None, -1).shape == (2, 256)
