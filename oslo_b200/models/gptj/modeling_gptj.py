@@ -117,8 +117,12 @@ class GPTJMLP(nn.Module):
         where the fused path applies. ``partial`` (tensor parallel, no dropout): the attention output projection's
         partial sum, reduced together with fc_out's."""
         if partial is not None:
-            act = self.fc_in(x, activation="gelu_new") if (self.fused and self.activation in GELU_TANH_NAMES) \
-                else ACT2FN[self.activation](self.fc_in(x))
+            if h is not None:
+                act = h
+            elif self.fused and self.activation in GELU_TANH_NAMES:
+                act = self.fc_in(x, activation="gelu_new")
+            else:
+                act = ACT2FN[self.activation](self.fc_in(x))
             return self.fc_out(act, partial=partial)
         if residual is not None:
             return self._forward(x, h, residual)
@@ -233,6 +237,31 @@ class GPTJBlock(nn.Module):
             z = z + fc_bias
         return z + hidden_states, None, None
 
+    def _tp_shared_input(self, x: Tensor):
+        """``(q, k, v, h)`` through ``fused_tp.tp_block_input`` when the four layers are plain column-parallel shards
+        (``[out_shard, in]`` weights, no gathered output, no sequence parallelism, bias only on fc_in) in training."""
+        from ...parallel.layers import ColumnParallelLinear
+        attn, mlp = self.attn, self.mlp
+        layers = (attn.q_proj, attn.k_proj, attn.v_proj, mlp.fc_in)
+        if not (get_config().tp_shared_input_grad and torch.is_grad_enabled() and mlp.activation in GELU_TANH_NAMES
+                and attn.fused == mlp.fused):
+            return None
+        for l in layers:
+            if not (type(l) is ColumnParallelLinear and not l.reversed and not l.gather_output and not l.sequence_parallel
+                    and l.mpu is not None and l.mpu.tp > 1 and l.oslo_fused == attn.fused):
+                return None
+        if any(l.bias is not None for l in layers[:3]):
+            return None
+        if x.is_cuda:
+            from ...ops import cuda_ops
+            if not (attn.fused and cuda_ops.qkv_linear_ok(x, *(l.weight for l in layers))):
+                return None
+        elif attn.fused:
+            return None
+        from ...parallel.fused_tp import tp_block_input
+        return tp_block_input(x, attn.q_proj.weight, attn.k_proj.weight, attn.v_proj.weight, mlp.fc_in.weight,
+                              mlp.fc_in.bias, attn.q_proj.mpu)
+
     def forward(self, hidden_states: Tensor, **kw):
         x = self.ln_1(hidden_states)
         packed = self._packed_decode_projections(x) if x.is_cuda else None
@@ -256,6 +285,10 @@ class GPTJBlock(nn.Module):
                 and self.attn.out_proj.mpu.tp > 1 and not self.attn.out_proj.sequence_parallel):
             # tensor parallel: attention projection and fc_out are both row-parallel and their sum is all the block
             # needs, so ONE collective reduces both (the projection's partial sum rides along in fc_out's kernel)
+            pre = self._tp_shared_input(x)
+            if pre is not None:   # q / k / v / fc_in as one node: ONE all-reduce of the block's input gradient too
+                a_part, present, probs = self.attn(x, qkv=pre[:3], partial_only=True, **kw)
+                return self.mlp(x, h=pre[3], partial=a_part) + hidden_states, present, probs
             a_part, present, probs = self.attn(x, partial_only=True, **kw)
             return self.mlp(x, partial=a_part) + hidden_states, present, probs
         a, present, probs = self.attn(x, **kw)

@@ -271,3 +271,120 @@ class _RowParallelSeqFused(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             dw = weight_grad(weight, x2, dy_full) if ctx.reversed else weight_grad(weight, dy_full, x2)
         return dx, dw, None, None
+
+
+class _TPBlockInput(torch.autograd.Function):
+    """The four column-parallel layers of a GPT-J block that read the same LayerNorm output - q, k, v and
+    fc_in (+ tanh-GeLU) - as ONE autograd node under tensor parallelism.
+
+    Forward is four local GEMMs. The point is the backward: the reference all-reduces the input gradient of every
+    column-parallel layer separately (oslo/parallelism/mpu.py:848-856, four collectives per block); here the three
+    short q / k / v products accumulate into one partial sum in their GEMM epilogues and that partial sum rides along
+    in the epilogue of fc_in's long GEMM + all-reduce kernel, so the block's input gradient costs ONE collective,
+    hidden behind the longest of the four products. Without the kernels (CPU / gloo) the same sum is formed with
+    library matmuls and reduced once.
+    """
+
+    @staticmethod
+    def forward(ctx, x, wq, wk, wv, w_in, b_in, mpu):
+        on_gpu = x.is_cuda
+        k = x.size(-1)
+        x2 = x.reshape(-1, k)
+        need_grad = any(ctx.needs_input_grad[:6])
+        outs = []
+        z = None
+        if on_gpu:
+            from ..ops.cuda_ops import FLAG_BIAS, FLAG_GELU, FLAG_SAVE_PREACT, gemm
+            for w in (wq, wk, wv):
+                y = torch.empty(*x.shape[:-1], w.size(0), dtype=x.dtype, device=x.device)
+                gemm(x2, w, False, False, out=y.view(-1, w.size(0)))
+                outs.append(y)
+            flags = FLAG_GELU | (FLAG_BIAS if b_in is not None else 0)
+            if need_grad:
+                flags |= FLAG_SAVE_PREACT
+                z = torch.empty(x2.size(0), w_in.size(0), dtype=x.dtype, device=x.device)
+            h = torch.empty(*x.shape[:-1], w_in.size(0), dtype=x.dtype, device=x.device)
+            gemm(x2, w_in, False, False, bias=b_in, out=h.view(-1, w_in.size(0)), aux_out=z, flags=flags)
+        else:
+            for w in (wq, wk, wv):
+                outs.append((x2 @ w.t()).view(*x.shape[:-1], w.size(0)))
+            z = x2 @ w_in.t()
+            if b_in is not None:
+                z = z + b_in
+            h = ops.reference.gelu_tanh(z).to(x.dtype).view(*x.shape[:-1], w_in.size(0))
+        ctx.save_for_backward(x2, wq, wk, wv, w_in, z)
+        ctx.mpu, ctx.in_shape, ctx.has_bias = mpu, x.shape, b_in is not None
+        ctx.fused = bool(on_gpu and fused_tp_usable(mpu, x, k))
+        return outs[0], outs[1], outs[2], h
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv, dh):
+        x2, wq, wk, wv, w_in, z = ctx.saved_tensors
+        mpu = ctx.mpu
+        on_gpu = x2.is_cuda
+        rows = x2.size(0)
+
+        def flat(t):
+            t = t.reshape(rows, -1)
+            return t if t.is_contiguous() else t.contiguous()
+
+        grads = [flat(d) if d is not None else None for d in (dq, dk, dv)]
+        dh2 = flat(dh) if dh is not None else None
+        dws = [None, None, None]
+        dw_in = db_in = dx = None
+        if on_gpu:
+            from ..ops.cuda_ops import FLAG_ACCUMULATE, gemm, weight_grad
+            ext = ops.load_ext(required=True)
+            dz = ext.bias_gelu_bwd(dh2, z, None) if dh2 is not None else None
+            part = None
+            if ctx.needs_input_grad[0]:
+                for d, w in zip(grads, (wq, wk, wv)):
+                    if d is None:
+                        continue
+                    if part is None:
+                        part = gemm(d, w, False, True)
+                    else:
+                        gemm(d, w, False, True, out=part, flags=FLAG_ACCUMULATE)
+                if dz is not None and ctx.fused:
+                    tp = get_fused_tp(mpu.get_tensor_parallel_group())
+                    dx = tp.gemm_all_reduce(dz, w_in, False, True, partial=part)      # the one collective
+                else:
+                    if dz is not None:
+                        if part is None:
+                            part = gemm(dz, w_in, False, True)
+                        else:
+                            gemm(dz, w_in, False, True, out=part, flags=FLAG_ACCUMULATE)
+                    dx = mpu._reduce(part) if (mpu is not None and mpu.tp > 1) else part
+            for i, (d, w) in enumerate(zip(grads, (wq, wk, wv))):
+                if d is not None and ctx.needs_input_grad[1 + i]:
+                    dws[i] = weight_grad(w, d, x2)
+            if dz is not None and ctx.needs_input_grad[4]:
+                dw_in = weight_grad(w_in, dz, x2)
+            if dz is not None and ctx.has_bias and ctx.needs_input_grad[5]:
+                db_in = ext.colsum(dz).to(dh.dtype)
+        else:
+            dz = None
+            if dh2 is not None:
+                zf = z.detach().float().requires_grad_(True)
+                with torch.enable_grad():
+                    ops.reference.gelu_tanh(zf).backward(dh2.float())
+                dz = zf.grad.to(x2.dtype)
+            if ctx.needs_input_grad[0]:
+                part = None
+                for d, w in zip(grads + [dz], (wq, wk, wv, w_in)):
+                    if d is not None:
+                        part = d @ w if part is None else part + d @ w
+                dx = mpu._reduce(part) if (mpu is not None and mpu.tp > 1) else part
+            for i, (d, w) in enumerate(zip(grads, (wq, wk, wv))):
+                if d is not None and ctx.needs_input_grad[1 + i]:
+                    dws[i] = d.t() @ x2
+            if dz is not None and ctx.needs_input_grad[4]:
+                dw_in = dz.t() @ x2
+            if dz is not None and ctx.has_bias and ctx.needs_input_grad[5]:
+                db_in = dz.sum(0)
+        return (dx.view(ctx.in_shape) if dx is not None else None, dws[0], dws[1], dws[2], dw_in, db_in, None)
+
+
+def tp_block_input(x: Tensor, wq: Tensor, wk: Tensor, wv: Tensor, w_in: Tensor, b_in: Optional[Tensor], mpu):
+    """``(q, k, v, gelu(fc_in(x)))`` for column-parallel weight shards ``[out_shard, in]``; see ``_TPBlockInput``."""
+    return _TPBlockInput.apply(x, wq, wk, wv, w_in, b_in, mpu)
