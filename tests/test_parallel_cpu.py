@@ -118,6 +118,16 @@ def test_tensor_parallel_training_matches_oracle(kind, fuse, out_logits):
         assert names == ["pytorch_model_tp=0_pp=0.bin", "pytorch_model_tp=1_pp=0.bin"]
 
 
+def test_tensor_parallel_shared_input_gradient_matches_oracle(monkeypatch):
+    """GPT-J block with q / k / v / fc_in as one autograd node and a single all-reduce of the block's input gradient
+    (``OSLO_B200_TP_SHARED_INPUT_GRAD=1``): same losses and merged weights as the single-process oracle."""
+    monkeypatch.setenv("OSLO_B200_TP_SHARED_INPUT_GRAD", "1")
+    losses, state = oracle_steps("gptj", steps=3)
+    with tempfile.TemporaryDirectory() as d:
+        run_distributed(_train_parallel, 2, "gptj", 2, 1, 3, None, losses, d, False, True)
+        _check_merged(d, state, 1e-3)
+
+
 @pytest.mark.parametrize("kind", ["gpt2", "gpt_neo", "gptj"])
 def test_sequence_parallel_training_matches_oracle(kind):
     """Megatron-style sequence parallelism inside the TP group (absent in the reference): same losses, same weights."""
