@@ -17,6 +17,10 @@
 //
 // 192 threads: warp 0 = TMA producer (+ statistics), warp 1 = TMEM owner and MMA issuer, warps 2-5 = transform and
 // epilogue. Every wait is bounded (ptx.cuh).
+//
+// Reference behaviour covered: the backward of the same path - softmax backward kernels of
+// oslo/fused_kernels/includes/fused_triang_softmax.h:253-351 / fused_softmax.h:224-325 around autograd's batched
+// matmuls - without ever materialising the [S, S] probabilities.
 #include "attention_sm100.cuh"
 
 namespace oslo {

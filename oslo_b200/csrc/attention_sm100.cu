@@ -13,6 +13,11 @@
 // under the softmax of block j+1. O (128 x D fp32) stays in TMEM for the whole row of blocks.
 // The K tile [BN x 64]-column sub-tiles are at the same time the MN-major image of V that P V needs, so K and V
 // use the same TMA box and no transposes exist anywhere. Every wait is bounded (ptx.cuh).
+//
+// Reference behaviour covered: the materialised-score path Q K^T -> scaled (upper-triangular | padding) masked
+// softmax -> P V of oslo/models/gptj/modeling_gptj.py:151-191 with the kernels of
+// oslo/fused_kernels/includes/fused_triang_softmax.h:134-351 and fused_softmax.h:111-325 (sequence length <= 2048
+// there; no limit here), plus GPT-Neo's local window (oslo/models/gpt_neo/modeling_gpt_neo.py:150-160).
 #include "attention_sm100.cuh"
 
 namespace oslo {

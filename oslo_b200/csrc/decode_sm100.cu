@@ -8,6 +8,10 @@
 //     (attention output and MLP activation feeding the merged out_proj / fc_out product of a parallel block).
 //   * rotary_append_kernel: GPT-J rotary on q and k of the new token, q to a contiguous buffer, k and v written
 //     into the static cache at the position held in device memory.
+//
+// Reference behaviour covered: one iteration of the token loop of oslo/generation_utils.py:1269-1361 through a
+// GPT-J block (oslo/models/gptj/modeling_gptj.py:196-320: rotary at the cache offset, torch.cat cache growth,
+// attention, out_proj, MLP, parallel residual).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math_constants.h>

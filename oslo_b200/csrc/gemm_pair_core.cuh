@@ -11,6 +11,9 @@
 //   tempty[b]  lives in the even CTA; 8 arrivals (4 epilogue warps of each CTA)
 // Each CTA fetches exactly the boxes it consumes itself. Every wait is bounded (ptx.cuh); the two
 // cluster-wide barriers (after set-up, before tear-down) are reached unconditionally by every thread.
+//
+// Reference behaviour covered: every torch.matmul of the parallel layers (oslo/modeling_utils.py:63-104) and their
+// autograd gradients; the reference has no GEMM kernel of its own.
 #pragma once
 #include "gemm_core.cuh"
 
