@@ -35,6 +35,7 @@ class OsloConfig:
     pg_timeout_s: float = 1800.0         # process-group timeout (collectives fail instead of hanging)
     heartbeat_s: float = 5.0             # watchdog heartbeat period
     heartbeat_misses: int = 6            # missed heartbeats before a rank is declared dead
+    debug_sync: bool = False             # synchronise and check the device error word after every operator call
     log_level: str = "INFO"
     metrics_path: str = ""               # JSONL sink for per-step metrics
 

@@ -23,8 +23,48 @@ _16BIT = (torch.bfloat16, torch.float16)
 _dropout_calls = itertools.count()
 
 
+class _CheckedOps:
+    """Debug wrapper around the operator namespace (``OSLO_B200_DEBUG_SYNC=1``): every operator call is followed by a
+    device synchronisation and a read of the per-device error word, so a kernel whose bounded wait ran out - or an
+    asynchronous CUDA error - is reported at the call that caused it, with the operator's name, instead of at some
+    later synchronisation point. The reference has nothing comparable (its kernels never wait on each other)."""
+
+    def __init__(self, ext) -> None:
+        self._ext = ext
+
+    def __getattr__(self, name):
+        fn = getattr(self._ext, name)
+        if name in ("error_word", "launch_count"):
+            return fn
+
+        def checked(*args, **kwargs):
+            out = fn(*args, **kwargs)
+            if torch.cuda.is_current_stream_capturing():
+                return out
+            torch.cuda.synchronize()
+            like = next((a for a in args if isinstance(a, Tensor) and a.is_cuda), None)
+            if like is not None:
+                code = int(self._ext.error_word(like).item())
+                if code:
+                    self._ext.error_word(like).zero_()
+                    raise RuntimeError(f"oslo_b200 kernel behind `{name}` gave up a bounded wait (device error code {code})")
+            return out
+
+        return checked
+
+
+_CHECKED = None
+
+
 def _ext():
-    return load_ext(required=True)
+    ext = load_ext(required=True)
+    from ..config import get_config
+    if getattr(get_config(), "debug_sync", False):
+        global _CHECKED
+        if _CHECKED is None or _CHECKED._ext is not ext:
+            _CHECKED = _CheckedOps(ext)
+        return _CHECKED
+    return ext
 
 
 def device_error_code(like: Tensor) -> int:

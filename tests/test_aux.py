@@ -138,3 +138,39 @@ def test_fake_tensor_implementations_trace_without_a_gpu():
         ln, mean, rstd = ext.layernorm_fwd(a, torch.empty(128, dtype=torch.bfloat16, device="cuda"), None, 1e-5)
         assert ln.shape == a.shape and mean.shape == (64,) and mean.dtype == torch.float32
         assert ext.gemv_rows(a[:2], None, w, None, -1).shape == (2, 256)
+
+
+def test_debug_sync_wrapper_reports_the_failing_operator(monkeypatch):
+    """OSLO_B200_DEBUG_SYNC: the checked namespace reads the error word after a call and names the operator."""
+    from oslo_b200.ops import cuda_ops
+
+    class FakeExt:
+        def __init__(self):
+            self.word = torch.zeros(1, dtype=torch.int32)
+            self.calls = []
+
+        def error_word(self, like):
+            return self.word
+
+        def gemm(self, a):
+            self.calls.append("gemm")
+            return a + 1
+
+        def bad(self, a):
+            self.word.fill_(5)
+            return a
+
+    class Cuda(torch.Tensor):      # a CPU tensor that claims to live on a GPU, so the wrapper looks at the error word
+        @property
+        def is_cuda(self):
+            return True
+
+    fake = FakeExt()
+    checked = cuda_ops._CheckedOps(fake)
+    monkeypatch.setattr(torch.cuda, "synchronize", lambda *a, **k: None)
+    monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", lambda: False)
+    x = torch.zeros(3).as_subclass(Cuda)
+    assert torch.equal(torch.Tensor(checked.gemm(x)), torch.ones(3)) and fake.calls == ["gemm"]
+    with pytest.raises(RuntimeError, match="`bad`.*code 5"):
+        checked.bad(x)
+    assert int(fake.word.item()) == 0      # the word is cleared once reported
