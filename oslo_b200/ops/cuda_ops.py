@@ -15,6 +15,7 @@ import torch
 from torch import Tensor
 
 from . import load_ext
+from ..config import get_config as _get_config
 from . import reference as ref
 
 FLAG_BIAS, FLAG_GELU, FLAG_SAVE_PREACT, FLAG_DGELU, FLAG_RESIDUAL, FLAG_OUT_FP32, FLAG_ACCUMULATE = 1, 2, 4, 8, 16, 32, 64
@@ -58,8 +59,7 @@ _CHECKED = None
 
 def _ext():
     ext = load_ext(required=True)
-    from ..config import get_config
-    if getattr(get_config(), "debug_sync", False):
+    if _get_config().debug_sync:
         global _CHECKED
         if _CHECKED is None or _CHECKED._ext is not ext:
             _CHECKED = _CheckedOps(ext)
