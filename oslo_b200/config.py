@@ -30,6 +30,7 @@ class OsloConfig:
     symm_allreduce_max_bytes: int = 1 << 20  # no-grad tensor-parallel all-reduces up to this size use the symmetric-memory kernel (0 = always NCCL)
     packed_decode: bool = True           # decode steps: one GEMM for the layers that share a LayerNorm output (GPT-J q/k/v/fc_in)
     tp_shared_input_grad: bool = True    # tensor-parallel GPT-J block: q/k/v/fc_in as one node, ONE all-reduce of the input gradient
+    tp_shared_reduction_sp: bool = False # sequence parallel: partial sums ride in the fused GEMM + reduce-scatter kernel (not yet run on GPUs)
     block_fusion: bool = True            # GPT-J block: q/k/v as one autograd node, residual additions inside GEMM epilogues
     ddp_bucket_mb: int = 256
     pg_timeout_s: float = 1800.0         # process-group timeout (collectives fail instead of hanging)

@@ -279,13 +279,16 @@ class GPTJBlock(nn.Module):
             # that sum
             a, present, probs = self.attn(x, residual=hidden_states, **kw)
             return self.mlp(x, residual=a), present, probs
-        if (no_dropout and get_config().block_fusion and kw.get("seq_shape") is None
+        sp = kw.get("seq_shape") is not None
+        if (no_dropout and get_config().block_fusion
                 and isinstance(self.attn.out_proj, RowParallelLinear) and isinstance(self.mlp.fc_out, RowParallelLinear)
                 and self.attn.out_proj.bias is None and getattr(self.attn.out_proj, "mpu", None) is not None
-                and self.attn.out_proj.mpu.tp > 1 and not self.attn.out_proj.sequence_parallel):
+                and self.attn.out_proj.mpu.tp > 1 and self.attn.out_proj.sequence_parallel == sp
+                and self.mlp.fc_out.sequence_parallel == sp
+                and (not sp or not x.is_cuda or get_config().tp_shared_reduction_sp)):
             # tensor parallel: attention projection and fc_out are both row-parallel and their sum is all the block
             # needs, so ONE collective reduces both (the projection's partial sum rides along in fc_out's kernel)
-            pre = self._tp_shared_input(x)
+            pre = None if sp else self._tp_shared_input(x)
             if pre is not None:   # q / k / v / fc_in as one node: ONE all-reduce of the block's input gradient too
                 a_part, present, probs = self.attn(x, qkv=pre[:3], partial_only=True, **kw)
                 return self.mlp(x, h=pre[3], partial=a_part) + hidden_states, present, probs

@@ -249,11 +249,19 @@ class _RowParallelSeqFused(torch.autograd.Function):
     fused into both gradient GEMMs' producer."""
 
     @staticmethod
-    def forward(ctx, x, weight, reversed_, tp: FusedTP):
+    def forward(ctx, x, weight, reversed_, tp: FusedTP, partial=None):
+        """``partial``: another row-parallel layer's partial sum over the same (gathered) rows; it joins this rank's
+        tiles before the reduce-scatter."""
         x2 = x.reshape(-1, x.size(-1))
-        y = tp.gemm_reduce_scatter(x2, weight, False, reversed_)
+        p2 = None
+        if partial is not None:
+            p2 = partial.reshape(x2.size(0), -1)
+            if p2.stride(-1) != 1:
+                p2 = p2.contiguous()
+        y = tp.gemm_reduce_scatter(x2, weight, False, reversed_, partial=p2)
         ctx.save_for_backward(x2, weight)
         ctx.reversed, ctx.tp, ctx.in_shape = reversed_, tp, x.shape
+        ctx.partial_shape = partial.shape if partial is not None else None
         lead = list(x.shape[:-1])
         lead[-1] //= tp.world
         return y.view(*lead, y.size(-1))
@@ -270,7 +278,10 @@ class _RowParallelSeqFused(torch.autograd.Function):
             dx = dx2.view(ctx.in_shape)
         if ctx.needs_input_grad[1]:
             dw = weight_grad(weight, x2, dy_full) if ctx.reversed else weight_grad(weight, dy_full, x2)
-        return dx, dw, None, None
+        d_partial = None
+        if ctx.partial_shape is not None and ctx.needs_input_grad[4]:
+            d_partial = dy_full.reshape(ctx.partial_shape)      # backward of a reduce-scatter is the all-gather
+        return dx, dw, None, None, d_partial
 
 
 class _TPBlockInput(torch.autograd.Function):

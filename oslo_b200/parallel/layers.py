@@ -186,8 +186,11 @@ class RowParallelLinear(nn.Linear):
             if fused_tp.fused_tp_usable(mpu, x, n_out) and (not self.sequence_parallel or rows % (mpu.tp * 128) == 0):
                 tp = fused_tp.get_fused_tp(mpu.get_tensor_parallel_group())
                 if self.sequence_parallel:
-                    y = fused_tp._RowParallelSeqFused.apply(x, self.weight, self.reversed, tp)
-                    if partial is not None:   # the sequence-parallel kernel path keeps the two reductions separate
+                    from ..config import get_config
+                    if partial is None or get_config().tp_shared_reduction_sp:
+                        y = fused_tp._RowParallelSeqFused.apply(x, self.weight, self.reversed, tp, partial)
+                    else:   # the shared form has not run on GPUs yet: keep the two reductions separate
+                        y = fused_tp._RowParallelSeqFused.apply(x, self.weight, self.reversed, tp, None)
                         y = y + mpu.reduce_scatter_sequence(partial, dim=-2)
                 else:
                     y = fused_tp._RowParallelFused.apply(x, self.weight, self.reversed, tp, partial)
