@@ -81,6 +81,14 @@ class ParallelizationMixin:
         return self.organize_fn(**kw)
 
     # ------------------------------------------------------------------ state queries
+    @staticmethod
+    def make_outputs(kwargs: Dict[str, Any], **outputs: Any) -> Dict[str, Any]:
+        """Merge a protocol function's results into the kwargs dict that threads through
+        ``preblock_fn -> block_fn -> postblock_fn -> head_fn -> loss_fn -> organize_fn``
+        (reference: oslo/parallelism_utils.py:128-131); custom models written against the reference call it."""
+        kwargs.update(outputs)
+        return kwargs
+
     def is_model_parallelized(self) -> bool:
         return self.is_tensor_parallelized() or self.is_pipeline_parallelized()
 
