@@ -569,6 +569,19 @@ Tensor vocab_embed(const Tensor& ids, const Tensor& weight, int64_t lo, int64_t 
   return out;
 }
 
+// Wait (bounded by limit_ms, at most 1000) until flag[0] >= target; returns the nanoseconds spent. A wait that runs
+// out leaves ERR_WAIT_PEER in the device error word, exactly like the waits inside the communication kernels.
+Tensor wait_probe(const Tensor& flag, int64_t target, double limit_ms) {
+  TORCH_CHECK(flag.is_cuda() && flag.scalar_type() == at::kInt && flag.numel() >= 1, "wait_probe: int32 CUDA flag");
+  c10::cuda::CUDAGuard guard(flag.device());
+  Tensor waited = at::zeros({1}, flag.options().dtype(at::kLong));
+  auto& st = dev_state(flag.get_device());
+  check_rc(oslo_wait_probe(reinterpret_cast<const uint32_t*>(flag.data_ptr<int>()), static_cast<uint32_t>(target),
+                           static_cast<unsigned long long>(limit_ms * 1e6), st.err.data_ptr<int>(),
+                           reinterpret_cast<unsigned long long*>(waited.data_ptr<int64_t>()), cur_stream()), "wait_probe");
+  return waited;
+}
+
 // In-place one-kernel all-reduce of a small tensor through two alternating staging halves of a symmetric buffer.
 void allreduce_oneshot(Tensor x, int64_t peer_ptrs_dev, int64_t mc_ptr, int64_t signal_ptrs_dev, Tensor counters,
                        int64_t stage_off, int64_t half_bytes, int64_t rank, int64_t world, bool use_multimem) {
@@ -615,6 +628,7 @@ TORCH_LIBRARY(oslo_b200, m) {
   m.def("gemv_rows(Tensor x1, Tensor? x2, Tensor w, Tensor? bias, int gelu_from, Tensor? res=None) -> Tensor");
   m.def("rotary_append(Tensor q, Tensor k, Tensor v, Tensor(a!) kc, Tensor(b!) vc, Tensor lengths, Tensor write_index, int rotary_dim, float base) -> Tensor");
   m.def("vocab_embed(Tensor ids, Tensor weight, int lo, int hi, int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(a!) counters, int half_bytes, int rank, int world, bool use_multimem) -> Tensor");
+  m.def("wait_probe(Tensor flag, int target, float limit_ms) -> Tensor");
   m.def("allreduce_oneshot(Tensor(a!) x, int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(b!) counters, int stage_off, int half_bytes, int rank, int world, bool use_multimem) -> ()");
   m.def("allreduce_symm(int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(a!) out, int numel, int rank, int world, bool use_multimem) -> ()");
 }
@@ -646,6 +660,7 @@ TORCH_LIBRARY_IMPL(oslo_b200, CUDA, m) {
   m.impl("gemv_rows", &gemv_rows);
   m.impl("rotary_append", &rotary_append);
   m.impl("vocab_embed", &vocab_embed);
+  m.impl("wait_probe", &wait_probe);
   m.impl("allreduce_oneshot", &allreduce_oneshot);
   m.impl("allreduce_symm", &allreduce_symm);
 }

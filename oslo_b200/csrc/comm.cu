@@ -171,6 +171,25 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const void* in, 
   if (threadIdx.x == 0) counters[blockIdx.x] += 1;
 }
 
+// Bounded wait on a word of ordinary device memory, with a caller-chosen limit: the same loop shape as the waits on
+// peer flags (acquire load, timer check, error word, clean return). It exists so that the give-up path can be
+// exercised by a test with a flag that nothing sets and a limit of a fraction of a second.
+__global__ void wait_probe_kernel(const uint32_t* flag, uint32_t target, unsigned long long limit_ns, int* err,
+                                  unsigned long long* waited_ns) {
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t v;
+  while (true) {
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (static_cast<int32_t>(v - target) >= 0) break;
+    if (globaltimer_ns() - t0 > limit_ns) {
+      if (err) atomicCAS(err, 0, ERR_WAIT_PEER);
+      break;
+    }
+    __nanosleep(200);
+  }
+  if (waited_ns) *waited_ns = globaltimer_ns() - t0;
+}
+
 // Vocab-parallel embedding lookup fused with its collective. Exactly one rank owns the row of a token id, so no
 // reduction is needed: the owner stores the row into EVERY rank's staging buffer (multimem.st through the switch,
 // or one plain store per peer), block b of every rank handles the same token range, meets block b of the other
@@ -212,6 +231,15 @@ __global__ void __launch_bounds__(512) vocab_embed_kernel(const long long* __res
 }
 
 }  // namespace oslo
+
+// one thread waits until *flag >= target or limit_ns (capped at 1 s) has passed; on expiry the error word gets
+// ERR_WAIT_PEER. waited_ns (device, optional) receives the time spent.
+extern "C" int oslo_wait_probe(const uint32_t* flag, uint32_t target, unsigned long long limit_ns, int* err_word,
+                               unsigned long long* waited_ns, cudaStream_t stream) {
+  if (limit_ns > 1000000000ull) limit_ns = 1000000000ull;
+  oslo::wait_probe_kernel<<<1, 1, 0, stream>>>(flag, target, limit_ns, err_word, waited_ns);
+  return static_cast<int>(cudaGetLastError());
+}
 
 // out [tokens, H] = rows of the vocabulary-sharded weight [hi - lo, H] (this rank owns ids in [lo, hi)); every id must
 // be owned by exactly one rank of the group. `half_bytes`: size of one of the two staging halves at the start of

@@ -155,6 +155,10 @@ int oslo_vocab_embed(const long long* ids, const void* weight, void* out, void* 
                      long long hi, long long half_bytes, int rank, int world, int dtype, int use_multimem, int* err_word,
                      int num_sms, cudaStream_t stream);
 
+// bounded wait on a local flag with a caller-chosen limit (<= 1 s); for tests of the give-up path (comm.cu)
+int oslo_wait_probe(const uint32_t* flag, uint32_t target, unsigned long long limit_ns, int* err_word,
+                    unsigned long long* waited_ns, cudaStream_t stream);
+
 // one-kernel all-reduce for small tensors (comm.cu): in -> staging half in symmetric memory -> sum over ranks -> out
 int oslo_allreduce_oneshot(const void* in, void* out, void* const* peer_ptrs_dev, void* mc_ptr,
                            uint32_t* const* signal_ptrs_dev, uint32_t* counters, long long n, long long stage_off,
