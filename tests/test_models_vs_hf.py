@@ -65,3 +65,23 @@ def test_fused_loss_without_logits(kind):
         b = ours(input_ids=x, labels=x, output_logits=False)
     assert b.logits is None
     assert torch.allclose(a.loss, b.loss, atol=1e-5)
+
+
+@pytest.mark.parametrize("kw", [
+    dict(num_beams=3),
+    dict(num_beams=4, no_repeat_ngram_size=2),
+    dict(num_beams=1, repetition_penalty=1.3, no_repeat_ngram_size=2),
+    dict(num_beams=3, length_penalty=0.6, early_stopping=True, eos_token_id=7, pad_token_id=0),
+    dict(num_beams=2, min_length=10, eos_token_id=7, pad_token_id=0),
+    dict(num_beams=4, num_return_sequences=3),
+    dict(num_beams=1, bad_words_ids=[[5], [9, 11]]),
+], ids=["beams", "beams_ngram", "penalty_ngram", "length_penalty_eos", "min_length", "return_sequences", "bad_words"])
+def test_beam_search_and_logits_processors_match_hf(kw):
+    """Beam search bookkeeping and the logits processors against Hugging Face's generate on the same weights."""
+    ours, hf = _pair("gpt2")
+    x = torch.randint(0, 97, (2, 5), generator=torch.Generator().manual_seed(3))
+    args = dict(max_length=16, do_sample=False, eos_token_id=None, pad_token_id=0)
+    args.update(kw)
+    a = ours.generate(x, **args)
+    b = hf.generate(x, **args)
+    assert a.shape == b.shape and torch.equal(a, b)
