@@ -85,3 +85,48 @@ def test_beam_search_and_logits_processors_match_hf(kw):
     a = ours.generate(x, **args)
     b = hf.generate(x, **args)
     assert a.shape == b.shape and torch.equal(a, b)
+
+
+def _load_into_hf(ours, hf):
+    missing, unexpected = hf.load_state_dict(ours.state_dict(), strict=False)
+    missing = [k for k in missing if not k.endswith((".attn.bias", ".attn.masked_bias", "attention.bias", "attention.masked_bias"))]
+    assert not missing and not unexpected, (missing, unexpected)
+    return ours.eval(), hf.eval()
+
+
+@pytest.mark.parametrize("kind", ["gpt2", "gpt_neo", "gptj"])
+def test_sequence_classification_heads_match_hf(kind):
+    torch.manual_seed(0)
+    common = dict(num_labels=3, pad_token_id=0)
+    if kind == "gpt2":
+        kw = dict(vocab_size=97, n_positions=32, n_embd=48, n_layer=2, n_head=4, resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
+        ours, hf = ob.GPT2ForSequenceClassification(ob.GPT2Config(**kw, **common)), \
+            transformers.GPT2ForSequenceClassification(transformers.GPT2Config(**kw, **common))
+    elif kind == "gpt_neo":
+        kw = dict(vocab_size=97, max_position_embeddings=32, hidden_size=48, num_layers=2, num_heads=4, window_size=4,
+                  attention_types=[[["global", "local"], 1]])
+        ours, hf = ob.GPTNeoForSequenceClassification(ob.GPTNeoConfig(**kw, **common)), \
+            transformers.GPTNeoForSequenceClassification(transformers.GPTNeoConfig(**kw, **common))
+    else:
+        kw = dict(vocab_size=97, n_positions=32, n_embd=48, n_layer=2, n_head=4, rotary_dim=8)
+        ours, hf = ob.GPTJForSequenceClassification(ob.GPTJConfig(**kw, **common)), \
+            transformers.GPTJForSequenceClassification(transformers.GPTJConfig(**kw, resid_pdrop=0.0, embd_pdrop=0.0,
+                                                                               attn_pdrop=0.0, **common))
+    ours, hf = _load_into_hf(ours, hf)
+    x = torch.randint(1, 97, (3, 9))
+    x[1, 6:] = 0                                   # right padding: the pooled position is the last non-pad token
+    labels = torch.tensor([0, 2, 1])
+    with torch.no_grad():
+        a, b = ours(input_ids=x, labels=labels), hf(input_ids=x, labels=labels)
+    assert torch.allclose(a.logits, b.logits, atol=2e-4, rtol=1e-4)
+    assert torch.allclose(a.loss, b.loss, atol=1e-5)
+
+
+def test_cache_modes_generate_the_same_tokens():
+    """Static in-place cache (default), grow-by-cat tuple cache (the reference's) and no cache at all agree."""
+    torch.manual_seed(0)
+    model = ob.GPTJForCausalLM(ob.GPTJConfig(vocab_size=97, n_positions=64, n_embd=48, n_layer=2, n_head=4, rotary_dim=8)).eval()
+    x = torch.randint(0, 97, (3, 5))
+    want = model.generate(x, max_length=20, do_sample=False)
+    assert torch.equal(want, model.generate(x, max_length=20, do_sample=False, use_static_cache=False))
+    assert torch.equal(want, model.generate(x, max_length=20, do_sample=False, use_cache=False))
