@@ -130,3 +130,33 @@ def test_cache_modes_generate_the_same_tokens():
     want = model.generate(x, max_length=20, do_sample=False)
     assert torch.equal(want, model.generate(x, max_length=20, do_sample=False, use_static_cache=False))
     assert torch.equal(want, model.generate(x, max_length=20, do_sample=False, use_cache=False))
+
+
+@pytest.mark.parametrize("kind", ["gpt2", "gpt_neo", "gptj"])
+def test_checkpoints_interchange_with_hf(kind, tmp_path):
+    """A directory written by Hugging Face (config.json + model.safetensors) loads here, and a directory written here
+    (config.json + pytorch_model.bin) loads in Hugging Face, with identical logits."""
+    torch.manual_seed(0)
+    if kind == "gpt2":
+        hf = transformers.GPT2LMHeadModel(transformers.GPT2Config(vocab_size=97, n_positions=32, n_embd=48, n_layer=2, n_head=4))
+        cls = ob.GPT2LMHeadModel
+    elif kind == "gpt_neo":
+        hf = transformers.GPTNeoForCausalLM(transformers.GPTNeoConfig(
+            vocab_size=97, max_position_embeddings=32, hidden_size=48, num_layers=2, num_heads=4, window_size=4,
+            attention_types=[[["global", "local"], 1]]))
+        cls = ob.GPTNeoForCausalLM
+    else:
+        hf = transformers.GPTJForCausalLM(transformers.GPTJConfig(vocab_size=97, n_positions=32, n_embd=48, n_layer=2,
+                                                                  n_head=4, rotary_dim=8))
+        cls = ob.GPTJForCausalLM
+    hf.eval()
+    x = torch.randint(0, 97, (2, 9))
+    hf.save_pretrained(tmp_path / "hf")
+    ours = cls.from_pretrained(str(tmp_path / "hf")).eval()
+    with torch.no_grad():
+        want = hf(input_ids=x).logits
+        assert torch.allclose(ours(input_ids=x).logits, want, atol=2e-4, rtol=1e-4)
+    ours.save_pretrained(str(tmp_path / "ours"))
+    back = type(hf).from_pretrained(tmp_path / "ours").eval()
+    with torch.no_grad():
+        assert torch.allclose(back(input_ids=x).logits, want, atol=2e-4, rtol=1e-4)
