@@ -160,3 +160,27 @@ def test_checkpoints_interchange_with_hf(kind, tmp_path):
     back = type(hf).from_pretrained(tmp_path / "ours").eval()
     with torch.no_grad():
         assert torch.allclose(back(input_ids=x).logits, want, atol=2e-4, rtol=1e-4)
+
+
+def test_logits_processors_match_hf():
+    """Each logits processor / warper against Hugging Face's on random scores (bad-words, forced tokens included)."""
+    import transformers.generation.logits_process as hlp
+    from oslo_b200.generation import logits_process as lp
+    torch.manual_seed(0)
+    ids = torch.randint(0, 50, (4, 9))
+    scores = torch.randn(4, 50)
+    pairs = [
+        (lp.TemperatureLogitsWarper(0.7), hlp.TemperatureLogitsWarper(0.7)),
+        (lp.TopKLogitsWarper(5), hlp.TopKLogitsWarper(5)),
+        (lp.TopKLogitsWarper(3, min_tokens_to_keep=4), hlp.TopKLogitsWarper(3, min_tokens_to_keep=4)),
+        (lp.TopPLogitsWarper(0.8), hlp.TopPLogitsWarper(0.8)),
+        (lp.TopPLogitsWarper(0.3, min_tokens_to_keep=2), hlp.TopPLogitsWarper(0.3, min_tokens_to_keep=2)),
+        (lp.RepetitionPenaltyLogitsProcessor(1.4), hlp.RepetitionPenaltyLogitsProcessor(1.4)),
+        (lp.NoRepeatNGramLogitsProcessor(2), hlp.NoRepeatNGramLogitsProcessor(2)),
+        (lp.NoRepeatNGramLogitsProcessor(3), hlp.NoRepeatNGramLogitsProcessor(3)),
+        (lp.MinLengthLogitsProcessor(12, 3), hlp.MinLengthLogitsProcessor(12, 3)),
+        (lp.InfNanRemoveLogitsProcessor(), hlp.InfNanRemoveLogitsProcessor()),
+    ]
+    for ours, theirs in pairs:
+        a, b = ours(ids, scores.clone()), theirs(ids, scores.clone())
+        assert torch.allclose(a, b, equal_nan=True), type(ours).__name__
