@@ -184,3 +184,18 @@ def test_logits_processors_match_hf():
     for ours, theirs in pairs:
         a, b = ours(ids, scores.clone()), theirs(ids, scores.clone())
         assert torch.allclose(a, b, equal_nan=True), type(ours).__name__
+
+
+def test_gpt2_double_heads_matches_hf():
+    torch.manual_seed(0)
+    kw = dict(vocab_size=97, n_positions=32, n_embd=48, n_layer=2, n_head=4, resid_pdrop=0.0, embd_pdrop=0.0,
+              attn_pdrop=0.0, summary_first_dropout=0.0, num_labels=1)
+    ours, hf = _load_into_hf(ob.GPT2DoubleHeadsModel(ob.GPT2Config(**kw)),
+                             transformers.GPT2DoubleHeadsModel(transformers.GPT2Config(**kw)))
+    x = torch.randint(0, 97, (2, 3, 9))
+    mc, mc_labels = torch.tensor([[8, 5, 7], [2, 8, 4]]), torch.tensor([1, 2])
+    with torch.no_grad():
+        a = ours(input_ids=x, mc_token_ids=mc, labels=x, mc_labels=mc_labels)
+        b = hf(input_ids=x, mc_token_ids=mc, labels=x, mc_labels=mc_labels)
+    assert torch.allclose(a.logits, b.logits, atol=2e-4, rtol=1e-4) and torch.allclose(a.mc_logits, b.mc_logits, atol=2e-4)
+    assert torch.allclose(a.loss, b.loss, atol=1e-5) and torch.allclose(a.mc_loss, b.mc_loss, atol=1e-5)
