@@ -199,3 +199,25 @@ def test_gpt2_double_heads_matches_hf():
         b = hf(input_ids=x, mc_token_ids=mc, labels=x, mc_labels=mc_labels)
     assert torch.allclose(a.logits, b.logits, atol=2e-4, rtol=1e-4) and torch.allclose(a.mc_logits, b.mc_logits, atol=2e-4)
     assert torch.allclose(a.loss, b.loss, atol=1e-5) and torch.allclose(a.mc_loss, b.mc_loss, atol=1e-5)
+
+
+@pytest.mark.parametrize("kind", ["gpt2", "gpt_neo", "gptj"])
+def test_masks_attentions_hidden_states_and_embeds_match_hf(kind):
+    """Left padding through ``attention_mask``, ``output_attentions``, ``output_hidden_states`` and ``inputs_embeds``."""
+    ours, hf = _pair(kind)
+    x = torch.randint(1, 97, (2, 10))
+    am = torch.ones(2, 10, dtype=torch.long)
+    am[0, :3] = 0
+    keep = am.bool()
+    with torch.no_grad():
+        a = ours(input_ids=x, attention_mask=am, output_attentions=True, output_hidden_states=True)
+        b = hf(input_ids=x, attention_mask=am, output_attentions=True, output_hidden_states=True)
+    assert torch.allclose(a.logits[keep], b.logits[keep], atol=3e-4)
+    assert len(a.hidden_states) == len(b.hidden_states) and len(a.attentions) == len(b.attentions)
+    for p, q in zip(a.hidden_states, b.hidden_states):
+        assert torch.allclose(p[keep], q[keep], atol=3e-4)
+    for p, q in zip(a.attentions, b.attentions):
+        assert torch.allclose(p[1], q[1], atol=3e-4)          # the row without padding
+    emb = hf.get_input_embeddings()(x)
+    with torch.no_grad():
+        assert torch.allclose(ours(inputs_embeds=emb).logits, hf(inputs_embeds=emb).logits, atol=3e-4)
