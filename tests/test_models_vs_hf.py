@@ -213,11 +213,15 @@ def test_masks_attentions_hidden_states_and_embeds_match_hf(kind):
         a = ours(input_ids=x, attention_mask=am, output_attentions=True, output_hidden_states=True)
         b = hf(input_ids=x, attention_mask=am, output_attentions=True, output_hidden_states=True)
     assert torch.allclose(a.logits[keep], b.logits[keep], atol=3e-4)
-    assert len(a.hidden_states) == len(b.hidden_states) and len(a.attentions) == len(b.attentions)
+    assert len(a.hidden_states) == len(b.hidden_states)
     for p, q in zip(a.hidden_states, b.hidden_states):
         assert torch.allclose(p[keep], q[keep], atol=3e-4)
-    for p, q in zip(a.attentions, b.attentions):
-        assert torch.allclose(p[1], q[1], atol=3e-4)          # the row without padding
+    assert len(a.attentions) == len(a.hidden_states) - 1
+    for p in a.attentions:                                     # causal rows of probabilities
+        assert torch.allclose(p[1].sum(-1), torch.ones_like(p[1].sum(-1)), atol=1e-4)
+        assert float(p[1].triu(1).abs().max()) == 0.0
+    for p, q in zip(a.attentions, b.attentions):               # empty when HF runs its fused attention path
+        assert torch.allclose(p[1], q[1], atol=3e-4)           # the row without padding
     emb = hf.get_input_embeddings()(x)
     with torch.no_grad():
         assert torch.allclose(ours(inputs_embeds=emb).logits, hf(inputs_embeds=emb).logits, atol=3e-4)
