@@ -174,3 +174,39 @@ def test_debug_sync_wrapper_reports_the_failing_operator(monkeypatch):
     with pytest.raises(RuntimeError, match="`bad`.*code 5"):
         checked.bad(x)
     assert int(fake.word.item()) == 0      # the word is cleared once reported
+
+
+def test_training_resumes_bit_exactly_from_model_and_optimizer_state(tmp_path):
+    """Checkpoint / resume: 2 steps + save + reload into fresh objects + 1 step == 3 uninterrupted steps."""
+    import oslo_b200 as ob
+    from oslo_b200.optim import FusedAdamW
+    cfg = ob.GPTJConfig(vocab_size=64, n_positions=32, n_embd=32, n_layer=2, n_head=4, rotary_dim=4)
+    ids = torch.randint(0, 64, (2, 16), generator=torch.Generator().manual_seed(3))
+
+    def make():
+        torch.manual_seed(0)
+        m = ob.GPTJForCausalLM(cfg).train()
+        return m, FusedAdamW(m.parameters(), lr=1e-2, weight_decay=0.1, max_grad_norm=1.0)
+
+    def step(m, o):
+        o.zero_grad()
+        loss = m(input_ids=ids, labels=ids).loss
+        loss.backward()
+        o.step()
+        return float(loss)
+
+    m, o = make()
+    want = [step(m, o) for _ in range(3)]
+    want_state = {k: v.clone() for k, v in m.state_dict().items()}
+
+    m, o = make()
+    got = [step(m, o) for _ in range(2)]
+    m.save_pretrained(str(tmp_path / "ckpt"))
+    torch.save(o.state_dict(), tmp_path / "optim.pt")
+    m2 = ob.GPTJForCausalLM.from_pretrained(str(tmp_path / "ckpt")).train()
+    o2 = FusedAdamW(m2.parameters(), lr=1e-2, weight_decay=0.1, max_grad_norm=1.0)
+    o2.load_state_dict(torch.load(tmp_path / "optim.pt", weights_only=False))
+    got.append(step(m2, o2))
+    assert got == want
+    for k, v in m2.state_dict().items():
+        assert torch.equal(v, want_state[k]), k
