@@ -200,3 +200,57 @@ def _bad_layout(rank, world, kind, tmpdir):
         cls.from_pretrained_with_parallel(os.path.join(tmpdir, "split"), tensor_parallel_size=4)
     except FileNotFoundError:
         raise
+
+
+def _train_zero_ddp(rank, world, kind, steps, tmpdir, accumulate):
+    """Data parallel over all ranks with the framework's own pieces: ZeRO-1 FusedAdamW on the flat buffers and the
+    bucketed DistributedDataParallel wrapper (tiny buckets so that several reductions are in flight)."""
+    import contextlib
+    import torch.distributed as dist
+    from oslo_b200.optim import FusedAdamW
+    from oslo_b200.parallel.data_parallel import DistributedDataParallel
+    model = build(kind).train()
+    model = ob.parallelize(model, tensor_parallel_size=1)
+    mpu = model.mpu
+    opt = FusedAdamW(model.gpu_parameters(), lr=1e-2, weight_decay=0.01, shard_group=mpu.get_data_parallel_group())
+    ddp = DistributedDataParallel(model, mpu, optimizer=opt, bucket_mb=0.01)
+    for s in range(steps):
+        b = batch(seed=3 + s, bsz=4 * world)
+        n = b["input_ids"].size(0) // world
+        mine = {k: v[rank * n:(rank + 1) * n] for k, v in b.items()}
+        opt.zero_grad()
+        if accumulate:   # two micro-batches, gradients reduced only after the second one
+            half = n // 2
+            for i in range(2):
+                mb = {k: v[i * half:(i + 1) * half] for k, v in mine.items()}
+                hold = ddp.no_sync() if i == 0 else contextlib.nullcontext()
+                with hold:
+                    (ddp(**mb).loss / 2).backward()
+        else:
+            ddp(**mine).loss.backward()
+        opt.step()
+    state = {k: v.detach().clone() for k, v in model.state_dict().items()}
+    gathered = [None] * world
+    dist.all_gather_object(gathered, {k: float(v.double().sum()) for k, v in state.items()})
+    assert all(g == gathered[0] for g in gathered), "replicas diverged"
+    if rank == 0:
+        torch.save(state, os.path.join(tmpdir, "state.pt"))
+
+
+@pytest.mark.parametrize("accumulate", [False, True])
+def test_zero1_and_bucketed_ddp_match_single_process(accumulate):
+    """2 data-parallel gloo ranks with ZeRO-1 + the bucketed DDP wrapper == one process on the whole batch."""
+    kind, steps, world = "gptj", 3, 2
+    torch.manual_seed(0)
+    ref = build(kind).train()
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.01)
+    for s in range(steps):
+        b = batch(seed=3 + s, bsz=4 * world)
+        opt.zero_grad()
+        ref(**b).loss.backward()
+        opt.step()
+    with tempfile.TemporaryDirectory() as d:
+        run_distributed(_train_zero_ddp, world, kind, steps, d, accumulate)
+        got = torch.load(os.path.join(d, "state.pt"), weights_only=True)
+    for k, v in ref.state_dict().items():
+        assert torch.allclose(got[k], v, atol=2e-4), (k, (got[k] - v).abs().max())
