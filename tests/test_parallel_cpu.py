@@ -33,8 +33,9 @@ def batch(seed=3, bsz=4, seq=16, vocab=101):
     return dict(input_ids=x, labels=x.clone())
 
 
-def oracle_steps(kind, steps, micro=None, lr=1e-2):
-    """Single-process training: returns losses per step and the final state dict."""
+def oracle_steps(kind, steps, micro=None, lr=1e-2, loss_scale=1.0):
+    """Single-process training: returns losses per step and the final state dict. ``loss_scale`` multiplies every
+    micro-batch loss before ``backward`` (1 / replicas reproduces gradient averaging over data-parallel replicas)."""
     model = build(kind).train()
     opt = torch.optim.AdamW(model.parameters(), lr=lr)
     losses = []
@@ -49,7 +50,7 @@ def oracle_steps(kind, steps, micro=None, lr=1e-2):
             tot = 0.0
             for i in range(0, b["input_ids"].size(0), micro):
                 out = model(input_ids=b["input_ids"][i:i + micro], labels=b["labels"][i:i + micro])
-                out.loss.backward()
+                (out.loss * loss_scale).backward()
                 tot += float(out.loss)
             losses.append(tot)
         opt.step()
@@ -254,3 +255,12 @@ def test_zero1_and_bucketed_ddp_match_single_process(accumulate):
         got = torch.load(os.path.join(d, "state.pt"), weights_only=True)
     for k, v in ref.state_dict().items():
         assert torch.allclose(got[k], v, atol=2e-4), (k, (got[k] - v).abs().max())
+
+
+def test_3d_parallel_with_data_parallel_replicas():
+    """TP=2 x PP=2 x DP=2 on 8 gloo ranks (the GPT-Neo configuration of the benchmark list, in miniature): merged
+    weights equal the single-process oracle whose two micro-batch gradients are averaged like the two replicas'."""
+    losses, state = oracle_steps("gpt_neo", steps=2, micro=2, loss_scale=0.5)
+    with tempfile.TemporaryDirectory() as d:
+        run_distributed(_train_parallel, 8, "gpt_neo", 2, 2, 2, 2, losses, d, False, True)
+        _check_merged(d, state, 1e-3)
