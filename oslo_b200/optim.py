@@ -10,7 +10,10 @@ The reference leaves optimisation to ``torch.optim.Adam`` or DeepSpeed ZeRO wrap
 * master weights and both moments are fp32; the kernel writes the refreshed bf16/fp16 copy;
 * with ``shard_group`` every rank keeps master/moments for ``1/dp`` of the flat buffer only:
   gradients are reduce-scattered, the owned shard is stepped, parameters are all-gathered;
-* gradient clipping uses a device-side norm, no host synchronisation.
+* gradient clipping uses a device-side norm, no host synchronisation;
+* fp16 training: ``DynamicLossScaler`` (the role DeepSpeed's fp16 optimizer or ``torch.cuda.amp.GradScaler``
+  plays for the reference, USAGE.md:243-267, tests/gpt2/gpt2_test_3d_training.py ZeRO config): the overflow
+  check reuses the norm reduction, so every data-, tensor- and pipeline-parallel rank takes the same decision.
 """
 from __future__ import annotations
 
@@ -37,6 +40,46 @@ def sync_sequence_parallel_grads(model) -> None:
     for p in params:
         p.grad.copy_(flat[off: off + p.numel()].view_as(p.grad))
         off += p.numel()
+
+
+class DynamicLossScaler:
+    """Loss scale for fp16 gradients: halve on overflow (and skip that step), double after
+    ``growth_interval`` clean steps. bf16 training does not need one."""
+
+    def __init__(self, init_scale: float = 2.0 ** 16, growth_factor: float = 2.0, backoff_factor: float = 0.5,
+                 growth_interval: int = 2000, min_scale: float = 1.0, max_scale: float = 2.0 ** 24) -> None:
+        if not (growth_factor > 1.0 and 0.0 < backoff_factor < 1.0 and growth_interval > 0 and init_scale > 0):
+            raise ValueError("need growth_factor > 1, 0 < backoff_factor < 1, growth_interval > 0, init_scale > 0")
+        self.loss_scale = float(init_scale)
+        self.growth_factor, self.backoff_factor = float(growth_factor), float(backoff_factor)
+        self.growth_interval = int(growth_interval)
+        self.min_scale, self.max_scale = float(min_scale), float(max_scale)
+        self.good_steps = 0
+        self.skipped_steps = 0
+
+    def scale(self, loss: Tensor) -> Tensor:
+        """``scaler.scale(loss).backward()``; pipeline stages without the head scale a proxy whose gradient
+        arrives already scaled from the next stage."""
+        return loss * self.loss_scale
+
+    def update(self, found_inf: bool) -> None:
+        if found_inf:
+            self.loss_scale = max(self.loss_scale * self.backoff_factor, self.min_scale)
+            self.good_steps = 0
+            self.skipped_steps += 1
+            return
+        self.good_steps += 1
+        if self.good_steps >= self.growth_interval:
+            self.loss_scale = min(self.loss_scale * self.growth_factor, self.max_scale)
+            self.good_steps = 0
+
+    def state_dict(self) -> Dict[str, float]:
+        return dict(loss_scale=self.loss_scale, good_steps=self.good_steps, skipped_steps=self.skipped_steps)
+
+    def load_state_dict(self, sd: Dict[str, float]) -> None:
+        self.loss_scale = float(sd["loss_scale"])
+        self.good_steps = int(sd["good_steps"])
+        self.skipped_steps = int(sd.get("skipped_steps", 0))
 
 
 class FlatBuffers:
@@ -85,9 +128,11 @@ class FusedAdamW:
 
     def __init__(self, params: Iterable[torch.nn.Parameter], lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 0.01, max_grad_norm: Optional[float] = None, shard_group=None,
-                 grad_average_group=None, model_parallel_group=None, model=None) -> None:
+                 grad_average_group=None, model_parallel_group=None, model=None,
+                 loss_scaler: Optional[DynamicLossScaler] = None) -> None:
         self.lr, self.betas, self.eps, self.weight_decay = lr, tuple(betas), eps, weight_decay
         self.max_grad_norm = max_grad_norm
+        self.loss_scaler = loss_scaler
         self.shard_group = shard_group
         self.model_parallel_group = model_parallel_group
         self.shards = dist.get_world_size(shard_group) if shard_group is not None else 1
@@ -137,9 +182,9 @@ class FusedAdamW:
             off += g.numel()
 
     @torch.no_grad()
-    def step(self) -> None:
+    def step(self) -> bool:
+        """One update; returns False when the loss scaler saw an overflow and the update was skipped."""
         self.sync_sequence_parallel_grads()
-        self.step_count += 1
         lr = self.param_groups[0]["lr"]
         b1, b2 = self.betas
         g_full = self.buf.flat_g
@@ -158,8 +203,20 @@ class FusedAdamW:
             g = g_full
             grad_scale = 1.0
         inv = None
+        norm = None
+        if self.loss_scaler is not None:
+            # the squared norm is summed over the shard and model-parallel groups, so every rank that shares
+            # these parameters (or the loss) reads the same value and skips or steps together
+            norm = self.grad_norm(g)
+            found_inf = not bool(torch.isfinite(norm).item())
+            if found_inf:
+                self.loss_scaler.update(True)
+                return False
+            grad_scale /= self.loss_scaler.loss_scale
+            self.loss_scaler.update(False)
+        self.step_count += 1
         if self.max_grad_norm is not None:
-            norm = self.grad_norm(g) * grad_scale
+            norm = (self.grad_norm(g) if norm is None else norm) * grad_scale
             inv = torch.clamp(self.max_grad_norm / (norm + 1e-6), max=1.0).float()
         lp = self.buf.flat_p[self._lo: self._hi]
         if g.is_cuda and ops.kernels_available():
@@ -179,11 +236,13 @@ class FusedAdamW:
                 self.buf.flat_p.copy_(torch.cat(parts))
             else:
                 dist.all_gather_into_tensor(self.buf.flat_p, lp.contiguous(), group=self.shard_group)
+        return True
 
     # ------------------------------------------------------------------ checkpoint sidecar
     def state_dict(self) -> Dict[str, object]:
         return dict(step=self.step_count, master=self.master.cpu(), exp_avg=self.exp_avg.cpu(),
-                    exp_avg_sq=self.exp_avg_sq.cpu(), shard_rank=self.shard_rank, shards=self.shards, lr=self.lr)
+                    exp_avg_sq=self.exp_avg_sq.cpu(), shard_rank=self.shard_rank, shards=self.shards, lr=self.lr,
+                    loss_scaler=self.loss_scaler.state_dict() if self.loss_scaler is not None else None)
 
     def load_state_dict(self, sd: Dict[str, object]) -> None:
         if sd["shards"] != self.shards or sd["shard_rank"] != self.shard_rank:
@@ -193,3 +252,5 @@ class FusedAdamW:
         self.exp_avg.copy_(sd["exp_avg"])
         self.exp_avg_sq.copy_(sd["exp_avg_sq"])
         self.buf.flat_p[self._lo: self._hi].copy_(self.master)
+        if self.loss_scaler is not None and sd.get("loss_scaler") is not None:
+            self.loss_scaler.load_state_dict(sd["loss_scaler"])

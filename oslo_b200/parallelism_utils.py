@@ -312,6 +312,17 @@ class ParallelizationMixin:
         _barrier()
         logger.info("saved %s", os.path.join(save_directory, fn))
 
+    # ------------------------------------------------------------------ resume (not in the reference)
+    def save_training_state(self, save_directory: str, optimizer=None, step: int = 0, extra=None) -> str:
+        """This rank's resume sidecar (optimizer shard, loss scale, step, generators) beside the model files;
+        call on every rank. See ``oslo_b200.utils.checkpoint``."""
+        from .utils.checkpoint import save_training_state
+        return save_training_state(save_directory, optimizer, step, getattr(self, "mpu", None), extra)
+
+    def load_training_state(self, save_directory: str, optimizer=None, restore_rng: bool = True):
+        from .utils.checkpoint import load_training_state
+        return load_training_state(save_directory, optimizer, getattr(self, "mpu", None), restore_rng)
+
     def _merged_config(self):
         import copy
         return copy.deepcopy(self.config)

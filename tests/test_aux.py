@@ -210,3 +210,89 @@ def test_training_resumes_bit_exactly_from_model_and_optimizer_state(tmp_path):
     assert got == want
     for k, v in m2.state_dict().items():
         assert torch.equal(v, want_state[k]), k
+
+
+def test_dynamic_loss_scaler_matches_unscaled_training_and_skips_overflow():
+    """Loss scaling: scaled and unscaled runs give the same parameters; an overflowed step changes nothing but the
+    scale; the scale grows again after `growth_interval` clean steps; the scaler state rides in the optimizer state."""
+    import oslo_b200 as ob
+    from oslo_b200.optim import DynamicLossScaler, FusedAdamW
+    cfg = ob.GPT2Config(vocab_size=64, n_positions=32, n_embd=32, n_layer=2, n_head=4, resid_pdrop=0.0,
+                        embd_pdrop=0.0, attn_pdrop=0.0)
+    ids = torch.randint(0, 64, (2, 16), generator=torch.Generator().manual_seed(5))
+
+    def make(scaler):
+        torch.manual_seed(0)
+        m = ob.GPT2LMHeadModel(cfg).train()
+        return m, FusedAdamW(m.parameters(), lr=1e-2, weight_decay=0.1, max_grad_norm=1.0, loss_scaler=scaler)
+
+    def step(m, o, poison=False):
+        o.zero_grad()
+        loss = m(input_ids=ids, labels=ids).loss
+        (o.loss_scaler.scale(loss) if o.loss_scaler is not None else loss).backward()
+        if poison:
+            o.buf.flat_g[3] = float("inf")
+        return o.step()
+
+    m0, o0 = make(None)
+    for _ in range(3):
+        assert step(m0, o0) is True
+    scaler = DynamicLossScaler(init_scale=2.0 ** 8, growth_interval=2)
+    m1, o1 = make(scaler)
+    assert step(m1, o1) is True and scaler.loss_scale == 2.0 ** 8
+    before = o1.buf.flat_p.clone()
+    assert step(m1, o1, poison=True) is False                    # skipped: nothing moves, the scale halves
+    assert torch.equal(o1.buf.flat_p, before) and o1.step_count == 1
+    assert scaler.loss_scale == 2.0 ** 7 and scaler.skipped_steps == 1
+    assert step(m1, o1) is True and step(m1, o1) is True         # two clean steps: the scale doubles again
+    assert scaler.loss_scale == 2.0 ** 8 and o1.step_count == 3
+    for a, b in zip(m0.parameters(), m1.parameters()):
+        assert torch.allclose(a, b, atol=1e-6), float((a - b).detach().abs().max())
+    sd = o1.state_dict()
+    s2 = DynamicLossScaler()
+    _, o2 = make(s2)
+    o2.load_state_dict(sd)
+    assert s2.loss_scale == scaler.loss_scale and s2.skipped_steps == 1
+    with pytest.raises(ValueError):
+        DynamicLossScaler(growth_factor=1.0)
+
+
+def test_training_state_sidecar_restores_optimizer_step_and_generators(tmp_path):
+    """`save_training_state` / `load_training_state`: the per-rank sidecar brings back the optimizer, the step
+    counter, user extras and the random generators (dropout masks continue where they left off)."""
+    import random
+    import oslo_b200 as ob
+    from oslo_b200.optim import FusedAdamW
+    from oslo_b200.utils import load_training_state, save_training_state, state_file
+    cfg = ob.GPT2Config(vocab_size=64, n_positions=32, n_embd=32, n_layer=1, n_head=4, resid_pdrop=0.1,
+                        embd_pdrop=0.1, attn_pdrop=0.1)
+    ids = torch.randint(0, 64, (2, 16), generator=torch.Generator().manual_seed(7))
+
+    def make():
+        torch.manual_seed(0)
+        m = ob.GPT2LMHeadModel(cfg).train()
+        return m, FusedAdamW(m.parameters(), lr=1e-2)
+
+    def step(m, o):
+        o.zero_grad()
+        loss = m(input_ids=ids, labels=ids).loss
+        loss.backward()
+        o.step()
+        return float(loss)
+
+    m, o = make()
+    step(m, o)
+    m.save_pretrained(str(tmp_path))
+    path = save_training_state(str(tmp_path), o, step=1, extra={"tokens_seen": 32})
+    assert path == state_file(str(tmp_path)) and path.endswith("oslo_state_tp=0_pp=0_dp=0.pt")
+    want = [step(m, o), random.random(), float(torch.rand(()))]
+
+    torch.manual_seed(123)
+    random.seed(99)
+    m2 = ob.GPT2LMHeadModel.from_pretrained(str(tmp_path)).train()
+    o2 = FusedAdamW(m2.parameters(), lr=1e-2)
+    info = load_training_state(str(tmp_path), o2)
+    assert info == {"step": 1, "extra": {"tokens_seen": 32}} and o2.step_count == 1
+    assert [step(m2, o2), random.random(), float(torch.rand(()))] == want
+    with pytest.raises(FileNotFoundError):
+        load_training_state(str(tmp_path / "nowhere"), o2)

@@ -264,3 +264,46 @@ def test_3d_parallel_with_data_parallel_replicas():
     with tempfile.TemporaryDirectory() as d:
         run_distributed(_train_parallel, 8, "gpt_neo", 2, 2, 2, 2, losses, d, False, True)
         _check_merged(d, state, 1e-3)
+
+
+def _zero_resume(rank, world, kind, tmpdir):
+    """3 uninterrupted ZeRO-1 steps == 2 steps + (split checkpoint, per-rank sidecar) + fresh objects + 1 step."""
+    from oslo_b200.optim import DynamicLossScaler, FusedAdamW
+    cls = getattr(ob, MODEL[kind])
+
+    def optimizer(model):
+        return FusedAdamW(model.gpu_parameters(), lr=1e-2, shard_group=model.mpu.get_data_parallel_group(),
+                          loss_scaler=DynamicLossScaler(init_scale=4.0))
+
+    def step(model, opt, s):
+        b = batch(seed=11 + s, bsz=2 * world)
+        mine = {k: v[rank * 2:(rank + 1) * 2] for k, v in b.items()}
+        opt.zero_grad()
+        opt.loss_scaler.scale(model(**mine).loss).backward()
+        assert opt.step()
+
+    model = ob.parallelize(build(kind).train(), tensor_parallel_size=1)
+    opt = optimizer(model)
+    for s in range(2):
+        step(model, opt, s)
+    ckpt = os.path.join(tmpdir, "ckpt")
+    model.save_pretrained_with_parallel(ckpt)
+    path = model.save_training_state(ckpt, opt, step=2)
+    assert path.endswith(f"oslo_state_tp=0_pp=0_dp={rank}.pt")
+    step(model, opt, 2)
+    want = {k: v.detach().clone() for k, v in model.state_dict().items()}
+
+    again = cls.from_pretrained_with_parallel(ckpt, tensor_parallel_size=1).train()
+    opt2 = optimizer(again)
+    info = again.load_training_state(ckpt, opt2)
+    assert info["step"] == 2 and opt2.step_count == 2
+    assert torch.equal(opt2.master, opt.master) is False      # opt has moved on; the shard on disk is step 2's
+    step(again, opt2, 2)
+    for k, v in again.state_dict().items():
+        assert torch.equal(v, want[k]), k
+    assert torch.equal(opt2.master, opt.master) and torch.equal(opt2.exp_avg_sq, opt.exp_avg_sq)
+
+
+def test_zero1_resume_from_per_rank_sidecars():
+    with tempfile.TemporaryDirectory() as d:
+        run_distributed(_zero_resume, 2, "gpt2", d)
