@@ -1,31 +1,350 @@
-"""Reference arm of ``bench.py``: runs the unmodified reference package installed under
-``baseline/_ref`` through its own public API, or reports why that is impossible on this stack."""
+"""Reference arm of ``bench.py``: trains the unmodified reference package installed under ``baseline/_ref``
+(``oslo`` 2.0.2) through its own public API - ``GPTJForCausalLM.from_config_with_parallel`` for the model,
+``model.gpu_modules()`` / ``model.gpu_parameters()`` / ``model.mpu.get_data_parallel_group()`` with torch's
+``DistributedDataParallel`` and a torch optimizer for data parallelism, exactly the recipe of the reference's
+USAGE.md ("Data Parallelism") - or reports why that is impossible on this stack.
+
+Nothing of ``oslo_b200`` is imported here. The reference was written against transformers 4.x and NumPy 1.x;
+``install_compat()`` makes ``import oslo`` possible on the installed versions WITHOUT touching a file of the
+reference:
+
+* module aliases: names that moved (``transformers.generation_logits_process`` ->
+  ``transformers.generation.logits_process``, ``transformers.modeling_utils.Conv1D`` ->
+  ``transformers.pytorch_utils.Conv1D``, ``transformers.file_utils.ModelOutput`` -> ``transformers.utils`` ...)
+  resolve to the same objects at their new home;
+* names that no longer exist anywhere (beam scorers, ONNX config, ``dacite``: all used by the reference's
+  generation / deployment / export code only) resolve to placeholders that raise when instantiated, so the
+  training path cannot silently use a stand-in;
+* ``PreTrainedModel.init_weights()`` (how 4.x models finish ``__init__``) forwards to 5.x ``post_init()``, and
+  ``get_head_mask(None, n)`` returns ``[None] * n`` as it did in 4.x (a head mask that is not None raises).
+
+The training step is the reference's own model code in eager PyTorch; only the measurement harness is ours.
+"""
 from __future__ import annotations
 
+import contextlib
+import importlib
 import json
 import os
 import sys
+import time
+import types
+from typing import List
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REF = os.path.join(HERE, "_ref")
 
+# GPT-J-6B (the reference's `gptj` family at the size of the headline benchmark)
+MODELS = {
+    "gptj-6b": dict(n_layer=28, n_embd=4096, n_head=16, rotary_dim=64, vocab_size=50400, n_positions=2048),
+    "gptj-small": dict(n_layer=4, n_embd=1024, n_head=8, rotary_dim=64, vocab_size=50400, n_positions=2048),
+    "gptj-tiny": dict(n_layer=2, n_embd=64, n_head=4, rotary_dim=8, vocab_size=128, n_positions=64),
+}
+
+_LEGACY_MODULES = ["transformers.generation_logits_process", "transformers.generation_stopping_criteria",
+                   "transformers.generation_utils", "transformers.generation_beam_search", "transformers.file_utils",
+                   "transformers.onnx", "transformers.utils.model_parallel_utils", "dacite"]
+_NEW_HOMES = ["transformers.generation.logits_process", "transformers.generation.stopping_criteria",
+              "transformers.generation.utils", "transformers.generation.beam_search", "transformers.generation",
+              "transformers.pytorch_utils", "transformers.modeling_utils", "transformers.utils",
+              "transformers.utils.hub", "transformers"]
+PLACEHOLDERS: List[str] = []
+
+
+def _lookup(name: str):
+    for mod_name in _NEW_HOMES:
+        try:
+            mod = importlib.import_module(mod_name)
+        except Exception:
+            continue
+        try:
+            return getattr(mod, name)
+        except Exception:
+            continue
+    return None
+
+
+def _placeholder(name: str):
+    PLACEHOLDERS.append(name)
+
+    def _init(self, *a, **k):
+        raise NotImplementedError(f"{name} does not exist in the installed transformers / environment")
+
+    return type(name, (), {"__init__": _init})
+
+
+class _AliasModule(types.ModuleType):
+    """``from legacy_module import X`` -> the object called X at its new home, else a raising placeholder."""
+
+    def __getattr__(self, name: str):
+        if name.startswith("__"):
+            raise AttributeError(name)
+        obj = _lookup(name)
+        if obj is None:
+            obj = _placeholder(name)
+        setattr(self, name, obj)
+        return obj
+
+
+def install_compat() -> None:
+    import numpy as np
+    if not hasattr(np, "float"):
+        np.float = float   # alias removed in NumPy 1.24; the reference uses it as a dtype name
+    import transformers
+    import transformers.modeling_utils as mu
+    for legacy in _LEGACY_MODULES:
+        if legacy in sys.modules:
+            continue
+        try:
+            importlib.import_module(legacy)
+        except Exception:
+            sys.modules[legacy] = _AliasModule(legacy)
+    for name in ("Conv1D", "SequenceSummary", "find_pruneable_heads_and_indices", "prune_conv1d_layer",
+                 "get_parameter_dtype", "unwrap_model"):
+        if not hasattr(mu, name):
+            setattr(mu, name, _lookup(name) or _placeholder(name))
+    if not hasattr(transformers, "cached_path"):
+        transformers.cached_path = _lookup("cached_file") or _placeholder("cached_path")
+    base = mu.PreTrainedModel
+    if not getattr(base, "_oslo_ref_compat", False):
+        orig_init_weights = base.init_weights
+
+        def init_weights(self, *a, **k):
+            if "all_tied_weights_keys" not in self.__dict__ and not hasattr(type(self), "all_tied_weights_keys"):
+                return self.post_init()
+            return orig_init_weights(self, *a, **k)
+
+        base.init_weights = init_weights
+        if not hasattr(base, "get_head_mask"):
+            def get_head_mask(self, head_mask, num_hidden_layers, is_attention_chunked=False):
+                if head_mask is not None:
+                    raise NotImplementedError("head_mask is not supported by the installed transformers")
+                return [None] * num_hidden_layers
+
+            base.get_head_mask = get_head_mask
+        base._oslo_ref_compat = True
+
 
 def probe() -> str:
-    """Empty string when ``import oslo`` works from baseline/_ref, else a one-line reason."""
+    """Empty string when ``import oslo`` works from baseline/_ref (with the compatibility aliases), else why not."""
     if not os.path.isdir(os.path.join(REF, "oslo")):
         return "reference package is not installed under baseline/_ref"
-    sys.path.insert(0, REF)
+    if REF not in sys.path:
+        sys.path.insert(0, REF)
     try:
+        install_compat()
         import oslo  # noqa: F401
         return ""
     except BaseException as e:  # noqa: BLE001
         return f"import oslo fails on this stack: {type(e).__name__}: {str(e).splitlines()[0][:160]}"
-    finally:
-        sys.path.remove(REF)
 
 
-def main(args) -> None:
-    why = probe()
+def _emit(obj) -> None:
     if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why or "runner for the importable reference is not wired up"}),
-              flush=True)
+        print(json.dumps(obj), flush=True)
+
+
+def _unavailable(why: str) -> None:
+    _emit({"impl": "reference", "unavailable": " ".join(str(why).split())[:300]})
+
+
+def _fits(torch, dev, extra_bytes: int, fraction: float = 0.85) -> bool:
+    if dev.type != "cuda":
+        return True
+    total = torch.cuda.get_device_properties(dev).total_memory
+    return torch.cuda.max_memory_allocated(dev) + extra_bytes < fraction * total
+
+
+def run_train(args, sampler_cls=None, force_cpu: bool = False) -> dict:
+    """The reference's training step at ``args.batch_per_gpu`` x ``args.seq`` tokens per GPU per step: forward /
+    backward over micro-batches (gradients reduced by torch DDP during the last one), gradient clipping, AdamW."""
+    import torch
+    import torch.distributed as dist
+    os.environ.setdefault("RANK", "0")
+    os.environ.setdefault("WORLD_SIZE", "1")
+    os.environ.setdefault("LOCAL_RANK", os.environ["RANK"])
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    world, rank, local = int(os.environ["WORLD_SIZE"]), int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
+    if world != args.gpus:
+        raise RuntimeError(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if force_cpu:
+        dev = torch.device("cpu")
+        if not dist.is_initialized():   # the reference's MPU would ask for NCCL; it keeps an existing group
+            dist.init_process_group("gloo", rank=rank, world_size=world)
+    else:
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+        if not dist.is_initialized():   # as under any launcher; the reference's MPU then only creates its groups
+            dist.init_process_group("nccl", rank=rank, world_size=world)
+
+    import oslo
+    from torch.nn.parallel import DistributedDataParallel
+    dims = MODELS[args.model]
+    seq, per_gpu = args.seq, args.batch_per_gpu
+    cfg = oslo.GPTJConfig(use_cache=False, **dims)
+
+    def build():
+        return oslo.GPTJForCausalLM.from_config_with_parallel(
+            cfg, tensor_parallel_size=1, pipeline_parallel_size=1, torch_dtype=torch.bfloat16)
+
+    try:                                # parameters created on the device (28 x 200 M values: minutes on the host)
+        with torch.device(dev):
+            model = build()
+        init = "on device"
+    except Exception:
+        model = build()
+        init = "on host"
+    model = model.to(dev).train()
+    mpu = model.mpu
+    dp = mpu.get_data_parallel_world_size()
+    if dp > 1:
+        kw = dict(device_ids=[local], output_device=local) if dev.type == "cuda" else {}
+        engine = DistributedDataParallel(model.gpu_modules(), process_group=mpu.get_data_parallel_group(), **kw)
+    else:
+        engine = model
+    params = list(model.gpu_parameters())
+    opt = torch.optim.AdamW(params, lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)
+    param_bytes = sum(p.numel() * p.element_size() for p in params)
+
+    gen = torch.Generator().manual_seed(1000 + mpu.get_data_parallel_rank())
+    n_host = 4
+    host = [torch.randint(0, dims["vocab_size"], (per_gpu, seq), generator=gen) for _ in range(n_host)]
+    if dev.type == "cuda":
+        host = [h.pin_memory() for h in host]
+    dev_inputs = [h.to(dev) for h in host]
+
+    def fwd_bwd(ids, micro, sync_last=True):
+        accum = per_gpu // micro
+        total = None
+        for i in range(accum):
+            mb = ids[i * micro:(i + 1) * micro]
+            hold = engine.no_sync() if (dp > 1 and (i < accum - 1 or not sync_last)) else contextlib.nullcontext()
+            with hold:
+                loss = engine(input_ids=mb, labels=mb).loss
+                (loss / accum).backward()
+            total = loss.detach().float() if total is None else total + loss.detach().float()
+        return total / accum
+
+    # largest micro-batch whose forward/backward leaves room for the optimizer state (the model materialises the
+    # attention matrix, so activation memory grows quickly with it); probed without collectives, then agreed
+    micro = 1
+    for cand in [m for m in (4, 2, 1) if m <= per_gpu and per_gpu % m == 0]:
+        ok = True
+        try:
+            if dev.type == "cuda":
+                torch.cuda.reset_peak_memory_stats(dev)
+            ids = dev_inputs[0][:cand]
+            model(input_ids=ids, labels=ids).loss.backward()   # the bare model: no collective can be left half done
+            ok = _fits(torch, dev, 4 * param_bytes)   # two moments + the multi-tensor update's temporaries
+        except RuntimeError as e:                     # torch.OutOfMemoryError is a RuntimeError
+            if not isinstance(e, torch.OutOfMemoryError) and "out of memory" not in str(e).lower():
+                raise
+            ok = False
+        opt.zero_grad(set_to_none=True)
+        if dev.type == "cuda":
+            torch.cuda.empty_cache()
+        if ok:
+            micro = cand
+            break
+    if dp > 1:
+        t = torch.tensor([micro], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        micro = int(t.item())
+
+    def train_step(ids):
+        opt.zero_grad(set_to_none=True)
+        loss = fwd_bwd(ids, micro)
+        torch.nn.utils.clip_grad_norm_(params, 1.0)
+        opt.step()
+        return loss
+
+    def sync():
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
+
+    def timed(steps, e2e):
+        dist.barrier()
+        sync()
+        sampler = sampler_cls(local) if (sampler_cls is not None and dev.type == "cuda") else None
+        if sampler is not None:
+            sampler.start()
+        if dev.type == "cuda":
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+        wall0 = time.perf_counter()
+        last = None
+        for s in range(steps):
+            if e2e:
+                ids = host[s % n_host].to(dev, non_blocking=True)
+                last = float(train_step(ids).item())
+            else:
+                last = train_step(dev_inputs[s % n_host])
+        if dev.type == "cuda":
+            t1.record()
+        sync()
+        wall = time.perf_counter() - wall0
+        dist.barrier()
+        clocks = sampler.stop() if sampler is not None else None
+        ms = wall * 1e3 if (e2e or dev.type != "cuda") else t0.elapsed_time(t1)
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item() / steps, clocks, last
+
+    for _ in range(args.warmup):
+        train_step(dev_inputs[0])
+    ms_step, clocks, _ = timed(args.steps, e2e=False)
+    tokens_step = dp * per_gpu * seq
+    e2e = None
+    if not getattr(args, "no_e2e", False):
+        ms_e2e, _, loss_host = timed(args.steps, e2e=True)
+        e2e = {"value": tokens_step / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": per_gpu * seq * 8, "d2h_bytes_per_step": 4, "last_loss": loss_host}
+    line = {
+        "impl": "reference",
+        "metric": "GPT-J-6B train tokens/sec" if args.model == "gptj-6b" else f"{args.model} train tokens/sec (debug)",
+        "value": tokens_step / (ms_step / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
+        "config": {"model": args.model, "global_batch": dp * per_gpu, "seq_len": seq,
+                   "parallelism": (f"dp{dp} (torch DistributedDataParallel over mpu.get_data_parallel_group())"
+                                   if dp > 1 else "single"),
+                   "micro_batch": micro, "grad_accum": per_gpu // micro,
+                   "optimizer": "torch.optim.AdamW on bf16 parameters + clip_grad_norm_",
+                   "code_path": "oslo 2.0.2 GPTJForCausalLM.from_config_with_parallel, eager (no fuse())",
+                   "weights_initialised": init, "device": dev.type,
+                   "l2": "working set per step >> 126 MB L2, no explicit flush"},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": None,
+        "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1) if dev.type == "cuda" else None,
+        "compat_placeholders": len(PLACEHOLDERS),
+    }
+    dist.barrier()
+    return line
+
+
+def main(args, sampler_cls=None) -> None:
+    """Print the reference's JSON line, or ``{"impl": "reference", "unavailable": ...}``; never raises."""
+    why = probe()
+    if why:
+        return _unavailable(why)
+    if getattr(args, "mode", "train") != "train":
+        return _unavailable("the reference's generate() needs transformers classes that no longer exist "
+                            "(BeamSearchScorer and the 4.x generation outputs); only the training arm runs")
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return _unavailable("no CUDA device visible")
+        line = run_train(args, sampler_cls)
+        _emit(line)
+    except BaseException as e:  # noqa: BLE001 - the arm must exit 0 with a reason, whatever went wrong
+        if isinstance(e, (KeyboardInterrupt, SystemExit)):
+            raise
+        _unavailable(f"reference training step failed on this stack: {type(e).__name__}: {e}")
+    finally:
+        with contextlib.suppress(Exception):
+            import torch
+            import torch.distributed as dist
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
+            if dist.is_initialized():
+                dist.destroy_process_group()

@@ -112,7 +112,7 @@ class ClockSampler(threading.Thread):
 def reference_arm(args) -> None:
     """Run the unmodified reference through its own public API, or say why it cannot run here."""
     from baseline import reference_runner
-    reference_runner.main(args)
+    reference_runner.main(args, ClockSampler)
 
 
 def main() -> None:

@@ -29,3 +29,38 @@ def test_argument_defaults_finish_quickly():
         sys.argv = old
     assert a.gpus == 1 and a.warmup >= 3 and 1 <= a.steps <= 10 and a.impl == "oslo_b200" and a.mode == "train"
     assert a.model == "gptj-6b" and a.seq == 2048
+
+
+def _reference_installed() -> bool:
+    return os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "oslo"))
+
+
+def _reference_ranks(rank, world, out_dir):
+    """The reference arm's training loop on CPU ranks (gloo): the unmodified reference package builds the model,
+    torch DDP over its data-parallel group reduces the gradients, every rank ends with the same weights."""
+    import types
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, ROOT)
+    from baseline import reference_runner as rr
+    assert rr.probe() == ""
+    args = types.SimpleNamespace(gpus=world, steps=2, warmup=1, model="gptj-tiny", seq=16, batch_per_gpu=4,
+                                 no_e2e=False, mode="train")
+    line = rr.run_train(args, None, force_cpu=True)
+    assert line["impl"] == "reference" and line["n_gpus"] == world and line["value"] > 0
+    assert line["config"]["global_batch"] == 4 * world and line["e2e"]["h2d_bytes_per_step"] == 4 * 16 * 8
+    assert 2.0 < line["e2e"]["last_loss"] < 5.5          # ln(128) = 4.85 at random init, falling
+    assert "oslo_b200" not in sys.modules                # nothing of this framework is on the reference's path
+    if rank == 0:
+        with open(os.path.join(out_dir, "line.json"), "w") as f:
+            json.dump(line, f)
+
+
+def test_reference_arm_trains_the_unmodified_reference_on_cpu_ranks(tmp_path):
+    import pytest
+    if not _reference_installed():
+        pytest.skip("reference package not installed under baseline/_ref")
+    from tests.dist_utils import run_distributed
+    run_distributed(_reference_ranks, 2, str(tmp_path))
+    rec = json.load(open(tmp_path / "line.json"))
+    assert rec["config"]["parallelism"].startswith("dp2") and rec["steps"] == 2 and rec["warmup"] == 1
