@@ -11,7 +11,7 @@ import os
 import time
 from concurrent.futures import ProcessPoolExecutor
 from functools import lru_cache
-from typing import Iterable, Iterator, List, Optional
+from typing import Iterable, Iterator, Optional
 
 import numpy as np
 

@@ -4,7 +4,6 @@ from __future__ import annotations
 from operator import itemgetter
 from typing import Iterator, Optional
 
-import torch
 from torch.utils.data import Dataset, DistributedSampler, Sampler
 
 

@@ -7,7 +7,7 @@ oslo/fused_kernels_utils.py:492-521) that runs on the current CUDA stream for an
 from __future__ import annotations
 
 import time
-from typing import Callable, Iterable, List, Optional
+from typing import Callable, List, Optional
 
 import torch
 from torch import Tensor

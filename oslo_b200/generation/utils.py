@@ -13,7 +13,7 @@ Decoding uses a static, in-place KV cache and asks the model for last-position l
 """
 from __future__ import annotations
 
-from typing import Any, Callable, Dict, Iterable, List, Optional, Tuple, Union
+from typing import Any, Callable, Dict, List, Optional, Union
 
 import torch
 import torch.distributed as dist

@@ -8,8 +8,7 @@ loss_fn -> organize_fn``; reference: oslo/parallelism_utils.py:71-131) that both
 """
 from __future__ import annotations
 
-import math
-from typing import Any, Dict, List, Optional, Tuple
+from typing import Any, Dict, Optional, Tuple
 
 import torch
 import torch.nn as nn

@@ -20,7 +20,7 @@ from ...modeling_utils import PretrainedConfig, PreTrainedModel
 from ...parallel.layers import Embedding, LayerNorm, Linear, RowParallelLinear
 from ...parallel.mpu import Layer, LayerPolicy
 from ..common import (AttentionCore, CausalLMHeadMixin, DecoderBackbone, SequenceClassificationMixin,
-                      maybe_dropout, merge_heads, split_heads, to_token_rows)
+                      maybe_dropout, merge_heads, to_token_rows)
 
 
 class GPTJConfig(PretrainedConfig):

@@ -17,7 +17,6 @@ The reference leaves optimisation to ``torch.optim.Adam`` or DeepSpeed ZeRO wrap
 """
 from __future__ import annotations
 
-import math
 from typing import Dict, Iterable, List, Optional
 
 import torch

@@ -17,7 +17,6 @@ from __future__ import annotations
 from typing import Dict, Optional, Tuple
 
 import torch
-import torch.distributed as dist
 from torch import Tensor
 
 from .. import ops

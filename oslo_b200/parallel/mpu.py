@@ -18,7 +18,7 @@ from __future__ import annotations
 
 import datetime
 import os
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Sequence
 
 import torch
