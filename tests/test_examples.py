@@ -1,0 +1,72 @@
+"""The example scripts run end to end on CPU ranks: preprocess a corpus, train TP2 x PP2 (and DP2 with ZeRO-1),
+interrupt, resume to the same weights, merge, generate from the merged checkpoint."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+EX = os.path.join(ROOT, "examples")
+
+
+def _port() -> int:
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run(cmd, **env):
+    e = dict(os.environ, OSLO_B200_BACKEND="gloo", OMP_NUM_THREADS="1", CUDA_VISIBLE_DEVICES="", **env)
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, cwd=ROOT, env=e)
+    assert r.returncode == 0, (cmd, r.stdout[-1500:], r.stderr[-3000:])
+    return r
+
+
+def _torchrun(n, script, *args):
+    return _run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                 "--master-addr", "127.0.0.1", "--master-port", str(_port()), os.path.join(EX, script), *args])
+
+
+def test_preprocess_train_resume_merge_generate(tmp_path):
+    corpus = tmp_path / "corpus.jsonl"
+    with open(corpus, "w") as f:
+        for i in range(200):
+            f.write(json.dumps({"text": f"document {i}: " + "the quick brown fox jumps over the lazy dog. " * (1 + i % 5)}) + "\n")
+    data = str(tmp_path / "data" / "corpus")
+    out = _run([sys.executable, os.path.join(EX, "preprocess.py"), "--input", str(corpus), "--output", data])
+    assert "200 documents" in out.stdout and os.path.isfile(data + ".bin") and os.path.isfile(data + ".idx")
+
+    common = ["--model", "gptj", "--tiny", "--tp", "2", "--pp", "2", "--batch-size", "4", "--micro-batch-size", "2",
+              "--seq", "32", "--data", data, "--lr", "1e-3"]
+    full, part = str(tmp_path / "full"), str(tmp_path / "part")
+    _torchrun(4, "train.py", *common, "--steps", "4", "--save", full, "--merge", "--metrics", str(tmp_path / "m.jsonl"))
+    recs = [json.loads(l) for l in open(tmp_path / "m.jsonl")]
+    assert [r["step"] for r in recs] == [1, 2, 3, 4] and recs[-1]["loss"] < recs[0]["loss"]
+    for tp in range(2):
+        for pp in range(2):
+            assert os.path.isfile(os.path.join(full, f"pytorch_model_tp={tp}_pp={pp}.bin"))
+            assert os.path.isfile(os.path.join(full, f"oslo_state_tp={tp}_pp={pp}_dp=0.pt"))
+
+    # 2 steps, stop, resume for 2 more: the same weights as 4 uninterrupted steps
+    _torchrun(4, "train.py", *common, "--steps", "2", "--save", part)
+    _torchrun(4, "train.py", *common, "--steps", "4", "--save", part, "--resume", "--merge")
+    a = torch.load(os.path.join(full, "merged", "pytorch_model.bin"), weights_only=True)
+    b = torch.load(os.path.join(part, "merged", "pytorch_model.bin"), weights_only=True)
+    assert a.keys() == b.keys()
+    for k in a:
+        assert torch.equal(a[k], b[k]), k
+
+    gen = _run([sys.executable, os.path.join(EX, "generate.py"), "--model", "gptj", "--checkpoint",
+                os.path.join(full, "merged"), "--prompt", "the quick", "--max-new-tokens", "8", "--num-beams", "2"])
+    assert gen.stdout.startswith("the quick") and "8 new tokens" in gen.stderr
+
+
+def test_train_example_data_parallel_zero1(tmp_path):
+    out = str(tmp_path / "dp")
+    _torchrun(2, "train.py", "--model", "gpt2", "--tiny", "--batch-size", "4", "--micro-batch-size", "2", "--seq", "16",
+              "--steps", "2", "--save", out)
+    assert os.path.isfile(os.path.join(out, "pytorch_model.bin"))      # no model parallelism: the plain HF file
+    assert all(os.path.isfile(os.path.join(out, f"oslo_state_tp=0_pp=0_dp={d}.pt")) for d in range(2))
