@@ -19,6 +19,9 @@ def get_logger(name: str = "oslo_b200") -> logging.Logger:
         if not logger.handlers:
             h = logging.StreamHandler()
             h.setFormatter(logging.Formatter("%(asctime)s [rank %(rank)s] %(levelname)s %(name)s: %(message)s"))
+            # records of child loggers (`oslo_b200.parallelism_utils`, ...) reach this handler without passing the
+            # logger's own filters, so the handler carries the filter too
+            h.addFilter(_RankFilter())
             logger.addHandler(h)
         logger.setLevel(os.environ.get("OSLO_B200_LOG_LEVEL", "INFO").upper())
         logger.propagate = False

@@ -296,3 +296,13 @@ def test_training_state_sidecar_restores_optimizer_step_and_generators(tmp_path)
     assert [step(m2, o2), random.random(), float(torch.rand(()))] == want
     with pytest.raises(FileNotFoundError):
         load_training_state(str(tmp_path / "nowhere"), o2)
+
+
+def test_rank_aware_logger_formats_records_of_child_loggers(capsys):
+    """Records logged through `logging.getLogger("oslo_b200.<module>")` reach the package handler with a rank."""
+    import logging
+    from oslo_b200.utils import get_logger
+    get_logger()
+    logging.getLogger("oslo_b200.some_module").info("child says %s", "hello")
+    err = capsys.readouterr().err
+    assert "child says hello" in err and "[rank 0]" in err and "Logging error" not in err
