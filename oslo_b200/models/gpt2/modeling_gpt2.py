@@ -292,6 +292,12 @@ class GPT2DoubleHeadsModel(CausalLMHeadMixin, GPT2PreTrainedModel):
         kw["mc_token_ids"], kw["mc_labels"] = mc_token_ids, mc_labels
         return self.transformer.preblock_fn(input_ids=input_ids, **kw)
 
+    def prepare_fn(self, input_ids=None, mc_token_ids=None, mc_labels=None, **kw):
+        """What ``preblock_fn`` records about the inputs, for pipeline stages that do not own the embeddings."""
+        kw["_in_shape"] = tuple(input_ids.shape) if input_ids is not None else None
+        kw["mc_token_ids"], kw["mc_labels"] = mc_token_ids, mc_labels
+        return self.transformer.prepare_fn(input_ids=input_ids, **kw)
+
     def head_fn(self, **kw):
         labels = kw.pop("labels", None)
         kw = CausalLMHeadMixin.head_fn(self, **kw)

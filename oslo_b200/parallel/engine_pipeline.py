@@ -241,7 +241,8 @@ class PipelineParallelEngine:
         if self.first:
             kw = model.preblock_fn(**mb_kw)
         else:
-            kw = model.base_model.prepare_fn(**mb_kw)
+            # head models that take extra inputs (multiple-choice ids and labels) normalise them themselves
+            kw = (getattr(model, "prepare_fn", None) or model.base_model.prepare_fn)(**mb_kw)
             kw["hidden_states"] = hidden
         for i in range(*self.block_range):
             kw = model.block_fn(layer_id=i, **kw)

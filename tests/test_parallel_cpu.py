@@ -307,3 +307,65 @@ def _zero_resume(rank, world, kind, tmpdir):
 def test_zero1_resume_from_per_rank_sidecars():
     with tempfile.TemporaryDirectory() as d:
         run_distributed(_zero_resume, 2, "gpt2", d)
+
+
+# ---------------------------------------------------------------------------- classification / multiple-choice heads
+def _head_config(name):
+    if name == "GPT2ForSequenceClassification":
+        return ob.GPT2Config(vocab_size=101, n_positions=32, n_embd=32, n_layer=4, n_head=4, resid_pdrop=0.0,
+                             embd_pdrop=0.0, attn_pdrop=0.0, num_labels=3, pad_token_id=0)
+    if name == "GPT2DoubleHeadsModel":
+        return ob.GPT2Config(vocab_size=101, n_positions=32, n_embd=32, n_layer=4, n_head=4, resid_pdrop=0.0,
+                             embd_pdrop=0.0, attn_pdrop=0.0, summary_first_dropout=0.0, num_labels=1)
+    if name == "GPTNeoForSequenceClassification":
+        return ob.GPTNeoConfig(vocab_size=101, max_position_embeddings=32, hidden_size=32, num_layers=4, num_heads=4,
+                               window_size=4, num_labels=3, pad_token_id=0)
+    return ob.GPTJConfig(vocab_size=104, n_positions=32, n_embd=32, n_layer=4, n_head=4, rotary_dim=4, num_labels=3,
+                         pad_token_id=0)
+
+
+def _head_inputs(name):
+    g = torch.Generator().manual_seed(1)
+    if name == "GPT2DoubleHeadsModel":      # [batch, choices, seq] ids, one summary position per choice
+        ids = torch.randint(1, 101, (4, 2, 16), generator=g)
+        return dict(input_ids=ids, mc_token_ids=torch.randint(0, 16, (4, 2), generator=g), labels=ids.clone(),
+                    mc_labels=torch.randint(0, 2, (4,), generator=g))
+    ids = torch.randint(1, 101, (4, 16), generator=g)
+    return dict(input_ids=ids, labels=torch.randint(0, 3, (4,), generator=g))
+
+
+def _head_model(name):
+    torch.manual_seed(5)
+    return getattr(ob, name)(_head_config(name)).train()
+
+
+def _head_ranks(rank, world, name, tp, pp, want):
+    model = ob.parallelize(_head_model(name), tensor_parallel_size=tp, pipeline_parallel_size=pp, micro_batch_size=2)
+    b = _head_inputs(name)
+    if pp > 1:
+        got = 0.0
+        for out in model(**b):
+            out.loss.backward()
+            got += float(out.loss.detach()) / 2
+    else:
+        out = model(**b)
+        out.loss.backward()
+        got = float(out.loss.detach())
+    assert abs(got - want) < 1e-4, (name, tp, pp, got, want)
+    if name != "GPT2DoubleHeadsModel":     # (its `loss` is the LM loss alone, as in HF: the choice head gets no gradient)
+        missing = [n for n, p in model.gpu_modules().named_parameters() if p.requires_grad and p.grad is None]
+        assert not missing, (rank, missing)
+
+
+@pytest.mark.parametrize("name,tp,pp", [("GPT2ForSequenceClassification", 2, 2), ("GPT2DoubleHeadsModel", 1, 2),
+                                        ("GPT2DoubleHeadsModel", 2, 2), ("GPTNeoForSequenceClassification", 2, 2),
+                                        ("GPTJForSequenceClassification", 2, 2)])
+def test_classification_and_double_heads_models_under_tp_and_pp(name, tp, pp):
+    """The non-LM heads go through the same engines: loss of the parallel model == single process (mean over the two
+    micro-batches under pipeline parallelism, where the last stage must see the multiple-choice inputs too)."""
+    model, b = _head_model(name), _head_inputs(name)
+    if pp > 1:
+        want = sum(float(model(**{k: v[i:i + 2] for k, v in b.items()}).loss.detach()) for i in (0, 2)) / 2
+    else:
+        want = float(model(**b).loss.detach())
+    run_distributed(_head_ranks, tp * pp, name, tp, pp, want)
