@@ -250,6 +250,8 @@ class PipelineParallelEngine:
             kw = model.postblock_fn(**kw)
             kw = model.head_fn(**kw)
             kw = model.loss_fn(**kw)
+        elif kw.get("cache") is not None:
+            kw["cache"].advance(kw["_seq"])   # what postblock_fn does on the last stage: this stage's layers are filled
         return kw
 
     def _recv_grad(self, mb: int, shape, dtype) -> Tensor:

@@ -369,3 +369,39 @@ def test_classification_and_double_heads_models_under_tp_and_pp(name, tp, pp):
     else:
         want = float(model(**b).loss.detach())
     run_distributed(_head_ranks, tp * pp, name, tp, pp, want)
+
+
+# ---------------------------------------------------------------------------- generation through the engines
+def _gen_inputs():
+    g = torch.Generator().manual_seed(2)
+    ids = torch.randint(1, 100, (2, 6), generator=g)
+    mask = torch.ones_like(ids)
+    mask[0, :2] = 0                      # row 0 is left-padded
+    return ids, mask
+
+
+def _generate(model, case):
+    ids, mask = _gen_inputs()
+    ids, mask = ids.to(model.device), mask.to(model.device)
+    if case == "greedy":
+        return model.generate(ids, attention_mask=mask, max_new_tokens=6, do_sample=False, pad_token_id=0)
+    if case == "beam":
+        return model.generate(ids, attention_mask=mask, max_new_tokens=6, num_beams=3, no_repeat_ngram_size=2,
+                              pad_token_id=0)
+    torch.manual_seed(11)
+    return model.generate(ids, attention_mask=mask, max_new_tokens=6, do_sample=True, top_k=5, pad_token_id=0)
+
+
+def _generate_ranks(rank, world, kind, tp, pp, case, want):
+    model = ob.parallelize(build(kind).eval(), tensor_parallel_size=tp, pipeline_parallel_size=pp, micro_batch_size=1)
+    got = _generate(model, case)
+    assert torch.equal(got.cpu(), want), (kind, tp, pp, case, got, want)
+
+
+@pytest.mark.parametrize("kind,tp,pp,case", [("gpt2", 1, 2, "beam"), ("gptj", 2, 2, "greedy"),
+                                             ("gpt_neo", 2, 2, "sample"), ("gptj", 2, 1, "beam")])
+def test_generate_through_tensor_and_pipeline_engines(kind, tp, pp, case):
+    """`generate()` with a KV cache on a TP / PP / TP x PP model returns, on every rank, the tokens of the
+    single-process model (every pipeline stage keeps and advances the cache of its own layers)."""
+    want = _generate(build(kind).eval(), case)
+    run_distributed(_generate_ranks, tp * pp, kind, tp, pp, case, want)
