@@ -405,3 +405,59 @@ def test_generate_through_tensor_and_pipeline_engines(kind, tp, pp, case):
     single-process model (every pipeline stage keeps and advances the cache of its own layers)."""
     want = _generate(build(kind).eval(), case)
     run_distributed(_generate_ranks, tp * pp, kind, tp, pp, case, want)
+
+
+# ---------------------------------------------------------------------------- further flows through the engines
+def _flow_ranks(rank, world, kind, tp, pp, sp, case, want):
+    model = build(kind)
+    model = model.train() if case == "checkpointing" else model.eval()
+    model = ob.parallelize(model, tensor_parallel_size=tp, pipeline_parallel_size=pp, micro_batch_size=2,
+                           sequence_parallel=sp)
+    ids, mask = _gen_inputs()
+    if case == "checkpointing":
+        model.gradient_checkpointing_enable()
+        b = batch(seed=3)
+        if pp > 1:
+            got = 0.0
+            for out in model(**b):
+                out.loss.backward()
+                got += float(out.loss.detach()) / 2
+        else:
+            out = model(**b)
+            out.loss.backward()
+            got = float(out.loss.detach())
+        got = torch.tensor(got)
+    elif case == "generate":
+        got = model.generate(ids, attention_mask=mask, max_new_tokens=5, do_sample=False, pad_token_id=0)
+    elif case == "inputs_embeds":
+        emb = build(kind).get_input_embeddings()(ids).detach()
+        with torch.no_grad():     # without gradients every stage receives the last stage's tensors
+            got = torch.cat([o.logits for o in model(inputs_embeds=emb, output_hidden_states=True)])
+    else:
+        from oslo_b200.generation import GraphedGreedyDecoder
+        got = GraphedGreedyDecoder(model, max_len=32, use_graph=False).generate(ids, max_new_tokens=5)
+    assert torch.allclose(got.float().cpu(), want.float(), atol=2e-4), (case, got, want)
+
+
+@pytest.mark.parametrize("kind,tp,pp,sp,case", [("gptj", 2, 2, False, "checkpointing"), ("gpt2", 2, 1, True, "checkpointing"),
+                                                ("gptj", 2, 1, True, "generate"), ("gpt2", 1, 2, False, "inputs_embeds"),
+                                                ("gptj", 2, 1, False, "graph_decoder")])
+def test_more_flows_through_the_engines(kind, tp, pp, sp, case):
+    """Activation checkpointing under TP x PP and under sequence parallelism, generation on a sequence-parallel
+    model, `inputs_embeds` through pipeline stages, the static-cache greedy decoder on a tensor-parallel model."""
+    model = build(kind)
+    ids, mask = _gen_inputs()
+    if case == "checkpointing":
+        model.train()
+        b = batch(seed=3)
+        if pp > 1:
+            want = torch.tensor(sum(float(model(**{k: v[i:i + 2] for k, v in b.items()}).loss.detach()) for i in (0, 2)) / 2)
+        else:
+            want = model(**b).loss.detach()
+    elif case == "generate":
+        want = model.eval().generate(ids, attention_mask=mask, max_new_tokens=5, do_sample=False, pad_token_id=0)
+    elif case == "inputs_embeds":
+        want = model.eval()(input_ids=ids).logits.detach()
+    else:
+        want = model.eval().generate(ids, max_new_tokens=5, do_sample=False, pad_token_id=0)
+    run_distributed(_flow_ranks, tp * pp, kind, tp, pp, sp, case, want)
