@@ -20,13 +20,14 @@ def gloo_env(monkeypatch):
     monkeypatch.setenv("OSLO_B200_BACKEND", "gloo")
 
 
-def test_deployment_generate_and_forward(gloo_env):
+@pytest.mark.parametrize("tp,pp", [(2, 1), (2, 2)])
+def test_deployment_generate_and_forward(gloo_env, tp, pp):
     ref = _model()
     ids = torch.randint(0, 61, (2, 5), generator=torch.Generator().manual_seed(1))
     want = ref.generate(ids, max_length=12, num_beams=3, eos_token_id=None, pad_token_id=0)
     with torch.no_grad():
         want_logits = ref(input_ids=ids).logits
-    model = ob.parallelize(_model(), tensor_parallel_size=2, pipeline_parallel_size=1, deployment=True,
+    model = ob.parallelize(_model(), tensor_parallel_size=tp, pipeline_parallel_size=pp, deployment=True,
                            startup_timeout_s=120, request_timeout_s=120)
     try:
         got = model.generate(ids, max_length=12, num_beams=3, eos_token_id=None, pad_token_id=0)
