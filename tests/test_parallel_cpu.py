@@ -461,3 +461,34 @@ def test_more_flows_through_the_engines(kind, tp, pp, sp, case):
     else:
         want = model.eval().generate(ids, max_new_tokens=5, do_sample=False, pad_token_id=0)
     run_distributed(_flow_ranks, tp * pp, kind, tp, pp, sp, case, want)
+
+
+def _torch_ddp_ranks(rank, world, kind, tp, pp):
+    """The reference's data-parallel recipe: torch DDP around `gpu_modules()` over `mpu.get_data_parallel_group()`."""
+    import torch.distributed as dist
+    from torch.nn.parallel import DistributedDataParallel as TorchDDP
+    model = ob.parallelize(build(kind).train(), tensor_parallel_size=tp, pipeline_parallel_size=pp, micro_batch_size=2)
+    mpu = model.mpu
+    ddp = TorchDDP(model.gpu_modules(), process_group=mpu.get_data_parallel_group())
+    opt = torch.optim.Adam(model.gpu_parameters(), lr=1e-2)
+    dp, dpr = mpu.get_data_parallel_world_size(), mpu.get_data_parallel_rank()
+    for s in range(2):
+        b = batch(seed=3 + s)
+        n = b["input_ids"].size(0) // dp
+        b = {k: v[dpr * n:(dpr + 1) * n] for k, v in b.items()}
+        opt.zero_grad()
+        if pp > 1:
+            for out in ddp(**b):        # one micro-batch per step: torch DDP reduces during the only backward
+                out.loss.backward()
+        else:
+            ddp(**b).loss.backward()
+        opt.step()
+    sums = {k: float(v.double().sum()) for k, v in model.state_dict().items() if v.is_floating_point()}
+    gathered = [None] * dp
+    dist.all_gather_object(gathered, sums, group=mpu.get_data_parallel_group())
+    assert all(g == gathered[0] for g in gathered), "replicas diverged"
+
+
+@pytest.mark.parametrize("kind,tp,pp", [("gptj", 2, 1), ("gpt2", 1, 2)])
+def test_torch_ddp_around_gpu_modules(kind, tp, pp):
+    run_distributed(_torch_ddp_ranks, 4, kind, tp, pp)
