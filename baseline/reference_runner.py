@@ -198,11 +198,6 @@ def run_train(args, sampler_cls=None, force_cpu: bool = False) -> dict:
     model = model.to(dev).train()
     mpu = model.mpu
     dp = mpu.get_data_parallel_world_size()
-    if dp > 1:
-        kw = dict(device_ids=[local], output_device=local) if dev.type == "cuda" else {}
-        engine = DistributedDataParallel(model.gpu_modules(), process_group=mpu.get_data_parallel_group(), **kw)
-    else:
-        engine = model
     params = list(model.gpu_parameters())
     opt = torch.optim.AdamW(params, lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)
     param_bytes = sum(p.numel() * p.element_size() for p in params)
@@ -213,6 +208,8 @@ def run_train(args, sampler_cls=None, force_cpu: bool = False) -> dict:
     if dev.type == "cuda":
         host = [h.pin_memory() for h in host]
     dev_inputs = [h.to(dev) for h in host]
+
+    engine = model      # wrapped in DistributedDataParallel below, after the memory probe
 
     def fwd_bwd(ids, micro, sync_last=True):
         accum = per_gpu // micro
@@ -236,7 +233,8 @@ def run_train(args, sampler_cls=None, force_cpu: bool = False) -> dict:
                 torch.cuda.reset_peak_memory_stats(dev)
             ids = dev_inputs[0][:cand]
             model(input_ids=ids, labels=ids).loss.backward()   # the bare model: no collective can be left half done
-            ok = _fits(torch, dev, 4 * param_bytes)   # two moments + the multi-tensor update's temporaries
+            # still to come: two moments + the multi-tensor update's temporaries, and DDP's gradient buckets
+            ok = _fits(torch, dev, (4 + (1 if dp > 1 else 0)) * param_bytes)
         except RuntimeError as e:                     # torch.OutOfMemoryError is a RuntimeError
             if not isinstance(e, torch.OutOfMemoryError) and "out of memory" not in str(e).lower():
                 raise
@@ -251,6 +249,8 @@ def run_train(args, sampler_cls=None, force_cpu: bool = False) -> dict:
         t = torch.tensor([micro], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MIN)
         micro = int(t.item())
+        kw = dict(device_ids=[local], output_device=local) if dev.type == "cuda" else {}
+        engine = DistributedDataParallel(model.gpu_modules(), process_group=mpu.get_data_parallel_group(), **kw)
 
     def train_step(ids):
         opt.zero_grad(set_to_none=True)
