@@ -131,6 +131,10 @@ class ParallelizationMixin:
         tp, pp = int(tensor_parallel_size), int(pipeline_parallel_size)
         if tp & (tp - 1):
             raise ValueError(f"tensor_parallel_size must be a power of two, got {tp}")
+        if self.is_model_parallelized():
+            # slicing sliced weights again would silently corrupt them
+            raise RuntimeError("this model is already parallelized; merge it first "
+                               "(save_pretrained_with_parallel(..., save_with_merging=True)) to change the layout")
         set_seed(seed)
         if resize_token_embeddings is not None:
             self.resize_token_embeddings(resize_token_embeddings)

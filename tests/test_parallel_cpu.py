@@ -492,3 +492,20 @@ def _torch_ddp_ranks(rank, world, kind, tp, pp):
 @pytest.mark.parametrize("kind,tp,pp", [("gptj", 2, 1), ("gpt2", 1, 2)])
 def test_torch_ddp_around_gpu_modules(kind, tp, pp):
     run_distributed(_torch_ddp_ranks, 4, kind, tp, pp)
+
+
+def _misuse_ranks(rank, world):
+    model = ob.parallelize(build("gptj"), tensor_parallel_size=2)
+    with pytest.raises(RuntimeError, match="already parallelized"):
+        ob.parallelize(model, tensor_parallel_size=2)
+    with pytest.raises(ValueError, match="exceeds world size"):
+        ob.parallelize(build("gptj"), tensor_parallel_size=2, pipeline_parallel_size=2)
+    with pytest.raises(ValueError, match="power of two"):
+        ob.parallelize(build("gptj"), tensor_parallel_size=3)
+    with pytest.raises(ValueError, match="keyword arguments only"):
+        pp_model = ob.parallelize(build("gpt2"), pipeline_parallel_size=2)
+        pp_model(batch()["input_ids"])
+
+
+def test_misuse_raises_clear_errors():
+    run_distributed(_misuse_ranks, 2)
