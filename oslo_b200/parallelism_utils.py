@@ -251,8 +251,22 @@ class ParallelizationMixin:
         if bad:
             raise RuntimeError(f"split checkpoint {fn} does not match this layout: {bad[:4]}")
         self.tie_weights()
+        self._sync_tied_embedding_across_stages()
         self.eval()
         logger.info("loaded %s", full)
+
+    @torch.no_grad()
+    def _sync_tied_embedding_across_stages(self) -> None:
+        """An output embedding tied to the input embedding lives twice under pipeline parallelism (first and last
+        stage). Split files written without the last stage's copy would leave it at its random initialisation, so
+        after loading the first stage's tensor is sent to the last stage."""
+        mpu, eng = self.mpu, getattr(self, "_pipe_engine", None)
+        if eng is None or mpu.get_pipeline_parallel_world_size() == 1 or not (eng.first or eng.last):
+            return
+        if not getattr(self.config, "tie_word_embeddings", True) or self.get_output_embeddings() is None:
+            return
+        w = self.get_input_embeddings().weight
+        dist.broadcast(w.data, src=mpu.stage_to_global_rank(0), group=mpu.get_embedding_tied_group())
 
     # ------------------------------------------------------------------ saving
     @torch.no_grad()
@@ -305,7 +319,9 @@ class ParallelizationMixin:
         eng = getattr(self, "_pipe_engine", None)
         out = {}
         for k, v in state.items():
-            if k in ignore:
+            # keys a model leaves out because they are tied to another tensor of the SAME file (GPT-Neo's lm_head);
+            # under pipeline parallelism the last stage's copy is the only one in its file, so it stays
+            if k in ignore and mpu.get_pipeline_parallel_world_size() == 1:
                 continue
             if eng is not None and not eng.owns_key(k):
                 continue
