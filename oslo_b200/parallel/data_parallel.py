@@ -48,9 +48,17 @@ class DistributedDataParallel(nn.Module):
             p.register_post_accumulate_grad_hook(self._hook)
             p._oslo_grad_hook = self._hook   # called by weight-gradient GEMMs that add straight into p.grad
         eng = getattr(model, "_pipe_engine", None)
+        self._deferred = set()
         if eng is not None:
             eng.on_last_backward = lambda last: setattr(self, "sync", bool(last))
             self._pipelined = True
+            # an embedding tied between the first and the last stage is summed over those two stages AFTER the last
+            # backward (engine_pipeline._allreduce_tied_embedding), in place, in this very buffer: its bucket must not
+            # be in flight then, so it is reduced from finish_gradient_sync() instead of from the hook
+            tied = (eng.pp > 1 and (eng.first or eng.last) and getattr(model.config, "tie_word_embeddings", True)
+                    and model.get_output_embeddings() is not None)
+            if tied:
+                self._deferred.add(id(model.get_input_embeddings().weight))
         else:
             self._pipelined = False
         if optimizer is not None:
@@ -77,7 +85,7 @@ class DistributedDataParallel(nn.Module):
                 cur, hi = [], lo
 
     def _hook(self, p: torch.Tensor) -> None:
-        if not self.sync or self.world == 1:
+        if not self.sync or self.world == 1 or id(p) in self._deferred:
             return
         b = self._bucket_of[id(p)]
         self._ready[b] += 1

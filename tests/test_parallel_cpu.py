@@ -538,3 +538,44 @@ def test_pipeline_split_checkpoint_restores_the_tied_head(kind):
             torch.save({"logits": model(input_ids=batch(seed=11)["input_ids"]).logits}, os.path.join(d, "ref.pt"))
         run_distributed(_pp_split_roundtrip, 2, kind, d, "save")
         run_distributed(_pp_split_roundtrip, 2, kind, d, "load")
+
+
+def _train_pp_zero_ddp(rank, world, kind, steps, tmpdir):
+    """Pipeline stages x data-parallel replicas with the framework's own wrapper and ZeRO-1 optimizer."""
+    from oslo_b200.optim import FusedAdamW
+    from oslo_b200.parallel.data_parallel import DistributedDataParallel
+    model = ob.parallelize(build(kind).train(), pipeline_parallel_size=2, micro_batch_size=1)
+    mpu = model.mpu
+    opt = FusedAdamW(model.gpu_parameters(), lr=1e-2, weight_decay=0.01, shard_group=mpu.get_data_parallel_group(),
+                     model_parallel_group=mpu.get_model_parallel_group())
+    ddp = DistributedDataParallel(model, mpu, optimizer=opt, bucket_mb=0.01)
+    dp, dpr = mpu.get_data_parallel_world_size(), mpu.get_data_parallel_rank()
+    for s in range(steps):
+        b = batch(seed=3 + s)
+        n = b["input_ids"].size(0) // dp
+        mine = {k: v[dpr * n:(dpr + 1) * n] for k, v in b.items()}
+        opt.zero_grad()
+        for out in ddp(**mine):
+            (out.loss / n).backward()
+        opt.step()
+    model.save_pretrained_with_parallel(os.path.join(tmpdir, "merged"), save_with_merging=True)
+
+
+@pytest.mark.parametrize("kind", ["gpt_neo", "gptj"])
+def test_pipeline_with_bucketed_ddp_and_zero1_matches_single_process(kind):
+    """PP2 x DP2 through the bucketed wrapper: with a tied embedding (GPT-Neo) the first / last stage sum of its
+    gradient and the data-parallel reduction of its bucket touch the same memory and must not overlap."""
+    steps = 3
+    torch.manual_seed(0)
+    ref = build(kind).train()
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.01)
+    for s in range(steps):
+        opt.zero_grad()
+        ref(**batch(seed=3 + s)).loss.backward()
+        opt.step()
+    with tempfile.TemporaryDirectory() as d:
+        run_distributed(_train_pp_zero_ddp, 4, kind, steps, d)
+        got = torch.load(os.path.join(d, "merged", "pytorch_model.bin"), weights_only=True)
+    for k, v in ref.state_dict().items():
+        if k in got:
+            assert torch.allclose(got[k], v, atol=2e-4), (k, (got[k] - v).abs().max())
