@@ -579,3 +579,31 @@ def test_pipeline_with_bucketed_ddp_and_zero1_matches_single_process(kind):
     for k, v in ref.state_dict().items():
         if k in got:
             assert torch.allclose(got[k], v, atol=2e-4), (k, (got[k] - v).abs().max())
+
+
+def _scaler_ranks(rank, world):
+    import torch.distributed as dist
+    from oslo_b200.optim import DynamicLossScaler, FusedAdamW
+    from oslo_b200.parallel.data_parallel import DistributedDataParallel
+    model = ob.parallelize(build("gpt2").train(), pipeline_parallel_size=2, micro_batch_size=2)
+    mpu = model.mpu
+    opt = FusedAdamW(model.gpu_parameters(), lr=1e-2, shard_group=mpu.get_data_parallel_group(),
+                     model_parallel_group=mpu.get_model_parallel_group(), loss_scaler=DynamicLossScaler(init_scale=8.0))
+    ddp = DistributedDataParallel(model, mpu, optimizer=opt)
+    stepped = []
+    for s in range(3):
+        opt.zero_grad()
+        for out in ddp(**batch(seed=3 + s)):
+            opt.loss_scaler.scale(out.loss / 2).backward()
+        if s == 1 and rank == 0:
+            opt.buf.flat_g[5] = float("nan")          # an overflow that ONE rank sees
+        stepped.append(opt.step())
+    seen = [None] * world
+    dist.all_gather_object(seen, (stepped, opt.step_count, opt.loss_scaler.loss_scale))
+    assert all(s == seen[0] for s in seen), seen
+    assert stepped == [True, False, True] and opt.step_count == 2 and opt.loss_scaler.loss_scale == 4.0, seen[0]
+
+
+def test_loss_scaler_skips_on_every_rank_when_one_rank_overflows():
+    """PP2 x DP2: the overflow check rides on the gradient-norm reduction over the shard and model-parallel groups."""
+    run_distributed(_scaler_ranks, 4)
