@@ -25,6 +25,9 @@ class GraphedGreedyDecoder:
     """
 
     def __init__(self, model, max_len: int, use_graph: Optional[bool] = None, warmup_steps: int = 2) -> None:
+        if getattr(model, "is_pipeline_parallelized", lambda: False)():
+            raise NotImplementedError("GraphedGreedyDecoder runs one model call per token on this rank; a pipeline-"
+                                      "parallel model needs the stage exchange of model.generate() instead")
         self.model = model
         self.max_len = int(max_len)
         self.use_graph = use_graph

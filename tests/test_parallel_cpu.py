@@ -502,9 +502,15 @@ def _misuse_ranks(rank, world):
         ob.parallelize(build("gptj"), tensor_parallel_size=2, pipeline_parallel_size=2)
     with pytest.raises(ValueError, match="power of two"):
         ob.parallelize(build("gptj"), tensor_parallel_size=3)
+    pp_model = ob.parallelize(build("gpt2"), pipeline_parallel_size=2)
     with pytest.raises(ValueError, match="keyword arguments only"):
-        pp_model = ob.parallelize(build("gpt2"), pipeline_parallel_size=2)
         pp_model(batch()["input_ids"])
+    from oslo_b200.generation import GraphedGreedyDecoder
+    with pytest.raises(NotImplementedError, match="pipeline"):
+        GraphedGreedyDecoder(pp_model, max_len=16)
+    ids = batch()["input_ids"][:, :4]          # the flag falls back to the ordinary greedy loop under PP
+    assert torch.equal(pp_model.generate(ids, max_new_tokens=3, cuda_graph=True, pad_token_id=0),
+                       pp_model.generate(ids, max_new_tokens=3, pad_token_id=0))
 
 
 def test_misuse_raises_clear_errors():
