@@ -62,6 +62,9 @@ def parse_args():
     ap.add_argument("--resume", action="store_true", help="continue from the checkpoint in --save")
     ap.add_argument("--metrics", help="JSONL file for per-step metrics (rank 0)")
     ap.add_argument("--seed", type=int, default=1234)
+    ap.add_argument("--watchdog", action="store_true",
+                    help="heartbeat through the rendezvous store: a rank that stops beating ends the others' next step "
+                         "with RankFailure instead of a hang; device-side wait time-outs are raised after every step")
     return ap.parse_args()
 
 
@@ -129,6 +132,11 @@ def main() -> None:
     scale = (lambda l: opt.loss_scaler.scale(l)) if opt.loss_scaler is not None else (lambda l: l)
     metrics = MetricsLogger(args.metrics or "")
     data = batches(args, mpu, model.config.vocab_size, mpu.device)
+    beat = None
+    if args.watchdog and dist.is_initialized() and dist.get_world_size() > 1:
+        from torch.distributed.distributed_c10d import _get_default_store
+        from oslo_b200.utils import Heartbeat
+        beat = Heartbeat(_get_default_store(), dist.get_rank(), dist.get_world_size()).start()
     for _ in range(step0):          # a resumed run continues with the batch the interrupted one would have seen
         next(data)
 
@@ -141,6 +149,8 @@ def main() -> None:
             model.save_pretrained_with_parallel(os.path.join(args.save, "merged"), save_with_merging=True)
 
     for step in range(step0 + 1, args.steps + 1):
+        if beat is not None:
+            beat.check_peers()      # host-side: raises before this rank enters a collective nobody will join
         ids = next(data)
         opt.zero_grad()
         total = 0.0
@@ -158,11 +168,16 @@ def main() -> None:
                     scale(loss / accum).backward()
                 total += float(loss.detach()) / accum
         stepped = opt.step()
+        if on_gpu and args.watchdog:
+            from oslo_b200.utils import raise_if_device_error
+            raise_if_device_error(ids)
         rec = metrics.log_step(step, loss=total, tokens=dp * args.batch_size * args.seq, skipped=not stepped)
         log.info("step %d loss %.4f %.0f tokens/s", step, total, rec.get("tokens_per_s", 0.0))
         if args.save_every and step % args.save_every == 0:
             save(step)
     save(args.steps)
+    if beat is not None:
+        beat.stop()
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()

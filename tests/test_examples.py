@@ -67,6 +67,6 @@ def test_preprocess_train_resume_merge_generate(tmp_path):
 def test_train_example_data_parallel_zero1(tmp_path):
     out = str(tmp_path / "dp")
     _torchrun(2, "train.py", "--model", "gpt2", "--tiny", "--batch-size", "4", "--micro-batch-size", "2", "--seq", "16",
-              "--steps", "2", "--save", out)
+              "--steps", "2", "--save", out, "--watchdog")
     assert os.path.isfile(os.path.join(out, "pytorch_model.bin"))      # no model parallelism: the plain HF file
     assert all(os.path.isfile(os.path.join(out, f"oslo_state_tp=0_pp=0_dp={d}.pt")) for d in range(2))
