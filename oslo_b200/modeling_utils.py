@@ -382,18 +382,44 @@ def _is_tied_key(model: PreTrainedModel, key: str) -> bool:
     return key.startswith("lm_head.weight") and getattr(model.config, "tie_word_embeddings", True)
 
 
+def _load_one_file(path: str) -> Dict[str, torch.Tensor]:
+    if path.endswith(".safetensors"):
+        from safetensors.torch import load_file
+        return load_file(path)
+    return torch.load(path, map_location="cpu", weights_only=True)
+
+
+def _load_sharded(directory: str, index_name: str) -> Dict[str, torch.Tensor]:
+    """Hugging Face sharded checkpoint: ``<name>.index.json`` maps every key to one of several shard files
+    (how multi-GB checkpoints such as GPT-J-6B are published)."""
+    import json
+    with open(os.path.join(directory, index_name)) as f:
+        weight_map = json.load(f)["weight_map"]
+    state: Dict[str, torch.Tensor] = {}
+    for shard in sorted(set(weight_map.values())):
+        full = os.path.join(directory, shard)
+        if not os.path.isfile(full):
+            raise FileNotFoundError(f"{index_name} names {shard}, which is missing from {directory!r}")
+        state.update(_load_one_file(full))
+    missing = [k for k in weight_map if k not in state]
+    if missing:
+        raise RuntimeError(f"{index_name}: {len(missing)} keys not found in their shard files, e.g. {missing[:3]}")
+    return state
+
+
 def load_checkpoint_file(name_or_path: str) -> Dict[str, torch.Tensor]:
     cands = []
     if os.path.isdir(name_or_path):
         cands = [os.path.join(name_or_path, WEIGHTS_NAME), os.path.join(name_or_path, SAFE_WEIGHTS_NAME)]
+        if not any(os.path.isfile(c) for c in cands):
+            for index_name in (WEIGHTS_NAME + ".index.json", SAFE_WEIGHTS_NAME + ".index.json"):
+                if os.path.isfile(os.path.join(name_or_path, index_name)):
+                    return _load_sharded(name_or_path, index_name)
     elif os.path.isfile(name_or_path):
         cands = [name_or_path]
     for c in cands:
         if os.path.isfile(c):
-            if c.endswith(".safetensors"):
-                from safetensors.torch import load_file
-                return load_file(c)
-            return torch.load(c, map_location="cpu", weights_only=True)
+            return _load_one_file(c)
     for fn in (WEIGHTS_NAME, SAFE_WEIGHTS_NAME):
         try:
             return load_checkpoint_file(_resolve_hub_file(name_or_path, fn))

@@ -1,4 +1,6 @@
 """Single-process model numerics against the Hugging Face implementations (same weights, CPU fp32)."""
+import os
+
 import pytest
 import torch
 
@@ -160,6 +162,40 @@ def test_checkpoints_interchange_with_hf(kind, tmp_path):
     back = type(hf).from_pretrained(tmp_path / "ours").eval()
     with torch.no_grad():
         assert torch.allclose(back(input_ids=x).logits, want, atol=2e-4, rtol=1e-4)
+
+
+def test_sharded_hf_checkpoints_load(tmp_path):
+    """Multi-file checkpoints (`*.index.json` + shard files), as large models are published: the safetensors shards
+    Hugging Face writes, and legacy `pytorch_model-0000x-of-0000y.bin` shards."""
+    import json
+    torch.manual_seed(0)
+    hf = transformers.GPTJForCausalLM(transformers.GPTJConfig(vocab_size=97, n_positions=32, n_embd=48, n_layer=2,
+                                                              n_head=4, rotary_dim=8)).eval()
+    x = torch.randint(0, 97, (2, 9))
+    with torch.no_grad():
+        want = hf(input_ids=x).logits
+    hf.save_pretrained(tmp_path / "st", max_shard_size="60KB")
+    assert (tmp_path / "st" / "model.safetensors.index.json").is_file() and not (tmp_path / "st" / "model.safetensors").exists()
+    ours = ob.GPTJForCausalLM.from_pretrained(str(tmp_path / "st")).eval()
+    with torch.no_grad():
+        assert torch.allclose(ours(input_ids=x).logits, want, atol=2e-4, rtol=1e-4)
+
+    ours.save_pretrained(str(tmp_path / "one"))                     # re-cut our single file into two .bin shards
+    state = torch.load(tmp_path / "one" / "pytorch_model.bin", weights_only=True)
+    keys = sorted(state)
+    shards = {"pytorch_model-00001-of-00002.bin": keys[: len(keys) // 2], "pytorch_model-00002-of-00002.bin": keys[len(keys) // 2:]}
+    (tmp_path / "bins").mkdir()
+    for name, ks in shards.items():
+        torch.save({k: state[k] for k in ks}, tmp_path / "bins" / name)
+    json.dump({"metadata": {}, "weight_map": {k: n for n, ks in shards.items() for k in ks}},
+              open(tmp_path / "bins" / "pytorch_model.bin.index.json", "w"))
+    (tmp_path / "bins" / "config.json").write_text((tmp_path / "one" / "config.json").read_text())
+    again = ob.GPTJForCausalLM.from_pretrained(str(tmp_path / "bins")).eval()
+    with torch.no_grad():
+        assert torch.allclose(again(input_ids=x).logits, want, atol=2e-4, rtol=1e-4)
+    os.remove(tmp_path / "bins" / "pytorch_model-00002-of-00002.bin")
+    with pytest.raises(FileNotFoundError, match="missing"):
+        ob.GPTJForCausalLM.from_pretrained(str(tmp_path / "bins"))
 
 
 def test_logits_processors_match_hf():
