@@ -8,6 +8,7 @@ combines the base with the parallelisation, kernel-fusion and generation mixins
 """
 from __future__ import annotations
 
+import contextlib
 import copy
 import json
 import os
@@ -233,8 +234,11 @@ class PreTrainedModel(nn.Module, ParallelizationMixin, FusedKernelMixin, Generat
     def get_output_embeddings(self) -> Optional[nn.Module]:
         return None
 
+    _skip_weight_init = False   # set by `no_weight_init()` while a checkpoint is about to overwrite every tensor
+
     def post_init(self) -> None:
-        self.apply(self._init_weights)
+        if not PreTrainedModel._skip_weight_init:
+            self.apply(self._init_weights)
         self.tie_weights()
 
     def _init_weights(self, module: nn.Module) -> None:
@@ -332,10 +336,23 @@ class PreTrainedModel(nn.Module, ParallelizationMixin, FusedKernelMixin, Generat
         torch_dtype = to_torch_dtype(torch_dtype)
         if torch_dtype is not None:
             config.torch_dtype = torch_dtype
-        model = cls._from_config(config, torch_dtype=torch_dtype)
         if state_dict is None:
             state_dict = load_checkpoint_file(name_or_path)
-        model.load_checkpoint_state(state_dict)
+        if low_cpu_mem_usage:
+            # reference: oslo/parallelism_utils.py:345-351. Random initialisation of tensors that the checkpoint
+            # overwrites anyway is the slow part of loading a multi-billion-parameter model on the host: skip it,
+            # then initialise only what the checkpoint did not bring (e.g. a new classification head)
+            with no_weight_init():
+                model = cls._from_config(config, torch_dtype=torch_dtype)
+            missing = set(model.load_checkpoint_state(state_dict))
+            state_dict.clear()
+            for name, module in model.named_modules():
+                own = [f"{name}.{n}" if name else n for n, _ in module.named_parameters(recurse=False)]
+                if any(k in missing for k in own):
+                    model._init_weights(module)
+        else:
+            model = cls._from_config(config, torch_dtype=torch_dtype)
+            model.load_checkpoint_state(state_dict)
         model.tie_weights()
         model.eval()
         return model
@@ -376,6 +393,25 @@ class PreTrainedModel(nn.Module, ParallelizationMixin, FusedKernelMixin, Generat
         ignore = self._keys_to_ignore_on_save or []
         state_dict = {k: v for k, v in state_dict.items() if k not in ignore}
         save_function(state_dict, os.path.join(save_directory, WEIGHTS_NAME))
+
+
+@contextlib.contextmanager
+def no_weight_init():
+    """Build modules without filling their parameters: ``torch.nn.init``'s random fills (what ``nn.Linear`` /
+    ``nn.Embedding`` run in their constructors) and ``PreTrainedModel.post_init``'s pass become no-ops."""
+    import torch.nn.init as init
+    names = ("kaiming_uniform_", "uniform_", "normal_", "trunc_normal_", "xavier_uniform_", "xavier_normal_")
+    saved = {n: getattr(init, n) for n in names}
+    prev = PreTrainedModel._skip_weight_init
+    try:
+        for n in names:
+            setattr(init, n, lambda tensor, *a, **k: tensor)
+        PreTrainedModel._skip_weight_init = True
+        yield
+    finally:
+        for n, f in saved.items():
+            setattr(init, n, f)
+        PreTrainedModel._skip_weight_init = prev
 
 
 def _is_tied_key(model: PreTrainedModel, key: str) -> bool:

@@ -221,10 +221,16 @@ class ParallelizationMixin:
     def _parallelize_from_split_checkpoint_files(cls, path: str, par: Dict[str, Any], **kwargs: Any):
         config = kwargs.pop("config", None) or cls.config_class.from_pretrained(path)
         torch_dtype = kwargs.pop("torch_dtype", getattr(config, "torch_dtype", None))
+        low_mem = bool(kwargs.pop("low_cpu_mem_usage", False))
         for k, v in kwargs.items():
             setattr(config, k, v)
         set_seed(par.get("seed"))
-        model = cls._from_config(config, torch_dtype=torch_dtype)
+        if low_mem:   # every tensor this rank keeps comes from its file: skip the random fill of the full model
+            from .modeling_utils import no_weight_init
+            with no_weight_init():
+                model = cls._from_config(config, torch_dtype=torch_dtype)
+        else:
+            model = cls._from_config(config, torch_dtype=torch_dtype)
         if par.get("deployment"):
             return cls._exec_deployment_engine(model, split_checkpoint_path=path, **par)
         par = {k: v for k, v in par.items() if k != "deployment"}

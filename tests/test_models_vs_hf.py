@@ -261,3 +261,36 @@ def test_masks_attentions_hidden_states_and_embeds_match_hf(kind):
     emb = hf.get_input_embeddings()(x)
     with torch.no_grad():
         assert torch.allclose(ours(inputs_embeds=emb).logits, hf(inputs_embeds=emb).logits, atol=3e-4)
+
+
+def test_low_cpu_mem_usage_skips_redundant_initialisation(tmp_path):
+    """`low_cpu_mem_usage=True`: same weights and logits, no random fill of tensors the checkpoint overwrites, and
+    tensors the checkpoint lacks (a new classification head) still get their proper initialisation."""
+    import torch.nn.init as init
+    torch.manual_seed(0)
+    cfg = ob.GPTJConfig(vocab_size=97, n_positions=32, n_embd=48, n_layer=2, n_head=4, rotary_dim=8)
+    model = ob.GPTJForCausalLM(cfg).eval()
+    model.save_pretrained(str(tmp_path))
+    x = torch.randint(0, 97, (2, 9))
+    calls = []
+    real = init.kaiming_uniform_
+    init.kaiming_uniform_ = lambda t, *a, **k: (calls.append(1), real(t, *a, **k))[1]
+    try:
+        slow = ob.GPTJForCausalLM.from_pretrained(str(tmp_path))
+        n_slow = len(calls)
+        fast = ob.GPTJForCausalLM.from_pretrained(str(tmp_path), low_cpu_mem_usage=True)
+        assert n_slow > 0 and len(calls) == n_slow          # no constructor fill on the fast path
+    finally:
+        init.kaiming_uniform_ = real
+    assert init.normal_.__name__ == "normal_"               # the patches are gone afterwards
+    with torch.no_grad():
+        want = model(input_ids=x).logits
+        assert torch.equal(fast(input_ids=x).logits, want) and torch.equal(slow(input_ids=x).logits, want)
+    cls_cfg = ob.GPTJConfig(vocab_size=97, n_positions=32, n_embd=48, n_layer=2, n_head=4, rotary_dim=8, num_labels=3,
+                            pad_token_id=0)
+    cls_cfg.save_pretrained(str(tmp_path))
+    head = ob.GPTJForSequenceClassification.from_pretrained(str(tmp_path), low_cpu_mem_usage=True)
+    w = head.score.weight.detach()
+    assert torch.isfinite(w).all() and 0.005 < float(w.std()) < 0.05    # initializer_range 0.02, not raw memory
+    fresh = ob.GPTJForCausalLM(cfg)
+    assert float(fresh.lm_head.weight.std()) > 0.005                     # ordinary construction still initialises
