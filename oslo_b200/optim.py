@@ -153,6 +153,16 @@ class FusedAdamW:
         self._sp_params = list(getattr(model, "_sp_partial_params", []) or []) if model is not None else []
         self._sp_group = model.mpu.get_tensor_parallel_group() if self._sp_params else None
         self.param_groups = [dict(params=self.buf.params, lr=lr, betas=self.betas, eps=eps, weight_decay=weight_decay)]
+        # gradients that another model-parallel rank also holds (tensors replicated over the tensor-parallel group,
+        # the last pipeline stage's copy of a tied embedding) count once in the global norm: the parts of them that
+        # fall into this rank's shard are subtracted again
+        self._dup_ranges: List[tuple] = []      # relative to this rank's shard of the flat buffer
+        for p, off in zip(self.buf.params, self.buf.offsets):
+            if getattr(p, "_oslo_norm_dup", False):
+                a, b = max(off, self._lo), min(off + p.numel(), self._hi)
+                if b > a:
+                    self._dup_ranges.append((a - self._lo, b - self._lo))
+        self._dup_cache = (None, [])            # (data_ptr of the gradient shard, its views)
 
     # ------------------------------------------------------------------ API
     def zero_grad(self, set_to_none: bool = False) -> None:
@@ -164,6 +174,15 @@ class FusedAdamW:
             sq = ops.load_ext().sumsq(g)
         else:
             sq = g.float().pow(2).sum().reshape(1)
+        if self._dup_ranges:
+            if g.untyped_storage().data_ptr() != self.buf.flat_g.untyped_storage().data_ptr():
+                views = [g[a:b] for a, b in self._dup_ranges]      # a temporary (reduce-scatter output): keep nothing
+            else:
+                if self._dup_cache[0] != g.data_ptr():
+                    self._dup_cache = (g.data_ptr(), [g[a:b] for a, b in self._dup_ranges])
+                views = self._dup_cache[1]
+            dup = torch.stack(torch._foreach_norm(views)).float().pow(2).sum()
+            sq = (sq - dup).clamp_min(0.0)
         for grp in (self.shard_group, self.model_parallel_group):
             if grp is not None and dist.get_world_size(grp) > 1:
                 dist.all_reduce(sq, group=grp)

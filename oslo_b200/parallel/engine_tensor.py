@@ -98,6 +98,12 @@ class TensorParallelEngine:
         for layer in model.get_head_layers():
             self._head(layer)
         model._tp_specs = self.specs
+        # parameters that were not cut exist once per tensor-parallel rank with the same gradient: in a global
+        # gradient norm only the copy on rank 0 counts (FusedAdamW.grad_norm leaves the marked ones out)
+        if self.rank != 0:
+            for p in model.parameters():
+                if not getattr(p, "_oslo_tp_sharded", False):
+                    p._oslo_norm_dup = True
         if self.sequence_parallel:
             model.base_model.sequence_parallel = True
             # parameters applied to a token shard see only 1/tp of the tokens: their gradients are partial sums
@@ -128,6 +134,7 @@ class TensorParallelEngine:
         if p is None:
             return
         self._record(p, ShardSpec(kind, dim, n_fused, p.size(dim) if p.numel() else -1))
+        p._oslo_tp_sharded = True
         if self.owned(p) and p.numel():
             p.data = shard_tensor(p.data, self.tp, self.rank, dim, n_fused)
 

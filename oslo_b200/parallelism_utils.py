@@ -146,6 +146,10 @@ class ParallelizationMixin:
             TensorParallelEngine(self, mpu, owned=pipe.owns_param, device=device,
                                  sequence_parallel=sequence_parallel).parallelize()
         pipe.finalize()
+        if pp > 1 and pipe.last and getattr(self.config, "tie_word_embeddings", True) \
+                and self.get_output_embeddings() is not None:
+            # the last stage's copy of a tied embedding carries the same (summed) gradient as the first stage's
+            self.get_input_embeddings().weight._oslo_norm_dup = True
         self.initial_parameters = dict(
             tensor_parallel_size=tp, pipeline_parallel_size=pp, micro_batch_size=micro_batch_size,
             resize_token_embeddings=resize_token_embeddings, seed=seed, sequence_parallel=sequence_parallel)

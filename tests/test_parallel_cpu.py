@@ -614,3 +614,48 @@ def _scaler_ranks(rank, world):
 def test_loss_scaler_skips_on_every_rank_when_one_rank_overflows():
     """PP2 x DP2: the overflow check rides on the gradient-norm reduction over the shard and model-parallel groups."""
     run_distributed(_scaler_ranks, 4)
+
+
+def _clip_ranks(rank, world, kind, tp, pp, steps, tmpdir):
+    from oslo_b200.optim import FusedAdamW
+    from oslo_b200.parallel.data_parallel import DistributedDataParallel
+    model = ob.parallelize(build(kind).train(), tensor_parallel_size=tp, pipeline_parallel_size=pp, micro_batch_size=1,
+                           sequence_parallel=(tp > 1 and pp == 1))
+    mpu = model.mpu
+    opt = FusedAdamW(model.gpu_parameters(), lr=1e-2, weight_decay=0.01, max_grad_norm=0.5, model=model,
+                     shard_group=mpu.get_data_parallel_group(), model_parallel_group=mpu.get_model_parallel_group())
+    ddp = DistributedDataParallel(model, mpu, optimizer=opt, bucket_mb=0.01)
+    dp, dpr = mpu.get_data_parallel_world_size(), mpu.get_data_parallel_rank()
+    for s in range(steps):
+        b = batch(seed=3 + s)
+        n = b["input_ids"].size(0) // dp
+        mine = {k: v[dpr * n:(dpr + 1) * n] for k, v in b.items()}
+        opt.zero_grad()
+        if pp > 1:
+            for out in ddp(**mine):
+                (out.loss / n).backward()
+        else:
+            ddp(**mine).loss.backward()
+        opt.step()
+    model.save_pretrained_with_parallel(os.path.join(tmpdir, "merged"), save_with_merging=True)
+
+
+@pytest.mark.parametrize("kind,tp,pp", [("gptj", 2, 1), ("gpt2", 1, 2), ("gpt_neo", 2, 2)])
+def test_gradient_clipping_counts_every_parameter_once(kind, tp, pp):
+    """Global-norm clipping on model-parallel ranks == `clip_grad_norm_` of one process: tensors replicated over the
+    tensor-parallel group and the last stage's copy of a tied embedding must not be counted twice."""
+    steps, world = 3, tp * pp * 2 if tp * pp < 4 else 4
+    torch.manual_seed(0)
+    ref = build(kind).train()
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.01)
+    for s in range(steps):
+        opt.zero_grad()
+        ref(**batch(seed=3 + s)).loss.backward()
+        torch.nn.utils.clip_grad_norm_(ref.parameters(), 0.5)
+        opt.step()
+    with tempfile.TemporaryDirectory() as d:
+        run_distributed(_clip_ranks, world, kind, tp, pp, steps, d)
+        got = torch.load(os.path.join(d, "merged", "pytorch_model.bin"), weights_only=True)
+    for k, v in ref.state_dict().items():
+        if k in got:
+            assert torch.allclose(got[k], v, atol=3e-4), (k, float((got[k] - v).abs().max()))
