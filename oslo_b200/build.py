@@ -22,8 +22,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 BUILD = os.path.join(HERE, "csrc", "build")
 
-CUDA_SOURCES = ["gemm_sm100.cu", "elementwise.cu", "attention.cu", "attention_sm100.cu", "attention_bwd_sm100.cu", "decode_sm100.cu", "comm.cu", "fused_comm_gemm.cu",
-                "noalloc_colsum.cu"]
+CUDA_SOURCES = ["gemm_sm100.cu", "elementwise.cu", "attention.cu", "attention_sm100.cu", "attention_bwd_sm100.cu",
+                "decode_sm100.cu", "comm.cu", "fused_comm_gemm.cu", "noalloc_colsum.cu"]
 CPP_SOURCES = ["bindings.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",
               "--use_fast_math", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

@@ -181,7 +181,7 @@ class FusedAdamW:
                 if self._dup_cache[0] != g.data_ptr():
                     self._dup_cache = (g.data_ptr(), [g[a:b] for a, b in self._dup_ranges])
                 views = self._dup_cache[1]
-            dup = torch.stack(torch._foreach_norm(views, 2, dtype=torch.float32)).pow(2).sum()   # fp32 out of 16-bit grads
+            dup = torch.stack(torch._foreach_norm(views, 2, dtype=torch.float32)).pow(2).sum()
             sq = (sq - dup).clamp_min(0.0)
         for grp in (self.shard_group, self.model_parallel_group):
             if grp is not None and dist.get_world_size(grp) > 1:
