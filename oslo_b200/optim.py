@@ -137,7 +137,14 @@ class FusedAdamW:
         self.shards = dist.get_world_size(shard_group) if shard_group is not None else 1
         self.shard_rank = dist.get_rank(shard_group) if shard_group is not None else 0
         self.grad_average_group = grad_average_group
-        self.buf = FlatBuffers(params, pad_to=8 * self.shards)
+        # `params` is an iterable of parameters or, as with torch optimizers, a list of groups
+        # ``{"params": [...], "weight_decay": 0.0, "lr": ...}``: the groups lie one after the other in the flat buffer
+        params = list(params)
+        if params and isinstance(params[0], dict):
+            groups = [dict(g, params=list(g["params"])) for g in params]
+        else:
+            groups = [dict(params=params)]
+        self.buf = FlatBuffers([p for g in groups for p in g["params"]], pad_to=8 * self.shards)
         n = self.buf.padded // self.shards
         self.shard_numel = n
         lo = self.shard_rank * n
@@ -152,7 +159,30 @@ class FusedAdamW:
         # gradients must be summed over the tensor-parallel group before the update
         self._sp_params = list(getattr(model, "_sp_partial_params", []) or []) if model is not None else []
         self._sp_group = model.mpu.get_tensor_parallel_group() if self._sp_params else None
-        self.param_groups = [dict(params=self.buf.params, lr=lr, betas=self.betas, eps=eps, weight_decay=weight_decay)]
+        # one entry per group, torch style (learning-rate schedulers write `param_groups[i]["lr"]`); `_group_ranges`
+        # holds each group's part of this rank's shard, relative to the shard
+        index = {id(p): i for i, p in enumerate(self.buf.params)}
+        self.param_groups, self._group_ranges = [], []
+        for g in groups:
+            kept = [p for p in g["params"] if id(p) in index]
+            self.param_groups.append(dict(params=kept, lr=g.get("lr", lr), betas=self.betas, eps=eps,
+                                          weight_decay=g.get("weight_decay", weight_decay)))
+        bounds, seen_ids = [], set()
+        for g in self.param_groups:
+            ids = [index[id(p)] for p in g["params"] if id(p) not in seen_ids]
+            seen_ids.update(id(p) for p in g["params"])
+            if ids and ids != list(range(ids[0], ids[-1] + 1)):
+                raise ValueError("a parameter appears in more than one group")
+            bounds.append((self.buf.offsets[ids[0]], None) if ids else None)
+        starts = [b[0] for b in bounds if b is not None] + [self.buf.padded]
+        k = 0
+        for b in bounds:
+            if b is None:
+                self._group_ranges.append(None)
+                continue
+            a, e = max(starts[k], self._lo), min(starts[k + 1], self._hi)
+            self._group_ranges.append((a - self._lo, e - self._lo) if e > a else None)
+            k += 1
         # gradients that another model-parallel rank also holds (tensors replicated over the tensor-parallel group,
         # the last pipeline stage's copy of a tied embedding) count once in the global norm: the parts of them that
         # fall into this rank's shard are subtracted again
@@ -203,7 +233,6 @@ class FusedAdamW:
     def step(self) -> bool:
         """One update; returns False when the loss scaler saw an overflow and the update was skipped."""
         self.sync_sequence_parallel_grads()
-        lr = self.param_groups[0]["lr"]
         b1, b2 = self.betas
         g_full = self.buf.flat_g
         if self.shards > 1 and self.grads_already_reduced:
@@ -237,16 +266,23 @@ class FusedAdamW:
             norm = (self.grad_norm(g) if norm is None else norm) * grad_scale
             inv = torch.clamp(self.max_grad_norm / (norm + 1e-6), max=1.0).float()
         lp = self.buf.flat_p[self._lo: self._hi]
-        if g.is_cuda and ops.kernels_available():
-            ops.load_ext().adam_step(self.master, g, self.exp_avg, self.exp_avg_sq,
-                                     lp if lp.dtype != torch.float32 else None, lr, b1, b2, self.eps,
-                                     self.weight_decay, self.step_count, grad_scale, inv)
-            if lp.dtype == torch.float32:
-                lp.copy_(self.master)
-        else:
-            scale = grad_scale * (float(inv) if inv is not None else 1.0)
-            ops.reference.adam_step(self.master, g, self.exp_avg, self.exp_avg_sq, self.step_count, lr, b1, b2,
-                                    self.eps, self.weight_decay, scale, lp)
+        use_kernel = g.is_cuda and ops.kernels_available()
+        scale = None if use_kernel else grad_scale * (float(inv) if inv is not None else 1.0)
+        for group, rng in zip(self.param_groups, self._group_ranges):     # one launch per group (usually one or two)
+            if rng is None:
+                continue
+            a, e = rng
+            whole = a == 0 and e == self.shard_numel
+            m_, g_, ea_, es_, lp_ = ((self.master, g, self.exp_avg, self.exp_avg_sq, lp) if whole else
+                                     (self.master[a:e], g[a:e], self.exp_avg[a:e], self.exp_avg_sq[a:e], lp[a:e]))
+            if use_kernel:
+                ops.load_ext().adam_step(m_, g_, ea_, es_, lp_ if lp.dtype != torch.float32 else None, group["lr"],
+                                         b1, b2, self.eps, group["weight_decay"], self.step_count, grad_scale, inv)
+            else:
+                ops.reference.adam_step(m_, g_, ea_, es_, self.step_count, group["lr"], b1, b2, self.eps,
+                                        group["weight_decay"], scale, lp_)
+        if use_kernel and lp.dtype == torch.float32:
+            lp.copy_(self.master)
         if self.shards > 1:
             if dist.get_backend(self.shard_group) == "gloo":
                 parts = [torch.empty_like(lp) for _ in range(self.shards)]

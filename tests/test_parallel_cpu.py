@@ -659,3 +659,49 @@ def test_gradient_clipping_counts_every_parameter_once(kind, tp, pp):
     for k, v in ref.state_dict().items():
         if k in got:
             assert torch.allclose(got[k], v, atol=3e-4), (k, float((got[k] - v).abs().max()))
+
+
+def _decay_groups(model):
+    """The usual split: matrices decay, biases and LayerNorm parameters do not."""
+    decay = [p for p in model.parameters() if p.dim() >= 2]
+    rest = [p for p in model.parameters() if p.dim() < 2]
+    return [dict(params=decay, weight_decay=0.1), dict(params=rest, weight_decay=0.0, lr=2e-2)]
+
+
+def _groups_ranks(rank, world, steps, tmpdir):
+    from oslo_b200.optim import FusedAdamW
+    from oslo_b200.parallel.data_parallel import DistributedDataParallel
+    model = ob.parallelize(build("gptj").train(), tensor_parallel_size=1)
+    mpu = model.mpu
+    opt = FusedAdamW(_decay_groups(model), lr=1e-2, shard_group=mpu.get_data_parallel_group())
+    assert [g["weight_decay"] for g in opt.param_groups] == [0.1, 0.0] and opt.param_groups[1]["lr"] == 2e-2
+    ddp = DistributedDataParallel(model, mpu, optimizer=opt, bucket_mb=0.01)
+    for s in range(steps):
+        b = batch(seed=3 + s)
+        n = b["input_ids"].size(0) // world
+        opt.zero_grad()
+        ddp(**{k: v[rank * n:(rank + 1) * n] for k, v in b.items()}).loss.backward()
+        if s == 1:
+            opt.param_groups[0]["lr"] = 5e-3          # what a learning-rate scheduler does
+        opt.step()
+    if rank == 0:
+        torch.save({k: v.detach().clone() for k, v in model.state_dict().items()}, os.path.join(tmpdir, "state.pt"))
+
+
+def test_parameter_groups_with_their_own_weight_decay_and_lr():
+    """Torch-style groups on the one flat buffer (ZeRO-1 over 2 ranks: the group boundary falls inside a shard)."""
+    steps = 3
+    torch.manual_seed(0)
+    ref = build("gptj").train()
+    opt = torch.optim.AdamW(_decay_groups(ref), lr=1e-2)
+    for s in range(steps):
+        opt.zero_grad()
+        ref(**batch(seed=3 + s)).loss.backward()
+        if s == 1:
+            opt.param_groups[0]["lr"] = 5e-3
+        opt.step()
+    with tempfile.TemporaryDirectory() as d:
+        run_distributed(_groups_ranks, 2, steps, d)
+        got = torch.load(os.path.join(d, "state.pt"), weights_only=True)
+    for k, v in ref.state_dict().items():
+        assert torch.allclose(got[k], v, atol=2e-4), (k, float((got[k] - v).abs().max()))
