@@ -118,7 +118,10 @@ def main() -> None:
         model.gradient_checkpointing_enable()
     mpu = model.mpu
     dp, mp = mpu.get_data_parallel_world_size(), args.tp * args.pp
-    opt = FusedAdamW(model.gpu_parameters(), lr=args.lr, betas=(0.9, 0.95), weight_decay=0.1, max_grad_norm=1.0,
+    params = list(model.gpu_parameters())
+    groups = [dict(params=[p for p in params if p.dim() >= 2], weight_decay=0.1),      # matrices decay,
+              dict(params=[p for p in params if p.dim() < 2], weight_decay=0.0)]       # biases and LayerNorm do not
+    opt = FusedAdamW(groups, lr=args.lr, betas=(0.9, 0.95), max_grad_norm=1.0,
                      shard_group=mpu.get_data_parallel_group() if dp > 1 else None,
                      model_parallel_group=mpu.get_model_parallel_group() if mp > 1 else None, model=model,
                      loss_scaler=DynamicLossScaler() if dtype == torch.float16 else None)
