@@ -296,7 +296,8 @@ class FusedAdamW:
     def state_dict(self) -> Dict[str, object]:
         return dict(step=self.step_count, master=self.master.cpu(), exp_avg=self.exp_avg.cpu(),
                     exp_avg_sq=self.exp_avg_sq.cpu(), shard_rank=self.shard_rank, shards=self.shards, lr=self.lr,
-                    loss_scaler=self.loss_scaler.state_dict() if self.loss_scaler is not None else None)
+                    loss_scaler=self.loss_scaler.state_dict() if self.loss_scaler is not None else None,
+                    group_lrs=[g["lr"] for g in self.param_groups])
 
     def load_state_dict(self, sd: Dict[str, object]) -> None:
         if sd["shards"] != self.shards or sd["shard_rank"] != self.shard_rank:
@@ -306,5 +307,9 @@ class FusedAdamW:
         self.exp_avg.copy_(sd["exp_avg"])
         self.exp_avg_sq.copy_(sd["exp_avg_sq"])
         self.buf.flat_p[self._lo: self._hi].copy_(self.master)
+        lrs = sd.get("group_lrs")
+        if lrs is not None and len(lrs) == len(self.param_groups):
+            for g, lr in zip(self.param_groups, lrs):     # where a schedule had brought each group
+                g["lr"] = lr
         if self.loss_scaler is not None and sd.get("loss_scaler") is not None:
             self.loss_scaler.load_state_dict(sd["loss_scaler"])
