@@ -85,12 +85,26 @@ class DistributedDataParallel(nn.Module):
                 cur, hi = [], lo
 
     def _hook(self, p: torch.Tensor) -> None:
+        g = p.grad
+        if g is not None and g.untyped_storage().data_ptr() != self.buf.flat_g.untyped_storage().data_ptr():
+            # something (a torch optimizer's zero_grad(set_to_none=True)) dropped the view into the flat buffer and
+            # autograd made a fresh tensor: a dropped gradient counts as zero, so the fresh one replaces the stale
+            # contents of the view, and later micro-batches accumulate into the view again
+            view = self._grad_view(p)
+            view.copy_(g)
+            p.grad = view
         if not self.sync or self.world == 1 or id(p) in self._deferred:
             return
         b = self._bucket_of[id(p)]
         self._ready[b] += 1
         if self._ready[b] == len(self.buckets[b][2]):
             self._launch(b)
+
+    def _grad_view(self, p: torch.Tensor) -> torch.Tensor:
+        if not hasattr(self, "_offset_of"):
+            self._offset_of = {id(q): off for q, off in zip(self.buf.params, self.buf.offsets)}
+        off = self._offset_of[id(p)]
+        return self.buf.flat_g[off: off + p.numel()].view(p.shape)
 
     def _launch(self, b: int) -> None:
         lo, hi, _ = self.buckets[b]

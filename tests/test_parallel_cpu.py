@@ -705,3 +705,41 @@ def test_parameter_groups_with_their_own_weight_decay_and_lr():
         got = torch.load(os.path.join(d, "state.pt"), weights_only=True)
     for k, v in ref.state_dict().items():
         assert torch.allclose(got[k], v, atol=2e-4), (k, float((got[k] - v).abs().max()))
+
+
+def _ddp_torch_optimizer_ranks(rank, world, steps, tmpdir):
+    from oslo_b200.parallel.data_parallel import DistributedDataParallel
+    model = ob.parallelize(build("gptj").train(), tensor_parallel_size=1)
+    ddp = DistributedDataParallel(model, model.mpu, bucket_mb=0.01)         # no FusedAdamW: gradients are averaged
+    opt = torch.optim.AdamW(model.gpu_parameters(), lr=1e-2, weight_decay=0.01)
+    for s in range(steps):
+        b = batch(seed=3 + s)
+        n = b["input_ids"].size(0) // world
+        mine = {k: v[rank * n:(rank + 1) * n] for k, v in b.items()}
+        opt.zero_grad()                                # set_to_none=True: drops the views into the flat buffer
+        for i in range(2):                             # two micro-batches, reduced once
+            mb = {k: v[i:i + 1] for k, v in mine.items()}
+            with (ddp.no_sync() if i == 0 else __import__("contextlib").nullcontext()):
+                (ddp(**mb).loss / 2).backward()
+        ddp.finish_gradient_sync()
+        opt.step()
+    if rank == 0:
+        torch.save({k: v.detach().clone() for k, v in model.state_dict().items()}, os.path.join(tmpdir, "state.pt"))
+
+
+def test_bucketed_ddp_with_a_torch_optimizer():
+    """The wrapper without FusedAdamW: a torch optimizer whose zero_grad() sets gradients to None still gets averaged
+    gradients (the hook puts fresh gradient tensors back into the flat buffer)."""
+    steps = 3
+    torch.manual_seed(0)
+    ref = build("gptj").train()
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.01)
+    for s in range(steps):
+        opt.zero_grad()
+        ref(**batch(seed=3 + s)).loss.backward()
+        opt.step()
+    with tempfile.TemporaryDirectory() as d:
+        run_distributed(_ddp_torch_optimizer_ranks, 2, steps, d)
+        got = torch.load(os.path.join(d, "state.pt"), weights_only=True)
+    for k, v in ref.state_dict().items():
+        assert torch.allclose(got[k], v, atol=2e-4), (k, float((got[k] - v).abs().max()))
