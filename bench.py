@@ -182,7 +182,7 @@ def main() -> None:
         opt.zero_grad()
         total = None
         if pp > 1:
-            for out in model(input_ids=ids, labels=ids, output_logits=False):
+            for out in (engine if engine is not None else model)(input_ids=ids, labels=ids, output_logits=False):
                 (out.loss / accum).backward()
                 total = out.loss.detach() if total is None else total + out.loss.detach()
         else:

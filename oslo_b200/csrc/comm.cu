@@ -117,6 +117,10 @@ __global__ void __launch_bounds__(512) allreduce_symm_kernel(void* const* peer_p
       const uint4* src = reinterpret_cast<const uint4*>(peer_ptrs[rank]);
       uint4* dst = reinterpret_cast<uint4*>(out);
       for (long long i = tid; i < n16; i += nthreads) dst[i] = src[i];
+      // the staging region is shared with other collectives of this workspace: nobody may write into it again
+      // (a peer's next call) before every rank has copied its result out. The first barrier's signal words are
+      // free again by now (each was consumed before its owner could reach the second barrier).
+      block_barrier_all_ranks(signal_ptrs, rank, world, 0, err);
     }
   } else {
     uint4* dst = reinterpret_cast<uint4*>(out);
@@ -195,7 +199,11 @@ __global__ void wait_probe_kernel(const uint32_t* flag, uint32_t target, unsigne
 // or one plain store per peer), block b of every rank handles the same token range, meets block b of the other
 // ranks once, and copies its range out of its own staging buffer. Half as many bytes cross the links as in the
 // "masked lookup + all-reduce" form, and the lookup, mask, zero-fill and collective are one launch. Staging halves
-// alternate by a device-side per-block counter exactly as in the one-shot all-reduce.
+// alternate by a device-side per-block counter; the launcher always starts the same number of blocks so that all
+// counters stay equal (the token -> block split changes with the token count, unlike the one-shot all-reduce's fixed
+// 512 vectors per block). Reuse of a half two calls later is then safe without a trailing barrier: a rank that writes
+// in call n+2 has finished call n+1, whose barriers every peer block reached only after the peer's call n kernel -
+// all of its copy-outs - had completed (launches of one stream do not overlap).
 template <typename T>
 __global__ void __launch_bounds__(512) vocab_embed_kernel(const long long* __restrict__ ids, const T* __restrict__ weight,
                                                           T* __restrict__ out, void* const* peer_ptrs, void* mc_ptr,
@@ -254,7 +262,11 @@ extern "C" int oslo_vocab_embed(const long long* ids, const void* weight, void* 
   int max_blocks = 2048 / 4 / (2 * world);
   if (max_blocks > 64) max_blocks = 64;
   if (max_blocks > num_sms) max_blocks = num_sms;
-  const int blocks = static_cast<int>(tokens < max_blocks ? tokens : max_blocks);
+  // Always the same grid, whatever the token count: blocks without tokens still meet their peers and bump their
+  // counter, so every block's parity moves in lockstep and "the other half" means the same thing for every token
+  // offset on every rank. (With a grid that followed the token count, a short call - a decode step - would advance
+  // only the first counters, and two later calls could then put one token offset into the same half twice in a row.)
+  const int blocks = max_blocks;
   if (dtype == OSLO_DT_BF16)
     vocab_embed_kernel<__nv_bfloat16><<<blocks, 512, 0, stream>>>(ids, (const __nv_bfloat16*)weight, (__nv_bfloat16*)out,
                                                                   peer_ptrs_dev, mc_ptr, signal_ptrs_dev, counters, tokens,

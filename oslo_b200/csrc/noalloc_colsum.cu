@@ -64,6 +64,11 @@ extern "C" int oslo_colsum_noalloc(const void* x, float* out, int rows, int cols
   if (cols > OSLO_NOALLOC_COLSUM_MAX_COLS) return -10;  // the built-in workspace is too small: nothing launched
   if (dtype != OSLO_DT_BF16 && dtype != OSLO_DT_FP16 && dtype != OSLO_DT_FP32) return -2;
   if (cols == 0) return 0;
+  {
+    // an error left behind by an earlier launch of somebody else is reported as such, before this call's launches
+    const cudaError_t stale = cudaGetLastError();
+    if (stale != cudaSuccess) return static_cast<int>(stale);
+  }
   float* scratch = nullptr;
   const int rc = scratch_for_current_device(&scratch);
   if (rc != 0) return rc;

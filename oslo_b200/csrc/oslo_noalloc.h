@@ -24,8 +24,11 @@ extern "C" {
 //   x     : [rows, cols] row-major device buffer, dtype = OSLO_DT_BF16 / OSLO_DT_FP16 / OSLO_DT_FP32
 //   out   : [cols] float device buffer
 //   stream: stream of the CURRENT device to enqueue on
-// Returns 0 on success; -2 unknown dtype; -3 bad pointer or negative size; -10 cols exceeds
-// OSLO_NOALLOC_COLSUM_MAX_COLS (nothing is launched); a positive value is a cudaError_t.
+// Returns 0 on success; -2 unknown dtype; -3 bad pointer or negative size, and also a current-device index
+// of 64 or more or a workspace whose address could not be resolved; -10 cols exceeds
+// OSLO_NOALLOC_COLSUM_MAX_COLS (nothing is launched); a positive value is a cudaError_t. A launch error
+// that an EARLIER, unrelated call left pending on this thread is returned (and cleared) before anything is
+// launched, so that it is not mistaken for a failure of this call's kernels.
 //
 // Never calls cudaMalloc, cudaFree or any allocating routine. The first call on each device looks up the
 // device address of the built-in workspace (cudaGetSymbolAddress) and remembers it; make that first call

@@ -249,6 +249,9 @@ class FusedAdamW:
         else:
             g = g_full
             grad_scale = 1.0
+            if self.grads_already_reduced and self.grad_average_group is not None:
+                # plain data parallelism (no sharded state): the wrapper summed the buckets, the mean is taken here
+                grad_scale = 1.0 / dist.get_world_size(self.grad_average_group)
         inv = None
         norm = None
         if self.loss_scaler is not None:

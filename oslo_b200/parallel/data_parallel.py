@@ -63,6 +63,9 @@ class DistributedDataParallel(nn.Module):
             self._pipelined = False
         if optimizer is not None:
             optimizer.grads_already_reduced = True
+            # the buckets are SUMMED over this group; the optimizer turns the sum into the mean (1 / group size), also
+            # when its state is not sharded
+            optimizer.grad_average_group = self.group
             self._wrap_optimizer_step(optimizer)
 
     # ------------------------------------------------------------------ buckets

@@ -335,6 +335,11 @@ class PipelineParallelEngine:
 
         warm = min(self.pp - 1 - self.stage, m)
         done = 0
+        if self.on_last_backward is not None and m > 1:
+            # a data-parallel wrapper reduces gradients during the LAST micro-batch's backward only; say so before the
+            # first one, so that calling the model directly (not through the wrapper's forward) cannot leave the
+            # reduction switched on for every micro-batch
+            self.on_last_backward(False)
         for _ in range(warm):
             do_forward(done)
             done += 1

@@ -79,11 +79,10 @@ class SymmetricWorkspace:
         stage = self.view(n, x.dtype)
         flat = x.reshape(-1)
         stage.copy_(flat)
+        # the result is written to `flat` by the kernel itself (in multimem mode: copied out of the staging region
+        # before a trailing cross-rank barrier, so a peer's next collective on this workspace cannot overwrite it)
         ops.load_ext(required=True).allreduce_symm(self.peer_ptrs_dev, self.mc_ptr, self.signal_ptrs_dev,
-                                                  stage if use_multimem else flat, n, self.rank, self.world,
-                                                  use_multimem)
-        if use_multimem:
-            flat.copy_(stage)
+                                                  flat, n, self.rank, self.world, use_multimem)
         return x
 
 

@@ -547,8 +547,10 @@ def test_pipeline_split_checkpoint_restores_the_tied_head(kind):
         run_distributed(_pp_split_roundtrip, 2, kind, d, "load")
 
 
-def _train_pp_zero_ddp(rank, world, kind, steps, tmpdir):
-    """Pipeline stages x data-parallel replicas with the framework's own wrapper and ZeRO-1 optimizer."""
+def _train_pp_zero_ddp(rank, world, kind, steps, tmpdir, direct=False):
+    """Pipeline stages x data-parallel replicas with the framework's own wrapper and ZeRO-1 optimizer.
+    ``direct``: call the model itself instead of the wrapper's ``forward`` (the wrapper then only learns from the
+    pipeline engine which micro-batch is the last one)."""
     from oslo_b200.optim import FusedAdamW
     from oslo_b200.parallel.data_parallel import DistributedDataParallel
     model = ob.parallelize(build(kind).train(), pipeline_parallel_size=2, micro_batch_size=1)
@@ -562,7 +564,7 @@ def _train_pp_zero_ddp(rank, world, kind, steps, tmpdir):
         n = b["input_ids"].size(0) // dp
         mine = {k: v[dpr * n:(dpr + 1) * n] for k, v in b.items()}
         opt.zero_grad()
-        for out in ddp(**mine):
+        for out in (model if direct else ddp)(**mine):
             (out.loss / n).backward()
         opt.step()
     model.save_pretrained_with_parallel(os.path.join(tmpdir, "merged"), save_with_merging=True)
@@ -586,6 +588,65 @@ def test_pipeline_with_bucketed_ddp_and_zero1_matches_single_process(kind):
     for k, v in ref.state_dict().items():
         if k in got:
             assert torch.allclose(got[k], v, atol=2e-4), (k, (got[k] - v).abs().max())
+
+
+def test_pipeline_with_bucketed_ddp_when_the_model_is_called_directly():
+    """PP2 x DP2 with two micro-batches per replica, driving ``model(...)`` and not the wrapper: the bucket reductions
+    must still start during the LAST micro-batch's backward only (started during the first one, the later
+    micro-batches' gradients would never be reduced)."""
+    kind, steps = "gptj", 3
+    torch.manual_seed(0)
+    ref = build(kind).train()
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.01)
+    for s in range(steps):
+        opt.zero_grad()
+        ref(**batch(seed=3 + s)).loss.backward()
+        opt.step()
+    with tempfile.TemporaryDirectory() as d:
+        run_distributed(_train_pp_zero_ddp, 4, kind, steps, d, True)
+        got = torch.load(os.path.join(d, "merged", "pytorch_model.bin"), weights_only=True)
+    for k, v in ref.state_dict().items():
+        if k in got:
+            assert torch.allclose(got[k], v, atol=2e-4), (k, (got[k] - v).abs().max())
+
+
+def _train_ddp_unsharded(rank, world, steps, tmpdir, clip):
+    from oslo_b200.optim import FusedAdamW
+    from oslo_b200.parallel.data_parallel import DistributedDataParallel
+    model = ob.parallelize(build("gptj").train(), tensor_parallel_size=1)
+    mpu = model.mpu
+    opt = FusedAdamW(model.gpu_parameters(), lr=1e-2, weight_decay=0.01, max_grad_norm=clip)   # no shard_group
+    ddp = DistributedDataParallel(model, mpu, optimizer=opt, bucket_mb=0.01)
+    for s in range(steps):
+        b = batch(seed=3 + s, bsz=4 * world)
+        n = b["input_ids"].size(0) // world
+        opt.zero_grad()
+        ddp(**{k: v[rank * n:(rank + 1) * n] for k, v in b.items()}).loss.backward()
+        opt.step()
+    if rank == 0:
+        torch.save({k: v.detach().clone() for k, v in model.state_dict().items()}, os.path.join(tmpdir, "state.pt"))
+
+
+def test_bucketed_ddp_with_unsharded_fused_adamw_averages_and_clips_like_one_process():
+    """Plain data parallelism (no ZeRO-1): the summed buckets become the mean inside the optimizer, so a clipping
+    threshold that bites sees the same norm as a single process on the whole batch."""
+    steps, world, clip = 3, 2, 1.0
+    torch.manual_seed(0)
+    ref = build("gptj").train()
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.01)
+    norms = []
+    for s in range(steps):
+        opt.zero_grad()
+        ref(**batch(seed=3 + s, bsz=4 * world)).loss.backward()
+        norms.append(float(torch.nn.utils.clip_grad_norm_(ref.parameters(), clip)))
+        opt.step()
+    # a gradient left as the SUM over two replicas has twice the norm: it would be clipped in steps where the mean is not
+    assert max(norms) > clip and any(clip / world < n < clip for n in norms), norms
+    with tempfile.TemporaryDirectory() as d:
+        run_distributed(_train_ddp_unsharded, world, steps, d, clip)
+        got = torch.load(os.path.join(d, "state.pt"), weights_only=True)
+    for k, v in ref.state_dict().items():
+        assert torch.allclose(got[k], v, atol=2e-4), (k, (got[k] - v).abs().max())
 
 
 def _scaler_ranks(rank, world):

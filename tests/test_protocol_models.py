@@ -80,3 +80,55 @@ def test_generation_tagged_words_survive_reuse_with_other_shapes():
         for i in order:
             words[i] = gen
         assert all(ready(i) for i in range(n))
+
+
+def _run_vocab_embed(world, token_counts, max_blocks, fixed_grid, delays):
+    """Model of ``vocab_embed_kernel``: the owner of a token (``t % world`` here) writes the token's row into EVERY
+    rank's staging half, the ranks meet once, every rank copies its rows out. Each block keeps its own half parity;
+    ``fixed_grid`` says whether the launcher always starts ``max_blocks`` blocks (the real launcher) or only as many
+    as there are tokens (the defect this model documents). Returns the violations."""
+    tmax = max(token_counts)
+    stage = [[[None] * tmax for _ in range(2)] for _ in range(world)]     # [rank][half][token offset]
+    barrier = threading.Barrier(world)
+    bad = []
+
+    def rank_fn(r):
+        rnd = random.Random(2000 + r)
+        counters = [0] * max_blocks
+        for call, tokens in enumerate(token_counts):
+            grid = max_blocks if fixed_grid else min(tokens, max_blocks)
+            per = -(-tokens // grid)
+            blocks = [(b, range(b * per, min(tokens, (b + 1) * per))) for b in range(grid)]
+            time.sleep(delays(r, call, "before_write", rnd))
+            for b, toks in blocks:
+                h = counters[b] & 1
+                for t in toks:
+                    if t % world == r:
+                        for peer in range(world):
+                            stage[peer][h][t] = (call, t)
+            barrier.wait()                                  # stands for the per-block cross-rank barriers
+            time.sleep(delays(r, call, "before_read", rnd))
+            for b, toks in blocks:
+                h = counters[b] & 1
+                for t in toks:
+                    if stage[r][h][t] != (call, t):
+                        bad.append((r, call, t, stage[r][h][t]))
+                counters[b] += 1
+
+    threads = [threading.Thread(target=rank_fn, args=(r,)) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(60)
+    return bad
+
+
+def test_vocab_embed_halves_stay_in_lockstep_for_any_token_counts():
+    """Prefill, a run of decode steps (1 token: fewer tokens than blocks), then two larger calls of different sizes:
+    with the fixed grid no rank ever reads a row of another call; with a grid that follows the token count the
+    per-block parities drift apart and a fast owner overwrites rows that a slow rank has not copied out yet."""
+    counts = [64, 1, 1, 1, 48, 24, 64, 3, 40, 20]
+    for world in (2, 4):
+        assert _run_vocab_embed(world, counts, 8, True, _slow_reader) == []
+        assert _run_vocab_embed(world, counts * 2, 8, True, _jitter) == []
+    assert _run_vocab_embed(2, counts, 8, False, _slow_reader), "the model failed to expose the drifting parities"
