@@ -6,6 +6,11 @@ JSON line on rank 0. Weak scaling: every GPU works on ``--batch-per-gpu`` sequen
 per step, so the global batch is ``8 N x 2048`` by default (64 x 2048 on 8 GPUs). Synthetic data: token
 ids uniform in [0, vocab) with a fixed seed; weights random-init.
 
+Without ``--tp`` / ``--pp`` the headline follows the model-parallel sweep: one GPU, ``tp2`` on 2 GPUs, ``tp4`` on
+4, ``tp2 x pp4`` (16 micro-batches of 4 sequences, 1F1B) on 8; the other named configurations of that GPU count
+(ZeRO-1 data parallelism over all GPUs; on 8 GPUs also ``tp8`` with a global batch of 8 x 2048) are measured in
+the same invocation and reported under ``"also"``. ``--tp`` / ``--pp`` time exactly one layout.
+
 Timed regions (CUDA events on the compute stream, barrier + synchronize on both sides, max over ranks):
   * ``value``: K full steps (forward, backward, gradient reduction, optimizer) with inputs already on
     the device;
@@ -48,7 +53,10 @@ def parse_args():
     ap.add_argument("--batch-per-gpu", type=int, default=8)
     ap.add_argument("--micro-batch", type=int, default=None, help="sequences per forward/backward (default: auto)")
     ap.add_argument("--tp", type=int, default=None)
-    ap.add_argument("--pp", type=int, default=1)
+    ap.add_argument("--pp", type=int, default=None)
+    ap.add_argument("--no-also", action="store_true", help="time the headline configuration only")
+    ap.add_argument("--also-timeout", type=float, default=600.0,
+                    help="seconds the extra configurations may take before the headline is printed without them")
     ap.add_argument("--checkpoint-activations", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--mode", default="train", choices=["train", "decode"],
@@ -112,14 +120,37 @@ class ClockSampler(threading.Thread):
 def reference_arm(args) -> None:
     """Run the unmodified reference through its own public API, or say why it cannot run here."""
     from baseline import reference_runner
+    if args.mode == "train" and args.tp is None and args.pp is None:
+        # the same sweep as this framework's arm: single, tp2, tp4, tp2 x pp4 (16 micro-batches of 4 sequences)
+        spec, _ = default_plan(args.gpus)
+        args.tp, args.pp = spec["tp"], spec["pp"]
+        if spec.get("micro") and spec["pp"] > 1:
+            args.micro_batch = args.micro_batch or spec["micro"]
     reference_runner.main(args, ClockSampler)
 
 
-def main() -> None:
-    args = parse_args()
-    if args.impl == "reference":
-        reference_arm(args)
-        return
+def default_plan(world: int):
+    """Configurations timed by ``bench.py --gpus N`` with no parallelism flag: the GPT-J-6B sweep (one GPU, tensor
+    parallel on 2 and 4, tensor x pipeline parallel on 8, 8 sequences of 2048 tokens per GPU per step) as the
+    headline, and the other named 6B configurations of the same GPU count as extra blocks of the same line."""
+    dp_block = dict(name=f"dp{world}_zero1", tp=1, pp=1)
+    if world == 1:
+        return dict(name="single", tp=1, pp=1), []
+    if world == 2:
+        return dict(name="tp2", tp=2, pp=1), [dp_block]
+    if world == 4:
+        return dict(name="tp4", tp=4, pp=1), [dp_block]
+    if world == 8:
+        # global batch 64 x 2048 as 16 micro-batches of 4 sequences through 4 stages of 7 layers, each stage on 2 GPUs
+        return (dict(name="tp2xpp4", tp=2, pp=4, micro=4),
+                [dict(name="tp8_b8x2048", tp=8, pp=1, replica_batch=8, micro=8), dp_block])
+    return dp_block, []
+
+
+def run_train_config(args, spec, dims, world, rank, local, dev):
+    """Build GPT-J with the parallel layout ``spec``, time ``--steps`` steps twice (device inputs; end to end through
+    pinned host memory), free everything again. Returns the result block (same keys on every rank)."""
+    import gc
 
     import torch
     import torch.distributed as dist
@@ -128,34 +159,16 @@ def main() -> None:
     from oslo_b200.optim import FusedAdamW
     from oslo_b200.parallel.data_parallel import DistributedDataParallel
 
-    os.environ.setdefault("RANK", "0")
-    os.environ.setdefault("WORLD_SIZE", "1")
-    os.environ.setdefault("LOCAL_RANK", os.environ["RANK"])
-    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    os.environ.setdefault("MASTER_PORT", "29531")
-    world = int(os.environ["WORLD_SIZE"])
-    rank = int(os.environ["RANK"])
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run --nproc-per-node {args.gpus}")
-    local = int(os.environ["LOCAL_RANK"])
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-
-    n_layer, n_embd, n_head, rotary, vocab, n_pos = MODELS[args.model]
-    if args.layers is not None:
-        n_layer = args.layers
-    if args.mode == "decode":
-        decode_main(args, world, rank, local, dev, (n_layer, n_embd, n_head, rotary, vocab, n_pos))
-        return
-    tp = args.tp or 1
-    pp = args.pp
+    n_layer, n_embd, n_head, rotary, vocab, n_pos = dims
+    tp, pp = spec["tp"], spec["pp"]
     dp = world // (tp * pp)
     cfg = ob.GPTJConfig(vocab_size=vocab, n_positions=n_pos, n_embd=n_embd, n_layer=n_layer, n_head=n_head,
                         rotary_dim=rotary, torch_dtype=torch.bfloat16, use_cache=False)
-    seqs_per_rank = args.batch_per_gpu * tp * pp          # sequences one model replica handles per step
-    # 4 sequences per forward/backward per GPU keeps activations within memory; model-parallel replicas
-    # spread a micro-batch over tp*pp GPUs, so they take proportionally more (fewer, larger launches)
-    micro = args.micro_batch or (4 * tp if args.model == "gptj-6b" else seqs_per_rank)
+    # sequences one model replica handles per step: weak scaling keeps 8 per GPU unless the configuration names a batch
+    seqs_per_rank = spec.get("replica_batch") or args.batch_per_gpu * tp * pp
+    # 4 sequences per forward/backward per GPU keeps activations within memory; tensor-parallel replicas spread a
+    # micro-batch over tp GPUs, so they take proportionally more (fewer, larger launches)
+    micro = spec.get("micro") or args.micro_batch or (4 * tp if args.model == "gptj-6b" else seqs_per_rank)
     micro = min(micro, seqs_per_rank)
     accum = seqs_per_rank // micro
 
@@ -171,6 +184,7 @@ def main() -> None:
                      shard_group=mpu.get_data_parallel_group() if dp > 1 else None,
                      model_parallel_group=mpu.get_model_parallel_group() if tp * pp > 1 else None)
     engine = DistributedDataParallel(model, mpu, optimizer=opt) if dp > 1 else None
+    call = engine if engine is not None else model
 
     gen = torch.Generator().manual_seed(1000 + mpu.get_data_parallel_rank())
     n_host = 4
@@ -182,7 +196,7 @@ def main() -> None:
         opt.zero_grad()
         total = None
         if pp > 1:
-            for out in (engine if engine is not None else model)(input_ids=ids, labels=ids, output_logits=False):
+            for out in call(input_ids=ids, labels=ids, output_logits=False):
                 (out.loss / accum).backward()
                 total = out.loss.detach() if total is None else total + out.loss.detach()
         else:
@@ -190,7 +204,7 @@ def main() -> None:
                 mb = ids[i * micro:(i + 1) * micro]
                 hold = engine.no_sync() if (engine is not None and i < accum - 1) else contextlib.nullcontext()
                 with hold:  # gradients are reduced over the data-parallel group during the last backward only
-                    loss = model(input_ids=mb, labels=mb, output_logits=False).loss
+                    loss = call(input_ids=mb, labels=mb, output_logits=False).loss
                     (loss / accum).backward()
                 total = loss.detach() if total is None else total + loss.detach()
         opt.step()
@@ -225,29 +239,147 @@ def main() -> None:
         train_step(dev_inputs[0])
     ms_step, clocks, launches, last = timed(args.steps, e2e=False)
     tokens_step = dp * seqs_per_rank * args.seq
-    value = tokens_step / (ms_step / 1e3)
     e2e = None
     if not args.no_e2e:
         ms_e2e, _, _, loss_host = timed(args.steps, e2e=True)
         e2e = {"value": tokens_step / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                "h2d_bytes_per_step": seqs_per_rank * args.seq * 8, "d2h_bytes_per_step": 4, "last_loss": loss_host}
-    err = int(ext.error_word(dev_inputs[0]).item())
-    mem_gb = torch.cuda.max_memory_allocated() / 2 ** 30
-    if rank == 0:
-        par = "x".join(f"{k}{v}" for k, v in (("tp", tp), ("pp", pp), ("dp", dp)) if v > 1) or "single"
+    pipe = None
+    if pp > 1:
+        # one more step with CUDA events around every forward / backward of every stage: how much of the step a stage
+        # sits idle, against the 1F1B ideal (P - 1) / (m + P - 1)
+        eng = model._pipe_engine
+        eng.profile = True
+        train_step(dev_inputs[0])
+        torch.cuda.synchronize()
+        rep = eng.schedule_report()
+        eng.profile = False
+        reps = [None] * world
+        dist.all_gather_object(reps, rep)
+        by_stage = {}
+        for r in reps:
+            by_stage.setdefault(r["stage"], []).append(r)
+        pipe = {"stages": pp, "micro_batches": accum, "ideal_idle_share": round((pp - 1) / (accum + pp - 1), 4),
+                "busy_ms_per_stage": [round(max(x["busy_ms"] for x in by_stage[s]), 1) for s in sorted(by_stage)],
+                "idle_share_of_step": [round(1.0 - max(x["busy_ms"] for x in by_stage[s]) / ms_step, 4)
+                                       for s in sorted(by_stage)]}
+    err = torch.tensor([int(ext.error_word(dev_inputs[0]).item())], device=dev)
+    dist.all_reduce(err, op=dist.ReduceOp.MAX)
+    mem = torch.tensor([torch.cuda.max_memory_allocated() / 2 ** 30], device=dev)
+    dist.all_reduce(mem, op=dist.ReduceOp.MAX)
+    par = "x".join(f"{k}{v}" for k, v in (("tp", tp), ("pp", pp), ("dp", dp)) if v > 1) or "single"
+    from oslo_b200.config import get_config
+    block = {
+        "value": tokens_step / (ms_step / 1e3), "unit": "tokens/s", "ms_per_step": ms_step,
+        "config": {"model": args.model, "global_batch": dp * seqs_per_rank, "seq_len": args.seq,
+                   "parallelism": par + ("+zero1" if dp > 1 else ""), "micro_batch": micro, "grad_accum": accum,
+                   "optimizer": "AdamW fp32 master (fused)", "activation_checkpointing": bool(args.checkpoint_activations),
+                   "fused_tp_collectives": bool(get_config().fused_tp_comm) if tp > 1 else None,
+                   "pipeline": pipe,
+                   "l2": "working set per step >> 126 MB L2, no explicit flush"},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "device_error_word": int(err.item()),
+        "peak_mem_gb": round(float(mem.item()), 1),
+    }
+    # free the model, the optimizer state and the symmetric workspaces before the next configuration is built
+    del model, opt, engine, call, dev_inputs, host, train_step, timed
+    from oslo_b200.parallel import fused_tp, symmetric
+    fused_tp._CONTEXTS.clear()
+    symmetric._WORKSPACES.clear()
+    gc.collect()
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    torch.cuda.reset_peak_memory_stats()
+    dist.barrier()
+    return block
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import oslo_b200 as ob  # noqa: F401
+    from oslo_b200.parallel.mpu import MPU
+
+    os.environ.setdefault("RANK", "0")
+    os.environ.setdefault("WORLD_SIZE", "1")
+    os.environ.setdefault("LOCAL_RANK", os.environ["RANK"])
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29531")
+    world = int(os.environ["WORLD_SIZE"])
+    rank = int(os.environ["RANK"])
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+
+    n_layer, n_embd, n_head, rotary, vocab, n_pos = MODELS[args.model]
+    if args.layers is not None:
+        n_layer = args.layers
+    dims = (n_layer, n_embd, n_head, rotary, vocab, n_pos)
+    if args.mode == "decode":
+        decode_main(args, world, rank, local, dev, dims)
+        return
+    if args.tp is None and args.pp is None:
+        primary, extra = default_plan(world)
+        if args.no_also:
+            extra = []
+    else:
+        tp, pp = args.tp or 1, args.pp or 1
+        primary, extra = dict(name="custom", tp=tp, pp=pp), []
+    MPU.initialize_distributed("nccl")
+
+    def emit(block, also):
+        full = args.model == "gptj-6b" and args.layers is None
         line = {
-            "metric": "GPT-J-6B train tokens/sec" if (args.model == "gptj-6b" and args.layers is None) else f"{args.model} train tokens/sec (debug)",
-            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "metric": "GPT-J-6B train tokens/sec" if full else f"{args.model} train tokens/sec (debug)",
+            "value": block["value"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": block["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights", "impl": "oslo_b200",
-            "config": {"model": args.model, "global_batch": dp * seqs_per_rank, "seq_len": args.seq,
-                       "parallelism": par + ("+zero1" if dp > 1 else ""), "micro_batch": micro, "grad_accum": accum,
-                       "optimizer": "AdamW fp32 master (fused)", "activation_checkpointing": bool(args.checkpoint_activations),
-                       "l2": "working set per step >> 126 MB L2, no explicit flush"},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "device_error_word": err,
-            "peak_mem_gb": round(mem_gb, 1),
+            "config": block["config"], "clocks": block["clocks"], "e2e": block["e2e"],
+            "gpu_launches": block["gpu_launches"], "device_error_word": block["device_error_word"],
+            "peak_mem_gb": block["peak_mem_gb"],
         }
+        if also:
+            line["also"] = also
         print(json.dumps(line), flush=True)
+
+    block = run_train_config(args, primary, dims, world, rank, local, dev)
+    also = {}
+    printed = threading.Event()
+
+    def give_up():
+        # an extra block that does not finish must not take the headline with it
+        if printed.is_set():
+            return
+        printed.set()
+        if rank == 0:
+            emit(block, dict(also, error=f"extra configurations not finished within {args.also_timeout} s"))
+        sys.stdout.flush()
+        os._exit(0)
+
+    guard = threading.Timer(args.also_timeout, give_up) if extra else None
+    if guard is not None:
+        guard.daemon = True
+        guard.start()
+    for spec in extra:
+        try:
+            b = run_train_config(args, spec, dims, world, rank, local, dev)
+            also[spec["name"]] = {k: b[k] for k in ("value", "unit", "ms_per_step", "e2e", "config", "gpu_launches",
+                                                    "device_error_word", "peak_mem_gb")}
+        except Exception as e:  # noqa: BLE001 - keep the headline; every rank sees shape / memory errors alike
+            also[spec["name"]] = {"error": f"{type(e).__name__}: {e}"[:300]}
+            break
+    if guard is not None:
+        guard.cancel()
+    if rank == 0 and not printed.is_set():
+        printed.set()
+        emit(block, also)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -3,7 +3,14 @@
 Public surface mirrors the reference package (oslo/__init__.py:3-17): models, configs, data
 classes, the parallel layers and ``oslo_b200.parallelize``.
 """
-from .__version__ import version as __version__  # noqa: F401
+import os as _os
+
+# A pipeline stage keeps receives posted on their own streams while it computes. With more streams than hardware work
+# queues (8 by default) two streams can share a queue, and a receive that waits for its sender would then hold up
+# the very computation the sender is waiting for. The variable is read when the CUDA context is created.
+_os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+
+from .__version__ import version as __version__  # noqa: F401,E402
 from .modeling_utils import *  # noqa: F401,F403
 from .modeling_utils import PreTrainedModel, PretrainedConfig, ModelOutput  # noqa: F401
 from .parallel.mpu import MPU, Layer, LayerPolicy  # noqa: F401

@@ -33,6 +33,8 @@ class OsloConfig:
     tp_shared_reduction_sp: bool = False # sequence parallel: partial sums ride in the fused GEMM + reduce-scatter kernel (not yet run on GPUs)
     block_fusion: bool = True            # GPT-J block: q/k/v as one autograd node, residual additions inside GEMM epilogues
     ddp_bucket_mb: int = 256
+    dp_symmetric: bool = True            # data parallel: flat gradient / parameter buffers in symmetric memory, reduce-scatter and all-gather by this package's kernels (off: NCCL)
+    dp_overlap_param_gather: bool = True # ZeRO-1: refreshed parameters travel bucket by bucket on a side stream, each forward unit waits for its own buckets
     pg_timeout_s: float = 1800.0         # process-group timeout (collectives fail instead of hanging)
     heartbeat_s: float = 5.0             # watchdog heartbeat period
     heartbeat_misses: int = 6            # missed heartbeats before a rank is declared dead

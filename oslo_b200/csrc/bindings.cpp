@@ -502,6 +502,27 @@ void allreduce_symm(int64_t peer_ptrs_dev, int64_t mc_ptr, int64_t signal_ptrs_d
                                st.err.data_ptr<int>(), cur_stream()), "allreduce_symm");
 }
 
+// One bucket of the data-parallel gradient reduce-scatter / parameter all-gather on a symmetric flat buffer.
+// `like` names the device and (reduce-scatter) the 16-bit dtype; the buffer itself is given by its address tables.
+void dp_reduce_scatter(const Tensor& like, int64_t peer_ptrs_dev, int64_t mc_ptr, int64_t signal_ptrs_dev, int64_t lo,
+                       int64_t hi, int64_t shard, int64_t rank, int64_t world, bool use_multimem) {
+  c10::cuda::CUDAGuard guard(like.device());
+  auto& st = dev_state(like.get_device());
+  check_rc(oslo_dp_reduce_scatter(reinterpret_cast<void* const*>(peer_ptrs_dev), reinterpret_cast<void*>(mc_ptr),
+                                  reinterpret_cast<uint32_t* const*>(signal_ptrs_dev), lo, hi, shard,
+                                  static_cast<int>(rank), static_cast<int>(world), dt_code(like), use_multimem ? 1 : 0,
+                                  st.err.data_ptr<int>(), cur_stream()), "dp_reduce_scatter");
+}
+void dp_all_gather(const Tensor& like, int64_t peer_ptrs_dev, int64_t mc_ptr, int64_t signal_ptrs_dev, int64_t lo,
+                   int64_t hi, int64_t shard, int64_t rank, int64_t world, bool use_multimem) {
+  c10::cuda::CUDAGuard guard(like.device());
+  auto& st = dev_state(like.get_device());
+  check_rc(oslo_dp_all_gather(reinterpret_cast<void* const*>(peer_ptrs_dev), reinterpret_cast<void*>(mc_ptr),
+                              reinterpret_cast<uint32_t* const*>(signal_ptrs_dev), lo, hi, shard, static_cast<int>(rank),
+                              static_cast<int>(world), use_multimem ? 1 : 0, st.err.data_ptr<int>(), cur_stream()),
+           "dp_all_gather");
+}
+
 // y [M, N] = act([x1 | x2] @ w^T + bias) for M <= 4 rows; w [N, K1 + K2]; x1 / x2 are 2-D with contiguous last dims
 Tensor gemv_rows(const Tensor& x1, const optional<Tensor>& x2, const Tensor& w, const optional<Tensor>& bias,
                  int64_t gelu_from, const optional<Tensor>& res) {
@@ -630,6 +651,8 @@ TORCH_LIBRARY(oslo_b200, m) {
   m.def("vocab_embed(Tensor ids, Tensor weight, int lo, int hi, int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(a!) counters, int half_bytes, int rank, int world, bool use_multimem) -> Tensor");
   m.def("wait_probe(Tensor flag, int target, float limit_ms) -> Tensor");
   m.def("allreduce_oneshot(Tensor(a!) x, int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(b!) counters, int stage_off, int half_bytes, int rank, int world, bool use_multimem) -> ()");
+  m.def("dp_reduce_scatter(Tensor like, int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, int lo, int hi, int shard, int rank, int world, bool use_multimem) -> ()");
+  m.def("dp_all_gather(Tensor like, int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, int lo, int hi, int shard, int rank, int world, bool use_multimem) -> ()");
   m.def("allreduce_symm(int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(a!) out, int numel, int rank, int world, bool use_multimem) -> ()");
 }
 
@@ -663,4 +686,6 @@ TORCH_LIBRARY_IMPL(oslo_b200, CUDA, m) {
   m.impl("wait_probe", &wait_probe);
   m.impl("allreduce_oneshot", &allreduce_oneshot);
   m.impl("allreduce_symm", &allreduce_symm);
+  m.impl("dp_reduce_scatter", &dp_reduce_scatter);
+  m.impl("dp_all_gather", &dp_all_gather);
 }

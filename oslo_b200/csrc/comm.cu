@@ -238,7 +238,169 @@ __global__ void __launch_bounds__(512) vocab_embed_kernel(const long long* __res
   if (threadIdx.x == 0) counters[blockIdx.x] += 1;
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Data-parallel gradient reduce-scatter and parameter all-gather, in place on SYMMETRIC flat buffers (ZeRO-1).
+//
+// The flat gradient buffer and the flat parameter buffer of a data-parallel replica live in symmetric memory (same
+// layout on every rank, peer-mapped, plus the NVSwitch multicast mapping). Rank r owns vectors
+// [r * shard16, (r + 1) * shard16) of either buffer. Both kernels work on one bucket [lo16, hi16) of the buffer:
+//
+//   reduce-scatter: all ranks meet (everybody's bucket is complete), then every rank pulls the SUM of the part of the
+//     bucket that lies in ITS shard - multimem.ld_reduce (the switch adds the ranks' copies, fp32 accumulation) or
+//     plain peer loads added in fp32 - and stores it into its own gradient buffer. Half the bytes of an all-reduce:
+//     nothing is broadcast back, because only the owner updates those parameters. A trailing meeting keeps every
+//     rank from touching the bucket again (zeroing it for the next step) while an owner still reads it.
+//   all-gather: all ranks meet (nobody still reads the old parameters), every rank stores the part of the bucket that
+//     lies in its shard - the parameters its optimizer step just wrote - into every rank's buffer (multimem.st, or
+//     one plain store per peer), and a second meeting makes the kernel's completion mean "every rank's part of this
+//     bucket has landed here".
+//
+// Every rank launches the same grid for a bucket (it depends on the bucket's size only).
+template <bool FP16>
+__device__ __forceinline__ void accumulate8(float (&acc)[8], const uint4& v) {
+  const uint32_t* pv = &v.x;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t;
+    if (FP16) t = __half22float2(*reinterpret_cast<const __half2*>(pv + i));
+    else t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pv + i));
+    acc[2 * i] += t.x;
+    acc[2 * i + 1] += t.y;
+  }
+}
+template <bool FP16>
+__device__ __forceinline__ uint4 pack8(const float (&acc)[8]) {
+  uint4 r;
+  uint32_t* pr = &r.x;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (FP16) {
+      __half2 h = __floats2half2_rn(acc[2 * i], acc[2 * i + 1]);
+      pr[i] = *reinterpret_cast<uint32_t*>(&h);
+    } else {
+      __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+      pr[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+  }
+  return r;
+}
+
+constexpr int DP_UNROLL = 8;   // 16-byte requests in flight per thread
+
+template <bool FP16>
+__global__ void __launch_bounds__(512) dp_reduce_scatter_kernel(void* const* peer_ptrs, void* mc_ptr,
+                                                                uint32_t* const* signal_ptrs, long long lo16,
+                                                                long long hi16, long long shard16, int rank, int world,
+                                                                int use_multimem, int* err) {
+  if (!block_barrier_all_ranks(signal_ptrs, rank, world, 0, err)) return;
+  const long long a = max(lo16, shard16 * rank), b = min(hi16, shard16 * (rank + 1));
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  uint4* own = reinterpret_cast<uint4*>(peer_ptrs[rank]);
+  if (use_multimem) {
+    const uint4* mc = reinterpret_cast<const uint4*>(mc_ptr);
+    for (long long i0 = a + tid; i0 < b; i0 += nthreads * DP_UNROLL) {
+      uint4 v[DP_UNROLL];
+#pragma unroll
+      for (int j = 0; j < DP_UNROLL; ++j) {
+        const long long i = i0 + j * nthreads;
+        if (i < b) v[j] = multimem_ld_reduce<FP16>(mc + i);
+      }
+#pragma unroll
+      for (int j = 0; j < DP_UNROLL; ++j) {
+        const long long i = i0 + j * nthreads;
+        if (i < b) own[i] = v[j];
+      }
+    }
+  } else {
+    for (long long i = a + tid; i < b; i += nthreads) {
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      for (int r = 0; r < world; ++r) {
+        const int peer = (rank + r) % world;
+        accumulate8<FP16>(acc, reinterpret_cast<const uint4*>(peer_ptrs[peer])[i]);
+      }
+      own[i] = pack8<FP16>(acc);
+    }
+  }
+  block_barrier_all_ranks(signal_ptrs, rank, world, gridDim.x * world, err);
+}
+
+__global__ void __launch_bounds__(512) dp_all_gather_kernel(void* const* peer_ptrs, void* mc_ptr,
+                                                            uint32_t* const* signal_ptrs, long long lo16, long long hi16,
+                                                            long long shard16, int rank, int world, int use_multimem,
+                                                            int* err) {
+  if (!block_barrier_all_ranks(signal_ptrs, rank, world, 0, err)) return;
+  const long long a = max(lo16, shard16 * rank), b = min(hi16, shard16 * (rank + 1));
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  const uint4* own = reinterpret_cast<const uint4*>(peer_ptrs[rank]);
+  for (long long i0 = a + tid; i0 < b; i0 += nthreads * DP_UNROLL) {
+    uint4 v[DP_UNROLL];
+#pragma unroll
+    for (int j = 0; j < DP_UNROLL; ++j) {
+      const long long i = i0 + j * nthreads;
+      if (i < b) v[j] = own[i];
+    }
+#pragma unroll
+    for (int j = 0; j < DP_UNROLL; ++j) {
+      const long long i = i0 + j * nthreads;
+      if (i < b) {
+        if (use_multimem) {
+          multimem_st(reinterpret_cast<uint4*>(mc_ptr) + i, v[j]);
+        } else {
+          for (int r = 1; r < world; ++r) reinterpret_cast<uint4*>(peer_ptrs[(rank + r) % world])[i] = v[j];
+        }
+      }
+    }
+  }
+  block_barrier_all_ranks(signal_ptrs, rank, world, gridDim.x * world, err);
+}
+
 }  // namespace oslo
+
+// Bucket [lo, hi) (element indices, multiples of 8) of a symmetric flat buffer of 16-bit elements whose rank r owns
+// elements [r * shard, (r + 1) * shard). reduce_scatter: every rank's own part of the bucket becomes the sum over all
+// ranks (in place, in its own buffer); all_gather: every rank's own part is copied into all ranks' buffers.
+static int dp_grid(long long n16, int world) {
+  int max_blocks = 2048 / 4 / (2 * world);   // two meetings x blocks x world signal words within the 2 KiB signal pad
+  if (max_blocks > 64) max_blocks = 64;
+  long long want = (n16 + 512LL * oslo::DP_UNROLL - 1) / (512LL * oslo::DP_UNROLL);
+  return static_cast<int>(want < 1 ? 1 : (want > max_blocks ? max_blocks : want));
+}
+extern "C" int oslo_dp_reduce_scatter(void* const* peer_ptrs_dev, void* mc_ptr, uint32_t* const* signal_ptrs_dev,
+                                      long long lo, long long hi, long long shard, int rank, int world, int dtype,
+                                      int use_multimem, int* err_word, cudaStream_t stream) {
+  using namespace oslo;
+  if (hi <= lo) return 0;
+  if (lo % 8 || hi % 8 || shard % 8 || lo < 0 || shard <= 0 || rank < 0 || rank >= world) return -3;
+  if (world > 16) return -4;
+  const int blocks = dp_grid((hi - lo) / 8, world);
+  const int mm = (use_multimem && mc_ptr != nullptr) ? 1 : 0;
+  if (dtype == OSLO_DT_FP16)
+    dp_reduce_scatter_kernel<true><<<blocks, 512, 0, stream>>>(peer_ptrs_dev, mc_ptr, signal_ptrs_dev, lo / 8, hi / 8,
+                                                               shard / 8, rank, world, mm, err_word);
+  else if (dtype == OSLO_DT_BF16)
+    dp_reduce_scatter_kernel<false><<<blocks, 512, 0, stream>>>(peer_ptrs_dev, mc_ptr, signal_ptrs_dev, lo / 8, hi / 8,
+                                                                shard / 8, rank, world, mm, err_word);
+  else
+    return -2;
+  return static_cast<int>(cudaGetLastError());
+}
+extern "C" int oslo_dp_all_gather(void* const* peer_ptrs_dev, void* mc_ptr, uint32_t* const* signal_ptrs_dev,
+                                  long long lo, long long hi, long long shard, int rank, int world, int use_multimem,
+                                  int* err_word, cudaStream_t stream) {
+  using namespace oslo;
+  if (hi <= lo) return 0;
+  if (lo % 8 || hi % 8 || shard % 8 || lo < 0 || shard <= 0 || rank < 0 || rank >= world) return -3;
+  if (world > 16) return -4;
+  const int blocks = dp_grid((hi - lo) / 8, world);
+  const int mm = (use_multimem && mc_ptr != nullptr) ? 1 : 0;
+  dp_all_gather_kernel<<<blocks, 512, 0, stream>>>(peer_ptrs_dev, mc_ptr, signal_ptrs_dev, lo / 8, hi / 8, shard / 8, rank,
+                                                   world, mm, err_word);
+  return static_cast<int>(cudaGetLastError());
+}
 
 // one thread waits until *flag >= target or limit_ns (capped at 1 s) has passed; on expiry the error word gets
 // ERR_WAIT_PEER. waited_ns (device, optional) receives the time spent.

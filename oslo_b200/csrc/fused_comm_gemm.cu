@@ -14,8 +14,10 @@
 //   * all-gather mode: communication warps copy this rank's shard into every rank's gather buffer chunk by
 //     chunk and raise per-chunk flags; the TMA warp waits for the chunk a tile needs before loading it - from
 //     LOCAL memory, with a plain (non-multicast) TMA load. Row blocks are walked starting at the local shard.
-// Flags are epoch-counted and never reset; two workspace slots alternate so a fast rank cannot overwrite data
-// a slow rank still reads. A wait that runs out records ERR_WAIT_PEER and the kernel tears down normally.
+// Flags are epoch-counted and never reset; the caller cycles through several workspace slots so a fast rank cannot
+// overwrite data a slow rank still reads: a rank can finish call c + k only when every peer has at least started
+// call c + k, so it reaches the call that reuses a slot after every peer has issued all but the last of the calls
+// in between. A wait that runs out records ERR_WAIT_PEER and the kernel tears down normally.
 #include <cstdlib>
 
 #include "gemm_core.cuh"

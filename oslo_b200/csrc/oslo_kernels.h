@@ -136,6 +136,15 @@ int oslo_allreduce_symm(void* const* peer_ptrs_dev, void* mc_ptr, uint32_t* cons
                         long long n, int rank, int world, int dtype, int use_multimem, int* err_word,
                         cudaStream_t stream);
 
+// data-parallel reduce-scatter / all-gather of one bucket [lo, hi) (16-bit elements) of a symmetric flat buffer whose
+// rank r owns [r * shard, (r + 1) * shard); in place (comm.cu)
+int oslo_dp_reduce_scatter(void* const* peer_ptrs_dev, void* mc_ptr, uint32_t* const* signal_ptrs_dev, long long lo,
+                           long long hi, long long shard, int rank, int world, int dtype, int use_multimem,
+                           int* err_word, cudaStream_t stream);
+int oslo_dp_all_gather(void* const* peer_ptrs_dev, void* mc_ptr, uint32_t* const* signal_ptrs_dev, long long lo,
+                       long long hi, long long shard, int rank, int world, int use_multimem, int* err_word,
+                       cudaStream_t stream);
+
 // decode-step kernels (decode_sm100.cu). gemv_rows: out[m, n] = act([x1 | x2][m, :] . W[n, :] + bias[n]) for M <= 4
 // rows, W [N, K1 + K2] K-major, tanh-GeLU on columns >= gelu_from (-1 = none); x2 may be null.
 // `res` [M, N] (row stride ldr) is added after the activation; bias and res may be null.

@@ -123,7 +123,7 @@ class GPTJMLP(nn.Module):
                 act = self.fc_in(x, activation="gelu_new")
             else:
                 act = ACT2FN[self.activation](self.fc_in(x))
-            return self.fc_out(act, partial=partial)
+            return self.fc_out(act, partial=partial, residual=residual)
         if residual is not None:
             return self._forward(x, h, residual)
         return self._forward(x, h, None)
@@ -291,9 +291,11 @@ class GPTJBlock(nn.Module):
             pre = None if sp else self._tp_shared_input(x)
             if pre is not None:   # q / k / v / fc_in as one node: ONE all-reduce of the block's input gradient too
                 a_part, present, probs = self.attn(x, qkv=pre[:3], partial_only=True, **kw)
-                return self.mlp(x, h=pre[3], partial=a_part) + hidden_states, present, probs
+                return self.mlp(x, h=pre[3], partial=a_part, residual=None if sp else hidden_states), present, probs
             a_part, present, probs = self.attn(x, partial_only=True, **kw)
-            return self.mlp(x, partial=a_part) + hidden_states, present, probs
+            if sp:
+                return self.mlp(x, partial=a_part) + hidden_states, present, probs
+            return self.mlp(x, partial=a_part, residual=hidden_states), present, probs
         a, present, probs = self.attn(x, **kw)
         m = self.mlp(x)
         return a + m + hidden_states, present, probs

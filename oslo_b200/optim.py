@@ -84,7 +84,11 @@ class DynamicLossScaler:
 class FlatBuffers:
     """One flat parameter buffer + one flat gradient buffer per dtype; tensors become views."""
 
-    def __init__(self, params: Iterable[torch.nn.Parameter], pad_to: int = 1, grad_dtype: Optional[torch.dtype] = None):
+    def __init__(self, params: Iterable[torch.nn.Parameter], pad_to: int = 1, grad_dtype: Optional[torch.dtype] = None,
+                 symmetric_group=None):
+        """``symmetric_group``: keep both buffers in symmetric memory of this (data-parallel) group when the device and
+        dtypes allow it (``parallel.symmetric.symmetric_flat_usable``), so gradient reduction and parameter
+        all-gather can run as this package's kernels; collective over the group."""
         self.params: List[torch.nn.Parameter] = []
         seen = set()
         for p in params:
@@ -105,8 +109,18 @@ class FlatBuffers:
             n += (p.numel() + 7) // 8 * 8  # keep every tensor 16-byte aligned for vector / TMA access
         self.numel = n
         self.padded = (n + pad_to - 1) // pad_to * pad_to
-        self.flat_p = torch.zeros(self.padded, dtype=self.dtype, device=self.device)
-        self.flat_g = torch.zeros(self.padded, dtype=grad_dtype or self.dtype, device=self.device)
+        self.symm_p = self.symm_g = None
+        if symmetric_group is not None:
+            from .parallel.symmetric import SymmetricFlat, symmetric_flat_usable
+            if (symmetric_flat_usable(symmetric_group, self.dtype, self.device)
+                    and (grad_dtype or self.dtype) == self.dtype):
+                self.symm_p = SymmetricFlat(symmetric_group, self.padded, self.dtype, self.device)
+                self.symm_g = SymmetricFlat(symmetric_group, self.padded, self.dtype, self.device)
+        if self.symm_p is not None:
+            self.flat_p, self.flat_g = self.symm_p.tensor, self.symm_g.tensor
+        else:
+            self.flat_p = torch.zeros(self.padded, dtype=self.dtype, device=self.device)
+            self.flat_g = torch.zeros(self.padded, dtype=grad_dtype or self.dtype, device=self.device)
         for p, off in zip(self.params, self.offsets):
             view = self.flat_p[off: off + p.numel()].view(p.shape)
             view.copy_(p.data)
@@ -144,7 +158,8 @@ class FusedAdamW:
             groups = [dict(g, params=list(g["params"])) for g in params]
         else:
             groups = [dict(params=params)]
-        self.buf = FlatBuffers([p for g in groups for p in g["params"]], pad_to=8 * self.shards)
+        self.buf = FlatBuffers([p for g in groups for p in g["params"]], pad_to=8 * self.shards,
+                               symmetric_group=shard_group if self.shards > 1 else grad_average_group)
         n = self.buf.padded // self.shards
         self.shard_numel = n
         lo = self.shard_rank * n
@@ -155,6 +170,7 @@ class FusedAdamW:
         self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
         self.step_count = 0
         self.grads_already_reduced = False  # set by DistributedDataParallel, which all-reduces buckets itself
+        self.param_gather = None            # set by DistributedDataParallel: how the refreshed parameters are spread
         # sequence parallelism: LayerNorm weights and row-parallel biases act on a token shard, so their
         # gradients must be summed over the tensor-parallel group before the update
         self._sp_params = list(getattr(model, "_sp_partial_params", []) or []) if model is not None else []
@@ -238,6 +254,10 @@ class FusedAdamW:
         if self.shards > 1 and self.grads_already_reduced:
             g = g_full[self._lo: self._hi]
             grad_scale = 1.0 / self.shards
+        elif self.shards > 1 and self.buf.symm_g is not None:
+            self.buf.symm_g.reduce_scatter_(0, self.buf.padded)      # in place: this rank's shard becomes the sum
+            g = g_full[self._lo: self._hi]
+            grad_scale = 1.0 / self.shards
         elif self.shards > 1:
             g = torch.empty(self.shard_numel, dtype=g_full.dtype, device=g_full.device)
             if dist.get_backend(self.shard_group) == "gloo":
@@ -286,7 +306,12 @@ class FusedAdamW:
                                         group["weight_decay"], scale, lp_)
         if use_kernel and lp.dtype == torch.float32:
             lp.copy_(self.master)
-        if self.shards > 1:
+        if self.shards > 1 and self.buf.symm_p is not None:
+            if self.param_gather is not None:
+                self.param_gather()          # the data-parallel wrapper: bucket by bucket, overlapped with the forward
+            else:
+                self.buf.symm_p.all_gather_(0, self.buf.padded)
+        elif self.shards > 1:
             if dist.get_backend(self.shard_group) == "gloo":
                 parts = [torch.empty_like(lp) for _ in range(self.shards)]
                 dist.all_gather(parts, lp.contiguous(), group=self.shard_group)

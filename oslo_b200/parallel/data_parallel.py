@@ -23,8 +23,26 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
+from ..config import get_config
 from ..optim import FlatBuffers, FusedAdamW
 from .mpu import MPU
+
+
+def forward_units(root: nn.Module) -> List[nn.Module]:
+    """The modules of ``root`` whose calls, in forward order, touch every parameter exactly at unit granularity: the
+    items of ``nn.ModuleList`` containers (transformer blocks, pipeline-stage items) and, outside of them, every
+    module that owns parameters directly (embeddings, the final norm, the head)."""
+    units: List[nn.Module] = []
+
+    def walk(m: nn.Module, in_list: bool) -> None:
+        if in_list or (m._parameters and any(p is not None for p in m._parameters.values())):
+            units.append(m)
+            return
+        for child in m.children():
+            walk(child, isinstance(m, nn.ModuleList))
+
+    walk(root, False)
+    return units
 
 
 class DistributedDataParallel(nn.Module):
@@ -37,7 +55,12 @@ class DistributedDataParallel(nn.Module):
         self.world = mpu.get_data_parallel_world_size()
         self.optimizer = optimizer
         gm = model.gpu_modules() if hasattr(model, "gpu_modules") else model
-        self.buf = optimizer.buf if optimizer is not None else FlatBuffers(gm.parameters())
+        self.buf = optimizer.buf if optimizer is not None else FlatBuffers(gm.parameters(), symmetric_group=self.group)
+        # buffers in symmetric memory: the bucket reductions are this package's reduce-scatter kernel on a side stream
+        # (followed by the all-gather kernel where every rank needs the whole sum); otherwise NCCL all-reduce
+        self._symm = self.buf.symm_g is not None and self.buf.symm_g.group is self.group
+        self._zero = (optimizer is not None and optimizer.shards > 1 and optimizer.shard_group is self.group)
+        self._side = torch.cuda.Stream() if self._symm else None
         self.sync = True
         self._pending: List = []
         self._ready: List[int] = []
@@ -61,6 +84,11 @@ class DistributedDataParallel(nn.Module):
                 self._deferred.add(id(model.get_input_embeddings().weight))
         else:
             self._pipelined = False
+        self._param_events: List = []
+        self._param_pending: set = set()
+        if (self._symm and self._zero and self.buf.symm_p is not None
+                and get_config().dp_overlap_param_gather):
+            self._install_param_gather(gm, optimizer)
         if optimizer is not None:
             optimizer.grads_already_reduced = True
             # the buckets are SUMMED over this group; the optimizer turns the sum into the mean (1 / group size), also
@@ -112,22 +140,79 @@ class DistributedDataParallel(nn.Module):
     def _launch(self, b: int) -> None:
         lo, hi, _ = self.buckets[b]
         self._ready[b] = -(10 ** 9)  # launched
+        if self._symm:
+            # the bucket is complete at this point of the compute stream; everything else happens on the side stream
+            self._side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self._side):
+                self.buf.symm_g.reduce_scatter_(lo, hi)
+                if not self._zero:
+                    self.buf.symm_g.all_gather_(lo, hi)      # every rank steps every parameter: spread the sums
+            return
         chunk = self.buf.flat_g[lo:hi]
         self._pending.append(dist.all_reduce(chunk, group=self.group, async_op=True))
 
     def finish_gradient_sync(self) -> None:
         """Wait for the bucket reductions of this step; launches any bucket that never became ready
         (parameters without gradient this step) so every rank issues the same collectives."""
+        self.finish_param_sync()     # nothing is pending after a whole forward pass; a step without one gets here
         if self.world > 1:
             for b in range(len(self.buckets)):
                 if self._ready[b] >= 0:
                     self._launch(b)
             for w in self._pending:
                 w.wait()
+            if self._symm:
+                torch.cuda.current_stream().wait_stream(self._side)
             if self.optimizer is None:
                 self.buf.flat_g.div_(self.world)
         self._pending = []
         self._ready = [0] * len(self.buckets)
+
+    # ------------------------------------------------------------------ ZeRO-1 parameter all-gather, overlapped
+    def _install_param_gather(self, gm: nn.Module, opt: FusedAdamW) -> None:
+        """After the optimizer step the refreshed parameters of every shard travel bucket by bucket, in the order in
+        which the forward pass needs them, on the side stream; every forward unit (an embedding, a transformer block,
+        the final norm, the head) makes the compute stream wait for the buckets that hold its own parameters only.
+        The first layers of the next step therefore start while the later layers' parameters are still in flight."""
+        self._param_events = [torch.cuda.Event() for _ in self.buckets]
+        units = forward_units(gm)
+        for m in units:
+            need = sorted({self._bucket_of[id(p)] for p in m.parameters() if id(p) in self._bucket_of}, reverse=True)
+            if need:
+                m.register_forward_pre_hook(self._make_unit_hook(need))
+        covered = {id(p) for m in units for p in m.parameters()}
+        if any(id(p) not in covered for p in self.buf.params):
+            raise RuntimeError("a parameter belongs to no forward unit")    # cannot happen by construction
+        gm.register_state_dict_pre_hook(lambda *a, **k: self.finish_param_sync())
+        opt.param_gather = self._gather_params
+
+    def _gather_params(self) -> None:
+        self._side.wait_stream(torch.cuda.current_stream())          # the optimizer step wrote this rank's shard
+        with torch.cuda.stream(self._side):
+            for b in range(len(self.buckets) - 1, -1, -1):           # bucket 0 holds the LAST parameters
+                lo, hi, _ = self.buckets[b]
+                self.buf.symm_p.all_gather_(lo, hi)
+                self._param_events[b].record(self._side)
+        self._param_pending = set(range(len(self.buckets)))
+
+    def _make_unit_hook(self, need: List[int]):
+        def hook(_module, _args):
+            if self._param_pending:
+                cur = torch.cuda.current_stream()
+                for b in need:
+                    if b in self._param_pending:
+                        cur.wait_event(self._param_events[b])
+                        self._param_pending.discard(b)
+        return hook
+
+    def finish_param_sync(self) -> None:
+        """Make the current stream wait for every parameter bucket that is still in flight (before anything other
+        than a forward pass reads the parameters: checkpoints, evaluation code that bypasses the modules)."""
+        if self._param_pending:
+            cur = torch.cuda.current_stream()
+            for b in sorted(self._param_pending):
+                cur.wait_event(self._param_events[b])
+            self._param_pending = set()
 
     def _wrap_optimizer_step(self, opt: FusedAdamW) -> None:
         inner = opt.step

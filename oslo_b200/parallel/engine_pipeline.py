@@ -75,34 +75,85 @@ class P2PCommunicator:
 
     The reference ships whole Python dicts element by element with a type-tagged protocol
     (oslo/parallelism/engine_pipeline.py:741-1199); here both sides derive shape and dtype
-    from their own copy of the batch, so a message is exactly one tensor.
+    from their own copy of the batch, so a message is exactly one tensor (or one batched pair).
+
+    Every (neighbour pair, direction) is its own two-rank process group, i.e. its own NCCL communicator and
+    stream: a channel is a FIFO between exactly two ranks, so a receive that was posted early and still waits for
+    its sender can never sit in front of a send to the other neighbour (on one shared communicator all
+    point-to-point kernels of a rank run in issue order, and a middle stage that pre-posts "receive activation
+    j + 1" before "send activation j" would wait for itself around the ring of 1F1B dependencies). Receives are
+    issued from a side stream, so they are ordered after nothing on the compute stream and can land while the
+    stage computes; the consumer makes the compute stream wait for exactly the message it needs.
     """
 
     def __init__(self, mpu: MPU) -> None:
         self.mpu = mpu
         ranks = mpu.get_pipeline_parallel_global_ranks()
-        self.fwd_group = self.bwd_group = None
-        # every rank creates every group (collective call), two per pipeline group
+        stage = mpu.get_pipeline_parallel_rank()
+        self._chan: Dict[tuple, Any] = {}     # (lower stage, "fwd" | "bwd") -> two-rank group
+        # every rank creates every group (collective call), in the same order
         for rs in mpu.get_pipeline_parallel_global_ranks_across_all_groups():
-            f = dist.new_group(ranks=rs, backend=mpu.backend)
-            b = dist.new_group(ranks=rs, backend=mpu.backend)
-            if rs == ranks:
-                self.fwd_group, self.bwd_group = f, b
+            for s in range(len(rs) - 1):
+                for direction in ("fwd", "bwd"):
+                    g = dist.new_group(ranks=[rs[s], rs[s + 1]], backend=mpu.backend)
+                    if rs == ranks and stage in (s, s + 1):
+                        self._chan[(s, direction)] = g
+        self.side = torch.cuda.Stream() if (mpu.backend == "nccl" and torch.cuda.is_available()) else None
 
     def _rank(self, stage: int) -> int:
         return self.mpu.stage_to_global_rank(stage)
 
+    def _post(self, ops):
+        if len(ops) == 1:
+            op = ops[0]
+            return [op.op(op.tensor, op.peer, group=op.group)]
+        return dist.batch_isend_irecv(ops)       # one NCCL group launch for the whole message
+
+    def send(self, tensors: List[Tensor], dst_stage: int, direction: str) -> List[Any]:
+        """Send ``tensors`` as one message to a neighbouring stage; returns the work handles."""
+        me = self.mpu.get_pipeline_parallel_rank()
+        g = self._chan[(min(me, dst_stage), direction)]
+        ops = [dist.P2POp(dist.isend, t.contiguous(), self._rank(dst_stage), group=g) for t in tensors]
+        return self._post(ops)
+
+    def recv(self, tensors: List[Tensor], src_stage: int, direction: str) -> List[Any]:
+        """Post the receive of one message (same tensor count and shapes as the sender's)."""
+        me = self.mpu.get_pipeline_parallel_rank()
+        g = self._chan[(min(me, src_stage), direction)]
+        ops = [dist.P2POp(dist.irecv, t, self._rank(src_stage), group=g) for t in tensors]
+        if self.side is None:
+            return self._post(ops)
+        with torch.cuda.stream(self.side):
+            return self._post(ops)
+
+    def alloc(self, shape, dtype, device) -> Tensor:
+        """Receive buffer; allocated on the side stream that the receive runs on."""
+        if self.side is None:
+            return torch.empty(shape, dtype=dtype, device=device)
+        with torch.cuda.stream(self.side):
+            return torch.empty(shape, dtype=dtype, device=device)
+
+    def finish(self, works: List[Any], tensors: List[Tensor]) -> None:
+        """Make the current (compute) stream wait for a posted receive and hand its buffers over to that stream."""
+        for w in works:
+            w.wait()
+        if self.side is not None:
+            cur = torch.cuda.current_stream()
+            for t in tensors:
+                t.record_stream(cur)
+
+    # one-tensor conveniences (kept for callers written against the earlier interface)
     def send_forward(self, t: Tensor, dst_stage: int):
-        return dist.isend(t.contiguous(), dst=self._rank(dst_stage), group=self.fwd_group)
+        return self.send([t], dst_stage, "fwd")[0]
 
     def recv_forward(self, t: Tensor, src_stage: int):
-        return dist.irecv(t, src=self._rank(src_stage), group=self.fwd_group)
+        return self.recv([t], src_stage, "fwd")[0]
 
     def send_backward(self, t: Tensor, dst_stage: int):
-        return dist.isend(t.contiguous(), dst=self._rank(dst_stage), group=self.bwd_group)
+        return self.send([t], dst_stage, "bwd")[0]
 
     def recv_backward(self, t: Tensor, src_stage: int):
-        return dist.irecv(t, src=self._rank(src_stage), group=self.bwd_group)
+        return self.recv([t], src_stage, "bwd")[0]
 
 
 class _StageModule(nn.ModuleList):
@@ -128,6 +179,8 @@ class PipelineParallelEngine:
         self.p2p: Optional[P2PCommunicator] = None
         self._grad_hooks_cb: List[Callable[[], None]] = []
         self.on_last_backward: Optional[Callable[[bool], None]] = None
+        self.profile = False                  # record CUDA events around every forward / backward (schedule_report)
+        self._events: Dict[tuple, Dict[str, Any]] = {}
 
     # ------------------------------------------------------------------ partition
     def _stage_modules(self, stage: int) -> List[nn.Module]:
@@ -254,17 +307,23 @@ class PipelineParallelEngine:
             kw["cache"].advance(kw["_seq"])   # what postblock_fn does on the last stage: this stage's layers are filled
         return kw
 
+    def _post_recv_grad(self, mb: int, shape, dtype) -> None:
+        """Post the receive of micro-batch ``mb``'s output gradient (+ loss value) from the next stage."""
+        if mb in self._grad_recv:
+            return
+        g = self.p2p.alloc(shape, dtype, self.device)
+        lossv = self.p2p.alloc((1,), torch.float32, self.device)
+        self._grad_recv[mb] = (g, lossv, self.p2p.recv([g, lossv], self.stage + 1, "bwd"))
+
     def _recv_grad(self, mb: int, shape, dtype) -> Tensor:
-        g = torch.empty(shape, dtype=dtype, device=self.device)
-        lossv = torch.empty(1, dtype=torch.float32, device=self.device)
-        w1 = self.p2p.recv_backward(g, self.stage + 1)
-        w2 = self.p2p.recv_backward(lossv, self.stage + 1)
-        w1.wait()
-        w2.wait()
+        self._post_recv_grad(mb, shape, dtype)
+        g, lossv, works = self._grad_recv.pop(mb)
+        self.p2p.finish(works, [g, lossv])
         proxy = self._proxies.pop(mb, None)
         if proxy is not None:
             proxy.data.copy_(lossv[0])
         self._loss_values[mb] = lossv
+        self._mark("B", mb, "start")
         return g
 
     def _make_input_hook(self, mb: int):
@@ -272,10 +331,39 @@ class PipelineParallelEngine:
             lossv = self._loss_values.pop(mb, None)
             if lossv is None:
                 lossv = torch.zeros(1, dtype=torch.float32, device=self.device)
-            self._pending.append(self.p2p.send_backward(grad, self.stage - 1))
-            self._pending.append(self.p2p.send_backward(lossv, self.stage - 1))
+            self._pending += self.p2p.send([grad, lossv], self.stage - 1, "bwd")
+            self._mark("B", mb, "end")
             return grad
         return hook
+
+    # ------------------------------------------------------------------ schedule timing (optional)
+    def _mark(self, kind: str, mb: int, edge: str) -> None:
+        """With ``profile = True``: CUDA events around every forward and backward of this stage."""
+        if not self.profile or not torch.cuda.is_available() or self.device.type != "cuda":
+            return
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self._events.setdefault((kind, mb), {})[edge] = ev
+
+    def schedule_report(self) -> Dict[str, float]:
+        """Busy time of this stage in the last step (sum of its forward / backward spans, device-timed), the span
+        from its first to its last event, and the idle share of that span. Call after a synchronize. The ideal
+        1F1B idle share with P stages and m micro-batches of equal cost is (P - 1) / (m + P - 1)."""
+        done = [e for e in self._events.values() if "start" in e and "end" in e]
+        spans = sum(e["start"].elapsed_time(e["end"]) for e in done)
+        total = 0.0
+        if done:
+            first, last = done[0]["start"], done[0]["end"]
+            for e in done[1:]:
+                if e["start"].elapsed_time(first) > 0:      # e started before the earliest start seen so far
+                    first = e["start"]
+                if last.elapsed_time(e["end"]) > 0:
+                    last = e["end"]
+            total = first.elapsed_time(last)
+        m = len({mb for (_k, mb) in self._events})
+        return {"busy_ms": spans, "span_ms": total, "idle_share": (1.0 - spans / total) if total > 0 else 0.0,
+                "ideal_idle_share": (self.pp - 1) / (m + self.pp - 1) if m else 0.0, "micro_batches": m,
+                "stage": self.stage}
 
     def forward(self, *args, **kwargs) -> Iterator[Any]:
         if args:
@@ -289,32 +377,38 @@ class PipelineParallelEngine:
         self._pending: List[Any] = []
         self._proxies: Dict[int, Tensor] = {}
         self._loss_values: Dict[int, Tensor] = {}
+        self._grad_recv: Dict[int, Any] = {}
+        self._events: Dict[tuple, Dict[str, Any]] = {}
         model = self.model
         dtype = model.dtype
         outputs: Dict[int, Any] = {}
         recv_buf: Dict[int, Any] = {}
+        out_shapes: Dict[int, Any] = {}
 
         def post_recv(j: int) -> None:
             if self.first or j >= m or j in recv_buf:
                 return
-            buf = torch.empty(self._hidden_shape(batches[j]), dtype=dtype, device=self.device)
-            recv_buf[j] = (buf, self.p2p.recv_forward(buf, self.stage - 1))
+            buf = self.p2p.alloc(self._hidden_shape(batches[j]), dtype, self.device)
+            recv_buf[j] = (buf, self.p2p.recv([buf], self.stage - 1, "fwd"))
 
         def do_forward(j: int) -> None:
             hidden = None
             if not self.first:
                 post_recv(j)
-                hidden, work = recv_buf.pop(j)
-                work.wait()
-                post_recv(j + 1)
+                hidden, works = recv_buf.pop(j)
+                post_recv(j + 1)                  # the next activation may arrive while this one is being used
+                self.p2p.finish(works, [hidden])
                 if train:
                     hidden.requires_grad_(True)
                     hidden.register_hook(self._make_input_hook(j))
+            self._mark("F", j, "start")
             kw = self._run_stage(batches[j], hidden)
+            self._mark("F", j, "end")
             if not self.last:
                 hs = kw["hidden_states"]
-                self._pending.append(self.p2p.send_forward(hs.detach(), self.stage + 1))
+                self._pending += self.p2p.send([hs.detach()], self.stage + 1, "fwd")
                 if train:
+                    out_shapes[j] = (hs.shape, hs.dtype)
                     proxy = MicroLossTensor.wrap(_ProxyLoss.apply(hs, self, j))
                     self._proxies[j] = proxy
                     kw["loss"] = proxy
@@ -344,12 +438,20 @@ class PipelineParallelEngine:
             do_forward(done)
             done += 1
         for i in range(m):
+            if not self.last and i in out_shapes:
+                # the gradient of micro-batch i is the next message from the stage below: post its receive before
+                # the forward that precedes backward i is enqueued, so it can land during that forward
+                self._post_recv_grad(i, *out_shapes.pop(i))
             if done < m:
                 do_forward(done)
                 done += 1
             if i == m - 1 and self.on_last_backward is not None:
                 self.on_last_backward(True)
+            if self.last:
+                self._mark("B", i, "start")
             yield outputs.pop(i)
+            if self.first:
+                self._mark("B", i, "end")         # no input hook on the first stage: backward i ends when the user returns
         self._flush()
         self._allreduce_tied_embedding()
 

@@ -9,8 +9,12 @@
 
 The autograd functions below use them for forward and backward, so one fused kernel replaces every
 ``matmul`` + NCCL all-reduce / all-gather pair of the reference's parallel layers
-(oslo/modeling_utils.py:67-104, oslo/parallelism/mpu.py:848-890). Two workspace slots alternate between
-calls (see the kernel's notes on why that makes reuse safe without a trailing barrier).
+(oslo/modeling_utils.py:67-104, oslo/parallelism/mpu.py:848-890). ``N_SLOTS`` workspace slots are used in turn
+(see the kernel's notes on why that makes reuse safe without a trailing barrier). The all-reduced matrix is handed
+out as a VIEW of its slot, not as a copy: it stays valid until ``N_SLOTS - 1`` further fused calls have been issued
+on this rank (a peer can only write into a slot again after this rank has itself reached the call before the one
+that reuses it), which covers "consume it with the next elementwise op"; anything that must live longer - a
+tensor saved for backward - has to be cloned by the caller.
 """
 from __future__ import annotations
 
@@ -26,6 +30,7 @@ from .symmetric import SymmetricWorkspace
 MODE_ALLREDUCE, MODE_REDUCE_SCATTER, MODE_ALLGATHER = 1, 2, 3
 _FLAG_RESIDUAL = 16            # GEMM epilogue flag: add the aux operand (here: another per-rank partial sum)
 _FLAG_BYTES = 4 << 20          # readiness words (one per tile, rank and warp) + the completion counter, per slot
+N_SLOTS = 4                    # workspace slots used in turn
 _CONTEXTS: Dict[str, "FusedTP"] = {}
 
 
@@ -33,11 +38,11 @@ class FusedTP:
     def __init__(self, group, workspace_mb: Optional[int] = None) -> None:
         mb = workspace_mb or get_config().symm_buffer_mb
         self.group = group
-        self.ws = SymmetricWorkspace(group, 2 * (mb * 2 ** 20 + _FLAG_BYTES))
+        self.ws = SymmetricWorkspace(group, N_SLOTS * (mb * 2 ** 20 + _FLAG_BYTES))
         self.world, self.rank = self.ws.world, self.ws.rank
         self.slot_bytes = mb * 2 ** 20
-        self.epochs = [0, 0]
-        self.done_totals = [0, 0]
+        self.epochs = [0] * N_SLOTS
+        self.done_totals = [0] * N_SLOTS
         self.calls = 0
         self.own_base = self.ws.buf.data_ptr()
         self.use_multimem = get_config().use_multimem and self.ws.has_multicast
@@ -47,7 +52,7 @@ class FusedTP:
         self.trace: Optional[Tensor] = None
 
     def _next_slot(self) -> Tuple[int, int, int, int]:
-        slot = self.calls & 1
+        slot = self.calls % N_SLOTS
         self.calls += 1
         self.epochs[slot] += 1
         data_off = slot * (self.slot_bytes + _FLAG_BYTES)
@@ -65,8 +70,10 @@ class FusedTP:
         self.done_totals[slot] += int(inc)
         return data_off
 
-    def gemm_all_reduce(self, a: Tensor, b: Tensor, a_mn: bool, b_mn: bool, partial: Optional[Tensor] = None) -> Tensor:
-        """``sum over ranks of (a @ b^T + partial)`` as a fresh ``[M, N]`` tensor (copied out of the workspace).
+    def gemm_all_reduce(self, a: Tensor, b: Tensor, a_mn: bool, b_mn: bool, partial: Optional[Tensor] = None,
+                        copy: bool = True) -> Tensor:
+        """``sum over ranks of (a @ b^T + partial)`` as ``[M, N]``: a fresh tensor, or with ``copy=False`` a view of
+        the workspace slot that must be consumed before ``N_SLOTS - 1`` further fused calls are issued.
         ``partial`` is another per-rank partial sum ``[M, N]`` that joins this rank's tiles before the reduction."""
         M = a.size(1) if a_mn else a.size(0)
         K = a.size(0) if a_mn else a.size(1)
@@ -74,7 +81,7 @@ class FusedTP:
         off = self._call(a, b, a_mn, b_mn, None, None, None, _FLAG_RESIDUAL if partial is not None else 0, M, N, K,
                          MODE_ALLREDUCE, aux=partial)
         view = self.ws.buf.view(torch.uint8)[off: off + M * N * 2].view(a.dtype).view(M, N)
-        return view.clone()
+        return view.clone() if copy else view
 
     def gemm_reduce_scatter(self, a: Tensor, b: Tensor, a_mn: bool, b_mn: bool, partial: Optional[Tensor] = None) -> Tensor:
         M = a.size(1) if a_mn else a.size(0)
@@ -130,16 +137,17 @@ class _RowParallelFused(torch.autograd.Function):
     """``y = all_reduce(x_shard @ W_shard^T)``; backward needs no communication."""
 
     @staticmethod
-    def forward(ctx, x, weight, reversed_, tp: FusedTP, partial=None):
+    def forward(ctx, x, weight, reversed_, tp: FusedTP, partial=None, copy=True):
         """``partial``: this rank's partial sum of another row-parallel product with the same output shape; it joins
-        the tiles before the reduction, so both products share the one all-reduce."""
+        the tiles before the reduction, so both products share the one all-reduce. ``copy=False``: the result is a
+        view of the workspace (the caller consumes it at once, e.g. by adding the bias)."""
         x2 = x.reshape(-1, x.size(-1))
         p2 = None
         if partial is not None:
             p2 = partial.reshape(x2.size(0), -1)
             if p2.stride(-1) != 1:
                 p2 = p2.contiguous()
-        y = tp.gemm_all_reduce(x2, weight, False, reversed_, partial=p2)
+        y = tp.gemm_all_reduce(x2, weight, False, reversed_, partial=p2, copy=copy)
         ctx.save_for_backward(x2, weight)
         ctx.reversed, ctx.in_shape = reversed_, x.shape
         ctx.partial_shape = partial.shape if partial is not None else None
@@ -158,7 +166,7 @@ class _RowParallelFused(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             dw = weight_grad(weight, x2, dy2) if ctx.reversed else weight_grad(weight, dy2, x2)
         d_partial = dy.reshape(ctx.partial_shape) if (ctx.partial_shape is not None and ctx.needs_input_grad[4]) else None
-        return dx, dw, None, None, d_partial
+        return dx, dw, None, None, d_partial, None
 
 
 class _ColumnParallelFused(torch.autograd.Function):
@@ -194,7 +202,9 @@ class _ColumnParallelFused(torch.autograd.Function):
             dy2 = ext.bias_gelu_bwd(dy2, z, None)
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
-            dx = ctx.tp.gemm_all_reduce(dy2, weight, False, not ctx.reversed).view(ctx.in_shape)
+            # the input gradient goes straight to the next backward node (or is summed, out of place, with the
+            # residual branch's gradient): a view of the workspace slot is enough
+            dx = ctx.tp.gemm_all_reduce(dy2, weight, False, not ctx.reversed, copy=False).view(ctx.in_shape)
         if ctx.needs_input_grad[1]:
             dw = weight_grad(weight, x2, dy2) if ctx.reversed else weight_grad(weight, dy2, x2)
         if ctx.has_bias and ctx.needs_input_grad[2]:
@@ -357,7 +367,7 @@ class _TPBlockInput(torch.autograd.Function):
                         gemm(d, w, False, True, out=part, flags=FLAG_ACCUMULATE)
                 if dz is not None and ctx.fused:
                     tp = get_fused_tp(mpu.get_tensor_parallel_group())
-                    dx = tp.gemm_all_reduce(dz, w_in, False, True, partial=part)      # the one collective
+                    dx = tp.gemm_all_reduce(dz, w_in, False, True, partial=part, copy=False)      # the one collective
                 else:
                     if dz is not None:
                         if part is None:

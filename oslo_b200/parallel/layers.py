@@ -173,9 +173,11 @@ class RowParallelLinear(nn.Linear):
             x = self.mpu.scatter(x, dim=-1)
         return _linear(x, self.weight, None, self.reversed, self.oslo_fused)
 
-    def forward(self, x: Tensor, activation: Optional[str] = None, partial: Optional[Tensor] = None) -> Tensor:
+    def forward(self, x: Tensor, activation: Optional[str] = None, partial: Optional[Tensor] = None,
+                residual: Optional[Tensor] = None) -> Tensor:
         """``partial``: partial sum of another row-parallel layer (``partial_forward``), reduced together with this
-        layer's product; that layer's bias, if any, is the caller's business."""
+        layer's product; that layer's bias, if any, is the caller's business. ``residual`` (full tensor, same shape
+        as the result) is added after the reduction, in the same pass as the bias on the kernel path."""
         mpu = self.mpu
         if mpu is not None and not self.input_is_parallel:
             x = mpu.scatter(x, dim=-1)
@@ -193,8 +195,15 @@ class RowParallelLinear(nn.Linear):
                         y = fused_tp._RowParallelSeqFused.apply(x, self.weight, self.reversed, tp, None)
                         y = y + mpu.reduce_scatter_sequence(partial, dim=-2)
                 else:
-                    y = fused_tp._RowParallelFused.apply(x, self.weight, self.reversed, tp, partial)
-                return y if self.bias is None else y + self.bias
+                    # with a bias the sum is consumed at once by the addition below, so the kernel's workspace slot
+                    # is handed out as it is; without one the caller gets a tensor of its own
+                    y = fused_tp._RowParallelFused.apply(x, self.weight, self.reversed, tp, partial,
+                                                         self.bias is None and residual is None)
+                if residual is not None and residual.shape == y.shape:
+                    from ..ops import cuda_ops
+                    return cuda_ops.bias_dropout_residual(y, self.bias, residual, 0.0, False)   # one pass over y
+                y = y if self.bias is None else y + self.bias
+                return y if residual is None else y + residual
         y = _linear(x, self.weight, None, self.reversed, self.oslo_fused)
         if partial is not None:
             y = y + partial
@@ -202,4 +211,4 @@ class RowParallelLinear(nn.Linear):
             y = mpu.reduce_scatter_sequence(y, dim=-2) if self.sequence_parallel else mpu.reduce(y)
         if self.bias is not None:
             y = y + self.bias
-        return y
+        return y if residual is None else y + residual

@@ -86,6 +86,58 @@ class SymmetricWorkspace:
         return x
 
 
+class SymmetricFlat:
+    """A flat 16-bit buffer in symmetric memory of a (data-parallel) group: same size on every rank, peer-mapped,
+    with the NVSwitch multicast mapping when there is one. The data-parallel wrapper and ``FusedAdamW`` keep the flat
+    gradient and parameter buffers in it, so that a bucket's reduce-scatter and the parameter all-gather are this
+    package's own kernels (``dp_reduce_scatter_kernel`` / ``dp_all_gather_kernel`` in ``csrc/comm.cu``): rank ``r``
+    owns elements ``[r * shard, (r + 1) * shard)``."""
+
+    def __init__(self, group, numel: int, dtype: torch.dtype, device: torch.device) -> None:
+        import torch.distributed._symmetric_memory as symm
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.tensor = symm.empty(int(numel), dtype=dtype, device=device)
+        self.handle = symm.rendezvous(self.tensor, group)
+        self.peer_ptrs_dev = int(self.handle.buffer_ptrs_dev)
+        self.signal_ptrs_dev = int(self.handle.signal_pad_ptrs_dev)
+        try:
+            self.mc_ptr = int(self.handle.multicast_ptr) if self.handle.has_multicast_support else 0
+        except Exception:
+            self.mc_ptr = 0
+        self.tensor.zero_()
+        self.shard = -(-int(numel) // (8 * self.world)) * 8      # elements per rank, a multiple of 8
+        self.handle.barrier()
+
+    def _mm(self) -> bool:
+        return bool(get_config().use_multimem) and self.mc_ptr != 0
+
+    def reduce_scatter_(self, lo: int, hi: int) -> None:
+        """Elements [lo, hi) (multiples of 8): this rank's part becomes the sum over the group, in place.
+        Collective: every rank of the group calls it with the same range, on a stream of its choice."""
+        ops.load_ext(required=True).dp_reduce_scatter(self.tensor, self.peer_ptrs_dev, self.mc_ptr, self.signal_ptrs_dev,
+                                                     int(lo), int(hi), self.shard, self.rank, self.world, self._mm())
+
+    def all_gather_(self, lo: int, hi: int) -> None:
+        """Elements [lo, hi): every rank's own part is copied into all ranks' buffers. Collective."""
+        ops.load_ext(required=True).dp_all_gather(self.tensor, self.peer_ptrs_dev, self.mc_ptr, self.signal_ptrs_dev,
+                                                 int(lo), int(hi), self.shard, self.rank, self.world, self._mm())
+
+
+def symmetric_flat_usable(group, dtype: torch.dtype, device) -> bool:
+    """The data-parallel buffers go to symmetric memory on CUDA devices, over NCCL groups of more than one rank,
+    for 16-bit gradients / parameters, when the kernels are built and ``OSLO_B200_DP_SYMMETRIC`` is not switched off.
+    Every condition is the same on all ranks of the group."""
+    if group is None or not get_config().dp_symmetric:
+        return False
+    if torch.device(device).type != "cuda" or dtype not in (torch.bfloat16, torch.float16):
+        return False
+    if dist.get_backend(group) != "nccl" or dist.get_world_size(group) < 2 or dist.get_world_size(group) > 16:
+        return False
+    return ops.kernels_available()
+
+
 class _VocabEmbed(torch.autograd.Function):
     """Lookup in a vocabulary-sharded table + its collective as one kernel (``vocab_embed_kernel``): the rank that
     owns a token's row stores it into every rank's staging buffer. Backward is local: every rank holds the whole

@@ -64,3 +64,37 @@ def test_reference_arm_trains_the_unmodified_reference_on_cpu_ranks(tmp_path):
     run_distributed(_reference_ranks, 2, str(tmp_path))
     rec = json.load(open(tmp_path / "line.json"))
     assert rec["config"]["parallelism"].startswith("dp2") and rec["steps"] == 2 and rec["warmup"] == 1
+
+
+def _reference_decode_rank(rank, world, out_dir):
+    import types
+    sys.path.insert(0, ROOT)
+    from baseline import reference_runner as rr
+    assert rr.probe() == ""
+    args = types.SimpleNamespace(gpus=world, steps=1, warmup=1, model="gptj-tiny", no_e2e=False, mode="decode",
+                                 prompt=8, new_tokens=6, decode_batch=2, tp=1)
+    line = rr.run_decode(args, None, force_cpu=True)
+    assert line["impl"] == "reference" and line["unit"] == "ms/token" and line["higher_is_better"] is False
+    assert line["value"] > 0 and line["e2e"]["d2h_bytes_per_step"] == 2 * 14 * 8
+    assert "oslo_b200" not in sys.modules
+
+
+def test_reference_arm_greedy_decode_runs_the_unmodified_reference_on_cpu(tmp_path):
+    """The reference's own ``generate()`` (greedy search, its vendored 4.x loop) runs on the installed stack."""
+    import pytest
+    if not _reference_installed():
+        pytest.skip("reference package not installed under baseline/_ref")
+    from tests.dist_utils import run_distributed
+    run_distributed(_reference_decode_rank, 1, str(tmp_path))
+
+
+def test_default_plan_follows_the_model_parallel_sweep():
+    sys.path.insert(0, ROOT)
+    import bench
+    names = {n: bench.default_plan(n) for n in (1, 2, 4, 8)}
+    assert names[1][0]["name"] == "single" and names[1][1] == []
+    assert (names[2][0]["tp"], names[2][0]["pp"]) == (2, 1) and names[2][1][0]["name"] == "dp2_zero1"
+    assert (names[4][0]["tp"], names[4][0]["pp"]) == (4, 1)
+    p8, also8 = names[8]
+    assert (p8["tp"], p8["pp"], p8["micro"]) == (2, 4, 4)          # 64 sequences as 16 micro-batches of 4
+    assert [a["name"] for a in also8] == ["tp8_b8x2048", "dp8_zero1"] and also8[0]["replica_batch"] == 8

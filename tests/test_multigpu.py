@@ -198,3 +198,216 @@ def test_zero1_data_parallel(tmp_path):
         losses.append(float(loss))
     torch.save({"state": state, "losses": losses}, tmp_path / "ref.pt")
     run_gpus(_zero_dp, 2, str(tmp_path))
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# pipeline / 3D parallel training on GPUs against a single-GPU run (the counterpart of the reference's
+# tests/gpt2/gpt2_test_3d_training_with_ddp.py:87-139, with assertions)
+
+def _make(kind):
+    import oslo_b200 as ob
+    if kind == "gptj":
+        cfg = ob.GPTJConfig(vocab_size=2048, n_positions=256, n_embd=512, n_layer=4, n_head=8, rotary_dim=32,
+                            torch_dtype=torch.bfloat16)
+        return ob.GPTJForCausalLM(cfg)
+    cfg = ob.GPTNeoConfig(vocab_size=2048, max_position_embeddings=256, hidden_size=512, num_layers=4, num_heads=8,
+                          window_size=64, torch_dtype=torch.bfloat16)
+    return ob.GPTNeoForCausalLM(cfg)
+
+
+def _ids(step):
+    return torch.randint(0, 2048, (8, 128), generator=torch.Generator().manual_seed(100 + step))
+
+
+def _oracle(kind, tmp_path, steps=3):
+    from oslo_b200.optim import FusedAdamW
+    torch.manual_seed(0)
+    model = _make(kind).to(torch.bfloat16)
+    state = {k: v.clone() for k, v in model.state_dict().items()}
+    model = model.cuda().fuse().train()
+    opt = FusedAdamW(model.parameters(), lr=1e-3, max_grad_norm=1.0)
+    losses = []
+    for s in range(steps):
+        ids = _ids(s).cuda()
+        opt.zero_grad()
+        loss = model(input_ids=ids, labels=ids, output_logits=False).loss
+        loss.backward()
+        opt.step()
+        losses.append(float(loss.detach()))
+    torch.save({"state": state, "losses": losses}, tmp_path / "ref.pt")
+
+
+def _train_3d(rank, world, tmp, kind, tp, pp, seq_par, steps=3):
+    import torch.distributed as dist
+    import oslo_b200 as ob
+    from oslo_b200.optim import FusedAdamW
+    from oslo_b200.parallel.data_parallel import DistributedDataParallel
+    ref = torch.load(os.path.join(tmp, "ref.pt"), weights_only=True)
+    torch.manual_seed(0)
+    model = _make(kind).to(torch.bfloat16)
+    model.load_state_dict(ref["state"])
+    model = ob.parallelize(model, tensor_parallel_size=tp, pipeline_parallel_size=pp, micro_batch_size=2,
+                           sequence_parallel=seq_par)
+    model.fuse().train()
+    mpu = model.mpu
+    dp, dpr = mpu.get_data_parallel_world_size(), mpu.get_data_parallel_rank()
+    opt = FusedAdamW(model.gpu_parameters(), lr=1e-3, max_grad_norm=1.0, model=model,
+                     shard_group=mpu.get_data_parallel_group() if dp > 1 else None,
+                     model_parallel_group=mpu.get_model_parallel_group() if tp * pp > 1 else None)
+    call = DistributedDataParallel(model, mpu, optimizer=opt, bucket_mb=1) if dp > 1 else model
+    losses = []
+    for s in range(steps):
+        ids = _ids(s).cuda()
+        n = ids.size(0) // dp
+        mine = ids[dpr * n:(dpr + 1) * n]
+        opt.zero_grad()
+        if pp > 1:
+            accum = n // 2
+            tot = 0.0
+            for out in call(input_ids=mine, labels=mine, output_logits=False):
+                (out.loss / accum).backward()
+                tot = tot + out.loss.detach().float()
+            loss = tot / accum
+        else:
+            loss = call(input_ids=mine, labels=mine, output_logits=False).loss
+            loss.backward()
+            loss = loss.detach().float()
+        opt.step()
+        t = loss.reshape(1).clone()
+        if dp > 1:
+            dist.all_reduce(t, group=mpu.get_data_parallel_group())
+            t /= dp
+        losses.append(float(t))
+    torch.cuda.synchronize()
+    # every stage reports the loss of the last stage; compare on every rank
+    for a, b in zip(losses, ref["losses"]):
+        assert abs(a - b) < 0.08, (rank, losses, ref["losses"])
+    assert int(ob.ops.load_ext().error_word(ids).item()) == 0
+
+
+_LAYOUTS = [  # kind, tp, pp, sequence parallel, GPUs
+    ("gptj", 1, 2, False, 2), ("gpt_neo", 1, 2, False, 2), ("gptj", 2, 1, True, 2),
+    ("gptj", 2, 2, False, 4), ("gpt_neo", 2, 2, False, 4), ("gptj", 4, 1, False, 4), ("gptj", 1, 4, False, 4),
+    ("gptj", 2, 2, True, 4),
+    ("gpt_neo", 2, 2, False, 8), ("gptj", 2, 4, False, 8), ("gptj", 8, 1, False, 8), ("gptj", 2, 2, False, 8),
+]
+
+
+@pytest.mark.parametrize("kind,tp,pp,seq_par,world", _LAYOUTS,
+                         ids=[f"{k}-tp{t}-pp{p}{'-sp' if sp else ''}-{w}gpus" for k, t, p, sp, w in _LAYOUTS])
+def test_model_parallel_training_matches_one_gpu(tmp_path, kind, tp, pp, seq_par, world):
+    """Tensor / pipeline / data parallel layouts (ZeRO-1 + bucketed reduction when there are replicas) reproduce the
+    loss curve of one GPU over 3 optimizer steps with gradient clipping."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _oracle(kind, tmp_path)
+    run_gpus(_train_3d, world, str(tmp_path), kind, tp, pp, seq_par)
+
+
+def _dp_kernels(rank, world):
+    """Bucket reduce-scatter / all-gather kernels on symmetric flat buffers against NCCL, NVSwitch multicast on and
+    off, ragged bucket boundaries, repeated calls (the signal words are reused)."""
+    import torch.distributed as dist
+    import oslo_b200 as ob
+    from oslo_b200.config import set_config
+    from oslo_b200.parallel.mpu import MPU
+    from oslo_b200.parallel.symmetric import SymmetricFlat
+    mpu = MPU(1, 1)
+    g = mpu.get_data_parallel_group()
+    n = 8 * world * 40000 + 8 * world          # not a multiple of the kernels' per-pass span
+    flat = SymmetricFlat(g, n, torch.bfloat16, torch.device("cuda", rank))
+    assert flat.shard * world == n
+    for mm in ([True, False] if flat.mc_ptr else [False]):
+        set_config(use_multimem=mm)
+        for rep, (lo, hi) in enumerate([(0, n), (8, n - 8), (flat.shard - 64, flat.shard + 4096), (1024, 1032), (0, n)]):
+            torch.manual_seed(1000 * rep + rank)
+            src = (torch.randn(n, device="cuda") * 2).to(torch.bfloat16)
+            flat.tensor.copy_(src)
+            want = src.float()
+            dist.all_reduce(want, group=g)
+            torch.cuda.synchronize()
+            dist.barrier()
+            flat.reduce_scatter_(lo, hi)
+            torch.cuda.synchronize()
+            a, b = max(lo, rank * flat.shard), min(hi, (rank + 1) * flat.shard)
+            got = flat.tensor.float()
+            if b > a:
+                assert torch.allclose(got[a:b], want[a:b], atol=0.06, rtol=0.02), ("RS", mm, lo, hi, (got[a:b] - want[a:b]).abs().max())
+            keep = torch.ones(n, dtype=torch.bool, device="cuda")
+            keep[a:max(a, b)] = False
+            assert torch.equal(flat.tensor[keep], src[keep]), ("RS touched elements outside this rank's part", mm, lo, hi)
+            # all-gather: after it every rank holds every owner's part of [lo, hi)
+            dist.barrier()
+            flat.all_gather_(lo, hi)
+            torch.cuda.synchronize()
+            full = [torch.empty_like(flat.tensor) for _ in range(world)]
+            dist.all_gather(full, flat.tensor.clone(), group=g)
+            for r in range(1, world):
+                assert torch.equal(full[r][lo:hi], full[0][lo:hi]), ("AG", mm, lo, hi, r)
+            own = flat.tensor.float()
+            assert torch.allclose(own[lo:hi], want[lo:hi], atol=0.06, rtol=0.02), ("AG values", mm, lo, hi)
+    assert int(ob.ops.load_ext().error_word(flat.tensor).item()) == 0
+
+
+def test_dp_symmetric_reduce_scatter_and_all_gather_kernels():
+    run_gpus(_dp_kernels, 2)
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_dp_symmetric_kernels_world_n(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    run_gpus(_dp_kernels, world)
+
+
+def _zero_dp_ab(rank, world, tmp):
+    """ZeRO-1 data parallelism with the symmetric-memory kernels and with NCCL: same losses, same final weights."""
+    import torch.distributed as dist
+    import oslo_b200 as ob
+    from oslo_b200.config import set_config
+    from oslo_b200.optim import FusedAdamW
+    from oslo_b200.parallel.data_parallel import DistributedDataParallel
+    ref = torch.load(os.path.join(tmp, "ref.pt"), weights_only=True)
+    finals = {}
+    for symmetric in (True, False):
+        set_config(dp_symmetric=symmetric)
+        torch.manual_seed(0)
+        model = ob.GPTJForCausalLM(_cfg()).to(torch.bfloat16)
+        model.load_state_dict(ref["state"])
+        model = ob.parallelize(model, tensor_parallel_size=1)
+        model.fuse().train()
+        mpu = model.mpu
+        opt = FusedAdamW(model.gpu_parameters(), lr=1e-3, max_grad_norm=1.0, shard_group=mpu.get_data_parallel_group())
+        ddp = DistributedDataParallel(model, mpu, optimizer=opt, bucket_mb=1)
+        assert ddp._symm == symmetric and (opt.param_gather is not None) == symmetric
+        ids = torch.randint(0, 2048, (4, 128), generator=torch.Generator().manual_seed(1)).cuda()
+        mine = ids[rank * 2:(rank + 1) * 2]
+        losses = []
+        for _ in range(4):
+            opt.zero_grad()
+            for i in range(2):                    # two micro-batches: reduction during the second backward only
+                import contextlib
+                with (ddp.no_sync() if i == 0 else contextlib.nullcontext()):
+                    loss = ddp(input_ids=mine[i:i + 1], labels=mine[i:i + 1], output_logits=False).loss
+                    (loss / 2).backward()
+            opt.step()
+            losses.append(float(loss.detach()))
+        finals[symmetric] = (losses, {k: v.detach().float().clone() for k, v in model.state_dict().items()})
+        # every replica ends with the same parameters
+        flat = opt.buf.flat_p.float()
+        other = flat.clone()
+        dist.all_reduce(other, op=dist.ReduceOp.MAX)
+        assert torch.equal(flat, other), "replicas diverged"
+    for a, b in zip(finals[True][0], finals[False][0]):
+        assert abs(a - b) < 0.03, finals
+    for k, v in finals[True][1].items():
+        assert torch.allclose(v, finals[False][1][k], atol=3e-2, rtol=3e-2), k
+    assert int(ob.ops.load_ext().error_word(ids).item()) == 0
+
+
+def test_zero1_symmetric_kernels_match_nccl(tmp_path):
+    import oslo_b200 as ob
+    torch.manual_seed(0)
+    model = ob.GPTJForCausalLM(_cfg()).to(torch.bfloat16)
+    torch.save({"state": {k: v.clone() for k, v in model.state_dict().items()}}, tmp_path / "ref.pt")
+    run_gpus(_zero_dp_ab, 2, str(tmp_path))
