@@ -32,19 +32,23 @@ def _entry(rank, world, port, fn, args, errq):
             dist.destroy_process_group()
 
 
-def run_gpus(fn, world, *args, timeout=600):
+def run_gpus(fn, world, *args, timeout=300):
     ctx = mp.get_context("spawn")
     errq = ctx.SimpleQueue()
     port = _free_port()
     procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, errq)) for r in range(world)]
+    import time
     for p in procs:
         p.start()
+    deadline = time.monotonic() + timeout          # for the whole group, not per process
     for p in procs:
-        p.join(timeout)
+        p.join(max(0.0, deadline - time.monotonic()))
     bad = [p for p in procs if p.exitcode != 0]
     for p in procs:
         if p.is_alive():
             p.kill()
+    for p in procs:
+        p.join(10)
     if bad:
         msgs = []
         while not errq.empty():
