@@ -179,6 +179,7 @@ class PipelineParallelEngine:
         self.p2p: Optional[P2PCommunicator] = None
         self._grad_hooks_cb: List[Callable[[], None]] = []
         self.on_last_backward: Optional[Callable[[bool], None]] = None
+        self.zero_stage: Optional[int] = None  # of a DeepSpeed engine around this model; looked up at the first call
         self.profile = False                  # record CUDA events around every forward / backward (schedule_report)
         self._events: Dict[tuple, Dict[str, Any]] = {}
 
@@ -365,9 +366,37 @@ class PipelineParallelEngine:
                 "ideal_idle_share": (self.pp - 1) / (m + self.pp - 1) if m else 0.0, "micro_batches": m,
                 "stage": self.stage}
 
+    def _guess_zero_stage(self) -> int:
+        """ZeRO stage of a DeepSpeed engine that is driving this model, found among the local variables of the calling
+        frames (reference: oslo/parallelism/engine_pipeline.py:457-480). Stages 2 and 3 partition gradients /
+        parameters in ways that do not survive several micro-batch backward passes per step, so they are refused."""
+        import inspect
+        try:
+            from deepspeed.runtime.engine import DeepSpeedEngine as _Engine
+        except Exception:      # DeepSpeed is not installed: recognise an engine by its class name
+            _Engine = None
+        frame = inspect.currentframe()
+        try:
+            while frame is not None:
+                for obj in list(frame.f_locals.values()):
+                    is_engine = isinstance(obj, _Engine) if _Engine is not None else type(obj).__name__ == "DeepSpeedEngine"
+                    if is_engine and callable(getattr(obj, "zero_optimization", None)):
+                        if obj.zero_optimization():
+                            return int(obj.zero_optimization_stage())
+                        return 0
+                frame = frame.f_back
+        finally:
+            del frame
+        return 0
+
     def forward(self, *args, **kwargs) -> Iterator[Any]:
         if args:
             raise ValueError("pipeline-parallel models take keyword arguments only, e.g. model(**batch)")
+        if self.zero_stage is None:
+            self.zero_stage = self._guess_zero_stage()
+        if self.zero_stage > 1:
+            raise RuntimeError("ZeRO-2 and ZeRO-3 are incompatible with pipeline parallelism "
+                               "(https://github.com/microsoft/DeepSpeed/issues/1110); use ZeRO stage 0 or 1")
         return self._generator(kwargs)
 
     def _generator(self, kwargs: Dict[str, Any]) -> Iterator[Any]:

@@ -1,0 +1,227 @@
+"""Smaller reference features: TensorFlow checkpoint names, the ONNX export description of GPT-2, ZeRO-stage
+detection under pipeline parallelism, and the two sentence-mapping index builders against NumPy statements."""
+import sys
+import types
+
+import numpy as np
+import pytest
+import torch
+
+import oslo_b200 as ob
+from tests.dist_utils import run_distributed
+
+
+def _tiny_gpt2():
+    torch.manual_seed(0)
+    return ob.GPT2LMHeadModel(ob.GPT2Config(vocab_size=61, n_positions=32, n_embd=16, n_layer=2, n_head=2))
+
+
+def test_tf_variable_names_map_to_state_dict_keys():
+    from oslo_b200.models.gpt2 import tf_name_to_key
+    assert tf_name_to_key("model/wte") == "transformer.wte.weight"
+    assert tf_name_to_key("model/wpe") == "transformer.wpe.weight"
+    assert tf_name_to_key("model/h11/attn/c_attn/w") == "transformer.h.11.attn.c_attn.weight"
+    assert tf_name_to_key("model/h0/mlp/c_proj/b") == "transformer.h.0.mlp.c_proj.bias"
+    assert tf_name_to_key("model/h3/ln_2/g") == "transformer.h.3.ln_2.weight"
+    assert tf_name_to_key("model/ln_f/b") == "transformer.ln_f.bias"
+    assert tf_name_to_key("global_step") is None
+    keys = set(_tiny_gpt2().state_dict())
+    for name in ("model/h1/attn/c_proj/w", "model/h1/mlp/c_fc/b", "model/h0/ln_1/g", "model/wte"):
+        assert tf_name_to_key(name) in keys
+
+
+def test_tf_checkpoint_loader_fills_every_weight(monkeypatch):
+    """A stand-in ``tensorflow.train`` serves the variables of an OpenAI-style checkpoint (projection weights stored
+    with a leading 1-sized axis); after loading, the model computes what the source weights compute."""
+    from oslo_b200.models.gpt2 import load_tf_weights_in_gpt2
+    src = _tiny_gpt2().eval()
+    store = {}
+    for key, p in src.named_parameters():
+        parts = key.replace("transformer.", "").split(".")
+        arr = p.detach().numpy().copy()
+        if parts[0] in ("wte", "wpe"):
+            store["model/" + parts[0]] = arr
+            continue
+        leaf = {"weight": "g" if "ln_" in key else "w", "bias": "b"}[parts[-1]]
+        mid = parts[:-1]
+        if mid[0] == "h":
+            mid = ["h" + mid[1]] + mid[2:]
+        store["model/" + "/".join(mid + [leaf])] = arr[None] if arr.ndim == 2 else arr     # projections: [1, in, out]
+    store["global_step"] = np.zeros(())
+    fake = types.ModuleType("tensorflow")
+    fake.train = types.SimpleNamespace(list_variables=lambda path: [(k, list(v.shape)) for k, v in store.items()],
+                                       load_variable=lambda path, name: store[name])
+    monkeypatch.setitem(sys.modules, "tensorflow", fake)
+    torch.manual_seed(123)
+    dst = ob.GPT2LMHeadModel(src.config).eval()
+    ids = torch.randint(0, 61, (2, 8))
+    assert not torch.allclose(dst(input_ids=ids).logits, src(input_ids=ids).logits)
+    load_tf_weights_in_gpt2(dst, dst.config, "/nonexistent/model.ckpt")
+    assert torch.allclose(dst(input_ids=ids).logits, src(input_ids=ids).logits, atol=1e-6)
+
+
+def test_tf_checkpoint_loader_needs_tensorflow(monkeypatch):
+    from oslo_b200.models.gpt2 import load_tf_weights_in_gpt2
+    monkeypatch.setitem(sys.modules, "tensorflow", None)
+    with pytest.raises(ImportError):
+        load_tf_weights_in_gpt2(_tiny_gpt2(), None, "x")
+
+
+def test_gpt2_onnx_config_describes_inputs_outputs_and_dummy_inputs():
+    cfg = _tiny_gpt2().config
+    oc = ob.GPT2OnnxConfig(cfg)
+    assert list(oc.inputs) == ["input_ids", "attention_mask"] and list(oc.outputs) == ["last_hidden_state"]
+    dummy = oc.generate_dummy_inputs(batch_size=3, seq_length=5)
+    assert dummy["input_ids"].shape == (3, 5) and dummy["attention_mask"].shape == (3, 5)
+    past = ob.GPT2OnnxConfig.with_past(cfg, task="causal-lm")
+    assert list(past.outputs)[0] == "logits" and len(past.inputs) == 2 + 2 * cfg.n_layer
+    d = past.generate_dummy_inputs()
+    assert len(d["past_key_values"]) == cfg.n_layer and list(d) == ["input_ids", "past_key_values", "attention_mask"]
+    k = d["past_key_values"][0][0]
+    assert k.shape == (2, cfg.n_head, 10, cfg.n_embd // cfg.n_head) and d["attention_mask"].shape == (2, 18)
+    # the dummy inputs run through the model
+    model = _tiny_gpt2().eval()
+    out = model(input_ids=d["input_ids"], past_key_values=d["past_key_values"], attention_mask=d["attention_mask"])
+    assert out.logits.shape == (2, 8, cfg.vocab_size)
+
+
+class DeepSpeedEngine:          # recognised by class name when DeepSpeed itself is not installed
+    def __init__(self, module, stage):
+        self.module, self.stage = module, stage
+
+    def zero_optimization(self):
+        return self.stage > 0
+
+    def zero_optimization_stage(self):
+        return self.stage
+
+    def __call__(self, **kw):
+        engine = self            # noqa: F841 - DeepSpeed's own forward keeps the engine in a local of the calling frame
+        return self.module(**kw)
+
+
+def _zero_stage_ranks(rank, world):
+    torch.manual_seed(0)
+    cfg = ob.GPT2Config(vocab_size=61, n_positions=16, n_embd=16, n_layer=2, n_head=2)
+    ids = torch.randint(0, 61, (2, 8))
+    for stage, ok in ((1, True), (2, False), (3, False)):
+        model = ob.parallelize(ob.GPT2LMHeadModel(cfg), pipeline_parallel_size=2, micro_batch_size=1)
+        engine = DeepSpeedEngine(model.gpu_modules(), stage)
+        if ok:
+            for out in engine(input_ids=ids, labels=ids):
+                out.loss.backward()
+            assert model._pipe_engine.zero_stage == 1
+        else:
+            with pytest.raises(RuntimeError, match="ZeRO-2 and ZeRO-3"):
+                engine(input_ids=ids, labels=ids)
+    del engine                  # the lookup walks the callers' local variables: no engine may be left in this frame
+    plain = ob.parallelize(ob.GPT2LMHeadModel(cfg), pipeline_parallel_size=2, micro_batch_size=1)
+    for out in plain(input_ids=ids, labels=ids):
+        out.loss.backward()
+    assert plain._pipe_engine.zero_stage == 0
+
+
+def test_pipeline_engine_refuses_zero_stage_2_and_3():
+    """Reference behaviour (oslo/parallelism/engine_pipeline.py:270-278, :457-480): the stage of a DeepSpeed engine
+    found in the calling frames decides; 0 / 1 run, 2 / 3 raise."""
+    run_distributed(_zero_stage_ranks, 2)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# sentence-span index builders (C++: csrc/data_builders.cpp) against plain-Python statements of the same rules
+
+def _py_mapping(docs, sizes, num_epochs, max_num_samples, max_seq_length, min_num_sent=2):
+    """Greedy packing of whole sentences into samples of about ``max_seq_length`` tokens, document by document:
+    a sample closes when it has reached the target and more than one sentence of the document is left, or when the
+    document ends; documents with fewer than ``min_num_sent`` sentences or a sentence above 512 tokens are skipped.
+    Rows: (first sentence, one past the last sentence, target length)."""
+    rows = []
+    for _epoch in range(num_epochs):
+        for d in range(len(docs) - 1):
+            first, last = int(docs[d]), int(docs[d + 1])
+            remain = last - first
+            if remain < min_num_sent or any(sizes[s] > 512 for s in range(first, last)):
+                continue
+            start, seq_len, num_sent = first, 0, 0
+            for s in range(first, last):
+                seq_len += int(sizes[s])
+                num_sent += 1
+                remain -= 1
+                if (seq_len >= max_seq_length and remain > 1 and num_sent >= min_num_sent) or remain == 0:
+                    if num_sent >= min_num_sent:
+                        rows.append((start, s + 1, max_seq_length))
+                        if len(rows) >= max_num_samples:
+                            return rows
+                    start, seq_len, num_sent = s + 1, 0, 0
+    return rows
+
+
+def _py_blocks(docs, sizes, titles, num_epochs, max_num_samples, max_seq_length, one_sent):
+    """Blocks of whole sentences whose token budget is ``max_seq_length`` minus the document's title length.
+    Rows: (first sentence, one past the last, document, running block id within the epoch)."""
+    rows, min_sent = [], (1 if one_sent else 2)
+    for _epoch in range(num_epochs):
+        block_id = 0
+        for d in range(len(docs) - 1):
+            first, last = int(docs[d]), int(docs[d + 1])
+            remain, budget = last - first, max_seq_length - int(titles[d])
+            if remain < min_sent or any(sizes[s] > 512 for s in range(first, last)):
+                continue
+            start, seq_len, num_sent = first, 0, 0
+            for s in range(first, last):
+                seq_len += int(sizes[s])
+                num_sent += 1
+                remain -= 1
+                if (seq_len >= budget and remain >= min_sent and num_sent >= min_sent) or remain == 0:
+                    rows.append((start, s + 1, d, block_id))
+                    block_id += 1
+                    if len(rows) >= max_num_samples:
+                        return rows
+                    start, seq_len, num_sent = s + 1, 0, 0
+    return rows
+
+
+def _corpus(seed):
+    rng = np.random.default_rng(seed)
+    sent_per_doc = rng.integers(1, 12, size=40)
+    docs = np.concatenate([[0], np.cumsum(sent_per_doc)]).astype(np.int64)
+    sizes = rng.integers(3, 90, size=int(docs[-1])).astype(np.int32)
+    sizes[rng.integers(0, len(sizes), size=2)] = 600          # two documents carry an over-long sentence
+    titles = rng.integers(2, 12, size=len(docs) - 1).astype(np.int32)
+    return docs, sizes, titles
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_build_mapping_matches_the_python_statement(seed):
+    from oslo_b200.data import cpp_builders
+    lib = cpp_builders.load()
+    if lib is None:
+        pytest.skip("_data_C.so is not built")
+    docs, sizes, _ = _corpus(seed)
+    for epochs, cap, max_len in ((1, 10 ** 6, 128), (2, 10 ** 6, 64), (3, 37, 100)):
+        want = _py_mapping(docs, sizes, epochs, cap, max_len)
+        got = lib.build_mapping(docs, sizes, epochs, cap, max_len, 0.0, 1234)
+        assert got.shape == (len(want), 3)
+        assert sorted(map(tuple, got.tolist())) == sorted(want)            # same samples; the order is shuffled
+        again = lib.build_mapping(docs, sizes, epochs, cap, max_len, 0.0, 1234)
+        assert np.array_equal(got, again), "the shuffle must be deterministic in the seed"
+        other = lib.build_mapping(docs, sizes, epochs, cap, max_len, 0.0, 99)
+        assert len(want) < 8 or not np.array_equal(got, other)
+    # short sequences: every target stays within [2, max], spans still tile each document without gaps
+    short = lib.build_mapping(docs, sizes, 1, 10 ** 6, 128, 0.5, 7)
+    assert short[:, 2].min() >= 2 and short[:, 2].max() <= 128 and (short[:, 2] < 128).any()
+    assert (short[:, 1] > short[:, 0]).all()
+
+
+@pytest.mark.parametrize("one_sent", [False, True])
+def test_build_blocks_mapping_matches_the_python_statement(one_sent):
+    from oslo_b200.data import cpp_builders
+    lib = cpp_builders.load()
+    if lib is None:
+        pytest.skip("_data_C.so is not built")
+    docs, sizes, titles = _corpus(3)
+    for epochs, cap, max_len in ((1, 10 ** 6, 128), (2, 10 ** 6, 72), (2, 25, 128)):
+        want = _py_blocks(docs, sizes, titles, epochs, cap, max_len, one_sent)
+        got = lib.build_blocks_mapping(docs, sizes, titles, epochs, cap, max_len, 5, use_one_sent_blocks=one_sent)
+        assert got.shape == (len(want), 4)
+        assert sorted(map(tuple, got.tolist())) == sorted(want)
