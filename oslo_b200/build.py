@@ -1,6 +1,7 @@
 """Ahead-of-time build of the in-tree extensions (``python -m oslo_b200.build``).
 
 * ``oslo_b200/_C.so``      - sm_100a CUDA kernels + ``torch.ops.oslo_b200`` bindings
+* ``oslo_b200/_C_bounds.so`` - the same, compiled with ``-DOSLO_DEBUG_BOUNDS`` (``--debug-bounds`` builds only this one)
 * ``oslo_b200/_data_C.so`` - host-only dataset index builders
 
 The reference compiles its kernels at first use with ``torch.utils.cpp_extension.load``
@@ -56,17 +57,22 @@ def _needs(out: str, stamp_file: str, stamp: str) -> bool:
         return f.read().strip() != stamp
 
 
-def build_kernels(force: bool = False, verbose: bool = True) -> str:
+def build_kernels(force: bool = False, verbose: bool = True, debug_bounds: bool = False) -> str:
+    """``debug_bounds``: the same sources with ``-DOSLO_DEBUG_BOUNDS`` into ``_C_bounds.so`` (loaded instead of
+    ``_C.so`` when ``OSLO_B200_DEBUG_BOUNDS=1``): data-dependent indices that had to be skipped or clamped are
+    reported through the device error word."""
     import torch
     from torch.utils import cpp_extension
 
     os.makedirs(BUILD, exist_ok=True)
-    out = os.path.join(HERE, "_C.so")
+    tag = "_C_bounds" if debug_bounds else "_C"
+    extra = ["-DOSLO_DEBUG_BOUNDS"] if debug_bounds else []
+    out = os.path.join(HERE, tag + ".so")
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     cu = [os.path.join(CSRC, f) for f in CUDA_SOURCES if os.path.exists(os.path.join(CSRC, f))]
     cpp = [os.path.join(CSRC, f) for f in CPP_SOURCES]
-    stamp = _stamp(cu + cpp + headers, torch.__version__ + " ".join(NVCC_FLAGS))
-    stamp_file = os.path.join(BUILD, "_C.stamp")
+    stamp = _stamp(cu + cpp + headers, torch.__version__ + " ".join(NVCC_FLAGS + extra))
+    stamp_file = os.path.join(BUILD, tag + ".stamp")
     if not force and not _needs(out, stamp_file, stamp):
         return out
     nvcc = _nvcc()
@@ -75,13 +81,14 @@ def build_kernels(force: bool = False, verbose: bool = True) -> str:
     tinc = ["-I" + p for p in cpp_extension.include_paths()]
     objs: List[str] = []
     jobs = []
+    suffix = ".bounds.o" if debug_bounds else ".o"
     for src in cu:
-        obj = os.path.join(BUILD, os.path.basename(src) + ".o")
+        obj = os.path.join(BUILD, os.path.basename(src) + suffix)
         objs.append(obj)
-        jobs.append([nvcc] + NVCC_FLAGS + inc + ["-c", src, "-o", obj])
+        jobs.append([nvcc] + NVCC_FLAGS + extra + inc + ["-c", src, "-o", obj])
     abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
     for src in cpp:
-        obj = os.path.join(BUILD, os.path.basename(src) + ".o")
+        obj = os.path.join(BUILD, os.path.basename(src) + suffix)
         objs.append(obj)
         jobs.append(["g++", "-std=c++17", "-O2", "-fPIC", "-fvisibility=hidden", f"-D_GLIBCXX_USE_CXX11_ABI={abi}",
                      "-DTORCH_EXTENSION_NAME=_C"] + inc + tinc + ["-c", src, "-o", obj])
@@ -119,10 +126,15 @@ def build_data(force: bool = False, verbose: bool = True) -> str:
     return out
 
 
-def build_all(force: bool = False, verbose: bool = True) -> None:
+def build_all(force: bool = False, verbose: bool = True, debug_bounds: bool = True) -> None:
     build_kernels(force, verbose)
+    if debug_bounds:
+        build_kernels(force, verbose, debug_bounds=True)
     build_data(force, verbose)
 
 
 if __name__ == "__main__":
-    build_all(force="--force" in sys.argv)
+    if "--debug-bounds" in sys.argv:
+        build_kernels(force="--force" in sys.argv, debug_bounds=True)
+    else:
+        build_all(force="--force" in sys.argv)

@@ -16,6 +16,7 @@
 #include <math_constants.h>
 
 #include "oslo_kernels.h"
+#include "ptx.cuh"
 
 namespace oslo {
 
@@ -477,14 +478,18 @@ template <typename T>
 __global__ void __launch_bounds__(128) decode_attn_kernel(const T* __restrict__ q, const T* __restrict__ kc,
                                                           const T* __restrict__ vc, const int* __restrict__ lengths,
                                                           float* __restrict__ ws, int H, int Tmax, int D, int splits,
-                                                          float scale, int window) {
+                                                          float scale, int window, int* err) {
   extern __shared__ float sm_dec[];
   float* qs = sm_dec;             // [D]
   float* red = qs + D;            // [4][D] per-warp partial outputs
   float* stat = red + 4 * D;      // [4][2]
   const int b = blockIdx.z, h = blockIdx.y, sp = blockIdx.x;
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
-  const int len = lengths[b];
+  int len = lengths[b];
+  if (len < 0 || len > Tmax) {   // a length that does not fit the cache: never read past it
+    OSLO_REPORT_BOUNDS(err);
+    len = len < 0 ? 0 : Tmax;
+  }
   int lo = 0;
   if (window > 0) lo = max(0, len - window);
   const int span = len - lo;
@@ -695,7 +700,7 @@ extern "C" int oslo_flash_bwd(const void* q, const void* k, const void* v, const
 
 extern "C" int oslo_decode_attn(const void* q, const void* kc, const void* vc, void* o, const int* lengths, float* ws,
                                 int B, int H, int T, int D, int splits, float scale, int window, int dtype,
-                                cudaStream_t st) {
+                                int* err_word, cudaStream_t st) {
   if (B * H == 0) return 0;
   if (D % 8 || D > 256) return -3;
   const size_t smem = (D + 4 * D + 8) * sizeof(float);
@@ -703,11 +708,11 @@ extern "C" int oslo_decode_attn(const void* q, const void* kc, const void* vc, v
   if (dtype == OSLO_DT_BF16) {
     decode_attn_kernel<__nv_bfloat16><<<grid, 128, smem, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kc,
                                                                (const __nv_bfloat16*)vc, lengths, ws, H, T, D, splits,
-                                                               scale, window);
+                                                               scale, window, err_word);
     decode_combine_kernel<__nv_bfloat16><<<B * H, 128, 0, st>>>(ws, (__nv_bfloat16*)o, D, splits);
   } else if (dtype == OSLO_DT_FP16) {
     decode_attn_kernel<__half><<<grid, 128, smem, st>>>((const __half*)q, (const __half*)kc, (const __half*)vc, lengths,
-                                                        ws, H, T, D, splits, scale, window);
+                                                        ws, H, T, D, splits, scale, window, err_word);
     decode_combine_kernel<__half><<<B * H, 128, 0, st>>>(ws, (__half*)o, D, splits);
   } else {
     return -2;

@@ -213,9 +213,16 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CU
           if (!vis) s[i] = -CUDART_INF_F;
         }
       }
-      float mx = s[0];
+      // four independent chains: one thread per row means nothing else hides the latency of a 64-long dependent chain
+      float mx4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-      for (int i = 1; i < BN; ++i) mx = fmaxf(mx, s[i]);
+      for (int i = 4; i < BN; i += 4) {
+        mx4[0] = fmaxf(mx4[0], s[i]);
+        mx4[1] = fmaxf(mx4[1], s[i + 1]);
+        mx4[2] = fmaxf(mx4[2], s[i + 2]);
+        mx4[3] = fmaxf(mx4[3], s[i + 3]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_ref, mx);
       // rescale O only when some row of this warp outgrew its reference by 2^8 (or on the first block)
       const bool grow = (j == 0) || (m_new - m_ref > FA_RESCALE_THRESHOLD);
@@ -227,13 +234,19 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CU
         l_sum *= factor;
       }
       const float m_use = (m_ref == -CUDART_INF_F) ? 0.f : m_ref;
-      float psum = 0.f;
+      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < BN; ++i) {
+      for (int i = 0; i < BN; i += 4) {
         s[i] = exp2f(s[i] - m_use);
-        psum += s[i];
+        s[i + 1] = exp2f(s[i + 1] - m_use);
+        s[i + 2] = exp2f(s[i + 2] - m_use);
+        s[i + 3] = exp2f(s[i + 3] - m_use);
+        ps4[0] += s[i];
+        ps4[1] += s[i + 1];
+        ps4[2] += s[i + 2];
+        ps4[3] += s[i + 3];
       }
-      l_sum += psum;
+      l_sum += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
       // the shared P tile is single-buffered, so P V of block j-1 must have finished before it is rewritten; the
       // TMEM P buffers alternate, so there only a rescale of O has to wait for it
       if (j > 0 && (!PT || rescale)) {

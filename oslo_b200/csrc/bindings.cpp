@@ -117,6 +117,65 @@ Tensor gemm(const Tensor& a, const Tensor& b, int64_t a_mn, int64_t b_mn, const 
   return d;
 }
 
+// LM-head projection whose epilogue does the cross-entropy work; the logits a @ b^T + bias are never stored.
+//   forward  (lse undefined): returns (rowmax, sumexp, target logit), fp32 [M] each
+//   backward (lse, scale given): returns ((softmax - onehot) * scale) [M, N] in the input dtype, written into `out`
+//   when given
+std::tuple<Tensor, Tensor, Tensor> gemm_ce_stats(const Tensor& a, const Tensor& b, int64_t b_mn, const optional<Tensor>& bias,
+                                                 const Tensor& labels, int64_t vocab_start) {
+  check_2d_operand(a, "a");
+  check_2d_operand(b, "b");
+  TORCH_CHECK(a.scalar_type() == b.scalar_type() && (a.scalar_type() == at::kBFloat16 || a.scalar_type() == at::kHalf),
+              "gemm_ce inputs must both be bf16 or fp16");
+  const int64_t M = a.size(0), K = a.size(1), N = b_mn ? b.size(1) : b.size(0);
+  TORCH_CHECK((b_mn ? b.size(0) : b.size(1)) == K, "contraction sizes differ");
+  TORCH_CHECK(labels.is_cuda() && labels.scalar_type() == at::kLong && labels.numel() == M && labels.is_contiguous(), "bad labels");
+  const bool has_bias = bias.has_value() && bias->defined();
+  if (has_bias) TORCH_CHECK(bias->numel() == N && bias->scalar_type() == a.scalar_type() && bias->is_contiguous(), "bad bias");
+  c10::cuda::CUDAGuard guard(a.device());
+  auto f32 = a.options().dtype(at::kFloat);
+  Tensor mx = at::empty({M}, f32), se = at::empty({M}, f32), tg = at::empty({M}, f32);
+  if (M == 0) return {mx, se, tg};
+  const int64_t blocks = (N + GEMM_CE_BLOCK - 1) / GEMM_CE_BLOCK;
+  Tensor stats = at::empty({blocks, M, 3}, f32);
+  auto& st = dev_state(a.get_device());
+  check_rc(oslo_gemm_ce_16bit(a.data_ptr(), b.data_ptr(), static_cast<int>(M), static_cast<int>(N), static_cast<int>(K),
+                              static_cast<int>(a.stride(0)), static_cast<int>(b.stride(0)), static_cast<int>(b_mn),
+                              has_bias ? bias->data_ptr() : nullptr,
+                              reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()), vocab_start, 0,
+                              stats.data_ptr<float>(), nullptr, nullptr, nullptr, 0, a.scalar_type() == at::kHalf ? 1 : 0,
+                              st.err.data_ptr<int>(), st.sms, cur_stream()), "gemm_ce_stats");
+  check_rc(oslo_ce_reduce_stats(stats.data_ptr<float>(), mx.data_ptr<float>(), se.data_ptr<float>(), tg.data_ptr<float>(),
+                                static_cast<int>(M), static_cast<int>(blocks), cur_stream()), "ce_reduce_stats");
+  return {mx, se, tg};
+}
+Tensor gemm_ce_grad(const Tensor& a, const Tensor& b, int64_t b_mn, const optional<Tensor>& bias, const Tensor& labels,
+                    int64_t vocab_start, const Tensor& lse, const Tensor& scale) {
+  check_2d_operand(a, "a");
+  check_2d_operand(b, "b");
+  TORCH_CHECK(a.scalar_type() == b.scalar_type() && (a.scalar_type() == at::kBFloat16 || a.scalar_type() == at::kHalf),
+              "gemm_ce inputs must both be bf16 or fp16");
+  const int64_t M = a.size(0), K = a.size(1), N = b_mn ? b.size(1) : b.size(0);
+  TORCH_CHECK((b_mn ? b.size(0) : b.size(1)) == K, "contraction sizes differ");
+  TORCH_CHECK(labels.is_cuda() && labels.scalar_type() == at::kLong && labels.numel() == M && labels.is_contiguous(), "bad labels");
+  TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.numel() == M && lse.is_contiguous() &&
+              scale.scalar_type() == at::kFloat && scale.numel() == M && scale.is_contiguous(), "lse / scale must be fp32 [M]");
+  const bool has_bias = bias.has_value() && bias->defined();
+  if (has_bias) TORCH_CHECK(bias->numel() == N && bias->scalar_type() == a.scalar_type() && bias->is_contiguous(), "bad bias");
+  c10::cuda::CUDAGuard guard(a.device());
+  Tensor d = at::empty({M, N}, a.options());
+  if (M == 0) return d;
+  auto& st = dev_state(a.get_device());
+  check_rc(oslo_gemm_ce_16bit(a.data_ptr(), b.data_ptr(), static_cast<int>(M), static_cast<int>(N), static_cast<int>(K),
+                              static_cast<int>(a.stride(0)), static_cast<int>(b.stride(0)), static_cast<int>(b_mn),
+                              has_bias ? bias->data_ptr() : nullptr,
+                              reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()), vocab_start, 1, nullptr,
+                              lse.data_ptr<float>(), scale.data_ptr<float>(), d.data_ptr(), static_cast<int>(d.stride(0)),
+                              a.scalar_type() == at::kHalf ? 1 : 0, st.err.data_ptr<int>(), st.sms, cur_stream()),
+           "gemm_ce_grad");
+  return d;
+}
+
 // y = act(a @ b^T + bias) for few rows (decode steps): split-K GEMM into fp32 planes, then one finalisation
 // kernel that sums them in a fixed order. Falls back to the ordinary GEMM when splitting the k range gains nothing.
 // `gelu_from`: -1 = no activation, c >= 0 = tanh-GeLU on output columns >= c (0 = all of them), which lets one GEMM
@@ -346,7 +405,8 @@ Tensor ngram_ban_(const Tensor& tokens, Tensor lprobs, int64_t n) {
   c10::cuda::CUDAGuard guard(lprobs.device());
   check_rc(oslo_ngram_ban(reinterpret_cast<const long long*>(tokens.data_ptr<int64_t>()), lprobs.data_ptr<float>(),
                           static_cast<int>(tokens.size(0)), static_cast<int>(tokens.size(1)),
-                          static_cast<int>(lprobs.size(1)), static_cast<int>(n), cur_stream()), "ngram_ban");
+                          static_cast<int>(lprobs.size(1)), static_cast<int>(n),
+                          dev_state(lprobs.get_device()).err.data_ptr<int>(), cur_stream()), "ngram_ban");
   return lprobs;
 }
 
@@ -430,7 +490,8 @@ Tensor decode_attn(const Tensor& q, const Tensor& kc, const Tensor& vc, const Te
   Tensor o = at::empty_like(q);
   check_rc(oslo_decode_attn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), lengths.data_ptr<int>(),
                             ws.data_ptr<float>(), B, H, T, D, splits, static_cast<float>(scale),
-                            static_cast<int>(window), dt_code(q), cur_stream(2)), "decode_attn");
+                            static_cast<int>(window), dt_code(q), dev_state(q.get_device()).err.data_ptr<int>(),
+                            cur_stream(2)), "decode_attn");
   return o;
 }
 
@@ -502,6 +563,22 @@ void allreduce_symm(int64_t peer_ptrs_dev, int64_t mc_ptr, int64_t signal_ptrs_d
                                st.err.data_ptr<int>(), cur_stream()), "allreduce_symm");
 }
 
+// (max, sum exp, label logit) per row combined over the ranks of a tensor-parallel group, in place
+void ce_combine(Tensor mx, Tensor se, Tensor tg, int64_t peer_ptrs_dev, int64_t signal_ptrs_dev, Tensor counters,
+                int64_t cap, int64_t rank, int64_t world) {
+  TORCH_CHECK(mx.is_cuda() && mx.scalar_type() == at::kFloat && mx.is_contiguous() && se.is_contiguous() &&
+                  tg.is_contiguous() && se.scalar_type() == at::kFloat && tg.scalar_type() == at::kFloat &&
+                  se.numel() == mx.numel() && tg.numel() == mx.numel(), "ce_combine: fp32 contiguous vectors of one length");
+  c10::cuda::CUDAGuard guard(mx.device());
+  auto& st = dev_state(mx.get_device());
+  check_rc(oslo_ce_combine(mx.data_ptr<float>(), se.data_ptr<float>(), tg.data_ptr<float>(), mx.data_ptr<float>(),
+                           se.data_ptr<float>(), tg.data_ptr<float>(), reinterpret_cast<void* const*>(peer_ptrs_dev),
+                           reinterpret_cast<uint32_t* const*>(signal_ptrs_dev),
+                           reinterpret_cast<uint32_t*>(counters.data_ptr<int>()), static_cast<int>(mx.numel()),
+                           static_cast<int>(cap), static_cast<int>(rank), static_cast<int>(world),
+                           st.err.data_ptr<int>(), cur_stream()), "ce_combine");
+}
+
 // One bucket of the data-parallel gradient reduce-scatter / parameter all-gather on a symmetric flat buffer.
 // `like` names the device and (reduce-scatter) the 16-bit dtype; the buffer itself is given by its address tables.
 void dp_reduce_scatter(const Tensor& like, int64_t peer_ptrs_dev, int64_t mc_ptr, int64_t signal_ptrs_dev, int64_t lo,
@@ -566,7 +643,8 @@ Tensor rotary_append(const Tensor& q, const Tensor& k, const Tensor& v, Tensor k
                               q_out.data_ptr(), kc.data_ptr(), vc.data_ptr(), lengths.data_ptr<int>(),
                               reinterpret_cast<const long long*>(write_index.data_ptr<int64_t>()), static_cast<int>(B),
                               static_cast<int>(H), static_cast<int>(D), static_cast<int>(T), static_cast<int>(rotary_dim),
-                              static_cast<float>(base), dt_code(q), cur_stream()), "rotary_append");
+                              static_cast<float>(base), dt_code(q), dev_state(q.get_device()).err.data_ptr<int>(),
+                              cur_stream()), "rotary_append");
   return q_out;
 }
 
@@ -625,6 +703,8 @@ TORCH_LIBRARY(oslo_b200, m) {
   m.def("error_word(Tensor like) -> Tensor");
   m.def("launch_count() -> int", &launch_count);
   m.def("gemm(Tensor a, Tensor b, int a_mn, int b_mn, Tensor? bias, Tensor? aux, Tensor(a!)? out, Tensor(b!)? aux_out, int flags, float alpha) -> Tensor");
+  m.def("gemm_ce_stats(Tensor a, Tensor b, int b_mn, Tensor? bias, Tensor labels, int vocab_start) -> (Tensor, Tensor, Tensor)");
+  m.def("gemm_ce_grad(Tensor a, Tensor b, int b_mn, Tensor? bias, Tensor labels, int vocab_start, Tensor lse, Tensor scale) -> Tensor");
   m.def("gemm_small_m(Tensor a, Tensor b, int b_mn, Tensor? bias, int gelu_from) -> Tensor");
   m.def("layernorm_fwd(Tensor x, Tensor w, Tensor? b, float eps) -> (Tensor, Tensor, Tensor)");
   m.def("layernorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor mean, Tensor rstd) -> (Tensor, Tensor, Tensor)");
@@ -651,6 +731,7 @@ TORCH_LIBRARY(oslo_b200, m) {
   m.def("vocab_embed(Tensor ids, Tensor weight, int lo, int hi, int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(a!) counters, int half_bytes, int rank, int world, bool use_multimem) -> Tensor");
   m.def("wait_probe(Tensor flag, int target, float limit_ms) -> Tensor");
   m.def("allreduce_oneshot(Tensor(a!) x, int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(b!) counters, int stage_off, int half_bytes, int rank, int world, bool use_multimem) -> ()");
+  m.def("ce_combine(Tensor(a!) mx, Tensor(b!) se, Tensor(c!) tg, int peer_ptrs_dev, int signal_ptrs_dev, Tensor(d!) counters, int cap, int rank, int world) -> ()");
   m.def("dp_reduce_scatter(Tensor like, int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, int lo, int hi, int shard, int rank, int world, bool use_multimem) -> ()");
   m.def("dp_all_gather(Tensor like, int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, int lo, int hi, int shard, int rank, int world, bool use_multimem) -> ()");
   m.def("allreduce_symm(int peer_ptrs_dev, int mc_ptr, int signal_ptrs_dev, Tensor(a!) out, int numel, int rank, int world, bool use_multimem) -> ()");
@@ -660,6 +741,8 @@ TORCH_LIBRARY_IMPL(oslo_b200, CUDA, m) {
   m.impl("error_word", &error_word);
   m.impl("gemm", &gemm);
   m.impl("gemm_small_m", &gemm_small_m);
+  m.impl("gemm_ce_stats", &gemm_ce_stats);
+  m.impl("gemm_ce_grad", &gemm_ce_grad);
   m.impl("layernorm_fwd", &layernorm_fwd);
   m.impl("layernorm_bwd", &layernorm_bwd);
   m.impl("bias_gelu_fwd", &bias_gelu_fwd);
@@ -686,6 +769,7 @@ TORCH_LIBRARY_IMPL(oslo_b200, CUDA, m) {
   m.impl("wait_probe", &wait_probe);
   m.impl("allreduce_oneshot", &allreduce_oneshot);
   m.impl("allreduce_symm", &allreduce_symm);
+  m.impl("ce_combine", &ce_combine);
   m.impl("dp_reduce_scatter", &dp_reduce_scatter);
   m.impl("dp_all_gather", &dp_all_gather);
 }

@@ -358,7 +358,58 @@ __global__ void __launch_bounds__(512) dp_all_gather_kernel(void* const* peer_pt
   block_barrier_all_ranks(signal_ptrs, rank, world, gridDim.x * world, err);
 }
 
+// Vocabulary-parallel cross-entropy: every rank holds (max, sum exp(x - max), label logit) of its vocabulary shard for
+// n rows; all ranks need the combination over the shards. One kernel, one meeting: copy the three vectors into this
+// rank's staging half in symmetric memory, meet, read every rank's triple with plain peer loads and combine in a
+// fixed rank order (so every rank computes bit-identical results): gm = max_r m_r, s = sum_r s_r exp(m_r - gm),
+// t = sum_r t_r. `cap` floats per vector per half; the launcher always starts the same grid, so the per-block
+// half parities stay equal and a half is rewritten only after every rank has finished the call in between.
+__global__ void __launch_bounds__(256) ce_combine_kernel(const float* __restrict__ mx, const float* __restrict__ se,
+                                                         const float* __restrict__ tg, float* __restrict__ out_mx,
+                                                         float* __restrict__ out_se, float* __restrict__ out_tg,
+                                                         void* const* peer_ptrs, uint32_t* const* signal_ptrs,
+                                                         uint32_t* counters, int n, int cap, int rank, int world,
+                                                         int* err) {
+  const uint32_t parity = counters[blockIdx.x] & 1u;
+  const size_t base = static_cast<size_t>(parity) * 3 * cap;
+  float* mine = reinterpret_cast<float*>(peer_ptrs[rank]) + base;
+  const int tid = blockIdx.x * blockDim.x + threadIdx.x, nthreads = gridDim.x * blockDim.x;
+  for (int i = tid; i < n; i += nthreads) {
+    mine[i] = mx[i];
+    mine[cap + i] = se[i];
+    mine[2 * cap + i] = tg[i];
+  }
+  if (!block_barrier_all_ranks(signal_ptrs, rank, world, 0, err)) return;
+  for (int i = tid; i < n; i += nthreads) {
+    float gm = -3.0e38f;
+    for (int r = 0; r < world; ++r) gm = fmaxf(gm, (reinterpret_cast<const float*>(peer_ptrs[r]) + base)[i]);
+    float s = 0.f, t = 0.f;
+    for (int r = 0; r < world; ++r) {
+      const float* pr = reinterpret_cast<const float*>(peer_ptrs[r]) + base;
+      s += pr[cap + i] * __expf(pr[i] - gm);
+      t += pr[2 * cap + i];
+    }
+    out_mx[i] = gm;
+    out_se[i] = s;
+    out_tg[i] = t;
+  }
+  if (threadIdx.x == 0) counters[blockIdx.x] += 1;
+}
+
 }  // namespace oslo
+
+// mx / se / tg and the outputs: fp32 [n] (outputs may alias the inputs). The symmetric buffer holds 2 x 3 x cap floats;
+// counters: device uint32[>= 8], zeroed once.
+extern "C" int oslo_ce_combine(const float* mx, const float* se, const float* tg, float* out_mx, float* out_se,
+                               float* out_tg, void* const* peer_ptrs_dev, uint32_t* const* signal_ptrs_dev,
+                               uint32_t* counters, int n, int cap, int rank, int world, int* err_word,
+                               cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (n > cap || world > 16 || rank < 0 || rank >= world) return -3;
+  oslo::ce_combine_kernel<<<8, 256, 0, stream>>>(mx, se, tg, out_mx, out_se, out_tg, peer_ptrs_dev, signal_ptrs_dev,
+                                                 counters, n, cap, rank, world, err_word);
+  return static_cast<int>(cudaGetLastError());
+}
 
 // Bucket [lo, hi) (element indices, multiples of 8) of a symmetric flat buffer of 16-bit elements whose rank r owns
 // elements [r * shard, (r + 1) * shard). reduce_scatter: every rank's own part of the bucket becomes the sum over all

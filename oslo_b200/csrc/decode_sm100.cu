@@ -17,6 +17,7 @@
 #include <math_constants.h>
 
 #include "oslo_kernels.h"
+#include "ptx.cuh"
 
 namespace oslo {
 
@@ -144,10 +145,13 @@ __global__ void rotary_append_kernel(const T* __restrict__ q, const T* __restric
                                      long long ldq, long long ldk, long long ldv, T* __restrict__ q_out,
                                      T* __restrict__ kc, T* __restrict__ vc, const int* __restrict__ lengths,
                                      const long long* __restrict__ write_index, int H, int D, int Tmax, int rotary_dim,
-                                     float log2_base) {
+                                     float log2_base, int* err) {
   const int b = blockIdx.y, h = blockIdx.x;
   const long long wi = write_index[0];
-  if (wi < 0 || wi >= Tmax) return;   // never write outside the cache
+  if (wi < 0 || wi >= Tmax) {   // never write outside the cache
+    OSLO_REPORT_BOUNDS(err);
+    return;
+  }
   const float pos = static_cast<float>(lengths[b]);
   const T* qp = q + b * ldq + static_cast<long long>(h) * D;
   const T* kp = k + b * ldk + static_cast<long long>(h) * D;
@@ -213,7 +217,7 @@ extern "C" int oslo_gemv_rows(const void* x1, int ld1, int K1, const void* x2, i
 extern "C" int oslo_rotary_append(const void* q, const void* k, const void* v, long long ldq, long long ldk,
                                   long long ldv, void* q_out, void* kc, void* vc, const int* lengths,
                                   const long long* write_index, int B, int H, int D, int Tmax, int rotary_dim, float base,
-                                  int dtype, cudaStream_t stream) {
+                                  int dtype, int* err_word, cudaStream_t stream) {
   using namespace oslo;
   if (B <= 0 || H <= 0) return 0;
   if (D % 2 || rotary_dim % 2 || rotary_dim > D) return -1;
@@ -222,11 +226,11 @@ extern "C" int oslo_rotary_append(const void* q, const void* k, const void* v, l
   if (dtype == OSLO_DT_BF16)
     rotary_append_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, ldq, ldk, ldv, (__nv_bfloat16*)q_out,
-        (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, lengths, write_index, H, D, Tmax, rotary_dim, log2f(base));
+        (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, lengths, write_index, H, D, Tmax, rotary_dim, log2f(base), err_word);
   else if (dtype == OSLO_DT_FP16)
     rotary_append_kernel<__half><<<grid, threads, 0, stream>>>((const __half*)q, (const __half*)k, (const __half*)v, ldq,
                                                                ldk, ldv, (__half*)q_out, (__half*)kc, (__half*)vc, lengths,
-                                                               write_index, H, D, Tmax, rotary_dim, log2f(base));
+                                                               write_index, H, D, Tmax, rotary_dim, log2f(base), err_word);
   else
     return -2;
   return static_cast<int>(cudaGetLastError());

@@ -6,6 +6,7 @@
 #include <math_constants.h>
 
 #include "oslo_kernels.h"
+#include "ptx.cuh"
 
 namespace oslo {
 
@@ -530,6 +531,26 @@ __global__ void __launch_bounds__(CE_THREADS) ce_grad_kernel(T* __restrict__ log
   }
 }
 
+// (max, sum exp, label logit) of a row from its per-128-column-block records [blocks, rows, 3] (written by the LM-head
+// GEMM's cross-entropy epilogue): one thread per row, fixed order, so the result does not depend on the tile schedule
+__global__ void ce_reduce_stats_kernel(const float* __restrict__ stats, float* __restrict__ rowmax,
+                                       float* __restrict__ sumexp, float* __restrict__ target, int rows, int blocks) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  float m = -3.0e38f, s = 0.f, t = 0.f;
+  for (int b = 0; b < blocks; ++b) {
+    const float* rec = stats + (static_cast<size_t>(b) * rows + row) * 3;
+    const float bm = rec[0], bs = rec[1];
+    const float nm = fmaxf(m, bm);
+    s = s * __expf(m - nm) + bs * __expf(bm - nm);
+    m = nm;
+    t += rec[2];
+  }
+  rowmax[row] = m;
+  sumexp[row] = s;
+  target[row] = t;
+}
+
 // ---------------------------------------------------------------------- AdamW / norms
 __device__ __forceinline__ void adam_update(float& p, float& m, float& v, float g, float lr, float beta1, float beta2,
                                             float eps, float decay, float inv_bc1, float inv_bc2) {
@@ -635,7 +656,7 @@ __global__ void splitk_finalize_kernel(const float* __restrict__ ws, const T* __
 // thread `c` compares the (n-1)-gram starting at c with the last (n-1) tokens of the row; on a match the
 // token that followed it is banned. No shared memory is used, so the row length is unbounded.
 __global__ void ngram_ban_kernel(const long long* __restrict__ tokens, float* __restrict__ lprobs, int len, int vocab,
-                                 int n) {
+                                 int n, int* err) {
   const int row = blockIdx.x;
   const long long* t = tokens + static_cast<size_t>(row) * len;
   const int starts = len - n + 1;  // candidate n-grams fully inside the row
@@ -647,6 +668,7 @@ __global__ void ngram_ban_kernel(const long long* __restrict__ tokens, float* __
     if (match) {
       const long long banned = t[c + n - 1];
       if (banned >= 0 && banned < vocab) lprobs[static_cast<size_t>(row) * vocab + banned] = -CUDART_INF_F;
+      else OSLO_REPORT_BOUNDS(err);   // a generated token outside the vocabulary: nothing to ban, skipped
     }
   }
 }
@@ -852,10 +874,17 @@ extern "C" int oslo_sumsq(const void* x, float* out, long long n, int dtype, cud
   RET_LAST();
 }
 
+extern "C" int oslo_ce_reduce_stats(const float* stats, float* rowmax, float* sumexp, float* target, int rows, int blocks,
+                                    cudaStream_t st) {
+  if (rows <= 0 || blocks <= 0) return 0;
+  ce_reduce_stats_kernel<<<(rows + 127) / 128, 128, 0, st>>>(stats, rowmax, sumexp, target, rows, blocks);
+  RET_LAST();
+}
+
 extern "C" int oslo_ngram_ban(const long long* tokens, float* lprobs, int rows, int len, int vocab, int n,
-                              cudaStream_t st) {
+                              int* err_word, cudaStream_t st) {
   if (rows == 0 || n <= 0 || len + 1 < n) return 0;
-  ngram_ban_kernel<<<rows, 256, 0, st>>>(tokens, lprobs, len, vocab, n);
+  ngram_ban_kernel<<<rows, 256, 0, st>>>(tokens, lprobs, len, vocab, n, err_word);
   RET_LAST();
 }
 

@@ -52,6 +52,12 @@ struct GemmParams {
   int group_m = 8;      // row blocks per column sweep of the tile raster
   int split_k = 1;      // > 1: every tile's k range is cut into this many work items; slice s writes its fp32 partial
                         // result to plane s of D ([split_k, M, ldd] fp32); other epilogue flags are ignored
+  // cross-entropy epilogues (GEMM_FLAG_CE_STATS / GEMM_FLAG_CE_GRAD)
+  const long long* ce_labels = nullptr;   // [M] global vocabulary ids
+  long long ce_vocab_start = 0;           // id of this matrix's column 0
+  float* ce_stats = nullptr;              // [ceil(N / 128), M, 3]
+  const float* ce_lse = nullptr;          // [M]
+  const float* ce_scale = nullptr;        // [M]
   CommParams comm;
 };
 
@@ -190,6 +196,69 @@ __device__ __forceinline__ int tile_owner(const CommParams& c, int idx, int tm, 
   return idx % c.world;
 }
 
+// Cross-entropy statistics of one row, accumulated over the 32-column chunks of a 128-column block in the epilogue:
+// running max, sum of exp(x - max) and the logit of the row's label when it lies in the block (x = acc + bias).
+struct CeAcc {
+  float m, s, t;
+};
+__device__ __forceinline__ void ce_reset(CeAcc& a) { a.m = -3.0e38f; a.s = 0.f; a.t = 0.f; }
+__device__ __forceinline__ void ce_accumulate(const GemmParams& p, int col0, const uint32_t (&r)[32], bool fp16,
+                                              long long label_local, CeAcc& a) {
+  float v[32];
+  const int ncols = min(32, p.N - col0);
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+  if (p.flags & GEMM_FLAG_BIAS) {
+    if (ncols == 32) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) {
+        float b[8];
+        unpack8(*reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias) + col0 + i), b, fp16);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i + j] += b[j];
+      }
+    } else {
+      _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) v[i] += ld_half_as_float(p.bias, col0 + i, fp16);
+    }
+  }
+  // the loss is defined on the 16-bit logits a separate GEMM would have written: round as that store would
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    const uint32_t pk = pack2(v[i], v[i + 1], fp16);
+    if (fp16) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pk));
+      v[i] = f.x; v[i + 1] = f.y;
+    } else {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk));
+      v[i] = f.x; v[i + 1] = f.y;
+    }
+  }
+  float mx = a.m;
+#pragma unroll
+  for (int i = 0; i < 32; ++i)
+    if (i < ncols) mx = fmaxf(mx, v[i]);
+  float s = a.s * exp2f((a.m - mx) * 1.4426950408889634f);
+#pragma unroll
+  for (int i = 0; i < 32; ++i)
+    if (i < ncols) s += exp2f((v[i] - mx) * 1.4426950408889634f);
+  a.m = mx;
+  a.s = s;
+  const long long d = label_local - col0;
+  if (d >= 0 && d < ncols) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i == d) a.t = v[i];
+  }
+}
+// one record per (128-column block, row); written after the block's last chunk that holds valid columns
+__device__ __forceinline__ void ce_flush_if_block_ends(const GemmParams& p, int row, int col0, CeAcc& a) {
+  const bool last_chunk_of_block = ((col0 + 32) % GEMM_CE_BLOCK) == 0 || col0 + 32 >= p.N;
+  if (!last_chunk_of_block) return;
+  float* rec = p.ce_stats + (static_cast<size_t>(col0 / GEMM_CE_BLOCK) * p.M + row) * 3;
+  rec[0] = a.m; rec[1] = a.s; rec[2] = a.t;
+  ce_reset(a);
+}
+
 // Epilogue of one [1 row x 32 columns] accumulator chunk held by a thread: alpha, bias, GeLU (+ saved
 // pre-activation), dGeLU, residual, accumulate, conversion and the store. `row` < M and `col0` < N are the
 // caller's responsibility.
@@ -223,6 +292,25 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int row, int
         }
       } else {
         _Pragma("unroll") for (int i = 0; i < 32; ++i) if (i < ncols) v[i] += ld_half_as_float(p.bias, col0 + i, fp16);
+      }
+    }
+    if (p.flags & GEMM_FLAG_CE_GRAD) {
+      // (softmax - onehot) * scale of the recomputed logits (rounded to the 16-bit value the forward pass used)
+      const float l = p.ce_lse[row], sc = p.ce_scale[row];
+      const long long d = p.ce_labels[row] - p.ce_vocab_start - col0;
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        const uint32_t pk = pack2(v[i], v[i + 1], fp16);
+        float2 f;
+        if (fp16) f = __half22float2(*reinterpret_cast<const __half2*>(&pk));
+        else f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk));
+        v[i] = exp2f((f.x - l) * 1.4426950408889634f);
+        v[i + 1] = exp2f((f.y - l) * 1.4426950408889634f);
+      }
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        if (i == d) v[i] -= 1.f;
+        v[i] *= sc;
       }
     }
     if (p.flags & GEMM_FLAG_SAVE_PREACT) {
@@ -529,6 +617,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       const int row = tm * BM + quad * 32 + lane;
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
+      const bool ce_stats = !COMM && (p.flags & GEMM_FLAG_CE_STATS);
+      CeAcc ce;
+      ce_reset(ce);
+      const long long label_local = (ce_stats && row_ok) ? p.ce_labels[row] - p.ce_vocab_start : -1;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
@@ -536,7 +628,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         tmem_wait_ld();
         const int col0 = tn * BN + c0;
         if (!row_ok || col0 >= p.N) continue;
-        epilogue_chunk(p, row, col0, r, fp16, out_f32, kslice);
+        if (ce_stats) {
+          ce_accumulate(p, col0, r, fp16, label_local, ce);
+          ce_flush_if_block_ends(p, row, col0, ce);
+        } else {
+          epilogue_chunk(p, row, col0, r, fp16, out_f32, kslice);
+        }
       }
       tc_fence_before();
       __syncwarp();

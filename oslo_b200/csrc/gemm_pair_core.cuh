@@ -171,6 +171,10 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       const int row = tm * PAIR_TILE + static_cast<int>(rank) * BM + quad * 32 + lane;
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * PAIR_TILE;
+      const bool ce_stats = (p.flags & GEMM_FLAG_CE_STATS) != 0;
+      CeAcc ce;
+      ce_reset(ce);
+      const long long label_local = (ce_stats && row_ok) ? p.ce_labels[row] - p.ce_vocab_start : -1;
 #pragma unroll 1
       for (int c0 = 0; c0 < PAIR_TILE; c0 += 32) {
         uint32_t r[32];
@@ -178,7 +182,12 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
         tmem_wait_ld();
         const int col0 = tn * PAIR_TILE + c0;
         if (!row_ok || col0 >= p.N) continue;
-        epilogue_chunk(p, row, col0, r, fp16, out_f32);
+        if (ce_stats) {
+          ce_accumulate(p, col0, r, fp16, label_local, ce);
+          ce_flush_if_block_ends(p, row, col0, ce);
+        } else {
+          epilogue_chunk(p, row, col0, r, fp16, out_f32);
+        }
       }
       tc_fence_before();
       __syncwarp();

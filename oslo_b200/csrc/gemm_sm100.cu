@@ -144,6 +144,9 @@ static bool pair_enabled() {
   return on;
 }
 
+// Tile shape selection, tensor maps and launch for a filled-in GemmParams (M, N, K, majors, flags, epilogue operands)
+static int dispatch_gemm(const void* A, const void* B, int lda, int ldb, GemmParams& p, int num_sms, cudaStream_t stream);
+
 }  // namespace oslo
 
 extern "C" int oslo_gemm_16bit(const void* A, const void* B, void* D, int M, int N, int K, int lda, int ldb, int ldd,
@@ -152,6 +155,35 @@ extern "C" int oslo_gemm_16bit(const void* A, const void* B, void* D, int M, int
                                cudaStream_t stream) {
   using namespace oslo;
   if (M <= 0 || N <= 0 || K <= 0) return -1;
+  if (flags & (GEMM_FLAG_CE_STATS | GEMM_FLAG_CE_GRAD)) return -7;   // those epilogues come through oslo_gemm_ce_16bit
+  GemmParams p;
+  p.D = D; p.bias = bias; p.aux = aux; p.aux_out = aux_out;
+  p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ld_aux = ld_aux; p.ld_aux_out = ld_aux_out;
+  p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major; p.flags = flags; p.alpha = alpha; p.err = err_word;
+  p.comm = CommParams{};
+  return dispatch_gemm(A, B, lda, ldb, p, num_sms, stream);
+}
+
+extern "C" int oslo_gemm_ce_16bit(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int b_mn_major,
+                                  const void* bias, const long long* labels, long long vocab_start, int mode,
+                                  float* stats, const float* lse, const float* scale, void* D, int ldd, int fp16,
+                                  int* err_word, int num_sms, cudaStream_t stream) {
+  using namespace oslo;
+  if (M <= 0 || N <= 0 || K <= 0 || labels == nullptr) return -1;
+  if (mode == 0 ? stats == nullptr : (lse == nullptr || scale == nullptr || D == nullptr)) return -1;
+  GemmParams p;
+  p.D = D; p.bias = bias; p.aux = nullptr; p.aux_out = nullptr;
+  p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ld_aux = 0; p.ld_aux_out = 0;
+  p.a_mn_major = 0; p.b_mn_major = b_mn_major; p.alpha = 1.f; p.err = err_word;
+  p.flags = (mode == 0 ? GEMM_FLAG_CE_STATS : GEMM_FLAG_CE_GRAD) | (bias ? GEMM_FLAG_BIAS : 0) | (fp16 ? GEMM_FLAG_FP16 : 0);
+  p.ce_labels = labels; p.ce_vocab_start = vocab_start; p.ce_stats = stats; p.ce_lse = lse; p.ce_scale = scale;
+  p.comm = CommParams{};
+  return dispatch_gemm(A, B, lda, ldb, p, num_sms, stream);
+}
+
+namespace oslo {
+static int dispatch_gemm(const void* A, const void* B, int lda, int ldb, GemmParams& p, int num_sms, cudaStream_t stream) {
+  const int M = p.M, N = p.N, K = p.K, a_mn_major = p.a_mn_major, b_mn_major = p.b_mn_major, flags = p.flags;
   // the tensor-map encoder is a driver-API call and needs the primary context bound to THIS thread; the
   // autograd engine's worker threads may not have made a runtime call yet
   static thread_local bool ctx_bound = false;
@@ -171,11 +203,6 @@ extern "C" int oslo_gemm_16bit(const void* A, const void* B, void* D, int M, int
   if (!b_mn_major) rc = make_tma_2d_16bit(&tb, B, K, N, ldb, bn, fp16);
   else rc = make_tma_2d_16bit(&tb, B, N, K, ldb, 64, fp16);
   if (rc) return rc - 1000;  // -(2000 + CUresult): encoding the B map failed
-  GemmParams p;
-  p.D = D; p.bias = bias; p.aux = aux; p.aux_out = aux_out;
-  p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ld_aux = ld_aux; p.ld_aux_out = ld_aux_out;
-  p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major; p.flags = flags; p.alpha = alpha; p.err = err_word;
-  p.comm = CommParams{};
   if (pair) {
     static const int stages = [] { const char* e = getenv("OSLO_B200_PAIR_STAGES"); return e ? atoi(e) : PAIR_STAGES; }();
     if (stages == 7) return launch_pair<7>(ta, tb, p, num_sms, stream);
@@ -184,6 +211,7 @@ extern "C" int oslo_gemm_16bit(const void* A, const void* B, void* D, int M, int
   if (bn == 256) return launch<256, 4>(ta, tb, p, num_sms, stream);
   return launch<128, 6>(ta, tb, p, num_sms, stream);
 }
+}  // namespace oslo
 
 // how many k slices a few-row GEMM should use so that about two work items exist per SM (1 = do not split)
 extern "C" int oslo_gemm_split_k_for(int M, int N, int K, int num_sms) {

@@ -13,6 +13,10 @@
 #define GEMM_FLAG_OUT_FP32 32     // D is fp32 (default: same 16-bit type as the inputs)
 #define GEMM_FLAG_ACCUMULATE 64   // D += result
 #define GEMM_FLAG_FP16 128        // inputs are fp16 (default bf16)
+#define GEMM_FLAG_CE_STATS 256    // LM head + cross-entropy, forward: no D; per (row, 128-column block) the epilogue emits
+                                  // (max, sum exp(x - max), logit of the row's label if it lies in the block)
+#define GEMM_FLAG_CE_GRAD 512     // LM head + cross-entropy, backward: D = (exp(x - lse[row]) - [col == label]) * scale[row]
+#define GEMM_CE_BLOCK 128         // columns per statistics record
 
 #define OSLO_DT_BF16 0
 #define OSLO_DT_FP16 1
@@ -25,6 +29,18 @@ extern "C" {
 int oslo_gemm_16bit(const void* A, const void* B, void* D, int M, int N, int K, int lda, int ldb, int ldd,
                     int a_mn_major, int b_mn_major, const void* bias, const void* aux, int ld_aux, void* aux_out,
                     int ld_aux_out, int flags, float alpha, int* err_word, int num_sms, cudaStream_t stream);
+
+// LM-head product with the cross-entropy pieces in its epilogue (x = A B^T + bias, never written as logits):
+//   mode 0 (GEMM_FLAG_CE_STATS): stats [ceil(N / 128), M, 3] fp32 records (max, sum exp, label logit or 0)
+//   mode 1 (GEMM_FLAG_CE_GRAD):  D [M, N] (input dtype) = (softmax - onehot) * scale, from lse / scale fp32 [M]
+// labels int64 [M] are global vocabulary ids; this rank's columns are ids vocab_start .. vocab_start + N - 1
+int oslo_gemm_ce_16bit(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int b_mn_major,
+                       const void* bias, const long long* labels, long long vocab_start, int mode, float* stats,
+                       const float* lse, const float* scale, void* D, int ldd, int fp16, int* err_word, int num_sms,
+                       cudaStream_t stream);
+// (max, sum exp, label logit) per row from the per-block records of mode 0
+int oslo_ce_reduce_stats(const float* stats, float* rowmax, float* sumexp, float* target, int rows, int blocks,
+                         cudaStream_t stream);
 
 // few-row GEMM for decode steps (M <= 128): k range cut into `split_k` slices, slice s writes its fp32 partial sums
 // to plane s of D [split_k, M, N]; oslo_gemm_split_k_for suggests the slice count (1 = use oslo_gemm_16bit)
@@ -88,7 +104,7 @@ int oslo_adam(float* p, const void* g, float* m, float* v, void* p_lp, long long
 int oslo_sumsq(const void* x, float* out, long long n, int dtype, cudaStream_t stream);
 
 // n-gram repeat blocking: lprobs[row, tok] = -inf for tokens that would complete a seen n-gram
-int oslo_ngram_ban(const long long* tokens, float* lprobs, int rows, int len, int vocab, int n,
+int oslo_ngram_ban(const long long* tokens, float* lprobs, int rows, int len, int vocab, int n, int* err_word,
                    cudaStream_t stream);
 
 // flash attention. q/k/v/o: element strides for (batch, head, seq); last dim contiguous
@@ -118,7 +134,8 @@ int oslo_flash_bwd_sm100(const void* q, const void* k, const void* v, const void
                          int window, int dtype, int* err_word, cudaStream_t stream);
 // single-query attention over a static cache [B, H, T, D]; lengths int32 [B]
 int oslo_decode_attn(const void* q, const void* kc, const void* vc, void* o, const int* lengths, float* ws, int B,
-                     int H, int T, int D, int splits, float scale, int window, int dtype, cudaStream_t stream);
+                     int H, int T, int D, int splits, float scale, int window, int dtype, int* err_word,
+                     cudaStream_t stream);
 
 // GEMM fused with a tensor-parallel collective (fused_comm_gemm.cu); mode 1 = all-reduce (result left in the
 // symmetric staging matrix), 2 = reduce-scatter into out, 3 = all-gather of A then GEMM into out
@@ -145,6 +162,12 @@ int oslo_dp_all_gather(void* const* peer_ptrs_dev, void* mc_ptr, uint32_t* const
                        long long hi, long long shard, int rank, int world, int use_multimem, int* err_word,
                        cudaStream_t stream);
 
+// vocabulary-parallel cross-entropy: combine every rank's per-row (max, sum exp, label logit) over the group in one
+// kernel through a symmetric staging buffer of 2 x 3 x cap floats (comm.cu)
+int oslo_ce_combine(const float* mx, const float* se, const float* tg, float* out_mx, float* out_se, float* out_tg,
+                    void* const* peer_ptrs_dev, uint32_t* const* signal_ptrs_dev, uint32_t* counters, int n, int cap,
+                    int rank, int world, int* err_word, cudaStream_t stream);
+
 // decode-step kernels (decode_sm100.cu). gemv_rows: out[m, n] = act([x1 | x2][m, :] . W[n, :] + bias[n]) for M <= 4
 // rows, W [N, K1 + K2] K-major, tanh-GeLU on columns >= gelu_from (-1 = none); x2 may be null.
 // `res` [M, N] (row stride ldr) is added after the activation; bias and res may be null.
@@ -155,7 +178,7 @@ int oslo_gemv_rows(const void* x1, int ld1, int K1, const void* x2, int ld2, int
 // the rotary position of row b is lengths[b]
 int oslo_rotary_append(const void* q, const void* k, const void* v, long long ldq, long long ldk, long long ldv,
                        void* q_out, void* kc, void* vc, const int* lengths, const long long* write_index, int B, int H,
-                       int D, int Tmax, int rotary_dim, float base, int dtype, cudaStream_t stream);
+                       int D, int Tmax, int rotary_dim, float base, int dtype, int* err_word, cudaStream_t stream);
 
 // vocab-parallel embedding lookup + its collective in one kernel (comm.cu): the owner of a token's row stores it into
 // every rank's staging half of the symmetric buffer, one cross-rank barrier, copy-out

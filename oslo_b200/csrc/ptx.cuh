@@ -20,6 +20,21 @@ enum : int {
   ERR_BOUNDS = 6,
 };
 
+// Debug build (-DOSLO_DEBUG_BOUNDS, `python -m oslo_b200.build --debug-bounds` -> _C_bounds.so): an index that is
+// computed from DATA (a token id, a cache position, a sequence length) and falls outside its buffer is always skipped
+// or clamped - in every build, so nothing ever faults - and in the debug build it also records ERR_BOUNDS in the
+// per-device error word, so that the silent skip becomes visible to the host (`raise_if_device_error`).
+#ifdef OSLO_DEBUG_BOUNDS
+#define OSLO_REPORT_BOUNDS(err)                                  \
+  do {                                                           \
+    if ((err) != nullptr) atomicCAS((err), 0, oslo::ERR_BOUNDS); \
+  } while (0)
+#else
+#define OSLO_REPORT_BOUNDS(err) \
+  do {                          \
+  } while (0)
+#endif
+
 #ifndef OSLO_WAIT_LIMIT_NS
 #define OSLO_WAIT_LIMIT_NS 2000000000ull  // 2 s
 #endif

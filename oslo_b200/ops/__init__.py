@@ -20,7 +20,11 @@ _EXT_ERR: Optional[BaseException] = None
 
 
 def ext_path() -> str:
-    return os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "_C.so")
+    """``_C.so``, or with ``OSLO_B200_DEBUG_BOUNDS=1`` the debug build ``_C_bounds.so`` (``python -m oslo_b200.build
+    --debug-bounds``): the same kernels compiled with ``-DOSLO_DEBUG_BOUNDS``, which record ``ERR_BOUNDS`` in the device
+    error word whenever a data-dependent index (token id, cache position, sequence length) had to be skipped or clamped."""
+    name = "_C_bounds.so" if os.environ.get("OSLO_B200_DEBUG_BOUNDS", "0").lower() in ("1", "true", "yes", "on") else "_C.so"
+    return os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), name)
 
 
 def load_ext(required: bool = False):

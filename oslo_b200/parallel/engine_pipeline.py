@@ -19,6 +19,7 @@ stage, so plain autograd drives the whole chain.
 from __future__ import annotations
 
 import logging
+import os
 from typing import Any, Callable, Dict, Iterator, List, Optional
 
 import torch
@@ -179,6 +180,14 @@ class PipelineParallelEngine:
         self.p2p: Optional[P2PCommunicator] = None
         self._grad_hooks_cb: List[Callable[[], None]] = []
         self.on_last_backward: Optional[Callable[[bool], None]] = None
+        # Receives are posted one micro-batch ahead only after this many complete runs of the generator (per mode:
+        # training / no-grad). A receive that is posted early is a kernel that spins until its sender runs; during the
+        # first pass every kernel is launched for the first time, CUDA loads a kernel's module at its first launch, and
+        # that load can wait for all running kernels of the context - the spinning receive among them, whose sender may
+        # in turn be waiting (on the host, in NCCL's first-use connection set-up, or on the device) for this rank to get
+        # further. Without look-ahead every receive is posted exactly when its data is needed, which is acyclic.
+        self.prepost_after = int(os.environ.get("OSLO_B200_PP_PREPOST_AFTER", "1"))
+        self._runs = {True: 0, False: 0}
         self.zero_stage: Optional[int] = None  # of a DeepSpeed engine around this model; looked up at the first call
         self.profile = False                  # record CUDA events around every forward / backward (schedule_report)
         self._events: Dict[tuple, Dict[str, Any]] = {}
@@ -414,8 +423,10 @@ class PipelineParallelEngine:
         recv_buf: Dict[int, Any] = {}
         out_shapes: Dict[int, Any] = {}
 
-        def post_recv(j: int) -> None:
-            if self.first or j >= m or j in recv_buf:
+        lookahead = self._runs[train] >= self.prepost_after
+
+        def post_recv(j: int, ahead: bool = False) -> None:
+            if self.first or j >= m or j in recv_buf or (ahead and not lookahead):
                 return
             buf = self.p2p.alloc(self._hidden_shape(batches[j]), dtype, self.device)
             recv_buf[j] = (buf, self.p2p.recv([buf], self.stage - 1, "fwd"))
@@ -425,7 +436,7 @@ class PipelineParallelEngine:
             if not self.first:
                 post_recv(j)
                 hidden, works = recv_buf.pop(j)
-                post_recv(j + 1)                  # the next activation may arrive while this one is being used
+                post_recv(j + 1, ahead=True)      # the next activation may arrive while this one is being used
                 self.p2p.finish(works, [hidden])
                 if train:
                     hidden.requires_grad_(True)
@@ -454,6 +465,7 @@ class PipelineParallelEngine:
                 do_forward(j)
                 yield self._broadcast_output(outputs.pop(j))
             self._flush()
+            self._runs[False] += 1
             return
 
         warm = min(self.pp - 1 - self.stage, m)
@@ -467,7 +479,7 @@ class PipelineParallelEngine:
             do_forward(done)
             done += 1
         for i in range(m):
-            if not self.last and i in out_shapes:
+            if not self.last and i in out_shapes and lookahead:
                 # the gradient of micro-batch i is the next message from the stage below: post its receive before
                 # the forward that precedes backward i is enqueued, so it can land during that forward
                 self._post_recv_grad(i, *out_shapes.pop(i))
@@ -483,6 +495,7 @@ class PipelineParallelEngine:
                 self._mark("B", i, "end")         # no input hook on the first stage: backward i ends when the user returns
         self._flush()
         self._allreduce_tied_embedding()
+        self._runs[True] += 1
 
     def _organize_partial(self, kw: Dict[str, Any]):
         """Output object of a stage that has no head: same type as the last stage's, loss = proxy."""

@@ -164,7 +164,12 @@ class MPU:
             kwargs["timeout"] = datetime.timedelta(seconds=timeout_s)
         if backend == "nccl":
             torch.cuda.set_device(local_rank % max(torch.cuda.device_count(), 1))
-            kwargs["device_id"] = torch.device("cuda", torch.cuda.current_device())
+            if os.environ.get("OSLO_B200_NCCL_EAGER_INIT", "1") != "0":
+                # binds the device now and creates every group's communicator by splitting the world communicator
+                # (quick group creation). All point-to-point operations of such a group share the group's one
+                # communicator and stream, which is why the pipeline engine gives every (neighbour pair, direction) a
+                # group of its own.
+                kwargs["device_id"] = torch.device("cuda", torch.cuda.current_device())
         dist.init_process_group(backend=backend, rank=rank, world_size=world, **kwargs)
 
     def _new_group(self, ranks: Sequence[int]):

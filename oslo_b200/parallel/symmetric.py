@@ -125,6 +125,46 @@ class SymmetricFlat:
                                                  int(lo), int(hi), self.shard, self.rank, self.world, self._mm())
 
 
+class CeCombine:
+    """Symmetric staging (two halves of 3 x ``cap`` floats) for ``ce_combine_kernel``: the per-row cross-entropy
+    statistics of the vocabulary shards are combined over the tensor-parallel group in ONE kernel with one
+    cross-rank meeting, instead of a MAX and a SUM all-reduce."""
+
+    CAP = 1 << 16     # rows per call (a chunked LM head hands over a micro-batch's rows at most)
+
+    def __init__(self, group, device) -> None:
+        import torch.distributed._symmetric_memory as symm
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.buf = symm.empty(2 * 3 * self.CAP, dtype=torch.float32, device=device)
+        self.handle = symm.rendezvous(self.buf, group)
+        self.peer_ptrs_dev = int(self.handle.buffer_ptrs_dev)
+        self.signal_ptrs_dev = int(self.handle.signal_pad_ptrs_dev)
+        self.counters = torch.zeros(8, dtype=torch.int32, device=device)
+        self.buf.zero_()
+        self.handle.barrier()
+
+    def __call__(self, mx: torch.Tensor, se: torch.Tensor, tg: torch.Tensor) -> None:
+        """In place: every rank ends with the same (max, sum exp relative to it, label logit) per row."""
+        ext = ops.load_ext(required=True)
+        for s in range(0, mx.numel(), self.CAP):
+            e = min(mx.numel(), s + self.CAP)
+            ext.ce_combine(mx[s:e], se[s:e], tg[s:e], self.peer_ptrs_dev, self.signal_ptrs_dev, self.counters,
+                           self.CAP, self.rank, self.world)
+
+
+_CE_COMBINERS: Dict[str, CeCombine] = {}
+
+
+def get_ce_combine(group, device) -> CeCombine:
+    name = group.group_name
+    c = _CE_COMBINERS.get(name)
+    if c is None:
+        c = CeCombine(group, device)
+        _CE_COMBINERS[name] = c
+    return c
+
+
 def symmetric_flat_usable(group, dtype: torch.dtype, device) -> bool:
     """The data-parallel buffers go to symmetric memory on CUDA devices, over NCCL groups of more than one rank,
     for 16-bit gradients / parameters, when the kernels are built and ``OSLO_B200_DP_SYMMETRIC`` is not switched off.

@@ -55,6 +55,29 @@ def _grad_inplace(logits: Tensor, labels: Tensor, lo: int, lse: Tensor, scale: T
     return logits
 
 
+def _epilogue_ce_ok(hidden: Tensor, weight: Tensor, bias: Optional[Tensor], fused: bool) -> bool:
+    """The LM-head GEMM can do the cross-entropy work in its epilogue: kernels in use, 16-bit operands of one dtype,
+    ``[vocab, hidden]`` weight with 16-byte aligned rows."""
+    if not (fused and hidden.is_cuda and hidden.dtype in (torch.bfloat16, torch.float16)):
+        return False
+    from ..config import get_config
+    if not get_config().ce_in_gemm_epilogue:
+        return False
+    ok = (weight.dtype == hidden.dtype and weight.dim() == 2 and weight.stride(1) == 1 and weight.stride(0) % 8 == 0
+          and hidden.size(-1) % 8 == 0 and weight.data_ptr() % 16 == 0
+          and weight.size(0) % 8 == 0)      # rows of the [rows, vocab shard] gradient matrix stay 16-byte aligned
+    return ok and (bias is None or (bias.dtype == hidden.dtype and bias.is_contiguous()))
+
+
+def _own_collectives() -> bool:
+    from ..config import get_config
+    return bool(get_config().fused_tp_comm)
+
+
+def _as_rows(x: Tensor) -> Tensor:
+    return x if (x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0) else x.contiguous()
+
+
 class _LinearCrossEntropy(torch.autograd.Function):
     @staticmethod
     def forward(ctx, hidden, weight, bias, labels, mpu, full_vocab, ignore_index, chunk_rows, fused):
@@ -67,11 +90,22 @@ class _LinearCrossEntropy(torch.autograd.Function):
         mx = torch.empty(n, dtype=torch.float32, device=hidden.device)
         se = torch.empty_like(mx)
         tg = torch.empty_like(mx)
+        in_epilogue = _epilogue_ce_ok(hidden, weight, bias, fused)
         for s in range(0, n, chunk_rows):
             e = min(n, s + chunk_rows)
+            if in_epilogue:
+                # per-row (max, sum exp, label logit) straight out of the GEMM's accumulators: no logits tensor
+                from .. import ops
+                mx[s:e], se[s:e], tg[s:e] = ops.load_ext(required=True).gemm_ce_stats(
+                    _as_rows(hidden[s:e]), weight, 0, bias, labels[s:e].contiguous(), lo)
+                continue
             lg = _proj(hidden[s:e], weight, bias, fused)
             mx[s:e], se[s:e], tg[s:e] = _stats(lg, labels[s:e], lo, fused)
-        if tp > 1:
+        if tp > 1 and in_epilogue and mpu.backend == "nccl" and _own_collectives():
+            # one kernel, one cross-rank meeting: peers' statistics read from symmetric memory and combined in place
+            from .symmetric import get_ce_combine
+            get_ce_combine(mpu.get_tensor_parallel_group(), hidden.device)(mx, se, tg)
+        elif tp > 1:
             gmx = mx.clone()
             dist.all_reduce(gmx, op=dist.ReduceOp.MAX, group=mpu.get_tensor_parallel_group())
             se = se * torch.exp(mx - gmx)
@@ -84,6 +118,7 @@ class _LinearCrossEntropy(torch.autograd.Function):
         loss = torch.where(valid, lse - tg, torch.zeros_like(lse)).sum() / count
         ctx.save_for_backward(hidden, weight, bias, labels, lse, valid, count)
         ctx.mpu, ctx.lo, ctx.chunk, ctx.fused = mpu, lo, chunk_rows, fused
+        ctx.in_epilogue = in_epilogue
         return loss
 
     @staticmethod
@@ -103,8 +138,15 @@ class _LinearCrossEntropy(torch.autograd.Function):
         for s in range(0, n, ctx.chunk):
             e = min(n, s + ctx.chunk)
             x = hidden[s:e]
-            lg = _proj(x, weight, bias, fused)
-            d = _grad_inplace(lg, labels[s:e], lo, lse[s:e], scale[s:e], fused)
+            if ctx.in_epilogue:
+                # recomputed logits leave the GEMM as (softmax - onehot) * scale
+                from .. import ops
+                x = _as_rows(x)
+                d = ops.load_ext(required=True).gemm_ce_grad(x, weight, 0, bias, labels[s:e].contiguous(), lo,
+                                                            lse[s:e].contiguous(), scale[s:e].contiguous())
+            else:
+                lg = _proj(x, weight, bias, fused)
+                d = _grad_inplace(lg, labels[s:e], lo, lse[s:e], scale[s:e], fused)
             if on_kernels:
                 from ..ops import cuda_ops
                 cuda_ops.gemm(d, weight, False, True, out=dx[s:e])      # written in place, no chunk copy

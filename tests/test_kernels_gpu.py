@@ -205,6 +205,70 @@ def test_linear_cross_entropy_fused():
     _close(b.grad, bf.grad, atol=2e-4, rtol=5e-2)
 
 
+@pytest.mark.parametrize("M,N,K,lo,with_bias", [(300, 1000, 256, 0, True), (128, 264, 64, 500, False),
+                                                (2560, 50400, 512, 0, True), (1024, 25200, 1024, 25200, True)])
+def test_lm_head_gemm_with_cross_entropy_epilogue(M, N, K, lo, with_bias):
+    """Row statistics and (softmax - onehot) * scale straight out of the GEMM accumulators against fp32 statements on
+    the 16-bit-rounded logits; labels outside this shard's columns and ignored labels included."""
+    ops, co = _ops()
+    ext = ops.load_ext()
+    torch.manual_seed(11)
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.1).to(torch.bfloat16)
+    b = (torch.randn(N, device="cuda") * 0.2).to(torch.bfloat16) if with_bias else None
+    full = lo + N + 300
+    lab = torch.randint(0, full, (M,), device="cuda")           # some labels belong to other shards
+    lab[1] = lo
+    lab[2] = lo + N - 1
+    lab[3] = -100
+    logits = x.float() @ w.float().t()
+    if b is not None:
+        logits = logits + b.float()
+    logits = logits.to(torch.bfloat16).float()
+    mx, se, tg = ext.gemm_ce_stats(x, w, 0, b, lab, lo)
+    want_mx = logits.max(-1).values
+    want_se = torch.exp(logits - want_mx[:, None]).sum(-1)
+    local = lab - lo
+    inside = (local >= 0) & (local < N)
+    want_tg = torch.where(inside, logits.gather(1, local.clamp(0, N - 1)[:, None]).squeeze(1), torch.zeros_like(want_mx))
+    # sums of K products in another order than the library's: bf16 rounding may differ by one step for a few logits
+    _close(mx, want_mx, atol=0.05, rtol=1e-2)
+    lse, want_lse = torch.log(se) + mx, torch.log(want_se) + want_mx
+    _close(lse, want_lse, atol=0.02, rtol=1e-3)
+    _close(tg, want_tg, atol=0.05, rtol=1e-2)
+    scale = torch.rand(M, device="cuda") * (lab != -100)
+    d = ext.gemm_ce_grad(x, w, 0, b, lab, lo, want_lse.contiguous(), scale.contiguous())
+    p = torch.exp(logits - want_lse[:, None])
+    rows = torch.nonzero(inside, as_tuple=True)[0]
+    p[rows, local[rows]] -= 1.0
+    p *= scale[:, None]
+    _close(d, p, atol=3e-3, rtol=5e-2)
+    assert d[3].abs().max() == 0
+    assert co.device_error_code(x) == 0
+
+
+def test_linear_cross_entropy_epilogue_and_separate_kernels_agree():
+    """Whole loss + gradients: the GEMM-epilogue route and the logits-chunk route give the same numbers."""
+    ops, _ = _ops()
+    from oslo_b200.config import set_config
+    res = {}
+    for flag in (True, False):
+        set_config(ce_in_gemm_epilogue=flag)
+        torch.manual_seed(8)
+        h = (torch.randn(700, 256, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+        w = (torch.randn(2048, 256, device="cuda") * 0.1).to(torch.bfloat16).requires_grad_(True)
+        b = (torch.randn(2048, device="cuda") * 0.1).to(torch.bfloat16).requires_grad_(True)
+        lab = torch.randint(0, 2048, (700,), device="cuda")
+        lab[:5] = -100
+        loss = ops.linear_cross_entropy(h, w, b, lab, chunk_rows=256)
+        loss.backward()
+        res[flag] = (loss.item(), h.grad.clone(), w.grad.clone(), b.grad.clone())
+    set_config(ce_in_gemm_epilogue=True)
+    assert abs(res[True][0] - res[False][0]) < 2e-3
+    for a, c in zip(res[True][1:], res[False][1:]):
+        _close(a, c, atol=3e-4, rtol=5e-2)
+
+
 def test_adam_and_ngram():
     ops, co = _ops()
     ext = ops.load_ext()

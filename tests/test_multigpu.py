@@ -21,6 +21,7 @@ def _entry(rank, world, port, fn, args, errq):
                       MASTER_PORT=str(port), NCCL_NVLS_ENABLE=os.environ.get("NCCL_NVLS_ENABLE", "1"))
     import traceback
     try:
+        import oslo_b200  # noqa: F401 - before the CUDA context exists: the package sets CUDA_DEVICE_MAX_CONNECTIONS
         torch.cuda.set_device(rank)
         fn(rank, world, *args)
     except BaseException:
