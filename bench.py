@@ -39,6 +39,8 @@ MODELS = {
     # name: (n_layer, n_embd, n_head, rotary_dim, vocab, n_positions)
     "gptj-6b": (28, 4096, 16, 64, 50400, 2048),
     "gptj-small": (4, 1024, 8, 64, 50400, 2048),   # debugging only; numbers from it are not benchmark values
+    # GPT-Neo 1.3B: alternating global / local (window 256) attention, learned positions; rotary_dim unused
+    "gpt-neo-1.3b": (24, 2048, 16, 0, 50257, 2048),
 }
 
 
@@ -51,6 +53,7 @@ def parse_args():
     ap.add_argument("--model", default="gptj-6b", choices=sorted(MODELS))
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--batch-per-gpu", type=int, default=8)
+    ap.add_argument("--replica-batch", type=int, default=None, help="sequences per model replica per step (default: batch-per-gpu x tp x pp)")
     ap.add_argument("--micro-batch", type=int, default=None, help="sequences per forward/backward (default: auto)")
     ap.add_argument("--tp", type=int, default=None)
     ap.add_argument("--pp", type=int, default=None)
@@ -65,6 +68,9 @@ def parse_args():
     ap.add_argument("--new-tokens", type=int, default=128, help="decode: tokens generated per call")
     ap.add_argument("--decode-batch", type=int, default=1, help="decode: sequences per call")
     ap.add_argument("--no-graph", action="store_true", help="decode: run the token loop eagerly (no CUDA graph)")
+    ap.add_argument("--deployment", action="store_true",
+                    help="decode: ONE ordinary process (no launcher); the model is created with deployment=True, which "
+                         "spawns one worker per GPU, and generate() is called on the parent's handle")
     ap.add_argument("--layers", type=int, default=None, help="profiling only: override the layer count (result is labelled debug)")
     return ap.parse_args()
 
@@ -162,8 +168,15 @@ def run_train_config(args, spec, dims, world, rank, local, dev):
     n_layer, n_embd, n_head, rotary, vocab, n_pos = dims
     tp, pp = spec["tp"], spec["pp"]
     dp = world // (tp * pp)
-    cfg = ob.GPTJConfig(vocab_size=vocab, n_positions=n_pos, n_embd=n_embd, n_layer=n_layer, n_head=n_head,
-                        rotary_dim=rotary, torch_dtype=torch.bfloat16, use_cache=False)
+    if args.model.startswith("gpt-neo"):
+        cfg = ob.GPTNeoConfig(vocab_size=vocab, max_position_embeddings=n_pos, hidden_size=n_embd, num_layers=n_layer,
+                              num_heads=n_head, window_size=256, attention_types=[[["global", "local"], n_layer // 2]],
+                              torch_dtype=torch.bfloat16, use_cache=False)
+        model_cls = ob.GPTNeoForCausalLM
+    else:
+        cfg = ob.GPTJConfig(vocab_size=vocab, n_positions=n_pos, n_embd=n_embd, n_layer=n_layer, n_head=n_head,
+                            rotary_dim=rotary, torch_dtype=torch.bfloat16, use_cache=False)
+        model_cls = ob.GPTJForCausalLM
     # sequences one model replica handles per step: weak scaling keeps 8 per GPU unless the configuration names a batch
     seqs_per_rank = spec.get("replica_batch") or args.batch_per_gpu * tp * pp
     # 4 sequences per forward/backward per GPU keeps activations within memory; tensor-parallel replicas spread a
@@ -172,7 +185,7 @@ def run_train_config(args, spec, dims, world, rank, local, dev):
     micro = min(micro, seqs_per_rank)
     accum = seqs_per_rank // micro
 
-    model = ob.GPTJForCausalLM.from_config_with_parallel(
+    model = model_cls.from_config_with_parallel(
         cfg, tensor_parallel_size=tp, pipeline_parallel_size=pp, micro_batch_size=micro, seed=1234,
         init_on_device=True, torch_dtype=torch.bfloat16)
     model.fuse()
@@ -285,6 +298,7 @@ def run_train_config(args, spec, dims, world, rank, local, dev):
     from oslo_b200.parallel import fused_tp, symmetric
     fused_tp._CONTEXTS.clear()
     symmetric._WORKSPACES.clear()
+    ext.set_reserved_sms(0)          # a pipeline-parallel configuration keeps a few SMs off the GEMM grids; the next one decides anew
     gc.collect()
     torch.cuda.synchronize()
     torch.cuda.empty_cache()
@@ -297,6 +311,10 @@ def main() -> None:
     args = parse_args()
     if args.impl == "reference":
         reference_arm(args)
+        return
+
+    if args.mode == "decode" and args.deployment:
+        decode_deployment_main(args)
         return
 
     import torch
@@ -331,13 +349,14 @@ def main() -> None:
             extra = []
     else:
         tp, pp = args.tp or 1, args.pp or 1
-        primary, extra = dict(name="custom", tp=tp, pp=pp), []
+        primary, extra = dict(name="custom", tp=tp, pp=pp, replica_batch=args.replica_batch), []
     MPU.initialize_distributed("nccl")
 
     def emit(block, also):
         full = args.model == "gptj-6b" and args.layers is None
+        name = {"gpt-neo-1.3b": "GPT-Neo-1.3B train tokens/sec"}.get(args.model if args.layers is None else "", f"{args.model} train tokens/sec (debug)")
         line = {
-            "metric": "GPT-J-6B train tokens/sec" if full else f"{args.model} train tokens/sec (debug)",
+            "metric": "GPT-J-6B train tokens/sec" if full else name,
             "value": block["value"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": block["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights", "impl": "oslo_b200",
@@ -382,6 +401,68 @@ def main() -> None:
         emit(block, also)
     dist.barrier()
     dist.destroy_process_group()
+
+
+def decode_deployment_main(args) -> None:
+    """Greedy decoding through the deployment launcher, the way a serving script uses the package: this process is
+    the only one the user starts; ``from_config_with_parallel(..., deployment=True)`` spawns one worker per GPU
+    (tensor parallel over all of them) and ``model.generate(...)`` on the returned handle fans the request out.
+    Timed in THIS process with the wall clock (request in, token ids out, through the worker queues). The per-token
+    latency is the difference between a call that generates ``new_tokens`` tokens and one that generates a single
+    token (prefill + first token), divided by ``new_tokens - 1``."""
+    import torch
+
+    import oslo_b200 as ob
+
+    n_layer, n_embd, n_head, rotary, vocab, n_pos = MODELS[args.model]
+    if args.layers is not None:
+        n_layer = args.layers
+    tp = args.tp or args.gpus
+    cfg = ob.GPTJConfig(vocab_size=vocab, n_positions=n_pos, n_embd=n_embd, n_layer=n_layer, n_head=n_head,
+                        rotary_dim=rotary, torch_dtype=torch.bfloat16, use_cache=True)
+    model = ob.GPTJForCausalLM.from_config_with_parallel(cfg, tensor_parallel_size=tp, pipeline_parallel_size=1,
+                                                         seed=1234, deployment=True, init_on_device=True,
+                                                         torch_dtype=torch.bfloat16)
+    model = model.fuse()
+    b, prompt, n_new = args.decode_batch, args.prompt, args.new_tokens
+    gen = torch.Generator().manual_seed(77)
+    host = [torch.randint(0, vocab, (b, prompt), generator=gen) for _ in range(4)]
+    try:
+        def call(ids, new):
+            return model.generate(ids, max_new_tokens=new, eos_token_id=None, pad_token_id=0,
+                                  cuda_graph=not args.no_graph)
+
+        def timed(steps, new):
+            t0 = time.perf_counter()
+            for s in range(steps):
+                out = call(host[s % 4], new)
+            return (time.perf_counter() - t0) * 1e3 / steps, out
+
+        for _ in range(args.warmup):
+            call(host[0], n_new)
+            call(host[0], 1)
+        ms_call, out = timed(args.steps, n_new)
+        ms_first, _ = timed(args.steps, 1)
+        assert tuple(out.shape) == (b, prompt + n_new), tuple(out.shape)
+        ms_tok = (ms_call - ms_first) / max(n_new - 1, 1)
+        full = args.model == "gptj-6b" and args.layers is None
+        line = {
+            "metric": f"GPT-J-6B TP={tp} decode ms/token" if full else f"{args.model} TP={tp} decode ms/token (debug)",
+            "value": ms_tok, "unit": "ms/token", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_call, "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic uniform token ids, random-init weights", "impl": "oslo_b200",
+            "config": {"model": args.model, "global_batch": b, "seq_len": prompt, "new_tokens": n_new,
+                       "parallelism": f"tp{tp}",
+                       "decode": "deployment launcher: parent process -> worker queues -> generate(cuda_graph=" + str(not args.no_graph) + ")",
+                       "timing": "wall clock in the parent process, host tensors in and out",
+                       "prefill_plus_first_token_ms": ms_first, "tokens_per_s": b * 1e3 / ms_tok if ms_tok > 0 else None},
+            "e2e": {"value": ms_call / n_new, "unit": "ms/token (whole generate call incl. prefill, host in/out)",
+                    "ms_per_step": ms_call, "h2d_bytes_per_step": b * prompt * 8, "d2h_bytes_per_step": b * (prompt + n_new) * 8},
+            "gpu_launches": None,
+        }
+        print(json.dumps(line), flush=True)
+    finally:
+        model.cpu()      # shuts the workers down
 
 
 def decode_main(args, world, rank, local, dev, dims) -> None:

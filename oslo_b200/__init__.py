@@ -9,6 +9,9 @@ import os as _os
 # queues (8 by default) two streams can share a queue, and a receive that waits for its sender would then hold up
 # the very computation the sender is waiting for. The variable is read when the CUDA context is created.
 _os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+# Point-to-point transfers between pipeline stages: two channels (two thread blocks per transfer kernel) are enough for
+# one activation per micro-batch over NVLink, and every block of a transfer that waits for its peer holds an SM.
+_os.environ.setdefault("NCCL_MAX_P2P_NCHANNELS", "2")
 
 from .__version__ import version as __version__  # noqa: F401,E402
 from .modeling_utils import *  # noqa: F401,F403

@@ -33,6 +33,7 @@ class OsloConfig:
     tp_shared_reduction_sp: bool = False # sequence parallel: partial sums ride in the fused GEMM + reduce-scatter kernel (not yet run on GPUs)
     block_fusion: bool = True            # GPT-J block: q/k/v as one autograd node, residual additions inside GEMM epilogues
     ce_in_gemm_epilogue: bool = True     # LM head + loss: row statistics / (softmax - onehot) computed in the GEMM epilogue, logits never stored
+    pp_reserved_sms: int = 8             # pipeline parallel: SMs the persistent GEMM grids leave free for the stage-to-stage transfers that wait on a neighbour
     ddp_bucket_mb: int = 256
     dp_symmetric: bool = True            # data parallel: flat gradient / parameter buffers in symmetric memory, reduce-scatter and all-gather by this package's kernels (off: NCCL)
     dp_overlap_param_gather: bool = True # ZeRO-1: refreshed parameters travel bucket by bucket on a side stream, each forward unit waits for its own buckets

@@ -34,6 +34,17 @@ cudaStream_t cur_stream(int kernels = 1) {
   return at::cuda::getCurrentCUDAStream().stream();
 }
 int64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
+// SMs that the persistent GEMM kernels leave free (their grids are sized for `SM count - reserved`). A pipeline stage
+// keeps point-to-point transfers in flight that wait for the neighbouring stage while holding an SM each; with a
+// statically scheduled persistent grid every SM taken away would delay that SM's whole share of the tiles to the end
+// of the kernel. Process-wide; every rank of a tensor-parallel group must use the same value (the fused GEMM +
+// collective kernels need the same grid on every rank).
+std::atomic<int> g_reserved_sms{0};
+int64_t set_reserved_sms(int64_t n) {
+  const int prev = g_reserved_sms.exchange(static_cast<int>(n < 0 ? 0 : n));
+  return prev;
+}
+int64_t reserved_sms() { return g_reserved_sms.load(); }
 const void* ptr_or_null(const optional<Tensor>& t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
 
 struct DevState {
@@ -52,6 +63,13 @@ DevState& dev_state(int dev) {
     it = states.emplace(dev, std::move(s)).first;
   }
   return it->second;
+}
+
+// SM count the persistent kernels may fill: all of them minus the reserved ones, an even number of at least 2
+int usable_sms(const DevState& st) {
+  int n = st.sms - g_reserved_sms.load(std::memory_order_relaxed);
+  if (n < 2) n = 2;
+  return n & ~1;
 }
 
 // The word that kernels set when a bounded wait runs out (0 = no error). Reading it synchronises.
@@ -112,7 +130,7 @@ Tensor gemm(const Tensor& a, const Tensor& b, int64_t a_mn, int64_t b_mn, const 
                                  static_cast<int>(d.stride(0)), static_cast<int>(a_mn), static_cast<int>(b_mn),
                                  ptr_or_null(bias), ptr_or_null(aux), ld_aux,
                                  const_cast<void*>(ptr_or_null(aux_out)), ld_aux_out, fl, static_cast<float>(alpha),
-                                 st.err.data_ptr<int>(), st.sms, cur_stream());
+                                 st.err.data_ptr<int>(), usable_sms(st), cur_stream());
   check_rc(rc, "gemm");
   return d;
 }
@@ -144,7 +162,7 @@ std::tuple<Tensor, Tensor, Tensor> gemm_ce_stats(const Tensor& a, const Tensor& 
                               has_bias ? bias->data_ptr() : nullptr,
                               reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()), vocab_start, 0,
                               stats.data_ptr<float>(), nullptr, nullptr, nullptr, 0, a.scalar_type() == at::kHalf ? 1 : 0,
-                              st.err.data_ptr<int>(), st.sms, cur_stream()), "gemm_ce_stats");
+                              st.err.data_ptr<int>(), usable_sms(st), cur_stream()), "gemm_ce_stats");
   check_rc(oslo_ce_reduce_stats(stats.data_ptr<float>(), mx.data_ptr<float>(), se.data_ptr<float>(), tg.data_ptr<float>(),
                                 static_cast<int>(M), static_cast<int>(blocks), cur_stream()), "ce_reduce_stats");
   return {mx, se, tg};
@@ -171,7 +189,7 @@ Tensor gemm_ce_grad(const Tensor& a, const Tensor& b, int64_t b_mn, const option
                               has_bias ? bias->data_ptr() : nullptr,
                               reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()), vocab_start, 1, nullptr,
                               lse.data_ptr<float>(), scale.data_ptr<float>(), d.data_ptr(), static_cast<int>(d.stride(0)),
-                              a.scalar_type() == at::kHalf ? 1 : 0, st.err.data_ptr<int>(), st.sms, cur_stream()),
+                              a.scalar_type() == at::kHalf ? 1 : 0, st.err.data_ptr<int>(), usable_sms(st), cur_stream()),
            "gemm_ce_grad");
   return d;
 }
@@ -190,7 +208,7 @@ Tensor gemm_small_m(const Tensor& a, const Tensor& b, int64_t b_mn, const option
   const int64_t N = b_mn ? b.size(1) : b.size(0), Kb = b_mn ? b.size(0) : b.size(1);
   TORCH_CHECK(K == Kb, "contraction sizes differ: ", K, " vs ", Kb);
   auto& st = dev_state(a.get_device());
-  const int split = std::max(1, oslo_gemm_split_k_for(static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), st.sms));
+  const int split = std::max(1, oslo_gemm_split_k_for(static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), usable_sms(st)));
   const bool has_bias = bias.has_value() && bias->defined();
   if (has_bias)
     TORCH_CHECK(bias->numel() == N && bias->scalar_type() == a.scalar_type() && bias->is_contiguous(), "bad bias");
@@ -202,7 +220,7 @@ Tensor gemm_small_m(const Tensor& a, const Tensor& b, int64_t b_mn, const option
   check_rc(oslo_gemm_splitk_16bit(a.data_ptr(), b.data_ptr(), ws.data_ptr<float>(), static_cast<int>(M),
                                   static_cast<int>(N), static_cast<int>(K), static_cast<int>(a.stride(0)),
                                   static_cast<int>(b.stride(0)), static_cast<int>(N), 0, static_cast<int>(b_mn),
-                                  a.scalar_type() == at::kHalf ? 1 : 0, split, st.err.data_ptr<int>(), st.sms,
+                                  a.scalar_type() == at::kHalf ? 1 : 0, split, st.err.data_ptr<int>(), usable_sms(st),
                                   cur_stream()), "gemm_splitk");
   Tensor y = at::empty({M, N}, a.options());
   check_rc(oslo_splitk_finalize(ws.data_ptr<float>(), has_bias ? bias->data_ptr() : nullptr, y.data_ptr(), M,
@@ -535,7 +553,7 @@ int64_t gemm_comm(const Tensor& a, const Tensor& b, int64_t a_mn, int64_t b_mn, 
   }
   auto& st = dev_state(a.get_device());
   // tile shape must be the same on every rank: decide from the problem size only
-  const int wide = (N >= 256 && ((M + 127) / 128) * ((N + 255) / 256) >= st.sms / 2) ? 1 : 0;
+  const int wide = (N >= 256 && ((M + 127) / 128) * ((N + 255) / 256) >= usable_sms(st) / 2) ? 1 : 0;
   const int rc = oslo_gemm_comm_16bit(
       a.data_ptr(), b.data_ptr(), static_cast<int>(M), static_cast<int>(N), static_cast<int>(K),
       static_cast<int>(a.stride(0)), static_cast<int>(b.stride(0)), static_cast<int>(a_mn), static_cast<int>(b_mn),
@@ -545,7 +563,7 @@ int64_t gemm_comm(const Tensor& a, const Tensor& b, int64_t a_mn, int64_t b_mn, 
       data_off, flag_off, flag_bytes, static_cast<int>(rank), static_cast<int>(world), static_cast<unsigned>(epoch),
       static_cast<unsigned>(done_base), static_cast<int>(mode), use_multimem ? 1 : 0, out_ptr, ld_out, wide,
       trace.has_value() && trace->defined() ? reinterpret_cast<unsigned long long*>(trace->data_ptr<int64_t>()) : nullptr,
-      st.err.data_ptr<int>(), st.sms, cur_stream());
+      st.err.data_ptr<int>(), usable_sms(st), cur_stream());
   check_rc(rc, "gemm_comm");
   // how far this call advances the slot's completion counter (the caller keeps the running total)
   const int64_t bn = wide ? 256 : 128;
@@ -624,7 +642,7 @@ Tensor gemv_rows(const Tensor& x1, const optional<Tensor>& x2, const Tensor& w, 
                           w.data_ptr(), static_cast<int>(w.stride(0)), has_bias ? bias->data_ptr() : nullptr,
                           has_res ? res->data_ptr() : nullptr, has_res ? static_cast<int>(res->stride(0)) : 0, y.data_ptr(),
                           static_cast<int>(N), static_cast<int>(M), static_cast<int>(N), static_cast<int>(gelu_from),
-                          dt_code(x1), st.sms, cur_stream()), "gemv_rows");
+                          dt_code(x1), usable_sms(st), cur_stream()), "gemv_rows");
   return y;
 }
 
@@ -664,7 +682,7 @@ Tensor vocab_embed(const Tensor& ids, const Tensor& weight, int64_t lo, int64_t 
                             reinterpret_cast<uint32_t* const*>(signal_ptrs_dev),
                             reinterpret_cast<uint32_t*>(counters.data_ptr<int>()), tokens, static_cast<int>(H), lo, hi,
                             half_bytes, static_cast<int>(rank), static_cast<int>(world), dt_code(weight),
-                            use_multimem ? 1 : 0, st.err.data_ptr<int>(), st.sms, cur_stream()), "vocab_embed");
+                            use_multimem ? 1 : 0, st.err.data_ptr<int>(), usable_sms(st), cur_stream()), "vocab_embed");
   return out;
 }
 
@@ -702,6 +720,8 @@ void allreduce_oneshot(Tensor x, int64_t peer_ptrs_dev, int64_t mc_ptr, int64_t 
 TORCH_LIBRARY(oslo_b200, m) {
   m.def("error_word(Tensor like) -> Tensor");
   m.def("launch_count() -> int", &launch_count);
+  m.def("set_reserved_sms(int n) -> int", &set_reserved_sms);
+  m.def("reserved_sms() -> int", &reserved_sms);
   m.def("gemm(Tensor a, Tensor b, int a_mn, int b_mn, Tensor? bias, Tensor? aux, Tensor(a!)? out, Tensor(b!)? aux_out, int flags, float alpha) -> Tensor");
   m.def("gemm_ce_stats(Tensor a, Tensor b, int b_mn, Tensor? bias, Tensor labels, int vocab_start) -> (Tensor, Tensor, Tensor)");
   m.def("gemm_ce_grad(Tensor a, Tensor b, int b_mn, Tensor? bias, Tensor labels, int vocab_start, Tensor lse, Tensor scale) -> Tensor");

@@ -714,24 +714,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         }
       }
     } else {
-      const int num_tiles_c = p.tiles_m * p.tiles_n;
       const int rows_per_rank = p.M / c.world;
-      // enumerate only the tiles this rank owns (no scan over all tiles: integer division is slow), and give
-      // every CTA each gridDim-th of them, in the order in which they are produced
-      const int per_rank_rows = p.tiles_m / c.world;
-      const int n_owned = c.mode == COMM_REDUCE_SCATTER ? per_rank_rows * p.tiles_n
-                                                        : (num_tiles_c - c.rank + c.world - 1) / c.world;
-      for (int j = blockIdx.x; j < n_owned && ok; j += gridDim.x) {
-        int tm, tn, tile;
-        if (c.mode == COMM_REDUCE_SCATTER) {
-          tm = c.rank * per_rank_rows + j / p.tiles_n;
-          tn = j % p.tiles_n;
-          tile = tm * p.tiles_n + tn;
-        } else {
-          tile = c.rank + c.world * j;
-          tm = tile / p.tiles_n;
-          tn = tile % p.tiles_n;
-        }
+      // This CTA reduces, of the tiles it PRODUCES itself (same raster walk as its MMA warp), the ones this rank owns.
+      // Every rank launches the same grid, so a tile is produced by the CTA of the same index on every rank: a CTA
+      // only ever waits for its namesakes on the peers. If some CTAs of the grid are not resident yet (their SMs are
+      // held by another kernel - a point-to-point transfer that is itself waiting for its peer), the resident ones
+      // still finish and leave, which is what lets the late ones in; nothing here needs the whole grid at once.
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        coords(t, tm, tn);
+        const int tile = tm * p.tiles_n + tn;
+        if (tile_owner(c, tile, tm, p.tiles_m) != c.rank) continue;
         const uint64_t tw0 = trace ? globaltimer_ns() : 0;
         ok = warp_wait_words(my_flags + static_cast<size_t>(tile) * c.world * 4, c.world * 4, c.epoch, abort_flag, p.err);
         if (!ok) break;
@@ -817,8 +810,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           }
         }
       }
-      if (c.mode == COMM_ALLREDUCE && ok && cw == 0) {
-        // the result is complete on this rank once every tile of every owner has been broadcast
+      if (c.mode == COMM_ALLREDUCE && ok && cw == 0 && blockIdx.x == 0) {
+        // the result is complete on this rank once every tile of every owner has been broadcast. ONE CTA waits for
+        // that (the kernel cannot end before its last CTA does); the others leave as soon as their own tiles are done
         wait_flag_ge(reinterpret_cast<const uint32_t*>(my_base + c.done_off), c.done_target, abort_flag, p.err);
       }
       if (trace && cw == 0) trace[4] = globaltimer_ns();

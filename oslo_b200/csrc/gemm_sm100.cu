@@ -131,9 +131,9 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams&
     cfg.dynamicSmemBytes = smem;
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_tcgen05_kernel<STAGES>, &cfg) != cudaSuccess || n <= 0) n = num_sms / 2;
-    max_pairs = std::min(n, num_sms / 2);
+    max_pairs = n;
   }
-  const int pairs = std::min(tiles, max_pairs);
+  const int pairs = std::min(tiles, std::min(max_pairs, num_sms / 2));   // num_sms already excludes reserved SMs
   gemm_pair_tcgen05_kernel<STAGES><<<2 * pairs, GEMM_THREADS, smem, stream>>>(ta, tb, p);
   return static_cast<int>(cudaGetLastError());
 }

@@ -4,8 +4,8 @@
 (no launcher). The parent spawns ``tp * pp`` worker processes, each of which joins a process group,
 parallelises its copy of the model on its own device and then serves requests; in the parent,
 ``model.generate`` / ``model.forward`` / ``model(...)`` are proxies that fan the call out to every worker
-and return rank 0's result, and ``model.cpu()`` / ``.cuda()`` / ``.to()`` shut the workers down
-(reference: oslo/parallelism/engine_deployment.py:22-375).
+and return rank 0's result, ``model.fuse()`` switches every worker's copy to the fused kernels, and ``model.cpu()`` /
+``.cuda()`` / ``.to()`` shut the workers down (reference: oslo/parallelism/engine_deployment.py:22-375).
 
 Differences from the reference: every wait in the parent has a deadline and checks worker liveness, so a
 dead worker raises ``DeploymentError`` instead of hanging; exceptions inside a worker travel back with
@@ -70,14 +70,23 @@ def _strip_for_pickle(obj):
 
 
 def _worker(rank: int, world: int, port: int, model, par: Dict[str, Any], split_path: Optional[str], in_q, out_q,
-            ready, backend: Optional[str]) -> None:
+            ready, backend: Optional[str], factory=None) -> None:
     try:
         os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
                           MASTER_PORT=str(port))
         if backend:
             os.environ["OSLO_B200_BACKEND"] = backend
-        if torch.cuda.is_available() and backend != "gloo":
+        on_gpu = torch.cuda.is_available() and backend != "gloo"
+        if on_gpu:
             torch.cuda.set_device(rank % torch.cuda.device_count())
+        if factory is not None:
+            # random-init model from its config, built by the worker itself on its own device: nothing of the size
+            # of the model crosses the process boundary. The shared seed makes every worker draw the same weights.
+            from ..parallelism_utils import set_seed
+            cls, config, torch_dtype = factory
+            set_seed(par.get("seed"))
+            with torch.device("cuda", torch.cuda.current_device()) if on_gpu else torch.device("cpu"):
+                model = cls._from_config(config, torch_dtype=torch_dtype)
         model._exec_both_engines(**par)
         if split_path is not None:
             model._load_split_checkpoint_files(split_path)
@@ -99,6 +108,8 @@ def _worker(rank: int, world: int, port: int, model, par: Dict[str, Any], split_
                     out = getattr(model, fn)(*args, **kwargs)
                     if model.is_pipeline_parallelized() and fn != "generate" and hasattr(out, "__next__"):
                         out = [o for o in out][0]
+                    if isinstance(out, torch.nn.Module):     # fuse() returns the model: the parent keeps its own handle
+                        out = None
                 out_q.put(("ok", _strip_for_pickle(out)))
             except BaseException:  # noqa: BLE001 - reported to the parent
                 out_q.put(("error", traceback.format_exc()))
@@ -119,8 +130,11 @@ class DeploymentParallelEngine:
                  micro_batch_size: int = 1, resize_token_embeddings: Optional[int] = None, seed: Optional[int] = None,
                  sequence_parallel: bool = False, split_checkpoint_path: Optional[str] = None,
                  backend: Optional[str] = None, startup_timeout_s: float = 600.0, request_timeout_s: float = 600.0,
-                 **_unused: Any) -> None:
+                 factory=None, **_unused: Any) -> None:
+        """``factory = (model class, config, torch_dtype)``: the workers build the (random-init) model themselves and
+        ``model`` is only the parent's handle (its tensors may live on the meta device)."""
         self.model = model
+        self.factory = factory
         self.world = int(tensor_parallel_size) * int(pipeline_parallel_size)
         self.par = dict(tensor_parallel_size=tensor_parallel_size, pipeline_parallel_size=pipeline_parallel_size,
                         micro_batch_size=micro_batch_size, resize_token_embeddings=resize_token_embeddings,
@@ -141,8 +155,8 @@ class DeploymentParallelEngine:
         for rank in range(self.world):
             in_q, out_q, ready = ctx.Queue(), ctx.Queue(), ctx.Event()
             p = ctx.Process(target=_worker, daemon=True,
-                            args=(rank, self.world, port, self.model, self.par, self.split_path, in_q, out_q, ready,
-                                  self.backend))
+                            args=(rank, self.world, port, None if self.factory is not None else self.model, self.par,
+                                  self.split_path, in_q, out_q, ready, self.backend, self.factory))
             p.start()
             self.procs.append(p)
             self.in_qs.append(in_q)
@@ -164,7 +178,7 @@ class DeploymentParallelEngine:
             raise DeploymentError(f"worker {rank} failed during start-up:\n{payload}")
         model = self.model
         object.__setattr__(model, "_deployment_engine", self)
-        for fn in ("generate", "forward"):
+        for fn in ("generate", "forward", "fuse"):
             object.__setattr__(model, fn, _Proxy(self, fn))
         for fn in ("cpu", "cuda", "to"):
             object.__setattr__(model, fn, _Shutdown(self, fn))
@@ -223,7 +237,8 @@ class _Proxy:
         self.engine, self.fn = engine, fn
 
     def __call__(self, *args, **kwargs):
-        return self.engine.forward(self.fn, *args, **kwargs)
+        out = self.engine.forward(self.fn, *args, **kwargs)
+        return self.engine.model if self.fn == "fuse" else out     # model.fuse() switches every worker to the kernels
 
 
 class _Shutdown:
@@ -235,6 +250,8 @@ class _Shutdown:
     def __call__(self, *args, **kwargs):
         self.engine.deparallelize()
         model = self.engine.model
-        for name in ("generate", "forward", "cpu", "cuda", "to"):
+        for name in ("generate", "forward", "fuse", "cpu", "cuda", "to"):
             model.__dict__.pop(name, None)
+        if self.engine.factory is not None:
+            return model         # a weightless handle (the workers built the model): nothing to move
         return getattr(model, self.fn)(*args, **kwargs)

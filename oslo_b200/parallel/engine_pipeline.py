@@ -255,6 +255,13 @@ class PipelineParallelEngine:
         if self.pp == 1:
             return
         self.p2p = P2PCommunicator(self.mpu)
+        if self.mpu.backend == "nccl" and torch.cuda.is_available():
+            # transfers between stages are kernels that hold an SM each while they wait for the neighbour: keep the
+            # persistent GEMM grids off a few SMs so that such a kernel never pushes GEMM work to the end of a launch
+            from .. import ops
+            from ..config import get_config
+            if ops.kernels_available() and get_config().pp_reserved_sms > 0:
+                ops.load_ext().set_reserved_sms(int(get_config().pp_reserved_sms))
         sm = _StageModule(self._owned_modules)
         sm._engine_forward = self.forward
         self.stage_module = sm

@@ -182,6 +182,15 @@ class ParallelizationMixin:
         for k, v in kwargs.items():
             setattr(config, k, v)
         set_seed(seed)
+        if init_on_device and deployment:
+            # the deployment workers build the model on their own devices; the parent keeps a weightless handle
+            with torch.device("meta"):
+                model = cls._from_config(config, torch_dtype=torch_dtype)
+            from .parallel.engine_deployment import DeploymentParallelEngine
+            return DeploymentParallelEngine(
+                model, tensor_parallel_size=tensor_parallel_size, pipeline_parallel_size=pipeline_parallel_size,
+                micro_batch_size=micro_batch_size, resize_token_embeddings=resize_token_embeddings, seed=seed,
+                sequence_parallel=sequence_parallel, factory=(cls, config, torch_dtype)).parallelize()
         if init_on_device and torch.cuda.is_available() and not deployment:
             from .parallel.mpu import MPU
             MPU.initialize_distributed()

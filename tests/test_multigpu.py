@@ -416,3 +416,40 @@ def test_zero1_symmetric_kernels_match_nccl(tmp_path):
     model = ob.GPTJForCausalLM(_cfg()).to(torch.bfloat16)
     torch.save({"state": {k: v.clone() for k, v in model.state_dict().items()}}, tmp_path / "ref.pt")
     run_gpus(_zero_dp_ab, 2, str(tmp_path))
+
+
+def test_deployment_launcher_on_gpus():
+    """The deployment launcher with GPU workers (the flow of the reference's tests/utils/test_deployment.py:6-35, with
+    assertions): this process spawns two tensor-parallel workers, beam search through them matches one GPU in fp32;
+    the fused bf16 model decodes greedily through the CUDA-graph path and agrees with one GPU on nearly every token."""
+    import oslo_b200 as ob
+    from oslo_b200.parallelism_utils import set_seed
+    cfg = ob.GPTJConfig(vocab_size=2048, n_positions=128, n_embd=256, n_layer=2, n_head=4, rotary_dim=16)
+    ids = torch.randint(0, 2048, (2, 12), generator=torch.Generator().manual_seed(3))
+    set_seed(41)
+    with torch.device("cuda", 0):                      # as the workers do: weights drawn by the device generator
+        one = ob.GPTJForCausalLM._from_config(cfg, torch_dtype=None).eval()
+    want = one.generate(ids.cuda(), max_length=24, num_beams=3, no_repeat_ngram_size=3, eos_token_id=None, pad_token_id=0).cpu()
+    model = ob.GPTJForCausalLM.from_config_with_parallel(cfg, tensor_parallel_size=2, seed=41, deployment=True,
+                                                         init_on_device=True)
+    try:
+        got = model.generate(ids, max_length=24, num_beams=3, no_repeat_ngram_size=3, eos_token_id=None, pad_token_id=0)
+        assert got.shape == want.shape and (got == want).float().mean() > 0.9, (got, want)
+    finally:
+        model.cpu()
+    del one
+    cfg16 = ob.GPTJConfig(vocab_size=2048, n_positions=128, n_embd=256, n_layer=2, n_head=4, rotary_dim=16,
+                          torch_dtype=torch.bfloat16)
+    set_seed(41)
+    with torch.device("cuda", 0):
+        one = ob.GPTJForCausalLM._from_config(cfg16, torch_dtype=torch.bfloat16).eval().fuse()
+    want = one.generate(ids.cuda(), max_new_tokens=16, eos_token_id=None, pad_token_id=0).cpu()
+    model = ob.GPTJForCausalLM.from_config_with_parallel(cfg16, tensor_parallel_size=2, seed=41, deployment=True,
+                                                         init_on_device=True, torch_dtype=torch.bfloat16).fuse()
+    try:
+        for _ in range(2):                           # the second call replays the captured step
+            got = model.generate(ids, max_new_tokens=16, eos_token_id=None, pad_token_id=0, cuda_graph=True)
+        assert got.shape == want.shape == (2, 28) and torch.equal(got[:, :12], ids)
+        assert (got == want).float().mean() > 0.7, (got, want)      # bf16 near-ties may flip a late token
+    finally:
+        model.cpu()
