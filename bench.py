@@ -71,6 +71,8 @@ def parse_args():
     ap.add_argument("--deployment", action="store_true",
                     help="decode: ONE ordinary process (no launcher); the model is created with deployment=True, which "
                          "spawns one worker per GPU, and generate() is called on the parent's handle")
+    ap.add_argument("--hang-dump", type=float, default=0.0,
+                    help="debugging: after this many seconds write every thread's Python stack to gpurun_out/hang_rank<r>.txt")
     ap.add_argument("--layers", type=int, default=None, help="profiling only: override the layer count (result is labelled debug)")
     return ap.parse_args()
 
@@ -309,6 +311,11 @@ def run_train_config(args, spec, dims, world, rank, local, dev):
 
 def main() -> None:
     args = parse_args()
+    if args.hang_dump > 0:
+        import faulthandler
+        os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
+        f = open(os.path.join(ROOT, "gpurun_out", f"hang_{os.environ.get('HANG_TAG', 'x')}_rank{os.environ.get('RANK', '0')}.txt"), "w")
+        faulthandler.dump_traceback_later(args.hang_dump, file=f, exit=False)
     if args.impl == "reference":
         reference_arm(args)
         return

@@ -13,6 +13,12 @@ _os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
 # one activation per micro-batch over NVLink, and every block of a transfer that waits for its peer holds an SM.
 _os.environ.setdefault("NCCL_MAX_P2P_NCHANNELS", "2")
 
+# Load every kernel when the CUDA context is created instead of at its first launch (costs about a second and 0.6 GB).
+# A first launch that has to load its kernel can wait for all kernels running in the context; under pipeline
+# parallelism one of those may be a transfer that waits for the neighbouring stage, which in turn waits for this
+# process to get further - the lazy default turns that into a deadlock in the first step.
+_os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
+
 from .__version__ import version as __version__  # noqa: F401,E402
 from .modeling_utils import *  # noqa: F401,F403
 from .modeling_utils import PreTrainedModel, PretrainedConfig, ModelOutput  # noqa: F401
