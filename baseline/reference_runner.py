@@ -482,7 +482,7 @@ def main(args, sampler_cls=None) -> None:
     if why:
         return _unavailable(why)
     import threading
-    limit = float(os.environ.get("OSLO_B200_REFERENCE_DEADLINE_S", "1500"))
+    limit = float(os.environ.get("OSLO_B200_REFERENCE_DEADLINE_S", "900"))
     done = threading.Event()
 
     def give_up():

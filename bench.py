@@ -58,7 +58,7 @@ def parse_args():
     ap.add_argument("--tp", type=int, default=None)
     ap.add_argument("--pp", type=int, default=None)
     ap.add_argument("--no-also", action="store_true", help="time the headline configuration only")
-    ap.add_argument("--also-timeout", type=float, default=600.0,
+    ap.add_argument("--also-timeout", type=float, default=420.0,
                     help="seconds the extra configurations may take before the headline is printed without them")
     ap.add_argument("--checkpoint-activations", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -72,7 +72,9 @@ def parse_args():
                     help="decode: ONE ordinary process (no launcher); the model is created with deployment=True, which "
                          "spawns one worker per GPU, and generate() is called on the parent's handle")
     ap.add_argument("--hang-dump", type=float, default=0.0,
-                    help="debugging: after this many seconds write every thread's Python stack to gpurun_out/hang_rank<r>.txt")
+                    help="debugging: after this many seconds write every thread's Python stack to "
+                         "<--hang-dump-dir>/hang_<HANG_TAG>_rank<r>.txt")
+    ap.add_argument("--hang-dump-dir", default=".", help="where --hang-dump writes (default: the working directory)")
     ap.add_argument("--layers", type=int, default=None, help="profiling only: override the layer count (result is labelled debug)")
     return ap.parse_args()
 
@@ -313,8 +315,8 @@ def main() -> None:
     args = parse_args()
     if args.hang_dump > 0:
         import faulthandler
-        os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-        f = open(os.path.join(ROOT, "gpurun_out", f"hang_{os.environ.get('HANG_TAG', 'x')}_rank{os.environ.get('RANK', '0')}.txt"), "w")
+        os.makedirs(args.hang_dump_dir, exist_ok=True)
+        f = open(os.path.join(args.hang_dump_dir, f"hang_{os.environ.get('HANG_TAG', 'x')}_rank{os.environ.get('RANK', '0')}.txt"), "w")
         faulthandler.dump_traceback_later(args.hang_dump, file=f, exit=False)
     if args.impl == "reference":
         reference_arm(args)
@@ -398,9 +400,20 @@ def main() -> None:
             b = run_train_config(args, spec, dims, world, rank, local, dev)
             also[spec["name"]] = {k: b[k] for k in ("value", "unit", "ms_per_step", "e2e", "config", "gpu_launches",
                                                     "device_error_word", "peak_mem_gb")}
-        except Exception as e:  # noqa: BLE001 - keep the headline; every rank sees shape / memory errors alike
+        except BaseException as e:  # noqa: BLE001 - the headline is measured already: an extra block must not lose it
+            if isinstance(e, (KeyboardInterrupt, SystemExit)):
+                raise
             also[spec["name"]] = {"error": f"{type(e).__name__}: {e}"[:300]}
-            break
+            # after a failure in the middle of a step the ranks are no longer in step with one another (and a CUDA
+            # error leaves no usable context): print what there is and leave without another collective. Ranks that
+            # are still waiting for this one are released by their own timers.
+            if guard is not None:
+                guard.cancel()
+            if rank == 0 and not printed.is_set():
+                printed.set()
+                emit(block, also)
+            sys.stdout.flush()
+            os._exit(0)
     if guard is not None:
         guard.cancel()
     if rank == 0 and not printed.is_set():

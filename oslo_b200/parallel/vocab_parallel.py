@@ -55,10 +55,20 @@ def _grad_inplace(logits: Tensor, labels: Tensor, lo: int, lse: Tensor, scale: T
     return logits
 
 
-def _epilogue_ce_ok(hidden: Tensor, weight: Tensor, bias: Optional[Tensor], fused: bool) -> bool:
+def shard_rows_aligned(full_vocab: int, tp: int) -> bool:
+    """Every rank's vocabulary shard has a multiple of 8 rows (50400 over 2 or 4 ranks: yes; 50257 over 2: 25129 and
+    25128, no; 50400 over 8: 6300, no). The same answer on every rank of the group."""
+    return all(s % 8 == 0 for s in ceil_split_sizes(int(full_vocab), max(int(tp), 1)))
+
+
+def _epilogue_ce_ok(hidden: Tensor, weight: Tensor, bias: Optional[Tensor], fused: bool, full_vocab: int, tp: int) -> bool:
     """The LM-head GEMM can do the cross-entropy work in its epilogue: kernels in use, 16-bit operands of one dtype,
-    ``[vocab, hidden]`` weight with 16-byte aligned rows."""
+    ``[vocab, hidden]`` weight with 16-byte aligned rows. The answer also selects the collective that combines the
+    shards' statistics, so it must not depend on anything that differs between the ranks of the tensor-parallel group:
+    the row count is checked for ALL shards, not for this rank's."""
     if not (fused and hidden.is_cuda and hidden.dtype in (torch.bfloat16, torch.float16)):
+        return False
+    if not shard_rows_aligned(full_vocab, tp):
         return False
     from ..config import get_config
     if not get_config().ce_in_gemm_epilogue:
@@ -66,6 +76,7 @@ def _epilogue_ce_ok(hidden: Tensor, weight: Tensor, bias: Optional[Tensor], fuse
     ok = (weight.dtype == hidden.dtype and weight.dim() == 2 and weight.stride(1) == 1 and weight.stride(0) % 8 == 0
           and hidden.size(-1) % 8 == 0 and weight.data_ptr() % 16 == 0
           and weight.size(0) % 8 == 0)      # rows of the [rows, vocab shard] gradient matrix stay 16-byte aligned
+    # (data_ptr alignment and strides of a shard come from the same allocator and the same slicing code on every rank)
     return ok and (bias is None or (bias.dtype == hidden.dtype and bias.is_contiguous()))
 
 
@@ -90,7 +101,7 @@ class _LinearCrossEntropy(torch.autograd.Function):
         mx = torch.empty(n, dtype=torch.float32, device=hidden.device)
         se = torch.empty_like(mx)
         tg = torch.empty_like(mx)
-        in_epilogue = _epilogue_ce_ok(hidden, weight, bias, fused)
+        in_epilogue = _epilogue_ce_ok(hidden, weight, bias, fused, full_vocab, tp)
         for s in range(0, n, chunk_rows):
             e = min(n, s + chunk_rows)
             if in_epilogue:
@@ -128,7 +139,9 @@ class _LinearCrossEntropy(torch.autograd.Function):
         n = hidden.size(0)
         scale = (g.float() / count) * valid.to(torch.float32)
         dx = torch.empty_like(hidden)
-        on_kernels = fused and hidden.is_cuda
+        # the gradient GEMMs take [rows, vocab shard] operands: with a shard whose row count is not a multiple of 8 the
+        # rows of that matrix are not 16-byte aligned and the library products below are used instead (a local choice)
+        on_kernels = fused and hidden.is_cuda and weight.size(0) % 8 == 0
         dw = None if on_kernels else torch.zeros_like(weight, dtype=torch.float32)
         dw_acc = None
         # weights whose gradient lives in the optimizer's flat buffer take the chunks' products there directly

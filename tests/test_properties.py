@@ -87,3 +87,18 @@ def test_one_f_one_b_schedule_is_complete_bounded_and_deadlock_free(stages, micr
                 pos[s] += 1
                 progressed = True
     assert all(pos[s] == len(orders[s]) for s in range(stages)), "the schedule dead-locks"
+
+
+def test_cross_entropy_route_is_the_same_on_every_tensor_parallel_rank():
+    """The choice between the symmetric-memory combine and the NCCL all-reduces of the vocabulary-parallel loss is made
+    from the sizes of ALL shards: an uneven split (50257 over 2 ranks gives 25129 and 25128 rows, only one of them a
+    multiple of 8) must not send the two ranks down different collectives."""
+    from oslo_b200.parallel.mpu import ceil_split_sizes
+    from oslo_b200.parallel.vocab_parallel import shard_rows_aligned
+    assert ceil_split_sizes(50257, 2) == [25129, 25128]
+    assert not shard_rows_aligned(50257, 2) and not shard_rows_aligned(50400, 8)
+    assert shard_rows_aligned(50400, 2) and shard_rows_aligned(50400, 4) and shard_rows_aligned(50400, 1)
+    for vocab in (50257, 50400, 2048, 1003):
+        for tp in (1, 2, 4, 8):
+            answers = {shard_rows_aligned(vocab, tp) for _rank in range(tp)}      # no rank-dependent input exists
+            assert len(answers) == 1
