@@ -58,6 +58,9 @@ def parse_args():
     ap.add_argument("--tp", type=int, default=None)
     ap.add_argument("--pp", type=int, default=None)
     ap.add_argument("--no-also", action="store_true", help="time the headline configuration only")
+    ap.add_argument("--even-partition", action="store_true",
+                    help="pipeline parallel: the same number of blocks on every stage (default: the last stage, which "
+                         "also runs the LM head and the loss, gets fewer blocks)")
     ap.add_argument("--also-timeout", type=float, default=420.0,
                     help="seconds the extra configurations may take before the headline is printed without them")
     ap.add_argument("--checkpoint-activations", action="store_true")
@@ -189,9 +192,13 @@ def run_train_config(args, spec, dims, world, rank, local, dev):
     micro = min(micro, seqs_per_rank)
     accum = seqs_per_rank // micro
 
+    partition = None
+    if pp > 1 and not args.even_partition:
+        from oslo_b200.parallel.engine_pipeline import balanced_partition
+        partition = balanced_partition(n_layer, pp)      # LM head + loss count as 1.5 blocks, the embedding as 0.15
     model = model_cls.from_config_with_parallel(
         cfg, tensor_parallel_size=tp, pipeline_parallel_size=pp, micro_batch_size=micro, seed=1234,
-        init_on_device=True, torch_dtype=torch.bfloat16)
+        init_on_device=True, torch_dtype=torch.bfloat16, pipeline_partition=partition)
     model.fuse()
     model.train()
     if args.checkpoint_activations:
@@ -276,7 +283,8 @@ def run_train_config(args, spec, dims, world, rank, local, dev):
         by_stage = {}
         for r in reps:
             by_stage.setdefault(r["stage"], []).append(r)
-        pipe = {"stages": pp, "micro_batches": accum, "ideal_idle_share": round((pp - 1) / (accum + pp - 1), 4),
+        pipe = {"stages": pp, "micro_batches": accum, "blocks_per_stage": partition or [n_layer // pp] * pp,
+                "ideal_idle_share": round((pp - 1) / (accum + pp - 1), 4),
                 "busy_ms_per_stage": [round(max(x["busy_ms"] for x in by_stage[s]), 1) for s in sorted(by_stage)],
                 "idle_share_of_step": [round(1.0 - max(x["busy_ms"] for x in by_stage[s]) / ms_step, 4)
                                        for s in sorted(by_stage)]}

@@ -810,9 +810,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           }
         }
       }
-      if (c.mode == COMM_ALLREDUCE && ok && cw == 0 && blockIdx.x == 0) {
+      if (c.mode == COMM_ALLREDUCE && ok && cw == 0 && blockIdx.x == gridDim.x - 1) {
         // the result is complete on this rank once every tile of every owner has been broadcast. ONE CTA waits for
-        // that (the kernel cannot end before its last CTA does); the others leave as soon as their own tiles are done
+        // that (the kernel cannot end before its last CTA does); the others leave as soon as their own tiles are done.
+        // It is the CTA with the highest index: blocks are handed to the SMs in index order, so by the time it
+        // runs every other CTA has been started and none is left waiting for the slot it holds
         wait_flag_ge(reinterpret_cast<const uint32_t*>(my_base + c.done_off), c.done_target, abort_flag, p.err);
       }
       if (trace && cw == 0) trace[4] = globaltimer_ns();

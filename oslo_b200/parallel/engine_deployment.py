@@ -130,7 +130,7 @@ class DeploymentParallelEngine:
                  micro_batch_size: int = 1, resize_token_embeddings: Optional[int] = None, seed: Optional[int] = None,
                  sequence_parallel: bool = False, split_checkpoint_path: Optional[str] = None,
                  backend: Optional[str] = None, startup_timeout_s: float = 600.0, request_timeout_s: float = 600.0,
-                 factory=None, **_unused: Any) -> None:
+                 factory=None, pipeline_partition: Optional[List[int]] = None, **_unused: Any) -> None:
         """``factory = (model class, config, torch_dtype)``: the workers build the (random-init) model themselves and
         ``model`` is only the parent's handle (its tensors may live on the meta device)."""
         self.model = model
@@ -139,7 +139,7 @@ class DeploymentParallelEngine:
         self.par = dict(tensor_parallel_size=tensor_parallel_size, pipeline_parallel_size=pipeline_parallel_size,
                         micro_batch_size=micro_batch_size, resize_token_embeddings=resize_token_embeddings,
                         seed=seed if seed is not None else int(time.time()) % (2 ** 31),
-                        sequence_parallel=sequence_parallel)
+                        sequence_parallel=sequence_parallel, pipeline_partition=pipeline_partition)
         self.split_path = split_checkpoint_path
         self.backend = backend or os.environ.get("OSLO_B200_BACKEND")
         self.startup_timeout_s, self.request_timeout_s = startup_timeout_s, request_timeout_s

@@ -45,6 +45,42 @@ def one_f_one_b_order(num_stages: int, stage: int, num_micro: int) -> List[str]:
     return order
 
 
+def balanced_partition(num_blocks: int, num_stages: int, head_blocks: float = 1.5, embed_blocks: float = 0.15) -> List[int]:
+    """Blocks per stage that minimise the load of the busiest stage when the first stage also embeds the tokens
+    (``embed_blocks`` block-equivalents of work) and the last stage also runs the LM head and the loss
+    (``head_blocks``). A 1F1B step lasts about (micro-batches + stages - 1) times the busiest stage's time per
+    micro-batch, so that stage is what the split should relieve. GPT-J-6B on 4 stages: [7, 7, 8, 6] instead of
+    [7, 7, 7, 7] (measured: LM head + loss weigh 1.5 blocks, the embedding 0.15). Among equally good splits the one
+    closest to the even split wins; every stage keeps at least one block."""
+    L, P = int(num_blocks), int(num_stages)
+    if P < 1 or L < P:
+        raise ValueError(f"{L} blocks cannot be split over {P} pipeline stages")
+    if P == 1:
+        return [L]
+    best, best_key = None, None
+    even = L / P
+
+    def rec(stage: int, left: int, acc: List[int]) -> None:
+        nonlocal best, best_key
+        if stage == P - 1:
+            parts = acc + [left]
+            loads = [n + (embed_blocks if i == 0 else 0.0) + (head_blocks if i == P - 1 else 0.0) for i, n in enumerate(parts)]
+            key = (round(max(loads), 6), round(sum((n - even) ** 2 for n in parts), 6), parts)
+            if best_key is None or key < best_key:
+                best, best_key = parts, key
+            return
+        lo = max(1, int(even) - 2)
+        hi = min(left - (P - 1 - stage), int(even) + 3)
+        for n in range(lo, hi + 1):
+            rec(stage + 1, left - n, acc + [n])
+
+    rec(0, L, [])
+    if best is None or min(best) < 1:      # the window around the even split found nothing valid (tiny models)
+        base = L // P
+        best = [base] * (P - 1) + [L - base * (P - 1)]
+    return best
+
+
 class MicroLossTensor(torch.Tensor):
     """Marker subclass for the loss yielded on stages that do not own the model head.
 
@@ -165,8 +201,13 @@ class _StageModule(nn.ModuleList):
 
 
 class PipelineParallelEngine:
-    def __init__(self, model: nn.Module, mpu: MPU, micro_batch_size: int = 1, device=None) -> None:
+    def __init__(self, model: nn.Module, mpu: MPU, micro_batch_size: int = 1, device=None,
+                 partition: Optional[List[int]] = None) -> None:
+        """``partition``: blocks per stage (e.g. ``[7, 8, 7, 6]``), when the stages should not get the reference's even
+        split (floor(L / P) each, remainder to the last stage, oslo/parallelism/mpu.py:934-948): the last stage also
+        runs the LM head and the loss, which for GPT-J-6B weigh about as much as one and a half blocks."""
         self.model, self.mpu = model, mpu
+        self.partition = [int(n) for n in partition] if partition else None
         self.micro_batch_size = int(micro_batch_size)
         self.device = device or mpu.device
         self.pp = mpu.get_pipeline_parallel_world_size()
@@ -193,10 +234,22 @@ class PipelineParallelEngine:
         self._events: Dict[tuple, Dict[str, Any]] = {}
 
     # ------------------------------------------------------------------ partition
+    def _bounds(self) -> List[int]:
+        """Block index at which every stage starts, plus the block count at the end."""
+        L = self.model.num_blocks()
+        if self.partition is None:
+            return self.mpu.make_pipeline_partition(L, self.pp)
+        if len(self.partition) != self.pp or sum(self.partition) != L or min(self.partition) < 1:
+            raise ValueError(f"pipeline_partition {self.partition} must give {self.pp} stages at least one block each "
+                             f"and {L} blocks in total")
+        bounds = [0]
+        for n in self.partition:
+            bounds.append(bounds[-1] + n)
+        return bounds
+
     def _stage_modules(self, stage: int) -> List[nn.Module]:
         model, cfg = self.model, self.model.config
-        L = model.num_blocks()
-        bounds = self.mpu.make_pipeline_partition(L, self.pp)
+        bounds = self._bounds()
         mods: List[nn.Module] = []
         for policy in model.get_layer_policies():
             blocks = policy.block_layers(model, cfg)
@@ -213,7 +266,7 @@ class PipelineParallelEngine:
         L = self.model.num_blocks()
         if L < self.pp:
             raise ValueError(f"{L} blocks cannot be split over {self.pp} pipeline stages")
-        bounds = self.mpu.make_pipeline_partition(L, self.pp)
+        bounds = self._bounds()
         self.block_range = (bounds[self.stage], bounds[self.stage + 1])
         names = {}
         for n, p in self.model.named_parameters(remove_duplicate=False):

@@ -24,7 +24,7 @@ logger = logging.getLogger(__name__)
 
 WEIGHTS_NAME_PARALLEL = "pytorch_model_tp={tp}_pp={pp}.bin"
 _PARALLEL_KEYS = ("tensor_parallel_size", "pipeline_parallel_size", "micro_batch_size",
-                  "resize_token_embeddings", "seed", "deployment", "sequence_parallel")
+                  "resize_token_embeddings", "seed", "deployment", "sequence_parallel", "pipeline_partition")
 
 
 def split_checkpoint_names(tp: int, pp: int) -> List[str]:
@@ -123,7 +123,8 @@ class ParallelizationMixin:
     def _exec_both_engines(self, tensor_parallel_size: int = 1, pipeline_parallel_size: int = 1,
                            micro_batch_size: int = 1, resize_token_embeddings: Optional[int] = None,
                            seed: Optional[int] = None, sequence_parallel: bool = False,
-                           device: Optional[torch.device] = None, **_unused: Any):
+                           device: Optional[torch.device] = None, pipeline_partition: Optional[List[int]] = None,
+                           **_unused: Any):
         from .parallel.engine_pipeline import PipelineParallelEngine
         from .parallel.engine_tensor import TensorParallelEngine
         from .parallel.mpu import MPU
@@ -140,7 +141,8 @@ class ParallelizationMixin:
             self.resize_token_embeddings(resize_token_embeddings)
         mpu = MPU(tp, pp)
         device = device or mpu.device
-        pipe = PipelineParallelEngine(self, mpu, micro_batch_size=micro_batch_size, device=device)
+        pipe = PipelineParallelEngine(self, mpu, micro_batch_size=micro_batch_size, device=device,
+                                      partition=pipeline_partition if pp > 1 else None)
         pipe.assign_stages()
         if tp > 1:
             TensorParallelEngine(self, mpu, owned=pipe.owns_param, device=device,
@@ -152,7 +154,8 @@ class ParallelizationMixin:
             self.get_input_embeddings().weight._oslo_norm_dup = True
         self.initial_parameters = dict(
             tensor_parallel_size=tp, pipeline_parallel_size=pp, micro_batch_size=micro_batch_size,
-            resize_token_embeddings=resize_token_embeddings, seed=seed, sequence_parallel=sequence_parallel)
+            resize_token_embeddings=resize_token_embeddings, seed=seed, sequence_parallel=sequence_parallel,
+            pipeline_partition=list(pipeline_partition) if (pipeline_partition and pp > 1) else None)
         self.mpu = mpu
         if self.base_model is not self:
             self.base_model.mpu = mpu
@@ -175,9 +178,11 @@ class ParallelizationMixin:
     def from_config_with_parallel(cls, config, tensor_parallel_size: int = 1, pipeline_parallel_size: int = 1,
                                   micro_batch_size: int = 1, resize_token_embeddings: Optional[int] = None,
                                   seed: Optional[int] = None, deployment: Optional[bool] = None,
-                                  sequence_parallel: bool = False, init_on_device: bool = False, **kwargs: Any):
+                                  sequence_parallel: bool = False, init_on_device: bool = False,
+                                  pipeline_partition: Optional[List[int]] = None, **kwargs: Any):
         """Random-init model from ``config``, then parallelise. ``init_on_device`` builds the full
-        model on this rank's accelerator (fast for multi-billion-parameter configs) before slicing."""
+        model on this rank's accelerator (fast for multi-billion-parameter configs) before slicing.
+        ``pipeline_partition``: blocks per pipeline stage, when the even split is not wanted."""
         torch_dtype = kwargs.pop("torch_dtype", getattr(config, "torch_dtype", None))
         for k, v in kwargs.items():
             setattr(config, k, v)
@@ -190,7 +195,8 @@ class ParallelizationMixin:
             return DeploymentParallelEngine(
                 model, tensor_parallel_size=tensor_parallel_size, pipeline_parallel_size=pipeline_parallel_size,
                 micro_batch_size=micro_batch_size, resize_token_embeddings=resize_token_embeddings, seed=seed,
-                sequence_parallel=sequence_parallel, factory=(cls, config, torch_dtype)).parallelize()
+                sequence_parallel=sequence_parallel, pipeline_partition=pipeline_partition,
+                factory=(cls, config, torch_dtype)).parallelize()
         if init_on_device and torch.cuda.is_available() and not deployment:
             from .parallel.mpu import MPU
             MPU.initialize_distributed()
@@ -201,20 +207,21 @@ class ParallelizationMixin:
         return cls._parallelize_from_model(
             model, tensor_parallel_size=tensor_parallel_size, pipeline_parallel_size=pipeline_parallel_size,
             micro_batch_size=micro_batch_size, resize_token_embeddings=resize_token_embeddings, seed=seed,
-            deployment=deployment, sequence_parallel=sequence_parallel)
+            deployment=deployment, sequence_parallel=sequence_parallel, pipeline_partition=pipeline_partition)
 
     @classmethod
     def from_pretrained_with_parallel(cls, pretrained_model_name_or_path: str, tensor_parallel_size: int = 1,
                                       pipeline_parallel_size: int = 1, micro_batch_size: int = 1,
                                       resize_token_embeddings: Optional[int] = None, seed: Optional[int] = None,
                                       deployment: Optional[bool] = None, sequence_parallel: bool = False,
-                                      **kwargs: Any):
+                                      pipeline_partition: Optional[List[int]] = None, **kwargs: Any):
         """Load and parallelise. A directory holding every ``pytorch_model_tp=*_pp=*.bin`` of the
         requested layout is read shard-wise (each rank opens only its own file); anything else is
         loaded as a merged HF checkpoint on the host and sliced."""
         par = dict(tensor_parallel_size=tensor_parallel_size, pipeline_parallel_size=pipeline_parallel_size,
                    micro_batch_size=micro_batch_size, resize_token_embeddings=resize_token_embeddings,
-                   seed=seed, deployment=deployment, sequence_parallel=sequence_parallel)
+                   seed=seed, deployment=deployment, sequence_parallel=sequence_parallel,
+                   pipeline_partition=pipeline_partition)
         path = pretrained_model_name_or_path
         if os.path.isdir(path):
             names = split_checkpoint_names(tensor_parallel_size, pipeline_parallel_size)

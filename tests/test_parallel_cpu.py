@@ -804,3 +804,68 @@ def test_bucketed_ddp_with_a_torch_optimizer():
         got = torch.load(os.path.join(d, "state.pt"), weights_only=True)
     for k, v in ref.state_dict().items():
         assert torch.allclose(got[k], v, atol=2e-4), (k, float((got[k] - v).abs().max()))
+
+
+def _train_custom_partition(rank, world, kind, partition, tp, steps, expected_losses, tmpdir):
+    model = ob.parallelize(build(kind).train(), tensor_parallel_size=tp, pipeline_parallel_size=world // tp,
+                           micro_batch_size=2, pipeline_partition=partition)
+    eng = model._pipe_engine
+    assert eng.block_range == (sum(partition[:eng.stage]), sum(partition[:eng.stage + 1]))
+    assert model.initial_parameters["pipeline_partition"] == partition
+    opt = torch.optim.AdamW([p for p in model.gpu_parameters() if p.requires_grad], lr=1e-2)
+    for s in range(steps):
+        opt.zero_grad()
+        tot = 0.0
+        for out in model(**batch(seed=3 + s)):
+            out.loss.backward()
+            tot += float(out.loss)
+        assert abs(tot - expected_losses[s]) < 2e-4, (s, tot, expected_losses[s])
+        opt.step()
+    model.save_pretrained_with_parallel(os.path.join(tmpdir, "merged"), save_with_merging=True)
+    model.save_pretrained_with_parallel(os.path.join(tmpdir, "split"))
+    # a split checkpoint comes back with the partition it was written with
+    again = getattr(ob, MODEL[kind]).from_pretrained_with_parallel(
+        os.path.join(tmpdir, "split"), tensor_parallel_size=tp, pipeline_parallel_size=world // tp, micro_batch_size=2,
+        pipeline_partition=partition)
+    own, got = model.state_dict(), again.state_dict()
+    for k, v in own.items():
+        if v.numel():
+            assert torch.equal(v, got[k]), k
+
+
+@pytest.mark.parametrize("kind,partition,tp", [("gptj", [1, 3], 1), ("gpt_neo", [3, 1], 1), ("gptj", [1, 3], 2)])
+def test_pipeline_stages_with_an_uneven_partition(kind, partition, tp):
+    """``pipeline_partition=[blocks per stage]`` instead of the even split: same losses and merged weights as one
+    process; the layout survives a split-checkpoint round trip."""
+    steps = 2
+    losses, state = oracle_steps(kind, steps, micro=2)
+    with tempfile.TemporaryDirectory() as d:
+        run_distributed(_train_custom_partition, 2 * tp, kind, partition, tp, steps, losses, d)
+        _check_merged(d, state, atol=2e-4)
+
+
+def test_pipeline_partition_is_validated():
+    from oslo_b200.parallel.engine_pipeline import PipelineParallelEngine
+
+    class _M:
+        def num_blocks(self):
+            return 4
+
+    class _Mpu:
+        device = torch.device("cpu")
+
+        def get_pipeline_parallel_world_size(self):
+            return 2
+
+        def get_pipeline_parallel_rank(self):
+            return 0
+
+        @staticmethod
+        def make_pipeline_partition(n, p):
+            return [0, 2, 4]
+
+    assert PipelineParallelEngine(_M(), _Mpu())._bounds() == [0, 2, 4]
+    assert PipelineParallelEngine(_M(), _Mpu(), partition=[1, 3])._bounds() == [0, 1, 4]
+    for bad in ([4], [1, 2], [0, 4], [2, 2, 0]):
+        with pytest.raises(ValueError):
+            PipelineParallelEngine(_M(), _Mpu(), partition=bad)._bounds()

@@ -132,3 +132,62 @@ def test_vocab_embed_halves_stay_in_lockstep_for_any_token_counts():
         assert _run_vocab_embed(world, counts, 8, True, _slow_reader) == []
         assert _run_vocab_embed(world, counts * 2, 8, True, _jitter) == []
     assert _run_vocab_embed(2, counts, 8, False, _slow_reader), "the model failed to expose the drifting parities"
+
+
+def _run_fused_grid(world, grid, tiles, resident, aligned, all_ctas_wait_for_done):
+    """Discrete model of the GEMM + all-reduce kernel's dependencies. Every rank launches ``grid`` CTAs but only
+    ``resident`` of them fit on the device at once (the rest start when a resident one exits - what happens when
+    another kernel holds some SMs). CTA c PRODUCES tiles c, c + grid, ...; tile t is REDUCED on rank t % world, by
+    the CTA that produces it there (``aligned``) or by CTA (j % grid) for the j-th owned tile (the earlier assignment);
+    a reduction needs the tile from every rank. ``all_ctas_wait_for_done``: no CTA exits before every tile is final
+    (the earlier kernel); otherwise only the last CTA of the grid waits for that. Returns True when every rank's kernel
+    finishes."""
+    produced = [set() for _ in range(world)]        # per rank: tiles whose partial sums are in place
+    final = set()                                   # tiles reduced and broadcast
+    ctas = {}
+    for r in range(world):
+        owned = [t for t in range(tiles) if t % world == r]
+        for c in range(grid):
+            mine = list(range(c, tiles, grid))
+            if aligned:
+                red = [t for t in mine if t % world == r]
+            else:
+                red = [t for j, t in enumerate(owned) if j % grid == c]
+            ctas[(r, c)] = dict(state="queued", prod=mine, red=red)
+    for r in range(world):
+        for c in range(min(resident, grid)):
+            ctas[(r, c)]["state"] = "run"
+    while True:
+        progress = False
+        for (r, c), s in ctas.items():
+            if s["state"] != "run":
+                continue
+            if s["prod"]:                                   # the tensor-core part never waits for anybody
+                produced[r].update(s["prod"])
+                s["prod"] = []
+                progress = True
+            while s["red"] and all(s["red"][0] in produced[q] for q in range(world)):
+                final.add(s["red"].pop(0))
+                progress = True
+            must_see_all = all_ctas_wait_for_done or c == grid - 1    # the highest-index CTA: started after all others
+            if not s["red"] and (not must_see_all or len(final) == tiles):
+                s["state"] = "done"
+                progress = True
+                nxt = next((k for k in range(grid) if ctas[(r, k)]["state"] == "queued"), None)
+                if nxt is not None:
+                    ctas[(r, nxt)]["state"] = "run"        # the freed SM takes the next CTA of the grid
+        if all(s["state"] == "done" for s in ctas.values()):
+            return True
+        if not progress:
+            return False
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_gemm_collective_does_not_need_its_whole_grid_resident(world):
+    grid, tiles = 16, 112
+    for resident in (16, 15, 9, 1):
+        assert _run_fused_grid(world, grid, tiles, resident, aligned=True, all_ctas_wait_for_done=False)
+    # the earlier kernel: fine when every CTA is resident, stuck as soon as one is not
+    assert _run_fused_grid(world, grid, tiles, 16, aligned=False, all_ctas_wait_for_done=True)
+    assert not _run_fused_grid(world, grid, tiles, 15, aligned=False, all_ctas_wait_for_done=True)
+    assert not _run_fused_grid(world, grid, tiles, 15, aligned=True, all_ctas_wait_for_done=True)
