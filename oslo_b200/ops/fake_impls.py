@@ -100,3 +100,12 @@ def register() -> None:
     @reg("oslo_b200::sumsq")
     def _(x):
         return x.new_empty((1,), dtype=torch.float32)
+
+    @reg("oslo_b200::gemm_ce_stats")
+    def _(a, b, b_mn, bias, labels, vocab_start):
+        s = a.new_empty((a.size(0),), dtype=torch.float32)
+        return s, torch.empty_like(s), torch.empty_like(s)
+
+    @reg("oslo_b200::gemm_ce_grad")
+    def _(a, b, b_mn, bias, labels, vocab_start, lse, scale):
+        return a.new_empty((a.size(0), b.size(1) if b_mn else b.size(0)))

@@ -179,19 +179,6 @@ class P2PCommunicator:
             for t in tensors:
                 t.record_stream(cur)
 
-    # one-tensor conveniences (kept for callers written against the earlier interface)
-    def send_forward(self, t: Tensor, dst_stage: int):
-        return self.send([t], dst_stage, "fwd")[0]
-
-    def recv_forward(self, t: Tensor, src_stage: int):
-        return self.recv([t], src_stage, "fwd")[0]
-
-    def send_backward(self, t: Tensor, dst_stage: int):
-        return self.send([t], dst_stage, "bwd")[0]
-
-    def recv_backward(self, t: Tensor, src_stage: int):
-        return self.recv([t], src_stage, "bwd")[0]
-
 
 class _StageModule(nn.ModuleList):
     """This rank's modules; calling it runs the pipeline generator (what DDP / ZeRO wrappers call)."""

@@ -138,6 +138,11 @@ def test_fake_tensor_implementations_trace_without_a_gpu():
         ln, mean, rstd = ext.layernorm_fwd(a, torch.empty(128, dtype=torch.bfloat16, device="cuda"), None, 1e-5)
         assert ln.shape == a.shape and mean.shape == (64,) and mean.dtype == torch.float32
         assert ext.gemv_rows(a[:2], None, w, None, -1).shape == (2, 256)
+        labels = torch.empty(64, dtype=torch.long, device="cuda")
+        mx, se, tg = ext.gemm_ce_stats(a, w, 0, None, labels, 0)
+        assert mx.shape == se.shape == tg.shape == (64,) and mx.dtype == torch.float32
+        d = ext.gemm_ce_grad(a, w, 0, None, labels, 0, mx, se)
+        assert d.shape == (64, 256) and d.dtype == torch.bfloat16
 
 
 def test_debug_sync_wrapper_reports_the_failing_operator(monkeypatch):
