@@ -183,7 +183,10 @@ class DistributedDataParallel(nn.Module):
         covered = {id(p) for m in units for p in m.parameters()}
         if any(id(p) not in covered for p in self.buf.params):
             raise RuntimeError("a parameter belongs to no forward unit")    # cannot happen by construction
-        gm.register_state_dict_pre_hook(lambda *a, **k: self.finish_param_sync())
+        # checkpoints read the parameters without running a forward pass: wait for every bucket first. Under pipeline
+        # parallelism the stage module is not a registered child of the model, so both get the hook.
+        for m in {id(x): x for x in (gm, self.module)}.values():
+            m.register_state_dict_pre_hook(lambda *a, **k: self.finish_param_sync())
         opt.param_gather = self._gather_params
 
     def _gather_params(self) -> None:
