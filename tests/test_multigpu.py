@@ -443,13 +443,20 @@ def test_deployment_launcher_on_gpus():
     set_seed(41)
     with torch.device("cuda", 0):
         one = ob.GPTJForCausalLM._from_config(cfg16, torch_dtype=torch.bfloat16).eval().fuse()
-    want = one.generate(ids.cuda(), max_new_tokens=16, eos_token_id=None, pad_token_id=0).cpu()
+    with torch.no_grad():
+        want_logits = one(input_ids=ids.cuda()).logits.float().cpu()
     model = ob.GPTJForCausalLM.from_config_with_parallel(cfg16, tensor_parallel_size=2, seed=41, deployment=True,
                                                          init_on_device=True, torch_dtype=torch.bfloat16).fuse()
     try:
-        for _ in range(2):                           # the second call replays the captured step
-            got = model.generate(ids, max_new_tokens=16, eos_token_id=None, pad_token_id=0, cuda_graph=True)
-        assert got.shape == want.shape == (2, 28) and torch.equal(got[:, :12], ids)
-        assert (got == want).float().mean() > 0.7, (got, want)      # bf16 near-ties may flip a late token
+        # tokens of a random-init model sit on near-ties that bf16 rounding may flip, so the comparison with one GPU
+        # is made on the logits; the decode loop is checked for what must hold exactly
+        logits = model(input_ids=ids).logits.float()
+        assert logits.shape == want_logits.shape
+        assert (logits - want_logits).abs().max() <= 0.05 * want_logits.abs().max() + 1e-3
+        outs = [model.generate(ids, max_new_tokens=16, eos_token_id=None, pad_token_id=0, cuda_graph=True)
+                for _ in range(2)]                   # the second call replays the captured step
+        assert outs[0].shape == (2, 28) and torch.equal(outs[0][:, :12], ids)
+        assert torch.equal(outs[0], outs[1])
+        assert int(outs[0].min()) >= 0 and int(outs[0].max()) < 2048
     finally:
         model.cpu()
