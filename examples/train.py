@@ -48,6 +48,9 @@ def parse_args():
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--pp", type=int, default=1)
     ap.add_argument("--sequence-parallel", action="store_true")
+    ap.add_argument("--pipeline-partition", default=None,
+                    help="blocks per pipeline stage: 'balanced' (fewer blocks where the LM head and the loss run), a "
+                         "comma-separated list such as 7,7,8,6, or nothing for the even split")
     ap.add_argument("--batch-size", type=int, default=8, help="sequences per model replica per step")
     ap.add_argument("--micro-batch-size", type=int, default=None)
     ap.add_argument("--seq", type=int, default=128)
@@ -74,6 +77,16 @@ def build_model(args, dtype):
                micro_batch_size=args.micro_batch_size or args.batch_size, seed=args.seed,
                sequence_parallel=args.sequence_parallel)
     source = args.save if args.resume else args.init
+    if args.pipeline_partition and args.pp > 1:
+        if args.pipeline_partition == "balanced":
+            from oslo_b200.parallel.engine_pipeline import balanced_partition
+            if args.tiny:
+                blocks = cfg_cls(**tiny).num_hidden_layers
+            else:
+                blocks = (cfg_cls.from_pretrained(source) if source else cfg_cls.from_json_file(args.config)).num_hidden_layers
+            par["pipeline_partition"] = balanced_partition(blocks, args.pp)
+        else:
+            par["pipeline_partition"] = [int(n) for n in args.pipeline_partition.split(",")]
     if source:
         return model_cls.from_pretrained_with_parallel(source, torch_dtype=dtype, **par)
     if args.tiny:

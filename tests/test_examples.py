@@ -59,6 +59,15 @@ def test_preprocess_train_resume_merge_generate(tmp_path):
     for k in a:
         assert torch.equal(a[k], b[k]), k
 
+    # the 4 blocks split 3 + 1 over the two stages instead of 2 + 2: where the stage boundary lies does not change
+    # the result (up to the summation order of the gradient norm over the ranks)
+    uneven = str(tmp_path / "uneven")
+    _torchrun(4, "train.py", *common, "--pipeline-partition", "balanced", "--steps", "4", "--save", uneven, "--merge")
+    c = torch.load(os.path.join(uneven, "merged", "pytorch_model.bin"), weights_only=True)
+    assert a.keys() == c.keys()
+    for k in a:
+        assert torch.allclose(a[k], c[k], atol=1e-5, rtol=1e-4), k
+
     gen = _run([sys.executable, os.path.join(EX, "generate.py"), "--model", "gptj", "--checkpoint",
                 os.path.join(full, "merged"), "--prompt", "the quick", "--max-new-tokens", "8", "--num-beams", "2"])
     assert gen.stdout.startswith("the quick") and "8 new tokens" in gen.stderr
