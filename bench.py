@@ -61,8 +61,9 @@ def parse_args():
     ap.add_argument("--even-partition", action="store_true",
                     help="pipeline parallel: the same number of blocks on every stage (default: the last stage, which "
                          "also runs the LM head and the loss, gets fewer blocks)")
-    ap.add_argument("--also-timeout", type=float, default=420.0,
-                    help="seconds the extra configurations may take before the headline is printed without them")
+    ap.add_argument("--also-timeout", type=float, default=240.0,
+                    help="seconds the extra configurations may take before the headline is printed without them (at "
+                         "least; the limit grows to 1.5 x the headline configuration's own run time per extra block)")
     ap.add_argument("--checkpoint-activations", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--mode", default="train", choices=["train", "decode"],
@@ -155,8 +156,9 @@ def default_plan(world: int):
         return dict(name="tp4", tp=4, pp=1), [dp_block]
     if world == 8:
         # global batch 64 x 2048 as 16 micro-batches of 4 sequences through 4 stages of 7 layers, each stage on 2 GPUs
+        # (extra blocks: the data-parallel one first, it is the same code as on 2 and 4 GPUs)
         return (dict(name="tp2xpp4", tp=2, pp=4, micro=4),
-                [dict(name="tp8_b8x2048", tp=8, pp=1, replica_batch=8, micro=8), dp_block])
+                [dp_block, dict(name="tp8_b8x2048", tp=8, pp=1, replica_batch=8, micro=8)])
     return dp_block, []
 
 
@@ -385,7 +387,9 @@ def main() -> None:
             line["also"] = also
         print(json.dumps(line), flush=True)
 
+    t_primary = time.time()
     block = run_train_config(args, primary, dims, world, rank, local, dev)
+    t_primary = time.time() - t_primary
     also = {}
     printed = threading.Event()
 
@@ -395,11 +399,12 @@ def main() -> None:
             return
         printed.set()
         if rank == 0:
-            emit(block, dict(also, error=f"extra configurations not finished within {args.also_timeout} s"))
+            emit(block, dict(also, error=f"extra configurations not finished within {also_limit:.0f} s"))
         sys.stdout.flush()
         os._exit(0)
 
-    guard = threading.Timer(args.also_timeout, give_up) if extra else None
+    also_limit = max(args.also_timeout, 1.5 * t_primary * len(extra))
+    guard = threading.Timer(also_limit, give_up) if extra else None
     if guard is not None:
         guard.daemon = True
         guard.start()

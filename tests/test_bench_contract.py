@@ -97,4 +97,4 @@ def test_default_plan_follows_the_model_parallel_sweep():
     assert (names[4][0]["tp"], names[4][0]["pp"]) == (4, 1)
     p8, also8 = names[8]
     assert (p8["tp"], p8["pp"], p8["micro"]) == (2, 4, 4)          # 64 sequences as 16 micro-batches of 4
-    assert [a["name"] for a in also8] == ["tp8_b8x2048", "dp8_zero1"] and also8[0]["replica_batch"] == 8
+    assert [a["name"] for a in also8] == ["dp8_zero1", "tp8_b8x2048"] and also8[1]["replica_batch"] == 8
