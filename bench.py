@@ -312,6 +312,7 @@ def run_train_config(args, spec, dims, world, rank, local, dev):
     from oslo_b200.parallel import fused_tp, symmetric
     fused_tp._CONTEXTS.clear()
     symmetric._WORKSPACES.clear()
+    symmetric._CE_COMBINERS.clear()
     ext.set_reserved_sms(0)          # a pipeline-parallel configuration keeps a few SMs off the GEMM grids; the next one decides anew
     gc.collect()
     torch.cuda.synchronize()
