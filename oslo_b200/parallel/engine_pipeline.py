@@ -136,6 +136,7 @@ class P2PCommunicator:
                     if rs == ranks and stage in (s, s + 1):
                         self._chan[(s, direction)] = g
         self.side = torch.cuda.Stream() if (mpu.backend == "nccl" and torch.cuda.is_available()) else None
+        mpu._p2p_communicator = self         # what MPU.get_p2p_communication_groups() / MPU.p2p() look up
 
     def _rank(self, stage: int) -> int:
         return self.mpu.stage_to_global_rank(stage)

@@ -252,8 +252,37 @@ class MPU:
         return self._pp_ranks[stage]
 
     def get_p2p_communication_groups(self):
-        """Point-to-point traffic uses send/recv on the default group; no per-pair groups exist."""
-        return {}
+        """``{(source global rank, destination global rank): two-rank group}`` for the neighbour channels this rank
+        takes part in (reference: oslo/parallelism/mpu.py:321-368). The groups belong to the pipeline engine's
+        ``P2PCommunicator`` - one per neighbour pair and direction - and exist once a pipeline-parallel model has been
+        built on this MPU; before that the dict is empty and ``p2p`` sends over the pipeline group."""
+        comm = getattr(self, "_p2p_communicator", None)
+        if comm is None:
+            return {}
+        out = {}
+        for (lower, direction), g in comm._chan.items():
+            a, b = self._pp_ranks[lower], self._pp_ranks[lower + 1]
+            out[(a, b) if direction == "fwd" else (b, a)] = g
+        return out
+
+    def p2p(self, tensor: Tensor, src_stage: int, dst_stage: int) -> bool:
+        """Move ``tensor`` from pipeline stage ``src_stage`` to the neighbouring stage ``dst_stage`` (in place on the
+        receiver). Every rank of a pipeline group may call it with the same arguments; it returns True on the two
+        ranks that took part and False elsewhere. The reference emulates the transfer with a broadcast in a two-rank
+        group (oslo/parallelism/mpu.py:892-920); here it is a send / receive on that pair's channel."""
+        pp = self.get_pipeline_parallel_world_size()
+        if not (0 <= src_stage < pp and 0 <= dst_stage < pp) or abs(src_stage - dst_stage) != 1:
+            raise ValueError(f"p2p needs two neighbouring pipeline stages, got src={src_stage}, dst={dst_stage}")
+        me = self.get_pipeline_parallel_rank()
+        if me not in (src_stage, dst_stage):
+            return False
+        src, dst = self._pp_ranks[src_stage], self._pp_ranks[dst_stage]
+        group = self.get_p2p_communication_groups().get((src, dst), self._pp_group)
+        if me == src_stage:
+            dist.send(tensor.contiguous(), dst, group=group)
+        else:
+            dist.recv(tensor, src, group=group)
+        return True
 
     def get_p2p_communication_world_size(self) -> int:
         return 2

@@ -36,3 +36,42 @@ def test_one_f_one_b_order():
                 peak = max(peak, live)
                 assert live >= 0
             assert peak <= P - s
+
+
+def _p2p_ranks(rank, world):
+    import torch
+    import oslo_b200 as ob
+
+    # before any pipeline engine exists: the transfer runs over the pipeline group, no per-pair groups yet
+    mpu = MPU(1, world)
+    assert mpu.get_p2p_communication_groups() == {}
+    t = torch.full((3,), float(rank))
+    took_part = mpu.p2p(t, 1, 2)
+    assert took_part == (rank in (1, 2))
+    assert t.tolist() == [1.0] * 3 if rank == 2 else t.tolist() == [float(rank)] * 3
+    t = torch.full((3,), float(rank))
+    assert mpu.p2p(t, 1, 0) == (rank in (0, 1))          # towards the first stage
+    assert t[0].item() == (1.0 if rank == 0 else float(rank))
+    for bad in ((0, 2), (0, 0), (-1, 0), (world - 1, world)):
+        try:
+            mpu.p2p(t, *bad)
+        except ValueError:
+            continue
+        raise AssertionError(f"stages {bad} were accepted")
+
+    # with a pipeline-parallel model: the engine's channels, keyed by (source rank, destination rank)
+    cfg = ob.GPTJConfig(vocab_size=64, n_positions=16, n_embd=16, n_layer=4, n_head=2, rotary_dim=4)
+    model = ob.parallelize(ob.GPTJForCausalLM(cfg), pipeline_parallel_size=world, micro_batch_size=1)
+    groups = model.mpu.get_p2p_communication_groups()
+    want = {(a, b) for a in range(world) for b in range(world) if abs(a - b) == 1 and rank in (a, b)}
+    assert set(groups) == want
+    t = torch.full((2,), float(rank))
+    assert model.mpu.p2p(t, 2, 3) == (rank in (2, 3))
+    assert t[0].item() == (2.0 if rank == 3 else float(rank))
+
+
+def test_p2p_between_neighbouring_stages():
+    """``mpu.p2p(tensor, src_stage, dst_stage)`` and ``get_p2p_communication_groups()`` of the reference's MPU
+    (oslo/parallelism/mpu.py:321-368, :892-920) on 4 pipeline stages."""
+    from tests.dist_utils import run_distributed
+    run_distributed(_p2p_ranks, 4)
