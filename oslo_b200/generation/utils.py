@@ -131,11 +131,14 @@ class GenerationMixin:
                  repetition_penalty: Optional[float] = None, bad_words_ids: Optional[List[List[int]]] = None,
                  bos_token_id: Optional[int] = None, pad_token_id: Optional[int] = None,
                  eos_token_id: Optional[int] = None, length_penalty: Optional[float] = None,
-                 no_repeat_ngram_size: Optional[int] = None, num_return_sequences: Optional[int] = None,
+                 no_repeat_ngram_size: Optional[int] = None, encoder_no_repeat_ngram_size: Optional[int] = None,
+                 num_return_sequences: Optional[int] = None,
                  max_time: Optional[float] = None, max_new_tokens: Optional[int] = None,
+                 decoder_start_token_id: Optional[int] = None,
                  use_cache: Optional[bool] = None, num_beam_groups: Optional[int] = None,
                  diversity_penalty: Optional[float] = None,
                  prefix_allowed_tokens_fn: Optional[Callable[[int, Tensor], List[int]]] = None,
+                 output_attentions: Optional[bool] = None, output_hidden_states: Optional[bool] = None,
                  output_scores: bool = False, return_dict_in_generate: bool = False,
                  forced_bos_token_id: Optional[int] = None, forced_eos_token_id: Optional[int] = None,
                  remove_invalid_values: Optional[bool] = None, synced_gpus: bool = False,
@@ -143,7 +146,13 @@ class GenerationMixin:
                  cuda_graph: bool = False, **model_kwargs) -> Union[Tensor, GenerateOutput]:
         """``cuda_graph=True`` (not in the reference) runs plain greedy decoding - one beam, no sampling, no logits
         processors, no attention mask - through ``GraphedGreedyDecoder``: eager prefill, then one CUDA-graph replay per
-        token. Any other combination ignores the flag."""
+        token. Any other combination ignores the flag.
+
+        ``output_attentions`` / ``output_hidden_states`` with ``return_dict_in_generate=True`` add ``attentions`` /
+        ``hidden_states`` to the result: one entry per generated token, each a tuple over the layers, as the reference's
+        decoder-only outputs do (oslo/generation_utils.py:53-121). ``encoder_no_repeat_ngram_size`` and
+        ``decoder_start_token_id`` exist in the signature for call compatibility; they only mean something for
+        encoder-decoder models, which this package (like the reference's model zoo) does not have."""
         cfg = self.config
 
         def pick(v, name, default=None):
@@ -199,6 +208,11 @@ class GenerationMixin:
         if num_beam_groups > num_beams:
             raise ValueError("num_beam_groups must be <= num_beams")
         model_kwargs["use_cache"] = use_cache
+        want_att = bool(pick(output_attentions, "output_attentions", False))
+        want_hid = bool(pick(output_hidden_states, "output_hidden_states", False))
+        if return_dict_in_generate and (want_att or want_hid):
+            model_kwargs["_gen_trace"] = {"attentions": [] if want_att else None, "hidden_states": [] if want_hid else None}
+            cuda_graph = False                         # the captured step returns token ids only
         if use_cache and use_static_cache and model_kwargs.get("past_key_values") is None:
             from ..models.common import StaticKVCache
             model_kwargs["past_key_values"] = StaticKVCache(max_length)
@@ -268,9 +282,23 @@ class GenerationMixin:
 
     def _step_logits(self, input_ids, model_kwargs):
         inputs = self.prepare_inputs_for_generation(input_ids, **model_kwargs)
+        trace = model_kwargs.get("_gen_trace")
+        if trace is not None:
+            inputs["output_attentions"] = trace["attentions"] is not None
+            inputs["output_hidden_states"] = trace["hidden_states"] is not None
         out = self._gen_forward(inputs)
+        if trace is not None:
+            for key in ("attentions", "hidden_states"):
+                if trace[key] is not None:
+                    trace[key].append(out.get(key) if hasattr(out, "get") else None)
         logits = out["logits"][:, -1, :].float()
         return out, logits
+
+    @staticmethod
+    def _traced(model_kwargs) -> Dict[str, Any]:
+        """``attentions`` / ``hidden_states`` collected by ``_step_logits`` (one tuple over the layers per step)."""
+        trace = model_kwargs.get("_gen_trace") or {}
+        return {k: tuple(v) for k, v in trace.items() if v is not None}
 
     def _finish(self, sequences, scores, return_dict, **extra):
         if return_dict:
@@ -298,7 +326,7 @@ class GenerationMixin:
             done = bool(unfinished.max() == 0) or stops(input_ids, scores)
             if self._all_done(done, synced_gpus):
                 break
-        return self._finish(input_ids, scores, return_dict_in_generate)
+        return self._finish(input_ids, scores, return_dict_in_generate, **self._traced(model_kwargs))
 
     def sample(self, input_ids, logits_processor=None, stopping_criteria=None, logits_warper=None,
                pad_token_id=None, eos_token_id=None, output_scores=False, return_dict_in_generate=False,
@@ -322,7 +350,7 @@ class GenerationMixin:
             done = bool(unfinished.max() == 0) or stops(input_ids, scores)
             if self._all_done(done, synced_gpus):
                 break
-        return self._finish(input_ids, scores, return_dict_in_generate)
+        return self._finish(input_ids, scores, return_dict_in_generate, **self._traced(model_kwargs))
 
     def _beam_loop(self, input_ids, scorer: BeamSearchScorer, procs, stops, warper, sample: bool, pad_token_id,
                    eos_token_id, output_scores, return_dict_in_generate, synced_gpus, model_kwargs):
@@ -367,7 +395,8 @@ class GenerationMixin:
             if self._all_done(done, synced_gpus):
                 break
         fin = scorer.finalize(input_ids, beam_scores, stops.max_length or cur_len, pad_token_id, eos_token_id)
-        return self._finish(fin["sequences"], scores, return_dict_in_generate, sequences_scores=fin["sequence_scores"])
+        return self._finish(fin["sequences"], scores, return_dict_in_generate, sequences_scores=fin["sequence_scores"],
+                            **self._traced(model_kwargs))
 
     def beam_search(self, input_ids, beam_scorer, logits_processor=None, stopping_criteria=None, pad_token_id=None,
                     eos_token_id=None, output_scores=False, return_dict_in_generate=False, synced_gpus=False,
@@ -434,4 +463,5 @@ class GenerationMixin:
             if self._all_done(done, synced_gpus):
                 break
         fin = beam_scorer.finalize(input_ids, beam_scores, stops.max_length or cur_len, pad_token_id, eos_token_id)
-        return self._finish(fin["sequences"], scores, return_dict_in_generate, sequences_scores=fin["sequence_scores"])
+        return self._finish(fin["sequences"], scores, return_dict_in_generate, sequences_scores=fin["sequence_scores"],
+                            **self._traced(model_kwargs))

@@ -294,3 +294,39 @@ def test_low_cpu_mem_usage_skips_redundant_initialisation(tmp_path):
     assert torch.isfinite(w).all() and 0.005 < float(w.std()) < 0.05    # initializer_range 0.02, not raw memory
     fresh = ob.GPTJForCausalLM(cfg)
     assert float(fresh.lm_head.weight.std()) > 0.005                     # ordinary construction still initialises
+
+
+@pytest.mark.parametrize("kind,beams", [("gpt2", 1), ("gptj", 1), ("gpt_neo", 2)])
+def test_generate_returns_attentions_and_hidden_states_like_hf(kind, beams):
+    """``generate(..., output_attentions=True, output_hidden_states=True, return_dict_in_generate=True)``: one entry
+    per generated token, each a tuple over the layers, as in HF (the first entry covers the prompt). The arguments of
+    encoder-decoder models are accepted and change nothing."""
+    ours, hf = _pair(kind)
+    x = torch.randint(1, 97, (2, 6))
+    kw = dict(max_new_tokens=4, num_beams=beams, eos_token_id=None, pad_token_id=0, output_attentions=True,
+              output_hidden_states=True, output_scores=True, return_dict_in_generate=True)
+    a = ours.generate(x, use_static_cache=False, encoder_no_repeat_ngram_size=3, decoder_start_token_id=1, **kw)
+    b = hf.generate(x, do_sample=False, **kw)
+    assert torch.equal(a.sequences, b.sequences)
+    assert len(a.hidden_states) == len(b.hidden_states) == 4 and len(a.attentions) == 4
+    for step, (p, q) in enumerate(zip(a.hidden_states, b.hidden_states)):
+        assert len(p) == len(q) == 3                           # embeddings + 2 layers
+        for u, v in zip(p, q):
+            assert u.shape == v.shape and u.shape[1] == (6 if step == 0 else 1)
+            assert torch.allclose(u, v, atol=3e-4)
+    for step, (p, q) in enumerate(zip(a.attentions, b.attentions)):
+        assert len(p) == 2
+        for u in p:
+            assert u.shape[0] == 2 * beams and u.shape[-2] == (6 if step == 0 else 1) and u.shape[-1] == 6 + step
+            assert torch.allclose(u.sum(-1), torch.ones_like(u.sum(-1)), atol=1e-4)
+        for u, v in zip(p, q):                                 # empty when HF runs its fused attention path
+            if v is not None:
+                assert torch.allclose(u, v, atol=3e-4)
+    # the default static cache gives the same tokens and states; without return_dict_in_generate nothing is collected
+    c = ours.generate(x, **kw)
+    assert torch.equal(c.sequences, a.sequences) and len(c.attentions) == 4
+    for p, q in zip(c.hidden_states, a.hidden_states):
+        for u, v in zip(p, q):
+            assert torch.allclose(u, v, atol=1e-5)
+    plain = ours.generate(x, max_new_tokens=4, eos_token_id=None, pad_token_id=0, output_attentions=True)
+    assert torch.is_tensor(plain) and plain.shape == (2, 10)
