@@ -15,6 +15,9 @@ import torch
 
 class GPT2OnnxConfig:
     default_onnx_opset = 13
+    # names of the config fields that hold the layer count, the head count and the hidden size (sub-classes for other
+    # decoder families only change these)
+    _layers_attr, _heads_attr, _hidden_attr = "n_layer", "n_head", "n_embd"
 
     def __init__(self, config, task: str = "default", use_past: bool = False) -> None:
         self._config = config
@@ -27,11 +30,11 @@ class GPT2OnnxConfig:
 
     @property
     def num_layers(self) -> int:
-        return self._config.n_layer
+        return getattr(self._config, self._layers_attr)
 
     @property
     def num_attention_heads(self) -> int:
-        return self._config.n_head
+        return getattr(self._config, self._heads_attr)
 
     @property
     def inputs(self) -> Mapping[str, Mapping[int, str]]:
@@ -67,7 +70,7 @@ class GPT2OnnxConfig:
         past = 0
         if self.use_past:
             past = seq + 2       # a past length that differs from the sequence length, so the two axes cannot be confused
-            head_dim = self._config.n_embd // self._config.n_head
+            head_dim = getattr(self._config, self._hidden_attr) // self.num_attention_heads
             shape = (batch, self.num_attention_heads, past, head_dim)
             ordered["past_key_values"] = [(torch.zeros(shape), torch.zeros(shape)) for _ in range(self.num_layers)]
         ordered["attention_mask"] = torch.ones(batch, past + seq, dtype=torch.long)

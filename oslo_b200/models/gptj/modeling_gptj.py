@@ -23,6 +23,28 @@ from ..common import (AttentionCore, CausalLMHeadMixin, DecoderBackbone, Sequenc
                       maybe_dropout, merge_heads, to_token_rows)
 
 
+def fixed_pos_embedding(x: Tensor, seq_dim: int = 1, seq_len: Optional[int] = None):
+    """``(sin, cos)`` tables ``[seq_len, x.shape[-1] // 2]`` for positions ``0 .. seq_len - 1`` (fp32, on ``x``'s device).
+    The three rotary helpers below keep the names and call conventions of the reference's module-level functions
+    (oslo/models/gptj/modeling_gptj.py:49-77) for code that imports them; the model itself goes through
+    ``ops.rotary_interleaved`` (one kernel on GPUs)."""
+    n = x.shape[seq_dim] if seq_len is None else int(seq_len)
+    return ops.reference.rotary_tables(torch.arange(n, device=x.device), x.shape[-1])
+
+
+def rotate_every_two(x: Tensor) -> Tensor:
+    """``(x0, x1, x2, x3, ...) -> (-x1, x0, -x3, x2, ...)`` along the last dimension."""
+    pairs = x.unflatten(-1, (-1, 2))
+    return torch.stack((-pairs[..., 1], pairs[..., 0]), dim=-1).flatten(-2)
+
+
+def apply_rotary_pos_emb(x: Tensor, sincos, offset: int = 0) -> Tensor:
+    """Rotate ``x`` ``[batch, seq, heads, dim]`` by the table rows ``offset .. offset + seq`` (each sin / cos value
+    serves one pair of neighbouring dimensions)."""
+    sin, cos = (t[offset: offset + x.shape[1]].repeat_interleave(2, dim=-1)[None, :, None, :] for t in sincos)
+    return x * cos + rotate_every_two(x) * sin
+
+
 class GPTJConfig(PretrainedConfig):
     model_type = "gptj"
     attribute_map = {"max_position_embeddings": "n_positions", "hidden_size": "n_embd",

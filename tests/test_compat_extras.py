@@ -85,6 +85,75 @@ def test_gpt2_onnx_config_describes_inputs_outputs_and_dummy_inputs():
     assert out.logits.shape == (2, 8, cfg.vocab_size)
 
 
+def _tiny_neo():
+    torch.manual_seed(0)
+    return ob.GPTNeoForCausalLM(ob.GPTNeoConfig(vocab_size=61, max_position_embeddings=32, hidden_size=16, num_layers=2,
+                                                num_heads=2, window_size=4, attention_types=[[["global", "local"], 1]]))
+
+
+def test_gpt_neo_tf_checkpoint_loader(monkeypatch):
+    """Mesh-tensorflow variable names of the GPT-Neo release (projection matrices stored [in, out], a vocabulary padded
+    beyond ``vocab_size``, optimizer slots beside the weights) against a stand-in ``tensorflow.train``."""
+    from oslo_b200.models.gpt_neo.convert_tf import load_tf_weights_in_gpt_neo, tf_name_to_key
+    assert tf_name_to_key("gpt2/h11/attn/q") == ("transformer.h.11.attn.attention.q_proj.weight", True)
+    assert tf_name_to_key("gpt2/h0/attn/compute_output_bias/o_b") == ("transformer.h.0.attn.attention.out_proj.bias", False)
+    assert tf_name_to_key("gpt2/h2/mlp/conv1d_main/c_proj/kernel") == ("transformer.h.2.mlp.c_proj.weight", True)
+    assert tf_name_to_key("gpt2/h2/norm_2/g") == ("transformer.h.2.ln_2.weight", False)
+    assert tf_name_to_key("gpt2/ln_f/b") == ("transformer.ln_f.bias", False)
+    assert tf_name_to_key("gpt2/h2/attn/q/adam_m") is None and tf_name_to_key("global_step") is None
+    src = _tiny_neo().eval()
+    store = {}
+    rev = {"q_proj": "q", "k_proj": "k", "v_proj": "v", "out_proj": "o"}
+    for key, p in src.named_parameters():
+        if key.startswith("lm_head"):
+            continue
+        parts = key.replace("transformer.", "").split(".")
+        arr = p.detach().numpy().copy()
+        if parts[0] in ("wte", "wpe"):
+            if parts[0] == "wte":
+                arr = np.concatenate([arr, np.zeros((3, arr.shape[1]), arr.dtype)])       # padded vocabulary
+            store["gpt2/" + parts[0]] = arr
+        elif parts[0] == "ln_f":
+            store["gpt2/ln_f/" + ("g" if parts[-1] == "weight" else "b")] = arr
+        else:
+            h, rest = "gpt2/h" + parts[1], parts[2:]
+            if rest[0] in ("ln_1", "ln_2"):
+                store[f"{h}/norm_{rest[0][-1]}/" + ("g" if rest[-1] == "weight" else "b")] = arr
+            elif rest[0] == "attn":
+                if rest[-1] == "bias":
+                    store[f"{h}/attn/compute_output_bias/o_b"] = arr
+                else:
+                    store[f"{h}/attn/{rev[rest[2]]}"] = arr.T.copy()
+                    store[f"{h}/attn/{rev[rest[2]]}/adam_v"] = np.ones_like(arr)
+            else:
+                store[f"{h}/mlp/conv1d_main/{rest[1]}/" + ("kernel" if rest[-1] == "weight" else "bias")] = \
+                    arr.T.copy() if rest[-1] == "weight" else arr
+    store["global_step"] = np.zeros(())
+    fake = types.ModuleType("tensorflow")
+    fake.train = types.SimpleNamespace(list_variables=lambda path: [(k, list(v.shape)) for k, v in store.items()],
+                                       load_variable=lambda path, name: store[name])
+    monkeypatch.setitem(sys.modules, "tensorflow", fake)
+    torch.manual_seed(5)
+    dst = ob.GPTNeoForCausalLM(src.config).eval()
+    ids = torch.randint(0, 61, (2, 8))
+    assert not torch.allclose(dst(input_ids=ids).logits, src(input_ids=ids).logits)
+    ob.load_tf_weights_in_gpt_neo(dst, dst.config, "/nonexistent/model.ckpt")
+    assert torch.allclose(dst(input_ids=ids).logits, src(input_ids=ids).logits, atol=1e-6)
+    assert dst.lm_head.weight.data_ptr() == dst.transformer.wte.weight.data_ptr()
+
+
+def test_gpt_neo_onnx_config():
+    cfg = _tiny_neo().config
+    oc = ob.GPTNeoOnnxConfig.with_past(cfg, task="causal-lm")
+    assert oc.num_layers == 2 and oc.num_attention_heads == 2
+    assert list(oc.outputs)[0] == "logits" and len(oc.inputs) == 2 + 2 * 2
+    d = oc.generate_dummy_inputs()
+    assert d["past_key_values"][1][1].shape == (2, 2, 10, 8) and d["attention_mask"].shape == (2, 18)
+    out = _tiny_neo().eval()(input_ids=d["input_ids"], past_key_values=d["past_key_values"],
+                             attention_mask=d["attention_mask"])
+    assert out.logits.shape == (2, 8, cfg.vocab_size)
+
+
 class DeepSpeedEngine:          # recognised by class name when DeepSpeed itself is not installed
     def __init__(self, module, stage):
         self.module, self.stage = module, stage
@@ -225,3 +294,17 @@ def test_build_blocks_mapping_matches_the_python_statement(one_sent):
         got = lib.build_blocks_mapping(docs, sizes, titles, epochs, cap, max_len, 5, use_one_sent_blocks=one_sent)
         assert got.shape == (len(want), 4)
         assert sorted(map(tuple, got.tolist())) == sorted(want)
+
+
+def test_gptj_rotary_helper_functions_agree_with_the_model_path():
+    """``fixed_pos_embedding`` / ``rotate_every_two`` / ``apply_rotary_pos_emb`` (the reference's module-level helpers,
+    oslo/models/gptj/modeling_gptj.py:49-77) against the rotary op the model uses, with a position offset."""
+    from oslo_b200 import ops
+    x = torch.randn(2, 7, 3, 16)
+    assert torch.equal(ob.rotate_every_two(torch.tensor([[[[1.0, 2.0, 3.0, 4.0]]]])), torch.tensor([[[[-2.0, 1.0, -4.0, 3.0]]]]))
+    sincos = ob.fixed_pos_embedding(x[..., :8], 1, seq_len=12)
+    assert sincos[0].shape == (12, 4) and sincos[1].dtype == torch.float32
+    got = torch.cat((ob.apply_rotary_pos_emb(x[..., :8], sincos, offset=5), x[..., 8:]), -1)
+    assert torch.allclose(got, ops.reference.rotary_interleaved(x, torch.arange(5, 12), 8), atol=1e-6)
+    full = ob.apply_rotary_pos_emb(x, ob.fixed_pos_embedding(x))
+    assert torch.allclose(full, ops.reference.rotary_interleaved(x, torch.arange(7), 16), atol=1e-6)
