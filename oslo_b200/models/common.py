@@ -159,13 +159,13 @@ class AttentionCore(nn.Module):
         sq, sk = q.size(-2), k.size(-2)
         scores = torch.matmul(q, k.transpose(-1, -2))
         if sq == sk and self.window is None and key_padding_mask is None:
-            probs = FusedScaleMaskSoftmax.apply(scores, self.scale, True)
+            probs = FusedScaleMaskSoftmax.apply(scores, None, self.scale, True)
         else:
             keep = ops.reference.attention_mask_bias(sq, sk, q.device, True, self.window)
             mask = ~keep[None, None]
             if key_padding_mask is not None:
                 mask = mask | ~key_padding_mask.to(torch.bool)[:, None, None, :]
-            probs = FusedScaleMaskSoftmax.apply(scores, self.scale, False, mask.expand(q.size(0), 1, sq, sk).to(torch.uint8))
+            probs = FusedScaleMaskSoftmax.apply(scores, mask.expand(q.size(0), 1, sq, sk), self.scale, False)
         return torch.matmul(probs, v), probs
 
     def attend_with_cache(self, q: Tensor, k: Tensor, v: Tensor, layer_past, cache: Optional[StaticKVCache],

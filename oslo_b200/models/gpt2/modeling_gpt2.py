@@ -117,7 +117,7 @@ class GPT2Attention(AttentionCore):
         else:
             mask = (encoder_attention_mask.view(b, 1, 1, sk) == 0).expand(b, 1, sq, sk).to(torch.uint8)
         if self.fused:
-            probs = FusedScaleMaskSoftmax.apply(scores, self.scale, False, mask)
+            probs = FusedScaleMaskSoftmax.apply(scores, mask, self.scale, False)
         else:
             probs = ops.reference.scaled_masked_softmax(scores, mask, self.scale)
         probs = maybe_dropout(probs, self.attn_pdrop, self.training)

@@ -308,3 +308,57 @@ def test_gptj_rotary_helper_functions_agree_with_the_model_path():
     assert torch.allclose(got, ops.reference.rotary_interleaved(x, torch.arange(5, 12), 8), atol=1e-6)
     full = ob.apply_rotary_pos_emb(x, ob.fixed_pos_embedding(x))
     assert torch.allclose(full, ops.reference.rotary_interleaved(x, torch.arange(7), 16), atol=1e-6)
+
+
+def test_fused_op_wrappers_take_the_reference_call_signatures():
+    """``Fused*.apply`` and the function-style entry points with the reference's argument orders
+    (oslo/fused_kernels_utils.py:260-479), against plain PyTorch statements."""
+    import os
+    import torch.nn.functional as F
+    from oslo_b200 import fused_kernels_utils as fk
+    torch.manual_seed(0)
+    x, bias, res = torch.randn(4, 6, 8), torch.randn(8), torch.randn(4, 6, 8)
+    assert torch.allclose(fk.FusedBiasDropout.apply(x, bias, False, 0.3), x + bias)
+    assert torch.allclose(fk.FusedBiasDropoutResidual.apply(x, bias, res, False, 0.3), x + bias + res)
+    assert torch.allclose(fk.bias_dropout_residual_inference(x, bias, res, 0.5), x + bias + res)
+    dropped = fk.bias_dropout_train(torch.ones(64, 64), None, 0.5)
+    assert 0.3 < float((dropped == 0).float().mean()) < 0.7 and float(dropped.max()) == 2.0
+    want = F.gelu(x + bias, approximate="tanh")
+    assert torch.allclose(fk.FusedBiasActivation.apply(x, bias, "gelu_new"), want, atol=1e-6)
+    assert torch.allclose(fk.FusedBiasGeLU.apply(x, bias), want, atol=1e-6)
+    assert torch.allclose(fk.bias_gelu_fwb(x, bias), want, atol=1e-6)
+    xg = x.clone().requires_grad_(True)
+    F.gelu(xg + bias, approximate="tanh").backward(res)
+    assert torch.allclose(fk.bias_gelu_bwd(res, x, bias), xg.grad, atol=1e-5)
+    # softmax: causal with an additive padding mask (the reference's convention) and with a boolean one; masked form
+    s = torch.randn(2, 3, 5, 5)
+    causal = torch.ones(5, 5, dtype=torch.bool).tril()
+    ref = torch.softmax((s * 0.5).masked_fill(~causal, float("-inf")), -1)
+    assert torch.allclose(fk.FusedScaleMaskSoftmax.apply(s, None, 0.5, True), ref, atol=1e-6)
+    assert torch.allclose(fk.ScaledUpperTriangMaskedSoftmaxFunction.apply(s.view(6, 5, 5), 0.5).view(2, 3, 5, 5), ref, atol=1e-6)
+    pad = torch.zeros(2, 1, 1, 5, dtype=torch.bool)
+    pad[0, ..., 0] = True
+    ref_pad = torch.softmax((s * 0.5).masked_fill(~causal | pad, float("-inf")), -1)
+    got = fk.FusedScaleMaskSoftmax.apply(s, pad, 0.5, True)
+    assert torch.allclose(got[1], ref_pad[1], atol=1e-6) and torch.allclose(got[0, :, 1:], ref_pad[0, :, 1:], atol=1e-4)
+    add = torch.zeros(2, 1, 1, 5).masked_fill(pad, -1e4)
+    assert torch.allclose(fk.FusedScaleMaskSoftmax.apply(s, add, 0.5, True)[0, :, 1:], ref_pad[0, :, 1:], atol=1e-4)
+    sq = torch.randn(2, 3, 4, 5)
+    ref_m = torch.softmax((sq * 2.0).masked_fill(pad, float("-inf")), -1)
+    assert torch.allclose(fk.FusedScaleMaskSoftmax.apply(sq, pad, 2.0, False), ref_m, atol=1e-4)
+    assert torch.allclose(fk.ScaledMaskedSoftmaxFunction.apply(sq, pad, 2.0), ref_m, atol=1e-4)
+    assert torch.allclose(fk.FusedScaleMaskSoftmax.apply(sq, None, None, False), torch.softmax(sq, -1), atol=1e-6)
+    assert fk.FusedScaleMaskSoftmax.is_available(torch.float16, 2, 3, 5, 5, True)
+    assert not fk.FusedScaleMaskSoftmax.is_available(torch.float16, 2, 3, 4, 5, True)
+    assert fk.FusedScaleMaskSoftmax.is_available(torch.bfloat16, 2, 3, 4, 5, False)
+    assert not fk.FusedScaleMaskSoftmax.is_available(torch.int8, 2, 3, 4, 5, False)
+    # n-gram blocking: after "7 8 7" the bigram (7, 8) bans 8
+    tokens = torch.tensor([[7, 8, 7], [1, 2, 3]])
+    lp = torch.zeros(2, 10)
+    out = fk.NGramRepeatBlockFunction.apply(tokens, lp, 2, 2, 1, 2)
+    assert out[0, 8] == float("-inf") and torch.isfinite(out[1]).all() and int(torch.isinf(out[0]).sum()) == 1
+    # builder handles
+    kb, db = fk.KernelBuilder(), fk.DatasetsBuilder()
+    assert all(os.path.isfile(f) for f in kb.sources() + db.sources()) and os.path.isdir(kb.includes()[0])
+    assert "-gencode" in kb.nvcc_args() and "-maxrregcount=64" in kb.nvcc_args(64)
+    assert db.load() is not None and hasattr(db.load(), "build_sample_idx")
