@@ -36,6 +36,36 @@ def data_path(prefix: str) -> str:
     return prefix + ".bin"
 
 
+class PathUtils:
+    """``idx_path`` / ``data_path`` under the reference's class name (oslo/data/indexing/__init__.py:8-40)."""
+
+    idx_path = staticmethod(index_path)
+    data_path = staticmethod(data_path)
+
+
+class NumpyUtils:
+    """Dtype codes of the index formats and the two int64 array helpers of the lazy index
+    (reference: oslo/data/indexing/__init__.py:43-109)."""
+
+    dtypes_by_code = DTYPE_BY_CODE
+    cody_by_dtypes = {v: k for k, v in DTYPE_BY_CODE.items()}        # (sic: the reference's spelling)
+    code_by_dtypes = cody_by_dtypes
+    element_sizes = {v: np.dtype(v).itemsize for v in DTYPE_BY_CODE.values()}
+
+    @staticmethod
+    def create_array_from_file(file, size) -> np.ndarray:
+        """``size`` int64 values read from the binary file at its current position."""
+        array = np.empty(size, dtype=np.int64)
+        got = file.readinto(array)
+        if got != array.nbytes:
+            raise EOFError(f"wanted {array.nbytes} bytes, file had {got}")
+        return array
+
+    @staticmethod
+    def write_file_from_array(file, array) -> None:
+        file.write(np.asarray(array, dtype=np.int64).tobytes(order="C"))
+
+
 def _as_numpy(item) -> np.ndarray:
     if isinstance(item, torch.Tensor):
         return item.detach().cpu().numpy()
@@ -124,6 +154,9 @@ class MMapIndex:
         return self.pointers[i], self.sizes[i]
 
 
+MmapIndex = MMapIndex      # the reference's spelling
+
+
 class MMapIndexedDataset(torch.utils.data.Dataset):
     def __init__(self, path: str) -> None:
         super().__init__()
@@ -162,6 +195,11 @@ class MMapIndexedDataset(torch.utils.data.Dataset):
             length = size - offset
         ptr += offset * self._index.dtype.itemsize
         return np.frombuffer(self._buf, dtype=self._index.dtype, count=length, offset=ptr)
+
+    @property
+    def dtype(self):
+        """Token type of the data file."""
+        return self._index.dtype
 
     @property
     def sizes(self) -> np.ndarray:
@@ -255,6 +293,16 @@ class IndexedDataset(torch.utils.data.Dataset):
             self.data_offsets = rd(self._len + 1)
             self.sizes = rd(n_sizes)
             self.doc_idx = rd(doc_count)
+
+    def read_index(self, path: str) -> None:
+        """Parse ``<path>.idx`` (what the constructor does; public under the reference's name)."""
+        self._read_index(path)
+
+    def read_data(self, path: str) -> None:
+        """Open ``<path>.bin`` unbuffered; otherwise it is opened at the first access."""
+        if self.data_file is not None:
+            self.data_file.close()
+        self.data_file = open(data_path(path), "rb", buffering=0)
 
     def _file(self):
         if self.data_file is None:

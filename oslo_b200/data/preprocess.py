@@ -49,6 +49,11 @@ class DatasetBinarizer:
     def __init__(self, impl: str = "mmap", log_interval: int = 10000) -> None:
         self.impl, self.log_interval = impl, log_interval
 
+    def create_builder(self, path: str):
+        """``(index file path, builder writing <path>.bin)`` for this binarizer's format
+        (reference: oslo/data/preprocess/binarizer.py:58-70)."""
+        return index_path(path), make_builder(data_path(path), self.impl, np.int32)
+
     def binarize(self, encoded: Iterable, save_file_name: str) -> dict:
         builder = make_builder(data_path(save_file_name), self.impl, np.int32)
         t0 = time.time()

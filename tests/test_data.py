@@ -124,3 +124,34 @@ def test_blender_sampler_loader():
     loader = D.InfiniteDataLoader(torch.utils.data.DataLoader(R(3, "x"), batch_size=2))
     seen = [next(loader) for _ in range(5)]
     assert len(seen) == 5 and loader.epoch == 2
+
+
+@pytest.mark.parametrize("impl", ["mmap", "lazy"])
+def test_builder_handles_and_index_helpers_of_the_reference_names(tmp_path, impl):
+    """``DatasetBinarizer.create_builder``, ``PathUtils``, ``NumpyUtils``, ``MMapIndexedDataset.dtype`` and the public
+    ``read_index`` / ``read_data`` of the lazy reader (oslo/data/indexing/__init__.py, lazy_indexing.py:165-264)."""
+    prefix = str(tmp_path / "hand")
+    idx, builder = D.DatasetBinarizer(impl).create_builder(prefix)
+    assert idx == D.PathUtils.idx_path(prefix) == prefix + ".idx" and D.PathUtils.data_path(prefix) == prefix + ".bin"
+    docs = [[5, 6, 7], [8], [9, 10]]
+    for d in docs:
+        builder.add_item(np.asarray(d, dtype=np.int32))
+        builder.end_document()
+    builder.finalize(idx)
+    if impl == "mmap":
+        ds = D.MMapIndexedDataset(prefix)
+        assert ds.dtype == np.int32 and D.MmapIndex is D.MMapIndex
+    else:
+        ds = D.IndexedDataset(prefix)
+        ds.read_index(prefix)
+        ds.read_data(prefix)
+        assert ds.data_file is not None and ds.num_tokens(2) == 2
+    assert [ds[i].tolist() for i in range(3)] == docs
+    assert D.NumpyUtils.dtypes_by_code[4] is np.int32 and D.NumpyUtils.cody_by_dtypes[np.uint16] == 8
+    path = tmp_path / "arr.bin"
+    with open(path, "wb") as f:
+        D.NumpyUtils.write_file_from_array(f, [3, 1, 4, 1, 5])
+    with open(path, "rb") as f:
+        assert D.NumpyUtils.create_array_from_file(f, 5).tolist() == [3, 1, 4, 1, 5]
+    with open(path, "rb") as f, pytest.raises(EOFError):
+        D.NumpyUtils.create_array_from_file(f, 6)
