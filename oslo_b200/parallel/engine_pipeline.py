@@ -20,7 +20,8 @@ from __future__ import annotations
 
 import logging
 import os
-from typing import Any, Callable, Dict, Iterator, List, Optional
+import pickle
+from typing import Any, Callable, Dict, Iterator, List, NamedTuple, Optional
 
 import torch
 import torch.distributed as dist
@@ -107,6 +108,66 @@ class _ProxyLoss(torch.autograd.Function):
         return grad, None, None
 
 
+class _TensorSlot(NamedTuple):
+    """Stand-in for a tensor inside the pickled structure of a message."""
+    index: int
+    shape: tuple
+    dtype: torch.dtype
+    requires_grad: bool
+
+
+def _strip_tensors(value: Any, tensors: List[Tensor]) -> Any:
+    """``value`` with every tensor replaced by a slot; the tensors are appended to ``tensors`` in slot order."""
+    if torch.is_tensor(value):
+        tensors.append(value)
+        return _TensorSlot(len(tensors) - 1, tuple(value.shape), value.dtype, bool(value.requires_grad))
+    if isinstance(value, dict):
+        items = [(k, _strip_tensors(v, tensors)) for k, v in value.items()]
+        try:
+            out = type(value)()
+            for k, v in items:
+                out[k] = v
+            return out
+        except Exception:      # a mapping class with a constructor of its own: ship it as a plain dict
+            return dict(items)
+    if isinstance(value, torch.Size):
+        return value
+    if isinstance(value, (list, tuple, set, frozenset)):
+        items = [_strip_tensors(v, tensors) for v in value]
+        if isinstance(value, tuple) and hasattr(value, "_fields"):
+            return type(value)(*items)
+        return type(value)(items)
+    return value
+
+
+def _collect_slots(value: Any, slots: List[_TensorSlot]) -> None:
+    if isinstance(value, _TensorSlot):
+        slots.append(value)
+    elif isinstance(value, dict):
+        for v in value.values():
+            _collect_slots(v, slots)
+    elif isinstance(value, (list, tuple, set, frozenset)) and not isinstance(value, torch.Size):
+        for v in value:
+            _collect_slots(v, slots)
+
+
+def _fill_slots(value: Any, received: Dict[int, Tensor]) -> Any:
+    if isinstance(value, _TensorSlot):
+        return received[value.index]
+    if isinstance(value, dict):
+        for k in list(value.keys()):
+            value[k] = _fill_slots(value[k], received)
+        return value
+    if isinstance(value, torch.Size):
+        return value
+    if isinstance(value, (list, tuple, set, frozenset)):
+        items = [_fill_slots(v, received) for v in value]
+        if isinstance(value, tuple) and hasattr(value, "_fields"):
+            return type(value)(*items)
+        return type(value)(items)
+    return value
+
+
 class P2PCommunicator:
     """Fixed-shape tensor exchange between neighbouring stages.
 
@@ -147,15 +208,22 @@ class P2PCommunicator:
             return [op.op(op.tensor, op.peer, group=op.group)]
         return dist.batch_isend_irecv(ops)       # one NCCL group launch for the whole message
 
-    def send(self, tensors: List[Tensor], dst_stage: int, direction: str) -> List[Any]:
-        """Send ``tensors`` as one message to a neighbouring stage; returns the work handles."""
+    def send(self, tensors: List[Tensor], dst_stage: int, direction: Optional[str] = None) -> List[Any]:
+        """Send ``tensors`` as one message to a neighbouring stage; returns the work handles. Without ``direction``
+        this is the reference's ``send(value, recv_stage)``: any value, blocking (``send_object``)."""
+        if direction is None:
+            self.send_object(tensors, dst_stage)
+            return []
         me = self.mpu.get_pipeline_parallel_rank()
         g = self._chan[(min(me, dst_stage), direction)]
         ops = [dist.P2POp(dist.isend, t.contiguous(), self._rank(dst_stage), group=g) for t in tensors]
         return self._post(ops)
 
-    def recv(self, tensors: List[Tensor], src_stage: int, direction: str) -> List[Any]:
-        """Post the receive of one message (same tensor count and shapes as the sender's)."""
+    def recv(self, tensors, src_stage: Optional[int] = None, direction: Optional[str] = None):
+        """Post the receive of one message (same tensor count and shapes as the sender's). With a single argument
+        this is the reference's ``recv(send_stage)``: returns the value the neighbour sent (``recv_object``)."""
+        if direction is None:
+            return self.recv_object(tensors if src_stage is None else src_stage)
         me = self.mpu.get_pipeline_parallel_rank()
         g = self._chan[(min(me, src_stage), direction)]
         ops = [dist.P2POp(dist.irecv, t, self._rank(src_stage), group=g) for t in tensors]
@@ -163,6 +231,72 @@ class P2PCommunicator:
             return self._post(ops)
         with torch.cuda.stream(self.side):
             return self._post(ops)
+
+    # ------------------------------------------------------------------ arbitrary values (cold path)
+    # The reference's communicator moves any Python value between stages - bool, int, float, complex, str, type,
+    # None, list, tuple, set, dict, torch.Size, tensors, nested - one small broadcast per scalar and per container
+    # element (oslo/parallelism/engine_pipeline.py:823-1199). The same capability here is three kinds of message per
+    # value: a two-number header, the pickled structure with every tensor replaced by a (shape, dtype) slot, and the
+    # tensors themselves, device to device. Not used by the training schedule, which only ever sends activations.
+    def send_object(self, value: Any, dst_stage: int) -> None:
+        """Send ``value`` (any picklable structure; tensors at any depth travel as tensors) to a neighbouring stage."""
+        me = self.mpu.get_pipeline_parallel_rank()
+        if abs(dst_stage - me) != 1:
+            raise ValueError(f"stage {me} can only send to a neighbouring stage, not to {dst_stage}")
+        g = self._chan[(min(me, dst_stage), "fwd" if dst_stage > me else "bwd")]
+        dst = self._rank(dst_stage)
+        tensors: List[Tensor] = []
+        payload = pickle.dumps(_strip_tensors(value, tensors), protocol=pickle.HIGHEST_PROTOCOL)
+        dev = self.mpu.device
+        dist.send(torch.tensor([len(payload), len(tensors)], dtype=torch.int64, device=dev), dst, group=g)
+        dist.send(torch.frombuffer(bytearray(payload), dtype=torch.uint8).to(dev), dst, group=g)
+        for t in tensors:
+            dist.send(t.detach().to(dev).contiguous(), dst, group=g)
+
+    def recv_object(self, src_stage: int) -> Any:
+        """Receive what the neighbouring stage ``src_stage`` passed to ``send_object``; tensors arrive on this rank's
+        device with the sender's ``requires_grad`` flag."""
+        me = self.mpu.get_pipeline_parallel_rank()
+        if abs(src_stage - me) != 1:
+            raise ValueError(f"stage {me} can only receive from a neighbouring stage, not from {src_stage}")
+        g = self._chan[(min(me, src_stage), "fwd" if src_stage < me else "bwd")]
+        src = self._rank(src_stage)
+        dev = self.mpu.device
+        head = torch.zeros(2, dtype=torch.int64, device=dev)
+        dist.recv(head, src, group=g)
+        nbytes, ntensors = (int(v) for v in head.tolist())
+        raw = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        dist.recv(raw, src, group=g)
+        skeleton = pickle.loads(raw.cpu().numpy().tobytes())
+        slots: List[_TensorSlot] = []
+        _collect_slots(skeleton, slots)
+        if len(slots) != ntensors:
+            raise RuntimeError(f"message announces {ntensors} tensors, its structure holds {len(slots)}")
+        received = {}
+        for slot in sorted(slots, key=lambda x: x.index):
+            t = torch.empty(slot.shape, dtype=slot.dtype, device=dev)
+            dist.recv(t, src, group=g)
+            received[slot.index] = t.requires_grad_(True) if slot.requires_grad else t
+        return _fill_slots(skeleton, received)
+
+    def ring_exchange_forward(self, value: Any) -> Any:
+        """The first stage's ``value`` travels 0 -> 1 -> ... -> last; every stage returns it
+        (reference: oslo/parallelism/engine_pipeline.py:795-807)."""
+        stage = self.mpu.get_pipeline_parallel_rank()
+        if not self.mpu.is_pipeline_first_stage():
+            value = self.recv_object(stage - 1)
+        if not self.mpu.is_pipeline_last_stage():
+            self.send_object(value, stage + 1)
+        return value
+
+    def ring_exchange_backward(self, value: Any) -> Any:
+        """The last stage's ``value`` travels last -> ... -> 1 -> 0; every stage returns it (reference: :809-821)."""
+        stage = self.mpu.get_pipeline_parallel_rank()
+        if not self.mpu.is_pipeline_last_stage():
+            value = self.recv_object(stage + 1)
+        if not self.mpu.is_pipeline_first_stage():
+            self.send_object(value, stage - 1)
+        return value
 
     def alloc(self, shape, dtype, device) -> Tensor:
         """Receive buffer; allocated on the side stream that the receive runs on."""
@@ -179,6 +313,37 @@ class P2PCommunicator:
             cur = torch.cuda.current_stream()
             for t in tensors:
                 t.record_stream(cur)
+
+
+def _add_typed_messages() -> None:
+    """``send_<kind>(value, recv_stage, send_type=False)`` / ``recv_<kind>(send_stage)`` for the value kinds the
+    reference's communicator names one by one (oslo/parallelism/engine_pipeline.py:837-1199). Every message here is
+    self-describing, so ``send_type`` is accepted and ignored; both ends check the kind."""
+    kinds = {"bool": bool, "int": int, "float": float, "complex": complex, "str": str, "type": type, "none": type(None),
+             "list": list, "tuple": tuple, "set": set, "dict": dict, "size": torch.Size, "tensor": Tensor}
+
+    def make(name, kind):
+        def send(self, value, recv_stage, send_type=False):
+            if not isinstance(value, kind) or (kind is int and isinstance(value, bool)):
+                raise TypeError(f"send_{name} got {type(value).__name__}")
+            self.send_object(value, recv_stage)
+
+        def recv(self, send_stage):
+            value = self.recv_object(send_stage)
+            if not isinstance(value, kind):
+                raise TypeError(f"recv_{name} got {type(value).__name__} from stage {send_stage}")
+            return value
+
+        send.__name__, recv.__name__ = f"send_{name}", f"recv_{name}"
+        return send, recv
+
+    for name, kind in kinds.items():
+        snd, rcv = make(name, kind)
+        setattr(P2PCommunicator, f"send_{name}", snd)
+        setattr(P2PCommunicator, f"recv_{name}", rcv)
+
+
+_add_typed_messages()
 
 
 class _StageModule(nn.ModuleList):

@@ -75,3 +75,53 @@ def test_p2p_between_neighbouring_stages():
     (oslo/parallelism/mpu.py:321-368, :892-920) on 4 pipeline stages."""
     from tests.dist_utils import run_distributed
     run_distributed(_p2p_ranks, 4)
+
+
+def _object_ranks(rank, world):
+    import torch
+    import oslo_b200 as ob
+    from oslo_b200.modeling_utils import ModelOutput
+    cfg = ob.GPTJConfig(vocab_size=64, n_positions=16, n_embd=16, n_layer=3, n_head=2, rotary_dim=4)
+    model = ob.parallelize(ob.GPTJForCausalLM(cfg), pipeline_parallel_size=world, micro_batch_size=1)
+    comm = model._pipe_engine.p2p
+    value = None
+    if rank == 0:
+        value = {"flag": True, "n": 7, "x": 2.5, "z": 1 + 2j, "s": "héllo", "none": None, "kind": float,
+                 "shape": torch.Size([2, 3]), "set": {1, 2}, "tup": (1, ("a", torch.arange(4))),
+                 "list": [torch.ones(2, 2, dtype=torch.bfloat16), torch.zeros(0)],
+                 "out": ModelOutput(loss=torch.tensor(0.5, requires_grad=True), logits=None)}
+    got = comm.ring_exchange_forward(value)
+    assert got["flag"] is True and got["n"] == 7 and got["x"] == 2.5 and got["z"] == 1 + 2j and got["s"] == "héllo"
+    assert got["none"] is None and got["kind"] is float and got["shape"] == torch.Size([2, 3]) and got["set"] == {1, 2}
+    assert isinstance(got["shape"], torch.Size) and isinstance(got["tup"], tuple)
+    assert got["tup"][1][0] == "a" and got["tup"][1][1].tolist() == [0, 1, 2, 3]
+    assert got["list"][0].dtype == torch.bfloat16 and got["list"][0].shape == (2, 2) and got["list"][1].numel() == 0
+    assert isinstance(got["out"], ModelOutput) and got["out"].loss.requires_grad and float(got["out"].loss) == 0.5
+    # the other way round, a bare tensor and scalars through the typed calls
+    back = comm.ring_exchange_backward(torch.full((3,), float(rank)) if rank == world - 1 else None)
+    assert back.tolist() == [float(world - 1)] * 3
+    if rank == 0:
+        comm.send_int(41, 1)
+        comm.send_str("x", recv_stage=1, send_type=True)
+        comm.send((1, 2), 1)
+        try:
+            comm.send_int(True, 1)
+        except TypeError:
+            pass
+        else:
+            raise AssertionError("a bool went through send_int")
+    elif rank == 1:
+        assert comm.recv_int(0) == 41 and comm.recv_str(0) == "x" and comm.recv(0) == (1, 2)
+    try:
+        comm.send_object(1, rank + 2)
+    except ValueError:
+        pass
+    else:
+        raise AssertionError("a non-neighbour was accepted")
+
+
+def test_values_of_any_kind_travel_between_stages():
+    """The object protocol of the reference's ``P2PCommunicator`` (oslo/parallelism/engine_pipeline.py:795-1199):
+    nested containers, scalars, ``None``, types, sizes and tensors from the first stage reach every stage."""
+    from tests.dist_utils import run_distributed
+    run_distributed(_object_ranks, 3)
