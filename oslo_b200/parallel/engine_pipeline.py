@@ -477,14 +477,35 @@ class PipelineParallelEngine:
         object.__setattr__(model, "forward", self.forward)
 
     # ------------------------------------------------------------------ batch handling
-    def _split_batches(self, kwargs: Dict[str, Any]) -> List[Dict[str, Any]]:
-        bsz = None
+    def set_micro_batch_size(self, micro_batch_size: int) -> None:
+        """Sequences per micro-batch from the next call on (``generate()`` sets it to the whole batch)."""
+        self.micro_batch_size = int(micro_batch_size)
+
+    def parallelize(self) -> None:
+        """Assign the stages and move / drop parameters in one call (what ``parallelize`` /
+        ``from_pretrained_with_parallel`` do around the tensor-parallel engine)."""
+        self.assign_stages()
+        self.finalize()
+
+    @staticmethod
+    def guess_batch_size(kwargs: Dict[str, Any]) -> int:
+        """Batch size of a call's keyword arguments: the leading dimension of ``input_ids``, ``attention_mask`` or
+        ``labels`` (reference: oslo/parallelism/engine_pipeline.py:306-322), else of the first batched tensor
+        (``inputs_embeds``, ...)."""
+        for key in ("input_ids", "attention_mask", "labels"):
+            v = kwargs.get(key)
+            if v is not None:
+                if not torch.is_tensor(v):
+                    raise ValueError(f"``{key}`` must be a tensor of shape (batch_size, ...), got {type(v).__name__}")
+                return v.size(0)
         for v in kwargs.values():
             if torch.is_tensor(v) and v.dim() >= 1:
-                bsz = v.size(0)
-                break
-        if bsz is None:
-            raise ValueError("no batched tensor found in the inputs")
+                return v.size(0)
+        kinds = {k: type(v).__qualname__ for k, v in kwargs.items()}
+        raise ValueError(f"no batched tensor found in the inputs (input_ids, attention_mask, labels, ...): {kinds}")
+
+    def _split_batches(self, kwargs: Dict[str, Any]) -> List[Dict[str, Any]]:
+        bsz = self.guess_batch_size(kwargs)
         mbs = max(1, min(self.micro_batch_size, bsz))
         if bsz % mbs:
             raise ValueError(f"batch size {bsz} is not divisible by micro_batch_size {mbs}")
