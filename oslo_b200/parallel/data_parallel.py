@@ -6,10 +6,15 @@ DeepSpeed with ``process_group=model.mpu.get_data_parallel_group()`` (USAGE.md:1
 pipeline parallelism torch DDP only reduces the first micro-batch's backward. This wrapper
 
 * keeps gradients in one flat buffer cut into buckets in reverse parameter order,
-* fires an asynchronous all-reduce per bucket as soon as every gradient of the bucket has been
-  accumulated - but only during the backward of the LAST micro-batch of a step (earlier
-  micro-batches accumulate locally), so the reduction overlaps that backward and runs once per step,
-* hands the already-averaged gradients to the optimizer (``FusedAdamW`` then only steps its shard).
+* reduces a bucket as soon as every gradient of the bucket has been accumulated - but only during the
+  backward of the LAST micro-batch of a step (earlier micro-batches accumulate locally), so the reduction
+  overlaps that backward and runs once per step. On GPUs the flat buffers live in symmetric memory and the
+  reduction is this package's reduce-scatter kernel on a side stream (``csrc/comm.cu``; followed by the
+  all-gather kernel when the optimizer state is not sharded); elsewhere it is an asynchronous all-reduce,
+* hands the summed gradients to the optimizer, which divides by the group size (``FusedAdamW`` then only
+  steps its shard),
+* with ZeRO-1 sends the refreshed parameters out bucket by bucket under the next forward pass: every forward
+  unit waits for the buckets that hold its own parameters only.
 
 ``torch.nn.parallel.DistributedDataParallel`` around ``gpu_modules()`` keeps working for steps that
 have a single micro-batch.
