@@ -481,6 +481,14 @@ def main(args, sampler_cls=None) -> None:
     why = probe()
     if why:
         return _unavailable(why)
+    if getattr(args, "mode", "train") == "fusion":
+        # its script generates with beam search; the beam scorer and the beam-search logits processors that the
+        # reference imports from transformers 4.x exist nowhere in the installed release (they are placeholders
+        # that raise when instantiated), and its fuse() compiles its kernels at first use for architectures up to
+        # sm_80 only
+        return _unavailable("the reference's kernel-fusion benchmark needs transformers 4.x beam search classes "
+                            "(BeamSearchScorer and others are gone from the installed release) and a JIT build of "
+                            "its CUDA kernels, which cannot target sm_100")
     import threading
     limit = float(os.environ.get("OSLO_B200_REFERENCE_DEADLINE_S", "900"))
     done = threading.Event()

@@ -66,8 +66,12 @@ def parse_args():
                          "least; the limit grows to 1.5 x the headline configuration's own run time per extra block)")
     ap.add_argument("--checkpoint-activations", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--mode", default="train", choices=["train", "decode"],
-                    help="train: tokens/s of a training step; decode: ms/token of greedy generation with a KV cache")
+    ap.add_argument("--mode", default="train", choices=["train", "decode", "fusion"],
+                    help="train: tokens/s of a training step; decode: ms/token of greedy generation with a KV cache; "
+                         "fusion: seconds of one GPT-2 small beam-search generate() call before and after fuse() (the "
+                         "benchmark behind the reference's published numbers)")
+    ap.add_argument("--fusion-dtype", default="fp32", choices=["fp32", "bf16"],
+                    help="fusion: parameter dtype (the reference's script runs the fp32 checkpoint)")
     ap.add_argument("--prompt", type=int, default=512, help="decode: prompt length")
     ap.add_argument("--new-tokens", type=int, default=128, help="decode: tokens generated per call")
     ap.add_argument("--decode-batch", type=int, default=1, help="decode: sequences per call")
@@ -336,6 +340,9 @@ def main() -> None:
     if args.mode == "decode" and args.deployment:
         decode_deployment_main(args)
         return
+    if args.mode == "fusion":
+        fusion_main(args)
+        return
 
     import torch
     import torch.distributed as dist
@@ -435,6 +442,110 @@ def main() -> None:
         emit(block, also)
     dist.barrier()
     dist.destroy_process_group()
+
+
+# seconds of one generate() call as printed in the reference's documentation and test docstrings; hardware not stated
+# (USAGE.md:326-327, :339-340; tests/gpt2/gpt2_test_kernel_fusion.py:14-15, :62-63)
+FUSION_PUBLISHED = {
+    1: {"before_fuse_s": 3.5706350803375244, "after_fuse_s": 3.2512128353118896, "no_repeat_ngram_size": 4},
+    4: {"before_fuse_s": 4.304628610610962, "after_fuse_s": 3.859266519546509,
+        "after_fuse_fused_ngram_s": 3.620283210294232, "no_repeat_ngram_size": 2},
+}
+
+
+def fusion_main(args) -> None:
+    """The reference's kernel-fusion benchmark (tests/gpt2/gpt2_test_kernel_fusion.py:11-107): GPT-2 small, one prompt,
+    ``generate(max_length=200, min_length=200, num_beams=5, no_repeat_ngram_size=4)`` on one GPU, or tensor parallel
+    over ``--gpus`` GPUs with ``no_repeat_ngram_size=2``, timed with the wall clock around the call (plus a device
+    synchronize) before ``model.fuse()``, after it, and after it with ``fused_no_repeat_ngram_blocking=True``. Random
+    weights instead of the hub checkpoint (``min_length`` pins the length, so the work per call is the same);
+    ``--warmup`` full-length calls before each timing, mean over ``--steps`` calls, max over ranks. ``value`` is the
+    after-fuse time; ``vs_baseline`` is it divided by the reference's published after-fuse time for the same GPU
+    count (1 or 4; null otherwise)."""
+    import torch
+    import torch.distributed as dist
+
+    import oslo_b200 as ob
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    on_gpu = torch.cuda.is_available() and os.environ.get("OSLO_B200_BACKEND", "nccl") != "gloo"
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    if on_gpu:
+        torch.cuda.set_device(local)
+    dtype = {"fp32": torch.float32, "bf16": torch.bfloat16}[args.fusion_dtype]
+    n_layer = args.layers if args.layers is not None else 12
+    cfg = ob.GPT2Config(vocab_size=50257, n_positions=1024, n_embd=768, n_layer=n_layer, n_head=12, torch_dtype=dtype)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        model = ob.GPT2LMHeadModel.from_config_with_parallel(cfg, tensor_parallel_size=world, seed=1234,
+                                                             init_on_device=on_gpu, torch_dtype=dtype)
+        dev = model.mpu.device
+    else:
+        dev = torch.device("cuda", local) if on_gpu else torch.device("cpu")
+        torch.manual_seed(1234)
+        with torch.device(dev):
+            model = ob.GPT2LMHeadModel._from_config(cfg, torch_dtype=dtype)
+    model.eval()
+    ngram = 4 if world == 1 else 2
+    max_len = args.new_tokens + 8 if args.new_tokens != 128 else 200      # 200 as in the reference unless overridden
+    prompt = torch.randint(0, 50257, (1, 8), generator=torch.Generator().manual_seed(7)).to(dev)
+    kw = dict(max_length=max_len, min_length=max_len, num_beams=5, no_repeat_ngram_size=ngram, pad_token_id=0)
+
+    def sync():
+        if on_gpu:
+            torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    def timed(**extra):
+        for _ in range(5):
+            model.generate(prompt, pad_token_id=0)                        # the reference's own warm-up: 5 default calls
+        for _ in range(args.warmup):
+            model.generate(prompt, **kw, **extra)
+        sync()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            out = model.generate(prompt, **kw, **extra)
+        sync()
+        sec = (time.perf_counter() - t0) / args.steps
+        if world > 1:
+            t = torch.tensor([sec], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            sec = float(t.item())
+        assert out.shape == (1, max_len), out.shape
+        return sec
+
+    ext = ob.ops.load_ext(required=True) if on_gpu else None
+    sampler = ClockSampler(local) if on_gpu else None
+    if sampler is not None:
+        sampler.start()
+    before = timed()
+    l0 = ext.launch_count() if ext is not None else 0
+    model.fuse()
+    after = timed()
+    after_ngram = timed(fused_no_repeat_ngram_blocking=True)
+    launches = (ext.launch_count() - l0) if ext is not None else 0
+    clocks = sampler.stop() if sampler is not None else None
+    pub = FUSION_PUBLISHED.get(world) if (n_layer == 12 and max_len == 200 and args.fusion_dtype == "fp32") else None
+    if rank == 0:
+        print(json.dumps({
+            "metric": "GPT-2 small generate() seconds, 200 tokens, 5 beams, after fuse()" + ("" if n_layer == 12 and max_len == 200 else " (debug)"),
+            "value": after, "unit": "s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": after * 1e3, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": (after / pub["after_fuse_s"]) if pub else None, "dtype": args.fusion_dtype,
+            "data": "8 synthetic prompt token ids, random-init weights", "impl": "oslo_b200",
+            "config": {"model": "gpt2-small", "parallelism": f"tp{world}" if world > 1 else "single", "num_beams": 5,
+                       "max_length": max_len, "no_repeat_ngram_size": ngram, "batch": 1},
+            "before_fuse_s": before, "after_fuse_s": after, "after_fuse_fused_ngram_s": after_ngram,
+            "fuse_speedup": before / after, "published_reference": pub, "clocks": clocks, "gpu_launches": launches,
+        }), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def decode_deployment_main(args) -> None:

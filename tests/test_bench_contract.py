@@ -98,3 +98,27 @@ def test_default_plan_follows_the_model_parallel_sweep():
     p8, also8 = names[8]
     assert (p8["tp"], p8["pp"], p8["micro"]) == (2, 4, 4)          # 64 sequences as 16 micro-batches of 4
     assert [a["name"] for a in also8] == ["dp8_zero1", "tp8_b8x2048"] and also8[1]["replica_batch"] == 8
+
+
+def test_fusion_mode_times_generate_before_and_after_fuse():
+    """``--mode fusion`` (the reference's tests/gpt2/gpt2_test_kernel_fusion.py as a benchmark) at a debug size on CPU:
+    one JSON line, time-like metric, the three timings; the reference arm says why it cannot run this mode here."""
+    env = dict(os.environ, OSLO_B200_BACKEND="gloo")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--mode", "fusion", "--layers", "1",
+                        "--new-tokens", "6", "--steps", "1", "--warmup", "1"], capture_output=True, text=True,
+                       timeout=600, cwd=ROOT, env=env)
+    assert r.returncode == 0, r.stderr[-800:]
+    lines = [l for l in r.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    rec = json.loads(lines[0])
+    assert rec["higher_is_better"] is False and rec["unit"] == "s" and rec["metric"].endswith("(debug)")
+    assert rec["value"] == rec["after_fuse_s"] > 0 and rec["before_fuse_s"] > 0 and rec["after_fuse_fused_ngram_s"] > 0
+    assert rec["vs_baseline"] is None and rec["config"]["num_beams"] == 5 and rec["config"]["no_repeat_ngram_size"] == 4
+    sys.path.insert(0, ROOT)
+    import bench
+    assert bench.FUSION_PUBLISHED[4]["after_fuse_s"] == 3.859266519546509
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--mode", "fusion"],
+                       capture_output=True, text=True, timeout=300, cwd=ROOT)
+    assert r.returncode == 0
+    rec = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][0])
+    assert rec["impl"] == "reference" and rec["unavailable"]
