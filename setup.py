@@ -43,7 +43,7 @@ setup(
     version="0.1.0",
     description="Blackwell-native 3D-parallel transformer training and inference framework with OSLO's API",
     packages=find_packages(include=["oslo_b200", "oslo_b200.*"]),
-    package_data={"oslo_b200": ["_C.so", "_data_C.so", "csrc/*"]},
+    package_data={"oslo_b200": ["_C.so", "_C_bounds.so", "_data_C.so", "csrc/*"]},
     python_requires=">=3.10",
     install_requires=["torch", "numpy"],
     cmdclass={"build_ext": BuildExt, "build_py": BuildPy},
