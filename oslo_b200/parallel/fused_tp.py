@@ -25,7 +25,7 @@ from torch import Tensor
 
 from .. import ops
 from ..config import get_config
-from .symmetric import SymmetricWorkspace
+from .symmetric import SymmetricWorkspace, group_on_one_node
 
 MODE_ALLREDUCE, MODE_REDUCE_SCATTER, MODE_ALLGATHER = 1, 2, 3
 _FLAG_RESIDUAL = 16            # GEMM epilogue flag: add the aux operand (here: another per-rank partial sum)
@@ -121,7 +121,7 @@ def fused_tp_usable(mpu, x: Tensor, n_out: int, rows: Optional[int] = None) -> b
         return False
     if x.dtype not in (torch.bfloat16, torch.float16) or x.size(-1) % 8 or n_out % 8 or x.numel() == 0:
         return False
-    if not ops.kernels_available():
+    if not ops.kernels_available() or not group_on_one_node(mpu.get_tensor_parallel_group()):
         return False
     rows = rows if rows is not None else x.numel() // x.size(-1)
     # decode-sized inputs gain nothing from overlapping tiles with their transfer, and the kernels take their

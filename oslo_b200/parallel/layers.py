@@ -103,8 +103,9 @@ class VocabParallelEmbedding(nn.Embedding):
         lo, hi = self.vocab_range()
         if self.oslo_fused and ids.is_cuda and self.mpu.backend == "nccl" and self.padding_idx is None:
             from ..config import get_config
-            if get_config().fused_tp_comm and get_config().fused_vocab_embed and ops.kernels_available():
-                from .symmetric import get_workspace, vocab_embed, vocab_embed_usable
+            from .symmetric import get_workspace, group_on_one_node, vocab_embed, vocab_embed_usable
+            if (get_config().fused_tp_comm and get_config().fused_vocab_embed and ops.kernels_available()
+                    and group_on_one_node(self.mpu.get_tensor_parallel_group())):
                 ws = get_workspace(self.mpu.get_tensor_parallel_group())
                 if vocab_embed_usable(ws, ids, self.weight):
                     return vocab_embed(ws, ids, self.weight, lo, hi)   # lookup + collective in one kernel

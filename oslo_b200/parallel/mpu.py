@@ -111,6 +111,18 @@ class MPU:
             g = self._new_group(emb)
             if rank in emb:
                 self._emb_group, self._emb_ranks = g, emb
+        # which host every rank runs on, asked once here (all ranks are present): the paths that map peers' memory
+        # (symmetric.group_on_one_node) then know the answer for this MPU's groups without another collective
+        from .symmetric import node_identity, remember_group_nodes
+        self.node_of_rank: List[str] = [None] * world
+        if world > 1:
+            dist.all_gather_object(self.node_of_rank, node_identity())
+        else:
+            self.node_of_rank = [node_identity()]
+        for g, ranks in ((self._tp_group, self._tp_ranks), (self._dp_group, self._dp_ranks),
+                         (self._pp_group, self._pp_ranks), (self._mp_group, self._mp_ranks)):
+            if g is not None:
+                remember_group_nodes(g, [self.node_of_rank[r] for r in ranks])
 
     # ------------------------------------------------------------------ layout (pure)
     @staticmethod
@@ -319,7 +331,10 @@ class MPU:
         from ..config import get_config
         cfg = get_config()
         limit = getattr(cfg, "symm_allreduce_max_bytes", 0)
-        return bool(limit) and x.numel() * 2 <= limit and not torch.is_grad_enabled()
+        if not (bool(limit) and x.numel() * 2 <= limit and not torch.is_grad_enabled()):
+            return False
+        from .symmetric import group_on_one_node
+        return group_on_one_node(self._tp_group)
 
     def _scatter(self, x: Tensor, dim: int = -1) -> Tensor:
         if self.tp == 1:

@@ -23,6 +23,54 @@ _WORKSPACES: Dict[str, "SymmetricWorkspace"] = {}
 ONESHOT_HALF = 1 << 20   # bytes per staging half of the one-kernel all-reduce
 
 
+_ONE_NODE: Dict[str, bool] = {}
+
+
+def node_identity() -> str:
+    """What two ranks must share to map each other's memory: the host (its name and the identifier of its current
+    boot). ``OSLO_B200_NODE_ID`` overrides it (tests; clusters whose host names are not unique)."""
+    import os
+    import socket
+    override = os.environ.get("OSLO_B200_NODE_ID")
+    if override:
+        return override
+    boot = ""
+    try:
+        with open("/proc/sys/kernel/random/boot_id") as f:
+            boot = f.read().strip()
+    except OSError:
+        pass
+    return f"{socket.gethostname()}|{boot}"
+
+
+def remember_group_nodes(group, nodes) -> None:
+    """Record the hosts of a group's ranks (the MPU knows them from its one exchange at construction)."""
+    _ONE_NODE[group.group_name] = len(set(nodes)) == 1
+
+
+def group_on_one_node(group) -> bool:
+    """All ranks of ``group`` run on the same host. Symmetric memory (peer mappings, the NVSwitch multicast object)
+    exists inside one NVLink domain only, so every path that uses it asks this first; a group that spans hosts stays
+    on NCCL. Groups of an ``MPU`` are known from its construction; for any other group the first call is collective
+    over the group (one small object all-gather), cached afterwards."""
+    if group is None:
+        return False
+    name = group.group_name
+    hit = _ONE_NODE.get(name)
+    if hit is None:
+        if torch.cuda.is_available() and torch.cuda.is_current_stream_capturing():
+            return False          # no collective inside a stream capture; the caller falls back to NCCL this once
+        n = dist.get_world_size(group)
+        if n == 1:
+            hit = True
+        else:
+            ids = [None] * n
+            dist.all_gather_object(ids, node_identity(), group=group)
+            hit = len(set(ids)) == 1
+        _ONE_NODE[name] = hit
+    return hit
+
+
 class SymmetricWorkspace:
     def __init__(self, group, nbytes: int, device: Optional[torch.device] = None) -> None:
         import torch.distributed._symmetric_memory as symm
@@ -167,15 +215,15 @@ def get_ce_combine(group, device) -> CeCombine:
 
 def symmetric_flat_usable(group, dtype: torch.dtype, device) -> bool:
     """The data-parallel buffers go to symmetric memory on CUDA devices, over NCCL groups of more than one rank,
-    for 16-bit gradients / parameters, when the kernels are built and ``OSLO_B200_DP_SYMMETRIC`` is not switched off.
-    Every condition is the same on all ranks of the group."""
+    for 16-bit gradients / parameters, when the kernels are built, ``OSLO_B200_DP_SYMMETRIC`` is not switched off and
+    the whole group sits on one host. Every condition is the same on all ranks of the group."""
     if group is None or not get_config().dp_symmetric:
         return False
     if torch.device(device).type != "cuda" or dtype not in (torch.bfloat16, torch.float16):
         return False
     if dist.get_backend(group) != "nccl" or dist.get_world_size(group) < 2 or dist.get_world_size(group) > 16:
         return False
-    return ops.kernels_available()
+    return ops.kernels_available() and group_on_one_node(group)
 
 
 class _VocabEmbed(torch.autograd.Function):

@@ -85,6 +85,11 @@ def _own_collectives() -> bool:
     return bool(get_config().fused_tp_comm)
 
 
+def _one_node(mpu) -> bool:
+    from .symmetric import group_on_one_node
+    return group_on_one_node(mpu.get_tensor_parallel_group())
+
+
 def _as_rows(x: Tensor) -> Tensor:
     return x if (x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0) else x.contiguous()
 
@@ -112,7 +117,7 @@ class _LinearCrossEntropy(torch.autograd.Function):
                 continue
             lg = _proj(hidden[s:e], weight, bias, fused)
             mx[s:e], se[s:e], tg[s:e] = _stats(lg, labels[s:e], lo, fused)
-        if tp > 1 and in_epilogue and mpu.backend == "nccl" and _own_collectives():
+        if tp > 1 and in_epilogue and mpu.backend == "nccl" and _own_collectives() and _one_node(mpu):
             # one kernel, one cross-rank meeting: peers' statistics read from symmetric memory and combined in place
             from .symmetric import get_ce_combine
             get_ce_combine(mpu.get_tensor_parallel_group(), hidden.device)(mx, se, tg)

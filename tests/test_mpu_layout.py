@@ -1,4 +1,6 @@
 """Rank layout and partition helpers (pure functions; no process group needed)."""
+import torch
+
 from oslo_b200.parallel.engine_pipeline import one_f_one_b_order
 from oslo_b200.parallel.mpu import MPU, ceil_split_sizes
 
@@ -125,3 +127,27 @@ def test_values_of_any_kind_travel_between_stages():
     nested containers, scalars, ``None``, types, sizes and tensors from the first stage reach every stage."""
     from tests.dist_utils import run_distributed
     run_distributed(_object_ranks, 3)
+
+
+def _node_ranks(rank, world):
+    import os
+    import torch.distributed as dist
+    from oslo_b200.parallel import symmetric
+    # ranks 0-1 on host "a", ranks 2-3 on host "b": tensor-parallel pairs stay on one host, data-parallel pairs do not
+    os.environ["OSLO_B200_NODE_ID"] = "a" if rank < 2 else "b"
+    mpu = MPU(2, 1)
+    assert mpu.node_of_rank == ["a", "a", "b", "b"]
+    assert symmetric.group_on_one_node(mpu.get_tensor_parallel_group()) is True
+    assert symmetric.group_on_one_node(mpu.get_data_parallel_group()) is False
+    assert symmetric.symmetric_flat_usable(mpu.get_data_parallel_group(), torch.bfloat16, "cpu") is False
+    # a group the MPU did not create: asked collectively on first use, then cached
+    g = dist.new_group(ranks=[0, 1, 2, 3], backend="gloo")
+    assert symmetric.group_on_one_node(g) is False and symmetric._ONE_NODE[g.group_name] is False
+    pair = dist.new_group(ranks=[2, 3], backend="gloo")
+    if rank >= 2:
+        assert symmetric.group_on_one_node(pair) is True
+
+
+def test_symmetric_memory_paths_ask_whether_a_group_sits_on_one_host():
+    from tests.dist_utils import run_distributed
+    run_distributed(_node_ranks, 4)
