@@ -191,3 +191,97 @@ def test_fused_gemm_collective_does_not_need_its_whole_grid_resident(world):
     assert _run_fused_grid(world, grid, tiles, 16, aligned=False, all_ctas_wait_for_done=True)
     assert not _run_fused_grid(world, grid, tiles, 15, aligned=False, all_ctas_wait_for_done=True)
     assert not _run_fused_grid(world, grid, tiles, 15, aligned=True, all_ctas_wait_for_done=True)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Signal words of the compare-and-swap barrier when consecutive kernels use DIFFERENT grids (comm.cu:
+# block_barrier_all_ranks; dp_reduce_scatter_kernel / dp_all_gather_kernel / allreduce_symm_kernel meet twice per
+# launch, the second time at slot offset grid * world, and a bucket's grid depends on its size). A word is a one-bit
+# mailbox from one source rank: "put" spins until it is empty, "wait" spins until it is full and empties it. The
+# model tags every put with (launch, meeting, block) and fails when a wait consumes a tag that is not its own.
+
+def _run_signal_words(world, grids, delays, meetings=2, blind_put=False):
+    words = [dict() for _ in range(world)]            # per rank: slot -> tag (absent = empty)
+    lock = threading.Lock()
+    bad, dead = [], []
+
+    def put(peer, slot, tag, deadline):
+        while True:
+            with lock:
+                if blind_put or slot not in words[peer]:
+                    words[peer][slot] = tag
+                    return True
+            if time.monotonic() > deadline:
+                return False
+            time.sleep(0)
+
+    def wait(me, slot, tag, deadline):
+        while True:
+            with lock:
+                got = words[me].pop(slot, None)
+            if got is not None:
+                if got != tag:
+                    bad.append((me, slot, tag, got))
+                return True
+            if time.monotonic() > deadline:
+                return False
+            time.sleep(0)
+
+    def block_fn(rank, launch, grid, block, rnd, deadline):
+        for meeting in range(meetings):
+            time.sleep(delays(rank, launch, block, meeting, "before", rnd))
+            slot0 = meeting * grid * world
+            for peer in range(world):                 # thread `peer` of the block: put to the peer, wait for its put
+                if not put(peer, slot0 + block * world + rank, (launch, meeting, block), deadline):
+                    dead.append(("put", rank, launch, block, meeting))
+                    return
+            time.sleep(delays(rank, launch, block, meeting, "between", rnd))
+            for peer in range(world):
+                if not wait(rank, slot0 + block * world + peer, (launch, meeting, block), deadline):
+                    dead.append(("wait", rank, launch, block, meeting))
+                    return
+
+    def rank_fn(rank):
+        rnd = random.Random(77 + rank)
+        deadline = time.monotonic() + (3 if blind_put else 30)
+        for launch, grid in enumerate(grids):         # launches of one stream run one after the other
+            blocks = [threading.Thread(target=block_fn, args=(rank, launch, grid, b, rnd, deadline)) for b in range(grid)]
+            for t in blocks:
+                t.start()
+            for t in blocks:
+                t.join(40)
+
+    ranks = [threading.Thread(target=rank_fn, args=(r,)) for r in range(world)]
+    for t in ranks:
+        t.start()
+    for t in ranks:
+        t.join(60)
+    leftovers = [w for w in words if w]
+    return bad, dead, leftovers
+
+
+def _jitter4(rank, launch, block, meeting, where, rnd):
+    return rnd.random() * 0.001
+
+
+def _one_rank_lags(rank, launch, block, meeting, where, rnd):
+    # rank 0 is slow to look at its own words after it has signalled its peers, who race ahead meanwhile
+    return 0.01 if (rank == 0 and where == "between") else 0.0
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_signal_words_survive_grids_that_change_between_launches(world):
+    """Growing, shrinking and repeated grids: the second meeting's words of one launch overlap the first meeting's
+    words of a launch with a larger grid, and still every wait consumes exactly the put that was meant for it (a
+    word is a one-deep FIFO from one source: puts wait for an empty word, and a rank puts in program order)."""
+    grids = [1, 4, 2, 4, 1, 3, 3, 2]
+    for delays in (_jitter4, _one_rank_lags):
+        bad, dead, leftovers = _run_signal_words(world, grids, delays)
+        assert not bad and not dead and not leftovers, (bad[:3], dead[:3], leftovers[:1])
+
+
+def test_signal_word_model_catches_a_put_that_does_not_wait_for_an_empty_word():
+    """Negative control: a put that stores without waiting for the word to be empty. A peer that races ahead then
+    overwrites the signal a slow rank has not consumed yet, which shows as a wrong tag or as a wait that never ends."""
+    bad, dead, leftovers = _run_signal_words(3, [1, 2, 1, 2, 1, 2], _one_rank_lags, blind_put=True)
+    assert bad or dead or leftovers, "the model failed to expose the overwritten signal"
