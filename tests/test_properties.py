@@ -142,3 +142,45 @@ def test_bf16_gradient_accumulation_over_16_micro_batches():
     assert one_rounding < 0.003
     assert err < 4 * one_rounding and err < 0.01, (float(err), float(one_rounding))
     assert cos > 0.9999
+
+
+_leaves = st.one_of(st.none(), st.booleans(), st.integers(-10 ** 12, 10 ** 12), st.floats(allow_nan=False),
+                    st.complex_numbers(allow_nan=False, allow_infinity=False), st.text(max_size=8),
+                    st.sampled_from([int, float, str, dict]),
+                    st.lists(st.integers(0, 5), max_size=3).map(torch.Size),
+                    st.lists(st.integers(1, 3), min_size=0, max_size=3).map(
+                        lambda shape: torch.arange(int(torch.tensor(shape or [1]).prod())).reshape(shape or [1]).float()))
+_values = st.recursive(_leaves, lambda inner: st.one_of(
+    st.lists(inner, max_size=3), st.lists(inner, max_size=3).map(tuple),
+    st.dictionaries(st.text(max_size=4), inner, max_size=3)), max_leaves=12)
+
+
+def _same(a, b) -> bool:
+    if torch.is_tensor(a) or torch.is_tensor(b):
+        return torch.is_tensor(a) and torch.is_tensor(b) and a.dtype == b.dtype and a.shape == b.shape and torch.equal(a, b)
+    if type(a) is not type(b):
+        return False
+    if isinstance(a, dict):
+        return a.keys() == b.keys() and all(_same(a[k], b[k]) for k in a)
+    if isinstance(a, (list, tuple)) and not isinstance(a, torch.Size):
+        return len(a) == len(b) and all(_same(x, y) for x, y in zip(a, b))
+    return a == b
+
+
+@given(_values)
+@settings(max_examples=150, deadline=None)
+def test_pipeline_message_structure_round_trips(value):
+    """What ``P2PCommunicator.send_object`` puts on the wire (pickled structure with tensor slots + the tensors) turns
+    back into the same value on the other side, for any nesting of the kinds the reference's communicator names."""
+    import pickle
+    from oslo_b200.parallel.engine_pipeline import _collect_slots, _fill_slots, _strip_tensors
+    tensors = []
+    wire = pickle.dumps(_strip_tensors(value, tensors))
+    skeleton = pickle.loads(wire)
+    slots = []
+    _collect_slots(skeleton, slots)
+    assert sorted(s.index for s in slots) == list(range(len(tensors)))
+    for s in slots:
+        assert s.shape == tuple(tensors[s.index].shape) and s.dtype == tensors[s.index].dtype
+    back = _fill_slots(skeleton, {i: t.clone() for i, t in enumerate(tensors)})
+    assert _same(back, value)
