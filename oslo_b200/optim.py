@@ -82,7 +82,13 @@ class DynamicLossScaler:
 
 
 class FlatBuffers:
-    """One flat parameter buffer + one flat gradient buffer per dtype; tensors become views."""
+    """One flat parameter buffer + one flat gradient buffer per dtype; tensors become views.
+
+    ``grad_dtype=torch.float32`` with 16-bit parameters keeps the gradient buffer in fp32 (main gradients): the
+    micro-batch gradients of a step then accumulate without 16-bit rounding, at the price of twice the gradient bytes
+    in memory and on the data-parallel wire, an extra pass per weight gradient (the 16-bit product is added into the
+    fp32 buffer by autograd instead of inside the GEMM epilogue) and NCCL instead of the symmetric-memory kernels,
+    which reduce 16-bit buffers. The default (gradients in the parameters' dtype) is what the benchmarks run."""
 
     def __init__(self, params: Iterable[torch.nn.Parameter], pad_to: int = 1, grad_dtype: Optional[torch.dtype] = None,
                  symmetric_group=None):
@@ -121,10 +127,17 @@ class FlatBuffers:
         else:
             self.flat_p = torch.zeros(self.padded, dtype=self.dtype, device=self.device)
             self.flat_g = torch.zeros(self.padded, dtype=grad_dtype or self.dtype, device=self.device)
+        wide = self.flat_g.dtype != self.dtype
+        if wide and not hasattr(torch.Tensor, "grad_dtype"):
+            raise RuntimeError("gradients in a dtype other than the parameters' need torch's Tensor.grad_dtype")
         for p, off in zip(self.params, self.offsets):
             view = self.flat_p[off: off + p.numel()].view(p.shape)
             view.copy_(p.data)
             p.data = view
+            if wide:
+                # autograd converts every incoming gradient to this dtype and accumulates in it: micro-batch gradients
+                # of 16-bit parameters add up in fp32
+                p.grad_dtype = self.flat_g.dtype
             p.grad = self.flat_g[off: off + p.numel()].view(p.shape)
             # the view lives as long as the buffer and is zeroed every step: weight-gradient GEMMs may add into it
             p._oslo_accum_grad = self.flat_g.dtype == p.dtype and not getattr(p, "_oslo_shared", False)
@@ -142,7 +155,7 @@ class FusedAdamW:
     def __init__(self, params: Iterable[torch.nn.Parameter], lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 0.01, max_grad_norm: Optional[float] = None, shard_group=None,
                  grad_average_group=None, model_parallel_group=None, model=None,
-                 loss_scaler: Optional[DynamicLossScaler] = None) -> None:
+                 loss_scaler: Optional[DynamicLossScaler] = None, grad_dtype: Optional[torch.dtype] = None) -> None:
         self.lr, self.betas, self.eps, self.weight_decay = lr, tuple(betas), eps, weight_decay
         self.max_grad_norm = max_grad_norm
         self.loss_scaler = loss_scaler
@@ -158,7 +171,7 @@ class FusedAdamW:
             groups = [dict(g, params=list(g["params"])) for g in params]
         else:
             groups = [dict(params=params)]
-        self.buf = FlatBuffers([p for g in groups for p in g["params"]], pad_to=8 * self.shards,
+        self.buf = FlatBuffers([p for g in groups for p in g["params"]], pad_to=8 * self.shards, grad_dtype=grad_dtype,
                                symmetric_group=shard_group if self.shards > 1 else grad_average_group)
         n = self.buf.padded // self.shards
         self.shard_numel = n

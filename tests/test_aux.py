@@ -311,3 +311,54 @@ def test_rank_aware_logger_formats_records_of_child_loggers(capsys):
     logging.getLogger("oslo_b200.some_module").info("child says %s", "hello")
     err = capsys.readouterr().err
     assert "child says hello" in err and "[rank 0]" in err and "Logging error" not in err
+
+
+def test_fp32_main_gradients_for_16_bit_parameters():
+    """``FusedAdamW(..., grad_dtype=torch.float32)``: bf16 parameters, gradients of the micro-batches of a step add up
+    in an fp32 flat buffer. The accumulated gradient equals the fp32 sum of the 16-bit micro-batch gradients exactly,
+    where accumulation in bf16 (the default) differs from it by a rounding per addition; a step runs on it."""
+    import oslo_b200 as ob
+    from oslo_b200.optim import FusedAdamW
+
+    def make():
+        torch.manual_seed(0)
+        cfg = ob.GPTJConfig(vocab_size=64, n_positions=16, n_embd=32, n_layer=2, n_head=2, rotary_dim=8,
+                            torch_dtype=torch.bfloat16)
+        return ob.GPTJForCausalLM(cfg).to(torch.bfloat16).train()
+
+    ids = [torch.randint(0, 64, (2, 12), generator=torch.Generator().manual_seed(10 + i)) for i in range(16)]
+
+    def accumulate(grad_dtype):
+        model = make()
+        opt = FusedAdamW(model.parameters(), lr=1e-3, grad_dtype=grad_dtype)
+        opt.zero_grad()
+        singles = []
+        for x in ids:
+            before = opt.buf.flat_g.clone()
+            (model(input_ids=x, labels=x).loss / len(ids)).backward()
+            singles.append((opt.buf.flat_g.double() - before.double()))
+        return model, opt, singles
+
+    model32, opt32, _ = accumulate(torch.float32)
+    assert opt32.buf.flat_g.dtype == torch.float32 and opt32.buf.flat_p.dtype == torch.bfloat16
+    p0 = next(model32.parameters())
+    assert p0.grad.dtype == torch.float32 and p0.grad.data_ptr() == opt32.buf.flat_g.data_ptr()
+    # every micro-batch gradient is a bf16 tensor that autograd adds into the fp32 buffer: replay that sum in fp64
+    replay = make()
+    exact = torch.zeros(opt32.buf.padded, dtype=torch.float64)
+    for x in ids:
+        replay.zero_grad()
+        (replay(input_ids=x, labels=x).loss / len(ids)).backward()
+        flat = torch.zeros_like(exact)
+        for p, off in zip(replay.parameters(), opt32.buf.offsets):
+            flat[off: off + p.numel()] = p.grad.reshape(-1).double()
+        exact += flat
+    err32 = (opt32.buf.flat_g.double() - exact).norm() / exact.norm()
+    model16, opt16, _ = accumulate(None)
+    assert opt16.buf.flat_g.dtype == torch.bfloat16
+    err16 = (opt16.buf.flat_g.double() - exact).norm() / exact.norm()
+    assert err32 < 1e-6 and err16 > 20 * err32, (float(err32), float(err16))
+    w0 = opt32.buf.flat_p.clone()
+    assert opt32.step() and not torch.equal(opt32.buf.flat_p, w0)
+    opt32.zero_grad()
+    assert float(opt32.buf.flat_g.abs().max()) == 0.0 and p0.grad.dtype == torch.float32

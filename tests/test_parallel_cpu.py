@@ -257,6 +257,57 @@ def test_zero1_and_bucketed_ddp_match_single_process(accumulate):
         assert torch.allclose(got[k], v, atol=2e-4), (k, (got[k] - v).abs().max())
 
 
+def _train_wide_grads(rank, world, tmpdir):
+    """bf16 parameters, fp32 gradient buffer, ZeRO-1 + bucketed wrapper on ``world`` ranks (one rank = the oracle)."""
+    import contextlib
+    import torch.distributed as dist
+    from oslo_b200.optim import FusedAdamW
+    from oslo_b200.parallel.data_parallel import DistributedDataParallel
+    torch.manual_seed(7)
+    model = ob.parallelize(ob.GPTJForCausalLM(tiny_config("gptj")).to(torch.bfloat16).train(), tensor_parallel_size=1)
+    mpu = model.mpu
+    opt = FusedAdamW(model.gpu_parameters(), lr=1e-2, grad_dtype=torch.float32, max_grad_norm=1.0,
+                     shard_group=mpu.get_data_parallel_group() if world > 1 else None)
+    call = DistributedDataParallel(model, mpu, optimizer=opt, bucket_mb=0.01) if world > 1 else model
+    assert opt.buf.flat_g.dtype == torch.float32 and opt.buf.symm_g is None
+    b = batch(seed=3, bsz=8, vocab=104)
+    n = 8 // world
+    mine = {k: v[rank * n:(rank + 1) * n] for k, v in b.items()}
+    opt.zero_grad()
+    for i in range(2):          # two micro-batches per step
+        mb = {k: v[i * (n // 2):(i + 1) * (n // 2)] for k, v in mine.items()}
+        hold = call.no_sync() if (world > 1 and i == 0) else contextlib.nullcontext()
+        with hold:
+            (call(**mb).loss / 2).backward()
+    if world > 1:
+        call.finish_gradient_sync()                     # buckets summed over the ranks, in fp32
+    grad = opt.buf.flat_g[: opt.buf.numel].clone() / world
+    if rank == 0:
+        torch.save(grad, os.path.join(tmpdir, f"grad{world}.pt"))
+    opt.step()
+    flat = opt.buf.flat_p.float().clone()
+    if world > 1:
+        other = [torch.empty_like(flat) for _ in range(world)]
+        dist.all_gather(other, flat)
+        assert all(torch.equal(o, other[0]) for o in other), "replicas diverged"
+        others_grad = [torch.empty_like(grad) for _ in range(world)]
+        dist.all_gather(others_grad, grad)
+        assert all(torch.equal(o, others_grad[0]) for o in others_grad), "summed gradients differ between the ranks"
+
+
+def test_fp32_gradient_buffer_with_zero1_and_bucketed_ddp():
+    """``grad_dtype=torch.float32`` under data parallelism: fp32 buckets through the all-reduce path, the owned shard
+    stepped, bf16 parameters gathered. The averaged gradient of two ranks equals one process's on the whole batch up
+    to the bf16 rounding of the individual micro-batch gradients (the micro-batches are cut differently)."""
+    with tempfile.TemporaryDirectory() as d:
+        run_distributed(_train_wide_grads, 1, d)
+        run_distributed(_train_wide_grads, 2, d)
+        one = torch.load(os.path.join(d, "grad1.pt"), weights_only=True)
+        two = torch.load(os.path.join(d, "grad2.pt"), weights_only=True)
+    assert one.dtype == two.dtype == torch.float32
+    assert (one - two).norm() / one.norm() < 2e-2, float((one - two).norm() / one.norm())
+
+
 def test_3d_parallel_with_data_parallel_replicas():
     """TP=2 x PP=2 x DP=2 on 8 gloo ranks (the GPT-Neo configuration of the benchmark list, in miniature): merged
     weights equal the single-process oracle whose two micro-batch gradients are averaged like the two replicas'."""
