@@ -59,6 +59,15 @@ def test_preprocess_train_resume_merge_generate(tmp_path):
     for k in a:
         assert torch.equal(a[k], b[k]), k
 
+    # the split files of the first run, merged by the stand-alone script, give the same file as --merge did; the script
+    # also checks the merged model's logits against the parallel model's
+    again = str(tmp_path / "again")
+    out = _torchrun(4, "merge.py", "--model", "gptj", "--checkpoint", full, "--tp", "2", "--pp", "2", "--output", again,
+                    "--check")
+    assert "logit difference" in out.stdout
+    m = torch.load(os.path.join(again, "pytorch_model.bin"), weights_only=True)
+    assert m.keys() == a.keys() and all(torch.equal(m[k], a[k]) for k in a)
+
     # the 4 blocks split 3 + 1 over the two stages instead of 2 + 2: where the stage boundary lies does not change
     # the result (up to the summation order of the gradient norm over the ranks)
     uneven = str(tmp_path / "uneven")
