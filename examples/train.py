@@ -4,6 +4,13 @@
         --model gptj --config config.json --tp 2 --pp 2 --micro-batch-size 2 --batch-size 8 --seq 2048 \
         --data corpus --steps 1000 --save out --save-every 200
 
+``--save-every`` writes checkpoint generations ``out/checkpoints/step-XXXXXXXX`` with a pointer to the newest complete
+one; ``--auto-resume`` continues from it when it exists, so that
+
+    python -m torch.distributed.run --max-restarts 3 ... examples/train.py ... --save out --save-every 200 --auto-resume
+
+restarts itself from its last checkpoint after a rank has died (torchrun re-launches all workers).
+
 ``--data`` is the prefix of a ``.bin`` / ``.idx`` pair written by ``examples/preprocess.py``; without it the
 script trains on synthetic token ids. ``--tiny`` replaces the config by a few-layer model (used by the CPU
 test of this script: ``OSLO_B200_BACKEND=gloo`` runs the same code on CPU ranks).
@@ -27,7 +34,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import oslo_b200 as ob  # noqa: E402
 from oslo_b200.optim import DynamicLossScaler, FusedAdamW  # noqa: E402
 from oslo_b200.parallel.data_parallel import DistributedDataParallel  # noqa: E402
-from oslo_b200.utils import MetricsLogger, get_logger  # noqa: E402
+from oslo_b200.utils import CheckpointManager, MetricsLogger, get_logger  # noqa: E402
 
 FAMILIES = {
     "gpt2": (ob.GPT2Config, ob.GPT2LMHeadModel, dict(n_embd=64, n_layer=4, n_head=4)),
@@ -62,7 +69,17 @@ def parse_args():
     ap.add_argument("--save", help="directory for checkpoints")
     ap.add_argument("--save-every", type=int, default=0)
     ap.add_argument("--merge", action="store_true", help="also write one merged HF-compatible pytorch_model.bin")
-    ap.add_argument("--resume", action="store_true", help="continue from the checkpoint in --save")
+    ap.add_argument("--resume", action="store_true",
+                    help="continue from the newest complete periodic checkpoint under <--save>/checkpoints, or from the "
+                         "final checkpoint in --save when there is none")
+    ap.add_argument("--auto-resume", action="store_true",
+                    help="continue from the newest complete periodic checkpoint under <--save>/checkpoints if there is "
+                         "one, else start fresh: with `torchrun --max-restarts N` a job that lost a rank restarts "
+                         "itself from its last checkpoint")
+    ap.add_argument("--keep", type=int, default=2, help="periodic checkpoints to keep (--save-every)")
+    ap.add_argument("--fail-at-step", type=int, default=0,
+                    help="testing: the last rank raises at this step during the first launch attempt (host-side fault "
+                         "injection for --auto-resume; restarts see TORCHELASTIC_RESTART_COUNT > 0 and run through)")
     ap.add_argument("--metrics", help="JSONL file for per-step metrics (rank 0)")
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--watchdog", action="store_true",
@@ -76,7 +93,7 @@ def build_model(args, dtype):
     par = dict(tensor_parallel_size=args.tp, pipeline_parallel_size=args.pp,
                micro_batch_size=args.micro_batch_size or args.batch_size, seed=args.seed,
                sequence_parallel=args.sequence_parallel)
-    source = args.save if args.resume else args.init
+    source = args.resume_dir or args.init
     if args.pipeline_partition and args.pp > 1:
         if args.pipeline_partition == "balanced":
             from oslo_b200.parallel.engine_pipeline import balanced_partition
@@ -123,6 +140,14 @@ def main() -> None:
     if on_gpu:
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     dtype = DTYPES[args.dtype or ("bf16" if on_gpu else "fp32")]
+    # periodic checkpoints are generations under <save>/checkpoints with a pointer to the newest complete one; the final
+    # checkpoint goes to <save> itself
+    manager = CheckpointManager(os.path.join(args.save, "checkpoints"), keep=args.keep) if args.save else None
+    args.resume_dir = args.save if args.resume else None
+    if (args.resume or args.auto_resume) and manager is not None:
+        from oslo_b200.parallel.mpu import MPU
+        MPU.initialize_distributed()                    # the ranks agree on the generation every one of them can read
+        args.resume_dir = manager.latest_usable(args.tp, args.pp) or args.resume_dir
     model = build_model(args, dtype)
     if on_gpu:
         model.fuse()
@@ -140,9 +165,9 @@ def main() -> None:
                      loss_scaler=DynamicLossScaler() if dtype == torch.float16 else None)
     engine = DistributedDataParallel(model, mpu, optimizer=opt) if dp > 1 else model
     step0 = 0
-    if args.resume:
-        step0 = model.load_training_state(args.save, opt)["step"]
-        log.info("resumed from %s at step %d", args.save, step0)
+    if args.resume_dir:
+        step0 = model.load_training_state(args.resume_dir, opt)["step"]
+        log.info("resumed from %s at step %d", args.resume_dir, step0)
     micro = args.micro_batch_size or args.batch_size
     accum = args.batch_size // micro
     scale = (lambda l: opt.loss_scaler.scale(l)) if opt.loss_scaler is not None else (lambda l: l)
@@ -164,7 +189,11 @@ def main() -> None:
         if args.merge:
             model.save_pretrained_with_parallel(os.path.join(args.save, "merged"), save_with_merging=True)
 
+    first_attempt = os.environ.get("TORCHELASTIC_RESTART_COUNT", "0") == "0"
     for step in range(step0 + 1, args.steps + 1):
+        if args.fail_at_step == step and first_attempt and dist.is_initialized() \
+                and dist.get_rank() == dist.get_world_size() - 1:
+            raise RuntimeError(f"injected failure at step {step} (--fail-at-step)")
         if beat is not None:
             beat.check_peers()      # host-side: raises before this rank enters a collective nobody will join
         ids = next(data)
@@ -189,9 +218,11 @@ def main() -> None:
             raise_if_device_error(ids)
         rec = metrics.log_step(step, loss=total, tokens=dp * args.batch_size * args.seq, skipped=not stepped)
         log.info("step %d loss %.4f %.0f tokens/s", step, total, rec.get("tokens_per_s", 0.0))
-        if args.save_every and step % args.save_every == 0:
-            save(step)
+        if args.save_every and step % args.save_every == 0 and step < args.steps:
+            manager.save(model, opt, step)              # collective; the pointer moves when every rank has written
     save(args.steps)
+    if args.save_every and manager is not None:
+        manager.save(model, opt, args.steps)            # the newest generation is never older than the final checkpoint
     if beat is not None:
         beat.stop()
     if dist.is_initialized():

@@ -392,7 +392,8 @@ class PreTrainedModel(nn.Module, ParallelizationMixin, FusedKernelMixin, Generat
             state_dict = self.state_dict()
         ignore = self._keys_to_ignore_on_save or []
         state_dict = {k: v for k, v in state_dict.items() if k not in ignore}
-        save_function(state_dict, os.path.join(save_directory, WEIGHTS_NAME))
+        from .utils.checkpoint import atomic_save
+        atomic_save(state_dict, os.path.join(save_directory, WEIGHTS_NAME), save_function)
 
 
 @contextlib.contextmanager

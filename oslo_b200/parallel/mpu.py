@@ -182,6 +182,16 @@ class MPU:
                 # communicator and stream, which is why the pipeline engine gives every (neighbour pair, direction) a
                 # group of its own.
                 kwargs["device_id"] = torch.device("cuda", torch.cuda.current_device())
+        attempt = os.environ.get("TORCHELASTIC_RESTART_COUNT")
+        if attempt is not None:
+            # Workers re-launched by `torchrun --max-restarts` meet through the SAME key-value store as the attempt
+            # before them, and a sub-group's rendezvous keys are named after the group ("1/...", "2/..."): without a
+            # prefix of their own the new ranks would read the addresses (gloo) or the communicator id (NCCL) that the
+            # dead ranks left there.
+            from torch.distributed.rendezvous import rendezvous
+            it = rendezvous("env://", rank, world, **({"timeout": kwargs["timeout"]} if "timeout" in kwargs else {}))
+            store, rank, world = next(it)
+            kwargs["store"] = dist.PrefixStore(f"attempt_{attempt}/", store)
         dist.init_process_group(backend=backend, rank=rank, world_size=world, **kwargs)
 
     def _new_group(self, ranks: Sequence[int]):

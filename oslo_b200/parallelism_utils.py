@@ -264,7 +264,8 @@ class ParallelizationMixin:
         full = os.path.join(path, fn)
         if not os.path.isfile(full):
             raise FileNotFoundError(full)
-        state = torch.load(full, map_location="cpu", weights_only=True)
+        from .utils.checkpoint import load_file
+        state = load_file(full)           # names the file if it is truncated or damaged
         own = self.state_dict()
         bad = []
         for k, v in state.items():
@@ -309,6 +310,7 @@ class ParallelizationMixin:
         """
         if os.path.isfile(save_directory):
             raise ValueError(f"{save_directory} is a file, expected a directory")
+        from .utils.checkpoint import atomic_save      # write beside, then rename: no truncated file after a crash
         os.makedirs(save_directory, exist_ok=True)
         mpu = getattr(self, "mpu", None)
         rank0 = (not dist.is_initialized()) or dist.get_rank() == 0
@@ -332,7 +334,7 @@ class ParallelizationMixin:
                     cfg.save_pretrained(save_directory)
                 ignore = self._keys_to_ignore_on_save or []
                 state = {k: v for k, v in state.items() if k not in ignore}
-                save_function(state, os.path.join(save_directory, "pytorch_model.bin"))
+                atomic_save(state, os.path.join(save_directory, "pytorch_model.bin"), save_function)
             _barrier()
             return
         if save_config and rank0:
@@ -354,7 +356,7 @@ class ParallelizationMixin:
             out[k] = v.detach().cpu()
         fn = WEIGHTS_NAME_PARALLEL.format(tp=mpu.get_tensor_parallel_rank(), pp=mpu.get_pipeline_parallel_rank())
         if mpu.get_data_parallel_rank() == 0:
-            save_function(out, os.path.join(save_directory, fn))
+            atomic_save(out, os.path.join(save_directory, fn), save_function)
         _barrier()
         logger.info("saved %s", os.path.join(save_directory, fn))
 

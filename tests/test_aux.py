@@ -1,5 +1,6 @@
 """Auxiliary subsystems on the host: heartbeat failure detection, deadlines, timers, metrics, config."""
 import json
+import os
 import time
 
 import pytest
@@ -362,3 +363,51 @@ def test_fp32_main_gradients_for_16_bit_parameters():
     assert opt32.step() and not torch.equal(opt32.buf.flat_p, w0)
     opt32.zero_grad()
     assert float(opt32.buf.flat_g.abs().max()) == 0.0 and p0.grad.dtype == torch.float32
+
+
+def test_checkpoint_generations_survive_a_failed_save_and_a_damaged_file(tmp_path):
+    """``CheckpointManager`` in one process: the pointer names the newest complete generation, old generations are
+    pruned, a save that dies half way (host-side injection: the sidecar writer raises) leaves pointer and files of
+    the previous generation alone, ``atomic_save`` never replaces a file by a partial one, and an unreadable file is
+    reported by name."""
+    import oslo_b200 as ob
+    from oslo_b200.optim import FusedAdamW
+    from oslo_b200.utils import CheckpointManager, CheckpointUnreadable, atomic_save
+    from oslo_b200.utils.checkpoint import load_file
+    torch.manual_seed(0)
+    model = ob.GPT2LMHeadModel(ob.GPT2Config(vocab_size=61, n_positions=16, n_embd=16, n_layer=1, n_head=2))
+    opt = FusedAdamW(model.parameters(), lr=1e-3)
+    mgr = CheckpointManager(str(tmp_path / "ck"), keep=2)
+    assert mgr.pointer() is None and mgr.latest_usable() is None
+    for step in (2, 4, 6):
+        mgr.save(model, opt, step)
+    assert [os.path.basename(g) for g in mgr.generations()] == ["step-00000006", "step-00000004"]
+    assert os.path.basename(mgr.pointer()) == "step-00000006" == os.path.basename(mgr.latest_usable())
+
+    def boom(*a, **k):
+        raise OSError("disk full")
+    good = model.save_training_state
+    object.__setattr__(model, "save_training_state", boom)
+    with pytest.raises(OSError):
+        mgr.save(model, opt, 8)
+    object.__setattr__(model, "save_training_state", good)
+    assert os.path.basename(mgr.pointer()) == "step-00000006"           # the half-written generation is not "latest"
+    assert os.path.basename(mgr.latest_usable()) == "step-00000006"     # ... and is skipped (no sidecar)
+
+    victim = os.path.join(mgr.pointer(), "pytorch_model.bin")
+    with open(victim, "r+b") as f:
+        f.truncate(100)
+    with pytest.raises(CheckpointUnreadable, match="pytorch_model.bin"):
+        load_file(victim)
+    assert os.path.basename(mgr.latest_usable()) == "step-00000004"     # falls back past the damaged generation
+
+    target = str(tmp_path / "value.pt")
+    atomic_save({"a": 1}, target)
+
+    def half_write(obj, path):
+        with open(path, "wb") as f:
+            f.write(b"partial")
+        raise OSError("killed while writing")
+    with pytest.raises(OSError):
+        atomic_save({"a": 2}, target, half_write)
+    assert torch.load(target)["a"] == 1

@@ -88,3 +88,34 @@ def test_train_example_data_parallel_zero1(tmp_path):
               "--steps", "2", "--save", out, "--watchdog")
     assert os.path.isfile(os.path.join(out, "pytorch_model.bin"))      # no model parallelism: the plain HF file
     assert all(os.path.isfile(os.path.join(out, f"oslo_state_tp=0_pp=0_dp={d}.pt")) for d in range(2))
+
+
+def test_training_restarts_itself_from_the_last_complete_checkpoint(tmp_path):
+    """Elastic recovery with a host-side fault: the last rank raises at step 5 of 6 during the first launch attempt;
+    ``torchrun --max-restarts 1`` launches the workers again, ``--auto-resume`` finds the generation of step 4 and the
+    run ends with exactly the weights of an uninterrupted run. A generation whose shard was damaged afterwards is
+    skipped by all ranks together."""
+    common = ["--model", "gptj", "--tiny", "--tp", "2", "--batch-size", "4", "--micro-batch-size", "2", "--seq", "16",
+              "--lr", "1e-3", "--steps", "6", "--save-every", "2", "--auto-resume"]
+    straight, broken = str(tmp_path / "straight"), str(tmp_path / "broken")
+    _torchrun(2, "train.py", *common, "--save", straight)
+    r = _run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--max-restarts=1",
+              "--master-addr", "127.0.0.1", "--master-port", str(_port()), os.path.join(EX, "train.py"), *common,
+              "--save", broken, "--fail-at-step", "5"])
+    assert "injected failure at step 5" in r.stderr and "resumed from" in r.stderr and "step-00000004" in r.stderr
+    for tp in range(2):
+        a = torch.load(os.path.join(straight, f"pytorch_model_tp={tp}_pp=0.bin"), weights_only=True)
+        b = torch.load(os.path.join(broken, f"pytorch_model_tp={tp}_pp=0.bin"), weights_only=True)
+        assert a.keys() == b.keys() and all(torch.equal(a[k], b[k]) for k in a)
+    gens = sorted(os.listdir(os.path.join(broken, "checkpoints")))
+    assert gens == ["latest", "step-00000004", "step-00000006"]          # --keep 2
+    assert open(os.path.join(broken, "checkpoints", "latest")).read().strip() == "step-00000006"
+
+    # damage one shard of the newest generation: every rank falls back to step 4 (and trains on to step 8)
+    victim = os.path.join(broken, "checkpoints", "step-00000006", "pytorch_model_tp=1_pp=0.bin")
+    with open(victim, "r+b") as f:
+        f.truncate(os.path.getsize(victim) // 2)
+    more = [("8" if x == "6" else x) for x in common]
+    r = _torchrun(2, "train.py", *more, "--save", broken)
+    assert "step-00000004" in r.stderr and "resumed from" in r.stderr
+    assert open(os.path.join(broken, "checkpoints", "latest")).read().strip() == "step-00000008"
