@@ -182,8 +182,8 @@ class MPU:
                 # communicator and stream, which is why the pipeline engine gives every (neighbour pair, direction) a
                 # group of its own.
                 kwargs["device_id"] = torch.device("cuda", torch.cuda.current_device())
-        attempt = os.environ.get("TORCHELASTIC_RESTART_COUNT")
-        if attempt is not None:
+        attempt = os.environ.get("TORCHELASTIC_RESTART_COUNT", "0")
+        if attempt != "0":         # (all workers of one attempt see the same count)
             # Workers re-launched by `torchrun --max-restarts` meet through the SAME key-value store as the attempt
             # before them, and a sub-group's rendezvous keys are named after the group ("1/...", "2/..."): without a
             # prefix of their own the new ranks would read the addresses (gloo) or the communicator id (NCCL) that the
