@@ -423,7 +423,8 @@ def _load_one_file(path: str) -> Dict[str, torch.Tensor]:
     if path.endswith(".safetensors"):
         from safetensors.torch import load_file
         return load_file(path)
-    return torch.load(path, map_location="cpu", weights_only=True)
+    from .utils.checkpoint import load_file as load_checked
+    return load_checked(path)      # a truncated / damaged file is reported by name
 
 
 def _load_sharded(directory: str, index_name: str) -> Dict[str, torch.Tensor]:

@@ -340,6 +340,34 @@ class FusedAdamW:
                     loss_scaler=self.loss_scaler.state_dict() if self.loss_scaler is not None else None,
                     group_lrs=[g["lr"] for g in self.param_groups])
 
+    @staticmethod
+    def reshard_state(states: List[Dict[str, object]], shards: int, shard_rank: int, shard_numel: int) -> Dict[str, object]:
+        """The state of shard ``shard_rank`` of ``shards`` (``shard_numel`` elements each) cut out of the states that the
+        ranks of ANOTHER data-parallel size saved: ZeRO-1 shards are consecutive slices of one flat buffer, so a job
+        that continues with fewer or more replicas (same tensor / pipeline layout) re-cuts them. ``states`` may hold
+        only the old shards that overlap the new one; what lies beyond the old buffer's padded end is padding here too."""
+        if not states:
+            raise ValueError("no optimizer states to re-cut")
+        old = sorted(states, key=lambda s: int(s["shard_rank"]))
+        n_old = old[0]["master"].numel()
+        lo, hi = shard_rank * shard_numel, (shard_rank + 1) * shard_numel
+        out = {k: torch.zeros(shard_numel, dtype=torch.float32) for k in ("master", "exp_avg", "exp_avg_sq")}
+        covered = 0
+        for s in old:
+            if s["master"].numel() != n_old or int(s["shards"]) != int(old[0]["shards"]):
+                raise ValueError("optimizer states of different shardings cannot be combined")
+            a = int(s["shard_rank"]) * n_old
+            x, y = max(a, lo), min(a + n_old, hi)
+            if y > x:
+                for k in out:
+                    out[k][x - lo: y - lo] = s[k][x - a: y - a]
+                covered += y - x
+        need = max(0, min(hi, int(old[0]["shards"]) * n_old) - lo)
+        if covered != need:
+            raise ValueError(f"the given states cover {covered} of the {need} elements shard {shard_rank} needs")
+        first = old[0]
+        return dict(first, shard_rank=shard_rank, shards=shards, **out)
+
     def load_state_dict(self, sd: Dict[str, object]) -> None:
         if sd["shards"] != self.shards or sd["shard_rank"] != self.shard_rank:
             raise ValueError("optimizer state was saved with a different sharding")

@@ -90,6 +90,9 @@ def load_training_state(directory: str, optimizer=None, mpu=None, restore_rng: b
     """Restore optimizer / loss scale / generators of this rank; returns ``{"step": ..., "extra": ...}``.
     The parallel layout must be the one the state was saved with (the optimizer shard is checked)."""
     path = state_file(directory, mpu)
+    resharded = _load_resharded(directory, optimizer, mpu)
+    if resharded is not None:
+        return resharded
     if not os.path.exists(path):
         raise FileNotFoundError(f"no training state for this rank: {path}")
     payload = load_file(path, weights_only=False)
@@ -104,6 +107,33 @@ def load_training_state(directory: str, optimizer=None, mpu=None, restore_rng: b
     if restore_rng:
         _set_rng_state(payload["rng"])
     return dict(step=payload["step"], extra=payload["extra"])
+
+
+def _load_resharded(directory: str, optimizer, mpu) -> Optional[Dict[str, Any]]:
+    """The job continues with another number of data-parallel replicas than it was saved with (same tensor / pipeline
+    layout): this rank's ZeRO-1 shard is re-cut from the old ranks' sidecars. Returns ``None`` when the saved sharding
+    is the current one (or there is nothing to re-cut). Generators are left alone: with another replica count the data
+    order changes anyway, so such a resume is exact in the optimizer state but not bit for bit in what follows."""
+    if optimizer is None or not hasattr(optimizer, "reshard_state"):
+        return None
+    c = _coords(mpu)
+    first = os.path.join(directory, STATE_NAME.format(tp=c["tp"], pp=c["pp"], dp=0))
+    if not os.path.exists(first):
+        return None
+    head = load_file(first, weights_only=False)
+    old_opt = head.get("optimizer")
+    if old_opt is None or int(old_opt["shards"]) == int(optimizer.shards):
+        return None
+    n_old, old_shards = old_opt["master"].numel(), int(old_opt["shards"])
+    lo, hi = optimizer.shard_rank * optimizer.shard_numel, (optimizer.shard_rank + 1) * optimizer.shard_numel
+    states = []
+    for r in range(old_shards):
+        if r * n_old < hi and (r + 1) * n_old > lo:
+            f = os.path.join(directory, STATE_NAME.format(tp=c["tp"], pp=c["pp"], dp=r))
+            states.append(old_opt if r == 0 else load_file(f, weights_only=False)["optimizer"])
+    sd = optimizer.reshard_state(states or [old_opt], optimizer.shards, optimizer.shard_rank, optimizer.shard_numel)
+    optimizer.load_state_dict(sd)
+    return dict(step=head["step"], extra=head["extra"], resharded_from=old_shards)
 
 
 # ---------------------------------------------------------------------------------------------------------------

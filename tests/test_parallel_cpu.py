@@ -360,6 +360,62 @@ def test_zero1_resume_from_per_rank_sidecars():
         run_distributed(_zero_resume, 2, "gpt2", d)
 
 
+def _elastic_dp(rank, world, tmpdir, phase):
+    """Phase "save": ``world`` data-parallel ranks with ZeRO-1 train 2 steps, save, train a third step and leave its
+    result behind. Phase "resume": another number of ranks loads that checkpoint (the optimizer shards are re-cut),
+    trains the third step on the same global batch and compares."""
+    import torch.distributed as dist
+    from oslo_b200.optim import FusedAdamW
+    cls = ob.GPTJForCausalLM
+    ckpt = os.path.join(tmpdir, "ckpt")
+
+    def step(model, opt, s):
+        b = batch(seed=21 + s, bsz=8, vocab=104)
+        n = 8 // world
+        mine = {k: v[rank * n:(rank + 1) * n] for k, v in b.items()}
+        opt.zero_grad()
+        model(**mine).loss.backward()
+        opt.step()
+
+    def optimizer(model):
+        return FusedAdamW(model.gpu_parameters(), lr=1e-2, shard_group=model.mpu.get_data_parallel_group() if world > 1 else None)
+
+    if phase == "save":
+        model = ob.parallelize(build("gptj").train(), tensor_parallel_size=1)
+        opt = optimizer(model)
+        for s in range(2):
+            step(model, opt, s)
+        model.save_pretrained_with_parallel(ckpt)
+        model.save_training_state(ckpt, opt, step=2)
+        full = [torch.empty_like(opt.master) for _ in range(world)]
+        dist.all_gather(full, opt.master)
+        step(model, opt, 2)
+        if rank == 0:
+            torch.save({"master": torch.cat(full)[: opt.buf.numel], "after": opt.buf.flat_p[: opt.buf.numel].clone()},
+                       os.path.join(tmpdir, "want.pt"))
+        return
+    want = torch.load(os.path.join(tmpdir, "want.pt"), weights_only=True)
+    model = cls.from_pretrained_with_parallel(ckpt, tensor_parallel_size=1).train()
+    opt = optimizer(model)
+    info = model.load_training_state(ckpt, opt)
+    assert info["step"] == 2 and info["resharded_from"] == 2 and opt.step_count == 2
+    lo, hi = opt._lo, min(opt._hi, opt.buf.numel)
+    assert torch.equal(opt.master[: hi - lo], want["master"][lo:hi])           # the re-cut shard is the saved state
+    assert float(opt.exp_avg_sq.abs().sum()) > 0
+    step(model, opt, 2)
+    got = opt.buf.flat_p[: opt.buf.numel]
+    assert torch.allclose(got, want["after"], atol=1e-5), float((got - want["after"]).abs().max())
+
+
+@pytest.mark.parametrize("new_world", [1, 4])
+def test_zero1_state_is_recut_when_the_number_of_replicas_changes(new_world):
+    """A job saved with 2 data-parallel replicas continues with 1 or with 4: every new rank builds its optimizer shard
+    from the old ranks' sidecars, and the next step lands where the original job's next step landed."""
+    with tempfile.TemporaryDirectory() as d:
+        run_distributed(_elastic_dp, 2, d, "save")
+        run_distributed(_elastic_dp, new_world, d, "resume")
+
+
 # ---------------------------------------------------------------------------- classification / multiple-choice heads
 def _head_config(name):
     if name == "GPT2ForSequenceClassification":
