@@ -223,9 +223,12 @@ class CheckpointManager:
         c = rank_coords(rank, world, tp, pp)
         model_file = (os.path.join(directory, WEIGHTS_NAME_PARALLEL.format(tp=c["tp"], pp=c["pp"]))
                       if tp * pp > 1 else os.path.join(directory, "pytorch_model.bin"))
+        own = os.path.join(directory, STATE_NAME.format(**c))
+        if not os.path.exists(own):      # saved with fewer data-parallel replicas: the shards get re-cut from theirs
+            own = os.path.join(directory, STATE_NAME.format(tp=c["tp"], pp=c["pp"], dp=0))
         try:
             load_file(model_file, weights_only=True)
-            load_file(os.path.join(directory, STATE_NAME.format(**c)), weights_only=False)
+            load_file(own, weights_only=False)
             return os.path.isfile(os.path.join(directory, "config.json"))
         except (OSError, CheckpointUnreadable):
             return False
