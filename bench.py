@@ -160,9 +160,11 @@ def default_plan(world: int):
         return dict(name="tp4", tp=4, pp=1), [dp_block]
     if world == 8:
         # global batch 64 x 2048 as 16 micro-batches of 4 sequences through 4 stages of 7 layers, each stage on 2 GPUs
-        # (extra blocks: the data-parallel one first, it is the same code as on 2 and 4 GPUs)
+        # (extra blocks: the data-parallel one first, it is the same code as on 2 and 4 GPUs; last GPT-Neo 1.3B as
+        # tp2 x pp2 x dp2 with 8 micro-batches of 4 sequences per replica and step)
         return (dict(name="tp2xpp4", tp=2, pp=4, micro=4),
-                [dp_block, dict(name="tp8_b8x2048", tp=8, pp=1, replica_batch=8, micro=8)])
+                [dp_block, dict(name="tp8_b8x2048", tp=8, pp=1, replica_batch=8, micro=8),
+                 dict(name="gptneo1.3b_tp2xpp2xdp2", model="gpt-neo-1.3b", tp=2, pp=2, replica_batch=32, micro=4)])
     return dp_block, []
 
 
@@ -178,10 +180,13 @@ def run_train_config(args, spec, dims, world, rank, local, dev):
     from oslo_b200.optim import FusedAdamW
     from oslo_b200.parallel.data_parallel import DistributedDataParallel
 
+    model_name = spec.get("model", args.model)
+    if "model" in spec and spec["model"] != args.model:
+        dims = MODELS[model_name]                       # an extra block on another architecture, always at full size
     n_layer, n_embd, n_head, rotary, vocab, n_pos = dims
     tp, pp = spec["tp"], spec["pp"]
     dp = world // (tp * pp)
-    if args.model.startswith("gpt-neo"):
+    if model_name.startswith("gpt-neo"):
         cfg = ob.GPTNeoConfig(vocab_size=vocab, max_position_embeddings=n_pos, hidden_size=n_embd, num_layers=n_layer,
                               num_heads=n_head, window_size=256, attention_types=[[["global", "local"], n_layer // 2]],
                               torch_dtype=torch.bfloat16, use_cache=False)
@@ -194,7 +199,7 @@ def run_train_config(args, spec, dims, world, rank, local, dev):
     seqs_per_rank = spec.get("replica_batch") or args.batch_per_gpu * tp * pp
     # 4 sequences per forward/backward per GPU keeps activations within memory; tensor-parallel replicas spread a
     # micro-batch over tp GPUs, so they take proportionally more (fewer, larger launches)
-    micro = spec.get("micro") or args.micro_batch or (4 * tp if args.model == "gptj-6b" else seqs_per_rank)
+    micro = spec.get("micro") or args.micro_batch or (4 * tp if model_name == "gptj-6b" else seqs_per_rank)
     micro = min(micro, seqs_per_rank)
     accum = seqs_per_rank // micro
 
@@ -302,7 +307,7 @@ def run_train_config(args, spec, dims, world, rank, local, dev):
     from oslo_b200.config import get_config
     block = {
         "value": tokens_step / (ms_step / 1e3), "unit": "tokens/s", "ms_per_step": ms_step,
-        "config": {"model": args.model, "global_batch": dp * seqs_per_rank, "seq_len": args.seq,
+        "config": {"model": model_name, "global_batch": dp * seqs_per_rank, "seq_len": args.seq,
                    "parallelism": par + ("+zero1" if dp > 1 else ""), "micro_batch": micro, "grad_accum": accum,
                    "optimizer": "AdamW fp32 master (fused)", "activation_checkpointing": bool(args.checkpoint_activations),
                    "fused_tp_collectives": bool(get_config().fused_tp_comm) if tp > 1 else None,

@@ -97,7 +97,10 @@ def test_default_plan_follows_the_model_parallel_sweep():
     assert (names[4][0]["tp"], names[4][0]["pp"]) == (4, 1)
     p8, also8 = names[8]
     assert (p8["tp"], p8["pp"], p8["micro"]) == (2, 4, 4)          # 64 sequences as 16 micro-batches of 4
-    assert [a["name"] for a in also8] == ["dp8_zero1", "tp8_b8x2048"] and also8[1]["replica_batch"] == 8
+    assert [a["name"] for a in also8] == ["dp8_zero1", "tp8_b8x2048", "gptneo1.3b_tp2xpp2xdp2"]
+    assert also8[1]["replica_batch"] == 8
+    neo = also8[2]       # GPT-Neo 1.3B: 2 replicas of tp2 x pp2, 8 micro-batches of 4 sequences per replica and step
+    assert neo["model"] == "gpt-neo-1.3b" and 8 // (neo["tp"] * neo["pp"]) == 2 and neo["replica_batch"] // neo["micro"] == 8
 
 
 def test_fusion_mode_times_generate_before_and_after_fuse():
