@@ -8,8 +8,8 @@ ids uniform in [0, vocab) with a fixed seed; weights random-init.
 
 Without ``--tp`` / ``--pp`` the headline follows the model-parallel sweep: one GPU, ``tp2`` on 2 GPUs, ``tp4`` on
 4, ``tp2 x pp4`` (16 micro-batches of 4 sequences, 1F1B) on 8; the other named configurations of that GPU count
-(ZeRO-1 data parallelism over all GPUs; on 8 GPUs also ``tp8`` with a global batch of 8 x 2048) are measured in
-the same invocation and reported under ``"also"``. ``--tp`` / ``--pp`` time exactly one layout.
+(ZeRO-1 data parallelism over all GPUs; on 8 GPUs also ``tp8`` with a global batch of 8 x 2048 and GPT-Neo 1.3B as
+``tp2 x pp2 x dp2``) are measured in the same invocation and reported under ``"also"``. ``--tp`` / ``--pp`` time exactly one layout.
 
 Timed regions (CUDA events on the compute stream, barrier + synchronize on both sides, max over ranks):
   * ``value``: K full steps (forward, backward, gradient reduction, optimizer) with inputs already on
