@@ -361,6 +361,19 @@ class DecoderBackbone(PreTrainedModel):
         return self.run_protocol(input_ids=input_ids, **kw)
 
 
+def run_forward_pre_hooks(module: nn.Module) -> None:
+    """Run ``module``'s forward pre-hooks without calling it. Code that reads a module's parameters directly (the LM
+    head's weight handed to the fused loss) calls this first: wrappers hang per-module work on those hooks - the
+    data-parallel wrapper makes the compute stream wait there for the parameter buckets that are still in flight
+    after the optimizer step - and they must see every use of the parameters, not only ``module(...)`` calls."""
+    with_kwargs = getattr(module, "_forward_pre_hooks_with_kwargs", {})
+    for hid, hook in list(module._forward_pre_hooks.items()):
+        if with_kwargs.get(hid):
+            hook(module, (), {})
+        else:
+            hook(module, ())
+
+
 def shifted_lm_labels(labels: Tensor) -> Tensor:
     """Labels aligned with logits rows: position ``i`` predicts token ``i+1``; the last column is ignored."""
     shifted = torch.full_like(labels, -100)
@@ -398,6 +411,8 @@ class CausalLMHeadMixin:
         kw["logits"] = None
         kw["loss"] = None
         vocab_sharded = mpu is not None and mpu.tp > 1 and getattr(head, "vocab_parallel", False)
+        if vocab_sharded or not want_logits:
+            run_forward_pre_hooks(head)      # the branches below read head.weight / head.bias without calling head
         if want_logits:
             if vocab_sharded:
                 x = mpu.broadcast(hs)

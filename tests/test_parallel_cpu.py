@@ -416,6 +416,44 @@ def test_zero1_state_is_recut_when_the_number_of_replicas_changes(new_world):
         run_distributed(_elastic_dp, new_world, d, "resume")
 
 
+def _every_unit_announces_itself(rank, world, kind, tp, pp):
+    """Forward pre-hooks on every forward unit of the (stage's) model: a training forward must fire all of them, also
+    for modules whose parameters are read without calling the module (the LM head inside the fused loss)."""
+    from oslo_b200.parallel.data_parallel import forward_units
+    model = build(kind).train()
+    if world > 1:
+        model = ob.parallelize(model, tensor_parallel_size=tp, pipeline_parallel_size=pp, micro_batch_size=2)
+    gm = model.gpu_modules() if world > 1 else model
+    units = forward_units(gm)
+    covered = {id(p) for m in units for p in m.parameters()}
+    assert all(id(p) in covered for p in gm.parameters())
+    for out_logits in (False, True):
+        fired = set()
+        handles = [m.register_forward_pre_hook(lambda mod, args: fired.add(id(mod))) for m in units]
+        b = batch(vocab=104 if kind == "gptj" else 101)
+        out = model(**b, output_logits=out_logits)
+        if pp > 1:
+            for o in out:
+                o.loss.backward()
+        else:
+            out.loss.backward()
+        missing = [type(m).__name__ for m in units if id(m) not in fired]
+        for h in handles:
+            h.remove()
+        assert not missing, (kind, tp, pp, out_logits, missing)
+
+
+@pytest.mark.parametrize("kind,tp,pp", [("gpt2", 1, 1), ("gpt_neo", 1, 1), ("gptj", 1, 1), ("gptj", 2, 1), ("gptj", 1, 2),
+                                        ("gpt2", 1, 2)])
+def test_every_forward_unit_runs_its_pre_hooks(kind, tp, pp):
+    """What the overlapped ZeRO-1 parameter all-gather relies on: it makes the compute stream wait for a unit's
+    parameter buckets in that unit's forward pre-hook."""
+    if tp * pp == 1:
+        _every_unit_announces_itself(0, 1, kind, 1, 1)
+    else:
+        run_distributed(_every_unit_announces_itself, tp * pp, kind, tp, pp)
+
+
 # ---------------------------------------------------------------------------- classification / multiple-choice heads
 def _head_config(name):
     if name == "GPT2ForSequenceClassification":
