@@ -28,6 +28,14 @@ def atomic_save(obj: Any, path: str, save_function: Callable = torch.save) -> No
     name (the previous file, if any, stays in place until the new one is complete)."""
     tmp = path + ".tmp"
     save_function(obj, tmp)
+    try:                                  # the bytes are on the device before the name changes
+        fd = os.open(tmp, os.O_RDONLY)
+        try:
+            os.fsync(fd)
+        finally:
+            os.close(fd)
+    except OSError:
+        pass                              # a save_function that wrote elsewhere, or a filesystem without fsync
     os.replace(tmp, path)
 
 
