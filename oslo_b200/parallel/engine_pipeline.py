@@ -61,21 +61,23 @@ def balanced_partition(num_blocks: int, num_stages: int, head_blocks: float = 1.
     best, best_key = None, None
     even = L / P
 
-    def rec(stage: int, left: int, acc: List[int]) -> None:
+    def rec(stage: int, left: int, acc: List[int], worst: float) -> None:
         nonlocal best, best_key
+        if best_key is not None and worst > best_key[0] + 1e-9:
+            return                                    # some stage of this prefix is already busier than the best split
         if stage == P - 1:
             parts = acc + [left]
-            loads = [n + (embed_blocks if i == 0 else 0.0) + (head_blocks if i == P - 1 else 0.0) for i, n in enumerate(parts)]
-            key = (round(max(loads), 6), round(sum((n - even) ** 2 for n in parts), 6), parts)
+            worst = max(worst, left + head_blocks)
+            key = (round(worst, 6), round(sum((n - even) ** 2 for n in parts), 6), parts)
             if best_key is None or key < best_key:
                 best, best_key = parts, key
             return
         lo = max(1, int(even) - 2)
         hi = min(left - (P - 1 - stage), int(even) + 3)
         for n in range(lo, hi + 1):
-            rec(stage + 1, left - n, acc + [n])
+            rec(stage + 1, left - n, acc + [n], max(worst, n + (embed_blocks if stage == 0 else 0.0)))
 
-    rec(0, L, [])
+    rec(0, L, [], 0.0)
     if best is None or min(best) < 1:      # the window around the even split found nothing valid (tiny models)
         base = L // P
         best = [base] * (P - 1) + [L - base * (P - 1)]
