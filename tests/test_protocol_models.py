@@ -283,5 +283,13 @@ def test_signal_words_survive_grids_that_change_between_launches(world):
 def test_signal_word_model_catches_a_put_that_does_not_wait_for_an_empty_word():
     """Negative control: a put that stores without waiting for the word to be empty. A peer that races ahead then
     overwrites the signal a slow rank has not consumed yet, which shows as a wrong tag or as a wait that never ends."""
-    bad, dead, leftovers = _run_signal_words(3, [1, 2, 1, 2, 1, 2], _one_rank_lags, blind_put=True)
-    assert bad or dead or leftovers, "the model failed to expose the overwritten signal"
+    def long_lag(rank, launch, block, meeting, where, rnd):
+        return 0.05 if (rank == 0 and where == "between") else 0.0
+
+    exposed = False
+    for _ in range(3):                                 # a loaded machine may hide the race once; not three times
+        bad, dead, leftovers = _run_signal_words(3, [1, 2, 1, 2, 1, 2], long_lag, blind_put=True)
+        exposed = bool(bad or dead or leftovers)
+        if exposed:
+            break
+    assert exposed, "the model failed to expose the overwritten signal"
