@@ -134,9 +134,11 @@ class FlatBuffers:
             view = self.flat_p[off: off + p.numel()].view(p.shape)
             view.copy_(p.data)
             p.data = view
-            if wide:
-                # autograd converts every incoming gradient to this dtype and accumulates in it: micro-batch gradients
-                # of 16-bit parameters add up in fp32
+            if getattr(p, "grad_dtype", self.flat_g.dtype) != self.flat_g.dtype:
+                # `grad_dtype` is what autograd converts incoming gradients to and accumulates in: with an fp32 buffer
+                # the micro-batch gradients of 16-bit parameters add up in fp32. (Also the way back: a parameter that
+                # an earlier buffer had switched to fp32 gradients.) The attribute only changes while .grad is unset.
+                p.grad = None
                 p.grad_dtype = self.flat_g.dtype
             p.grad = self.flat_g[off: off + p.numel()].view(p.shape)
             # the view lives as long as the buffer and is zeroed every step: weight-gradient GEMMs may add into it
