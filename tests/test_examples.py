@@ -119,3 +119,29 @@ def test_training_restarts_itself_from_the_last_complete_checkpoint(tmp_path):
     r = _torchrun(2, "train.py", *more, "--save", broken)
     assert "step-00000004" in r.stderr and "resumed from" in r.stderr
     assert open(os.path.join(broken, "checkpoints", "latest")).read().strip() == "step-00000008"
+
+
+def test_preprocess_example_converts_a_directory_tree_and_continues_after_an_interruption(tmp_path):
+    src = tmp_path / "corpora"
+    (src / "a").mkdir(parents=True)
+    (src / "b").mkdir()
+    with open(src / "a" / "big.jsonl", "w") as f:
+        for i in range(30):
+            f.write(json.dumps({"text": f"document number {i} of the big file"}) + "\n")
+    with open(src / "b" / "small.txt", "w") as f:
+        f.write("first document\n\nsecond document\n")
+    out = tmp_path / "data"
+    cmd = [sys.executable, os.path.join(EX, "preprocess.py"), "--input-dir", str(src), "--output", str(out), "--small-first"]
+    r = _run(cmd)
+    lines = [l for l in r.stdout.splitlines() if ".bin/.idx" in l]
+    assert "small" in lines[0] and "2 documents" in lines[0] and "30 documents" in lines[1]      # smallest file first
+    assert open(out / "done.txt").read().split() == [os.path.join("b", "small.txt"), os.path.join("a", "big.jsonl")]
+    from oslo_b200.data import MMapIndexedDataset
+    assert len(MMapIndexedDataset(str(out / "a" / "big"))) == 30 and len(MMapIndexedDataset(str(out / "b" / "small"))) == 2
+    # a batch that was interrupted after the first file: only the second is converted now
+    os.remove(out / "a" / "big.bin")
+    os.remove(out / "a" / "big.idx")
+    with open(out / "done.txt", "w") as f:
+        f.write(os.path.join("b", "small.txt") + "\n")
+    r = _run(cmd)
+    assert "already converted" in r.stdout and os.path.isfile(out / "a" / "big.bin")
