@@ -61,7 +61,7 @@ def test_reference_arm_trains_the_unmodified_reference_on_cpu_ranks(tmp_path):
     if not _reference_installed():
         pytest.skip("reference package not installed under baseline/_ref")
     from tests.dist_utils import run_distributed
-    run_distributed(_reference_ranks, 2, str(tmp_path))
+    run_distributed(_reference_ranks, 2, str(tmp_path), fresh=True)
     rec = json.load(open(tmp_path / "line.json"))
     assert rec["config"]["parallelism"].startswith("dp2") and rec["steps"] == 2 and rec["warmup"] == 1
 
@@ -85,7 +85,7 @@ def test_reference_arm_greedy_decode_runs_the_unmodified_reference_on_cpu(tmp_pa
     if not _reference_installed():
         pytest.skip("reference package not installed under baseline/_ref")
     from tests.dist_utils import run_distributed
-    run_distributed(_reference_decode_rank, 1, str(tmp_path))
+    run_distributed(_reference_decode_rank, 1, str(tmp_path), fresh=True)
 
 
 def test_default_plan_follows_the_model_parallel_sweep():
