@@ -161,6 +161,18 @@ def test_3d_parallel_training_gpt_neo():
         _check_merged(d, state, 1e-3)
 
 
+@pytest.mark.parametrize("kind,tp,pp,fuse", [("gpt_neo", 1, 2, True), ("gpt2", 2, 2, True), ("gptj", 2, 2, True),
+                                             ("gpt2", 2, 2, False), ("gptj", 2, 2, False), ("gpt_neo", 2, 2, True)])
+def test_training_matrix_over_families_and_layouts(kind, tp, pp, fuse):
+    """The remaining cells of the reference's {tp, pp, 3d} x {training, training_with_fusion} matrix for the three
+    families: losses of every step and the merged weights equal the single-process oracle."""
+    micro = 2 if pp > 1 else None
+    losses, state = oracle_steps(kind, steps=2, micro=micro)
+    with tempfile.TemporaryDirectory() as d:
+        run_distributed(_train_parallel, tp * pp, kind, tp, pp, 2, micro, losses, d, fuse, not fuse)
+        _check_merged(d, state, 1e-3)
+
+
 def _roundtrip(rank, world, kind, tmpdir):
     cls = getattr(ob, MODEL[kind])
     model = cls.from_pretrained_with_parallel(os.path.join(tmpdir, "split"), tensor_parallel_size=2)
@@ -193,6 +205,52 @@ def test_split_checkpoint_roundtrip(kind):
         run_distributed(_roundtrip, 2, kind, d)
         with pytest.raises(AssertionError):  # wrong layout must be refused, not silently mis-loaded
             run_distributed(_bad_layout, 4, kind, d)
+
+
+def _inference_matrix(rank, world, kind, tp, pp, fuse, tmpdir):
+    """The reference's ``*_inference`` / ``*_inference_with_fusion`` / ``*_deparallelization`` scripts in one flow:
+    merged checkpoint -> parallel model -> logits and beam search equal one process's -> split files -> reloaded in
+    the same layout -> merged again -> one process reproduces the logits."""
+    cls = getattr(ob, MODEL[kind])
+    ref = torch.load(os.path.join(tmpdir, "ref.pt"), weights_only=True)
+    b = batch(seed=11, vocab=104 if kind == "gptj" else 101)
+
+    def check(model):
+        model.eval()
+        with torch.no_grad():
+            out = model(input_ids=b["input_ids"])
+            logits = torch.cat([o.logits for o in out]) if pp > 1 else out.logits     # one output per micro-batch
+        assert torch.allclose(logits, ref["logits"], atol=3e-4), float((logits - ref["logits"]).abs().max())
+        gen = model.generate(b["input_ids"][:, :4], max_length=9, num_beams=2, eos_token_id=None, pad_token_id=0)
+        assert torch.equal(gen, ref["gen"])
+
+    model = cls.from_pretrained_with_parallel(os.path.join(tmpdir, "hf"), tensor_parallel_size=tp,
+                                              pipeline_parallel_size=pp, micro_batch_size=2)
+    if fuse:
+        model.fuse()
+    check(model)
+    model.save_pretrained_with_parallel(os.path.join(tmpdir, "split"))
+    again = cls.from_pretrained_with_parallel(os.path.join(tmpdir, "split"), tensor_parallel_size=tp,
+                                              pipeline_parallel_size=pp, micro_batch_size=2)
+    check(again)
+    again.save_pretrained_with_parallel(os.path.join(tmpdir, "merged"), save_with_merging=True)
+
+
+@pytest.mark.parametrize("kind", ["gpt2", "gpt_neo", "gptj"])
+@pytest.mark.parametrize("tp,pp,fuse", [(2, 1, False), (1, 2, True), (2, 2, False), (2, 2, True)])
+def test_inference_and_deparallelization_matrix(kind, tp, pp, fuse):
+    with tempfile.TemporaryDirectory() as d:
+        model = build(kind).eval()
+        model.save_pretrained(os.path.join(d, "hf"))
+        b = batch(seed=11, vocab=104 if kind == "gptj" else 101)
+        with torch.no_grad():
+            logits = model(input_ids=b["input_ids"]).logits
+        gen = model.generate(b["input_ids"][:, :4], max_length=9, num_beams=2, eos_token_id=None, pad_token_id=0)
+        torch.save({"logits": logits, "gen": gen}, os.path.join(d, "ref.pt"))
+        run_distributed(_inference_matrix, tp * pp, kind, tp, pp, fuse, d)
+        single = getattr(ob, MODEL[kind]).from_pretrained(os.path.join(d, "merged")).eval()
+        with torch.no_grad():
+            assert torch.allclose(single(input_ids=b["input_ids"]).logits, logits, atol=3e-4)
 
 
 def _bad_layout(rank, world, kind, tmpdir):
@@ -238,10 +296,10 @@ def _train_zero_ddp(rank, world, kind, steps, tmpdir, accumulate):
         torch.save(state, os.path.join(tmpdir, "state.pt"))
 
 
-@pytest.mark.parametrize("accumulate", [False, True])
-def test_zero1_and_bucketed_ddp_match_single_process(accumulate):
+@pytest.mark.parametrize("kind,accumulate", [("gptj", False), ("gptj", True), ("gpt2", True), ("gpt_neo", False)])
+def test_zero1_and_bucketed_ddp_match_single_process(kind, accumulate):
     """2 data-parallel gloo ranks with ZeRO-1 + the bucketed DDP wrapper == one process on the whole batch."""
-    kind, steps, world = "gptj", 3, 2
+    steps, world = 3, 2
     torch.manual_seed(0)
     ref = build(kind).train()
     opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.01)
