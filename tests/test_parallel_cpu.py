@@ -793,6 +793,53 @@ def test_pipeline_with_bucketed_ddp_and_zero1_matches_single_process(kind):
             assert torch.allclose(got[k], v, atol=2e-4), (k, (got[k] - v).abs().max())
 
 
+def _train_wrapper_layout(rank, world, kind, tp, pp, steps, tmpdir, seq_par):
+    """Any tp x pp layout with data-parallel replicas over the remaining ranks: bucketed wrapper, ZeRO-1, clipping."""
+    from oslo_b200.optim import FusedAdamW
+    from oslo_b200.parallel.data_parallel import DistributedDataParallel
+    model = ob.parallelize(build(kind).train(), tensor_parallel_size=tp, pipeline_parallel_size=pp, micro_batch_size=1,
+                           sequence_parallel=seq_par)
+    mpu = model.mpu
+    opt = FusedAdamW(model.gpu_parameters(), lr=1e-2, weight_decay=0.01, max_grad_norm=0.5, model=model,
+                     shard_group=mpu.get_data_parallel_group(), model_parallel_group=mpu.get_model_parallel_group())
+    ddp = DistributedDataParallel(model, mpu, optimizer=opt, bucket_mb=0.01)
+    dp, dpr = mpu.get_data_parallel_world_size(), mpu.get_data_parallel_rank()
+    for s in range(steps):
+        b = batch(seed=3 + s, vocab=104 if kind == "gptj" else 101)
+        n = b["input_ids"].size(0) // dp
+        mine = {k: v[dpr * n:(dpr + 1) * n] for k, v in b.items()}
+        opt.zero_grad()
+        if pp > 1:
+            for out in ddp(**mine):
+                (out.loss / n).backward()
+        else:
+            ddp(**mine).loss.backward()
+        opt.step()
+    model.save_pretrained_with_parallel(os.path.join(tmpdir, "merged"), save_with_merging=True)
+
+
+@pytest.mark.parametrize("kind,tp,pp,world,seq_par", [("gptj", 2, 1, 4, False), ("gpt2", 2, 1, 4, True),
+                                                       ("gptj", 2, 2, 8, False), ("gpt2", 2, 2, 8, False)])
+def test_wrapper_zero1_and_clipping_under_tensor_and_pipeline_parallel_replicas(kind, tp, pp, world, seq_par):
+    """Tensor (and pipeline) parallel replicas x 2 data-parallel replicas with this package's wrapper, ZeRO-1 and
+    global-norm clipping: merged weights equal one process training on the whole batch with ``clip_grad_norm_``."""
+    steps = 2
+    torch.manual_seed(0)
+    ref = build(kind).train()
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.01)
+    for s in range(steps):
+        opt.zero_grad()
+        ref(**batch(seed=3 + s, vocab=104 if kind == "gptj" else 101)).loss.backward()
+        torch.nn.utils.clip_grad_norm_(ref.parameters(), 0.5)
+        opt.step()
+    with tempfile.TemporaryDirectory() as d:
+        run_distributed(_train_wrapper_layout, world, kind, tp, pp, steps, d, seq_par)
+        got = torch.load(os.path.join(d, "merged", "pytorch_model.bin"), weights_only=True)
+    for k, v in ref.state_dict().items():
+        if k in got:
+            assert torch.allclose(got[k], v, atol=3e-4), (k, float((got[k] - v).abs().max()))
+
+
 def test_pipeline_with_bucketed_ddp_when_the_model_is_called_directly():
     """PP2 x DP2 with two micro-batches per replica, driving ``model(...)`` and not the wrapper: the bucket reductions
     must still start during the LAST micro-batch's backward only (started during the first one, the later
