@@ -305,13 +305,26 @@ def run_train_config(args, spec, dims, world, rank, local, dev):
     dist.all_reduce(mem, op=dist.ReduceOp.MAX)
     par = "x".join(f"{k}{v}" for k, v in (("tp", tp), ("pp", pp), ("dp", dp)) if v > 1) or "single"
     from oslo_b200.config import get_config
+    # model FLOPs of a step (6 x matrix parameters x tokens + the attention products, no recomputation counted) against
+    # the measured GEMM throughput of this machine; never allowed to cost the measurement
+    try:
+        from oslo_b200.utils.metrics import load_measured_peaks, transformer_train_flops
+        flops = transformer_train_flops(12.0 * n_layer * n_embd ** 2 + float(vocab) * n_embd, tokens_step, n_layer, n_embd,
+                                        args.seq)
+        peaks = load_measured_peaks(os.path.join(ROOT, "MEASURED_PEAKS.json"))
+        per_gpu = flops / (ms_step / 1e3) / world / 1e12
+        util = {"model_tflops_per_gpu": round(per_gpu, 1),
+                "of_sustained_gemm_throughput": round(per_gpu / peaks["bf16_tflops_sustained"], 3),
+                "peaks": peaks["source"]}
+    except Exception as e:  # noqa: BLE001
+        util = {"error": f"{type(e).__name__}: {e}"[:120]}
     block = {
         "value": tokens_step / (ms_step / 1e3), "unit": "tokens/s", "ms_per_step": ms_step,
         "config": {"model": model_name, "global_batch": dp * seqs_per_rank, "seq_len": args.seq,
                    "parallelism": par + ("+zero1" if dp > 1 else ""), "micro_batch": micro, "grad_accum": accum,
                    "optimizer": "AdamW fp32 master (fused)", "activation_checkpointing": bool(args.checkpoint_activations),
                    "fused_tp_collectives": bool(get_config().fused_tp_comm) if tp > 1 else None,
-                   "pipeline": pipe,
+                   "pipeline": pipe, "utilisation": util,
                    "l2": "working set per step >> 126 MB L2, no explicit flush"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "device_error_word": int(err.item()),
         "peak_mem_gb": round(float(mem.item()), 1),
