@@ -1,0 +1,93 @@
+"""Static checks over the whole source tree (no GPU, nothing imported): every global name a function loads is
+defined in its module or is a builtin, and every kernel operator the Python side calls has a schema in the
+bindings. They cover the branches that only run on GPUs, which the CPU suite never executes."""
+import ast
+import builtins
+import dis
+import os
+import re
+import types
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TREES = ["oslo_b200", "examples", "tests", "baseline/reference_runner.py", "bench.py", "__graft_entry__.py", "setup.py"]
+
+
+def _files():
+    for t in TREES:
+        p = os.path.join(ROOT, t)
+        if p.endswith(".py"):
+            yield p
+            continue
+        for d, _, fs in os.walk(p):
+            if "__pycache__" in d:
+                continue
+            for f in fs:
+                if f.endswith(".py"):
+                    yield os.path.join(d, f)
+
+
+def _module_names(tree):
+    names = set()
+    for node in ast.walk(tree):
+        if isinstance(node, (ast.Import, ast.ImportFrom)):
+            names.update((a.asname or a.name).split(".")[0] for a in node.names)
+        elif isinstance(node, (ast.FunctionDef, ast.AsyncFunctionDef, ast.ClassDef)):
+            names.add(node.name)
+        elif isinstance(node, ast.Name) and isinstance(node.ctx, (ast.Store, ast.Del)):
+            names.add(node.id)
+        elif isinstance(node, ast.Global):
+            names.update(node.names)
+        elif isinstance(node, ast.ExceptHandler) and node.name:
+            names.add(node.name)
+    return names
+
+
+def _code_objects(co):
+    yield co
+    for c in co.co_consts:
+        if isinstance(c, types.CodeType):
+            yield from _code_objects(c)
+
+
+_IMPLICIT = set(dir(builtins)) | {"__file__", "__name__", "__doc__", "__spec__", "__path__", "__class__",
+                                  "__annotations__", "__qualname__", "__module__"}
+
+
+def _undefined(src: str, path: str):
+    tree = ast.parse(src)
+    if any(isinstance(n, ast.ImportFrom) and any(a.name == "*" for a in n.names) for n in ast.walk(tree)):
+        return []                                      # names of a star import cannot be listed without importing
+    known = _module_names(tree) | _IMPLICIT
+    bad = []
+    for co in _code_objects(compile(src, path, "exec")):
+        for ins in dis.get_instructions(co):
+            if ins.opname in ("LOAD_GLOBAL", "LOAD_NAME") and ins.argval not in known:
+                line = ins.positions.lineno if ins.positions else "?"
+                bad.append(f"{path}:{line}: {ins.argval!r} in {co.co_name}")
+    return bad
+
+
+def test_no_function_loads_an_undefined_global_name():
+    probe = "import os\n\ndef f(x):\n    if x:\n        return os.getcwd()\n    return missing_name(x)\n"
+    assert _undefined(probe, "probe.py") == ["probe.py:6: 'missing_name' in f"]       # the check sees untaken branches
+    bad = []
+    for path in _files():
+        bad += _undefined(open(path).read(), os.path.relpath(path, ROOT))
+    assert not bad, "\n".join(bad)
+
+
+def test_every_operator_called_from_python_has_a_schema():
+    bindings = open(os.path.join(ROOT, "oslo_b200", "csrc", "bindings.cpp")).read()
+    schemas = set(re.findall(r'm\.def\(\s*"([A-Za-z0-9_]+)\s*\(', bindings))
+    impls = set(re.findall(r'm\.impl\(\s*"([A-Za-z0-9_]+)"', bindings))
+    assert impls <= schemas and len(schemas) > 30
+    call = re.compile(r'(?:_ext\(\)|load_ext\([^)]*\)|\bext|torch\.ops\.oslo_b200|get_custom_kernels\(\))\.([A-Za-z_][A-Za-z0-9_]*)')
+    missing = []
+    for path in _files():
+        if path.endswith("test_static.py"):
+            continue
+        for i, line in enumerate(open(path), 1):
+            for m in call.finditer(line):
+                if m.group(1) not in schemas:
+                    missing.append(f"{os.path.relpath(path, ROOT)}:{i}: {m.group(1)}")
+    assert not missing, "\n".join(missing)
