@@ -91,3 +91,42 @@ def test_every_operator_called_from_python_has_a_schema():
                 if m.group(1) not in schemas:
                     missing.append(f"{os.path.relpath(path, ROOT)}:{i}: {m.group(1)}")
     assert not missing, "\n".join(missing)
+
+
+def _schemas():
+    """``{operator: (required positional count, total count, argument names)}`` from the ``m.def`` lines."""
+    bindings = open(os.path.join(ROOT, "oslo_b200", "csrc", "bindings.cpp")).read()
+    out = {}
+    for name, args in re.findall(r'm\.def\(\s*"([A-Za-z0-9_]+)\s*\((.*?)\)\s*->', bindings):
+        params = [a.strip() for a in args.split(",") if a.strip()]
+        names = [re.sub(r"=.*", "", a).split()[-1] for a in params]
+        required = sum(1 for a in params if "=" not in a)
+        out[name] = (required, len(params), names)
+    return out
+
+
+def test_operator_calls_pass_as_many_arguments_as_the_schema_takes():
+    """Every ``<extension>.<operator>(...)`` call in the tree against the operator's schema: argument count within
+    [required, total], keyword names known. (Calls that splat ``*args`` are skipped.)"""
+    schemas = _schemas()
+    assert schemas["gemm_comm"][1] > 20 and schemas["flash_fwd"][0] == schemas["flash_fwd"][1] - 1
+    receiver = re.compile(r"(^_ext\(\)$|load_ext\(.*\)$|^ext$|^torch\.ops\.oslo_b200$|get_custom_kernels\(\)$)")
+    bad, seen = [], 0
+    for path in _files():
+        tree = ast.parse(open(path).read())
+        for node in ast.walk(tree):
+            if not (isinstance(node, ast.Call) and isinstance(node.func, ast.Attribute) and node.func.attr in schemas):
+                continue
+            if not receiver.search(ast.unparse(node.func.value)):
+                continue
+            if any(isinstance(a, ast.Starred) for a in node.args) or any(k.arg is None for k in node.keywords):
+                continue
+            seen += 1
+            required, total, names = schemas[node.func.attr]
+            n = len(node.args) + len(node.keywords)
+            unknown = [k.arg for k in node.keywords if k.arg not in names]
+            if not (required <= n <= total) or unknown:
+                bad.append(f"{os.path.relpath(path, ROOT)}:{node.lineno}: {node.func.attr} takes {required}..{total} "
+                           f"arguments, called with {n}" + (f", unknown keywords {unknown}" if unknown else ""))
+    assert seen > 40, seen
+    assert not bad, "\n".join(bad)
