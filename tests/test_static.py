@@ -130,3 +130,48 @@ def test_operator_calls_pass_as_many_arguments_as_the_schema_takes():
                            f"arguments, called with {n}" + (f", unknown keywords {unknown}" if unknown else ""))
     assert seen > 40, seen
     assert not bad, "\n".join(bad)
+
+
+def _signatures(path):
+    """``{function: (min positional, max positional or None, keyword names, takes **kwargs)}`` of a module's top level."""
+    out = {}
+    for node in ast.parse(open(path).read()).body:
+        if isinstance(node, ast.FunctionDef):
+            a = node.args
+            pos = [x.arg for x in a.posonlyargs + a.args]
+            required = len(pos) - len(a.defaults)
+            kwonly_required = [x.arg for x, d in zip(a.kwonlyargs, a.kw_defaults) if d is None]
+            out[node.name] = (required, None if a.vararg else len(pos), set(pos) | {x.arg for x in a.kwonlyargs},
+                              a.kwarg is not None, kwonly_required)
+    return out
+
+
+def test_calls_into_the_gpu_only_wrapper_module_match_its_signatures():
+    """``ops/cuda_ops.py`` only runs on GPUs, and so do most of its call sites: check every ``cuda_ops.f(...)`` call in
+    the tree against ``f``'s signature."""
+    sigs = _signatures(os.path.join(ROOT, "oslo_b200", "ops", "cuda_ops.py"))
+    bad, seen = [], 0
+    for path in _files():
+        for node in ast.walk(ast.parse(open(path).read())):
+            if not (isinstance(node, ast.Call) and isinstance(node.func, ast.Attribute) and node.func.attr in sigs
+                    and isinstance(node.func.value, ast.Name) and node.func.value.id in ("cuda_ops", "co")):
+                continue
+            if any(isinstance(a, ast.Starred) for a in node.args) or any(k.arg is None for k in node.keywords):
+                continue
+            seen += 1
+            required, most, names, var_kw, kwonly_required = sigs[node.func.attr]
+            given_kw = {k.arg for k in node.keywords}
+            n_pos = len(node.args)
+            problems = []
+            if most is not None and n_pos > most:
+                problems.append(f"{n_pos} positional arguments, at most {most}")
+            if not var_kw and given_kw - names:
+                problems.append(f"unknown keywords {sorted(given_kw - names)}")
+            if n_pos + len(given_kw) < required:
+                problems.append(f"{n_pos + len(given_kw)} arguments, at least {required}")
+            if [k for k in kwonly_required if k not in given_kw]:
+                problems.append("missing keyword-only arguments")
+            if problems:
+                bad.append(f"{os.path.relpath(path, ROOT)}:{node.lineno}: cuda_ops.{node.func.attr}: " + "; ".join(problems))
+    assert seen > 40, seen
+    assert not bad, "\n".join(bad)
