@@ -175,3 +175,33 @@ def test_calls_into_the_gpu_only_wrapper_module_match_its_signatures():
                 bad.append(f"{os.path.relpath(path, ROOT)}:{node.lineno}: cuda_ops.{node.func.attr}: " + "; ".join(problems))
     assert seen > 40, seen
     assert not bad, "\n".join(bad)
+
+
+def test_calls_of_the_symmetric_memory_methods_match_their_signatures():
+    """The GPU-only methods of ``FusedTP`` / ``SymmetricFlat`` / ``SymmetricWorkspace`` (unique names) by signature."""
+    wanted = {"gemm_all_reduce", "gemm_reduce_scatter", "all_gather_gemm", "reduce_scatter_", "all_gather_", "all_reduce_"}
+    sigs = {}
+    for rel in ("oslo_b200/parallel/fused_tp.py", "oslo_b200/parallel/symmetric.py"):
+        for node in ast.walk(ast.parse(open(os.path.join(ROOT, rel)).read())):
+            if isinstance(node, ast.ClassDef):
+                for f in node.body:
+                    if isinstance(f, ast.FunctionDef) and f.name in wanted:
+                        pos = [x.arg for x in f.args.args][1:]                      # without self
+                        sigs[f.name] = (len(pos) - len(f.args.defaults), len(pos), set(pos) | {x.arg for x in f.args.kwonlyargs})
+    assert set(sigs) == wanted, sorted(wanted - set(sigs))
+    bad, seen = [], 0
+    for path in _files():
+        for node in ast.walk(ast.parse(open(path).read())):
+            if not (isinstance(node, ast.Call) and isinstance(node.func, ast.Attribute) and node.func.attr in sigs):
+                continue
+            if any(isinstance(a, ast.Starred) for a in node.args) or any(k.arg is None for k in node.keywords):
+                continue
+            seen += 1
+            required, most, names = sigs[node.func.attr]
+            kw = {k.arg for k in node.keywords}
+            n = len(node.args)
+            if n > most or kw - names or n + len(kw) < required:
+                bad.append(f"{os.path.relpath(path, ROOT)}:{node.lineno}: {node.func.attr} takes {required}..{most}, "
+                           f"got {n} positional and keywords {sorted(kw)}")
+    assert seen > 15, seen
+    assert not bad, "\n".join(bad)
