@@ -205,3 +205,24 @@ def test_calls_of_the_symmetric_memory_methods_match_their_signatures():
                            f"got {n} positional and keywords {sorted(kw)}")
     assert seen > 15, seen
     assert not bad, "\n".join(bad)
+
+
+def test_configuration_switches_that_the_code_reads_exist():
+    """``get_config().<name>`` anywhere in the tree names a field of ``OsloConfig`` (a misspelt switch in a GPU-only
+    branch would only show on a GPU)."""
+    cfg_src = ast.parse(open(os.path.join(ROOT, "oslo_b200", "config.py")).read())
+    fields = set()
+    for node in ast.walk(cfg_src):
+        if isinstance(node, ast.ClassDef) and node.name == "OsloConfig":
+            fields = {s.target.id for s in node.body if isinstance(s, ast.AnnAssign)} | \
+                     {f.name for f in node.body if isinstance(f, ast.FunctionDef)}
+    assert "fused_tp_comm" in fields and "pp_reserved_sms" in fields
+    bad, seen = [], 0
+    for path in _files():
+        for node in ast.walk(ast.parse(open(path).read())):
+            if (isinstance(node, ast.Attribute) and isinstance(node.value, ast.Call)
+                    and isinstance(node.value.func, ast.Name) and node.value.func.id == "get_config"):
+                seen += 1
+                if node.attr not in fields:
+                    bad.append(f"{os.path.relpath(path, ROOT)}:{node.lineno}: get_config().{node.attr}")
+    assert seen > 10 and not bad, "\n".join(bad)
