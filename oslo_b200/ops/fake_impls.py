@@ -109,3 +109,36 @@ def register() -> None:
     @reg("oslo_b200::gemm_ce_grad")
     def _(a, b, b_mn, bias, labels, vocab_start, lse, scale):
         return a.new_empty((a.size(0), b.size(1) if b_mn else b.size(0)))
+
+    @reg("oslo_b200::error_word")
+    def _(like):
+        return like.new_empty((1,), dtype=torch.int32)
+
+    @reg("oslo_b200::bias_dropout_residual")
+    def _(x, bias, residual, p, seed, mode):
+        return torch.empty_like(x)
+
+    @reg("oslo_b200::rotary_")
+    def _(x, positions, heads, head_dim, rotary_dim, base, inverse):
+        return x
+
+    @reg("oslo_b200::ce_grad_")
+    def _(logits, labels, vocab_start, lse, scale):
+        return logits
+
+    @reg("oslo_b200::adam_step")
+    def _(p, g, m, v, p_lp, lr, beta1, beta2, eps, wd, step, grad_scale, inv_scale):
+        return None
+
+    @reg("oslo_b200::ngram_ban_")
+    def _(tokens, lprobs, n):
+        return lprobs
+
+    @reg("oslo_b200::rotary_append")
+    def _(q, k, v, kc, vc, lengths, write_index, rotary_dim, base):
+        return q.new_empty((kc.size(0), kc.size(1), kc.size(3)))
+
+    @reg("oslo_b200::wait_probe")
+    def _(flag, target, limit_ms):
+        return flag.new_empty((1,), dtype=torch.int64)
+

@@ -1,0 +1,98 @@
+"""The GPU-only Python paths on a machine without a GPU: fused models run forward on FAKE CUDA tensors
+(``FakeTensorMode``: shapes, dtypes, strides and devices flow, no memory, no kernels). Every ``x.is_cuda`` branch of
+the models, of ``ops/cuda_ops.py`` and of the autograd functions' forward halves executes, with the operators'
+shape implementations (``ops/fake_impls.py``) standing in for the kernels. The autograd ENGINE needs a CUDA runtime (it
+asks for the device's context), so the backward halves are run by walking the graph and calling every custom
+function's ``backward`` with gradients of the recorded shapes."""
+import pytest
+import torch
+from torch._subclasses.fake_tensor import FakeTensorMode
+
+import oslo_b200 as ob
+from oslo_b200 import ops
+
+
+def _model(kind):
+    if kind == "gpt2":
+        return ob.GPT2LMHeadModel, ob.GPT2Config(vocab_size=1024, n_positions=256, n_embd=512, n_layer=2, n_head=8,
+                                                  attn_pdrop=0.0)       # with attention dropout the scores are materialised
+    if kind == "gpt_neo":
+        return ob.GPTNeoForCausalLM, ob.GPTNeoConfig(vocab_size=1024, max_position_embeddings=256, hidden_size=512,
+                                                     num_layers=2, num_heads=8, window_size=64,
+                                                     attention_types=[[["global", "local"], 1]])
+    return ob.GPTJForCausalLM, ob.GPTJConfig(vocab_size=1024, n_positions=256, n_embd=512, n_layer=2, n_head=4, rotary_dim=32)
+
+
+def run_custom_backwards(root):
+    """Call ``backward`` of every ``torch.autograd.Function`` node reachable from ``root`` once, with empty gradients
+    of the shapes / dtypes / devices the node recorded for its outputs. Returns the names of the functions run."""
+    seen, keep, stack, ran = set(), [], [root], []
+    while stack:
+        node = stack.pop()
+        if node is None or id(node) in seen:
+            continue
+        seen.add(id(node))
+        keep.append(node)                  # a live reference: ids of collected wrapper objects would be reused
+        stack += [fn for fn, _ in node.next_functions]
+        cls = getattr(node, "_forward_cls", None)
+        if cls is None:
+            continue
+        grads = [torch.empty(m.shape, dtype=m.dtype, device=m.device) for m in node._input_metadata]
+        out = cls.backward(node, *grads)
+        out = out if isinstance(out, tuple) else (out,)
+        assert len(out) >= len(node.next_functions), cls.__name__
+        for g in out:
+            assert g is None or (torch.is_tensor(g) and g.is_cuda), cls.__name__
+        ran.append(cls.__name__)
+    return ran
+
+
+@pytest.fixture
+def kernels(monkeypatch):
+    if ops.load_ext() is None:
+        pytest.skip("extension not built")
+    monkeypatch.setattr(ops, "kernels_available", lambda: True)
+
+
+@pytest.mark.parametrize("kind", ["gpt2", "gpt_neo", "gptj"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_fused_forward_paths_run_on_fake_cuda_tensors(kernels, kind, dtype):
+    cls, cfg = _model(kind)
+    with FakeTensorMode():
+        with torch.device("cuda"):
+            model = cls._from_config(cfg, torch_dtype=dtype)
+        model.fuse().train()
+        ids = torch.randint(0, 1024, (2, 256), device="cuda")
+        out = model(input_ids=ids, labels=ids, output_logits=False)                 # LM head fused with the loss
+        assert out.loss.shape == () and out.loss.is_cuda and out.logits is None
+        ran = run_custom_backwards(out.loss.grad_fn)                                 # every backward half of the step
+        assert ran.count("_Flash") == 2 and ran.count("_LayerNorm") >= 3 and "_LinearCrossEntropy" in ran, ran
+        out = model(input_ids=ids, labels=ids)                                       # logits materialised
+        assert out.logits.shape == (2, 256, 1024) and out.logits.dtype == dtype
+        mask = torch.ones(2, 256, dtype=torch.long, device="cuda")
+        out = model(input_ids=ids, attention_mask=mask, output_attentions=True, output_hidden_states=True)
+        assert len(out.hidden_states) == 3 and out.attentions[0].shape[-2:] == (256, 256)
+        model.gradient_checkpointing_enable()
+        assert model(input_ids=ids, labels=ids, output_logits=False).loss.shape == ()
+        model.eval()
+        with torch.no_grad():
+            out = model(input_ids=ids[:, :16], use_cache=True)                       # prefill, then one decode step
+            nxt = model(input_ids=ids[:, 16:17], past_key_values=out.past_key_values, use_cache=True)
+        assert nxt.logits.shape == (2, 1, 1024)
+
+
+def test_optimizer_and_elementwise_wrappers_on_fake_cuda_tensors(kernels):
+    from oslo_b200.optim import FusedAdamW
+    with FakeTensorMode():
+        with torch.device("cuda"):
+            lin = torch.nn.Linear(64, 64, dtype=torch.bfloat16)
+        opt = FusedAdamW(lin.parameters(), lr=1e-3, max_grad_norm=1.0)
+        assert opt.buf.flat_g.is_cuda and opt.master.dtype == torch.float32
+        assert opt.step() is True                                                    # norm kernel + Adam kernel
+        x = torch.empty(4, 8, 64, dtype=torch.bfloat16, device="cuda")
+        assert ops.bias_gelu(x, lin.bias).shape == x.shape
+        assert ops.bias_dropout_residual(x, lin.bias, x, 0.1, True).shape == x.shape
+        assert ops.layer_norm(x, lin.bias, lin.bias, 1e-5).shape == x.shape
+        lp = torch.empty(2, 1024, dtype=torch.float32, device="cuda")
+        toks = torch.zeros(2, 9, dtype=torch.long, device="cuda")
+        assert ops.ban_repeated_ngrams(toks, lp, 3).shape == lp.shape
