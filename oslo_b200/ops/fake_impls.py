@@ -142,3 +142,34 @@ def register() -> None:
     def _(flag, target, limit_ms):
         return flag.new_empty((1,), dtype=torch.int64)
 
+    # collectives over symmetric memory: the data moves between GPUs inside the kernels; for tracing only the local
+    # outputs matter (in-place operators return nothing)
+    @reg("oslo_b200::gemm_comm")
+    def _(a, b, a_mn, b_mn, bias, aux, aux_out, out, flags, alpha, M, N, K, peer_bufs_dev, own_buf, mc_base, data_off,
+          flag_off, flag_bytes, rank, world, epoch, done_base, mode, use_multimem, trace):
+        return 0
+
+    @reg("oslo_b200::vocab_embed")
+    def _(ids, weight, lo, hi, peer_ptrs_dev, mc_ptr, signal_ptrs_dev, counters, half_bytes, rank, world, use_multimem):
+        return weight.new_empty((ids.numel(), weight.size(1)))
+
+    @reg("oslo_b200::allreduce_oneshot")
+    def _(x, peer_ptrs_dev, mc_ptr, signal_ptrs_dev, counters, stage_off, half_bytes, rank, world, use_multimem):
+        return None
+
+    @reg("oslo_b200::allreduce_symm")
+    def _(peer_ptrs_dev, mc_ptr, signal_ptrs_dev, out, numel, rank, world, use_multimem):
+        return None
+
+    @reg("oslo_b200::ce_combine")
+    def _(mx, se, tg, peer_ptrs_dev, signal_ptrs_dev, counters, cap, rank, world):
+        return None
+
+    @reg("oslo_b200::dp_reduce_scatter")
+    def _(like, peer_ptrs_dev, mc_ptr, signal_ptrs_dev, lo, hi, shard, rank, world, use_multimem):
+        return None
+
+    @reg("oslo_b200::dp_all_gather")
+    def _(like, peer_ptrs_dev, mc_ptr, signal_ptrs_dev, lo, hi, shard, rank, world, use_multimem):
+        return None
+

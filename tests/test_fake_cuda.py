@@ -96,3 +96,71 @@ def test_optimizer_and_elementwise_wrappers_on_fake_cuda_tensors(kernels):
         lp = torch.empty(2, 1024, dtype=torch.float32, device="cuda")
         toks = torch.zeros(2, 9, dtype=torch.long, device="cuda")
         assert ops.ban_repeated_ngrams(toks, lp, 3).shape == lp.shape
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Tensor-parallel fused paths: rank 0 of a two-rank "fake" process group (collectives return without moving data),
+# symmetric memory replaced by fake CUDA buffers. The fused GEMM + collective autograd functions, the fused
+# vocabulary lookup and the loss combine then run their Python halves - forward and backward - without a GPU.
+
+def _fake_tp_rank(rank, world, kind, seq_par, tp=2):
+    import os
+    from collections import Counter
+    import torch.distributed as dist
+    from torch.testing._internal.distributed.fake_pg import FakeStore
+    from oslo_b200.parallel import fused_tp, symmetric
+    os.environ["OSLO_B200_BACKEND"] = "fake"
+    ops.load_ext()
+    ops.kernels_available = lambda: True
+    torch.cuda.is_current_stream_capturing = lambda: False
+    dist.init_process_group(backend="fake", rank=0, world_size=tp, store=FakeStore())
+
+    class FakeWorkspace:
+        def __init__(self, group, nbytes, device=None):
+            self.group, self.world, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
+            self.numel = (int(nbytes) + 255) // 256 * 128
+            self.buf = torch.empty(self.numel, dtype=torch.bfloat16, device="cuda")
+            self.peer_ptrs_dev = self.signal_ptrs_dev = self.mc_ptr = 0
+            self.has_multicast = False
+            self.oneshot_half = symmetric.ONESHOT_HALF
+            self.oneshot_off = self.numel * 2 - 2 * self.oneshot_half
+            self.embed_half = (self.oneshot_off // 2) // 256 * 256
+            self.embed_counters = torch.empty(64, dtype=torch.int32, device="cuda")
+            self.oneshot_counters = torch.empty(64, dtype=torch.int32, device="cuda")
+
+    class FakeCombine(symmetric.CeCombine):
+        def __init__(self, group, device):
+            self.group, self.world, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
+            self.peer_ptrs_dev = self.signal_ptrs_dev = 0
+            self.counters = torch.empty(8, dtype=torch.int32, device="cuda")
+
+    fused_tp.SymmetricWorkspace = symmetric.SymmetricWorkspace = FakeWorkspace
+    symmetric.CeCombine = FakeCombine
+    cls, cfg = _model(kind)
+    cfg.torch_dtype = torch.bfloat16
+    model = ob.parallelize(cls(cfg).to(torch.bfloat16), tensor_parallel_size=tp, sequence_parallel=seq_par)
+    model.fuse().train()
+    model.mpu.backend, model.mpu.device = "nccl", torch.device("cuda")        # what the fused paths ask for
+    with FakeTensorMode():
+        fake = {}
+        for k, v in list(model.named_parameters()) + list(model.named_buffers()):
+            t = torch.empty(v.shape, dtype=v.dtype, device="cuda")
+            fake[k] = torch.nn.Parameter(t, requires_grad=v.requires_grad) if isinstance(v, torch.nn.Parameter) else t
+        ids = torch.randint(0, 1024, (2, 256), device="cuda")
+        out = torch.func.functional_call(model, fake, (), dict(input_ids=ids, labels=ids, output_logits=False))
+        assert out.loss.shape == () and out.loss.is_cuda
+        ran = Counter(run_custom_backwards(out.loss.grad_fn))
+    fused = [n for n in ran if "Fused" in n or "TPBlock" in n or "VocabEmbed" in n]
+    assert fused, ran                                                          # GEMM + collective functions took part
+    assert ran["_LinearCrossEntropy"] == 1 and ran["_LayerNorm"] >= 3, ran
+    if kind == "gptj" and not seq_par and tp == 2:
+        assert ran["_TPBlockInput"] == 2 and ran["_RowParallelFused"] == 2 and ran["_VocabEmbed"] == 1, ran
+
+
+@pytest.mark.parametrize("kind,seq_par,tp", [("gptj", False, 2), ("gptj", True, 2), ("gpt2", False, 2), ("gpt_neo", True, 2),
+                                             ("gptj", False, 4), ("gpt2", False, 8), ("gpt_neo", False, 8)])
+def test_tensor_parallel_fused_paths_on_a_fake_process_group(kind, seq_par, tp):
+    from tests.dist_utils import run_distributed
+    if ops.load_ext() is None:
+        pytest.skip("extension not built")
+    run_distributed(_fake_tp_rank, 1, kind, seq_par, tp)
