@@ -12,15 +12,15 @@ import oslo_b200 as ob
 from oslo_b200 import ops
 
 
-def _model(kind):
+def _model(kind, vocab=1024):
     if kind == "gpt2":
-        return ob.GPT2LMHeadModel, ob.GPT2Config(vocab_size=1024, n_positions=256, n_embd=512, n_layer=2, n_head=8,
+        return ob.GPT2LMHeadModel, ob.GPT2Config(vocab_size=vocab, n_positions=256, n_embd=512, n_layer=2, n_head=8,
                                                   attn_pdrop=0.0)       # with attention dropout the scores are materialised
     if kind == "gpt_neo":
-        return ob.GPTNeoForCausalLM, ob.GPTNeoConfig(vocab_size=1024, max_position_embeddings=256, hidden_size=512,
+        return ob.GPTNeoForCausalLM, ob.GPTNeoConfig(vocab_size=vocab, max_position_embeddings=256, hidden_size=512,
                                                      num_layers=2, num_heads=8, window_size=64,
                                                      attention_types=[[["global", "local"], 1]])
-    return ob.GPTJForCausalLM, ob.GPTJConfig(vocab_size=1024, n_positions=256, n_embd=512, n_layer=2, n_head=4, rotary_dim=32)
+    return ob.GPTJForCausalLM, ob.GPTJConfig(vocab_size=vocab, n_positions=256, n_embd=512, n_layer=2, n_head=8, rotary_dim=32)
 
 
 def run_custom_backwards(root):
@@ -103,7 +103,7 @@ def test_optimizer_and_elementwise_wrappers_on_fake_cuda_tensors(kernels):
 # symmetric memory replaced by fake CUDA buffers. The fused GEMM + collective autograd functions, the fused
 # vocabulary lookup and the loss combine then run their Python halves - forward and backward - without a GPU.
 
-def _fake_tp_rank(rank, world, kind, seq_par, tp=2):
+def _fake_tp_rank(rank, world, kind, seq_par, tp=2, vocab=1024, as_rank=0):
     import os
     from collections import Counter
     import torch.distributed as dist
@@ -113,7 +113,7 @@ def _fake_tp_rank(rank, world, kind, seq_par, tp=2):
     ops.load_ext()
     ops.kernels_available = lambda: True
     torch.cuda.is_current_stream_capturing = lambda: False
-    dist.init_process_group(backend="fake", rank=0, world_size=tp, store=FakeStore())
+    dist.init_process_group(backend="fake", rank=as_rank, world_size=tp, store=FakeStore())
 
     class FakeWorkspace:
         def __init__(self, group, nbytes, device=None):
@@ -136,7 +136,7 @@ def _fake_tp_rank(rank, world, kind, seq_par, tp=2):
 
     fused_tp.SymmetricWorkspace = symmetric.SymmetricWorkspace = FakeWorkspace
     symmetric.CeCombine = FakeCombine
-    cls, cfg = _model(kind)
+    cls, cfg = _model(kind, vocab)
     cfg.torch_dtype = torch.bfloat16
     model = ob.parallelize(cls(cfg).to(torch.bfloat16), tensor_parallel_size=tp, sequence_parallel=seq_par)
     model.fuse().train()
@@ -146,7 +146,7 @@ def _fake_tp_rank(rank, world, kind, seq_par, tp=2):
         for k, v in list(model.named_parameters()) + list(model.named_buffers()):
             t = torch.empty(v.shape, dtype=v.dtype, device="cuda")
             fake[k] = torch.nn.Parameter(t, requires_grad=v.requires_grad) if isinstance(v, torch.nn.Parameter) else t
-        ids = torch.randint(0, 1024, (2, 256), device="cuda")
+        ids = torch.randint(0, vocab, (2, 256), device="cuda")
         out = torch.func.functional_call(model, fake, (), dict(input_ids=ids, labels=ids, output_logits=False))
         assert out.loss.shape == () and out.loss.is_cuda
         ran = Counter(run_custom_backwards(out.loss.grad_fn))
@@ -164,3 +164,15 @@ def test_tensor_parallel_fused_paths_on_a_fake_process_group(kind, seq_par, tp):
     if ops.load_ext() is None:
         pytest.skip("extension not built")
     run_distributed(_fake_tp_rank, 1, kind, seq_par, tp)
+
+
+@pytest.mark.parametrize("kind,vocab,tp,as_rank", [("gptj", 50400, 8, 0), ("gpt_neo", 50257, 2, 0), ("gpt_neo", 50257, 2, 1)])
+def test_vocabulary_shards_with_unaligned_row_counts_on_fake_cuda(kind, vocab, tp, as_rank):
+    """GPT-J's vocabulary over 8 ranks (6300 rows each) and GPT-Neo's over 2 (25129 and 25128 rows): shards whose row
+    count is not a multiple of 8 take the logits + separate-kernel route of the loss and library products for the
+    gradient GEMMs; both ranks of the uneven split must choose the same collectives."""
+    from tests.dist_utils import run_distributed
+    if ops.load_ext() is None:
+        pytest.skip("extension not built")
+    run_distributed(_fake_tp_rank, 1, kind, False, tp, vocab, as_rank)
+
