@@ -79,6 +79,11 @@ def test_fused_forward_paths_run_on_fake_cuda_tensors(kernels, kind, dtype):
             out = model(input_ids=ids[:, :16], use_cache=True)                       # prefill, then one decode step
             nxt = model(input_ids=ids[:, 16:17], past_key_values=out.past_key_values, use_cache=True)
         assert nxt.logits.shape == (2, 1, 1024)
+        from oslo_b200.models.common import StaticKVCache
+        with torch.no_grad():                                                        # static cache: the decode kernels' wrappers
+            out = model(input_ids=ids[:, :16], past_key_values=StaticKVCache(64), use_cache=True, last_token_logits=True)
+            nxt = model(input_ids=ids[:, 16:17], past_key_values=out.past_key_values, use_cache=True)
+        assert isinstance(out.past_key_values, StaticKVCache) and nxt.logits.shape == (2, 1, 1024)
 
 
 def test_optimizer_and_elementwise_wrappers_on_fake_cuda_tensors(kernels):
