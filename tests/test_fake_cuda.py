@@ -120,13 +120,12 @@ def _fake_tp_rank(rank, world, kind, seq_par, tp=2, vocab=1024, as_rank=0):
     torch.cuda.is_current_stream_capturing = lambda: False
     dist.init_process_group(backend="fake", rank=as_rank, world_size=tp, store=FakeStore())
 
-    class FakeWorkspace:
+    class FakeWorkspace(symmetric.SymmetricWorkspace):
         def __init__(self, group, nbytes, device=None):
             self.group, self.world, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
             self.numel = (int(nbytes) + 255) // 256 * 128
             self.buf = torch.empty(self.numel, dtype=torch.bfloat16, device="cuda")
             self.peer_ptrs_dev = self.signal_ptrs_dev = self.mc_ptr = 0
-            self.has_multicast = False
             self.oneshot_half = symmetric.ONESHOT_HALF
             self.oneshot_off = self.numel * 2 - 2 * self.oneshot_half
             self.embed_half = (self.oneshot_off // 2) // 256 * 256
@@ -155,6 +154,14 @@ def _fake_tp_rank(rank, world, kind, seq_par, tp=2, vocab=1024, as_rank=0):
         out = torch.func.functional_call(model, fake, (), dict(input_ids=ids, labels=ids, output_logits=False))
         assert out.loss.shape == () and out.loss.is_cuda
         ran = Counter(run_custom_backwards(out.loss.grad_fn))
+        from oslo_b200.models.common import StaticKVCache
+        model.eval()
+        with torch.no_grad():                      # decode: few-row GEMMs and the one-kernel all-reduce
+            pre = torch.func.functional_call(model, fake, (), dict(input_ids=ids[:, :16], past_key_values=StaticKVCache(64),
+                                                                   use_cache=True, last_token_logits=True))
+            nxt = torch.func.functional_call(model, fake, (), dict(input_ids=ids[:, 16:17], use_cache=True,
+                                                                   past_key_values=pre.past_key_values))
+        assert nxt.logits.shape == (2, 1, vocab), nxt.logits.shape
     fused = [n for n in ran if "Fused" in n or "TPBlock" in n or "VocabEmbed" in n]
     assert fused, ran                                                          # GEMM + collective functions took part
     assert ran["_LinearCrossEntropy"] == 1 and ran["_LayerNorm"] >= 3, ran
