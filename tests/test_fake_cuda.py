@@ -188,3 +188,91 @@ def test_vocabulary_shards_with_unaligned_row_counts_on_fake_cuda(kind, vocab, t
         pytest.skip("extension not built")
     run_distributed(_fake_tp_rank, 1, kind, False, tp, vocab, as_rank)
 
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Data-parallel wrapper on symmetric buffers (ZeRO-1): bucket launches on the side stream, the parameter all-gather
+# after the optimizer step and the per-unit waits of the next forward, with stand-ins for CUDA streams / events.
+
+def _fake_dp_rank(rank, world):
+    import contextlib
+    import os
+    import torch.distributed as dist
+    from torch.testing._internal.distributed.fake_pg import FakeStore
+    from oslo_b200.optim import FusedAdamW
+    from oslo_b200.parallel import symmetric
+    from oslo_b200.parallel.data_parallel import DistributedDataParallel
+    from oslo_b200.parallel.mpu import MPU
+    os.environ["OSLO_B200_BACKEND"] = "fake"
+    ops.load_ext()
+    ops.kernels_available = lambda: True
+    dist.init_process_group(backend="fake", rank=0, world_size=2, store=FakeStore())
+    log = []
+
+    class Stream:
+        def wait_stream(self, other):
+            log.append("wait_stream")
+
+        def wait_event(self, ev):
+            log.append(("wait_event", ev.tag))
+
+    class Event:
+        count = 0
+
+        def __init__(self, *a, **k):
+            Event.count += 1
+            self.tag = Event.count
+
+        def record(self, stream=None):
+            log.append(("record", self.tag))
+
+    cur = Stream()
+    torch.cuda.Stream, torch.cuda.Event = Stream, Event
+    torch.cuda.current_stream = lambda *a: cur
+    torch.cuda.stream = lambda s: contextlib.nullcontext()
+
+    class FakeFlat(symmetric.SymmetricFlat):
+        def __init__(self, group, numel, dtype, device):
+            self.group, self.world, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
+            self.tensor = torch.empty(int(numel), dtype=dtype, device=device)
+            self.peer_ptrs_dev = self.signal_ptrs_dev = self.mc_ptr = 0
+            self.shard = -(-int(numel) // (8 * self.world)) * 8
+
+    symmetric.SymmetricFlat = FakeFlat
+    symmetric.symmetric_flat_usable = lambda group, dtype, device: True
+    mpu = MPU(1, 1)                                    # two data-parallel replicas
+    cls, cfg = _model("gptj")
+    with FakeTensorMode():
+        with torch.device("cuda"):
+            model = cls._from_config(cfg, torch_dtype=torch.bfloat16)
+        model.fuse().train()
+        opt = FusedAdamW(model.parameters(), lr=1e-4, max_grad_norm=1.0, shard_group=mpu.get_data_parallel_group())
+        ddp = DistributedDataParallel(model, mpu, optimizer=opt, bucket_mb=1.0)
+        n = len(ddp.buckets)
+        assert ddp._symm and ddp._zero and n > 3 and len(ddp._param_events) == n
+        ids = torch.randint(0, 1024, (2, 256), device="cuda")
+        for _ in range(2):
+            opt.zero_grad()
+            for i in range(2):
+                with (ddp.no_sync() if i == 0 else contextlib.nullcontext()):
+                    out = ddp(input_ids=ids, labels=ids, output_logits=False)
+                    assert not ddp._param_pending                  # every unit has waited for its parameter buckets
+                    run_custom_backwards(out.loss.grad_fn)
+                    before = log.count("wait_stream")
+                    for p in reversed(opt.buf.params):             # what autograd's post-accumulate hooks do
+                        ddp._hook(p)
+                    launched = log.count("wait_stream") - before
+                    assert launched == (0 if i == 0 else n), (i, launched)     # reductions in the last micro-batch only
+            assert opt.step() is True
+            assert sorted(ddp._param_pending) == list(range(n))     # all parameter buckets are in flight
+            records = [e for e in log if isinstance(e, tuple) and e[0] == "record"][-n:]
+            assert sorted(e[1] for e in records) == sorted(ev.tag for ev in ddp._param_events)
+        model.state_dict()                                          # a checkpoint waits for everything that is left
+        assert not ddp._param_pending
+
+
+def test_symmetric_data_parallel_bookkeeping_on_fake_cuda():
+    from tests.dist_utils import run_distributed
+    if ops.load_ext() is None:
+        pytest.skip("extension not built")
+    run_distributed(_fake_dp_rank, 1)
