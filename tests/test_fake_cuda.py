@@ -108,9 +108,10 @@ def test_optimizer_and_elementwise_wrappers_on_fake_cuda_tensors(kernels):
 # symmetric memory replaced by fake CUDA buffers. The fused GEMM + collective autograd functions, the fused
 # vocabulary lookup and the loss combine then run their Python halves - forward and backward - without a GPU.
 
-def _fake_tp_rank(rank, world, kind, seq_par, tp=2, vocab=1024, as_rank=0):
+def _fake_group(tp, as_rank=0):
+    """This process becomes rank ``as_rank`` of a ``tp``-rank fake process group whose symmetric memory is fake CUDA
+    buffers."""
     import os
-    from collections import Counter
     import torch.distributed as dist
     from torch.testing._internal.distributed.fake_pg import FakeStore
     from oslo_b200.parallel import fused_tp, symmetric
@@ -140,16 +141,26 @@ def _fake_tp_rank(rank, world, kind, seq_par, tp=2, vocab=1024, as_rank=0):
 
     fused_tp.SymmetricWorkspace = symmetric.SymmetricWorkspace = FakeWorkspace
     symmetric.CeCombine = FakeCombine
+
+
+def _fake_parameters(model):
+    fake = {}
+    for k, v in list(model.named_parameters()) + list(model.named_buffers()):
+        t = torch.empty(v.shape, dtype=v.dtype, device="cuda")
+        fake[k] = torch.nn.Parameter(t, requires_grad=v.requires_grad) if isinstance(v, torch.nn.Parameter) else t
+    return fake
+
+
+def _fake_tp_rank(rank, world, kind, seq_par, tp=2, vocab=1024, as_rank=0):
+    from collections import Counter
+    _fake_group(tp, as_rank)
     cls, cfg = _model(kind, vocab)
     cfg.torch_dtype = torch.bfloat16
     model = ob.parallelize(cls(cfg).to(torch.bfloat16), tensor_parallel_size=tp, sequence_parallel=seq_par)
     model.fuse().train()
     model.mpu.backend, model.mpu.device = "nccl", torch.device("cuda")        # what the fused paths ask for
     with FakeTensorMode():
-        fake = {}
-        for k, v in list(model.named_parameters()) + list(model.named_buffers()):
-            t = torch.empty(v.shape, dtype=v.dtype, device="cuda")
-            fake[k] = torch.nn.Parameter(t, requires_grad=v.requires_grad) if isinstance(v, torch.nn.Parameter) else t
+        fake = _fake_parameters(model)
         ids = torch.randint(0, vocab, (2, 256), device="cuda")
         out = torch.func.functional_call(model, fake, (), dict(input_ids=ids, labels=ids, output_logits=False))
         assert out.loss.shape == () and out.loss.is_cuda
@@ -276,3 +287,54 @@ def test_symmetric_data_parallel_bookkeeping_on_fake_cuda():
     if ops.load_ext() is None:
         pytest.skip("extension not built")
     run_distributed(_fake_dp_rank, 1)
+
+
+def _bench_shape_rank(rank, world, tp, micro):
+    """One GPT-J-6B-wide block + embeddings + head at the benchmark's per-step shapes on rank 0 of ``tp`` ranks."""
+    from collections import Counter
+    from oslo_b200.modeling_utils import no_weight_init
+    from oslo_b200.parallel import fused_tp, vocab_parallel
+    _fake_group(tp)
+    calls, routes = Counter(), []
+    real_call = fused_tp.FusedTP._call
+
+    def spy(self, a, b, a_mn, b_mn, bias, aux_out, out, flags, M, N, K, mode, aux=None):
+        calls[(mode, M, N, K)] += 1
+        return real_call(self, a, b, a_mn, b_mn, bias, aux_out, out, flags, M, N, K, mode, aux)
+
+    real_route = vocab_parallel._epilogue_ce_ok
+
+    def route(*a):
+        routes.append(real_route(*a))
+        return routes[-1]
+
+    fused_tp.FusedTP._call = spy
+    vocab_parallel._epilogue_ce_ok = route
+    cfg = ob.GPTJConfig(vocab_size=50400, n_positions=2048, n_embd=4096, n_layer=1, n_head=16, rotary_dim=64,
+                        torch_dtype=torch.bfloat16)
+    with no_weight_init():
+        model = ob.GPTJForCausalLM(cfg).to(torch.bfloat16)
+    model = ob.parallelize(model, tensor_parallel_size=tp)
+    model.fuse().train()
+    model.mpu.backend, model.mpu.device = "nccl", torch.device("cuda")
+    with FakeTensorMode():
+        ids = torch.randint(0, 50400, (micro, 2048), device="cuda")
+        out = torch.func.functional_call(model, _fake_parameters(model), (), dict(input_ids=ids, labels=ids, output_logits=False))
+        ran = Counter(run_custom_backwards(out.loss.grad_fn))
+    tokens = micro * 2048
+    # forward: attention projection + fc_out as ONE fused GEMM + all-reduce; backward: ONE for the four input gradients
+    assert calls == {(1, tokens, 4096, 4 * 4096 // tp): 2}, dict(calls)
+    assert ran["_TPBlockInput"] == 1 and ran["_RowParallelFused"] == 1 and ran["_Flash"] == 1, dict(ran)
+    # the loss: cross-entropy inside the LM-head GEMM where every vocabulary shard has a multiple of 8 rows
+    assert routes == [50400 // tp % 8 == 0], routes
+
+
+@pytest.mark.parametrize("tp,micro", [(2, 8), (4, 16), (8, 8)])
+def test_benchmark_shapes_take_the_fused_paths(tp, micro):
+    """The per-step shapes of ``bench.py`` (GPT-J-6B width, 8 x 2048 tokens per GPU, tp2 / tp4 / tp8): which fused
+    kernels the step consists of, checked on fake CUDA tensors."""
+    from tests.dist_utils import run_distributed
+    if ops.load_ext() is None:
+        pytest.skip("extension not built")
+    run_distributed(_bench_shape_rank, 1, tp, micro)
+
