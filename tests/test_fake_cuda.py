@@ -338,3 +338,43 @@ def test_benchmark_shapes_take_the_fused_paths(tp, micro):
         pytest.skip("extension not built")
     run_distributed(_bench_shape_rank, 1, tp, micro)
 
+
+def _neo_shape_rank(rank, world, as_rank):
+    """Two GPT-Neo-1.3B-wide blocks (one global, one local) at 4 x 2048 tokens per micro-batch on rank ``as_rank`` of 2:
+    the shapes of the tp2 x pp2 x dp2 configuration, with its 50257-word vocabulary split 25129 / 25128."""
+    from collections import Counter
+    from oslo_b200.modeling_utils import no_weight_init
+    from oslo_b200.parallel import fused_tp
+    _fake_group(2, as_rank)
+    calls = Counter()
+    real_call = fused_tp.FusedTP._call
+
+    def spy(self, a, b, a_mn, b_mn, bias, aux_out, out, flags, M, N, K, mode, aux=None):
+        calls[(mode, M, N, K)] += 1
+        return real_call(self, a, b, a_mn, b_mn, bias, aux_out, out, flags, M, N, K, mode, aux)
+
+    fused_tp.FusedTP._call = spy
+    cfg = ob.GPTNeoConfig(vocab_size=50257, max_position_embeddings=2048, hidden_size=2048, num_layers=2, num_heads=16,
+                          window_size=256, attention_types=[[["global", "local"], 1]], torch_dtype=torch.bfloat16)
+    with no_weight_init():
+        model = ob.GPTNeoForCausalLM(cfg).to(torch.bfloat16)
+    model = ob.parallelize(model, tensor_parallel_size=2)
+    model.fuse().train()
+    model.mpu.backend, model.mpu.device = "nccl", torch.device("cuda")
+    assert model.transformer.wte.weight.size(0) == (25129 if as_rank == 0 else 25128)
+    with FakeTensorMode():
+        ids = torch.randint(0, 50257, (4, 2048), device="cuda")
+        out = torch.func.functional_call(model, _fake_parameters(model), (), dict(input_ids=ids, labels=ids, output_logits=False))
+        ran = Counter(run_custom_backwards(out.loss.grad_fn))
+    # per block: out_proj and c_proj forward, q / k / v / c_fc input gradients backward, each a GEMM + all-reduce
+    assert calls == {(1, 8192, 2048, 1024): 8, (1, 8192, 2048, 4096): 4}, dict(calls)
+    assert ran["_VocabEmbed"] == 1 and ran["_Flash"] == 2 and ran["_LinearCrossEntropy"] == 1, dict(ran)
+
+
+@pytest.mark.parametrize("as_rank", [0, 1])
+def test_gpt_neo_1_3b_shapes_on_both_ranks_of_an_uneven_vocabulary_split(as_rank):
+    from tests.dist_utils import run_distributed
+    if ops.load_ext() is None:
+        pytest.skip("extension not built")
+    run_distributed(_neo_shape_rank, 1, as_rank)
+
