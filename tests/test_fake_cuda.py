@@ -339,21 +339,52 @@ def test_benchmark_shapes_take_the_fused_paths(tp, micro):
     run_distributed(_bench_shape_rank, 1, tp, micro)
 
 
-def _neo_shape_rank(rank, world, as_rank):
+def _record_collectives(trace):
+    """Append (name, shape, group size) of every collective this process issues - torch.distributed calls and this
+    package's collective operators - to ``trace``."""
+    import torch.distributed as dist
+    from oslo_b200.parallel import fused_tp, symmetric
+
+    def wrap_dist(name):
+        real = getattr(dist, name)
+
+        def spy(tensor, *a, **k):
+            t = tensor[0] if isinstance(tensor, (list, tuple)) else tensor
+            trace.append((name, tuple(t.shape), dist.get_world_size(k.get("group"))))
+            return real(tensor, *a, **k)
+        setattr(dist, name, spy)
+
+    for name in ("all_reduce", "broadcast", "all_gather_into_tensor", "reduce_scatter_tensor", "all_gather"):
+        wrap_dist(name)
+    real_call = fused_tp.FusedTP._call
+
+    def fused(self, a, b, a_mn, b_mn, bias, aux_out, out, flags, M, N, K, mode, aux=None):
+        trace.append(("gemm_comm", (mode, M, N, K), self.world))
+        return real_call(self, a, b, a_mn, b_mn, bias, aux_out, out, flags, M, N, K, mode, aux)
+    fused_tp.FusedTP._call = fused
+    real_combine = symmetric.CeCombine.__call__
+
+    def combine(self, mx, se, tg):
+        trace.append(("ce_combine", tuple(mx.shape), self.world))
+        return real_combine(self, mx, se, tg)
+    symmetric.CeCombine.__call__ = combine
+    real_embed = symmetric.vocab_embed
+
+    def embed(ws, ids, weight, lo, hi):
+        trace.append(("vocab_embed", tuple(ids.shape), ws.world))
+        return real_embed(ws, ids, weight, lo, hi)
+    symmetric.vocab_embed = embed
+
+
+def _neo_shape_rank(rank, world, as_rank, out_dir=None):
     """Two GPT-Neo-1.3B-wide blocks (one global, one local) at 4 x 2048 tokens per micro-batch on rank ``as_rank`` of 2:
     the shapes of the tp2 x pp2 x dp2 configuration, with its 50257-word vocabulary split 25129 / 25128."""
     from collections import Counter
     from oslo_b200.modeling_utils import no_weight_init
     from oslo_b200.parallel import fused_tp
     _fake_group(2, as_rank)
-    calls = Counter()
-    real_call = fused_tp.FusedTP._call
-
-    def spy(self, a, b, a_mn, b_mn, bias, aux_out, out, flags, M, N, K, mode, aux=None):
-        calls[(mode, M, N, K)] += 1
-        return real_call(self, a, b, a_mn, b_mn, bias, aux_out, out, flags, M, N, K, mode, aux)
-
-    fused_tp.FusedTP._call = spy
+    trace = []
+    _record_collectives(trace)
     cfg = ob.GPTNeoConfig(vocab_size=50257, max_position_embeddings=2048, hidden_size=2048, num_layers=2, num_heads=16,
                           window_size=256, attention_types=[[["global", "local"], 1]], torch_dtype=torch.bfloat16)
     with no_weight_init():
@@ -367,14 +398,65 @@ def _neo_shape_rank(rank, world, as_rank):
         out = torch.func.functional_call(model, _fake_parameters(model), (), dict(input_ids=ids, labels=ids, output_logits=False))
         ran = Counter(run_custom_backwards(out.loss.grad_fn))
     # per block: out_proj and c_proj forward, q / k / v / c_fc input gradients backward, each a GEMM + all-reduce
+    calls = Counter(shape for name, shape, _ in trace if name == "gemm_comm")
     assert calls == {(1, 8192, 2048, 1024): 8, (1, 8192, 2048, 4096): 4}, dict(calls)
     assert ran["_VocabEmbed"] == 1 and ran["_Flash"] == 2 and ran["_LinearCrossEntropy"] == 1, dict(ran)
+    if out_dir:
+        import json
+        import os
+        with open(os.path.join(out_dir, f"trace{as_rank}.json"), "w") as f:
+            json.dump(trace, f)
 
 
-@pytest.mark.parametrize("as_rank", [0, 1])
-def test_gpt_neo_1_3b_shapes_on_both_ranks_of_an_uneven_vocabulary_split(as_rank):
+def test_gpt_neo_1_3b_shapes_issue_the_same_collectives_on_both_ranks_of_an_uneven_vocabulary_split(tmp_path):
+    """A rank that takes another route than its tensor-parallel peer (which the 25129 / 25128 split of GPT-Neo's
+    vocabulary once caused in the loss) issues another sequence of collectives and the job hangs: the sequences of
+    the two ranks - names, shapes, group sizes, in order - are compared."""
+    import json
     from tests.dist_utils import run_distributed
     if ops.load_ext() is None:
         pytest.skip("extension not built")
-    run_distributed(_neo_shape_rank, 1, as_rank)
+    for r in (0, 1):
+        run_distributed(_neo_shape_rank, 1, r, str(tmp_path))
+    a, b = (json.load(open(tmp_path / f"trace{r}.json")) for r in (0, 1))
+    assert len(a) > 15 and a == b, [(x, y) for x, y in zip(a, b) if x != y][:5]
+
+
+def _trace_rank(rank, world, kind, tp, vocab, seq_par, as_rank, out_dir):
+    import json
+    import os
+    _fake_group(tp, as_rank)
+    trace = []
+    _record_collectives(trace)
+    cls, cfg = _model(kind, vocab)
+    cfg.torch_dtype = torch.bfloat16
+    model = ob.parallelize(cls(cfg).to(torch.bfloat16), tensor_parallel_size=tp, sequence_parallel=seq_par)
+    model.fuse().train()
+    model.mpu.backend, model.mpu.device = "nccl", torch.device("cuda")
+    with FakeTensorMode():
+        ids = torch.randint(0, vocab, (2, 256), device="cuda")
+        for out_logits in (False, True):
+            out = torch.func.functional_call(model, _fake_parameters(model), (),
+                                             dict(input_ids=ids, labels=ids, output_logits=out_logits))
+            run_custom_backwards(out.loss.grad_fn)
+    with open(os.path.join(out_dir, f"trace{as_rank}.json"), "w") as f:
+        json.dump(trace, f)
+
+
+@pytest.mark.parametrize("kind,tp,vocab,seq_par", [("gptj", 2, 1021, False), ("gpt2", 4, 1021, False), ("gpt_neo", 4, 1030, True),
+                                                   ("gptj", 8, 1000, False)])
+def test_all_tensor_parallel_ranks_issue_the_same_collectives(tmp_path, kind, tp, vocab, seq_par):
+    """Vocabulary sizes that do not divide evenly (1021 over 2 or 4 ranks) or leave shards with unaligned row counts
+    (1000 over 8: 125 rows): every rank of the group issues the same collectives in the same order, for the fused loss
+    and for materialised logits."""
+    import json
+    from tests.dist_utils import run_distributed
+    if ops.load_ext() is None:
+        pytest.skip("extension not built")
+    for r in range(tp):
+        run_distributed(_trace_rank, 1, kind, tp, vocab, seq_par, r, str(tmp_path))
+    traces = [json.load(open(tmp_path / f"trace{r}.json")) for r in range(tp)]
+    assert len(traces[0]) > 10
+    for r in range(1, tp):
+        assert traces[r] == traces[0], (r, [(x, y) for x, y in zip(traces[0], traces[r]) if x != y][:5])
 
