@@ -1119,3 +1119,53 @@ def test_pipeline_partition_is_validated():
     for bad in ([4], [1, 2], [0, 4], [2, 2, 0]):
         with pytest.raises(ValueError):
             PipelineParallelEngine(_M(), _Mpu(), partition=bad)._bounds()
+
+
+def _bench_layout_in_miniature(rank, world, steps, expected_losses, tmpdir):
+    """tp2 x pp4 on 8 ranks with the balanced split of 8 blocks (2-2-3-1), 4 micro-batches per step, the fused loss,
+    ``FusedAdamW`` with global-norm clipping over the model-parallel group: the 8-GPU benchmark layout, small."""
+    from oslo_b200.optim import FusedAdamW
+    from oslo_b200.parallel.engine_pipeline import balanced_partition
+    torch.manual_seed(7)
+    cfg = ob.GPTJConfig(vocab_size=104, n_positions=32, n_embd=32, n_layer=8, n_head=4, rotary_dim=4)
+    partition = balanced_partition(8, 4)
+    assert partition == [2, 2, 3, 1]
+    model = ob.parallelize(ob.GPTJForCausalLM(cfg).train(), tensor_parallel_size=2, pipeline_parallel_size=4,
+                           micro_batch_size=2, pipeline_partition=partition)
+    mpu = model.mpu
+    opt = FusedAdamW(model.gpu_parameters(), lr=1e-2, weight_decay=0.01, max_grad_norm=0.5,
+                     model_parallel_group=mpu.get_model_parallel_group())
+    for s in range(steps):
+        b = batch(seed=3 + s, bsz=8, vocab=104)
+        opt.zero_grad()
+        tot = 0.0
+        for out in model(**b, output_logits=False):
+            (out.loss / 4).backward()
+            tot += float(out.loss.detach()) / 4
+        assert abs(tot - expected_losses[s]) < 3e-4, (s, tot, expected_losses[s])
+        opt.step()
+    model.save_pretrained_with_parallel(os.path.join(tmpdir, "merged"), save_with_merging=True)
+
+
+def test_the_eight_gpu_benchmark_layout_in_miniature():
+    steps = 2
+    torch.manual_seed(7)
+    cfg = ob.GPTJConfig(vocab_size=104, n_positions=32, n_embd=32, n_layer=8, n_head=4, rotary_dim=4)
+    ref = ob.GPTJForCausalLM(cfg).train()
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.01)
+    losses = []
+    for s in range(steps):
+        b = batch(seed=3 + s, bsz=8, vocab=104)
+        opt.zero_grad()
+        loss = ref(**b).loss
+        loss.backward()
+        torch.nn.utils.clip_grad_norm_(ref.parameters(), 0.5)
+        opt.step()
+        losses.append(float(loss.detach()))
+    with tempfile.TemporaryDirectory() as d:
+        run_distributed(_bench_layout_in_miniature, 8, steps, losses, d)
+        got = torch.load(os.path.join(d, "merged", "pytorch_model.bin"), weights_only=True)
+    for k, v in ref.state_dict().items():
+        if k in got:
+            assert torch.allclose(got[k], v, atol=3e-4), (k, float((got[k] - v).abs().max()))
+
