@@ -793,12 +793,13 @@ def test_pipeline_with_bucketed_ddp_and_zero1_matches_single_process(kind):
             assert torch.allclose(got[k], v, atol=2e-4), (k, (got[k] - v).abs().max())
 
 
-def _train_wrapper_layout(rank, world, kind, tp, pp, steps, tmpdir, seq_par):
+def _train_wrapper_layout(rank, world, kind, tp, pp, steps, tmpdir, seq_par, balanced=False):
     """Any tp x pp layout with data-parallel replicas over the remaining ranks: bucketed wrapper, ZeRO-1, clipping."""
     from oslo_b200.optim import FusedAdamW
     from oslo_b200.parallel.data_parallel import DistributedDataParallel
+    from oslo_b200.parallel.engine_pipeline import balanced_partition
     model = ob.parallelize(build(kind).train(), tensor_parallel_size=tp, pipeline_parallel_size=pp, micro_batch_size=1,
-                           sequence_parallel=seq_par)
+                           sequence_parallel=seq_par, pipeline_partition=balanced_partition(4, pp) if balanced else None)
     mpu = model.mpu
     opt = FusedAdamW(model.gpu_parameters(), lr=1e-2, weight_decay=0.01, max_grad_norm=0.5, model=model,
                      shard_group=mpu.get_data_parallel_group(), model_parallel_group=mpu.get_model_parallel_group())
@@ -810,7 +811,7 @@ def _train_wrapper_layout(rank, world, kind, tp, pp, steps, tmpdir, seq_par):
         mine = {k: v[dpr * n:(dpr + 1) * n] for k, v in b.items()}
         opt.zero_grad()
         if pp > 1:
-            for out in ddp(**mine):
+            for out in ddp(**mine, output_logits=not balanced):
                 (out.loss / n).backward()
         else:
             ddp(**mine).loss.backward()
@@ -818,9 +819,11 @@ def _train_wrapper_layout(rank, world, kind, tp, pp, steps, tmpdir, seq_par):
     model.save_pretrained_with_parallel(os.path.join(tmpdir, "merged"), save_with_merging=True)
 
 
-@pytest.mark.parametrize("kind,tp,pp,world,seq_par", [("gptj", 2, 1, 4, False), ("gpt2", 2, 1, 4, True),
-                                                       ("gptj", 2, 2, 8, False), ("gpt2", 2, 2, 8, False)])
-def test_wrapper_zero1_and_clipping_under_tensor_and_pipeline_parallel_replicas(kind, tp, pp, world, seq_par):
+@pytest.mark.parametrize("kind,tp,pp,world,seq_par,balanced", [
+    ("gptj", 2, 1, 4, False, False), ("gpt2", 2, 1, 4, True, False), ("gptj", 2, 2, 8, False, False),
+    ("gpt2", 2, 2, 8, False, False),
+    ("gpt_neo", 2, 2, 8, False, True)])     # the GPT-Neo benchmark layout: uneven vocabulary, 3 + 1 blocks, fused loss
+def test_wrapper_zero1_and_clipping_under_tensor_and_pipeline_parallel_replicas(kind, tp, pp, world, seq_par, balanced):
     """Tensor (and pipeline) parallel replicas x 2 data-parallel replicas with this package's wrapper, ZeRO-1 and
     global-norm clipping: merged weights equal one process training on the whole batch with ``clip_grad_norm_``."""
     steps = 2
@@ -833,7 +836,7 @@ def test_wrapper_zero1_and_clipping_under_tensor_and_pipeline_parallel_replicas(
         torch.nn.utils.clip_grad_norm_(ref.parameters(), 0.5)
         opt.step()
     with tempfile.TemporaryDirectory() as d:
-        run_distributed(_train_wrapper_layout, world, kind, tp, pp, steps, d, seq_par)
+        run_distributed(_train_wrapper_layout, world, kind, tp, pp, steps, d, seq_par, balanced)
         got = torch.load(os.path.join(d, "merged", "pytorch_model.bin"), weights_only=True)
     for k, v in ref.state_dict().items():
         if k in got:
