@@ -162,7 +162,8 @@ def test_3d_parallel_training_gpt_neo():
 
 
 @pytest.mark.parametrize("kind,tp,pp,fuse", [("gpt_neo", 1, 2, True), ("gpt2", 2, 2, True), ("gptj", 2, 2, True),
-                                             ("gpt2", 2, 2, False), ("gptj", 2, 2, False), ("gpt_neo", 2, 2, True)])
+                                             ("gpt2", 2, 2, False), ("gptj", 2, 2, False), ("gpt_neo", 2, 2, True),
+                                             ("gptj", 4, 1, True), ("gpt2", 4, 1, False), ("gpt_neo", 4, 2, True)])
 def test_training_matrix_over_families_and_layouts(kind, tp, pp, fuse):
     """The remaining cells of the reference's {tp, pp, 3d} x {training, training_with_fusion} matrix for the three
     families: losses of every step and the merged weights equal the single-process oracle."""
